@@ -1,0 +1,735 @@
+// TEST INFRASTRUCTURE -- NOT PART OF THE PRODUCT PATH.
+//
+// CPU restatement of the ParallelReverseAutoDiff (RMAD / PRADLite) backward hot path.
+// It is the checker the CUDA library is compared with, and the timed CPU baseline.
+// Only the test-suite, the smoke entry and the benchmark's CPU-baseline / reference
+// arm may load it.  The CUDA library never links, loads or calls anything here.
+//
+// Parity status: the reference is C# and cannot be executed where this file is
+// built (no .NET runtime), so this restatement is pinned only by the few
+// known-answer / relational tests the reference itself holds for this path
+// (exact gather/scatter vectors, the LayerNorm dual-number relation at 1e-9, the
+// GPU==CPU matmul relation at 1e-10).  Activations, softmax, losses, clip and Adam
+// are PARITY UNPINNED: they follow the cited source lines, nothing more.
+//
+// Restatement rules (they decide bits):
+//  * every function is instantiated for double (PRAD/RMAD) and float (PRADLite);
+//    float expressions round to float after every operation, as RyuJIT's SSE code
+//    does; the build uses -ffp-contract=off so no FMA is formed;
+//  * dot products accumulate sequentially in storage precision into the output
+//    element (`Output[i][j] += a*b`);
+//  * PradMath float overloads compute in double and cast: (float)Math.Exp(x);
+//  * Math.Pow(x, 2) stays a pow() call;
+//  * System.Linq Sum()/Average() over float sequences accumulate in double and
+//    cast the result to float (BCL behaviour; the BCL source is not available
+//    where this is built, so this detail is an assumption stated in the docs);
+//  * Math.Min(a, b) returns NaN if either argument is NaN (unlike fmin).
+//
+// OpenMP parallelises exactly the index the C# code hands to Parallel.For, so the
+// per-element summation order is unchanged.
+//
+// Citations are paths inside the reference project.
+
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <limits>
+#include <vector>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+namespace {
+
+// ---- scalar helpers: src/PRAD/PradMath.cs:122-239, src/PRAD/PradTools.cs:20-75 -----------
+template <typename T> struct Consts;
+template <> struct Consts<double> {
+  static constexpr double eps15 = 1e-15;   // PradTools.Epsilon
+  static constexpr double eps9 = 1e-9;     // LayerNormalizationOperation.cs:17
+  static double pi() { return M_PI; }      // Math.PI
+};
+template <> struct Consts<float> {
+  static constexpr float eps15 = 1e-15f;   // lite PradTools.Epsilon
+  static constexpr float eps9 = 1e-9f;     // lite LayerNormalizationOperation EPSILON
+  static float pi() { return (float)M_PI; }  // PradMath.PI = (float)Math.PI
+};
+
+template <typename T> inline T p_exp(T x) { return (T)std::exp((double)x); }
+template <typename T> inline T p_tanh(T x) { return (T)std::tanh((double)x); }
+template <typename T> inline T p_sqrt(T x) { return (T)std::sqrt((double)x); }
+template <typename T> inline T p_log(T x) { return (T)std::log((double)x); }
+template <typename T> inline T p_pow(T x, T y) { return (T)std::pow((double)x, (double)y); }
+
+// Math.Min / Math.Abs semantics of .NET (NaN propagates through Min).
+template <typename T> inline T net_min(T a, T b) {
+  if (std::isnan(a) || std::isnan(b)) return std::numeric_limits<T>::quiet_NaN();
+  return a < b ? a : b;
+}
+
+// LINQ Sum over a sequence of T: double accumulator, result cast to T.
+template <typename T> struct LinqSum {
+  double acc = 0.0;
+  inline void add(T v) { acc += (double)v; }
+  inline T result() const { return (T)acc; }
+};
+
+// ---- MatrixMultiplyOperation.cs:50-80 (Forward), :83-126 (Backward) ----------------------
+template <typename T>
+void matmul_forward(const T* A, const T* B, T* C, int M, int K, int N) {
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < M; ++i) {
+    for (int j = 0; j < N; ++j) {
+      T acc = 0;
+      for (int k = 0; k < K; ++k) {
+        T p = A[(size_t)i * K + k] * B[(size_t)k * N + j];
+        acc = acc + p;
+      }
+      C[(size_t)i * N + j] = acc;
+    }
+  }
+}
+
+template <typename T>
+void matmul_backward(const T* A, const T* B, const T* dC, T* dA, T* dB, int M, int K, int N) {
+  if (dA) {
+#pragma omp parallel for schedule(static)
+    for (int i = 0; i < M; ++i) {
+      for (int j = 0; j < K; ++j) {
+        T acc = 0;
+        for (int k = 0; k < N; ++k) {
+          T p = dC[(size_t)i * N + k] * B[(size_t)j * N + k];
+          acc = acc + p;
+        }
+        dA[(size_t)i * K + j] = acc;
+      }
+    }
+  }
+  if (dB) {
+#pragma omp parallel for schedule(static)
+    for (int i = 0; i < K; ++i) {
+      for (int j = 0; j < N; ++j) {
+        T acc = 0;
+        for (int k = 0; k < M; ++k) {
+          T p = A[(size_t)k * K + i] * dC[(size_t)k * N + j];
+          acc = acc + p;
+        }
+        dB[(size_t)i * N + j] = acc;
+      }
+    }
+  }
+}
+
+// ---- BatchMatrixMultiplyOperation.cs:51-94: one MatrixMultiplyOperation per depth slice ---
+// strideB == 0 is the (DeepMatrix, Matrix) overload: every slice multiplies the same B
+// and each slice returns its own dB (the visitor combines them afterwards).
+template <typename T>
+void batch_matmul_forward(const T* A, const T* B, T* C, int depth, int M, int K, int N,
+                          int b_shared) {
+  for (int d = 0; d < depth; ++d)
+    matmul_forward<T>(A + (size_t)d * M * K, B + (b_shared ? 0 : (size_t)d * K * N),
+                      C + (size_t)d * M * N, M, K, N);
+}
+template <typename T>
+void batch_matmul_backward(const T* A, const T* B, const T* dC, T* dA, T* dB, int depth, int M,
+                           int K, int N, int b_shared) {
+  for (int d = 0; d < depth; ++d)
+    matmul_backward<T>(A + (size_t)d * M * K, B + (b_shared ? 0 : (size_t)d * K * N),
+                       dC + (size_t)d * M * N, dA + (size_t)d * M * K, dB + (size_t)d * K * N, M,
+                       K, N);
+}
+
+// ---- MatrixMultiplyAndSumOperation.cs:50-89 / GpuMatrixMultiplyAndSumOperation.cs:114-154 ---
+// forward: out[q] = sum_ij (A * B_q)_ij ; `a * slice` is Matrix.operator* (Matrix.cs:297-330,
+// local `sum` accumulator), Matrix.Sum() adds row by row.
+template <typename T>
+void matmul_and_sum_forward(const T* A, const T* B, T* out, int R, int Cc, int N, int P) {
+  std::vector<T> tmp((size_t)R * N);
+  for (int q = 0; q < P; ++q) {
+    matmul_forward<T>(A, B + (size_t)q * Cc * N, tmp.data(), R, Cc, N);
+    LinqSum<T> s;  // Matrix.Sum() (Matrix.cs:588-606): per-row T accumulator, rowSums.Sum()
+    for (int i = 0; i < R; ++i) {
+      T rs = 0;
+      for (int j = 0; j < N; ++j) rs = rs + tmp[(size_t)i * N + j];
+      s.add(rs);
+    }
+    out[q] = s.result();
+  }
+}
+// backward: dB_q = A^T * dOut[q] ; dA = sum_q B_q^T * dOut[q]   (scalar products, no GEMM).
+// As in the reference the shapes only agree for square slices (R == Cc == N).
+template <typename T>
+void matmul_and_sum_backward(const T* A, const T* B, const T* dOut, T* dA, T* dB, int R, int Cc,
+                             int N, int P) {
+  for (size_t i = 0; i < (size_t)R * Cc; ++i) dA[i] = 0;
+  for (int q = 0; q < P; ++q) {
+    T s = dOut[q];
+    for (int i = 0; i < Cc; ++i)
+      for (int j = 0; j < R; ++j) dB[(size_t)q * Cc * R + (size_t)i * R + j] = A[(size_t)j * Cc + i] * s;
+    const T* Bq = B + (size_t)q * Cc * N;
+    for (int i = 0; i < N; ++i)
+      for (int j = 0; j < Cc; ++j) {
+        T t = Bq[(size_t)j * N + i] * s;
+        dA[(size_t)i * Cc + j] = dA[(size_t)i * Cc + j] + t;
+      }
+  }
+}
+
+// ---- LeakyReLUOperation.cs:54-93 ---------------------------------------------------------
+template <typename T>
+void leaky_relu_forward(const T* x, T* y, size_t n, T alpha) {
+  for (size_t i = 0; i < n; ++i) y[i] = x[i] > 0 ? x[i] : alpha * x[i];
+}
+template <typename T>
+void leaky_relu_backward(const T* x, const T* dy, T* dx, size_t n, T alpha) {
+#pragma omp parallel for schedule(static)
+  for (long long i = 0; i < (long long)n; ++i) {
+    T g = x[i] > 0 ? (T)1 : alpha;
+    dx[i] = dy[i] * g;
+  }
+}
+
+// ---- SigmoidOperation.cs:46-84 (backward uses the stored OUTPUT) --------------------------
+template <typename T>
+void sigmoid_forward(const T* x, T* y, size_t n) {
+  for (size_t i = 0; i < n; ++i) y[i] = (T)1 / ((T)1 + p_exp<T>(-x[i]));
+}
+template <typename T>
+void sigmoid_backward(const T* y, const T* dy, T* dx, size_t n) {
+  for (size_t i = 0; i < n; ++i) {
+    T d = y[i] * ((T)1 - y[i]);
+    dx[i] = dy[i] * d;
+  }
+}
+
+// ---- TanhOperation.cs:42-78 ---------------------------------------------------------------
+template <typename T>
+void tanh_forward(const T* x, T* y, size_t n) {
+  for (size_t i = 0; i < n; ++i) y[i] = p_tanh<T>(x[i]);
+}
+template <typename T>
+void tanh_backward(const T* y, const T* dy, T* dx, size_t n) {
+  for (size_t i = 0; i < n; ++i) {
+    T d = (T)1 - p_pow<T>(y[i], (T)2);
+    dx[i] = dy[i] * d;
+  }
+}
+
+// ---- GELUOperation.cs:44-101 ; lite/.../Lite/GELUOperation.cs (float constants) -----------
+// The derivative is reproduced as written: c = (1-b^2)^2 and the extra 0.5*x*b term.
+inline double gelu_fwd(double x) {
+  double a = 0.5 * (1.0 + std::tanh(std::sqrt(2 / M_PI) * (x + (0.044715 * std::pow(x, 3)))));
+  return a * x;
+}
+inline double gelu_der(double x) {
+  double b = std::tanh(std::sqrt(2 / M_PI) * (x + (0.044715 * std::pow(x, 3))));
+  double c = std::pow(1 - std::pow(b, 2), 2);
+  double d = std::sqrt(2 / M_PI) * ((0.044715 * 3 * std::pow(x, 2)) + 1);
+  return (0.5 * x * ((c * d) + b)) + (0.5 * (1 + b));
+}
+inline float gelu_fwd(float x) {
+  const float pi = Consts<float>::pi();
+  float inner = p_sqrt<float>(2 / pi) * (x + (0.044715f * p_pow<float>(x, 3.0f)));
+  float a = 0.5f * (1.0f + p_tanh<float>(inner));
+  return a * x;
+}
+inline float gelu_der(float x) {
+  const float pi = Consts<float>::pi();
+  float b = p_tanh<float>(p_sqrt<float>(2 / pi) * (x + (0.044715f * p_pow<float>(x, 3.0f))));
+  float c = p_pow<float>(1 - p_pow<float>(b, 2.0f), 2.0f);
+  float k3 = 0.044715f * 3;
+  float d = p_sqrt<float>(2.0f / pi) * ((k3 * p_pow<float>(x, 2.0f)) + 1);
+  float t0 = 0.5f * x;
+  float t1 = (c * d) + b;
+  float t2 = 0.5f * (1 + b);
+  return (t0 * t1) + t2;
+}
+template <typename T>
+void gelu_forward(const T* x, T* y, size_t n) {
+  for (size_t i = 0; i < n; ++i) y[i] = gelu_fwd(x[i]);
+}
+template <typename T>
+void gelu_backward(const T* x, const T* dy, T* dx, size_t n) {
+#pragma omp parallel for schedule(static)
+  for (long long i = 0; i < (long long)n; ++i) dx[i] = dy[i] * gelu_der(x[i]);
+}
+
+// ---- HadamardProductOperation.cs:50-118 ---------------------------------------------------
+template <typename T>
+void hadamard_forward(const T* a, const T* b, T* y, size_t n) {
+  for (size_t i = 0; i < n; ++i) y[i] = a[i] * b[i];
+}
+template <typename T>
+void hadamard_backward(const T* a, const T* b, const T* dy, T* da, T* db, size_t n) {
+  for (size_t i = 0; i < n; ++i) {
+    da[i] = dy[i] * b[i];
+    db[i] = dy[i] * a[i];
+  }
+}
+
+// ---- MatrixAddOperation.cs:29-68 ; MatrixAddThreeOperation.cs:30-67 -----------------------
+template <typename T>
+void add_forward(const T* a, const T* b, T* y, size_t n) {
+  for (size_t i = 0; i < n; ++i) y[i] = a[i] + b[i];
+}
+template <typename T>
+void add3_forward(const T* a, const T* b, const T* c, T* y, size_t n) {
+  for (size_t i = 0; i < n; ++i) y[i] = (a[i] + b[i]) + c[i];
+}
+// every input gradient is a copy of dOut
+template <typename T>
+void add_backward(const T* dy, T* d0, T* d1, T* d2, size_t n) {
+  for (size_t i = 0; i < n; ++i) {
+    if (d0) d0[i] = dy[i];
+    if (d1) d1[i] = dy[i];
+    if (d2) d2[i] = dy[i];
+  }
+}
+
+// ---- MatrixAddBroadcastingOperation.cs:32-69 + Matrix.Column (Matrix.cs:785-794) ----------
+template <typename T>
+void add_broadcast_forward(const T* x, const T* bias, T* y, int R, int C) {
+  for (int i = 0; i < R; ++i)
+    for (int j = 0; j < C; ++j) y[(size_t)i * C + j] = x[(size_t)i * C + j] + bias[j];
+}
+// dBias[j] = Column(j).Sum() (LINQ: double accumulator) ; the input gradient is dOut itself.
+template <typename T>
+void add_broadcast_backward(const T* dy, T* dbias, int R, int C) {
+#pragma omp parallel for schedule(static)
+  for (int j = 0; j < C; ++j) {
+    LinqSum<T> s;
+    for (int i = 0; i < R; ++i) s.add(dy[(size_t)i * C + j]);
+    dbias[j] = (T)0 + s.result();
+  }
+}
+
+// ---- SoftmaxOperation.cs:45-109 -----------------------------------------------------------
+template <typename T>
+void softmax_forward(const T* x, T* y, int R, int C) {
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < R; ++i) {
+    const T* xr = x + (size_t)i * C;
+    T* yr = y + (size_t)i * C;
+    T mx = xr[0];
+    for (int j = 1; j < C; ++j)
+      if (xr[j] > mx) mx = xr[j];
+    T sum = 0;
+    for (int j = 0; j < C; ++j) {
+      T e = p_exp<T>(xr[j] - mx);
+      sum = sum + e;
+      yr[j] = e;
+    }
+    for (int j = 0; j < C; ++j) yr[j] = yr[j] / sum;
+  }
+}
+// explicit Jacobian product accumulated in k order (SoftmaxOperation.cs:53-83)
+template <typename T>
+void softmax_backward(const T* y, const T* dy, T* dx, int R, int C) {
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < R; ++i) {
+    const T* yr = y + (size_t)i * C;
+    const T* dr = dy + (size_t)i * C;
+    for (int j = 0; j < C; ++j) {
+      T sum = 0;
+      for (int k = 0; k < C; ++k) {
+        if (j == k) {
+          T t = dr[k] * yr[j];
+          T u = (T)1 - yr[j];
+          sum = sum + t * u;
+        } else {
+          T t = dr[k] * yr[j];
+          sum = sum - t * yr[k];
+        }
+      }
+      dx[(size_t)i * C + j] = sum;
+    }
+  }
+}
+
+// ---- LayerNormalizationOperation.cs:56-112 (+ lite twin) ----------------------------------
+// population sigma, eps added to sigma; backward = diagonal term only.
+template <typename T>
+void layernorm_stats(const T* x, T* mean, T* stdv, int R, int C) {
+  for (int i = 0; i < R; ++i) {
+    const T* xr = x + (size_t)i * C;
+    LinqSum<T> s;  // Average(): double sum / count, cast to T
+    for (int j = 0; j < C; ++j) s.add(xr[j]);
+    mean[i] = (T)(s.acc / (double)C);
+    LinqSum<T> v;
+    for (int j = 0; j < C; ++j) v.add(p_pow<T>(xr[j] - mean[i], (T)2));
+    stdv[i] = p_sqrt<T>(v.result() / (T)C);
+  }
+}
+template <typename T>
+void layernorm_forward(const T* x, T* y, T* mean, T* stdv, int R, int C) {
+  layernorm_stats<T>(x, mean, stdv, R, C);
+  const T eps = Consts<T>::eps9;
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < R; ++i)
+    for (int j = 0; j < C; ++j)
+      y[(size_t)i * C + j] = (x[(size_t)i * C + j] - mean[i]) / (stdv[i] + eps);
+}
+template <typename T>
+void layernorm_backward(const T* x, const T* mean, const T* stdv, const T* dy, T* dx, int R,
+                        int C) {
+  const T eps = Consts<T>::eps9;
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < R; ++i) {
+    T inv = (T)1 / (stdv[i] + eps);
+    T exp1 = ((T)1 - ((T)1 / (T)C)) * inv;
+    for (int j = 0; j < C; ++j) {
+      T num = p_pow<T>(x[(size_t)i * C + j] - mean[i], (T)2);
+      T den = (T)C * p_pow<T>(stdv[i] + eps, (T)3);
+      T exp2 = num / den;
+      T exp3 = exp1 - exp2;
+      dx[(size_t)i * C + j] = dy[(size_t)i * C + j] * exp3;
+    }
+  }
+}
+
+// ---- MatrixTransposeOperation.cs:28-64 ; MatrixMultiplyScalarOperation.cs:48-88 -----------
+template <typename T>
+void transpose(const T* x, T* y, int R, int C) {  // y is C x R
+  for (int i = 0; i < C; ++i)
+    for (int j = 0; j < R; ++j) y[(size_t)i * R + j] = x[(size_t)j * C + i];
+}
+template <typename T>
+void scale(const T* x, T* y, size_t n, T s) {
+  for (size_t i = 0; i < n; ++i) y[i] = x[i] * s;
+}
+
+// ---- Loss/MeanSquaredErrorLossOperation.cs:37-84 ------------------------------------------
+template <typename T>
+T mse_forward(const T* out, const T* target, int R, int C) {
+  LinqSum<T> s;
+  for (size_t i = 0; i < (size_t)R * C; ++i) {
+    T diff = out[i] - target[i];
+    s.add(diff * diff);
+  }
+  return s.result() / (T)(R * C);
+}
+// rows_total lets a row shard use the whole batch's normaliser (rows_total == R normally).
+template <typename T>
+void mse_backward(const T* out, const T* target, T* grad, int R, int C, long long rows_total) {
+  T sc = (T)2 / (T)(rows_total * C);
+#pragma omp parallel for schedule(static)
+  for (long long i = 0; i < (long long)R * C; ++i) grad[i] = sc * (out[i] - target[i]);
+}
+
+// ---- Loss/CategoricalCrossEntropyLossOperation.cs:37-87 -----------------------------------
+template <typename T>
+T cce_forward(const T* out, const T* target, int R, int C) {
+  LinqSum<T> s;
+  const T eps = Consts<T>::eps15;
+  for (size_t i = 0; i < (size_t)R * C; ++i) {
+    T y = target[i];
+    s.add(-y * p_log<T>(out[i] + eps));
+  }
+  return s.result() / (T)R;
+}
+template <typename T>
+void cce_backward(const T* out, const T* target, T* grad, int R, int C, long long rows_total) {
+  const T eps = Consts<T>::eps15;
+  T sc = (T)1 / (T)rows_total;
+  for (size_t i = 0; i < (size_t)R * C; ++i) {
+    T t = -sc * target[i];
+    grad[i] = t / (out[i] + eps);
+  }
+}
+
+// ---- EmbeddingOperation.cs:49-86: row gather, sequential scatter-add in input-row order ---
+template <typename T>
+void embedding_forward(const T* index_col, const T* W, T* out, int n, int D) {
+  for (int i = 0; i < n; ++i) {
+    int idx = (int)index_col[i];
+    std::memcpy(out + (size_t)i * D, W + (size_t)idx * D, sizeof(T) * D);
+  }
+}
+template <typename T>
+void embedding_backward(const T* index_col, const T* dOut, T* dW, int n, int V, int D) {
+  for (size_t i = 0; i < (size_t)V * D; ++i) dW[i] = 0;
+  for (int i = 0; i < n; ++i) {
+    int idx = (int)index_col[i];
+    for (int j = 0; j < D; ++j) dW[(size_t)idx * D + j] = dW[(size_t)idx * D + j] + dOut[(size_t)i * D + j];
+  }
+}
+
+// ---- GradientUtils.cs:22-42: out = gradients.Sum(g => g[i][j]) (LINQ, list order) ---------
+template <typename T>
+void accumulate_gradients(const T* const* grads, int count, T* out, size_t n) {
+#pragma omp parallel for schedule(static)
+  for (long long i = 0; i < (long long)n; ++i) {
+    LinqSum<T> s;
+    for (int g = 0; g < count; ++g) s.add(grads[g][i]);
+    out[i] = s.result();
+  }
+}
+// ---- OperationBase.cs:295-303: dest[i][j] += output[i][j] ---------------------------------
+template <typename T>
+void accumulate_into(T* dest, const T* src, size_t n) {
+  for (size_t i = 0; i < n; ++i) dest[i] = dest[i] + src[i];
+}
+// ---- OperationNeuralNetworkVisitor.cs:449-478: Aggregate((a,b)=>a+b) * (1/count) ----------
+template <typename T>
+void batch_mean(const T* const* grads, int count, T* out, size_t n) {
+  T inv = (T)1 / (T)count;
+#pragma omp parallel for schedule(static)
+  for (long long i = 0; i < (long long)n; ++i) {
+    T acc = grads[0][i];
+    for (int g = 1; g < count; ++g) acc = acc + grads[g][i];
+    out[i] = acc * inv;
+  }
+}
+
+// ---- GradientClipper.cs:118-157 + StandardizedMatrix :212-253 (+ lite float accumulators) --
+template <typename T>
+void clip_reference(T* g, size_t n, T clip, T minv) {
+  T sum = 0;
+  for (size_t i = 0; i < n; ++i) sum = sum + g[i];
+  T mean = sum / (T)(long long)n;
+  T var = 0;
+  for (size_t i = 0; i < n; ++i) var = var + p_pow<T>(g[i] - mean, (T)2);
+  T sd = p_sqrt<T>(var / (T)(long long)n);
+  for (size_t i = 0; i < n; ++i) {
+    T z = (g[i] - mean) / sd;
+    T lim = net_min<T>(clip, (T)1 + std::fabs(z));
+    T v = g[i];
+    if (v > lim) v = lim;
+    else if (v < -lim) v = -lim;
+    if (v > 0 && v < minv) v = minv;
+    else if (v < 0 && v > -minv) v = -minv;
+    g[i] = v;
+  }
+}
+
+// ---- src/PRAD/GradientClipper.cs:37-72: tensor form, no minimum-threshold step ------------
+// (PradOp.ClipGradients discards its result, PradOp.cs:3236-3239; kept for completeness.)
+template <typename T>
+void clip_prad(const T* g, T* out, size_t n, T clip) {
+  double s = 0;
+  for (size_t i = 0; i < n; ++i) s += (double)g[i];
+  double mean = s / (double)n;
+  double v = 0;
+  for (size_t i = 0; i < n; ++i) v += std::pow((double)g[i] - mean, 2);
+  double sd = std::sqrt(v / (double)n);
+  T meanT = (T)mean, sdT = (T)sd;
+  for (size_t i = 0; i < n; ++i) {
+    T z = (g[i] - meanT) / sdT;
+    T dyn = std::fabs(z) + (T)1;
+    dyn = dyn < clip ? dyn : clip;
+    T c = g[i] < dyn ? g[i] : dyn;
+    out[i] = c > -dyn ? c : -dyn;
+  }
+}
+
+// ---- global-norm clip over a set of tensors (NOT in the reference: it has only the per-
+// tensor z-score clamp above; this restates the textbook rule the benchmark config asks for:
+// scale = max_norm / max(norm, max_norm)) --------------------------------------------------
+template <typename T>
+double clip_global_norm(T* const* g, const long long* n, int count, double max_norm) {
+  double ss = 0;
+  for (int t = 0; t < count; ++t)
+    for (long long i = 0; i < n[t]; ++i) ss += (double)g[t][i] * (double)g[t][i];
+  double norm = std::sqrt(ss);
+  if (norm > max_norm) {
+    T sc = (T)(max_norm / norm);
+    for (int t = 0; t < count; ++t)
+      for (long long i = 0; i < n[t]; ++i) g[t][i] = g[t][i] * sc;
+  }
+  return norm;
+}
+
+// ---- AdamOptimizer.cs:195-239 via MatrixUtils.cs:71-137 (reciprocal bias correction) -------
+template <typename T>
+void adam_rmad(T* w, T* m, T* v, const T* g, size_t n, T lr, T b1, T b2, T eps, T iter) {
+  T c1 = (T)1 / ((T)1 - p_pow<T>(b1, iter));
+  T c2 = (T)1 / ((T)1 - p_pow<T>(b2, iter));
+  T omb1 = (T)1 - b1, omb2 = (T)1 - b2;
+#pragma omp parallel for schedule(static)
+  for (long long i = 0; i < (long long)n; ++i) {
+    T a0 = b1 * m[i];
+    T a1 = omb1 * g[i];
+    T fm = a0 + a1;
+    T gg = g[i] * g[i];
+    T s0 = b2 * v[i];
+    T s1 = omb2 * gg;
+    T sm = s0 + s1;
+    T mh = c1 * fm;
+    T vh = c2 * sm;
+    T num = lr * mh;
+    T den = p_sqrt<T>(vh) + eps;
+    w[i] = w[i] - num / den;
+    m[i] = fm;
+    v[i] = sm;
+  }
+}
+// ---- src/PRAD/AdamOptimizer.cs:79-103 (divide by the bias correction; t is an int) --------
+template <typename T>
+void adam_prad(T* w, T* m, T* v, const T* g, size_t n, T lr, T b1, T b2, T eps, int t) {
+  T d1 = (T)1 - p_pow<T>(b1, (T)t);
+  T d2 = (T)1 - p_pow<T>(b2, (T)t);
+  T omb1 = (T)1 - b1, omb2 = (T)1 - b2;
+  for (size_t i = 0; i < n; ++i) {
+    T a0 = m[i] * b1;
+    T a1 = g[i] * omb1;
+    T fm = a0 + a1;
+    T gg = g[i] * g[i];
+    T s0 = v[i] * b2;
+    T s1 = gg * omb2;
+    T sm = s0 + s1;
+    T mh = fm / d1;
+    T vh = sm / d2;
+    T num = mh * lr;
+    T den = (T)std::sqrt(vh) + eps;
+    w[i] = w[i] - num / den;
+    m[i] = fm;
+    v[i] = sm;
+  }
+}
+
+}  // namespace
+
+#define ORACLE_EXPORT(T, S)                                                                        \
+  extern "C" {                                                                                     \
+  void oracle_matmul_forward_##S(const T* A, const T* B, T* C, int M, int K, int N) {              \
+    matmul_forward<T>(A, B, C, M, K, N);                                                           \
+  }                                                                                                \
+  void oracle_matmul_backward_##S(const T* A, const T* B, const T* dC, T* dA, T* dB, int M, int K, \
+                                  int N) {                                                         \
+    matmul_backward<T>(A, B, dC, dA, dB, M, K, N);                                                 \
+  }                                                                                                \
+  void oracle_batch_matmul_forward_##S(const T* A, const T* B, T* C, int depth, int M, int K,      \
+                                       int N, int b_shared) {                                      \
+    batch_matmul_forward<T>(A, B, C, depth, M, K, N, b_shared);                                    \
+  }                                                                                                \
+  void oracle_batch_matmul_backward_##S(const T* A, const T* B, const T* dC, T* dA, T* dB,         \
+                                        int depth, int M, int K, int N, int b_shared) {            \
+    batch_matmul_backward<T>(A, B, dC, dA, dB, depth, M, K, N, b_shared);                          \
+  }                                                                                                \
+  void oracle_matmul_and_sum_forward_##S(const T* A, const T* B, T* out, int R, int C, int N,      \
+                                         int P) {                                                  \
+    matmul_and_sum_forward<T>(A, B, out, R, C, N, P);                                              \
+  }                                                                                                \
+  void oracle_matmul_and_sum_backward_##S(const T* A, const T* B, const T* dOut, T* dA, T* dB,     \
+                                          int R, int C, int N, int P) {                            \
+    matmul_and_sum_backward<T>(A, B, dOut, dA, dB, R, C, N, P);                                    \
+  }                                                                                                \
+  void oracle_leaky_relu_forward_##S(const T* x, T* y, long long n, T a) {                         \
+    leaky_relu_forward<T>(x, y, (size_t)n, a);                                                     \
+  }                                                                                                \
+  void oracle_leaky_relu_backward_##S(const T* x, const T* dy, T* dx, long long n, T a) {          \
+    leaky_relu_backward<T>(x, dy, dx, (size_t)n, a);                                               \
+  }                                                                                                \
+  void oracle_sigmoid_forward_##S(const T* x, T* y, long long n) {                                 \
+    sigmoid_forward<T>(x, y, (size_t)n);                                                           \
+  }                                                                                                \
+  void oracle_sigmoid_backward_##S(const T* y, const T* dy, T* dx, long long n) {                  \
+    sigmoid_backward<T>(y, dy, dx, (size_t)n);                                                     \
+  }                                                                                                \
+  void oracle_tanh_forward_##S(const T* x, T* y, long long n) { tanh_forward<T>(x, y, (size_t)n); }\
+  void oracle_tanh_backward_##S(const T* y, const T* dy, T* dx, long long n) {                     \
+    tanh_backward<T>(y, dy, dx, (size_t)n);                                                        \
+  }                                                                                                \
+  void oracle_gelu_forward_##S(const T* x, T* y, long long n) { gelu_forward<T>(x, y, (size_t)n); }\
+  void oracle_gelu_backward_##S(const T* x, const T* dy, T* dx, long long n) {                     \
+    gelu_backward<T>(x, dy, dx, (size_t)n);                                                        \
+  }                                                                                                \
+  void oracle_hadamard_forward_##S(const T* a, const T* b, T* y, long long n) {                    \
+    hadamard_forward<T>(a, b, y, (size_t)n);                                                       \
+  }                                                                                                \
+  void oracle_hadamard_backward_##S(const T* a, const T* b, const T* dy, T* da, T* db,             \
+                                    long long n) {                                                 \
+    hadamard_backward<T>(a, b, dy, da, db, (size_t)n);                                             \
+  }                                                                                                \
+  void oracle_add_forward_##S(const T* a, const T* b, T* y, long long n) {                         \
+    add_forward<T>(a, b, y, (size_t)n);                                                            \
+  }                                                                                                \
+  void oracle_add3_forward_##S(const T* a, const T* b, const T* c, T* y, long long n) {            \
+    add3_forward<T>(a, b, c, y, (size_t)n);                                                        \
+  }                                                                                                \
+  void oracle_add_backward_##S(const T* dy, T* d0, T* d1, T* d2, long long n) {                    \
+    add_backward<T>(dy, d0, d1, d2, (size_t)n);                                                    \
+  }                                                                                                \
+  void oracle_add_broadcast_forward_##S(const T* x, const T* b, T* y, int R, int C) {              \
+    add_broadcast_forward<T>(x, b, y, R, C);                                                       \
+  }                                                                                                \
+  void oracle_add_broadcast_backward_##S(const T* dy, T* db, int R, int C) {                       \
+    add_broadcast_backward<T>(dy, db, R, C);                                                       \
+  }                                                                                                \
+  void oracle_softmax_forward_##S(const T* x, T* y, int R, int C) {                                \
+    softmax_forward<T>(x, y, R, C);                                                                \
+  }                                                                                                \
+  void oracle_softmax_backward_##S(const T* y, const T* dy, T* dx, int R, int C) {                 \
+    softmax_backward<T>(y, dy, dx, R, C);                                                          \
+  }                                                                                                \
+  void oracle_layernorm_forward_##S(const T* x, T* y, T* mean, T* stdv, int R, int C) {            \
+    layernorm_forward<T>(x, y, mean, stdv, R, C);                                                  \
+  }                                                                                                \
+  void oracle_layernorm_backward_##S(const T* x, const T* mean, const T* stdv, const T* dy,        \
+                                     T* dx, int R, int C) {                                        \
+    layernorm_backward<T>(x, mean, stdv, dy, dx, R, C);                                            \
+  }                                                                                                \
+  void oracle_transpose_##S(const T* x, T* y, int R, int C) { transpose<T>(x, y, R, C); }          \
+  void oracle_scale_##S(const T* x, T* y, long long n, T s) { scale<T>(x, y, (size_t)n, s); }      \
+  T oracle_mse_forward_##S(const T* o, const T* t, int R, int C) {                                 \
+    return mse_forward<T>(o, t, R, C);                                                             \
+  }                                                                                                \
+  void oracle_mse_backward_##S(const T* o, const T* t, T* g, int R, int C, long long rt) {         \
+    mse_backward<T>(o, t, g, R, C, rt);                                                            \
+  }                                                                                                \
+  T oracle_cce_forward_##S(const T* o, const T* t, int R, int C) {                                 \
+    return cce_forward<T>(o, t, R, C);                                                             \
+  }                                                                                                \
+  void oracle_cce_backward_##S(const T* o, const T* t, T* g, int R, int C, long long rt) {         \
+    cce_backward<T>(o, t, g, R, C, rt);                                                            \
+  }                                                                                                \
+  void oracle_embedding_forward_##S(const T* idx, const T* W, T* out, int n, int D) {              \
+    embedding_forward<T>(idx, W, out, n, D);                                                       \
+  }                                                                                                \
+  void oracle_embedding_backward_##S(const T* idx, const T* dOut, T* dW, int n, int V, int D) {    \
+    embedding_backward<T>(idx, dOut, dW, n, V, D);                                                 \
+  }                                                                                                \
+  void oracle_accumulate_gradients_##S(const T* const* g, int count, T* out, long long n) {        \
+    accumulate_gradients<T>(g, count, out, (size_t)n);                                             \
+  }                                                                                                \
+  void oracle_accumulate_into_##S(T* d, const T* s, long long n) {                                 \
+    accumulate_into<T>(d, s, (size_t)n);                                                           \
+  }                                                                                                \
+  void oracle_batch_mean_##S(const T* const* g, int count, T* out, long long n) {                  \
+    batch_mean<T>(g, count, out, (size_t)n);                                                       \
+  }                                                                                                \
+  void oracle_clip_reference_##S(T* g, long long n, T clip, T minv) {                              \
+    clip_reference<T>(g, (size_t)n, clip, minv);                                                   \
+  }                                                                                                \
+  void oracle_clip_prad_##S(const T* g, T* out, long long n, T clip) {                             \
+    clip_prad<T>(g, out, (size_t)n, clip);                                                         \
+  }                                                                                                \
+  double oracle_clip_global_norm_##S(T* const* g, const long long* n, int count, double mx) {      \
+    return clip_global_norm<T>(g, n, count, mx);                                                   \
+  }                                                                                                \
+  void oracle_adam_rmad_##S(T* w, T* m, T* v, const T* g, long long n, T lr, T b1, T b2, T eps,    \
+                            T iter) {                                                              \
+    adam_rmad<T>(w, m, v, g, (size_t)n, lr, b1, b2, eps, iter);                                    \
+  }                                                                                                \
+  void oracle_adam_prad_##S(T* w, T* m, T* v, const T* g, long long n, T lr, T b1, T b2, T eps,    \
+                            int t) {                                                               \
+    adam_prad<T>(w, m, v, g, (size_t)n, lr, b1, b2, eps, t);                                       \
+  }                                                                                                \
+  }
+
+ORACLE_EXPORT(float, f32)
+ORACLE_EXPORT(double, f64)
+
+extern "C" int oracle_num_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}
+extern "C" void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
