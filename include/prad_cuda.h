@@ -1,0 +1,302 @@
+/*
+ * libprad_cuda -- C ABI of the B200 (sm_100a) backward-pass engine for
+ * ParallelReverseAutoDiff (RMAD double / PRADLite float).
+ *
+ * The reference has no native ABI of its own: its seam is the managed
+ * IOperation / IBatchOperation contract (src/RMAD/IOperation.cs:17-25,
+ * src/RMAD/IBatchOperation.cs:11-19) plus the CudaBlas singleton lifecycle
+ * (src/RMAD/CudaBlas.cs:104-160).  Every entry point below names the managed
+ * member it stands in for; a C# operation class binds it with [DllImport].
+ *
+ * Conventions
+ *  - every call returns a prad_status (0 = PRAD_OK); nothing throws or aborts;
+ *    prad_last_error() returns the calling thread's last message;
+ *  - matrices are dense row-major (the device form of the reference's jagged
+ *    T[rows][cols]); a DeepMatrix is `depth` consecutive matrices;
+ *  - device buffers are plain device pointers obtained from prad_alloc (or any
+ *    other CUDA allocation of the same device); host spans say so in their name;
+ *  - work is enqueued on the context's stream; prad_sync waits for it; calls on
+ *    one context must not overlap, different contexts may be used concurrently
+ *    from different threads (the visitor calls Backward from thread-pool threads,
+ *    src/RMAD/OperationNeuralNetworkVisitor.cs:303-306);
+ *  - dtype selects the arithmetic and storage type: PRAD_F64 for RMAD/PRAD,
+ *    PRAD_F32 for PRADLite.
+ *  - there is no CPU fallback: without a usable CUDA device every call fails.
+ */
+#ifndef PRAD_CUDA_H_
+#define PRAD_CUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int32_t prad_status;
+enum {
+  PRAD_OK = 0,
+  PRAD_ERR_INVALID = 1,          /* null pointer / bad enum / negative size            */
+  PRAD_ERR_SHAPE = 2,            /* InvalidOperationException("... do not match ...")  */
+  PRAD_ERR_NOT_INITIALIZED = 3,  /* CudaNotInitializedException                        */
+  PRAD_ERR_CUDA = 4,             /* InvalidOperationException("CUBLAS failure.") class */
+  PRAD_ERR_OOM = 5,
+  PRAD_ERR_UNSUPPORTED = 6,
+  PRAD_ERR_COMM = 7,             /* NCCL error                                          */
+  PRAD_ERR_TIMEOUT = 8           /* a bounded wait ran out (visitor TimeoutInMinutes)   */
+};
+
+typedef enum { PRAD_F32 = 0, PRAD_F64 = 1 } prad_dtype;
+
+/* activation selector for the fused and stand-alone kernels */
+typedef enum {
+  PRAD_ACT_NONE = 0,
+  PRAD_ACT_LEAKY_RELU = 1, /* LeakyReLUOperation: backward reads the INPUT x           */
+  PRAD_ACT_SIGMOID = 2,    /* SigmoidOperation:   backward reads the OUTPUT y          */
+  PRAD_ACT_TANH = 3,       /* TanhOperation:      backward reads the OUTPUT y          */
+  PRAD_ACT_GELU = 4        /* GELUOperation:      backward reads the INPUT x           */
+} prad_act;
+
+typedef enum { PRAD_ADAM_RMAD = 0, PRAD_ADAM_PRAD = 1 } prad_adam_form;
+
+typedef struct prad_ctx prad_ctx;
+
+/* ---------------------------------------------------------------- lifecycle
+ * prad_init / prad_shutdown replace CudaBlas.Instance.Initialize() / Dispose()
+ * with DeviceId (src/RMAD/CudaBlas.cs:104,120-160). */
+prad_status prad_init(int device, prad_ctx** out_ctx);
+prad_status prad_shutdown(prad_ctx* ctx);
+/* thread-local text of the last failure on this thread ("" if none) */
+const char* prad_last_error(void);
+/* library version string and the sm architecture it was built for */
+const char* prad_version(void);
+/* options: "gemm_f32" = "auto" | "simt" | "tf32x3" ; "gemm_f64" = "auto" | "simt" | "dmma" */
+prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value);
+/* wait for everything enqueued on the context (what the managed code gets for free
+ * because GetAsArray2D blocks, src/RMAD/GpuMatrixMultiplyOperation.cs:199-201) */
+prad_status prad_sync(prad_ctx* ctx);
+/* number of kernels this context has launched since prad_init (introspection) */
+prad_status prad_launch_count(prad_ctx* ctx, int64_t* out_count);
+/* cudaStream_t of the context (so that a caller can order its own work against it) */
+prad_status prad_stream(prad_ctx* ctx, void** out_stream);
+/* makes the context enqueue on a caller-provided cudaStream_t (NULL restores its own) */
+prad_status prad_use_stream(prad_ctx* ctx, void* stream);
+
+/* ---------------------------------------------------------------- memory
+ * Stand in for accelerator.Allocate2DDenseX / CopyFromCPU / GetAsArray2D
+ * (src/RMAD/GpuMatrixMultiplyOperation.cs:190-201) and for the jagged<->flat
+ * conversion (:210-271), but buffers persist across operations. */
+prad_status prad_alloc(prad_ctx* ctx, size_t bytes, void** out_dptr);
+prad_status prad_free(prad_ctx* ctx, void* dptr);
+prad_status prad_zero(prad_ctx* ctx, void* dptr, size_t bytes);
+prad_status prad_copy(prad_ctx* ctx, void* dst, const void* src, size_t bytes);
+prad_status prad_upload(prad_ctx* ctx, void* dst, const void* src_host, size_t bytes);
+prad_status prad_download(prad_ctx* ctx, void* dst_host, const void* src, size_t bytes);
+/* jagged form: `rows` host row pointers of row_bytes each <-> one dense device matrix */
+prad_status prad_upload_rows(prad_ctx* ctx, void* dst, const void* const* src_rows, int rows,
+                             size_t row_bytes);
+prad_status prad_download_rows(prad_ctx* ctx, void* const* dst_rows, const void* src, int rows,
+                               size_t row_bytes);
+/* pinned host staging memory for the two calls above and for *_host entry points */
+prad_status prad_alloc_host(prad_ctx* ctx, size_t bytes, void** out_hptr);
+prad_status prad_free_host(prad_ctx* ctx, void* hptr);
+
+/* ---------------------------------------------------------------- GEMM
+ * General row-major product C = alpha*op(A)*op(B) + beta*C over `batch` slices
+ * (stride 0 = operand shared by all slices).  op(A) is MxK, op(B) is KxN.
+ * Replaces the ILGPU tiled kernel (src/RMAD/GpuMatrixMultiplyOperation.cs:39-91)
+ * and the cuBLAS Gemm call (src/RMAD/CudaBlas.cs:245,293). */
+prad_status prad_gemm(prad_ctx* ctx, prad_dtype dt, int transA, int transB, int M, int N, int K,
+                      double alpha, const void* A, int lda, const void* B, int ldb, double beta,
+                      void* C, int ldc, int batch, int64_t strideA, int64_t strideB,
+                      int64_t strideC);
+
+/* MatrixMultiplyOperation.Forward (src/RMAD/MatrixMultiplyOperation.cs:50-80) with the
+ * optional fused tail  Z = A*B (+ bias row), Y = act(Z):  bias, Z_out and the activation
+ * may each be absent (NULL / PRAD_ACT_NONE).  A is MxK, B is KxN. */
+prad_status prad_matmul_forward(prad_ctx* ctx, prad_dtype dt, const void* A, const void* B,
+                                void* Y, int M, int K, int N, const void* bias, void* Z_out,
+                                prad_act act, double act_alpha);
+
+/* MatrixMultiplyOperation.Backward (src/RMAD/MatrixMultiplyOperation.cs:83-126):
+ *   dA = dC * B^T (MxK),  dB = A^T * dC (KxN).  Either output may be NULL.
+ * accumulate_dB != 0 adds into dB (OperationBase.AccumulateGradient,
+ * src/RMAD/OperationBase.cs:295-303) instead of overwriting it; dB_scale multiplies the
+ * product first (1/count for the batch mean of OperationNeuralNetworkVisitor.cs:449-478).
+ * If act_below != PRAD_ACT_NONE the dA result is multiplied in the epilogue by the
+ * derivative of the activation that produced A (saved_below = that op's saved tensor),
+ * i.e. the call also performs the next node's elementwise Backward. */
+prad_status prad_matmul_backward(prad_ctx* ctx, prad_dtype dt, const void* A, const void* B,
+                                 const void* dC, void* dA, void* dB, int M, int K, int N,
+                                 int accumulate_dB, double dB_scale, prad_act act_below,
+                                 const void* saved_below, double act_alpha);
+
+/* The node of benchmark config 1: MatMul -> activation.  dPre = dOut (.) act'(saved),
+ * dA = dPre*B^T, dB = A^T*dPre, all three returned (dPre must be non-NULL). */
+prad_status prad_matmul_act_backward(prad_ctx* ctx, prad_dtype dt, const void* A, const void* B,
+                                     const void* dOut, prad_act act, const void* saved,
+                                     double act_alpha, void* dPre, void* dA, void* dB, int M,
+                                     int K, int N);
+
+/* Same node with HOST buffers (what a managed caller holding jagged Matrix data pays):
+ * uploads A, B, dOut, saved; runs prad_matmul_act_backward; downloads dPre, dA, dB and
+ * returns after the copies completed.  Host spans are dense row-major. */
+prad_status prad_matmul_act_backward_host(prad_ctx* ctx, prad_dtype dt, const void* A_host,
+                                          const void* B_host, const void* dOut_host,
+                                          prad_act act, const void* saved_host, double act_alpha,
+                                          void* dPre_host, void* dA_host, void* dB_host, int M,
+                                          int K, int N);
+
+/* BatchMatrixMultiplyOperation.Forward/Backward (src/RMAD/BatchMatrixMultiplyOperation.cs:
+ * 51-94) over `depth` slices; b_shared != 0 is the (DeepMatrix, Matrix) overload.  With
+ * b_shared the per-slice dB results are returned slice by slice (depth x K x N) exactly as
+ * the reference does when dB_mean == NULL; if dB_mean != NULL the library instead writes the
+ * visitor's combined result sum_d(dB_d)*(1/depth) (OperationNeuralNetworkVisitor.cs:
+ * 449-478) there with one long-K product and dB may be NULL. */
+prad_status prad_batch_matmul_forward(prad_ctx* ctx, prad_dtype dt, const void* A, const void* B,
+                                      void* C, int depth, int M, int K, int N, int b_shared);
+prad_status prad_batch_matmul_backward(prad_ctx* ctx, prad_dtype dt, const void* A,
+                                       const void* B, const void* dC, void* dA, void* dB,
+                                       void* dB_mean, int depth, int M, int K, int N,
+                                       int b_shared);
+
+/* (Gpu)MatrixMultiplyAndSumOperation (src/RMAD/GpuMatrixMultiplyAndSumOperation.cs:114-154,
+ * src/RMAD/MatrixMultiplyAndSumOperation.cs:50-89): out[q] = sum_ij (A*B_q)_ij ; backward
+ * dB_q = A^T*dOut[q], dA = sum_q B_q^T*dOut[q] (scalar products, not GEMMs).
+ * A is RxC, B is P slices of CxN, out/dOut is 1xP, dA is NxC, dB is P slices of CxR. */
+prad_status prad_matmul_and_sum_forward(prad_ctx* ctx, prad_dtype dt, const void* A,
+                                        const void* B, void* out, int R, int C, int N, int P);
+prad_status prad_matmul_and_sum_backward(prad_ctx* ctx, prad_dtype dt, const void* A,
+                                         const void* B, const void* dOut, void* dA, void* dB,
+                                         int R, int C, int N, int P);
+
+/* ---------------------------------------------------------------- elementwise
+ * LeakyReLUOperation.cs:54-93, SigmoidOperation.cs:46-84, TanhOperation.cs:42-78,
+ * GELUOperation.cs:44-101 (and the lite float twins).  `saved` is the tensor the managed
+ * op keeps for Backward: the input x for LeakyReLU/GELU, the output y for Sigmoid/Tanh. */
+prad_status prad_act_forward(prad_ctx* ctx, prad_dtype dt, prad_act act, const void* x, void* y,
+                             int64_t n, double act_alpha);
+prad_status prad_act_backward(prad_ctx* ctx, prad_dtype dt, prad_act act, const void* saved,
+                              const void* dy, void* dx, int64_t n, double act_alpha);
+/* HadamardProductOperation.cs:50-118 */
+prad_status prad_hadamard_forward(prad_ctx* ctx, prad_dtype dt, const void* a, const void* b,
+                                  void* y, int64_t n);
+prad_status prad_hadamard_backward(prad_ctx* ctx, prad_dtype dt, const void* a, const void* b,
+                                   const void* dy, void* da, void* db, int64_t n);
+/* MatrixAddOperation.cs:29-68 / MatrixAddThreeOperation.cs:30-67 (c may be NULL).  Their
+ * Backward returns copies of dOut; prad_copy (or simply aliasing dOut) provides that. */
+prad_status prad_add_forward(prad_ctx* ctx, prad_dtype dt, const void* a, const void* b,
+                             const void* c, void* y, int64_t n);
+/* MatrixAddBroadcastingOperation.cs:32-69: y = x + bias row; backward: dBias[j] = sum_i
+ * dOut[i][j] (the input gradient is dOut itself).  accumulate != 0 adds into dbias. */
+prad_status prad_add_broadcast_forward(prad_ctx* ctx, prad_dtype dt, const void* x,
+                                       const void* bias, void* y, int rows, int cols);
+prad_status prad_add_broadcast_backward(prad_ctx* ctx, prad_dtype dt, const void* dy,
+                                        void* dbias, int rows, int cols, int accumulate);
+/* MatrixMultiplyScalarOperation.cs:48-88 (forward and backward are the same scaling) */
+prad_status prad_scale(prad_ctx* ctx, prad_dtype dt, const void* x, void* y, int64_t n,
+                       double s);
+/* MatrixTransposeOperation.cs:28-64 over `depth` slices: y (cols x rows) = x^T */
+prad_status prad_transpose(prad_ctx* ctx, prad_dtype dt, const void* x, void* y, int rows,
+                           int cols, int depth);
+
+/* ---------------------------------------------------------------- row operations
+ * SoftmaxOperation.cs:45-109 (rows = all rows of all slices) */
+prad_status prad_softmax_forward(prad_ctx* ctx, prad_dtype dt, const void* x, void* y,
+                                 int64_t rows, int cols);
+prad_status prad_softmax_backward(prad_ctx* ctx, prad_dtype dt, const void* y, const void* dy,
+                                  void* dx, int64_t rows, int cols);
+/* LayerNormalizationOperation.cs:56-112: population sigma, eps (1e-9) added to sigma; the
+ * backward is the reference's diagonal-only form.  mean/stdv are rows long (the op's state). */
+prad_status prad_layernorm_forward(prad_ctx* ctx, prad_dtype dt, const void* x, void* y,
+                                   void* mean, void* stdv, int64_t rows, int cols);
+prad_status prad_layernorm_backward(prad_ctx* ctx, prad_dtype dt, const void* x,
+                                    const void* mean, const void* stdv, const void* dy, void* dx,
+                                    int64_t rows, int cols);
+
+/* ---------------------------------------------------------------- losses
+ * Loss/MeanSquaredErrorLossOperation.cs:37-84 and
+ * Loss/CategoricalCrossEntropyLossOperation.cs:37-87.  loss_out is one device scalar.
+ * rows_total is the row count used in the normaliser (== rows unless the batch is sharded
+ * over several GPUs, where it is the global row count). */
+prad_status prad_mse_forward(prad_ctx* ctx, prad_dtype dt, const void* out, const void* target,
+                             void* loss_out, int64_t rows, int cols);
+prad_status prad_mse_backward(prad_ctx* ctx, prad_dtype dt, const void* out, const void* target,
+                              void* grad, int64_t rows, int cols, int64_t rows_total);
+prad_status prad_cce_forward(prad_ctx* ctx, prad_dtype dt, const void* out, const void* target,
+                             void* loss_out, int64_t rows, int cols);
+prad_status prad_cce_backward(prad_ctx* ctx, prad_dtype dt, const void* out, const void* target,
+                              void* grad, int64_t rows, int cols, int64_t rows_total);
+
+/* ---------------------------------------------------------------- embedding
+ * EmbeddingOperation.cs:49-86.  index_col holds the row indices as values of the matrix
+ * type (column 0 of the input matrix, cast with (int)).  The backward adds duplicate
+ * indices in input-row order, so the result is bit-identical to the sequential loop. */
+prad_status prad_embedding_forward(prad_ctx* ctx, prad_dtype dt, const void* index_col,
+                                   const void* W, void* out, int n, int vocab, int dim);
+prad_status prad_embedding_backward(prad_ctx* ctx, prad_dtype dt, const void* index_col,
+                                    const void* dOut, void* dW, int n, int vocab, int dim);
+
+/* ---------------------------------------------------------------- gradient accumulation
+ * prad_segmented_sum: GradientUtils.AccumulateGradients (src/RMAD/GradientUtils.cs:22-42),
+ * out[i] = sum over the `count` sources in list order (deterministic; replaces the
+ * visitor's lock + semaphore hand-off, OperationNeuralNetworkVisitor.cs:231-273).
+ * srcs_host is a HOST array of `count` device pointers.
+ * prad_accumulate: dest += src (OperationBase.cs:295-303).
+ * prad_batch_mean: left-fold sum times 1/count (OperationNeuralNetworkVisitor.cs:449-478). */
+prad_status prad_segmented_sum(prad_ctx* ctx, prad_dtype dt, const void* const* srcs_host,
+                               int count, void* out, int64_t n);
+prad_status prad_accumulate(prad_ctx* ctx, prad_dtype dt, void* dest, const void* src,
+                            int64_t n);
+prad_status prad_batch_mean(prad_ctx* ctx, prad_dtype dt, const void* const* srcs_host,
+                            int count, void* out, int64_t n);
+
+/* ---------------------------------------------------------------- clip + Adam
+ * Multi-tensor calls: *_host arguments are HOST arrays of `count` device pointers / sizes
+ * (one entry per model element, as GradientClipper.Clip / AdamOptimizer.Optimize walk the
+ * layers' identifiers, src/RMAD/GradientClipper.cs:31-71, AdamOptimizer.cs:32-90).
+ * prad_clip_reference: per-tensor z-score clamp + minimum threshold, in place
+ *   (GradientClipper.cs:118-157,212-253).
+ * prad_clip_global_norm: NOT in the reference; scale all tensors by max_norm/max(norm,
+ *   max_norm); norm_out (host double, may be NULL) receives the norm before clipping.
+ * prad_adam: form RMAD = AdamOptimizer.cs:195-239 (reciprocal bias correction),
+ *   form PRAD = src/PRAD/AdamOptimizer.cs:79-103; `iteration` is NeuralNetworkParameters.
+ *   AdamIteration (set by the caller); zero_grad != 0 also clears the gradients
+ *   (GradientClearer.Clear, src/RMAD/GradientClearer.cs:21-86).
+ * prad_clip_adam: the two steps in one pass over the gradients (clip_mode 0 = none,
+ *   1 = reference, 2 = global norm). */
+prad_status prad_clip_reference(prad_ctx* ctx, prad_dtype dt, void* const* grads_host,
+                                const int64_t* sizes_host, int count, double clip_value,
+                                double min_value);
+prad_status prad_clip_global_norm(prad_ctx* ctx, prad_dtype dt, void* const* grads_host,
+                                  const int64_t* sizes_host, int count, double max_norm,
+                                  double* norm_out);
+prad_status prad_adam(prad_ctx* ctx, prad_dtype dt, void* const* w_host, void* const* g_host,
+                      void* const* m_host, void* const* v_host, const int64_t* sizes_host,
+                      int count, double lr, double beta1, double beta2, double eps,
+                      double iteration, prad_adam_form form, int zero_grad);
+prad_status prad_clip_adam(prad_ctx* ctx, prad_dtype dt, void* const* w_host,
+                           void* const* g_host, void* const* m_host, void* const* v_host,
+                           const int64_t* sizes_host, int count, int clip_mode,
+                           double clip_value, double min_value, double lr, double beta1,
+                           double beta2, double eps, double iteration, prad_adam_form form,
+                           int zero_grad);
+
+/* ---------------------------------------------------------------- data parallel
+ * Not in the reference (it has no multi-device code; its closest relative is the offline
+ * averaging of GradientStore.AverageGradients, src/RMAD/GradientStore.cs:24-104).
+ * One process per GPU.  Rank 0 calls prad_dp_unique_id and ships the 128 bytes to the
+ * other ranks by any host channel; every rank then calls prad_dp_init.
+ * prad_dp_allreduce enqueues a SUM all-reduce on the context's communication stream after
+ * everything enqueued so far on the compute stream, so it overlaps with later compute;
+ * prad_dp_wait makes the compute stream wait for all outstanding all-reduces. */
+prad_status prad_dp_unique_id(void* out_id_128_bytes);
+prad_status prad_dp_init(prad_ctx* ctx, const void* id_128_bytes, int rank, int world_size);
+prad_status prad_dp_allreduce(prad_ctx* ctx, prad_dtype dt, void* buf, int64_t n);
+prad_status prad_dp_wait(prad_ctx* ctx);
+prad_status prad_dp_shutdown(prad_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PRAD_CUDA_H_ */

@@ -1,0 +1,124 @@
+"""ctypes binding of ``libprad_cuda.so`` -- the same C ABI a C# caller binds with P/Invoke.
+
+Loading fails loudly when the shared library has not been built; there is no fallback of
+any kind.  Every function declared in ``include/prad_cuda.h`` is given its argument types
+here, so a signature drift shows up as a ctypes error instead of a corrupted call.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libprad_cuda.so")
+
+vp, i32, i64, f64, sz = C.c_void_p, C.c_int, C.c_int64, C.c_double, C.c_size_t
+pvp = C.POINTER(C.c_void_p)
+pi64 = C.POINTER(C.c_int64)
+
+# name -> argument types (return type is int32 status unless stated otherwise)
+SIGNATURES = {
+    "prad_init": [i32, pvp],
+    "prad_shutdown": [vp],
+    "prad_set_option": [vp, C.c_char_p, C.c_char_p],
+    "prad_sync": [vp],
+    "prad_launch_count": [vp, pi64],
+    "prad_stream": [vp, pvp],
+    "prad_use_stream": [vp, vp],
+    "prad_alloc": [vp, sz, pvp],
+    "prad_free": [vp, vp],
+    "prad_zero": [vp, vp, sz],
+    "prad_copy": [vp, vp, vp, sz],
+    "prad_upload": [vp, vp, vp, sz],
+    "prad_download": [vp, vp, vp, sz],
+    "prad_upload_rows": [vp, vp, pvp, i32, sz],
+    "prad_download_rows": [vp, pvp, vp, i32, sz],
+    "prad_alloc_host": [vp, sz, pvp],
+    "prad_free_host": [vp, vp],
+    "prad_gemm": [vp, i32, i32, i32, i32, i32, i32, f64, vp, i32, vp, i32, f64, vp, i32, i32, i64,
+                  i64, i64],
+    "prad_matmul_forward": [vp, i32, vp, vp, vp, i32, i32, i32, vp, vp, i32, f64],
+    "prad_matmul_backward": [vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, f64, i32, vp, f64],
+    "prad_matmul_act_backward": [vp, i32, vp, vp, vp, i32, vp, f64, vp, vp, vp, i32, i32, i32],
+    "prad_matmul_act_backward_host": [vp, i32, vp, vp, vp, i32, vp, f64, vp, vp, vp, i32, i32,
+                                      i32],
+    "prad_batch_matmul_forward": [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32],
+    "prad_batch_matmul_backward": [vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32],
+    "prad_matmul_and_sum_forward": [vp, i32, vp, vp, vp, i32, i32, i32, i32],
+    "prad_matmul_and_sum_backward": [vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, i32],
+    "prad_act_forward": [vp, i32, i32, vp, vp, i64, f64],
+    "prad_act_backward": [vp, i32, i32, vp, vp, vp, i64, f64],
+    "prad_hadamard_forward": [vp, i32, vp, vp, vp, i64],
+    "prad_hadamard_backward": [vp, i32, vp, vp, vp, vp, vp, i64],
+    "prad_add_forward": [vp, i32, vp, vp, vp, vp, i64],
+    "prad_add_broadcast_forward": [vp, i32, vp, vp, vp, i32, i32],
+    "prad_add_broadcast_backward": [vp, i32, vp, vp, i32, i32, i32],
+    "prad_scale": [vp, i32, vp, vp, i64, f64],
+    "prad_transpose": [vp, i32, vp, vp, i32, i32, i32],
+    "prad_softmax_forward": [vp, i32, vp, vp, i64, i32],
+    "prad_softmax_backward": [vp, i32, vp, vp, vp, i64, i32],
+    "prad_layernorm_forward": [vp, i32, vp, vp, vp, vp, i64, i32],
+    "prad_layernorm_backward": [vp, i32, vp, vp, vp, vp, vp, i64, i32],
+    "prad_mse_forward": [vp, i32, vp, vp, vp, i64, i32],
+    "prad_mse_backward": [vp, i32, vp, vp, vp, i64, i32, i64],
+    "prad_cce_forward": [vp, i32, vp, vp, vp, i64, i32],
+    "prad_cce_backward": [vp, i32, vp, vp, vp, i64, i32, i64],
+    "prad_embedding_forward": [vp, i32, vp, vp, vp, i32, i32, i32],
+    "prad_embedding_backward": [vp, i32, vp, vp, vp, i32, i32, i32],
+    "prad_segmented_sum": [vp, i32, pvp, i32, vp, i64],
+    "prad_accumulate": [vp, i32, vp, vp, i64],
+    "prad_batch_mean": [vp, i32, pvp, i32, vp, i64],
+    "prad_clip_reference": [vp, i32, pvp, pi64, i32, f64, f64],
+    "prad_clip_global_norm": [vp, i32, pvp, pi64, i32, f64, C.POINTER(f64)],
+    "prad_adam": [vp, i32, pvp, pvp, pvp, pvp, pi64, i32, f64, f64, f64, f64, f64, i32, i32],
+    "prad_clip_adam": [vp, i32, pvp, pvp, pvp, pvp, pi64, i32, i32, f64, f64, f64, f64, f64, f64,
+                       f64, i32, i32],
+    "prad_dp_unique_id": [vp],
+    "prad_dp_init": [vp, vp, i32, i32],
+    "prad_dp_allreduce": [vp, i32, vp, i64],
+    "prad_dp_wait": [vp],
+    "prad_dp_shutdown": [vp],
+}
+STRING_FUNCS = ("prad_last_error", "prad_version")
+
+_lib = None
+
+
+class PradError(RuntimeError):
+    """A non-zero status from libprad_cuda; ``status`` holds the code."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"[prad status {status}] {message}")
+        self.status = status
+
+
+# status codes of include/prad_cuda.h
+OK, ERR_INVALID, ERR_SHAPE, ERR_NOT_INITIALIZED, ERR_CUDA, ERR_OOM, ERR_UNSUPPORTED, ERR_COMM, \
+    ERR_TIMEOUT = range(9)
+
+
+def load() -> C.CDLL:
+    """Loads the library (once).  Raises if it is missing: there is no other code path."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m parallelreverseautodiff_b200.build` "
+            "(nvcc, sm_100a).  This package has no CPU or PyTorch fallback.")
+    lib = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
+    for name, args in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here == header and library disagree
+        fn.argtypes = args
+        fn.restype = C.c_int32
+    for name in STRING_FUNCS:
+        fn = getattr(lib, name)
+        fn.argtypes = []
+        fn.restype = C.c_char_p
+    _lib = lib
+    return lib
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise PradError(status, load().prad_last_error().decode("utf-8", "replace"))

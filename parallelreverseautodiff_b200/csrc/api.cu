@@ -1,0 +1,278 @@
+// Lifecycle, error reporting and memory entry points of libprad_cuda.
+#include <cstring>
+
+#include "common.cuh"
+
+namespace prad {
+
+static thread_local char g_err[1024] = {0};
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+static prad_status grow(void** p, size_t* have, size_t need, bool host) {
+  if (*have >= need) return PRAD_OK;
+  size_t want = need + need / 4;
+  want = (want + 255) & ~(size_t)255;
+  if (*p) {
+    if (host) cudaFreeHost(*p); else cudaFree(*p);
+    *p = nullptr;
+    *have = 0;
+  }
+  cudaError_t e = host ? cudaMallocHost(p, want) : cudaMalloc(p, want);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    set_error("scratch allocation of %zu bytes failed: %s", want, cudaGetErrorString(e));
+    return PRAD_ERR_OOM;
+  }
+  *have = want;
+  return PRAD_OK;
+}
+
+prad_status ensure_workspace(prad_ctx* ctx, size_t bytes) {
+  if (ctx->ws_bytes < bytes) {
+    // earlier kernels may still read the old block
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) { set_error("sync before workspace growth: %s", cudaGetErrorString(e)); return PRAD_ERR_CUDA; }
+  }
+  return grow(&ctx->ws, &ctx->ws_bytes, bytes, false);
+}
+prad_status ensure_host_workspace(prad_ctx* ctx, size_t bytes) {
+  if (ctx->host_ws_bytes < bytes) {
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) { set_error("sync before host scratch growth: %s", cudaGetErrorString(e)); return PRAD_ERR_CUDA; }
+  }
+  return grow(&ctx->host_ws, &ctx->host_ws_bytes, bytes, true);
+}
+prad_status ensure_stage(prad_ctx* ctx, size_t bytes) {
+  if (ctx->stage_bytes < bytes) {
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) { set_error("sync before staging growth: %s", cudaGetErrorString(e)); return PRAD_ERR_CUDA; }
+  }
+  return grow(&ctx->stage, &ctx->stage_bytes, bytes, false);
+}
+
+prad_status dp_destroy(prad_ctx* ctx);  // dp.cu
+
+}  // namespace prad
+
+using namespace prad;
+
+extern "C" {
+
+const char* prad_last_error(void) { return g_err; }
+
+const char* prad_version(void) { return "libprad_cuda 0.1 (sm_100a)"; }
+
+prad_status prad_init(int device, prad_ctx** out_ctx) {
+  PRAD_REQUIRE(out_ctx != nullptr, PRAD_ERR_INVALID, "prad_init: out_ctx is null");
+  *out_ctx = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0) {
+    (void)cudaGetLastError();
+    set_error("prad_init: no usable CUDA device (%s); this library has no CPU fallback",
+              e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+    return PRAD_ERR_NOT_INITIALIZED;
+  }
+  PRAD_REQUIRE(device >= 0 && device < count, PRAD_ERR_INVALID,
+               "prad_init: device %d out of range (0..%d)", device, count - 1);
+  PRAD_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  PRAD_CUDA(cudaGetDeviceProperties(&prop, device));
+  PRAD_REQUIRE(prop.major == 10, PRAD_ERR_UNSUPPORTED,
+               "prad_init: device %d is sm_%d%d; this library is built for sm_100a only", device,
+               prop.major, prop.minor);
+  prad_ctx* c = new prad_ctx();
+  c->device = device;
+  c->sm_count = prop.multiProcessorCount;
+  e = cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking);
+  if (e != cudaSuccess) {
+    set_error("prad_init: cudaStreamCreate: %s", cudaGetErrorString(e));
+    delete c;
+    return PRAD_ERR_CUDA;
+  }
+  c->stream = c->own_stream;
+  *out_ctx = c;
+  g_err[0] = 0;
+  return PRAD_OK;
+}
+
+prad_status prad_shutdown(prad_ctx* ctx) {
+  PRAD_CHECK_CTX(ctx);
+  cudaStreamSynchronize(ctx->stream);
+  dp_destroy(ctx);
+  if (ctx->ws) cudaFree(ctx->ws);
+  if (ctx->stage) cudaFree(ctx->stage);
+  if (ctx->host_ws) cudaFreeHost(ctx->host_ws);
+  if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
+  ctx->magic = 0;
+  delete ctx;
+  return PRAD_OK;
+}
+
+prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(key && value, PRAD_ERR_INVALID, "prad_set_option: null key or value");
+  if (!strcmp(key, "gemm_f32")) {
+    if (!strcmp(value, "auto")) ctx->gemm_f32 = GemmF32::Auto;
+    else if (!strcmp(value, "simt")) ctx->gemm_f32 = GemmF32::Simt;
+    else if (!strcmp(value, "tf32x3")) ctx->gemm_f32 = GemmF32::Tf32x3;
+    else { set_error("prad_set_option: gemm_f32 must be auto|simt|tf32x3, got '%s'", value); return PRAD_ERR_INVALID; }
+    return PRAD_OK;
+  }
+  if (!strcmp(key, "gemm_f64")) {
+    if (!strcmp(value, "auto")) ctx->gemm_f64 = GemmF64::Auto;
+    else if (!strcmp(value, "simt")) ctx->gemm_f64 = GemmF64::Simt;
+    else if (!strcmp(value, "dmma")) ctx->gemm_f64 = GemmF64::Dmma;
+    else { set_error("prad_set_option: gemm_f64 must be auto|simt|dmma, got '%s'", value); return PRAD_ERR_INVALID; }
+    return PRAD_OK;
+  }
+  set_error("prad_set_option: unknown key '%s'", key);
+  return PRAD_ERR_INVALID;
+}
+
+prad_status prad_sync(prad_ctx* ctx) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_CUDA(cudaStreamSynchronize(ctx->stream));
+  return PRAD_OK;
+}
+
+prad_status prad_launch_count(prad_ctx* ctx, int64_t* out_count) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(out_count, PRAD_ERR_INVALID, "prad_launch_count: null output");
+  *out_count = ctx->launches;
+  return PRAD_OK;
+}
+
+prad_status prad_stream(prad_ctx* ctx, void** out_stream) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(out_stream, PRAD_ERR_INVALID, "prad_stream: null output");
+  *out_stream = (void*)ctx->stream;
+  return PRAD_OK;
+}
+
+prad_status prad_use_stream(prad_ctx* ctx, void* stream) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_CUDA(cudaStreamSynchronize(ctx->stream));
+  ctx->stream = stream ? (cudaStream_t)stream : ctx->own_stream;
+  return PRAD_OK;
+}
+
+prad_status prad_alloc(prad_ctx* ctx, size_t bytes, void** out_dptr) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(out_dptr, PRAD_ERR_INVALID, "prad_alloc: null output");
+  *out_dptr = nullptr;
+  if (bytes == 0) bytes = 16;
+  cudaError_t e = cudaMalloc(out_dptr, bytes);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    set_error("prad_alloc(%zu bytes): %s", bytes, cudaGetErrorString(e));
+    return e == cudaErrorMemoryAllocation ? PRAD_ERR_OOM : PRAD_ERR_CUDA;
+  }
+  return PRAD_OK;
+}
+
+prad_status prad_free(prad_ctx* ctx, void* dptr) {
+  PRAD_CHECK_CTX(ctx);
+  if (!dptr) return PRAD_OK;
+  PRAD_CUDA(cudaStreamSynchronize(ctx->stream));
+  PRAD_CUDA(cudaFree(dptr));
+  return PRAD_OK;
+}
+
+prad_status prad_alloc_host(prad_ctx* ctx, size_t bytes, void** out_hptr) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(out_hptr, PRAD_ERR_INVALID, "prad_alloc_host: null output");
+  *out_hptr = nullptr;
+  if (bytes == 0) bytes = 16;
+  cudaError_t e = cudaMallocHost(out_hptr, bytes);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    set_error("prad_alloc_host(%zu bytes): %s", bytes, cudaGetErrorString(e));
+    return PRAD_ERR_OOM;
+  }
+  return PRAD_OK;
+}
+
+prad_status prad_free_host(prad_ctx* ctx, void* hptr) {
+  PRAD_CHECK_CTX(ctx);
+  if (!hptr) return PRAD_OK;
+  PRAD_CUDA(cudaFreeHost(hptr));
+  return PRAD_OK;
+}
+
+prad_status prad_zero(prad_ctx* ctx, void* dptr, size_t bytes) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dptr || bytes == 0, PRAD_ERR_INVALID, "prad_zero: null pointer");
+  if (bytes) PRAD_CUDA(cudaMemsetAsync(dptr, 0, bytes, ctx->stream));
+  return PRAD_OK;
+}
+
+prad_status prad_copy(prad_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE((dst && src) || bytes == 0, PRAD_ERR_INVALID, "prad_copy: null pointer");
+  if (bytes) PRAD_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  return PRAD_OK;
+}
+
+prad_status prad_upload(prad_ctx* ctx, void* dst, const void* src_host, size_t bytes) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE((dst && src_host) || bytes == 0, PRAD_ERR_INVALID, "prad_upload: null pointer");
+  if (bytes) PRAD_CUDA(cudaMemcpyAsync(dst, src_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+  return PRAD_OK;
+}
+
+prad_status prad_download(prad_ctx* ctx, void* dst_host, const void* src, size_t bytes) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE((dst_host && src) || bytes == 0, PRAD_ERR_INVALID, "prad_download: null pointer");
+  if (bytes) {
+    PRAD_CUDA(cudaMemcpyAsync(dst_host, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    PRAD_CUDA(cudaStreamSynchronize(ctx->stream));
+  }
+  return PRAD_OK;
+}
+
+// Jagged rows are gathered into one pinned block first, so the device sees ONE copy.
+prad_status prad_upload_rows(prad_ctx* ctx, void* dst, const void* const* src_rows, int rows,
+                             size_t row_bytes) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(rows >= 0, PRAD_ERR_INVALID, "prad_upload_rows: negative row count");
+  if (rows == 0 || row_bytes == 0) return PRAD_OK;
+  PRAD_REQUIRE(dst && src_rows, PRAD_ERR_INVALID, "prad_upload_rows: null pointer");
+  size_t total = (size_t)rows * row_bytes;
+  prad_status s = ensure_host_workspace(ctx, total);
+  if (s) return s;
+  // the pinned block may still feed an earlier asynchronous copy
+  PRAD_CUDA(cudaStreamSynchronize(ctx->stream));
+  for (int i = 0; i < rows; ++i) {
+    PRAD_REQUIRE(src_rows[i], PRAD_ERR_INVALID, "prad_upload_rows: row %d is null", i);
+    memcpy((char*)ctx->host_ws + (size_t)i * row_bytes, src_rows[i], row_bytes);
+  }
+  PRAD_CUDA(cudaMemcpyAsync(dst, ctx->host_ws, total, cudaMemcpyHostToDevice, ctx->stream));
+  return PRAD_OK;
+}
+
+prad_status prad_download_rows(prad_ctx* ctx, void* const* dst_rows, const void* src, int rows,
+                               size_t row_bytes) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(rows >= 0, PRAD_ERR_INVALID, "prad_download_rows: negative row count");
+  if (rows == 0 || row_bytes == 0) return PRAD_OK;
+  PRAD_REQUIRE(dst_rows && src, PRAD_ERR_INVALID, "prad_download_rows: null pointer");
+  size_t total = (size_t)rows * row_bytes;
+  prad_status s = ensure_host_workspace(ctx, total);
+  if (s) return s;
+  PRAD_CUDA(cudaMemcpyAsync(ctx->host_ws, src, total, cudaMemcpyDeviceToHost, ctx->stream));
+  PRAD_CUDA(cudaStreamSynchronize(ctx->stream));
+  for (int i = 0; i < rows; ++i) {
+    PRAD_REQUIRE(dst_rows[i], PRAD_ERR_INVALID, "prad_download_rows: row %d is null", i);
+    memcpy(dst_rows[i], (const char*)ctx->host_ws + (size_t)i * row_bytes, row_bytes);
+  }
+  return PRAD_OK;
+}
+
+}  // extern "C"

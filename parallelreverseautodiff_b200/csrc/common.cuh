@@ -1,0 +1,128 @@
+// Shared plumbing of libprad_cuda: context, error reporting, launch helpers.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+#include <vector>
+
+#include "../../include/prad_cuda.h"
+
+namespace prad {
+
+void set_error(const char* fmt, ...);
+
+enum class GemmF32 { Auto, Simt, Tf32x3 };
+enum class GemmF64 { Auto, Simt, Dmma };
+
+struct DpState;  // data-parallel state (dp.cu)
+
+}  // namespace prad
+
+struct prad_ctx {
+  int device = 0;
+  cudaStream_t own_stream = nullptr;  // created by prad_init
+  cudaStream_t stream = nullptr;      // the stream work is enqueued on
+  int sm_count = 0;
+  int64_t launches = 0;
+  prad::GemmF32 gemm_f32 = prad::GemmF32::Auto;
+  prad::GemmF64 gemm_f64 = prad::GemmF64::Auto;
+  // scratch (grown on demand, never shrunk): device workspace, pointer tables, pinned host
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+  void* host_ws = nullptr;
+  size_t host_ws_bytes = 0;
+  // host-buffer entry points keep their device staging here
+  void* stage = nullptr;
+  size_t stage_bytes = 0;
+  prad::DpState* dp = nullptr;
+  uint32_t magic = 0x50524144u;  // "PRAD"
+};
+
+namespace prad {
+
+inline bool ctx_ok(const prad_ctx* c) { return c != nullptr && c->magic == 0x50524144u; }
+
+#define PRAD_CHECK_CTX(ctx)                                                              \
+  do {                                                                                   \
+    if (!prad::ctx_ok(ctx)) {                                                            \
+      prad::set_error("context is null or was shut down (call prad_init first)");        \
+      return PRAD_ERR_NOT_INITIALIZED;                                                   \
+    }                                                                                    \
+    cudaError_t e_ = cudaSetDevice((ctx)->device);                                       \
+    if (e_ != cudaSuccess) {                                                             \
+      prad::set_error("cudaSetDevice(%d): %s", (ctx)->device, cudaGetErrorString(e_));   \
+      return PRAD_ERR_CUDA;                                                              \
+    }                                                                                    \
+  } while (0)
+
+#define PRAD_CUDA(call)                                                                  \
+  do {                                                                                   \
+    cudaError_t e_ = (call);                                                             \
+    if (e_ != cudaSuccess) {                                                             \
+      prad::set_error("%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__,  \
+                      __LINE__);                                                         \
+      return e_ == cudaErrorMemoryAllocation ? PRAD_ERR_OOM : PRAD_ERR_CUDA;             \
+    }                                                                                    \
+  } while (0)
+
+#define PRAD_REQUIRE(cond, code, ...)                                                    \
+  do {                                                                                   \
+    if (!(cond)) {                                                                       \
+      prad::set_error(__VA_ARGS__);                                                      \
+      return code;                                                                       \
+    }                                                                                    \
+  } while (0)
+
+// after a kernel launch: count it and surface launch-configuration errors
+#define PRAD_LAUNCHED(ctx)                                                               \
+  do {                                                                                   \
+    (ctx)->launches++;                                                                   \
+    cudaError_t e_ = cudaPeekAtLastError();                                              \
+    if (e_ != cudaSuccess) {                                                             \
+      (void)cudaGetLastError();                                                          \
+      prad::set_error("kernel launch failed: %s (%s:%d)", cudaGetErrorString(e_),        \
+                      __FILE__, __LINE__);                                               \
+      return PRAD_ERR_CUDA;                                                              \
+    }                                                                                    \
+  } while (0)
+
+inline bool dtype_ok(prad_dtype dt) { return dt == PRAD_F32 || dt == PRAD_F64; }
+inline size_t dtype_size(prad_dtype dt) { return dt == PRAD_F64 ? 8 : 4; }
+
+// grows ctx->ws to at least `bytes` (256-byte aligned) ; previous contents are lost
+prad_status ensure_workspace(prad_ctx* ctx, size_t bytes);
+// grows the pinned host scratch
+prad_status ensure_host_workspace(prad_ctx* ctx, size_t bytes);
+prad_status ensure_stage(prad_ctx* ctx, size_t bytes);
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// grid size for a grid-stride streaming kernel: a multiple of the SM count
+inline int stream_grid(const prad_ctx* ctx, int64_t work_items, int per_block, int ctas_per_sm) {
+  int64_t need = ceil_div(work_items, per_block);
+  int64_t cap = (int64_t)ctx->sm_count * ctas_per_sm;
+  if (need < 1) need = 1;
+  return (int)(need < cap ? need : cap);
+}
+
+// ---- internal entry points shared between translation units -------------------------------
+struct GemmEpilogue {
+  // C = alpha*acc + beta*C ; then  + bias[n] ; store Z_out ; then act / act' multiply
+  const void* bias = nullptr;      // row vector of N (forward)
+  void* z_out = nullptr;           // pre-activation copy (forward)
+  prad_act act = PRAD_ACT_NONE;    // forward activation applied to the value
+  prad_act dact = PRAD_ACT_NONE;   // backward: multiply by act'(saved[m][n])
+  const void* saved = nullptr;     // M x N tensor (ld = ldc) read by dact
+  double act_alpha = 0.0;
+};
+
+prad_status gemm_dispatch(prad_ctx* ctx, prad_dtype dt, bool transA, bool transB, int M, int N,
+                          int K, double alpha, const void* A, int lda, const void* B, int ldb,
+                          double beta, void* C, int ldc, int batch, int64_t sA, int64_t sB,
+                          int64_t sC, const GemmEpilogue& epi);
+
+}  // namespace prad

@@ -1,0 +1,440 @@
+// Stand-alone elementwise kernels of the backward path: HBM-bound streams with 128-bit
+// loads and stores, grid sized as a multiple of the SM count, grid-stride loop.
+// (Compiled with -fmad=false so that products and sums round as the managed code's do.)
+#include "act_math.cuh"
+#include "common.cuh"
+
+namespace prad {
+
+template <typename T> struct Vec16;
+template <> struct Vec16<float> { using type = float4; static constexpr int N = 4; };
+template <> struct Vec16<double> { using type = double2; static constexpr int N = 2; };
+
+template <int N> struct PtrsIn { const void* p[N > 0 ? N : 1]; };
+template <int N> struct PtrsOut { void* p[N > 0 ? N : 1]; };
+
+// out[0..NOUT) = f(in[0..NIN)) per element.  UNROLL vectors per thread per trip keep
+// several 128-bit loads in flight per thread.
+template <typename T, int NIN, int NOUT, typename F, int UNROLL>
+__global__ void __launch_bounds__(256)
+map_kernel(PtrsIn<NIN> in, PtrsOut<NOUT> out, int64_t n, bool vec, F f) {
+  constexpr int VEC = Vec16<T>::N;
+  using V = typename Vec16<T>::type;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  if (vec) {
+    const int64_t nvec = n / VEC;
+    for (int64_t base = tid; base < nvec; base += nthreads * UNROLL) {
+      V vin[UNROLL][NIN > 0 ? NIN : 1];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        int64_t i = base + (int64_t)u * nthreads;
+        if (i < nvec) {
+#pragma unroll
+          for (int k = 0; k < NIN; ++k) vin[u][k] = __ldcs(reinterpret_cast<const V*>(in.p[k]) + i);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        int64_t i = base + (int64_t)u * nthreads;
+        if (i < nvec) {
+          V vout[NOUT];
+#pragma unroll
+          for (int q = 0; q < VEC; ++q) {
+            T a[NIN > 0 ? NIN : 1], r[NOUT];
+#pragma unroll
+            for (int k = 0; k < NIN; ++k) a[k] = reinterpret_cast<const T*>(&vin[u][k])[q];
+            f(a, r);
+#pragma unroll
+            for (int k = 0; k < NOUT; ++k) reinterpret_cast<T*>(&vout[k])[q] = r[k];
+          }
+#pragma unroll
+          for (int k = 0; k < NOUT; ++k) __stcs(reinterpret_cast<V*>(out.p[k]) + i, vout[k]);
+        }
+      }
+    }
+    // tail
+    for (int64_t i = nvec * VEC + tid; i < n; i += nthreads) {
+      T a[NIN > 0 ? NIN : 1], r[NOUT];
+#pragma unroll
+      for (int k = 0; k < NIN; ++k) a[k] = reinterpret_cast<const T*>(in.p[k])[i];
+      f(a, r);
+#pragma unroll
+      for (int k = 0; k < NOUT; ++k) reinterpret_cast<T*>(out.p[k])[i] = r[k];
+    }
+  } else {
+    for (int64_t i = tid; i < n; i += nthreads) {
+      T a[NIN > 0 ? NIN : 1], r[NOUT];
+#pragma unroll
+      for (int k = 0; k < NIN; ++k) a[k] = reinterpret_cast<const T*>(in.p[k])[i];
+      f(a, r);
+#pragma unroll
+      for (int k = 0; k < NOUT; ++k) reinterpret_cast<T*>(out.p[k])[i] = r[k];
+    }
+  }
+}
+
+template <typename T, int NIN, int NOUT, typename F>
+static prad_status launch_map(prad_ctx* ctx, const void* const (&in)[NIN], void* const (&out)[NOUT],
+                              int64_t n, F f) {
+  if (n <= 0) return PRAD_OK;
+  PtrsIn<NIN> pi;
+  PtrsOut<NOUT> po;
+  bool vec = true;
+  for (int k = 0; k < NIN; ++k) { pi.p[k] = in[k]; vec = vec && (((uintptr_t)in[k] & 15) == 0); }
+  for (int k = 0; k < NOUT; ++k) { po.p[k] = out[k]; vec = vec && (((uintptr_t)out[k] & 15) == 0); }
+  constexpr int UNROLL = 4;
+  constexpr int VEC = Vec16<T>::N;
+  int grid = stream_grid(ctx, ceil_div(n, VEC * UNROLL), 256, 8);
+  map_kernel<T, NIN, NOUT, F, UNROLL><<<grid, 256, 0, ctx->stream>>>(pi, po, n, vec, f);
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
+
+// ---------------------------------------------------------------- functors
+template <typename T> struct ActFwd {
+  prad_act act; T alpha;
+  __device__ void operator()(const T* a, T* r) const { r[0] = act_value<T>(act, a[0], alpha); }
+};
+template <typename T> struct ActBwd {  // a[0] = saved, a[1] = dy
+  prad_act act; T alpha;
+  __device__ void operator()(const T* a, T* r) const {
+    r[0] = mul_rn(a[1], act_derivative<T>(act, a[0], alpha));
+  }
+};
+template <typename T> struct HadFwd {
+  __device__ void operator()(const T* a, T* r) const { r[0] = mul_rn(a[0], a[1]); }
+};
+template <typename T> struct HadBwd {  // a, b, dy -> da = dy*b, db = dy*a (HadamardProductOperation.cs:98,110)
+  __device__ void operator()(const T* a, T* r) const {
+    r[0] = mul_rn(a[2], a[1]);
+    r[1] = mul_rn(a[2], a[0]);
+  }
+};
+template <typename T> struct Add2 {
+  __device__ void operator()(const T* a, T* r) const { r[0] = add_rn(a[0], a[1]); }
+};
+template <typename T> struct Add3 {
+  __device__ void operator()(const T* a, T* r) const { r[0] = add_rn(add_rn(a[0], a[1]), a[2]); }
+};
+template <typename T> struct Scale {
+  T s;
+  __device__ void operator()(const T* a, T* r) const { r[0] = mul_rn(a[0], s); }
+};
+template <typename T> struct Accum {  // dest += src  (OperationBase.cs:299)
+  __device__ void operator()(const T* a, T* r) const { r[0] = add_rn(a[0], a[1]); }
+};
+
+template <typename T>
+static prad_status act_forward_t(prad_ctx* ctx, prad_act act, const void* x, void* y, int64_t n,
+                                 double alpha) {
+  const void* in[1] = {x};
+  void* out[1] = {y};
+  return launch_map<T, 1, 1>(ctx, in, out, n, ActFwd<T>{act, (T)alpha});
+}
+template <typename T>
+static prad_status act_backward_t(prad_ctx* ctx, prad_act act, const void* saved, const void* dy,
+                                  void* dx, int64_t n, double alpha) {
+  const void* in[2] = {saved, dy};
+  void* out[1] = {dx};
+  return launch_map<T, 2, 1>(ctx, in, out, n, ActBwd<T>{act, (T)alpha});
+}
+
+// ---------------------------------------------------------------- add-broadcast
+template <typename T>
+__global__ void add_broadcast_kernel(const T* __restrict__ x, const T* __restrict__ bias,
+                                     T* __restrict__ y, int64_t n, int cols) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    y[i] = add_rn(x[i], bias[i % cols]);
+}
+
+// Column sums  dBias[j] = sum_i dOut[i][j]  (MatrixAddBroadcastingOperation.cs:60-63).
+// Two deterministic stages: each CTA sums a band of rows for a 32-column strip into
+// partial[band][col] (coalesced 128-byte row segments), then one pass adds the bands in
+// band order.  Accumulation is in double for float data (LINQ Sum accumulates in double).
+template <typename T>
+__global__ void __launch_bounds__(256)
+colsum_partial_kernel(const T* __restrict__ x, double* __restrict__ partial, int64_t rows,
+                      int cols, int rows_per_band) {
+  __shared__ double sm[8][33];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + lane;
+  const int64_t r0 = (int64_t)blockIdx.y * rows_per_band;
+  int64_t r1 = r0 + rows_per_band;
+  if (r1 > rows) r1 = rows;
+  double acc = 0.0;
+  if (col < cols)
+    for (int64_t r = r0 + w; r < r1; r += 8) acc += (double)x[r * cols + col];
+  sm[w][lane] = acc;
+  __syncthreads();
+  if (w == 0) {
+    double s = 0.0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s += sm[k][lane];
+    if (col < cols) partial[(int64_t)blockIdx.y * cols + col] = s;
+  }
+}
+template <typename T>
+__global__ void colsum_final_kernel(const double* __restrict__ partial, T* __restrict__ out,
+                                    int cols, int bands, int accumulate) {
+  int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= cols) return;
+  double s = 0.0;
+  for (int b = 0; b < bands; ++b) s += partial[(int64_t)b * cols + col];
+  T v = (T)s;
+  out[col] = accumulate ? add_rn(out[col], v) : v;
+}
+
+template <typename T>
+static prad_status add_broadcast_backward_t(prad_ctx* ctx, const void* dy, void* dbias,
+                                            int64_t rows, int cols, int accumulate) {
+  int strips = (int)ceil_div(cols, 32);
+  int64_t want_bands = ceil_div((int64_t)ctx->sm_count * 8, strips);
+  int64_t max_bands = ceil_div(rows, 64);
+  int bands = (int)(want_bands < max_bands ? want_bands : max_bands);
+  if (bands < 1) bands = 1;
+  if (bands > 65535) bands = 65535;
+  int rows_per_band = (int)ceil_div(rows, bands);
+  bands = (int)ceil_div(rows, rows_per_band);
+  prad_status s = ensure_workspace(ctx, (size_t)bands * cols * sizeof(double));
+  if (s) return s;
+  colsum_partial_kernel<T><<<dim3(strips, bands), 256, 0, ctx->stream>>>(
+      (const T*)dy, (double*)ctx->ws, rows, cols, rows_per_band);
+  PRAD_LAUNCHED(ctx);
+  colsum_final_kernel<T><<<(unsigned)ceil_div(cols, 128), 128, 0, ctx->stream>>>(
+      (const double*)ctx->ws, (T*)dbias, cols, bands, accumulate);
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
+
+// ---------------------------------------------------------------- transpose (per slice)
+template <typename T>
+__global__ void transpose_kernel(const T* __restrict__ x, T* __restrict__ y, int rows, int cols) {
+  __shared__ T tile[32][33];
+  const int64_t slice = blockIdx.z;
+  x += slice * (int64_t)rows * cols;
+  y += slice * (int64_t)rows * cols;
+  int c = blockIdx.x * 32 + threadIdx.x;
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    int r = blockIdx.y * 32 + j;
+    if (r < rows && c < cols) tile[j][threadIdx.x] = x[(int64_t)r * cols + c];
+  }
+  __syncthreads();
+  int r2 = blockIdx.y * 32 + threadIdx.x;  // becomes the fast index of y
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    int c2 = blockIdx.x * 32 + j;
+    if (c2 < cols && r2 < rows) y[(int64_t)c2 * rows + r2] = tile[threadIdx.x][j];
+  }
+}
+
+// ---------------------------------------------------------------- n-ary sums
+#define PRAD_MAX_SRCS 16
+struct SrcTable { const void* p[PRAD_MAX_SRCS]; int count; };
+
+// out[i] = sum_g src_g[i] in list order (GradientUtils.cs:33-39).  LINQ's Sum over float
+// accumulates in double and casts once; for double it is a plain left fold.
+template <typename T>
+__global__ void __launch_bounds__(256)
+nary_sum_kernel(SrcTable t, T* __restrict__ out, int64_t n, int mode, T inv_count) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    if (mode == 0) {  // segmented sum, double accumulator
+      double acc = 0.0;
+      for (int g = 0; g < t.count; ++g) acc += (double)reinterpret_cast<const T*>(t.p[g])[i];
+      out[i] = (T)acc;
+    } else {  // batch mean: left fold in T, then * (1/count)
+      T acc = reinterpret_cast<const T*>(t.p[0])[i];
+      for (int g = 1; g < t.count; ++g) acc = add_rn(acc, reinterpret_cast<const T*>(t.p[g])[i]);
+      out[i] = mul_rn(acc, inv_count);
+    }
+  }
+}
+
+template <typename T>
+static prad_status nary_t(prad_ctx* ctx, const void* const* srcs, int count, void* out, int64_t n,
+                          int mode) {
+  if (n <= 0) return PRAD_OK;
+  // more than PRAD_MAX_SRCS sources: fold in groups, keeping list order.  The running value
+  // is carried in `out`, which is exact for mode 1 (left fold) and for double mode 0; for
+  // float mode 0 the carry rounds to float between groups of 15.
+  T inv = (T)1 / (T)count;
+  int done = 0;
+  bool first = true;
+  while (done < count) {
+    SrcTable t;
+    int k = 0;
+    if (!first) t.p[k++] = out;
+    while (k < PRAD_MAX_SRCS && done < count) t.p[k++] = srcs[done++];
+    t.count = k;
+    bool last = done == count;
+    int grid = stream_grid(ctx, n, 256, 8);
+    int m = mode == 0 ? 0 : 1;
+    nary_sum_kernel<T><<<grid, 256, 0, ctx->stream>>>(t, (T*)out, n, m,
+                                                      (mode == 1 && last) ? inv : (T)1);
+    PRAD_LAUNCHED(ctx);
+    first = false;
+  }
+  return PRAD_OK;
+}
+
+}  // namespace prad
+
+using namespace prad;
+
+#define DISPATCH_DT(dt, CALL_F32, CALL_F64) ((dt) == PRAD_F32 ? (CALL_F32) : (CALL_F64))
+
+extern "C" {
+
+prad_status prad_act_forward(prad_ctx* ctx, prad_dtype dt, prad_act act, const void* x, void* y,
+                             int64_t n, double act_alpha) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && act >= PRAD_ACT_NONE && act <= PRAD_ACT_GELU, PRAD_ERR_INVALID,
+               "prad_act_forward: bad dtype or activation");
+  PRAD_REQUIRE(n >= 0 && (n == 0 || (x && y)), PRAD_ERR_INVALID, "prad_act_forward: null pointer or negative size");
+  return DISPATCH_DT(dt, act_forward_t<float>(ctx, act, x, y, n, act_alpha),
+                     act_forward_t<double>(ctx, act, x, y, n, act_alpha));
+}
+
+prad_status prad_act_backward(prad_ctx* ctx, prad_dtype dt, prad_act act, const void* saved,
+                              const void* dy, void* dx, int64_t n, double act_alpha) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && act >= PRAD_ACT_NONE && act <= PRAD_ACT_GELU, PRAD_ERR_INVALID,
+               "prad_act_backward: bad dtype or activation");
+  PRAD_REQUIRE(n >= 0 && (n == 0 || (saved && dy && dx)), PRAD_ERR_INVALID,
+               "prad_act_backward: null pointer or negative size");
+  return DISPATCH_DT(dt, act_backward_t<float>(ctx, act, saved, dy, dx, n, act_alpha),
+                     act_backward_t<double>(ctx, act, saved, dy, dx, n, act_alpha));
+}
+
+prad_status prad_hadamard_forward(prad_ctx* ctx, prad_dtype dt, const void* a, const void* b,
+                                  void* y, int64_t n) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && n >= 0 && (n == 0 || (a && b && y)), PRAD_ERR_INVALID,
+               "prad_hadamard_forward: bad argument");
+  const void* in[2] = {a, b};
+  void* out[1] = {y};
+  return DISPATCH_DT(dt, (launch_map<float, 2, 1>(ctx, in, out, n, HadFwd<float>{})),
+                     (launch_map<double, 2, 1>(ctx, in, out, n, HadFwd<double>{})));
+}
+
+prad_status prad_hadamard_backward(prad_ctx* ctx, prad_dtype dt, const void* a, const void* b,
+                                   const void* dy, void* da, void* db, int64_t n) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && n >= 0 && (n == 0 || (a && b && dy && da && db)), PRAD_ERR_INVALID,
+               "prad_hadamard_backward: bad argument");
+  const void* in[3] = {a, b, dy};
+  void* out[2] = {da, db};
+  return DISPATCH_DT(dt, (launch_map<float, 3, 2>(ctx, in, out, n, HadBwd<float>{})),
+                     (launch_map<double, 3, 2>(ctx, in, out, n, HadBwd<double>{})));
+}
+
+prad_status prad_add_forward(prad_ctx* ctx, prad_dtype dt, const void* a, const void* b,
+                             const void* c, void* y, int64_t n) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && n >= 0 && (n == 0 || (a && b && y)), PRAD_ERR_INVALID,
+               "prad_add_forward: bad argument");
+  void* out[1] = {y};
+  if (c) {
+    const void* in[3] = {a, b, c};
+    return DISPATCH_DT(dt, (launch_map<float, 3, 1>(ctx, in, out, n, Add3<float>{})),
+                       (launch_map<double, 3, 1>(ctx, in, out, n, Add3<double>{})));
+  }
+  const void* in[2] = {a, b};
+  return DISPATCH_DT(dt, (launch_map<float, 2, 1>(ctx, in, out, n, Add2<float>{})),
+                     (launch_map<double, 2, 1>(ctx, in, out, n, Add2<double>{})));
+}
+
+prad_status prad_add_broadcast_forward(prad_ctx* ctx, prad_dtype dt, const void* x,
+                                       const void* bias, void* y, int rows, int cols) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0, PRAD_ERR_INVALID,
+               "prad_add_broadcast_forward: bad argument");
+  int64_t n = (int64_t)rows * cols;
+  if (n == 0) return PRAD_OK;
+  PRAD_REQUIRE(x && bias && y, PRAD_ERR_INVALID, "prad_add_broadcast_forward: null pointer");
+  int grid = stream_grid(ctx, n, 256, 8);
+  if (dt == PRAD_F32)
+    add_broadcast_kernel<float><<<grid, 256, 0, ctx->stream>>>((const float*)x, (const float*)bias, (float*)y, n, cols);
+  else
+    add_broadcast_kernel<double><<<grid, 256, 0, ctx->stream>>>((const double*)x, (const double*)bias, (double*)y, n, cols);
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
+
+prad_status prad_add_broadcast_backward(prad_ctx* ctx, prad_dtype dt, const void* dy,
+                                        void* dbias, int rows, int cols, int accumulate) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0, PRAD_ERR_INVALID,
+               "prad_add_broadcast_backward: bad argument");
+  if (cols == 0) return PRAD_OK;
+  PRAD_REQUIRE(dbias && (dy || rows == 0), PRAD_ERR_INVALID, "prad_add_broadcast_backward: null pointer");
+  if (rows == 0) {
+    if (!accumulate) return prad_zero(ctx, dbias, (size_t)cols * dtype_size(dt));
+    return PRAD_OK;
+  }
+  return DISPATCH_DT(dt, add_broadcast_backward_t<float>(ctx, dy, dbias, rows, cols, accumulate),
+                     add_broadcast_backward_t<double>(ctx, dy, dbias, rows, cols, accumulate));
+}
+
+prad_status prad_scale(prad_ctx* ctx, prad_dtype dt, const void* x, void* y, int64_t n,
+                       double s) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && n >= 0 && (n == 0 || (x && y)), PRAD_ERR_INVALID,
+               "prad_scale: bad argument");
+  const void* in[1] = {x};
+  void* out[1] = {y};
+  return DISPATCH_DT(dt, (launch_map<float, 1, 1>(ctx, in, out, n, Scale<float>{(float)s})),
+                     (launch_map<double, 1, 1>(ctx, in, out, n, Scale<double>{s})));
+}
+
+prad_status prad_transpose(prad_ctx* ctx, prad_dtype dt, const void* x, void* y, int rows,
+                           int cols, int depth) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0 && depth >= 0, PRAD_ERR_INVALID,
+               "prad_transpose: bad argument");
+  if ((int64_t)rows * cols * depth == 0) return PRAD_OK;
+  PRAD_REQUIRE(x && y && x != y, PRAD_ERR_INVALID, "prad_transpose: null or aliased pointers");
+  PRAD_REQUIRE(depth <= 65535 && ceil_div(rows, 32) <= 65535, PRAD_ERR_UNSUPPORTED,
+               "prad_transpose: too many slices or rows for one launch");
+  dim3 grid((unsigned)ceil_div(cols, 32), (unsigned)ceil_div(rows, 32), (unsigned)depth), blk(32, 8);
+  if (dt == PRAD_F32) transpose_kernel<float><<<grid, blk, 0, ctx->stream>>>((const float*)x, (float*)y, rows, cols);
+  else transpose_kernel<double><<<grid, blk, 0, ctx->stream>>>((const double*)x, (double*)y, rows, cols);
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
+
+prad_status prad_segmented_sum(prad_ctx* ctx, prad_dtype dt, const void* const* srcs_host,
+                               int count, void* out, int64_t n) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && count >= 1 && n >= 0 && srcs_host && (out || n == 0),
+               PRAD_ERR_INVALID, "prad_segmented_sum: bad argument");
+  for (int i = 0; i < count; ++i)
+    PRAD_REQUIRE(srcs_host[i] || n == 0, PRAD_ERR_INVALID, "prad_segmented_sum: source %d is null", i);
+  return DISPATCH_DT(dt, nary_t<float>(ctx, srcs_host, count, out, n, 0),
+                     nary_t<double>(ctx, srcs_host, count, out, n, 0));
+}
+
+prad_status prad_batch_mean(prad_ctx* ctx, prad_dtype dt, const void* const* srcs_host,
+                            int count, void* out, int64_t n) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && count >= 1 && n >= 0 && srcs_host && (out || n == 0),
+               PRAD_ERR_INVALID, "prad_batch_mean: bad argument");
+  for (int i = 0; i < count; ++i)
+    PRAD_REQUIRE(srcs_host[i] || n == 0, PRAD_ERR_INVALID, "prad_batch_mean: source %d is null", i);
+  return DISPATCH_DT(dt, nary_t<float>(ctx, srcs_host, count, out, n, 1),
+                     nary_t<double>(ctx, srcs_host, count, out, n, 1));
+}
+
+prad_status prad_accumulate(prad_ctx* ctx, prad_dtype dt, void* dest, const void* src,
+                            int64_t n) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && n >= 0 && (n == 0 || (dest && src)), PRAD_ERR_INVALID,
+               "prad_accumulate: bad argument");
+  const void* in[2] = {dest, src};
+  void* out[1] = {dest};
+  return DISPATCH_DT(dt, (launch_map<float, 2, 1>(ctx, in, out, n, Accum<float>{})),
+                     (launch_map<double, 2, 1>(ctx, in, out, n, Accum<double>{})));
+}
+
+}  // extern "C"

@@ -1,0 +1,294 @@
+// SIMT GEMM family (FP32 FMA / FP64 DFMA): C = alpha*op(A)*op(B) + beta*C, row-major,
+// any M/N/K, strided-batched, with the fused epilogues of the backward path.
+//
+// This is the always-correct variant: it computes every product in the storage precision
+// with FMA accumulation, for all transpose forms the backward needs
+//   NN  C = A*B          MatrixMultiplyOperation.Forward   (MatrixMultiplyOperation.cs:50-80)
+//   NT  dA = dC*B^T      MatrixMultiplyOperation.Backward  (:94-104)
+//   TN  dB = A^T*dC      MatrixMultiplyOperation.Backward  (:110-120)
+// Register-tiled: a CTA owns a BM x BN tile, every thread a TM x TN sub-tile made of
+// VEC-wide chunks so that shared-memory reads are 128-bit and conflict free; operand
+// tiles are staged through registers (global -> reg -> smem) so the next tile's loads
+// are in flight while the current one is multiplied.
+#include "act_math.cuh"
+#include "common.cuh"
+
+namespace prad {
+
+template <typename T> struct VecOf;
+template <> struct VecOf<float> { using type = float4; static constexpr int N = 4; };
+template <> struct VecOf<double> { using type = double2; static constexpr int N = 2; };
+
+template <typename T> struct EpiParams {
+  const T* bias;
+  T* z_out;
+  int act;
+  int dact;
+  const T* saved;
+  T act_alpha;
+};
+
+// Tile loader.  The logical operand tile is ROWS(mn) x BK(k); in memory either the k index
+// is contiguous (K_CONTIG) or the mn index is.  Shared layout is always [BK][ROWS + PAD].
+template <typename T, int ROWS, int BK, int NT, bool K_CONTIG>
+struct TileLoader {
+  static constexpr int VEC = VecOf<T>::N;
+  using V = typename VecOf<T>::type;
+  static constexpr int VECS = ROWS * BK / VEC;
+  static constexpr int PER_THREAD = (VECS + NT - 1) / NT;
+  T regs[PER_THREAD][VEC];
+
+  // mn0: first mn index of the tile, k0: first k index; MN, K: operand extents
+  __device__ __forceinline__ void load(const T* __restrict__ p, int64_t ld, int mn0, int k0,
+                                       int MN, int K, bool vec_ok, int tid) {
+#pragma unroll
+    for (int it = 0; it < PER_THREAD; ++it) {
+      int idx = tid + it * NT;
+      if (VECS % NT != 0 && idx >= VECS) break;
+      int r, c;  // r: slow index in memory, c: fast (contiguous) index, both tile-local
+      if (K_CONTIG) {
+        r = idx / (BK / VEC);
+        c = (idx % (BK / VEC)) * VEC;
+      } else {
+        r = idx / (ROWS / VEC);
+        c = (idx % (ROWS / VEC)) * VEC;
+      }
+      int mn = K_CONTIG ? mn0 + r : mn0 + c;
+      int k = K_CONTIG ? k0 + c : k0 + r;
+      int slow = K_CONTIG ? mn : k, fast = K_CONTIG ? k : mn;
+      int slow_lim = K_CONTIG ? MN : K, fast_lim = K_CONTIG ? K : MN;
+      const T* src = p + (int64_t)slow * ld + fast;
+      if (slow < slow_lim && fast + VEC <= fast_lim && vec_ok) {
+        V v = *reinterpret_cast<const V*>(src);
+        const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) regs[it][q] = e[q];
+      } else {
+#pragma unroll
+        for (int q = 0; q < VEC; ++q)
+          regs[it][q] = (slow < slow_lim && fast + q < fast_lim) ? src[q] : (T)0;
+      }
+    }
+  }
+
+  template <int LDS>
+  __device__ __forceinline__ void store(T (*sm)[LDS], int tid) {
+#pragma unroll
+    for (int it = 0; it < PER_THREAD; ++it) {
+      int idx = tid + it * NT;
+      if (VECS % NT != 0 && idx >= VECS) break;
+      if (K_CONTIG) {
+        int r = idx / (BK / VEC);
+        int c = (idx % (BK / VEC)) * VEC;
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) sm[c + q][r] = regs[it][q];
+      } else {
+        int r = idx / (ROWS / VEC);
+        int c = (idx % (ROWS / VEC)) * VEC;
+        V v;
+        T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) e[q] = regs[it][q];
+        *reinterpret_cast<V*>(&sm[r][c]) = v;
+      }
+    }
+  }
+};
+
+template <typename T, int BM, int BN, int BK, int TM, int TN, bool TA, bool TB>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+gemm_simt_kernel(int M, int N, int K, T alpha, const T* __restrict__ A, int64_t lda,
+                 const T* __restrict__ B, int64_t ldb, T beta, T* __restrict__ C, int64_t ldc,
+                 int64_t sA, int64_t sB, int64_t sC, bool vecA, bool vecB, bool vecC,
+                 EpiParams<T> epi) {
+  constexpr int VEC = VecOf<T>::N;
+  using V = typename VecOf<T>::type;
+  constexpr int NT = (BM / TM) * (BN / TN);
+  constexpr int TX = BN / TN;  // threads along n
+  constexpr int CM = TM / VEC, CN = TN / VEC;  // chunks per thread
+  constexpr int PAD = VEC;                     // keeps rows 16-byte aligned
+  static_assert(TM % VEC == 0 && TN % VEC == 0, "thread tile must be made of vectors");
+
+  __shared__ __align__(16) T As[2][BK][BM + PAD];
+  __shared__ __align__(16) T Bs[2][BK][BN + PAD];
+
+  const int tid = threadIdx.x;
+  const int tx = tid % TX, ty = tid / TX;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int64_t bz = blockIdx.z;
+  A += bz * sA;
+  B += bz * sB;
+  C += bz * sC;
+  const T* saved = epi.saved ? epi.saved + bz * sC : nullptr;
+  T* z_out = epi.z_out ? epi.z_out + bz * sC : nullptr;
+
+  // op(A) is M x K: memory has k contiguous when !TA.  op(B) is K x N: memory has k
+  // contiguous when TB.
+  TileLoader<T, BM, BK, NT, !TA> la;
+  TileLoader<T, BN, BK, NT, TB> lb;
+
+  T acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = (T)0;
+
+  const int ktiles = (K + BK - 1) / BK;
+  la.load(A, lda, m0, 0, M, K, vecA, tid);
+  lb.load(B, ldb, n0, 0, N, K, vecB, tid);
+  la.store(As[0], tid);
+  lb.store(Bs[0], tid);
+  __syncthreads();
+
+  for (int kt = 0; kt < ktiles; ++kt) {
+    const int cur = kt & 1;
+    if (kt + 1 < ktiles) {
+      la.load(A, lda, m0, (kt + 1) * BK, M, K, vecA, tid);
+      lb.load(B, ldb, n0, (kt + 1) * BK, N, K, vecB, tid);
+    }
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      T a[TM], b[TN];
+#pragma unroll
+      for (int c = 0; c < CM; ++c) {
+        V v = *reinterpret_cast<const V*>(&As[cur][k][c * (BM / CM) + ty * VEC]);
+        const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) a[c * VEC + q] = e[q];
+      }
+#pragma unroll
+      for (int c = 0; c < CN; ++c) {
+        V v = *reinterpret_cast<const V*>(&Bs[cur][k][c * (BN / CN) + tx * VEC]);
+        const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) b[c * VEC + q] = e[q];
+      }
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = fma(a[i], b[j], acc[i][j]);
+    }
+    if (kt + 1 < ktiles) {
+      la.store(As[cur ^ 1], tid);
+      lb.store(Bs[cur ^ 1], tid);
+    }
+    __syncthreads();
+  }
+
+  // epilogue
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int m = m0 + (i / VEC) * (BM / CM) + ty * VEC + (i % VEC);
+    if (m >= M) continue;
+#pragma unroll
+    for (int c = 0; c < CN; ++c) {
+      const int n = n0 + c * (BN / CN) + tx * VEC;
+      if (n >= N) continue;
+      T out[VEC];
+      const int64_t off = (int64_t)m * ldc + n;
+      const bool full = vecC && (n + VEC <= N);
+      T old[VEC];
+      if (beta != (T)0) {
+        if (full) {
+          V v = *reinterpret_cast<const V*>(C + off);
+          const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+          for (int q = 0; q < VEC; ++q) old[q] = e[q];
+        } else {
+#pragma unroll
+          for (int q = 0; q < VEC; ++q) old[q] = (n + q < N) ? C[off + q] : (T)0;
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) {
+        T v = alpha * acc[i][c * VEC + q];
+        if (beta != (T)0) v = fma(beta, old[q], v);
+        if (n + q < N) {
+          if (epi.bias) v += epi.bias[n + q];
+          if (z_out) z_out[off + q] = v;
+          if (epi.act != PRAD_ACT_NONE) v = act_value<T>((prad_act)epi.act, v, epi.act_alpha);
+          if (epi.dact != PRAD_ACT_NONE)
+            v = mul_rn(v, act_derivative<T>((prad_act)epi.dact, saved[off + q], epi.act_alpha));
+        }
+        out[q] = v;
+      }
+      if (full) {
+        V v;
+        T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) e[q] = out[q];
+        *reinterpret_cast<V*>(C + off) = v;
+      } else {
+#pragma unroll
+        for (int q = 0; q < VEC; ++q)
+          if (n + q < N) C[off + q] = out[q];
+      }
+    }
+  }
+}
+
+template <typename T> static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+template <typename T, int BM, int BN, int BK, int TM, int TN>
+static prad_status launch_cfg(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, T alpha,
+                              const T* A, int64_t lda, const T* B, int64_t ldb, T beta, T* C,
+                              int64_t ldc, int batch, int64_t sA, int64_t sB, int64_t sC,
+                              const EpiParams<T>& epi) {
+  constexpr int VEC = VecOf<T>::N;
+  constexpr int NT = (BM / TM) * (BN / TN);
+  dim3 grid((unsigned)ceil_div(N, BN), (unsigned)ceil_div(M, BM), (unsigned)batch);
+  PRAD_REQUIRE(grid.y <= 65535 && grid.z <= 65535, PRAD_ERR_UNSUPPORTED,
+               "gemm: grid too large (M tiles %u, batch %u)", grid.y, grid.z);
+  bool vA = aligned16<T>(A) && lda % VEC == 0 && sA % VEC == 0;
+  bool vB = aligned16<T>(B) && ldb % VEC == 0 && sB % VEC == 0;
+  bool vC = aligned16<T>(C) && ldc % VEC == 0 && sC % VEC == 0;
+#define PRAD_GEMM_LAUNCH(TA_, TB_)                                                           \
+  gemm_simt_kernel<T, BM, BN, BK, TM, TN, TA_, TB_><<<grid, NT, 0, ctx->stream>>>(           \
+      M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, sA, sB, sC, vA, vB, vC, epi)
+  if (!tA && !tB) PRAD_GEMM_LAUNCH(false, false);
+  else if (!tA && tB) PRAD_GEMM_LAUNCH(false, true);
+  else if (tA && !tB) PRAD_GEMM_LAUNCH(true, false);
+  else PRAD_GEMM_LAUNCH(true, true);
+#undef PRAD_GEMM_LAUNCH
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
+
+template <typename T>
+prad_status gemm_simt(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, double alpha,
+                      const void* A, int lda, const void* B, int ldb, double beta, void* C,
+                      int ldc, int batch, int64_t sA, int64_t sB, int64_t sC,
+                      const GemmEpilogue& e) {
+  EpiParams<T> epi{(const T*)e.bias, (T*)e.z_out, (int)e.act, (int)e.dact, (const T*)e.saved,
+                   (T)e.act_alpha};
+  // tile choice: big tiles when the output fills the machine, small ones otherwise
+  int64_t big_tiles = ceil_div(M, 128) * ceil_div(N, 128) * batch;
+  const bool use_big = big_tiles >= ctx->sm_count && M >= 96 && N >= 96;
+  if constexpr (sizeof(T) == 4) {
+    if (use_big)
+      return launch_cfg<T, 128, 128, 16, 8, 8>(ctx, tA, tB, M, N, K, (T)alpha, (const T*)A, lda,
+                                               (const T*)B, ldb, (T)beta, (T*)C, ldc, batch, sA,
+                                               sB, sC, epi);
+    return launch_cfg<T, 64, 64, 16, 4, 4>(ctx, tA, tB, M, N, K, (T)alpha, (const T*)A, lda,
+                                           (const T*)B, ldb, (T)beta, (T*)C, ldc, batch, sA, sB,
+                                           sC, epi);
+  } else {
+    int64_t t64 = ceil_div(M, 64) * ceil_div(N, 64) * batch;
+    if (t64 >= ctx->sm_count && M >= 48 && N >= 48)
+      return launch_cfg<T, 64, 64, 16, 4, 4>(ctx, tA, tB, M, N, K, (T)alpha, (const T*)A, lda,
+                                             (const T*)B, ldb, (T)beta, (T*)C, ldc, batch, sA,
+                                             sB, sC, epi);
+    return launch_cfg<T, 32, 32, 16, 2, 2>(ctx, tA, tB, M, N, K, (T)alpha, (const T*)A, lda,
+                                           (const T*)B, ldb, (T)beta, (T*)C, ldc, batch, sA, sB,
+                                           sC, epi);
+  }
+}
+
+template prad_status gemm_simt<float>(prad_ctx*, bool, bool, int, int, int, double, const void*,
+                                      int, const void*, int, double, void*, int, int, int64_t,
+                                      int64_t, int64_t, const GemmEpilogue&);
+template prad_status gemm_simt<double>(prad_ctx*, bool, bool, int, int, int, double,
+                                       const void*, int, const void*, int, double, void*, int,
+                                       int, int64_t, int64_t, int64_t, const GemmEpilogue&);
+
+}  // namespace prad

@@ -1,0 +1,273 @@
+// Loss values and loss gradients (MSE, categorical cross-entropy) and the embedding
+// gather / ordered scatter-add.  (Compiled with -fmad=false.)
+#include "act_math.cuh"
+#include "common.cuh"
+#include "reduce.cuh"
+
+namespace prad {
+
+template <typename T> struct Eps15;
+template <> struct Eps15<float> { __device__ static float v() { return 1e-15f; } };   // lite PradTools.Epsilon
+template <> struct Eps15<double> { __device__ static double v() { return 1e-15; } };  // PradTools.Epsilon
+
+constexpr int LOSS_THREADS = 256;
+
+// kind 0: MSE term (o-t)^2 (MeanSquaredErrorLossOperation.cs:50-55)
+// kind 1: CCE term -t*log(o+eps) (CategoricalCrossEntropyLossOperation.cs:53-59)
+template <typename T>
+__global__ void __launch_bounds__(LOSS_THREADS)
+loss_partial_kernel(const T* __restrict__ o, const T* __restrict__ t, double* __restrict__ partial,
+                    int64_t n, int kind) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  double acc = 0.0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    T term;
+    if (kind == 0) {
+      T d = sub_rn(o[i], t[i]);
+      term = mul_rn(d, d);
+    } else {
+      term = mul_rn(-t[i], t_log(add_rn(o[i], Eps15<T>::v())));
+    }
+    acc += (double)term;
+  }
+  double s = block_sum_d<LOSS_THREADS>(acc);
+  if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+template <typename T>
+__global__ void loss_final_kernel(const double* __restrict__ partial, int nblocks, T* loss,
+                                  T divisor) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    double s = 0.0;
+    for (int b = 0; b < nblocks; ++b) s += partial[b];
+    loss[0] = div_rn((T)s, divisor);
+  }
+}
+
+// MeanSquaredErrorLossOperation.cs:71-78: grad = (2/(R*C)) * (o - t)
+template <typename T>
+__global__ void __launch_bounds__(256)
+mse_backward_kernel(const T* __restrict__ o, const T* __restrict__ t, T* __restrict__ g, int64_t n,
+                    T scale) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    g[i] = mul_rn(scale, sub_rn(o[i], t[i]));
+}
+// CategoricalCrossEntropyLossOperation.cs:72-83: grad = -scale*y / (yHat + eps)
+template <typename T>
+__global__ void __launch_bounds__(256)
+cce_backward_kernel(const T* __restrict__ o, const T* __restrict__ t, T* __restrict__ g, int64_t n,
+                    T scale) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    g[i] = div_rn(mul_rn(-scale, t[i]), add_rn(o[i], Eps15<T>::v()));
+}
+
+template <typename T>
+static prad_status loss_forward_t(prad_ctx* ctx, const void* o, const void* t, void* loss,
+                                  int64_t rows, int cols, int kind) {
+  int64_t n = rows * cols;
+  int grid = stream_grid(ctx, n, LOSS_THREADS * 4, 4);
+  prad_status s = ensure_workspace(ctx, (size_t)grid * sizeof(double));
+  if (s) return s;
+  loss_partial_kernel<T><<<grid, LOSS_THREADS, 0, ctx->stream>>>((const T*)o, (const T*)t,
+                                                                  (double*)ctx->ws, n, kind);
+  PRAD_LAUNCHED(ctx);
+  T divisor = kind == 0 ? (T)(rows * cols) : (T)rows;
+  loss_final_kernel<T><<<1, 32, 0, ctx->stream>>>((const double*)ctx->ws, grid, (T*)loss, divisor);
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
+
+// ---------------------------------------------------------------- embedding
+// EmbeddingOperation.cs:56-60: out[i] = W[(int)input[i,0]]
+template <typename T>
+__global__ void __launch_bounds__(256)
+embedding_gather_kernel(const T* __restrict__ index_col, const T* __restrict__ W,
+                        T* __restrict__ out, int n, int vocab, int dim, int* __restrict__ bad) {
+  for (int i = blockIdx.x; i < n; i += gridDim.x) {
+    int idx = (int)index_col[i];
+    if (idx < 0 || idx >= vocab) {  // the managed code would throw IndexOutOfRange
+      if (threadIdx.x == 0) atomicExch(bad, i + 1);
+      continue;
+    }
+    for (int j = threadIdx.x; j < dim; j += blockDim.x)
+      out[(int64_t)i * dim + j] = W[(int64_t)idx * dim + j];
+  }
+}
+
+// EmbeddingOperation.cs:69-76: dW[idx[i]][j] += dOut[i][j] for i = 0..n-1 IN THAT ORDER.
+// Vocabulary rows are dealt to CTAs round-robin.  A CTA scans the index column in tiles,
+// compacts (stably) the positions whose row it owns, and adds those rows of dOut one after
+// the other; column j is always handled by the same thread, so every dW element sees its
+// contributions in input-row order and the sum is bit-identical to the sequential loop.
+// No floating-point atomics anywhere.
+constexpr int EMB_THREADS = 256;
+constexpr int EMB_ITEMS = 4;
+constexpr int EMB_TILE = EMB_THREADS * EMB_ITEMS;
+
+template <typename T>
+__global__ void __launch_bounds__(EMB_THREADS)
+embedding_scatter_ordered_kernel(const T* __restrict__ index_col, const T* __restrict__ dOut,
+                                 T* __restrict__ dW, int n, int vocab, int dim,
+                                 int* __restrict__ bad) {
+  __shared__ int list[EMB_TILE];
+  __shared__ int warp_cnt[EMB_THREADS / 32];
+  __shared__ int tile_cnt;
+  const int B = gridDim.x, b = blockIdx.x;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+
+  for (int v = b; v < vocab; v += B)
+    for (int j = threadIdx.x; j < dim; j += EMB_THREADS) dW[(int64_t)v * dim + j] = (T)0;
+  __syncthreads();
+
+  for (int tile = 0; tile < n; tile += EMB_TILE) {
+    int mine[EMB_ITEMS];
+    int c = 0;
+#pragma unroll
+    for (int q = 0; q < EMB_ITEMS; ++q) {
+      int i = tile + threadIdx.x * EMB_ITEMS + q;
+      mine[q] = -1;
+      if (i < n) {
+        int idx = (int)index_col[i];
+        if (idx < 0 || idx >= vocab) {
+          if (b == 0) atomicExch(bad, i + 1);
+        } else if (idx % B == b) {
+          mine[q] = i;
+          ++c;
+        }
+      }
+    }
+    // exclusive scan of c over the block (thread order == element order)
+    int incl = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int u = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += u;
+    }
+    if (lane == 31) warp_cnt[w] = incl;
+    __syncthreads();
+    int base = 0;
+    for (int k = 0; k < w; ++k) base += warp_cnt[k];
+    if (threadIdx.x == EMB_THREADS - 1) tile_cnt = base + incl;
+    int pos = base + incl - c;
+#pragma unroll
+    for (int q = 0; q < EMB_ITEMS; ++q)
+      if (mine[q] >= 0) list[pos++] = mine[q];
+    __syncthreads();
+    const int cnt = tile_cnt;
+    for (int e = 0; e < cnt; ++e) {
+      const int i = list[e];
+      const int idx = (int)index_col[i];
+      for (int j = threadIdx.x; j < dim; j += EMB_THREADS) {
+        const int64_t o = (int64_t)idx * dim + j;
+        dW[o] = add_rn(dW[o], dOut[(int64_t)i * dim + j]);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+static prad_status check_bad_index(prad_ctx* ctx, int* d_bad, const char* who) {
+  int h = 0;
+  PRAD_CUDA(cudaMemcpyAsync(&h, d_bad, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+  PRAD_CUDA(cudaStreamSynchronize(ctx->stream));
+  PRAD_REQUIRE(h == 0, PRAD_ERR_INVALID, "%s: index at input row %d is outside [0, vocab)", who, h - 1);
+  return PRAD_OK;
+}
+
+}  // namespace prad
+
+using namespace prad;
+
+extern "C" {
+
+prad_status prad_mse_forward(prad_ctx* ctx, prad_dtype dt, const void* out, const void* target,
+                             void* loss_out, int64_t rows, int cols) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && rows > 0 && cols > 0 && out && target && loss_out, PRAD_ERR_INVALID,
+               "prad_mse_forward: bad argument");
+  return dt == PRAD_F32 ? loss_forward_t<float>(ctx, out, target, loss_out, rows, cols, 0)
+                        : loss_forward_t<double>(ctx, out, target, loss_out, rows, cols, 0);
+}
+
+prad_status prad_cce_forward(prad_ctx* ctx, prad_dtype dt, const void* out, const void* target,
+                             void* loss_out, int64_t rows, int cols) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && rows > 0 && cols > 0 && out && target && loss_out, PRAD_ERR_INVALID,
+               "prad_cce_forward: bad argument");
+  return dt == PRAD_F32 ? loss_forward_t<float>(ctx, out, target, loss_out, rows, cols, 1)
+                        : loss_forward_t<double>(ctx, out, target, loss_out, rows, cols, 1);
+}
+
+prad_status prad_mse_backward(prad_ctx* ctx, prad_dtype dt, const void* out, const void* target,
+                              void* grad, int64_t rows, int cols, int64_t rows_total) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0 && rows_total >= rows, PRAD_ERR_INVALID,
+               "prad_mse_backward: bad argument");
+  int64_t n = rows * cols;
+  if (n == 0) return PRAD_OK;
+  PRAD_REQUIRE(out && target && grad, PRAD_ERR_INVALID, "prad_mse_backward: null pointer");
+  int grid = stream_grid(ctx, n, 256 * 4, 8);
+  if (dt == PRAD_F32)
+    mse_backward_kernel<float><<<grid, 256, 0, ctx->stream>>>((const float*)out, (const float*)target, (float*)grad, n, 2.0f / (float)(rows_total * cols));
+  else
+    mse_backward_kernel<double><<<grid, 256, 0, ctx->stream>>>((const double*)out, (const double*)target, (double*)grad, n, 2.0 / (double)(rows_total * cols));
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
+
+prad_status prad_cce_backward(prad_ctx* ctx, prad_dtype dt, const void* out, const void* target,
+                              void* grad, int64_t rows, int cols, int64_t rows_total) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0 && rows_total >= rows, PRAD_ERR_INVALID,
+               "prad_cce_backward: bad argument");
+  int64_t n = rows * cols;
+  if (n == 0) return PRAD_OK;
+  PRAD_REQUIRE(out && target && grad, PRAD_ERR_INVALID, "prad_cce_backward: null pointer");
+  int grid = stream_grid(ctx, n, 256 * 4, 8);
+  if (dt == PRAD_F32)
+    cce_backward_kernel<float><<<grid, 256, 0, ctx->stream>>>((const float*)out, (const float*)target, (float*)grad, n, 1.0f / (float)rows_total);
+  else
+    cce_backward_kernel<double><<<grid, 256, 0, ctx->stream>>>((const double*)out, (const double*)target, (double*)grad, n, 1.0 / (double)rows_total);
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
+
+prad_status prad_embedding_forward(prad_ctx* ctx, prad_dtype dt, const void* index_col,
+                                   const void* W, void* out, int n, int vocab, int dim) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && n >= 0 && vocab >= 0 && dim >= 0, PRAD_ERR_INVALID,
+               "prad_embedding_forward: bad argument");
+  if (n == 0 || dim == 0) return PRAD_OK;
+  PRAD_REQUIRE(index_col && W && out, PRAD_ERR_INVALID, "prad_embedding_forward: null pointer");
+  prad_status s = ensure_workspace(ctx, 256);
+  if (s) return s;
+  int* bad = (int*)ctx->ws;
+  PRAD_CUDA(cudaMemsetAsync(bad, 0, sizeof(int), ctx->stream));
+  int grid = stream_grid(ctx, n, 1, 8);
+  if (dt == PRAD_F32) embedding_gather_kernel<float><<<grid, 256, 0, ctx->stream>>>((const float*)index_col, (const float*)W, (float*)out, n, vocab, dim, bad);
+  else embedding_gather_kernel<double><<<grid, 256, 0, ctx->stream>>>((const double*)index_col, (const double*)W, (double*)out, n, vocab, dim, bad);
+  PRAD_LAUNCHED(ctx);
+  return check_bad_index(ctx, bad, "prad_embedding_forward");
+}
+
+prad_status prad_embedding_backward(prad_ctx* ctx, prad_dtype dt, const void* index_col,
+                                    const void* dOut, void* dW, int n, int vocab, int dim) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && n >= 0 && vocab >= 0 && dim >= 0, PRAD_ERR_INVALID,
+               "prad_embedding_backward: bad argument");
+  if (vocab == 0 || dim == 0) return PRAD_OK;
+  PRAD_REQUIRE(dW && (n == 0 || (index_col && dOut)), PRAD_ERR_INVALID,
+               "prad_embedding_backward: null pointer");
+  prad_status s = ensure_workspace(ctx, 256);
+  if (s) return s;
+  int* bad = (int*)ctx->ws;
+  PRAD_CUDA(cudaMemsetAsync(bad, 0, sizeof(int), ctx->stream));
+  int grid = vocab < ctx->sm_count * 8 ? vocab : ctx->sm_count * 8;
+  if (dt == PRAD_F32) embedding_scatter_ordered_kernel<float><<<grid, EMB_THREADS, 0, ctx->stream>>>((const float*)index_col, (const float*)dOut, (float*)dW, n, vocab, dim, bad);
+  else embedding_scatter_ordered_kernel<double><<<grid, EMB_THREADS, 0, ctx->stream>>>((const double*)index_col, (const double*)dOut, (double*)dW, n, vocab, dim, bad);
+  PRAD_LAUNCHED(ctx);
+  return check_bad_index(ctx, bad, "prad_embedding_backward");
+}
+
+}  // extern "C"

@@ -1,0 +1,500 @@
+"""Thin object layer over the C ABI: a context (``Engine``) and device-resident matrices.
+
+Nothing here computes: every method forwards to one ``prad_*`` entry point of
+``libprad_cuda.so``.  numpy arrays only appear at the upload / download boundary.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Iterable, Optional, Sequence
+
+import numpy as np
+
+from . import _lib
+from ._lib import check
+
+F32, F64 = 0, 1
+ACT_NONE, ACT_LEAKY_RELU, ACT_SIGMOID, ACT_TANH, ACT_GELU = range(5)
+ADAM_RMAD, ADAM_PRAD = 0, 1
+CLIP_NONE, CLIP_REFERENCE, CLIP_GLOBAL_NORM = 0, 1, 2
+
+_DT = {np.dtype(np.float32): F32, np.dtype(np.float64): F64}
+
+
+def dtype_code(dtype) -> int:
+    try:
+        return _DT[np.dtype(dtype)]
+    except KeyError:
+        raise TypeError(f"only float32 (PRADLite) and float64 (PRAD) are supported, got {dtype}")
+
+
+class DeviceMatrix:
+    """A dense row-major device buffer: Matrix (2-D) or DeepMatrix (3-D, depth first)."""
+
+    __slots__ = ("engine", "ptr", "shape", "dtype", "_owned")
+
+    def __init__(self, engine: "Engine", ptr: int, shape: Sequence[int], dtype, owned=True):
+        self.engine = engine
+        self.ptr = ptr
+        self.shape = tuple(int(s) for s in shape)
+        self.dtype = np.dtype(dtype)
+        self._owned = owned
+
+    @property
+    def size(self) -> int:
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n
+
+    @property
+    def nbytes(self) -> int:
+        return self.size * self.dtype.itemsize
+
+    @property
+    def Rows(self) -> int:
+        return self.shape[-2]
+
+    @property
+    def Cols(self) -> int:
+        return self.shape[-1]
+
+    @property
+    def Depth(self) -> int:
+        return self.shape[0] if len(self.shape) == 3 else 1
+
+    def numpy(self) -> np.ndarray:
+        return self.engine.download(self)
+
+    def view(self, shape: Sequence[int], offset_elems: int = 0) -> "DeviceMatrix":
+        """A non-owning alias of (part of) this buffer with another shape."""
+        return DeviceMatrix(self.engine, self.ptr + offset_elems * self.dtype.itemsize, shape,
+                            self.dtype, owned=False)
+
+    def slice(self, d: int) -> "DeviceMatrix":
+        """Slice d of a DeepMatrix as a Matrix (alias)."""
+        per = self.shape[-2] * self.shape[-1]
+        return self.view(self.shape[-2:], d * per)
+
+    def free(self) -> None:
+        if self._owned and self.ptr and self.engine is not None and self.engine.ctx:
+            self.engine._free(self.ptr)
+        self.ptr = 0
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Engine:
+    """One libprad_cuda context on one GPU (CudaBlas.Instance of the reference, per device)."""
+
+    def __init__(self, device: int = 0):
+        self.lib = _lib.load()
+        ctx = C.c_void_p()
+        check(self.lib.prad_init(int(device), C.byref(ctx)))
+        self.ctx = ctx
+        self.device = device
+
+    # ------------------------------------------------------------ lifecycle
+    def close(self) -> None:
+        if self.ctx:
+            check(self.lib.prad_shutdown(self.ctx))
+            self.ctx = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def sync(self) -> None:
+        check(self.lib.prad_sync(self.ctx))
+
+    def set_option(self, key: str, value: str) -> None:
+        check(self.lib.prad_set_option(self.ctx, key.encode(), value.encode()))
+
+    def launch_count(self) -> int:
+        n = C.c_int64()
+        check(self.lib.prad_launch_count(self.ctx, C.byref(n)))
+        return n.value
+
+    def stream(self) -> int:
+        s = C.c_void_p()
+        check(self.lib.prad_stream(self.ctx, C.byref(s)))
+        return s.value or 0
+
+    def use_stream(self, stream: int) -> None:
+        check(self.lib.prad_use_stream(self.ctx, C.c_void_p(stream)))
+
+    # ------------------------------------------------------------ memory
+    def empty(self, shape, dtype) -> DeviceMatrix:
+        dtype = np.dtype(dtype)
+        dtype_code(dtype)
+        shape = (shape,) if isinstance(shape, int) else tuple(shape)
+        n = 1
+        for s in shape:
+            n *= int(s)
+        p = C.c_void_p()
+        check(self.lib.prad_alloc(self.ctx, n * dtype.itemsize, C.byref(p)))
+        return DeviceMatrix(self, p.value, shape, dtype)
+
+    def zeros(self, shape, dtype) -> DeviceMatrix:
+        m = self.empty(shape, dtype)
+        check(self.lib.prad_zero(self.ctx, m.ptr, m.nbytes))
+        return m
+
+    def zero_(self, m: DeviceMatrix) -> None:
+        check(self.lib.prad_zero(self.ctx, m.ptr, m.nbytes))
+
+    def _free(self, ptr: int) -> None:
+        check(self.lib.prad_free(self.ctx, C.c_void_p(ptr)))
+
+    def upload(self, a: np.ndarray, out: Optional[DeviceMatrix] = None) -> DeviceMatrix:
+        a = np.ascontiguousarray(a)
+        if out is None:
+            out = self.empty(a.shape, a.dtype)
+        assert out.nbytes == a.nbytes
+        check(self.lib.prad_upload(self.ctx, out.ptr, a.ctypes.data, a.nbytes))
+        # pageable host memory: the copy has consumed `a` when the call returns
+        return out
+
+    def upload_rows(self, rows: Sequence[np.ndarray]) -> DeviceMatrix:
+        """Jagged upload: one host array per matrix row (the reference's T[rows][cols])."""
+        rows = [np.ascontiguousarray(r) for r in rows]
+        out = self.empty((len(rows), rows[0].size), rows[0].dtype)
+        ptrs = (C.c_void_p * len(rows))(*[r.ctypes.data for r in rows])
+        check(self.lib.prad_upload_rows(self.ctx, out.ptr, ptrs, len(rows), rows[0].nbytes))
+        self.sync()
+        return out
+
+    def download(self, m: DeviceMatrix) -> np.ndarray:
+        out = np.empty(m.shape, m.dtype)
+        check(self.lib.prad_download(self.ctx, out.ctypes.data, m.ptr, m.nbytes))
+        return out
+
+    def download_rows(self, m: DeviceMatrix):
+        rows = [np.empty(m.shape[1], m.dtype) for _ in range(m.shape[0])]
+        ptrs = (C.c_void_p * len(rows))(*[r.ctypes.data for r in rows])
+        check(self.lib.prad_download_rows(self.ctx, ptrs, m.ptr, len(rows), rows[0].nbytes))
+        return rows
+
+    def copy(self, dst: DeviceMatrix, src: DeviceMatrix) -> None:
+        assert dst.nbytes == src.nbytes
+        check(self.lib.prad_copy(self.ctx, dst.ptr, src.ptr, src.nbytes))
+
+    def clone(self, src: DeviceMatrix) -> DeviceMatrix:
+        out = self.empty(src.shape, src.dtype)
+        self.copy(out, src)
+        return out
+
+    # ------------------------------------------------------------ helpers
+    @staticmethod
+    def _p(m: Optional[DeviceMatrix]):
+        return C.c_void_p(m.ptr) if m is not None else None
+
+    @staticmethod
+    def _ptr_list(ms: Iterable[DeviceMatrix]):
+        ms = list(ms)
+        return (C.c_void_p * len(ms))(*[m.ptr for m in ms])
+
+    @staticmethod
+    def _size_list(ms: Iterable[DeviceMatrix]):
+        ms = list(ms)
+        return (C.c_int64 * len(ms))(*[m.size for m in ms])
+
+    # ------------------------------------------------------------ GEMM family
+    def gemm(self, A, B, Cm, transA=False, transB=False, alpha=1.0, beta=0.0, M=None, N=None,
+             K=None, lda=None, ldb=None, ldc=None, batch=1, strideA=0, strideB=0, strideC=0):
+        dt = dtype_code(A.dtype)
+        if M is None:
+            M = A.shape[-1] if transA else A.shape[-2]
+            K = A.shape[-2] if transA else A.shape[-1]
+            N = B.shape[-2] if transB else B.shape[-1]
+        lda = lda or A.shape[-1]
+        ldb = ldb or B.shape[-1]
+        ldc = ldc or Cm.shape[-1]
+        check(self.lib.prad_gemm(self.ctx, dt, int(transA), int(transB), M, N, K, alpha, A.ptr, lda,
+                                 B.ptr, ldb, beta, Cm.ptr, ldc, batch, strideA, strideB, strideC))
+
+    def matmul_forward(self, A, B, Y=None, bias=None, Z_out=None, act=ACT_NONE, act_alpha=0.0):
+        M, K = A.shape
+        K2, N = B.shape
+        if K != K2:
+            raise _lib.PradError(_lib.ERR_SHAPE, "Input 1 columns do not match Input 2 rows")
+        Y = Y or self.empty((M, N), A.dtype)
+        check(self.lib.prad_matmul_forward(self.ctx, dtype_code(A.dtype), A.ptr, B.ptr, Y.ptr, M, K,
+                                           N, self._p(bias), self._p(Z_out), act, act_alpha))
+        return Y
+
+    def matmul_backward(self, A, B, dC, dA=None, dB=None, need_dA=True, need_dB=True,
+                        accumulate_dB=False, dB_scale=1.0, act_below=ACT_NONE, saved_below=None,
+                        act_alpha=0.0):
+        M, N = dC.shape
+        K = B.shape[0] if B is not None else A.shape[1]
+        if need_dA and dA is None:
+            dA = self.empty((M, K), dC.dtype)
+        if need_dB and dB is None:
+            dB = self.empty((K, N), dC.dtype)
+        check(self.lib.prad_matmul_backward(
+            self.ctx, dtype_code(dC.dtype), self._p(A), self._p(B), dC.ptr,
+            self._p(dA if need_dA else None), self._p(dB if need_dB else None), M, K, N,
+            int(accumulate_dB), dB_scale, act_below, self._p(saved_below), act_alpha))
+        return dA, dB
+
+    def matmul_act_backward(self, A, B, dOut, act, saved, act_alpha=0.0):
+        M, K = A.shape
+        N = B.shape[1]
+        dPre = self.empty((M, N), A.dtype)
+        dA = self.empty((M, K), A.dtype)
+        dB = self.empty((K, N), A.dtype)
+        check(self.lib.prad_matmul_act_backward(self.ctx, dtype_code(A.dtype), A.ptr, B.ptr, dOut.ptr,
+                                                act, self._p(saved), act_alpha, dPre.ptr, dA.ptr,
+                                                dB.ptr, M, K, N))
+        return dPre, dA, dB
+
+    def matmul_act_backward_host(self, A, B, dOut, act, saved, act_alpha=0.0, out=None):
+        """numpy in, numpy out: uploads, computes, downloads inside the one C call."""
+        A = np.ascontiguousarray(A)
+        M, K = A.shape
+        N = B.shape[1]
+        if out is None:
+            out = (np.empty((M, N), A.dtype), np.empty((M, K), A.dtype), np.empty((K, N), A.dtype))
+        dPre, dA, dB = out
+        check(self.lib.prad_matmul_act_backward_host(
+            self.ctx, dtype_code(A.dtype), A.ctypes.data, B.ctypes.data, dOut.ctypes.data, act,
+            saved.ctypes.data if saved is not None else None, act_alpha, dPre.ctypes.data,
+            dA.ctypes.data, dB.ctypes.data, M, K, N))
+        return dPre, dA, dB
+
+    def batch_matmul_forward(self, A, B, Cm=None):
+        depth, M, K = A.shape
+        shared = len(B.shape) == 2
+        N = B.shape[-1]
+        Cm = Cm or self.empty((depth, M, N), A.dtype)
+        check(self.lib.prad_batch_matmul_forward(self.ctx, dtype_code(A.dtype), A.ptr, B.ptr, Cm.ptr,
+                                                 depth, M, K, N, int(shared)))
+        return Cm
+
+    def batch_matmul_backward(self, A, B, dC, per_slice_dB=True, mean_dB=False):
+        depth, M, K = A.shape
+        shared = len(B.shape) == 2
+        N = B.shape[-1]
+        dA = self.empty((depth, M, K), A.dtype)
+        dB = self.empty((depth, K, N), A.dtype) if per_slice_dB else None
+        dBm = self.empty((K, N), A.dtype) if mean_dB else None
+        check(self.lib.prad_batch_matmul_backward(self.ctx, dtype_code(A.dtype), A.ptr, B.ptr, dC.ptr,
+                                                  dA.ptr, self._p(dB), self._p(dBm), depth, M, K,
+                                                  N, int(shared)))
+        return dA, dB, dBm
+
+    def matmul_and_sum_forward(self, A, B):
+        R, Cc = A.shape
+        P, _, N = B.shape
+        out = self.empty((1, P), A.dtype)
+        check(self.lib.prad_matmul_and_sum_forward(self.ctx, dtype_code(A.dtype), A.ptr, B.ptr,
+                                                   out.ptr, R, Cc, N, P))
+        return out
+
+    def matmul_and_sum_backward(self, A, B, dOut):
+        R, Cc = A.shape
+        P, _, N = B.shape
+        dA = self.empty((N, Cc), A.dtype)
+        dB = self.empty((P, Cc, R), A.dtype)
+        check(self.lib.prad_matmul_and_sum_backward(self.ctx, dtype_code(A.dtype), A.ptr, B.ptr,
+                                                    dOut.ptr, dA.ptr, dB.ptr, R, Cc, N, P))
+        return dA, dB
+
+    # ------------------------------------------------------------ elementwise
+    def act_forward(self, act, x, alpha=0.0, out=None):
+        out = out or self.empty(x.shape, x.dtype)
+        check(self.lib.prad_act_forward(self.ctx, dtype_code(x.dtype), act, x.ptr, out.ptr, x.size,
+                                        alpha))
+        return out
+
+    def act_backward(self, act, saved, dy, alpha=0.0, out=None):
+        out = out or self.empty(dy.shape, dy.dtype)
+        check(self.lib.prad_act_backward(self.ctx, dtype_code(dy.dtype), act, saved.ptr, dy.ptr,
+                                         out.ptr, dy.size, alpha))
+        return out
+
+    def hadamard_forward(self, a, b, out=None):
+        out = out or self.empty(a.shape, a.dtype)
+        check(self.lib.prad_hadamard_forward(self.ctx, dtype_code(a.dtype), a.ptr, b.ptr, out.ptr,
+                                             a.size))
+        return out
+
+    def hadamard_backward(self, a, b, dy):
+        da, db = self.empty(a.shape, a.dtype), self.empty(a.shape, a.dtype)
+        check(self.lib.prad_hadamard_backward(self.ctx, dtype_code(a.dtype), a.ptr, b.ptr, dy.ptr,
+                                              da.ptr, db.ptr, a.size))
+        return da, db
+
+    def add_forward(self, a, b, c=None, out=None):
+        out = out or self.empty(a.shape, a.dtype)
+        check(self.lib.prad_add_forward(self.ctx, dtype_code(a.dtype), a.ptr, b.ptr, self._p(c),
+                                        out.ptr, a.size))
+        return out
+
+    def add_broadcast_forward(self, x, bias, out=None):
+        out = out or self.empty(x.shape, x.dtype)
+        check(self.lib.prad_add_broadcast_forward(self.ctx, dtype_code(x.dtype), x.ptr, bias.ptr,
+                                                  out.ptr, x.shape[0], x.shape[1]))
+        return out
+
+    def add_broadcast_backward(self, dy, dbias=None, accumulate=False):
+        dbias = dbias or self.empty((1, dy.shape[1]), dy.dtype)
+        check(self.lib.prad_add_broadcast_backward(self.ctx, dtype_code(dy.dtype), dy.ptr, dbias.ptr,
+                                                   dy.shape[0], dy.shape[1], int(accumulate)))
+        return dbias
+
+    def scale(self, x, s, out=None):
+        out = out or self.empty(x.shape, x.dtype)
+        check(self.lib.prad_scale(self.ctx, dtype_code(x.dtype), x.ptr, out.ptr, x.size, s))
+        return out
+
+    def transpose(self, x, out=None):
+        depth = x.shape[0] if len(x.shape) == 3 else 1
+        r, c = x.shape[-2:]
+        shape = (depth, c, r) if len(x.shape) == 3 else (c, r)
+        out = out or self.empty(shape, x.dtype)
+        check(self.lib.prad_transpose(self.ctx, dtype_code(x.dtype), x.ptr, out.ptr, r, c, depth))
+        return out
+
+    # ------------------------------------------------------------ row operations
+    def softmax_forward(self, x, out=None):
+        out = out or self.empty(x.shape, x.dtype)
+        check(self.lib.prad_softmax_forward(self.ctx, dtype_code(x.dtype), x.ptr, out.ptr,
+                                            x.size // x.shape[-1], x.shape[-1]))
+        return out
+
+    def softmax_backward(self, y, dy, out=None):
+        out = out or self.empty(y.shape, y.dtype)
+        check(self.lib.prad_softmax_backward(self.ctx, dtype_code(y.dtype), y.ptr, dy.ptr, out.ptr,
+                                             y.size // y.shape[-1], y.shape[-1]))
+        return out
+
+    def layernorm_forward(self, x):
+        rows = x.size // x.shape[-1]
+        y = self.empty(x.shape, x.dtype)
+        mean = self.empty((rows,), x.dtype)
+        std = self.empty((rows,), x.dtype)
+        check(self.lib.prad_layernorm_forward(self.ctx, dtype_code(x.dtype), x.ptr, y.ptr, mean.ptr,
+                                              std.ptr, rows, x.shape[-1]))
+        return y, mean, std
+
+    def layernorm_backward(self, x, mean, std, dy, out=None):
+        out = out or self.empty(x.shape, x.dtype)
+        check(self.lib.prad_layernorm_backward(self.ctx, dtype_code(x.dtype), x.ptr, mean.ptr,
+                                               std.ptr, dy.ptr, out.ptr, x.size // x.shape[-1],
+                                               x.shape[-1]))
+        return out
+
+    # ------------------------------------------------------------ losses
+    def _loss_fwd(self, fn, out, target):
+        loss = self.empty((1, 1), out.dtype)
+        check(fn(self.ctx, dtype_code(out.dtype), out.ptr, target.ptr, loss.ptr, out.shape[0],
+                 out.shape[1]))
+        return loss
+
+    def mse_forward(self, out, target):
+        return self._loss_fwd(self.lib.prad_mse_forward, out, target)
+
+    def cce_forward(self, out, target):
+        return self._loss_fwd(self.lib.prad_cce_forward, out, target)
+
+    def mse_backward(self, out, target, rows_total=None, grad=None):
+        grad = grad or self.empty(out.shape, out.dtype)
+        check(self.lib.prad_mse_backward(self.ctx, dtype_code(out.dtype), out.ptr, target.ptr,
+                                         grad.ptr, out.shape[0], out.shape[1],
+                                         rows_total or out.shape[0]))
+        return grad
+
+    def cce_backward(self, out, target, rows_total=None, grad=None):
+        grad = grad or self.empty(out.shape, out.dtype)
+        check(self.lib.prad_cce_backward(self.ctx, dtype_code(out.dtype), out.ptr, target.ptr,
+                                         grad.ptr, out.shape[0], out.shape[1],
+                                         rows_total or out.shape[0]))
+        return grad
+
+    # ------------------------------------------------------------ embedding
+    def embedding_forward(self, index_col, W):
+        n = index_col.size
+        out = self.empty((n, W.shape[1]), W.dtype)
+        check(self.lib.prad_embedding_forward(self.ctx, dtype_code(W.dtype), index_col.ptr, W.ptr,
+                                              out.ptr, n, W.shape[0], W.shape[1]))
+        return out
+
+    def embedding_backward(self, index_col, dOut, vocab):
+        dW = self.empty((vocab, dOut.shape[1]), dOut.dtype)
+        check(self.lib.prad_embedding_backward(self.ctx, dtype_code(dOut.dtype), index_col.ptr,
+                                               dOut.ptr, dW.ptr, index_col.size, vocab,
+                                               dOut.shape[1]))
+        return dW
+
+    # ------------------------------------------------------------ accumulation
+    def segmented_sum(self, srcs, out=None):
+        srcs = list(srcs)
+        out = out or self.empty(srcs[0].shape, srcs[0].dtype)
+        check(self.lib.prad_segmented_sum(self.ctx, dtype_code(out.dtype), self._ptr_list(srcs),
+                                          len(srcs), out.ptr, out.size))
+        return out
+
+    def batch_mean(self, srcs, out=None):
+        srcs = list(srcs)
+        out = out or self.empty(srcs[0].shape, srcs[0].dtype)
+        check(self.lib.prad_batch_mean(self.ctx, dtype_code(out.dtype), self._ptr_list(srcs),
+                                       len(srcs), out.ptr, out.size))
+        return out
+
+    def accumulate(self, dest, src):
+        check(self.lib.prad_accumulate(self.ctx, dtype_code(dest.dtype), dest.ptr, src.ptr,
+                                       dest.size))
+
+    # ------------------------------------------------------------ clip + Adam
+    def clip_reference(self, grads, clip_value, min_value):
+        grads = list(grads)
+        check(self.lib.prad_clip_reference(self.ctx, dtype_code(grads[0].dtype),
+                                           self._ptr_list(grads), self._size_list(grads),
+                                           len(grads), clip_value, min_value))
+
+    def clip_global_norm(self, grads, max_norm) -> float:
+        grads = list(grads)
+        norm = C.c_double()
+        check(self.lib.prad_clip_global_norm(self.ctx, dtype_code(grads[0].dtype),
+                                             self._ptr_list(grads), self._size_list(grads),
+                                             len(grads), max_norm, C.byref(norm)))
+        return norm.value
+
+    def clip_adam(self, w, g, m, v, clip_mode, clip_value, min_value, lr, beta1, beta2, eps,
+                  iteration, form=ADAM_RMAD, zero_grad=False):
+        w, g, m, v = list(w), list(g), list(m), list(v)
+        check(self.lib.prad_clip_adam(self.ctx, dtype_code(w[0].dtype), self._ptr_list(w),
+                                      self._ptr_list(g), self._ptr_list(m), self._ptr_list(v),
+                                      self._size_list(w), len(w), clip_mode, clip_value, min_value,
+                                      lr, beta1, beta2, eps, iteration, form, int(zero_grad)))
+
+    def adam(self, w, g, m, v, lr, beta1, beta2, eps, iteration, form=ADAM_RMAD, zero_grad=False):
+        self.clip_adam(w, g, m, v, CLIP_NONE, 0.0, 0.0, lr, beta1, beta2, eps, iteration, form,
+                       zero_grad)
+
+    # ------------------------------------------------------------ data parallel
+    @staticmethod
+    def dp_unique_id() -> bytes:
+        buf = C.create_string_buffer(128)
+        check(_lib.load().prad_dp_unique_id(buf))
+        return buf.raw
+
+    def dp_init(self, unique_id: bytes, rank: int, world: int) -> None:
+        check(self.lib.prad_dp_init(self.ctx, C.create_string_buffer(unique_id, 128), rank, world))
+
+    def dp_allreduce(self, m: DeviceMatrix) -> None:
+        check(self.lib.prad_dp_allreduce(self.ctx, dtype_code(m.dtype), m.ptr, m.size))
+
+    def dp_wait(self) -> None:
+        check(self.lib.prad_dp_wait(self.ctx))
+
+    def dp_shutdown(self) -> None:
+        check(self.lib.prad_dp_shutdown(self.ctx))

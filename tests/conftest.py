@@ -1,0 +1,22 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")
+
+
+@pytest.fixture(scope="session")
+def engine():
+    """One libprad_cuda context for the whole GPU session (fails loudly without a GPU)."""
+    from parallelreverseautodiff_b200.engine import Engine
+
+    eng = Engine(0)
+    yield eng
+    eng.close()

@@ -1,0 +1,417 @@
+"""GPU parity: every kernel family of libprad_cuda against the CPU oracle, through the C ABI.
+
+Inputs are seeded; sizes are small enough for the oracle to finish in seconds and include
+the ragged shapes (1, 7, 8, 9, 63, 64, 65, ...) that exercise tile edges.
+"""
+import numpy as np
+import pytest
+
+import oracle as O
+from parallelreverseautodiff_b200 import engine as E
+from util import assert_close, normal, rms, rng, uniform
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [np.float64, np.float32]
+ACTS = {
+    "leaky": (E.ACT_LEAKY_RELU, 0.01),
+    "sigmoid": (E.ACT_SIGMOID, 0.0),
+    "tanh": (E.ACT_TANH, 0.0),
+    "gelu": (E.ACT_GELU, 0.0),
+}
+
+
+def _act_oracle(name, x, alpha):
+    fwd = {"leaky": lambda v: O.leaky_relu_forward(v, alpha), "sigmoid": O.sigmoid_forward,
+           "tanh": O.tanh_forward, "gelu": O.gelu_forward}[name]
+    return fwd(x)
+
+
+def _act_oracle_bwd(name, x, y, dy, alpha):
+    if name == "leaky":
+        return O.leaky_relu_backward(x, dy, alpha)
+    if name == "sigmoid":
+        return O.sigmoid_backward(y, dy)
+    if name == "tanh":
+        return O.tanh_backward(y, dy)
+    return O.gelu_backward(x, dy)
+
+
+GEMM_SHAPES = [(1, 1, 1), (7, 5, 3), (8, 9, 63), (64, 65, 33), (65, 64, 129), (130, 257, 100),
+               (512, 784, 256), (256, 512, 10), (300, 1, 17), (1, 300, 1)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", GEMM_SHAPES)
+def test_matmul_forward_backward(engine, dtype, shape):
+    M, K, N = shape
+    r = rng(hash(shape) % 1000)
+    A = uniform(r, (M, K), -1, 1, dtype)
+    B = normal(r, (K, N), np.sqrt(2.0 / K), dtype)
+    dC = normal(r, (M, N), 1.0, dtype)
+    dA_ref, dB_ref = O.matmul_backward(A, B, dC)
+    C_ref = O.matmul_forward(A, B)
+    dA_, dB_, dC_ = engine.upload(A), engine.upload(B), engine.upload(dC)
+    Cg = engine.matmul_forward(dA_, dB_).numpy()
+    gA, gB = engine.matmul_backward(dA_, dB_, dC_)
+    assert_close(Cg, C_ref, np.abs(A).astype(np.float64) @ np.abs(B), "C")
+    assert_close(gA.numpy(), dA_ref, np.abs(dC).astype(np.float64) @ np.abs(B.T), "dA")
+    assert_close(gB.numpy(), dB_ref, np.abs(A.T).astype(np.float64) @ np.abs(dC), "dB")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_matmul_backward_accumulate_and_scale(engine, dtype):
+    r = rng(5)
+    M, K, N = 96, 70, 45
+    A, B, dC = normal(r, (M, K), 1, dtype), normal(r, (K, N), 1, dtype), normal(r, (M, N), 1, dtype)
+    dest = normal(r, (K, N), 1, dtype)
+    _, dB_ref = O.matmul_backward(A, B, dC, need_dA=False)
+    expect = (dest + dB_ref * dtype(0.25)).astype(dtype)
+    d = engine.upload(dest)
+    engine.matmul_backward(engine.upload(A), engine.upload(B), engine.upload(dC), dB=d,
+                           need_dA=False, accumulate_dB=True, dB_scale=0.25)
+    assert_close(d.numpy(), expect, np.abs(A.T).astype(np.float64) @ np.abs(dC) + np.abs(dest), "dB+=")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("act", list(ACTS))
+def test_matmul_act_backward_node(engine, dtype, act):
+    """MatMul -> activation node: dPre, dA, dB (benchmark config 1 is the leaky/float64 case)."""
+    code, alpha = ACTS[act]
+    r = rng(42)
+    M, K, N = 128, 200, 72
+    A = uniform(r, (M, K), -1, 1, dtype)
+    B = normal(r, (K, N), np.sqrt(2.0 / K), dtype)
+    dOut = normal(r, (M, N), 1.0, dtype)
+    pre = O.matmul_forward(A, B)
+    y = _act_oracle(act, pre, alpha)
+    saved = y if act in ("sigmoid", "tanh") else pre
+    dPre_ref = _act_oracle_bwd(act, pre, y, dOut, alpha)
+    dA_ref, dB_ref = O.matmul_backward(A, B, dPre_ref)
+    dPre, dA, dB = engine.matmul_act_backward(engine.upload(A), engine.upload(B), engine.upload(dOut),
+                                              code, engine.upload(saved), alpha)
+    assert_close(dPre.numpy(), dPre_ref, rms(dPre_ref), "dPre")
+    assert_close(dA.numpy(), dA_ref, np.abs(dPre_ref).astype(np.float64) @ np.abs(B.T), "dA")
+    assert_close(dB.numpy(), dB_ref, np.abs(A.T).astype(np.float64) @ np.abs(dPre_ref), "dB")
+    # the host-buffer form of the same node
+    hPre, hA, hB = engine.matmul_act_backward_host(A, B, dOut, code, saved, alpha)
+    np.testing.assert_array_equal(hPre, dPre.numpy())
+    np.testing.assert_array_equal(hA, dA.numpy())
+    np.testing.assert_array_equal(hB, dB.numpy())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_matmul_backward_fused_activation_below(engine, dtype):
+    """dA epilogue multiplies by the derivative of the activation that produced A."""
+    r = rng(9)
+    M, K, N = 77, 130, 64
+    Zb = normal(r, (M, K), 1.0, dtype)          # pre-activation of the layer below
+    A = O.gelu_forward(Zb)
+    B = normal(r, (K, N), 0.1, dtype)
+    dC = normal(r, (M, N), 1.0, dtype)
+    dA_ref, _ = O.matmul_backward(A, B, dC, need_dB=False)
+    dZ_ref = O.gelu_backward(Zb, dA_ref)
+    dZ, _ = engine.matmul_backward(engine.upload(A), engine.upload(B), engine.upload(dC),
+                                   need_dB=False, act_below=E.ACT_GELU, saved_below=engine.upload(Zb))
+    bound = (np.abs(dC).astype(np.float64) @ np.abs(B.T)) * 1.2
+    assert_close(dZ.numpy(), dZ_ref, bound, "dZ")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shared", [False, True])
+def test_batch_matmul(engine, dtype, shared):
+    r = rng(3)
+    depth, M, K, N = 13, 49, 32, 49
+    A = normal(r, (depth, M, K), 1, dtype)
+    B = normal(r, (K, N) if shared else (depth, K, N), 1, dtype)
+    dC = normal(r, (depth, M, N), 1, dtype)
+    C_ref = O.batch_matmul_forward(A, B)
+    dA_ref, dB_ref = O.batch_matmul_backward(A, B, dC)
+    a, b, dc = engine.upload(A), engine.upload(B), engine.upload(dC)
+    assert_close(engine.batch_matmul_forward(a, b).numpy(), C_ref, 40.0, "C")
+    dA, dB, dBm = engine.batch_matmul_backward(a, b, dc, per_slice_dB=True, mean_dB=shared)
+    assert_close(dA.numpy(), dA_ref, 60.0, "dA")
+    assert_close(dB.numpy(), dB_ref, 60.0, "dB")
+    if shared:
+        mean_ref = O.batch_mean([dB_ref[d] for d in range(depth)])
+        assert_close(dBm.numpy(), mean_ref, 60.0, "dB mean")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_matmul_and_sum(engine, dtype):
+    r = rng(4)
+    n, P = 24, 5
+    A = normal(r, (n, n), 1, dtype)
+    B = normal(r, (P, n, n), 1, dtype)
+    dOut = normal(r, (1, P), 1, dtype)
+    out_ref = O.matmul_and_sum_forward(A, B)
+    dA_ref, dB_ref = O.matmul_and_sum_backward(A, B, dOut)
+    a, b = engine.upload(A), engine.upload(B)
+    assert_close(engine.matmul_and_sum_forward(a, b).numpy(), out_ref, 600.0, "out")
+    dA, dB = engine.matmul_and_sum_backward(a, b, engine.upload(dOut))
+    np.testing.assert_array_equal(dB.numpy(), dB_ref)   # one product per element: exact
+    assert_close(dA.numpy(), dA_ref, 5.0, "dA")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("act", list(ACTS))
+@pytest.mark.parametrize("n", [1, 5, 1023, 4096 + 3, 300001])
+def test_activation_forward_backward(engine, dtype, act, n):
+    code, alpha = ACTS[act]
+    r = rng(n)
+    x = normal(r, (1, n), 2.0, dtype)
+    dy = normal(r, (1, n), 1.0, dtype)
+    y_ref = _act_oracle(act, x, alpha)
+    dx_ref = _act_oracle_bwd(act, x, y_ref, dy, alpha)
+    xd = engine.upload(x)
+    y = engine.act_forward(code, xd, alpha)
+    assert_close(y.numpy(), y_ref, rms(y_ref), f"{act} forward")
+    saved = engine.upload(y_ref) if act in ("sigmoid", "tanh") else xd
+    dx = engine.act_backward(code, saved, engine.upload(dy), alpha)
+    if act in ("leaky", "sigmoid"):
+        np.testing.assert_array_equal(dx.numpy(), dx_ref)   # same roundings: bit-exact
+    else:
+        assert_close(dx.numpy(), dx_ref, rms(dx_ref), f"{act} backward")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_hadamard_add_scale_transpose(engine, dtype):
+    r = rng(11)
+    a, b, c, dy = (normal(r, (37, 53), 1, dtype) for _ in range(4))
+    A, B, Cc, DY = (engine.upload(v) for v in (a, b, c, dy))
+    np.testing.assert_array_equal(engine.hadamard_forward(A, B).numpy(), O.hadamard_forward(a, b))
+    da, db = engine.hadamard_backward(A, B, DY)
+    da_ref, db_ref = O.hadamard_backward(a, b, dy)
+    np.testing.assert_array_equal(da.numpy(), da_ref)
+    np.testing.assert_array_equal(db.numpy(), db_ref)
+    np.testing.assert_array_equal(engine.add_forward(A, B).numpy(), O.add_forward(a, b))
+    np.testing.assert_array_equal(engine.add_forward(A, B, Cc).numpy(), O.add3_forward(a, b, c))
+    np.testing.assert_array_equal(engine.scale(A, 1 / np.sqrt(32)).numpy(),
+                                  O.scale(a, dtype(1 / np.sqrt(32))))
+    np.testing.assert_array_equal(engine.transpose(A).numpy(), O.transpose(a))
+    deep = normal(r, (5, 49, 32), 1, dtype)
+    np.testing.assert_array_equal(engine.transpose(engine.upload(deep)).numpy(),
+                                  np.stack([O.transpose(deep[d]) for d in range(5)]))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(1, 1), (256, 10), (333, 96), (4097, 33), (64, 4096)])
+def test_add_broadcast(engine, dtype, shape):
+    r = rng(shape[1])
+    x, dy = normal(r, shape, 1, dtype), normal(r, shape, 1, dtype)
+    bias = normal(r, (1, shape[1]), 1, dtype)
+    np.testing.assert_array_equal(
+        engine.add_broadcast_forward(engine.upload(x), engine.upload(bias)).numpy(),
+        O.add_broadcast_forward(x, bias))
+    _, db_ref = O.add_broadcast_backward(dy)
+    db = engine.add_broadcast_backward(engine.upload(dy))
+    assert_close(db.numpy(), db_ref, np.abs(dy).astype(np.float64).sum(0, keepdims=True), "dBias")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(1, 1), (256, 10), (49 * 12, 49), (7, 1000), (3, 4097)])
+def test_softmax(engine, dtype, shape):
+    r = rng(shape[0])
+    x, dy = normal(r, shape, 2.0, dtype), normal(r, shape, 1.0, dtype)
+    y_ref = O.softmax_forward(x)
+    dx_ref = O.softmax_backward(y_ref, dy)
+    y = engine.softmax_forward(engine.upload(x))
+    assert_close(y.numpy(), y_ref, 1.0 / shape[1], "softmax")
+    dx = engine.softmax_backward(engine.upload(y_ref), engine.upload(dy))
+    # row scale of the Jacobian product: sum_k |dy_k| y_k y_j
+    bound = np.abs(y_ref) * (np.abs(dy) + (np.abs(dy) * y_ref).sum(1, keepdims=True))
+    assert_close(dx.numpy(), dx_ref, bound.astype(np.float64) + 1e-300, "softmax backward")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(1, 2), (22, 22), (333, 96), (5, 4097)])
+def test_layernorm(engine, dtype, shape):
+    r = rng(shape[1])
+    x, dy = normal(r, shape, 3.0, dtype) + dtype(0.5), normal(r, shape, 1.0, dtype)
+    y_ref, mean_ref, std_ref = O.layernorm_forward(x)
+    dx_ref = O.layernorm_backward(x, mean_ref, std_ref, dy)
+    y, mean, std = engine.layernorm_forward(engine.upload(x))
+    assert_close(mean.numpy(), mean_ref, rms(x), "mean")
+    assert_close(std.numpy(), std_ref, rms(x), "std")
+    assert_close(y.numpy(), y_ref, 1.0, "layernorm")
+    dx = engine.layernorm_backward(engine.upload(x), engine.upload(mean_ref), engine.upload(std_ref),
+                                   engine.upload(dy))
+    assert_close(dx.numpy(), dx_ref, rms(dx_ref), "layernorm backward")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_losses(engine, dtype):
+    r = rng(21)
+    out = normal(r, (256, 10), 1, dtype)
+    tgt = normal(r, (256, 10), 1, dtype)
+    o, t = engine.upload(out), engine.upload(tgt)
+    assert_close(engine.mse_forward(o, t).numpy().reshape(()), np.asarray(O.mse_forward(out, tgt), dtype), 1.0, "mse")
+    np.testing.assert_array_equal(engine.mse_backward(o, t).numpy(), O.mse_backward(out, tgt))
+    np.testing.assert_array_equal(engine.mse_backward(o, t, rows_total=1024).numpy(),
+                                  O.mse_backward(out, tgt, rows_total=1024))
+    probs = O.softmax_forward(out)
+    onehot = np.eye(10, dtype=dtype)[r.integers(0, 10, 256)]
+    p, h = engine.upload(probs), engine.upload(onehot)
+    assert_close(engine.cce_forward(p, h).numpy().reshape(()), np.asarray(O.cce_forward(probs, onehot), dtype), 1.0, "cce")
+    np.testing.assert_array_equal(engine.cce_backward(p, h).numpy(), O.cce_backward(probs, onehot))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", [(2, 3, 2, "unique"), (1000, 50, 96, "dups"), (5000, 7, 33, "heavy"),
+                                  (300, 2000, 8, "sparse")])
+def test_embedding_bit_exact(engine, dtype, case):
+    n, vocab, dim, _ = case
+    r = rng(n)
+    W = normal(r, (vocab, dim), 1, dtype)
+    idx = r.integers(0, vocab, n)
+    if case[3] == "unique":
+        idx = np.array([2, 0])
+    col = idx.astype(dtype).reshape(-1, 1)
+    dOut = normal(r, (n, dim), 1, dtype)
+    icol = engine.upload(col)
+    np.testing.assert_array_equal(engine.embedding_forward(icol, engine.upload(W)).numpy(),
+                                  O.embedding_forward(col, W))
+    np.testing.assert_array_equal(engine.embedding_backward(icol, engine.upload(dOut), vocab).numpy(),
+                                  O.embedding_backward(col, dOut, vocab))
+
+
+def test_embedding_rejects_bad_index(engine):
+    from parallelreverseautodiff_b200._lib import PradError
+    col = engine.upload(np.array([[0.0], [5.0]], np.float32))
+    with pytest.raises(PradError):
+        engine.embedding_forward(col, engine.upload(np.zeros((3, 4), np.float32)))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("count", [1, 2, 5, 20])
+def test_segmented_sum_accumulate_batch_mean(engine, dtype, count):
+    r = rng(count)
+    gs = [normal(r, (64, 33), 1, dtype) for _ in range(count)]
+    dev = [engine.upload(g) for g in gs]
+    got = engine.segmented_sum(dev).numpy()
+    if count <= 16 or dtype == np.float64:
+        np.testing.assert_array_equal(got, O.accumulate_gradients(gs))
+    else:
+        assert_close(got, O.accumulate_gradients(gs), count, "segmented sum")
+    np.testing.assert_array_equal(engine.batch_mean(dev).numpy(), O.batch_mean(gs))
+    dest = normal(r, (64, 33), 1, dtype)
+    d = engine.upload(dest)
+    engine.accumulate(d, dev[0])
+    np.testing.assert_array_equal(d.numpy(), O.accumulate_into(dest.copy(), gs[0]))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_clip_reference(engine, dtype):
+    r = rng(77)
+    shapes = [(784, 64), (1, 64), (33, 7), (1, 1), (300, 300)]
+    gs = [normal(r, s, 3.0, dtype) for s in shapes]
+    gs[2][0, :3] = [1e-20, -1e-20, 0.0]          # minimum-threshold branch
+    gs[3][0, 0] = 2.5                            # one element: sigma = 0 -> NaN limit, unchanged
+    minv = 1e-16 if dtype == np.float64 else 1e-8
+    ref = [O.clip_reference(g.copy(), 4.0, minv) for g in gs]
+    dev = [engine.upload(g) for g in gs]
+    engine.clip_reference(dev, 4.0, minv)
+    for d, e, g in zip(dev, ref, gs):
+        got = d.numpy()
+        # clamped values are (1+|z|): sensitive to mean/sigma rounding, hence a tolerance
+        assert_close(got, e, 1.0, "clip")
+        assert (np.abs(got) <= np.abs(g) + minv).all()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_clip_global_norm(engine, dtype):
+    r = rng(78)
+    gs = [normal(r, s, 1.0, dtype) for s in [(100, 50), (1, 50), (50, 10)]]
+    ref = [g.copy() for g in gs]
+    norm_ref = O.clip_global_norm(ref, 4.0)
+    dev = [engine.upload(g) for g in gs]
+    norm = engine.clip_global_norm(dev, 4.0)
+    assert abs(norm - norm_ref) <= 1e-12 * norm_ref
+    for d, e in zip(dev, ref):
+        assert_close(d.numpy(), e, rms(e), "global-norm clip")
+    small = [engine.upload(g * dtype(1e-3)) for g in gs]
+    engine.clip_global_norm(small, 4.0)
+    np.testing.assert_array_equal(small[0].numpy(), gs[0] * dtype(1e-3))   # below the limit: untouched
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("form", ["rmad", "prad"])
+def test_adam(engine, dtype, form):
+    r = rng(79)
+    shapes = [(784, 32), (1, 32), (9000,)]
+    w = [normal(r, s, 1, dtype) for s in shapes]
+    g = [normal(r, s, 0.1, dtype) for s in shapes]
+    m = [normal(r, s, 0.01, dtype) for s in shapes]
+    v = [np.abs(normal(r, s, 0.01, dtype)) for s in shapes]
+    W, G, M_, V = ([engine.upload(a) for a in arrs] for arrs in (w, g, m, v))
+    for it in (1, 2, 3):
+        for k in range(len(shapes)):
+            if form == "rmad":
+                O.adam_rmad(w[k], m[k], v[k], g[k], 1e-3, 0.9, 0.999, 1e-8, float(it))
+            else:
+                O.adam_prad(w[k], m[k], v[k], g[k], 1e-3, 0.9, 0.999, 1e-8, it)
+        engine.adam(W, G, M_, V, 1e-3, 0.9, 0.999, 1e-8, float(it),
+                    form=E.ADAM_RMAD if form == "rmad" else E.ADAM_PRAD)
+    for k in range(len(shapes)):
+        # same operations in the same order with IEEE sqrt/div: bit-exact
+        np.testing.assert_array_equal(W[k].numpy(), w[k])
+        np.testing.assert_array_equal(M_[k].numpy(), m[k])
+        np.testing.assert_array_equal(V[k].numpy(), v[k])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_clip_adam_fused_equals_separate(engine, dtype):
+    r = rng(80)
+    shapes = [(300, 40), (1, 40)]
+    w0 = [normal(r, s, 1, dtype) for s in shapes]
+    g0 = [normal(r, s, 2.0, dtype) for s in shapes]
+    zeros = [np.zeros(s, dtype) for s in shapes]
+    minv = 1e-16 if dtype == np.float64 else 1e-8
+    for mode in (E.CLIP_REFERENCE, E.CLIP_GLOBAL_NORM):
+        W1, G1, M1, V1 = ([engine.upload(a) for a in arrs] for arrs in (w0, g0, zeros, zeros))
+        if mode == E.CLIP_REFERENCE:
+            engine.clip_reference(G1, 4.0, minv)
+        else:
+            engine.clip_global_norm(G1, 4.0)
+        engine.adam(W1, G1, M1, V1, 1e-3, 0.9, 0.999, 1e-8, 1.0)
+        W2, G2, M2, V2 = ([engine.upload(a) for a in arrs] for arrs in (w0, g0, zeros, zeros))
+        engine.clip_adam(W2, G2, M2, V2, mode, 4.0, minv, 1e-3, 0.9, 0.999, 1e-8, 1.0, zero_grad=True)
+        for k in range(len(shapes)):
+            np.testing.assert_array_equal(W2[k].numpy(), W1[k].numpy())
+            np.testing.assert_array_equal(M2[k].numpy(), M1[k].numpy())
+            np.testing.assert_array_equal(V2[k].numpy(), V1[k].numpy())
+            assert not G2[k].numpy().any()
+
+
+def test_jagged_rows_roundtrip(engine):
+    r = rng(1)
+    rows = [r.standard_normal(17) for _ in range(9)]
+    m = engine.upload_rows(rows)
+    np.testing.assert_array_equal(m.numpy(), np.stack(rows))
+    back = engine.download_rows(m)
+    for a, b in zip(rows, back):
+        np.testing.assert_array_equal(a, b)
+
+
+def test_errors_are_status_codes(engine):
+    from parallelreverseautodiff_b200._lib import PradError, ERR_SHAPE
+    a = engine.upload(np.zeros((4, 5)))
+    b = engine.upload(np.zeros((6, 3)))
+    with pytest.raises(PradError) as ei:
+        engine.matmul_forward(a, b)
+    assert ei.value.status == ERR_SHAPE
+    with pytest.raises(PradError):
+        engine.set_option("gemm_f32", "bogus")
+
+
+def test_determinism_run_twice(engine):
+    r = rng(2)
+    A, B, dC = (normal(r, s, 1, np.float32) for s in [(300, 200), (200, 150), (300, 150)])
+    a, b, dc = engine.upload(A), engine.upload(B), engine.upload(dC)
+    x1 = [t.numpy() for t in engine.matmul_backward(a, b, dc)]
+    x2 = [t.numpy() for t in engine.matmul_backward(a, b, dc)]
+    for p, q in zip(x1, x2):
+        np.testing.assert_array_equal(p, q)
+    db1 = engine.add_broadcast_backward(dc).numpy()
+    db2 = engine.add_broadcast_backward(dc).numpy()
+    np.testing.assert_array_equal(db1, db2)
