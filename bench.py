@@ -1,0 +1,340 @@
+#!/usr/bin/env python
+"""Benchmark of the backward hot path on the large data-parallel MLP (PRADLite float32):
+8 layers of 4096x4096 with GELU, MSE loss, global batch 65536 rows sharded over N GPUs,
+weight-gradient all-reduce overlapped with the backward, then clip + Adam.
+
+    python bench.py --gpus N --steps K --warmup W            # this library (one JSON line)
+    python bench.py --impl reference --steps K --warmup W    # CPU restatement of the C# loops
+
+A step of the device-resident measurement (`value`) is one backward pass of the whole
+network (loss gradient, per layer dW and dA GEMMs with the GELU derivative fused in, the
+all-reduces) followed by gradient clip + Adam, on activations that already sit in HBM.
+`e2e` is the same metric through the host-buffer API: each step uploads the batch and the
+targets from page-locked host memory, runs forward, loss, backward, clip + Adam and reads
+the loss back.  Data is synthetic (seeded N(0,1) inputs and targets, He-initialised weights).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WIDTH, LAYERS, GLOBAL_BATCH = 4096, 8, 65536
+METRIC, UNIT = "backward_samples_per_s", "samples/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch rows")
+    ap.add_argument("--width", type=int, default=WIDTH)
+    ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--clip", default="reference", choices=["reference", "global_norm", "none"])
+    ap.add_argument("--gemm", default="auto", choices=["auto", "simt", "tf32x3"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU baseline sample budget")
+    return ap.parse_args()
+
+
+def backward_flops(batch, width, layers):
+    # MatrixMultiplyOperation.Backward: two products of 2*M*N*K each, per layer
+    return 4.0 * batch * width * width * layers
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples nvidia-smi (read-only) while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()  # the exact child we started
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # samples under load: the upper half of the observed clocks
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------ CPU baseline (oracle)
+def cpu_backward_sample(width, layers, seconds, seed=42):
+    """Times the CPU restatement of the reference's loops on a bounded slice of the workload:
+    ONE layer's backward (GELU derivative + both MatrixMultiplyOperation.Backward loops) on
+    `rows` rows; cost is linear in rows and layers, so samples/s for the whole network is
+    rows / (layers * t).  Returns (samples_per_s, rows, seconds_measured, threads)."""
+    import oracle as O
+
+    r = np.random.default_rng(seed)
+    W = (r.standard_normal((width, width)) * np.sqrt(2.0 / width)).astype(np.float32)
+
+    def run(rows):
+        A = r.standard_normal((rows, width)).astype(np.float32)
+        Z = r.standard_normal((rows, width)).astype(np.float32)
+        dOut = r.standard_normal((rows, width)).astype(np.float32)
+        t0 = time.perf_counter()
+        dZ = O.gelu_backward(Z, dOut)
+        O.matmul_backward(A, W, dZ)
+        return time.perf_counter() - t0
+
+    rows = 8
+    t = run(rows)
+    target_rows = int(max(8, min(4096, rows * seconds / max(t, 1e-6))))
+    target_rows = max(8, (target_rows // 8) * 8)
+    t = run(target_rows)
+    return target_rows / (layers * t), target_rows, t, O.num_threads()
+
+
+def run_reference(args, rank):
+    """--impl reference: the reference's CPU path (restated in C++, OpenMP over the index the
+    C# code gives Parallel.For) on the box's host cores.  Rank 0 only."""
+    if rank != 0:
+        return
+    vals, sample = [], None
+    for i in range(args.warmup + args.steps):
+        sps, rows, t, threads = cpu_backward_sample(args.width, args.layers,
+                                                    max(2.0, args.cpu_seconds / max(1, args.steps)))
+        if i >= args.warmup:
+            vals.append((sps, t))
+        sample = (rows, threads)
+    sps = statistics.mean(v[0] for v in vals)
+    rows, threads = sample
+    desc = (f"one {args.width}x{args.width} layer backward (GELU' + dA + dB loops) on {rows} rows, "
+            f"extrapolated linearly to {args.layers} layers; C++ restatement of the C# loops, "
+            f"not the .NET runtime")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": sps, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * args.batch / sps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"C5 data-parallel MLP {args.layers}x({args.width}x{args.width}, GELU), "
+                               f"MSE, global batch {args.batch}", "global_batch": args.batch,
+                   "parallelism": "cpu"},
+        "tflops": backward_flops(1, args.width, args.layers) * sps / 1e12,
+        "cpu_baseline": {"value": sps, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
+        "e2e": {"value": sps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------ native arm
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p.get("hbm_gbs"), "tensor_tflops": p.get("bf16_tflops_sustained") or p.get("bf16_tflops"),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tensor_tflops": 1400.0, "source": "fallback"}
+
+
+def run_native(args, rank, world, local_rank):
+    import torch
+
+    from parallelreverseautodiff_b200 import engine as E
+    from parallelreverseautodiff_b200.networks import FeedForwardNetwork
+
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    assert args.batch % world == 0, "global batch must divide over the ranks"
+    rows = args.batch // world
+
+    eng = E.Engine(local_rank)
+    eng.set_option("gemm_f32", args.gemm)
+    if world > 1:
+        ids = [E.Engine.dp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        eng.dp_init(ids[0], rank, world)
+
+    clip = {"reference": E.CLIP_REFERENCE, "global_norm": E.CLIP_GLOBAL_NORM, "none": E.CLIP_NONE}[args.clip]
+    sizes = [args.width] * (args.layers + 1)
+    net = FeedForwardNetwork(eng, np.float32, sizes, hidden_act=E.ACT_GELU, output_act=E.ACT_GELU,
+                             loss="mse", use_bias=False, clip_mode=clip, rank=rank, world=world)
+    wr = np.random.default_rng(42)  # identical weights on every rank
+    net.set_weights([(wr.standard_normal((args.width, args.width), dtype=np.float32)
+                      * np.float32(np.sqrt(2.0 / args.width))) for _ in range(args.layers)])
+    dr = np.random.default_rng(1000 + rank)  # this rank's rows of the batch
+    x_host = eng.pinned_empty((rows, args.width), np.float32)
+    t_host = eng.pinned_empty((rows, args.width), np.float32)
+    chunk = 4096
+    for r0 in range(0, rows, chunk):
+        r1 = min(rows, r0 + chunk)
+        x_host[r0:r1] = dr.standard_normal((r1 - r0, args.width), dtype=np.float32)
+        t_host[r0:r1] = dr.standard_normal((r1 - r0, args.width), dtype=np.float32)
+
+    stream = torch.cuda.ExternalStream(eng.stream(), device=torch.device("cuda", local_rank))
+
+    def barrier():
+        eng.sync()
+        torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
+        eng.sync()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if not dist:
+            return ms
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # warm-up: full end-to-end steps (they also leave valid activations in HBM)
+    loss = None
+    for _ in range(max(args.warmup, 1)):
+        loss = net.train_step_host(x_host, t_host, rows_total=args.batch)
+
+    # ---- (A) device-resident hot path: backward + clip + Adam ---------------------------
+    gemm_events = []
+
+    def probe(kind, begin):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(stream)
+        gemm_events.append(ev)
+
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    launches0 = eng.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(args.steps):
+        net.backward(rows_total=args.batch, probe=probe)
+        net.clip_and_optimize()
+    ev1.record(stream)
+    barrier()
+    launches = eng.launch_count() - launches0
+    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+    ms_step = ms_total / args.steps
+    gemm_ms = sum(gemm_events[i].elapsed_time(gemm_events[i + 1]) for i in range(0, len(gemm_events), 2))
+    n_gemm = len(gemm_events) // 2
+
+    # ---- (B) end to end through the host-buffer API -------------------------------------
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        loss = net.train_step_host(x_host, t_host, rows_total=args.batch)
+    e1.record(stream)
+    barrier()
+    clocks = sampler.stop()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+
+    flops_step = backward_flops(args.batch, args.width, args.layers)
+    value = args.batch / (ms_step * 1e-3)
+    peaks = measured_peaks()
+    flops_per_gemm = 2.0 * rows * args.width * args.width
+    achieved_tflops = flops_per_gemm * n_gemm / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            sps, crow, ct, threads = cpu_backward_sample(args.width, args.layers, args.cpu_seconds)
+            cpu = {"value": sps, "unit": UNIT, "cores": threads, "kind": "port",
+                   "sample": f"one {args.width}x{args.width} layer backward on {crow} rows "
+                             f"({ct:.1f} s), extrapolated linearly to {args.layers} layers"}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 1), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"C5 data-parallel MLP {args.layers}x({args.width}x{args.width}, GELU), "
+                                   f"MSE, global batch {args.batch}, clip={args.clip} + Adam",
+                       "global_batch": args.batch, "rows_per_gpu": rows, "parallelism": f"dp{world}",
+                       "gemm": args.gemm, "l2": "inputs larger than L2 (activations >= 1 GiB per layer)"},
+            "tflops": flops_step / (ms_step * 1e-3) / 1e12,
+            "roofline": {"bound": "tensor", "achieved": achieved_tflops, "peak": peaks["tensor_tflops"],
+                         "unit": "TFLOP/s",
+                         "frac": (achieved_tflops / peaks["tensor_tflops"]) if achieved_tflops else None,
+                         "traffic": None, "kernel": "backward GEMMs (dW = A^T dZ, dA = dZ W^T)",
+                         "peak_source": peaks["source"] + " dense bf16, sustained",
+                         "launches_timed": n_gemm},
+            "cpu_baseline": cpu,
+            "e2e": {"value": args.batch / (e2e_ms * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": int(x_host.nbytes + t_host.nbytes) * world,
+                    "d2h_bytes_per_step": 4 * world, "ms_per_step": e2e_ms, "loss": loss},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        eng.dp_shutdown()
+    eng.close()
+    if dist:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
+    run_native(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

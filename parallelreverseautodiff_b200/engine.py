@@ -181,6 +181,22 @@ class Engine:
         check(self.lib.prad_download_rows(self.ctx, ptrs, m.ptr, len(rows), rows[0].nbytes))
         return rows
 
+    def pinned_empty(self, shape, dtype) -> np.ndarray:
+        """numpy array over page-locked host memory (freed with the engine's process)."""
+        dtype = np.dtype(dtype)
+        shape = (shape,) if isinstance(shape, int) else tuple(shape)
+        n = int(np.prod(shape, dtype=np.int64))
+        p = C.c_void_p()
+        check(self.lib.prad_alloc_host(self.ctx, n * dtype.itemsize, C.byref(p)))
+        buf = (C.c_char * (n * dtype.itemsize)).from_address(p.value)
+        return np.frombuffer(buf, dtype=dtype, count=n).reshape(shape)
+
+    def upload_async(self, a: np.ndarray, out: DeviceMatrix) -> None:
+        """Enqueue a host->device copy; `a` must stay untouched until the stream reaches it
+        (page-locked memory from pinned_empty makes the copy truly asynchronous)."""
+        assert a.flags.c_contiguous and out.nbytes == a.nbytes
+        check(self.lib.prad_upload(self.ctx, out.ptr, a.ctypes.data, a.nbytes))
+
     def copy(self, dst: DeviceMatrix, src: DeviceMatrix) -> None:
         assert dst.nbytes == src.nbytes
         check(self.lib.prad_copy(self.ctx, dst.ptr, src.ptr, src.nbytes))
