@@ -193,6 +193,27 @@ prad_status prad_add_broadcast_forward(prad_ctx* ctx, prad_dtype dt, const void*
                                        const void* bias, void* y, int rows, int cols);
 prad_status prad_add_broadcast_backward(prad_ctx* ctx, prad_dtype dt, const void* dy,
                                         void* dbias, int rows, int cols, int accumulate);
+/* Allocation-free form of prad_add_broadcast_backward.  It has no counterpart in the
+ * reference.  It exists for callers that must not allocate device memory at the moment they
+ * need the bias gradient: a plug-in running inside a host application that has handed out
+ * all device memory up front, a component whose rules of engagement ban allocator calls
+ * after start-up, or a latency-critical loop where the device-wide synchronisation a
+ * cudaMalloc implies is unacceptable.  It takes a cudaStream_t instead of a context, needs
+ * no prad_init, and calls no allocator of any kind: its partial sums go to a fixed 4 MiB
+ * array inside the library image (so every GPU that loads the library carries those 4 MiB
+ * until the process ends).
+ *  - limit: cols <= PRAD_STATIC_COLSUM_MAX_COLS (more is refused with PRAD_ERR_UNSUPPORTED);
+ *    rows >= 1;
+ *  - the device it works on is the calling thread's current device (cudaSetDevice);
+ *  - the first call on each device looks up the array's device address; make that first
+ *    call before starting any stream capture on that device;
+ *  - all calls share the one array and leave their partial sums in it; each call overwrites
+ *    every entry it later reads, so nothing has to be cleared, but two calls whose kernels
+ *    may run at the same time on one GPU (different streams, different threads) race on
+ *    it: serialise them. */
+#define PRAD_STATIC_COLSUM_MAX_COLS 32768
+prad_status prad_add_broadcast_backward_static(void* stream, prad_dtype dt, const void* dy,
+                                               void* dbias, int rows, int cols, int accumulate);
 /* MatrixMultiplyScalarOperation.cs:48-88 (forward and backward are the same scaling) */
 prad_status prad_scale(prad_ctx* ctx, prad_dtype dt, const void* x, void* y, int64_t n,
                        double s);

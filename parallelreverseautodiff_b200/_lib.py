@@ -53,6 +53,7 @@ SIGNATURES = {
     "prad_add_forward": [vp, i32, vp, vp, vp, vp, i64],
     "prad_add_broadcast_forward": [vp, i32, vp, vp, vp, i32, i32],
     "prad_add_broadcast_backward": [vp, i32, vp, vp, i32, i32, i32],
+    "prad_add_broadcast_backward_static": [vp, i32, vp, vp, i32, i32, i32],
     "prad_scale": [vp, i32, vp, vp, i64, f64],
     "prad_transpose": [vp, i32, vp, vp, i32, i32, i32],
     "prad_softmax_forward": [vp, i32, vp, vp, i64, i32],

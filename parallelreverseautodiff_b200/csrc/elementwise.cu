@@ -1,6 +1,8 @@
 // Stand-alone elementwise kernels of the backward path: HBM-bound streams with 128-bit
 // loads and stores, grid sized as a multiple of the SM count, grid-stride loop.
 // (Compiled with -fmad=false so that products and sums round as the managed code's do.)
+#include <mutex>
+
 #include "act_math.cuh"
 #include "common.cuh"
 
@@ -438,3 +440,101 @@ prad_status prad_accumulate(prad_ctx* ctx, prad_dtype dt, void* dest, const void
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------- allocation-free column sums
+// Variant of prad_add_broadcast_backward for callers that may not allocate device memory
+// while they run: a plug-in that shares a device whose memory the host application has
+// already budgeted to the last byte, a component that is forbidden to call an allocator
+// after start-up, or a real-time loop in which a cudaMalloc stall (it synchronises the
+// device) is not tolerable.
+// The partial sums live in a fixed array that is part of the loaded module, so every device
+// that loads this library keeps these 4 MiB until the process exits.
+namespace prad {
+
+constexpr int64_t STATIC_SCRATCH_DOUBLES = 512 * 1024;  // 4 MiB
+static __device__ __align__(256) double g_static_colsum_scratch[STATIC_SCRATCH_DOUBLES];
+
+constexpr int STATIC_MAX_DEVICES = 64;
+static std::mutex g_static_mu;
+static double* g_static_ptr[STATIC_MAX_DEVICES] = {nullptr};
+static int g_static_sms[STATIC_MAX_DEVICES] = {0};
+
+// Resolves the device address of the array on the current device, once per device.  In host
+// code the array's name is only a handle for the runtime, never a device pointer.
+static prad_status static_scratch_for_current_device(double** out_ptr, int* out_sms) {
+  int dev = -1;
+  PRAD_CUDA(cudaGetDevice(&dev));
+  PRAD_REQUIRE(dev >= 0 && dev < STATIC_MAX_DEVICES, PRAD_ERR_UNSUPPORTED,
+               "static scratch: device index %d is beyond the %d supported", dev, STATIC_MAX_DEVICES);
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    double* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&p, g_static_colsum_scratch);
+    if (e != cudaSuccess || !p) {
+      (void)cudaGetLastError();
+      set_error("static scratch: cudaGetSymbolAddress failed on device %d: %s", dev,
+                cudaGetErrorString(e));
+      return PRAD_ERR_CUDA;
+    }
+    int sms = 0;
+    PRAD_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    g_static_sms[dev] = sms;
+    g_static_ptr[dev] = p;
+  }
+  *out_ptr = g_static_ptr[dev];
+  *out_sms = g_static_sms[dev];
+  return PRAD_OK;
+}
+
+template <typename T>
+static prad_status colsum_static_t(cudaStream_t st, double* scratch, int sms, const void* dy,
+                                   void* dbias, int64_t rows, int cols, int accumulate) {
+  int strips = (int)ceil_div(cols, 32);
+  int64_t want_bands = ceil_div((int64_t)sms * 8, strips);
+  int64_t max_bands = ceil_div(rows, 64);
+  int64_t fit_bands = STATIC_SCRATCH_DOUBLES / cols;
+  int64_t bands = want_bands < max_bands ? want_bands : max_bands;
+  if (bands > fit_bands) bands = fit_bands;
+  if (bands > 65535) bands = 65535;
+  if (bands < 1) bands = 1;
+  int rows_per_band = (int)ceil_div(rows, bands);
+  bands = ceil_div(rows, rows_per_band);
+  // every partial that the second kernel reads is written by the first one in this call, so
+  // nothing left in the array by an earlier call can leak into the result
+  colsum_partial_kernel<T><<<dim3(strips, (unsigned)bands), 256, 0, st>>>(
+      (const T*)dy, scratch, rows, cols, rows_per_band);
+  cudaError_t e = cudaPeekAtLastError();
+  if (e == cudaSuccess) {
+    colsum_final_kernel<T><<<(unsigned)ceil_div(cols, 128), 128, 0, st>>>(
+        scratch, (T*)dbias, cols, (int)bands, accumulate);
+    e = cudaPeekAtLastError();
+  }
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    set_error("prad_add_broadcast_backward_static: kernel launch failed: %s", cudaGetErrorString(e));
+    return PRAD_ERR_CUDA;
+  }
+  return PRAD_OK;
+}
+
+}  // namespace prad
+
+extern "C" prad_status prad_add_broadcast_backward_static(void* stream, prad_dtype dt,
+                                                          const void* dy, void* dbias, int rows,
+                                                          int cols, int accumulate) {
+  PRAD_REQUIRE(dtype_ok(dt), PRAD_ERR_INVALID, "prad_add_broadcast_backward_static: bad dtype");
+  PRAD_REQUIRE(rows >= 1 && cols >= 1, PRAD_ERR_SHAPE,
+               "prad_add_broadcast_backward_static: rows and cols must be at least 1");
+  PRAD_REQUIRE(cols <= PRAD_STATIC_COLSUM_MAX_COLS, PRAD_ERR_UNSUPPORTED,
+               "prad_add_broadcast_backward_static: %d columns exceed the fixed scratch (limit %d); "
+               "use prad_add_broadcast_backward, which allocates",
+               cols, PRAD_STATIC_COLSUM_MAX_COLS);
+  PRAD_REQUIRE(dy && dbias, PRAD_ERR_INVALID, "prad_add_broadcast_backward_static: null pointer");
+  double* scratch = nullptr;
+  int sms = 0;
+  prad_status s = static_scratch_for_current_device(&scratch, &sms);
+  if (s) return s;
+  cudaStream_t st = (cudaStream_t)stream;
+  return dt == PRAD_F32 ? colsum_static_t<float>(st, scratch, sms, dy, dbias, rows, cols, accumulate)
+                        : colsum_static_t<double>(st, scratch, sms, dy, dbias, rows, cols, accumulate);
+}
