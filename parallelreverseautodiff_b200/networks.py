@@ -43,6 +43,16 @@ class NeuralNetworkParameters:
 _SAVES_OUTPUT = {E.ACT_SIGMOID, E.ACT_TANH}
 
 
+def row_shard(total_rows: int, rank: int, world: int):
+    """Contiguous block of batch rows owned by `rank`: the first `total % world` ranks get one
+    extra row.  Returns (start, stop)."""
+    if not (0 <= rank < world):
+        raise ValueError(f"rank {rank} outside world of {world}")
+    base, extra = divmod(total_rows, world)
+    start = rank * base + min(rank, extra)
+    return start, start + base + (1 if rank < extra else 0)
+
+
 class FeedForwardNetwork:
     def __init__(self, eng: E.Engine, dtype, sizes: Sequence[int], hidden_act=E.ACT_LEAKY_RELU,
                  output_act=E.ACT_NONE, softmax_output=False, loss="mse", use_bias=True,
