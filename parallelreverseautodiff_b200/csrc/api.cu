@@ -97,6 +97,14 @@ prad_status prad_init(int device, prad_ctx** out_ctx) {
     return PRAD_ERR_CUDA;
   }
   c->stream = c->own_stream;
+  e = cudaMalloc((void**)&c->tc_err, 256);
+  if (e == cudaSuccess) e = cudaMemset(c->tc_err, 0, 256);
+  if (e != cudaSuccess) {
+    set_error("prad_init: flag allocation: %s", cudaGetErrorString(e));
+    cudaStreamDestroy(c->own_stream);
+    delete c;
+    return PRAD_ERR_CUDA;
+  }
   *out_ctx = c;
   g_err[0] = 0;
   return PRAD_OK;
@@ -107,6 +115,7 @@ prad_status prad_shutdown(prad_ctx* ctx) {
   cudaStreamSynchronize(ctx->stream);
   dp_destroy(ctx);
   if (ctx->ws) cudaFree(ctx->ws);
+  if (ctx->tc_err) cudaFree(ctx->tc_err);
   if (ctx->stage) cudaFree(ctx->stage);
   if (ctx->host_ws) cudaFreeHost(ctx->host_ws);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
@@ -139,7 +148,7 @@ prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value) {
 prad_status prad_sync(prad_ctx* ctx) {
   PRAD_CHECK_CTX(ctx);
   PRAD_CUDA(cudaStreamSynchronize(ctx->stream));
-  return PRAD_OK;
+  return gemm_tf32x3_check(ctx);
 }
 
 prad_status prad_launch_count(prad_ctx* ctx, int64_t* out_count) {
@@ -234,7 +243,7 @@ prad_status prad_download(prad_ctx* ctx, void* dst_host, const void* src, size_t
     PRAD_CUDA(cudaMemcpyAsync(dst_host, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
     PRAD_CUDA(cudaStreamSynchronize(ctx->stream));
   }
-  return PRAD_OK;
+  return gemm_tf32x3_check(ctx);
 }
 
 // Jagged rows are gathered into one pinned block first, so the device sees ONE copy.

@@ -39,6 +39,9 @@ struct prad_ctx {
   void* stage = nullptr;
   size_t stage_bytes = 0;
   prad::DpState* dp = nullptr;
+  // give-up flag of the tensor-core GEMMs (device int, sticky until the host reads it)
+  int* tc_err = nullptr;
+  bool tc_pending_check = false;
   uint32_t magic = 0x50524144u;  // "PRAD"
 };
 
@@ -119,6 +122,9 @@ struct GemmEpilogue {
   const void* saved = nullptr;     // M x N tensor (ld = ldc) read by dact
   double act_alpha = 0.0;
 };
+
+// reads (and clears) the tensor-core GEMM give-up flag; PRAD_ERR_TIMEOUT if it was raised
+prad_status gemm_tf32x3_check(prad_ctx* ctx);
 
 prad_status gemm_dispatch(prad_ctx* ctx, prad_dtype dt, bool transA, bool transB, int M, int N,
                           int K, double alpha, const void* A, int lda, const void* B, int ldb,

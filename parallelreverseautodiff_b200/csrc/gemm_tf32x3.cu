@@ -1,9 +1,545 @@
-// placeholder until the tcgen05 kernel lands: reports every shape as unsupported
+// FP32 GEMM on the 5th-generation tensor cores: C = alpha*op(A)*op(B) + beta*C computed as
+// three TF32 products per k-slice ("3xTF32"),
+//     a*b ~= a_hi*b_hi + a_lo*b_hi + a_hi*b_lo,   a_hi = tf32(a), a_lo = tf32(a - a_hi),
+// accumulated in FP32 in tensor memory.  The dropped a_lo*b_lo term is ~2^-22 relative, so
+// the result matches an FP32 FMA chain to well inside the 1e-5 PRADLite tolerance.
+//
+// Structure of one CTA (320 threads, one 128 x 256 output tile, BK = 32 floats = one
+// 128-byte swizzle atom):
+//   warp 0     TMA producer: cp.async.bulk.tensor loads of the four operand tiles of a
+//              k-block (A_hi, A_lo, B_hi, B_lo) into a ring of shared-memory stages;
+//   warp 1     allocates tensor memory, then one lane issues tcgen05.mma (kind::tf32,
+//              M=128, N=256, K=8): 4 k-slices x 3 products per stage, releases the stage
+//              with tcgen05.commit, and finally signals the accumulator;
+//   warps 2-9  epilogue: after every chunk of 256 k they tcgen05.ld that chunk's 128 x 256
+//              accumulator (each warp its own 32-lane TMEM sub-partition and half of the
+//              columns) and add it to running sums in registers; at the end they apply
+//              alpha/beta, bias, activation or activation derivative and store 128-byte
+//              row segments.  Two TMEM accumulators alternate, so chunk c+1 is multiplied
+//              while chunk c is drained.
+// Both operands are consumed K-major (k contiguous).  A pre-pass writes the hi/lo pair of
+// each operand into scratch in that orientation (transposing when the caller's matrix has
+// the other orientation), padded so every TMA coordinate is 16-byte aligned.
+//
+// Every wait on an mbarrier is bounded: after SPIN_LIMIT polls the waiter raises a global
+// error flag (which all other waiters poll and obey), the CTA drains, frees its tensor
+// memory and returns; the host then reports PRAD_ERR_TIMEOUT.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "act_math.cuh"
 #include "common.cuh"
+
 namespace prad {
-prad_status gemm_tf32x3(prad_ctx*, bool, bool, int, int, int, double, const void*, int, const void*,
-                        int, double, void*, int, int, int64_t, int64_t, int64_t,
-                        const GemmEpilogue&, bool) {
-  return PRAD_ERR_UNSUPPORTED;
+
+namespace tc {
+
+constexpr int BM = 128, BN = 256, BK = 32;       // BK floats = 128 bytes
+constexpr int UMMA_K = 8;                        // tf32: 32 bytes per k-slice
+constexpr int STAGES = 2;
+constexpr int A_TILE_BYTES = BM * BK * 4;        // 16 KiB
+constexpr int B_TILE_BYTES = BN * BK * 4;        // 32 KiB
+constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;  // hi + lo of both: 96 KiB
+constexpr int TMEM_COLS = 512;                   // two 128 x 256 FP32 accumulators
+constexpr int CHUNK_KB = 8;                      // k-blocks per accumulation chunk (256 k)
+constexpr int EPI_WARPS = 8;
+constexpr int THREADS = 64 + EPI_WARPS * 32;     // producer warp, MMA warp, epilogue warps
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+
+// ---- raw PTX wrappers -------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
 }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false if it gave up (own limit or somebody else's error flag).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err_flag, int code) {
+  for (uint32_t spins = 0;; ++spins) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spins & 0x3ff) == 0x3ff) {
+      if (*((volatile int*)err_flag) != 0) return false;
+      if (spins >= SPIN_LIMIT) { atomicCAS(err_flag, 0, code); return false; }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the
+// 128-byte swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): 8-row groups are
+// 1024 bytes apart (stride byte offset), the leading byte offset is unused for swizzled
+// K-major layouts, descriptor version 1 (sm_100), layout type 2 = SWIZZLE_128B.
+__device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
+  d |= (uint64_t)1 << 16;                 // leading byte offset (ignored)
+  d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
+  d |= (uint64_t)1 << 46;                 // version
+  d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: D = F32, A = B = TF32, both K-major, M = 128, N = 256.
+__host__ __device__ constexpr uint32_t idesc_tf32() {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+struct Epi {
+  const float* bias;
+  float* z_out;
+  int act;
+  int dact;
+  const float* saved;
+  float act_alpha;
+  float alpha, beta;
+};
+
+// One epilogue thread's share of the finished tile: 32 consecutive columns of one row.
+__device__ __forceinline__ void epilogue_store32(const float (&acc)[32], int row, int col0, int M, int N,
+                                                 float* __restrict__ C, int64_t ldc, bool vecC, const Epi& epi) {
+  if (row >= M || col0 >= N) return;
+  const int64_t off = (int64_t)row * ldc + col0;
+  const bool full = vecC && (col0 + 32 <= N);
+  float out[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) out[j] = epi.alpha * acc[j];
+  if (epi.beta != 0.f) {
+    if (full) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 o = *reinterpret_cast<const float4*>(C + off + j);
+        out[j] = fmaf(epi.beta, o.x, out[j]); out[j + 1] = fmaf(epi.beta, o.y, out[j + 1]);
+        out[j + 2] = fmaf(epi.beta, o.z, out[j + 2]); out[j + 3] = fmaf(epi.beta, o.w, out[j + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) if (col0 + j < N) out[j] = fmaf(epi.beta, C[off + j], out[j]);
+    }
+  }
+  if (epi.bias) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) if (col0 + j < N) out[j] += epi.bias[col0 + j];
+  }
+  if (epi.z_out) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) if (col0 + j < N) epi.z_out[off + j] = out[j];
+  }
+  if (epi.act != PRAD_ACT_NONE) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) out[j] = act_value<float>((prad_act)epi.act, out[j], epi.act_alpha);
+  }
+  if (epi.dact != PRAD_ACT_NONE) {
+    if (full) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 sv = *reinterpret_cast<const float4*>(epi.saved + off + j);
+        out[j] = mul_rn(out[j], act_derivative<float>((prad_act)epi.dact, sv.x, epi.act_alpha));
+        out[j + 1] = mul_rn(out[j + 1], act_derivative<float>((prad_act)epi.dact, sv.y, epi.act_alpha));
+        out[j + 2] = mul_rn(out[j + 2], act_derivative<float>((prad_act)epi.dact, sv.z, epi.act_alpha));
+        out[j + 3] = mul_rn(out[j + 3], act_derivative<float>((prad_act)epi.dact, sv.w, epi.act_alpha));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < N) out[j] = mul_rn(out[j], act_derivative<float>((prad_act)epi.dact, epi.saved[off + j], epi.act_alpha));
+    }
+  }
+  if (full) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4)
+      *reinterpret_cast<float4*>(C + off + j) = make_float4(out[j], out[j + 1], out[j + 2], out[j + 3]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) if (col0 + j < N) C[off + j] = out[j];
+  }
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                   const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                   int M, int N, int K, float* __restrict__ C, int64_t ldc, bool vecC, Epi epi,
+                   int* __restrict__ err_flag) {
+  extern __shared__ uint8_t smem_raw[];
+  // stage buffers must sit on a 1024-byte boundary (swizzle atom = 8 rows x 128 bytes)
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto acc_full = [&](int b) { return bars + 8u * (2 * STAGES + b); };
+  auto acc_empty = [&](int b) { return bars + 8u * (2 * STAGES + 2 + b); };
+  const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 4);
+  uint8_t* generic_base = smem_raw + (base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(generic_base + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 4));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int num_kb = (K + BK - 1) / BK;
+  const int num_chunks = (num_kb + CHUNK_KB - 1) / CHUNK_KB;
+
+  // an earlier CTA gave up: do not start (one read per CTA so that all threads agree)
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) s_abort = *((volatile int*)err_flag);
+  __syncthreads();
+  if (s_abort != 0) return;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), EPI_WARPS); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % STAGES;
+        const uint32_t round = kb / STAGES;
+        if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, err_flag, 1)) break;
+        const uint32_t st = base + s * STAGE_BYTES;
+        mbar_expect_tx(full_bar(s), STAGE_BYTES);
+        tma_load_2d(st, &map_a_hi, full_bar(s), kb * BK, m0);
+        tma_load_2d(st + A_TILE_BYTES, &map_a_lo, full_bar(s), kb * BK, m0);
+        tma_load_2d(st + 2 * A_TILE_BYTES, &map_b_hi, full_bar(s), kb * BK, n0);
+        tma_load_2d(st + 2 * A_TILE_BYTES + B_TILE_BYTES, &map_b_lo, full_bar(s), kb * BK, n0);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    // The tensor core adds each product into the FP32 accumulator with truncation, so a long
+    // accumulation chain drifts towards zero.  The K loop is therefore cut into chunks of
+    // CHUNK_KB k-blocks; each chunk accumulates from zero into one of two TMEM buffers and
+    // the epilogue warps add finished chunks in registers with round-to-nearest.
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_tf32();
+      bool ok = true;
+      for (int ch = 0; ch < num_chunks && ok; ++ch) {
+        const int buf = ch & 1;
+        const uint32_t use = ch >> 1;   // how many times this buffer has been used before
+        if (use > 0) {
+          ok = mbar_wait(acc_empty(buf), (use - 1) & 1, err_flag, 4);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        const int kb_end = min(num_kb, (ch + 1) * CHUNK_KB);
+        for (int kb = ch * CHUNK_KB; kb < kb_end; ++kb) {
+          const int s = kb % STAGES;
+          const uint32_t round = kb / STAGES;
+          ok = mbar_wait(full_bar(s), round & 1, err_flag, 2);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t st = base + s * STAGE_BYTES;
+          const uint64_t a_hi = kmajor_sw128_desc(st);
+          const uint64_t a_lo = kmajor_sw128_desc(st + A_TILE_BYTES);
+          const uint64_t b_hi = kmajor_sw128_desc(st + 2 * A_TILE_BYTES);
+          const uint64_t b_lo = kmajor_sw128_desc(st + 2 * A_TILE_BYTES + B_TILE_BYTES);
+          const bool first_kb = kb == ch * CHUNK_KB;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adv = (uint64_t)((k * UMMA_K * 4) >> 4);   // +32 bytes per k-slice
+            umma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, !(first_kb && k == 0));
+            umma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1);
+            umma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1);
+          }
+          umma_commit(empty_bar(s));   // the stage may be refilled once these MMAs have read it
+        }
+        umma_commit(acc_full(buf));    // chunk complete (arrives even after a give-up)
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..9)
+    const int sub = warp & 3;                 // TMEM sub-partition this warp may read
+    const int half = (warp - 2) >> 2;         // which 128 columns of the tile
+    const int row = m0 + sub * 32 + lane;
+    float sum[4][32];
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+#pragma unroll
+      for (int j = 0; j < 32; ++j) sum[g][j] = 0.f;
+    bool ok = true;
+    for (int ch = 0; ch < num_chunks && ok; ++ch) {
+      const int buf = ch & 1;
+      ok = mbar_wait(acc_full(buf), (ch >> 1) & 1, err_flag, 3);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + (uint32_t)(buf * BN + half * 128);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint32_t v[32];
+        tmem_ld32(taddr + (uint32_t)(g * 32), v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) sum[g][j] = __fadd_rn(sum[g][j], __uint_as_float(v[j]));
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty(buf));
+    }
+    if (ok && *((volatile int*)err_flag) == 0) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+        epilogue_store32(sum[g], row, n0 + half * 128 + g * 32, M, N, C, ldc, vecC, epi);
+    }
+  }
+
+  // drain: nobody leaves while tensor-core work or bulk copies of this CTA may be in flight.
+  // In the normal path every issued TMA load was consumed by an MMA and every MMA was
+  // waited for through acc_full before the last chunk was read.
+  tc_fence_before();
+  __syncthreads();
+  if (*((volatile int*)err_flag) != 0) {
+    // give-up path: bulk copies or MMAs issued before the give-up may still be running;
+    // they finish within microseconds, so a fixed, bounded pause covers them
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- operand preparation: hi/lo split (optionally transposing) into K-major scratch -----
+__device__ __forceinline__ float to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+// src is rows x cols (ld = src_ld); dst_hi/dst_lo are rows x dst_ld with the same orientation
+__global__ void __launch_bounds__(256)
+split_kernel(const float* __restrict__ src, int64_t src_ld, float* __restrict__ hi, float* __restrict__ lo,
+             int64_t dst_ld, int rows, int cols) {
+  const int64_t total = (int64_t)rows * (dst_ld / 4);
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const bool vec = ((src_ld & 3) == 0) && (((uintptr_t)src & 15) == 0);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int r = (int)(i / (dst_ld / 4));
+    const int c = (int)(i % (dst_ld / 4)) * 4;
+    float x[4];
+    if (vec && c + 4 <= cols) {
+      float4 v = *reinterpret_cast<const float4*>(src + (int64_t)r * src_ld + c);
+      x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) x[q] = (c + q < cols) ? src[(int64_t)r * src_ld + c + q] : 0.f;
+    }
+    float h[4], l[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) { h[q] = to_tf32(x[q]); l[q] = to_tf32(x[q] - h[q]); }
+    *reinterpret_cast<float4*>(hi + (int64_t)r * dst_ld + c) = make_float4(h[0], h[1], h[2], h[3]);
+    *reinterpret_cast<float4*>(lo + (int64_t)r * dst_ld + c) = make_float4(l[0], l[1], l[2], l[3]);
+  }
+}
+// src is rows x cols; dst is cols x dst_ld (transposed), dst_ld >= rows
+__global__ void __launch_bounds__(256)
+split_transpose_kernel(const float* __restrict__ src, int64_t src_ld, float* __restrict__ hi,
+                       float* __restrict__ lo, int64_t dst_ld, int rows, int cols) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
+  const int c = blockIdx.x * 32 + tx;
+#pragma unroll
+  for (int j = ty; j < 32; j += 8) {
+    const int r = blockIdx.y * 32 + j;
+    tile[j][tx] = (r < rows && c < cols) ? src[(int64_t)r * src_ld + c] : 0.f;
+  }
+  __syncthreads();
+  const int r2 = blockIdx.y * 32 + tx;   // fast index of dst
+#pragma unroll
+  for (int j = ty; j < 32; j += 8) {
+    const int c2 = blockIdx.x * 32 + j;
+    if (c2 < cols && r2 < dst_ld) {
+      const float x = tile[tx][j];       // zero beyond `rows` (padding columns of dst)
+      const float h = to_tf32(x);
+      hi[(int64_t)c2 * dst_ld + r2] = h;
+      lo[(int64_t)c2 * dst_ld + r2] = to_tf32(x - h);
+    }
+  }
+}
+
+// ---- host side --------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+    else
+      (void)cudaGetLastError();
+  });
+  return fn;
+}
+
+// K-major operand: `rows` rows of `k` floats, row pitch ld floats (ld % 4 == 0)
+static bool make_map(CUtensorMap* map, const float* ptr, int rows, int k, int64_t ld, int box_rows) {
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)ptr, dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+}  // namespace tc
+
+prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, double alpha,
+                        const void* A, int lda, const void* B, int ldb, double beta, void* C,
+                        int ldc, int batch, int64_t sA, int64_t sB, int64_t sC,
+                        const GemmEpilogue& e, bool probe_only) {
+  using namespace tc;
+  (void)sA; (void)sB; (void)sC;
+  // shapes this kernel is meant for; everything else stays on the SIMT variant
+  const bool forced = ctx->gemm_f32 == GemmF32::Tf32x3;
+  const bool big = (int64_t)M * N * K >= ((int64_t)1 << 27) && M >= BM && N >= 128 && K >= BK;
+  if (batch != 1 || K < 1 || !(big || forced) || encode_fn() == nullptr) {
+    if (probe_only || !forced) return PRAD_ERR_UNSUPPORTED;
+    set_error("gemm tf32x3: unsupported shape (batch %d) or driver without cuTensorMapEncodeTiled", batch);
+    return PRAD_ERR_UNSUPPORTED;
+  }
+  if (probe_only) return PRAD_OK;
+
+  static std::once_flag attr_once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(attr_once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  });
+  PRAD_REQUIRE(attr_err == cudaSuccess, PRAD_ERR_CUDA, "gemm tf32x3: cannot reserve %d bytes of shared memory: %s",
+               SMEM_BYTES, cudaGetErrorString(attr_err));
+
+  // scratch: [A_hi | A_lo | B_hi | B_lo], operands K-major with pitch kp
+  const int64_t kp = ceil_div(K, BK) * BK;
+  const size_t a_elems = (size_t)M * kp, b_elems = (size_t)N * kp;
+  const size_t need = 2 * (a_elems + b_elems) * sizeof(float);
+  prad_status s = ensure_workspace(ctx, need);
+  if (s) return s;
+  int* err_flag = ctx->tc_err;
+  float* a_hi = (float*)ctx->ws;
+  float* a_lo = a_hi + a_elems;
+  float* b_hi = a_lo + a_elems;
+  float* b_lo = b_hi + b_elems;
+
+  const float* Af = (const float*)A;
+  const float* Bf = (const float*)B;
+  // op(A) is M x K.  !tA: memory already M x K (k contiguous).  tA: memory is K x M.
+  if (!tA) {
+    int grid = stream_grid(ctx, (int64_t)M * (kp / 4), 256, 8);
+    split_kernel<<<grid, 256, 0, ctx->stream>>>(Af, lda, a_hi, a_lo, kp, M, K);
+  } else {
+    dim3 grid((unsigned)ceil_div(M, 32), (unsigned)ceil_div(kp, 32));
+    split_transpose_kernel<<<grid, 256, 0, ctx->stream>>>(Af, lda, a_hi, a_lo, kp, K, M);
+  }
+  PRAD_LAUNCHED(ctx);
+  // op(B) is K x N; the kernel wants B^T = N x K (k contiguous).  tB: memory is N x K already.
+  if (tB) {
+    int grid = stream_grid(ctx, (int64_t)N * (kp / 4), 256, 8);
+    split_kernel<<<grid, 256, 0, ctx->stream>>>(Bf, ldb, b_hi, b_lo, kp, N, K);
+  } else {
+    dim3 grid((unsigned)ceil_div(N, 32), (unsigned)ceil_div(kp, 32));
+    split_transpose_kernel<<<grid, 256, 0, ctx->stream>>>(Bf, ldb, b_hi, b_lo, kp, K, N);
+  }
+  PRAD_LAUNCHED(ctx);
+
+  CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
+  bool ok = make_map(&ma_hi, a_hi, M, (int)kp, kp, BM) && make_map(&ma_lo, a_lo, M, (int)kp, kp, BM) &&
+            make_map(&mb_hi, b_hi, N, (int)kp, kp, BN) && make_map(&mb_lo, b_lo, N, (int)kp, kp, BN);
+  PRAD_REQUIRE(ok, PRAD_ERR_CUDA, "gemm tf32x3: cuTensorMapEncodeTiled failed (M %d N %d K %d)", M, N, K);
+
+  Epi epi{(const float*)e.bias, (float*)e.z_out, (int)e.act, (int)e.dact, (const float*)e.saved,
+          (float)e.act_alpha, (float)alpha, (float)beta};
+  const bool vecC = (((uintptr_t)C & 15) == 0) && (ldc % 4 == 0) &&
+                    (!e.saved || ((uintptr_t)e.saved & 15) == 0);
+  dim3 grid((unsigned)ceil_div(N, BN), (unsigned)ceil_div(M, BM));
+  PRAD_REQUIRE(grid.y <= 65535, PRAD_ERR_UNSUPPORTED, "gemm tf32x3: too many row tiles (%u)", grid.y);
+  gemm_tf32x3_kernel<<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, M, N, (int)kp,
+                                                                (float*)C, ldc, vecC, epi, err_flag);
+  PRAD_LAUNCHED(ctx);
+  ctx->tc_pending_check = true;
+  return PRAD_OK;
+}
+
+// Reads the give-up flag of the most recent tensor-core GEMMs (called by prad_sync).
+prad_status gemm_tf32x3_check(prad_ctx* ctx) {
+  if (!ctx->tc_pending_check || !ctx->tc_err) return PRAD_OK;
+  ctx->tc_pending_check = false;
+  int flag = 0;
+  PRAD_CUDA(cudaMemcpyAsync(&flag, ctx->tc_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+  PRAD_CUDA(cudaStreamSynchronize(ctx->stream));
+  if (flag != 0) PRAD_CUDA(cudaMemsetAsync(ctx->tc_err, 0, sizeof(int), ctx->stream));
+  PRAD_REQUIRE(flag == 0, PRAD_ERR_TIMEOUT,
+               "gemm tf32x3: a bounded wait ran out inside the kernel (role %d: 1 producer, 2 MMA, 3 epilogue); "
+               "the results of that product are invalid", flag);
+  return PRAD_OK;
+}
+
 }  // namespace prad

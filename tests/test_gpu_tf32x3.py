@@ -1,0 +1,89 @@
+"""The tensor-core FP32 GEMM (3xTF32 on tcgen05) against the CPU oracle, forced on for shapes
+of every raggedness, for all transpose forms and the fused epilogues."""
+import numpy as np
+import pytest
+
+import oracle as O
+from parallelreverseautodiff_b200 import engine as E
+from util import assert_close, normal, rng, uniform
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def tc_engine(engine):
+    engine.set_option("gemm_f32", "tf32x3")
+    yield engine
+    engine.set_option("gemm_f32", "auto")
+
+
+SHAPES = [(128, 32, 256), (128, 64, 256), (256, 96, 512), (200, 70, 300), (129, 33, 257),
+          (1, 5, 3), (384, 1000, 130), (512, 784, 256)]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_tf32x3_matmul_forward_backward(tc_engine, shape):
+    eng = tc_engine
+    M, K, N = shape
+    r = rng(sum(shape))
+    A = uniform(r, (M, K), -1, 1, np.float32)
+    B = normal(r, (K, N), np.sqrt(2.0 / K), np.float32)
+    dC = normal(r, (M, N), 1.0, np.float32)
+    a, b, dc = eng.upload(A), eng.upload(B), eng.upload(dC)
+    n0 = eng.launch_count()
+    C = eng.matmul_forward(a, b).numpy()
+    dA, dB = eng.matmul_backward(a, b, dc)
+    assert eng.launch_count() - n0 == 9          # 3 products x (2 operand splits + 1 GEMM)
+    assert_close(C, O.matmul_forward(A, B), np.abs(A).astype(np.float64) @ np.abs(B), "C")
+    dA_ref, dB_ref = O.matmul_backward(A, B, dC)
+    assert_close(dA.numpy(), dA_ref, np.abs(dC).astype(np.float64) @ np.abs(B.T), "dA")
+    assert_close(dB.numpy(), dB_ref, np.abs(A.T).astype(np.float64) @ np.abs(dC), "dB")
+
+
+def test_tf32x3_is_as_accurate_as_fp32_fma(tc_engine):
+    """Error against an exact (float64) product is of FP32 size, not of TF32 size."""
+    eng = tc_engine
+    r = rng(1)
+    M, K, N = 256, 2048, 256
+    A, B = normal(r, (M, K), 1, np.float32), normal(r, (K, N), 1, np.float32)
+    exact = A.astype(np.float64) @ B.astype(np.float64)
+    got = eng.matmul_forward(eng.upload(A), eng.upload(B)).numpy().astype(np.float64)
+    rel = np.abs(got - exact).max() / np.abs(exact).max()
+    assert rel < 5e-6, rel          # plain TF32 would be ~1e-3
+
+
+def test_tf32x3_epilogues(tc_engine):
+    eng = tc_engine
+    r = rng(2)
+    M, K, N = 256, 160, 384
+    Zb = normal(r, (M, K), 1.0, np.float32)
+    A = O.gelu_forward(Zb)
+    B = normal(r, (K, N), 0.1, np.float32)
+    dC = normal(r, (M, N), 1.0, np.float32)
+    dA_ref, dB_ref = O.matmul_backward(A, B, dC)
+    dZ, _ = eng.matmul_backward(eng.upload(A), eng.upload(B), eng.upload(dC), need_dB=False,
+                                act_below=E.ACT_GELU, saved_below=eng.upload(Zb))
+    bound = (np.abs(dC).astype(np.float64) @ np.abs(B.T)) * 1.2
+    assert_close(dZ.numpy(), O.gelu_backward(Zb, dA_ref), bound, "dA * gelu'")
+    dest = normal(r, (K, N), 1, np.float32)
+    d = eng.upload(dest)
+    eng.matmul_backward(eng.upload(A), eng.upload(B), eng.upload(dC), dB=d, need_dA=False,
+                        accumulate_dB=True, dB_scale=0.5)
+    assert_close(d.numpy(), (dest + dB_ref * np.float32(0.5)).astype(np.float32),
+                 np.abs(A.T).astype(np.float64) @ np.abs(dC) + np.abs(dest), "dB accumulate")
+    bias = normal(r, (1, N), 1, np.float32)
+    Zf = eng.empty((M, N), np.float32)
+    Y = eng.matmul_forward(eng.upload(A), eng.upload(B), bias=eng.upload(bias), Z_out=Zf,
+                           act=E.ACT_LEAKY_RELU, act_alpha=0.01)
+    z_ref = O.add_broadcast_forward(O.matmul_forward(A, B), bias)
+    bound = np.abs(A).astype(np.float64) @ np.abs(B) + 1.0
+    assert_close(Zf.numpy(), z_ref, bound, "Z")
+    assert_close(Y.numpy(), O.leaky_relu_forward(z_ref, 0.01), bound, "Y")
+
+
+def test_tf32x3_deterministic(tc_engine):
+    eng = tc_engine
+    r = rng(3)
+    A, B = normal(r, (300, 200), 1, np.float32), normal(r, (200, 280), 1, np.float32)
+    a, b = eng.upload(A), eng.upload(B)
+    np.testing.assert_array_equal(eng.matmul_forward(a, b).numpy(), eng.matmul_forward(a, b).numpy())
