@@ -70,7 +70,8 @@ prad_status prad_shutdown(prad_ctx* ctx);
 const char* prad_last_error(void);
 /* library version string and the sm architecture it was built for */
 const char* prad_version(void);
-/* options: "gemm_f32" = "auto" | "simt" | "tf32x3" ; "gemm_f64" = "auto" | "simt" | "dmma" */
+/* options: "gemm_f32" = "auto" | "simt" | "tf32x3" ; "gemm_f64" = "auto" | "simt" | "dmma" ;
+ * "tc_pipeline" = "16x4" | "32x2" | "8x8" (k-block floats x stages of the tensor-core GEMM) */
 prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value);
 /* wait for everything enqueued on the context (what the managed code gets for free
  * because GetAsArray2D blocks, src/RMAD/GpuMatrixMultiplyOperation.cs:199-201) */

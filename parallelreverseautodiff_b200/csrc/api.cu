@@ -141,6 +141,13 @@ prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value) {
     else { set_error("prad_set_option: gemm_f64 must be auto|simt|dmma, got '%s'", value); return PRAD_ERR_INVALID; }
     return PRAD_OK;
   }
+  if (!strcmp(key, "tc_pipeline")) {  // tensor-core GEMM pipeline: k-block floats x stages
+    if (!strcmp(value, "16x4")) ctx->tc_variant = 0;
+    else if (!strcmp(value, "32x2")) ctx->tc_variant = 1;
+    else if (!strcmp(value, "8x8")) ctx->tc_variant = 2;
+    else { set_error("prad_set_option: tc_pipeline must be 32x2|16x4|8x8, got '%s'", value); return PRAD_ERR_INVALID; }
+    return PRAD_OK;
+  }
   set_error("prad_set_option: unknown key '%s'", key);
   return PRAD_ERR_INVALID;
 }

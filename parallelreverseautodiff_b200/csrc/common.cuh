@@ -42,6 +42,7 @@ struct prad_ctx {
   // give-up flag of the tensor-core GEMMs (device int, sticky until the host reads it)
   int* tc_err = nullptr;
   bool tc_pending_check = false;
+  int tc_variant = 0;  // pipeline shape of the tensor-core GEMM (option "tc_pipeline")
   uint32_t magic = 0x50524144u;  // "PRAD"
 };
 

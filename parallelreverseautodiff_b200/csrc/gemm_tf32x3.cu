@@ -4,12 +4,12 @@
 // accumulated in FP32 in tensor memory.  The dropped a_lo*b_lo term is ~2^-22 relative, so
 // the result matches an FP32 FMA chain to well inside the 1e-5 PRADLite tolerance.
 //
-// Structure of one CTA (320 threads, one 128 x 256 output tile, BK = 32 floats = one
-// 128-byte swizzle atom):
+// Structure of one CTA (320 threads, one 128 x 256 output tile; a k-block is one swizzle
+// atom wide, by default 16 floats = 64 bytes with 4 stages in flight):
 //   warp 0     TMA producer: cp.async.bulk.tensor loads of the four operand tiles of a
 //              k-block (A_hi, A_lo, B_hi, B_lo) into a ring of shared-memory stages;
 //   warp 1     allocates tensor memory, then one lane issues tcgen05.mma (kind::tf32,
-//              M=128, N=256, K=8): 4 k-slices x 3 products per stage, releases the stage
+//              M=128, N=256, K=8): 3 products per 8-wide k-slice of a stage, releases the stage
 //              with tcgen05.commit, and finally signals the accumulator;
 //   warps 2-9  epilogue: after every chunk of 256 k they tcgen05.ld that chunk's 128 x 256
 //              accumulator (each warp its own 32-lane TMEM sub-partition and half of the
@@ -35,17 +35,27 @@ namespace prad {
 
 namespace tc {
 
-constexpr int BM = 128, BN = 256, BK = 32;       // BK floats = 128 bytes
+constexpr int BM = 128, BN = 256;
+constexpr int KPAD = 32;                         // operands are padded to a multiple of this in k
 constexpr int UMMA_K = 8;                        // tf32: 32 bytes per k-slice
-constexpr int STAGES = 2;
-constexpr int A_TILE_BYTES = BM * BK * 4;        // 16 KiB
-constexpr int B_TILE_BYTES = BN * BK * 4;        // 32 KiB
-constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;  // hi + lo of both: 96 KiB
 constexpr int TMEM_COLS = 512;                   // two 128 x 256 FP32 accumulators
-constexpr int CHUNK_KB = 8;                      // k-blocks per accumulation chunk (256 k)
+constexpr int CHUNK_K = 256;                     // k per accumulation chunk
 constexpr int EPI_WARPS = 8;
 constexpr int THREADS = 64 + EPI_WARPS * 32;     // producer warp, MMA warp, epilogue warps
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+// Pipeline shape: a k-block of BK floats is one swizzle atom wide (BK*4 = 128, 64 or 32
+// bytes); STAGES k-blocks of the four operand tiles (A_hi, A_lo, B_hi, B_lo) are in flight.
+template <int BK_, int STAGES_> struct Cfg {
+  static constexpr int BK = BK_, STAGES = STAGES_;
+  static constexpr int SWIZZLE_BYTES = BK * 4;
+  static constexpr int A_TILE_BYTES = BM * BK * 4;
+  static constexpr int B_TILE_BYTES = BN * BK * 4;
+  static constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;
+  static constexpr int CHUNK_KB = CHUNK_K / BK;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static_assert(SWIZZLE_BYTES == 128 || SWIZZLE_BYTES == 64 || SWIZZLE_BYTES == 32, "BK must be 32, 16 or 8");
+  static_assert(SMEM_BYTES <= 227 * 1024, "stages do not fit in shared memory");
+};
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 // ---- raw PTX wrappers -------------------------------------------------------------------
@@ -119,17 +129,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor of a K-major tile stored as rows of 128 bytes with the
-// 128-byte swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): 8-row groups are
-// 1024 bytes apart (stride byte offset), the leading byte offset is unused for swizzled
-// K-major layouts, descriptor version 1 (sm_100), layout type 2 = SWIZZLE_128B.
-__device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t smem_addr) {
+// Shared-memory matrix descriptor of a K-major tile stored as rows of SW bytes (SW = 128, 64
+// or 32) with the SW-byte swizzle, i.e. what TMA writes with CU_TENSOR_MAP_SWIZZLE_{SW}B:
+// 8-row groups are 8*SW bytes apart (stride byte offset), the leading byte offset is unused
+// for swizzled K-major layouts, descriptor version 1 (sm_100), layout type 2 / 4 / 6 for
+// the 128 / 64 / 32-byte swizzle.
+template <int SW>
+__device__ __forceinline__ uint64_t kmajor_desc(uint32_t smem_addr) {
+  constexpr uint64_t layout = SW == 128 ? 2 : (SW == 64 ? 4 : 6);
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
   d |= (uint64_t)1 << 16;                 // leading byte offset (ignored)
-  d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
+  d |= (uint64_t)((8 * SW) >> 4) << 32;   // stride byte offset
   d |= (uint64_t)1 << 46;                 // version
-  d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+  d |= layout << 61;
   return d;
 }
 // Instruction descriptor: D = F32, A = B = TF32, both K-major, M = 128, N = 256.
@@ -207,11 +220,15 @@ __device__ __forceinline__ void epilogue_store32(const float (&acc)[32], int row
   }
 }
 
+template <class CFG>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                    const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
                    int M, int N, int K, float* __restrict__ C, int64_t ldc, bool vecC, Epi epi,
                    int* __restrict__ err_flag) {
+  constexpr int BK = CFG::BK, STAGES = CFG::STAGES, STAGE_BYTES = CFG::STAGE_BYTES;
+  constexpr int A_TILE_BYTES = CFG::A_TILE_BYTES, B_TILE_BYTES = CFG::B_TILE_BYTES;
+  constexpr int CHUNK_KB = CFG::CHUNK_KB, SW = CFG::SWIZZLE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   // stage buffers must sit on a 1024-byte boundary (swizzle atom = 8 rows x 128 bytes)
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -291,10 +308,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
           if (!ok) break;
           tc_fence_after();
           const uint32_t st = base + s * STAGE_BYTES;
-          const uint64_t a_hi = kmajor_sw128_desc(st);
-          const uint64_t a_lo = kmajor_sw128_desc(st + A_TILE_BYTES);
-          const uint64_t b_hi = kmajor_sw128_desc(st + 2 * A_TILE_BYTES);
-          const uint64_t b_lo = kmajor_sw128_desc(st + 2 * A_TILE_BYTES + B_TILE_BYTES);
+          const uint64_t a_hi = kmajor_desc<SW>(st);
+          const uint64_t a_lo = kmajor_desc<SW>(st + A_TILE_BYTES);
+          const uint64_t b_hi = kmajor_desc<SW>(st + 2 * A_TILE_BYTES);
+          const uint64_t b_lo = kmajor_desc<SW>(st + 2 * A_TILE_BYTES + B_TILE_BYTES);
           const bool first_kb = kb == ch * CHUNK_KB;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
@@ -440,15 +457,43 @@ static EncodeTiledFn encode_fn() {
 }
 
 // K-major operand: `rows` rows of `k` floats, row pitch ld floats (ld % 4 == 0)
-static bool make_map(CUtensorMap* map, const float* ptr, int rows, int k, int64_t ld, int box_rows) {
+static bool make_map(CUtensorMap* map, const float* ptr, int rows, int k, int64_t ld, int box_rows, int bk) {
   cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {(cuuint32_t)bk, (cuuint32_t)box_rows};
+  CUtensorMapSwizzle sw = bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : (bk == 16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
   cuuint32_t estr[2] = {1, 1};
   CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)ptr, dims, strides, box, estr,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
+}
+
+
+
+template <class CFG>
+static prad_status launch_tf32x3(prad_ctx* ctx, const float* a_hi, const float* a_lo, const float* b_hi,
+                                 const float* b_lo, int M, int N, int64_t kp, float* C, int64_t ldc,
+                                 bool vecC, const Epi& epi) {
+  static std::once_flag attr_once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(attr_once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_tf32x3_kernel<CFG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    CFG::SMEM_BYTES);
+  });
+  PRAD_REQUIRE(attr_err == cudaSuccess, PRAD_ERR_CUDA, "gemm tf32x3: cannot reserve %d bytes of shared memory: %s",
+               CFG::SMEM_BYTES, cudaGetErrorString(attr_err));
+  CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
+  bool ok = make_map(&ma_hi, a_hi, M, (int)kp, kp, BM, CFG::BK) && make_map(&ma_lo, a_lo, M, (int)kp, kp, BM, CFG::BK) &&
+            make_map(&mb_hi, b_hi, N, (int)kp, kp, BN, CFG::BK) && make_map(&mb_lo, b_lo, N, (int)kp, kp, BN, CFG::BK);
+  PRAD_REQUIRE(ok, PRAD_ERR_CUDA, "gemm tf32x3: cuTensorMapEncodeTiled failed (M %d N %d K %lld)", M, N, (long long)kp);
+  dim3 grid((unsigned)ceil_div(N, BN), (unsigned)ceil_div(M, BM));
+  PRAD_REQUIRE(grid.y <= 65535, PRAD_ERR_UNSUPPORTED, "gemm tf32x3: too many row tiles (%u)", grid.y);
+  gemm_tf32x3_kernel<CFG><<<grid, THREADS, CFG::SMEM_BYTES, ctx->stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, M, N, (int)kp,
+                                                                         C, ldc, vecC, epi, ctx->tc_err);
+  PRAD_LAUNCHED(ctx);
+  ctx->tc_pending_check = true;
+  return PRAD_OK;
 }
 
 }  // namespace tc
@@ -461,7 +506,7 @@ prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, do
   (void)sA; (void)sB; (void)sC;
   // shapes this kernel is meant for; everything else stays on the SIMT variant
   const bool forced = ctx->gemm_f32 == GemmF32::Tf32x3;
-  const bool big = (int64_t)M * N * K >= ((int64_t)1 << 27) && M >= BM && N >= 128 && K >= BK;
+  const bool big = (int64_t)M * N * K >= ((int64_t)1 << 27) && M >= BM && N >= 128 && K >= KPAD;
   if (batch != 1 || K < 1 || !(big || forced) || encode_fn() == nullptr) {
     if (probe_only || !forced) return PRAD_ERR_UNSUPPORTED;
     set_error("gemm tf32x3: unsupported shape (batch %d) or driver without cuTensorMapEncodeTiled", batch);
@@ -469,21 +514,12 @@ prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, do
   }
   if (probe_only) return PRAD_OK;
 
-  static std::once_flag attr_once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(attr_once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-  });
-  PRAD_REQUIRE(attr_err == cudaSuccess, PRAD_ERR_CUDA, "gemm tf32x3: cannot reserve %d bytes of shared memory: %s",
-               SMEM_BYTES, cudaGetErrorString(attr_err));
-
   // scratch: [A_hi | A_lo | B_hi | B_lo], operands K-major with pitch kp
-  const int64_t kp = ceil_div(K, BK) * BK;
+  const int64_t kp = ceil_div(K, KPAD) * KPAD;
   const size_t a_elems = (size_t)M * kp, b_elems = (size_t)N * kp;
   const size_t need = 2 * (a_elems + b_elems) * sizeof(float);
   prad_status s = ensure_workspace(ctx, need);
   if (s) return s;
-  int* err_flag = ctx->tc_err;
   float* a_hi = (float*)ctx->ws;
   float* a_lo = a_hi + a_elems;
   float* b_hi = a_lo + a_elems;
@@ -510,22 +546,15 @@ prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, do
   }
   PRAD_LAUNCHED(ctx);
 
-  CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
-  bool ok = make_map(&ma_hi, a_hi, M, (int)kp, kp, BM) && make_map(&ma_lo, a_lo, M, (int)kp, kp, BM) &&
-            make_map(&mb_hi, b_hi, N, (int)kp, kp, BN) && make_map(&mb_lo, b_lo, N, (int)kp, kp, BN);
-  PRAD_REQUIRE(ok, PRAD_ERR_CUDA, "gemm tf32x3: cuTensorMapEncodeTiled failed (M %d N %d K %d)", M, N, K);
-
   Epi epi{(const float*)e.bias, (float*)e.z_out, (int)e.act, (int)e.dact, (const float*)e.saved,
           (float)e.act_alpha, (float)alpha, (float)beta};
   const bool vecC = (((uintptr_t)C & 15) == 0) && (ldc % 4 == 0) &&
                     (!e.saved || ((uintptr_t)e.saved & 15) == 0);
-  dim3 grid((unsigned)ceil_div(N, BN), (unsigned)ceil_div(M, BM));
-  PRAD_REQUIRE(grid.y <= 65535, PRAD_ERR_UNSUPPORTED, "gemm tf32x3: too many row tiles (%u)", grid.y);
-  gemm_tf32x3_kernel<<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, M, N, (int)kp,
-                                                                (float*)C, ldc, vecC, epi, err_flag);
-  PRAD_LAUNCHED(ctx);
-  ctx->tc_pending_check = true;
-  return PRAD_OK;
+  switch (ctx->tc_variant) {
+    case 1: return launch_tf32x3<Cfg<32, 2>>(ctx, a_hi, a_lo, b_hi, b_lo, M, N, kp, (float*)C, ldc, vecC, epi);
+    case 2: return launch_tf32x3<Cfg<8, 8>>(ctx, a_hi, a_lo, b_hi, b_lo, M, N, kp, (float*)C, ldc, vecC, epi);
+    default: return launch_tf32x3<Cfg<16, 4>>(ctx, a_hi, a_lo, b_hi, b_lo, M, N, kp, (float*)C, ldc, vecC, epi);
+  }
 }
 
 // Reads the give-up flag of the most recent tensor-core GEMMs (called by prad_sync).
