@@ -1,0 +1,85 @@
+"""Data parallel on real GPUs (needs >= 2): two ranks, one process per GPU, NCCL all-reduce of
+the weight gradients through prad_dp_*; the reduced gradients and the updated weights must
+match the single-process CPU oracle on the whole batch.  Skipped on a one-GPU box."""
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, id_path, out_dir):
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import time
+
+    from parallelreverseautodiff_b200 import engine as E
+    from parallelreverseautodiff_b200.networks import FeedForwardNetwork, row_shard
+
+    eng = E.Engine(rank)
+    if rank == 0:
+        uid = E.Engine.dp_unique_id()
+        with open(id_path + ".tmp", "wb") as f:
+            f.write(uid)
+        os.replace(id_path + ".tmp", id_path)
+    else:
+        for _ in range(600):
+            if os.path.exists(id_path):
+                break
+            time.sleep(0.05)
+        uid = open(id_path, "rb").read()
+    eng.dp_init(uid, rank, world)
+    r = np.random.default_rng(42)
+    batch, sizes = 96, [40, 64, 24]
+    x = r.standard_normal((batch, sizes[0])).astype(np.float32)
+    t = r.standard_normal((batch, sizes[-1])).astype(np.float32)
+    Ws = [(r.standard_normal((sizes[i], sizes[i + 1])) * np.sqrt(2.0 / sizes[i])).astype(np.float32) for i in range(2)]
+    net = FeedForwardNetwork(eng, np.float32, sizes, hidden_act=E.ACT_GELU, output_act=E.ACT_GELU, loss="mse",
+                             use_bias=True, clip_mode=E.CLIP_REFERENCE, rank=rank, world=world)
+    net.set_weights(Ws)
+    a, b = row_shard(batch, rank, world)
+    net._ensure_buffers(b - a)
+    eng.upload(x[a:b], out=net.A[0])
+    eng.upload(t[a:b], out=net.target)
+    net.forward()
+    net.backward(rows_total=batch)
+    grads = [g.numpy() for g in net.grads]
+    net.clip_and_optimize(zero_grad=False)
+    weights = [w.numpy() for w in net.params]
+    np.savez(os.path.join(out_dir, f"rank{rank}.npz"), *grads, *weights)
+    eng.dp_shutdown()
+    eng.close()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_gradients_match_oracle(tmp_path):
+    import oracle as O
+
+    world = 2
+    mp.spawn(_worker, args=(world, str(tmp_path / "nccl_id"), str(tmp_path)), nprocs=world, join=True)
+    r = np.random.default_rng(42)
+    batch, sizes = 96, [40, 64, 24]
+    x = r.standard_normal((batch, sizes[0])).astype(np.float32)
+    t = r.standard_normal((batch, sizes[-1])).astype(np.float32)
+    Ws = [(r.standard_normal((sizes[i], sizes[i + 1])) * np.sqrt(2.0 / sizes[i])).astype(np.float32) for i in range(2)]
+    acts, pres = [x], []
+    for W in Ws:
+        z = O.add_broadcast_forward(O.matmul_forward(acts[-1], W), np.zeros((1, W.shape[1]), np.float32))
+        pres.append(z)
+        acts.append(O.gelu_forward(z))
+    d = O.mse_backward(acts[-1], t)
+    dW, db = [None, None], [None, None]
+    for l in (1, 0):
+        d = O.gelu_backward(pres[l], d)
+        db[l] = O.add_broadcast_backward(d)[1]
+        dA, dW[l] = O.matmul_backward(acts[l], Ws[l], d)
+        d = dA
+    ref = dW + db
+    r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
+    for k in r0.files:
+        np.testing.assert_array_equal(r0[k], r1[k])          # ranks hold identical results
+    for i, g in enumerate(ref):
+        got = r0[f"arr_{i}"]
+        assert np.abs(got - g).max() <= 1e-5 * np.abs(g).max() + 1e-7, i
