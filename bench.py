@@ -45,6 +45,9 @@ def parse():
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--clip", default="reference", choices=["reference", "global_norm", "none"])
     ap.add_argument("--gemm", default="auto", choices=["auto", "simt", "tf32x3"])
+    ap.add_argument("--lr", type=float, default=1e-5,
+                    help="Adam learning rate (1e-3, the reference default, makes this 8-layer GELU net "
+                         "diverge within ten steps on random targets; the arithmetic per step is the same)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU baseline sample budget")
     return ap.parse_args()
@@ -209,6 +212,7 @@ def run_native(args, rank, world, local_rank):
     sizes = [args.width] * (args.layers + 1)
     net = FeedForwardNetwork(eng, np.float32, sizes, hidden_act=E.ACT_GELU, output_act=E.ACT_GELU,
                              loss="mse", use_bias=False, clip_mode=clip, rank=rank, world=world)
+    net.Parameters.LearningRate = args.lr
     wr = np.random.default_rng(42)  # identical weights on every rank
     net.set_weights([(wr.standard_normal((args.width, args.width), dtype=np.float32)
                       * np.float32(np.sqrt(2.0 / args.width))) for _ in range(args.layers)])
@@ -299,7 +303,7 @@ def run_native(args, rank, world, local_rank):
             "config": {"workload": f"C5 data-parallel MLP {args.layers}x({args.width}x{args.width}, GELU), "
                                    f"MSE, global batch {args.batch}, clip={args.clip} + Adam",
                        "global_batch": args.batch, "rows_per_gpu": rows, "parallelism": f"dp{world}",
-                       "gemm": args.gemm, "l2": "inputs larger than L2 (activations >= 1 GiB per layer)"},
+                       "gemm": args.gemm, "lr": args.lr, "l2": "inputs larger than L2 (activations >= 1 GiB per layer)"},
             "tflops": flops_step / (ms_step * 1e-3) / 1e12,
             "roofline": {"bound": "tensor", "achieved": achieved_tflops, "peak": peaks["tensor_tflops"],
                          "unit": "TFLOP/s",

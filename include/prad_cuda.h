@@ -70,7 +70,13 @@ prad_status prad_shutdown(prad_ctx* ctx);
 const char* prad_last_error(void);
 /* library version string and the sm architecture it was built for */
 const char* prad_version(void);
-/* options: "gemm_f32" = "auto" | "simt" | "tf32x3" ; "gemm_f64" = "auto" | "simt" | "dmma" ;
+/* options:
+ *  "gemm_f32" = "auto" | "simt" | "simt_fma" | "tf32x3"; "gemm_f64" = "auto" | "simt" | "simt_fma" | "dmma"
+ *    simt     : multiply and add rounded separately, k ascending -- bit-identical to the managed
+ *               code's sequential `Output[i][j] += a*b` loop (the default for small products);
+ *    simt_fma : same order with fused multiply-add (twice the rate, one rounding per step);
+ *    tf32x3 / dmma : tensor-core kernels (results within the documented tolerance);
+ *    auto     : tensor-core kernel for large products, "simt" otherwise;
  * "tc_pipeline" = "16x4" | "32x2" | "8x8" (k-block floats x stages of the tensor-core GEMM) */
 prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value);
 /* wait for everything enqueued on the context (what the managed code gets for free
@@ -239,8 +245,9 @@ prad_status prad_layernorm_backward(prad_ctx* ctx, prad_dtype dt, const void* x,
 /* ---------------------------------------------------------------- losses
  * Loss/MeanSquaredErrorLossOperation.cs:37-84 and
  * Loss/CategoricalCrossEntropyLossOperation.cs:37-87.  loss_out is one device scalar.
- * rows_total is the row count used in the normaliser (== rows unless the batch is sharded
- * over several GPUs, where it is the global row count). */
+ * rows_total is the row count used in the normaliser: == rows for one matrix; the global row
+ * count when the batch is sharded over several GPUs; 1 when every row is a separate sample
+ * with its own loss operation (the Batch* graph spelling). */
 prad_status prad_mse_forward(prad_ctx* ctx, prad_dtype dt, const void* out, const void* target,
                              void* loss_out, int64_t rows, int cols);
 prad_status prad_mse_backward(prad_ctx* ctx, prad_dtype dt, const void* out, const void* target,

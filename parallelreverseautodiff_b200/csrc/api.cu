@@ -130,15 +130,17 @@ prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value) {
   if (!strcmp(key, "gemm_f32")) {
     if (!strcmp(value, "auto")) ctx->gemm_f32 = GemmF32::Auto;
     else if (!strcmp(value, "simt")) ctx->gemm_f32 = GemmF32::Simt;
+    else if (!strcmp(value, "simt_fma")) ctx->gemm_f32 = GemmF32::SimtFma;
     else if (!strcmp(value, "tf32x3")) ctx->gemm_f32 = GemmF32::Tf32x3;
-    else { set_error("prad_set_option: gemm_f32 must be auto|simt|tf32x3, got '%s'", value); return PRAD_ERR_INVALID; }
+    else { set_error("prad_set_option: gemm_f32 must be auto|simt|simt_fma|tf32x3, got '%s'", value); return PRAD_ERR_INVALID; }
     return PRAD_OK;
   }
   if (!strcmp(key, "gemm_f64")) {
     if (!strcmp(value, "auto")) ctx->gemm_f64 = GemmF64::Auto;
     else if (!strcmp(value, "simt")) ctx->gemm_f64 = GemmF64::Simt;
+    else if (!strcmp(value, "simt_fma")) ctx->gemm_f64 = GemmF64::SimtFma;
     else if (!strcmp(value, "dmma")) ctx->gemm_f64 = GemmF64::Dmma;
-    else { set_error("prad_set_option: gemm_f64 must be auto|simt|dmma, got '%s'", value); return PRAD_ERR_INVALID; }
+    else { set_error("prad_set_option: gemm_f64 must be auto|simt|simt_fma|dmma, got '%s'", value); return PRAD_ERR_INVALID; }
     return PRAD_OK;
   }
   if (!strcmp(key, "tc_pipeline")) {  // tensor-core GEMM pipeline: k-block floats x stages

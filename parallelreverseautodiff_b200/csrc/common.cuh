@@ -15,8 +15,8 @@ namespace prad {
 
 void set_error(const char* fmt, ...);
 
-enum class GemmF32 { Auto, Simt, Tf32x3 };
-enum class GemmF64 { Auto, Simt, Dmma };
+enum class GemmF32 { Auto, Simt, SimtFma, Tf32x3 };
+enum class GemmF64 { Auto, Simt, SimtFma, Dmma };
 
 struct DpState;  // data-parallel state (dp.cu)
 

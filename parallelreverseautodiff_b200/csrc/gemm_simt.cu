@@ -1,8 +1,10 @@
 // SIMT GEMM family (FP32 FMA / FP64 DFMA): C = alpha*op(A)*op(B) + beta*C, row-major,
 // any M/N/K, strided-batched, with the fused epilogues of the backward path.
 //
-// This is the always-correct variant: it computes every product in the storage precision
-// with FMA accumulation, for all transpose forms the backward needs
+// This is the always-available variant: every product in the storage precision, k ascending,
+// either with separately rounded multiply and add (EXACT: bit-identical to the managed
+// code's sequential `+=` loop, the default) or with FMA accumulation (twice the rate), for
+// all transpose forms the backward needs
 //   NN  C = A*B          MatrixMultiplyOperation.Forward   (MatrixMultiplyOperation.cs:50-80)
 //   NT  dA = dC*B^T      MatrixMultiplyOperation.Backward  (:94-104)
 //   TN  dB = A^T*dC      MatrixMultiplyOperation.Backward  (:110-120)
@@ -95,7 +97,7 @@ struct TileLoader {
   }
 };
 
-template <typename T, int BM, int BN, int BK, int TM, int TN, bool TA, bool TB>
+template <typename T, int BM, int BN, int BK, int TM, int TN, bool TA, bool TB, bool EXACT>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_simt_kernel(int M, int N, int K, T alpha, const T* __restrict__ A, int64_t lda,
                  const T* __restrict__ B, int64_t ldb, T beta, T* __restrict__ C, int64_t ldc,
@@ -166,7 +168,12 @@ gemm_simt_kernel(int M, int N, int K, T alpha, const T* __restrict__ A, int64_t 
 #pragma unroll
       for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[i][j] = fma(a[i], b[j], acc[i][j]);
+        for (int j = 0; j < TN; ++j) {
+          // EXACT: round the product, then the sum, as `Output[i][j] += a * b` does in the
+          // managed code (k ascending), so the result is bit-identical to that loop
+          if (EXACT) acc[i][j] = add_rn(acc[i][j], mul_rn(a[i], b[j]));
+          else acc[i][j] = fma(a[i], b[j], acc[i][j]);
+        }
     }
     if (kt + 1 < ktiles) {
       la.store(As[cur ^ 1], tid);
@@ -201,8 +208,8 @@ gemm_simt_kernel(int M, int N, int K, T alpha, const T* __restrict__ A, int64_t 
       }
 #pragma unroll
       for (int q = 0; q < VEC; ++q) {
-        T v = alpha * acc[i][c * VEC + q];
-        if (beta != (T)0) v = fma(beta, old[q], v);
+        T v = mul_rn(alpha, acc[i][c * VEC + q]);
+        if (beta != (T)0) v = (beta == (T)1) ? add_rn(old[q], v) : fma(beta, old[q], v);
         if (n + q < N) {
           if (epi.bias) v += epi.bias[n + q];
           if (z_out) z_out[off + q] = v;
@@ -230,7 +237,7 @@ gemm_simt_kernel(int M, int N, int K, T alpha, const T* __restrict__ A, int64_t 
 template <typename T> static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
 template <typename T, int BM, int BN, int BK, int TM, int TN>
-static prad_status launch_cfg(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, T alpha,
+static prad_status launch_cfg(prad_ctx* ctx, bool exact, bool tA, bool tB, int M, int N, int K, T alpha,
                               const T* A, int64_t lda, const T* B, int64_t ldb, T beta, T* C,
                               int64_t ldc, int batch, int64_t sA, int64_t sB, int64_t sC,
                               const EpiParams<T>& epi) {
@@ -243,8 +250,14 @@ static prad_status launch_cfg(prad_ctx* ctx, bool tA, bool tB, int M, int N, int
   bool vB = aligned16<T>(B) && ldb % VEC == 0 && sB % VEC == 0;
   bool vC = aligned16<T>(C) && ldc % VEC == 0 && sC % VEC == 0;
 #define PRAD_GEMM_LAUNCH(TA_, TB_)                                                           \
-  gemm_simt_kernel<T, BM, BN, BK, TM, TN, TA_, TB_><<<grid, NT, 0, ctx->stream>>>(           \
-      M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, sA, sB, sC, vA, vB, vC, epi)
+  do {                                                                                       \
+    if (exact)                                                                               \
+      gemm_simt_kernel<T, BM, BN, BK, TM, TN, TA_, TB_, true><<<grid, NT, 0, ctx->stream>>>( \
+          M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, sA, sB, sC, vA, vB, vC, epi);        \
+    else                                                                                     \
+      gemm_simt_kernel<T, BM, BN, BK, TM, TN, TA_, TB_, false><<<grid, NT, 0, ctx->stream>>>(\
+          M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, sA, sB, sC, vA, vB, vC, epi);        \
+  } while (0)
   if (!tA && !tB) PRAD_GEMM_LAUNCH(false, false);
   else if (!tA && tB) PRAD_GEMM_LAUNCH(false, true);
   else if (tA && !tB) PRAD_GEMM_LAUNCH(true, false);
@@ -255,9 +268,9 @@ static prad_status launch_cfg(prad_ctx* ctx, bool tA, bool tB, int M, int N, int
 }
 
 template <typename T>
-prad_status gemm_simt(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, double alpha,
-                      const void* A, int lda, const void* B, int ldb, double beta, void* C,
-                      int ldc, int batch, int64_t sA, int64_t sB, int64_t sC,
+prad_status gemm_simt(prad_ctx* ctx, bool exact, bool tA, bool tB, int M, int N, int K,
+                      double alpha, const void* A, int lda, const void* B, int ldb, double beta,
+                      void* C, int ldc, int batch, int64_t sA, int64_t sB, int64_t sC,
                       const GemmEpilogue& e) {
   EpiParams<T> epi{(const T*)e.bias, (T*)e.z_out, (int)e.act, (int)e.dact, (const T*)e.saved,
                    (T)e.act_alpha};
@@ -266,28 +279,28 @@ prad_status gemm_simt(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, doub
   const bool use_big = big_tiles >= ctx->sm_count && M >= 96 && N >= 96;
   if constexpr (sizeof(T) == 4) {
     if (use_big)
-      return launch_cfg<T, 128, 128, 16, 8, 8>(ctx, tA, tB, M, N, K, (T)alpha, (const T*)A, lda,
+      return launch_cfg<T, 128, 128, 16, 8, 8>(ctx, exact, tA, tB, M, N, K, (T)alpha, (const T*)A, lda,
                                                (const T*)B, ldb, (T)beta, (T*)C, ldc, batch, sA,
                                                sB, sC, epi);
-    return launch_cfg<T, 64, 64, 16, 4, 4>(ctx, tA, tB, M, N, K, (T)alpha, (const T*)A, lda,
+    return launch_cfg<T, 64, 64, 16, 4, 4>(ctx, exact, tA, tB, M, N, K, (T)alpha, (const T*)A, lda,
                                            (const T*)B, ldb, (T)beta, (T*)C, ldc, batch, sA, sB,
                                            sC, epi);
   } else {
     int64_t t64 = ceil_div(M, 64) * ceil_div(N, 64) * batch;
     if (t64 >= ctx->sm_count && M >= 48 && N >= 48)
-      return launch_cfg<T, 64, 64, 16, 4, 4>(ctx, tA, tB, M, N, K, (T)alpha, (const T*)A, lda,
+      return launch_cfg<T, 64, 64, 16, 4, 4>(ctx, exact, tA, tB, M, N, K, (T)alpha, (const T*)A, lda,
                                              (const T*)B, ldb, (T)beta, (T*)C, ldc, batch, sA,
                                              sB, sC, epi);
-    return launch_cfg<T, 32, 32, 16, 2, 2>(ctx, tA, tB, M, N, K, (T)alpha, (const T*)A, lda,
+    return launch_cfg<T, 32, 32, 16, 2, 2>(ctx, exact, tA, tB, M, N, K, (T)alpha, (const T*)A, lda,
                                            (const T*)B, ldb, (T)beta, (T*)C, ldc, batch, sA, sB,
                                            sC, epi);
   }
 }
 
-template prad_status gemm_simt<float>(prad_ctx*, bool, bool, int, int, int, double, const void*,
-                                      int, const void*, int, double, void*, int, int, int64_t,
-                                      int64_t, int64_t, const GemmEpilogue&);
-template prad_status gemm_simt<double>(prad_ctx*, bool, bool, int, int, int, double,
+template prad_status gemm_simt<float>(prad_ctx*, bool, bool, bool, int, int, int, double,
+                                      const void*, int, const void*, int, double, void*, int, int,
+                                      int64_t, int64_t, int64_t, const GemmEpilogue&);
+template prad_status gemm_simt<double>(prad_ctx*, bool, bool, bool, int, int, int, double,
                                        const void*, int, const void*, int, double, void*, int,
                                        int, int64_t, int64_t, int64_t, const GemmEpilogue&);
 

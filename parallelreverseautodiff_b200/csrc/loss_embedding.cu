@@ -202,7 +202,7 @@ prad_status prad_cce_forward(prad_ctx* ctx, prad_dtype dt, const void* out, cons
 prad_status prad_mse_backward(prad_ctx* ctx, prad_dtype dt, const void* out, const void* target,
                               void* grad, int64_t rows, int cols, int64_t rows_total) {
   PRAD_CHECK_CTX(ctx);
-  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0 && rows_total >= rows, PRAD_ERR_INVALID,
+  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0 && rows_total >= 1, PRAD_ERR_INVALID,
                "prad_mse_backward: bad argument");
   int64_t n = rows * cols;
   if (n == 0) return PRAD_OK;
@@ -219,7 +219,7 @@ prad_status prad_mse_backward(prad_ctx* ctx, prad_dtype dt, const void* out, con
 prad_status prad_cce_backward(prad_ctx* ctx, prad_dtype dt, const void* out, const void* target,
                               void* grad, int64_t rows, int cols, int64_t rows_total) {
   PRAD_CHECK_CTX(ctx);
-  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0 && rows_total >= rows, PRAD_ERR_INVALID,
+  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0 && rows_total >= 1, PRAD_ERR_INVALID,
                "prad_cce_backward: bad argument");
   int64_t n = rows * cols;
   if (n == 0) return PRAD_OK;

@@ -8,9 +8,9 @@
 namespace prad {
 
 template <typename T>
-prad_status gemm_simt(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, double alpha,
-                      const void* A, int lda, const void* B, int ldb, double beta, void* C,
-                      int ldc, int batch, int64_t sA, int64_t sB, int64_t sC,
+prad_status gemm_simt(prad_ctx* ctx, bool exact, bool tA, bool tB, int M, int N, int K,
+                      double alpha, const void* A, int lda, const void* B, int ldb, double beta,
+                      void* C, int ldc, int batch, int64_t sA, int64_t sB, int64_t sC,
                       const GemmEpilogue& e);
 
 // tensor-core variants (return PRAD_ERR_UNSUPPORTED when a shape does not fit them)
@@ -29,27 +29,27 @@ prad_status gemm_dispatch(prad_ctx* ctx, prad_dtype dt, bool tA, bool tB, int M,
                           int64_t sC, const GemmEpilogue& epi) {
   if (M == 0 || N == 0 || batch == 0) return PRAD_OK;
   if (dt == PRAD_F32) {
-    if (ctx->gemm_f32 != GemmF32::Simt) {
+    const bool want_tc = ctx->gemm_f32 == GemmF32::Auto || ctx->gemm_f32 == GemmF32::Tf32x3;
+    if (want_tc) {
       prad_status p = gemm_tf32x3(ctx, tA, tB, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc,
                                   batch, sA, sB, sC, epi, true);
       if (p == PRAD_OK)
         return gemm_tf32x3(ctx, tA, tB, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, batch, sA,
                            sB, sC, epi, false);
-      PRAD_REQUIRE(ctx->gemm_f32 != GemmF32::Tf32x3 || p == PRAD_ERR_UNSUPPORTED, p,
-                   "%s", prad_last_error());
     }
-    return gemm_simt<float>(ctx, tA, tB, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, batch, sA,
-                            sB, sC, epi);
+    return gemm_simt<float>(ctx, ctx->gemm_f32 != GemmF32::SimtFma, tA, tB, M, N, K, alpha, A, lda,
+                            B, ldb, beta, C, ldc, batch, sA, sB, sC, epi);
   }
-  if (ctx->gemm_f64 != GemmF64::Simt) {
+  const bool want_dmma = ctx->gemm_f64 == GemmF64::Auto || ctx->gemm_f64 == GemmF64::Dmma;
+  if (want_dmma) {
     prad_status p = gemm_f64_dmma(ctx, tA, tB, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc,
                                   batch, sA, sB, sC, epi, true);
     if (p == PRAD_OK)
       return gemm_f64_dmma(ctx, tA, tB, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, batch, sA,
                            sB, sC, epi, false);
   }
-  return gemm_simt<double>(ctx, tA, tB, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, batch, sA,
-                           sB, sC, epi);
+  return gemm_simt<double>(ctx, ctx->gemm_f64 != GemmF64::SimtFma, tA, tB, M, N, K, alpha, A, lda,
+                           B, ldb, beta, C, ldc, batch, sA, sB, sC, epi);
 }
 
 // ---- MultiplyAndSum ------------------------------------------------------------------------

@@ -342,8 +342,8 @@ class Engine:
                                              a.size))
         return out
 
-    def hadamard_backward(self, a, b, dy):
-        da, db = self.empty(a.shape, a.dtype), self.empty(a.shape, a.dtype)
+    def hadamard_backward(self, a, b, dy, out=None):
+        da, db = out if out is not None else (self.empty(a.shape, a.dtype), self.empty(a.shape, a.dtype))
         check(self.lib.prad_hadamard_backward(self.ctx, dtype_code(a.dtype), a.ptr, b.ptr, dy.ptr,
                                               da.ptr, db.ptr, a.size))
         return da, db

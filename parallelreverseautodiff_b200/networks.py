@@ -210,3 +210,244 @@ class FeedForwardNetwork:
         self.backward(rows_total=rows_total)
         self.clip_and_optimize()
         return float(loss.numpy()[0, 0])
+
+
+class LstmNetwork:
+    """Single-layer LSTM with full BPTT over the C ABI (benchmark config 3, PRAD double).
+
+    Reference graph (test/.../GraphAttentionPaths/LSTM/Architecture/NodeProcessing.json style,
+    README.md:396-430): per sample a column vector, gates through
+    BatchGpuMatrixMultiplyOperation(W, x) + (U, h) + bias, Sigmoid / Tanh, HadamardProduct,
+    MatrixAdd; weight gradients are averaged over the batch by the visitor
+    (OperationNeuralNetworkVisitor.cs:449-478) and added up over the time steps
+    (OperationBase.cs:295-303).
+
+    Device layout: one row per sample (batch-major), time steps stacked along the rows, so the
+    input contribution of every gate for ALL steps is one GEMM, and every shared weight's
+    gradient is ONE long-K product over the T*B stacked rows with alpha = 1/B -- the
+    deterministic replacement of the visitor's per-step `+=`.  The fan-in at h_t (loss + four
+    gate products of step t+1) and at c_t is a fixed-order prad_segmented_sum.
+    """
+
+    GATES = ("i", "f", "g", "o")
+
+    def __init__(self, eng: E.Engine, dtype, n_in: int, n_hidden: int, steps: int, batch: int):
+        self.eng, self.dtype = eng, np.dtype(dtype)
+        self.n_in, self.n_h, self.T, self.B = n_in, n_hidden, steps, batch
+        e, dt = eng, self.dtype
+        z = lambda *s: e.zeros(s, dt)  # noqa: E731
+        self.W = {g: z(n_hidden, n_in) for g in self.GATES}       # [hidden x in], as in the reference
+        self.U = {g: z(n_hidden, n_hidden) for g in self.GATES}
+        self.b = {g: z(1, n_hidden) for g in self.GATES}
+        self.dW = {g: z(n_hidden, n_in) for g in self.GATES}
+        self.dU = {g: z(n_hidden, n_hidden) for g in self.GATES}
+        self.db = {g: z(1, n_hidden) for g in self.GATES}
+        TB = steps * batch
+        self.X = z(TB, n_in)
+        self.Y = z(TB, n_hidden)                                  # targets
+        self.pre = {g: z(TB, n_hidden) for g in self.GATES}      # gate pre-activations
+        self.gate = {g: z(TB, n_hidden) for g in self.GATES}     # gate outputs
+        self.C = z(TB, n_hidden)
+        self.tanhC = z(TB, n_hidden)
+        self.H = z(TB, n_hidden)
+        self.Hprev = z(TB, n_hidden)                              # H shifted by one step (h_{-1} = 0)
+        self.FC = z(TB, n_hidden)                                 # f (.) c_{t-1}
+        self.IG = z(TB, n_hidden)                                 # i (.) g
+        self.dpre = {g: z(TB, n_hidden) for g in self.GATES}
+        self.dX = z(TB, n_in)
+        self._tmp = [z(batch, n_hidden) for _ in range(12)]
+
+    def set_parameters(self, W, U, b):
+        for g in self.GATES:
+            self.eng.upload(np.ascontiguousarray(W[g], self.dtype), out=self.W[g])
+            self.eng.upload(np.ascontiguousarray(U[g], self.dtype), out=self.U[g])
+            self.eng.upload(np.ascontiguousarray(b[g], self.dtype).reshape(1, -1), out=self.b[g])
+
+    def _step(self, m: E.DeviceMatrix, t: int) -> E.DeviceMatrix:
+        return m.view((self.B, m.shape[1]), t * self.B * m.shape[1])
+
+    def forward(self, x_host: np.ndarray, y_host: np.ndarray):
+        """x_host [T, B, in], y_host [T, B, hidden]."""
+        e, T, B = self.eng, self.T, self.B
+        e.upload(np.ascontiguousarray(x_host, self.dtype).reshape(T * B, -1), out=self.X)
+        e.upload(np.ascontiguousarray(y_host, self.dtype).reshape(T * B, -1), out=self.Y)
+        e.zero_(self.Hprev)
+        for g in self.GATES:    # input contribution of all steps: X_all * W_g^T
+            e.gemm(self.X, self.W[g], self.pre[g], transB=True)
+        acts = {"i": E.ACT_SIGMOID, "f": E.ACT_SIGMOID, "g": E.ACT_TANH, "o": E.ACT_SIGMOID}
+        for t in range(T):
+            hp = self._step(self.Hprev, t)
+            for g in self.GATES:
+                p = self._step(self.pre[g], t)
+                if t > 0:       # + h_{t-1} * U_g^T (MatrixAddThree: (Wx + Uh) + b)
+                    e.gemm(hp, self.U[g], p, transB=True, beta=1.0)
+                e.add_broadcast_forward(p, self.b[g], out=p)
+                e.act_forward(acts[g], p, out=self._step(self.gate[g], t))
+            c, fc, ig = self._step(self.C, t), self._step(self.FC, t), self._step(self.IG, t)
+            e.hadamard_forward(self._step(self.gate["i"], t), self._step(self.gate["g"], t), out=ig)
+            if t > 0:
+                e.hadamard_forward(self._step(self.gate["f"], t), self._step(self.C, t - 1), out=fc)
+            else:
+                e.zero_(fc)
+            e.add_forward(fc, ig, out=c)
+            tc = self._step(self.tanhC, t)
+            e.act_forward(E.ACT_TANH, c, out=tc)
+            h = self._step(self.H, t)
+            e.hadamard_forward(self._step(self.gate["o"], t), tc, out=h)
+            if t + 1 < T:
+                e.copy(self._step(self.Hprev, t + 1), h)
+        return self.H
+
+    def backward(self):
+        """MSE per sample and step (MeanSquaredErrorLossOperation on each [hidden x 1] column),
+        BPTT, then the time- and batch-reduced weight gradients."""
+        e, T, B, nh = self.eng, self.T, self.B, self.n_h
+        tmp = self._tmp
+        dh_rec = None           # four buffers: dZ_g(t+1) * U_g
+        dc_next = None          # dc_{t+1} (.) f_{t+1}
+        for t in range(T - 1, -1, -1):
+            # per-sample MSE over a [hidden x 1] column: 2/(hidden*1) * (h - y)
+            dloss = tmp[0]
+            e.mse_backward(self._step(self.H, t), self._step(self.Y, t), rows_total=1, grad=dloss)
+            dh = tmp[1]
+            if dh_rec is None:
+                e.copy(dh, dloss)
+            else:
+                e.segmented_sum([dloss] + dh_rec, out=dh)
+            o, tc = self._step(self.gate["o"], t), self._step(self.tanhC, t)
+            d_o, d_tc = tmp[2], tmp[3]
+            e.hadamard_backward(o, tc, dh, out=(d_o, d_tc))
+            dc_a = tmp[4]
+            e.act_backward(E.ACT_TANH, tc, d_tc, out=dc_a)
+            dc = tmp[5]
+            if dc_next is None:
+                e.copy(dc, dc_a)
+            else:
+                e.segmented_sum([dc_a, dc_next], out=dc)
+            # c = f*c_prev + i*g : MatrixAdd copies dc to both products
+            i_, g_, f_ = (self._step(self.gate[k], t) for k in ("i", "g", "f"))
+            d_i, d_g = e.hadamard_backward(i_, g_, dc)
+            if t > 0:
+                d_f, dc_next = e.hadamard_backward(f_, self._step(self.C, t - 1), dc)
+            else:
+                d_f = tmp[7]
+                e.zero_(d_f)    # c_{-1} = 0 -> dc (.) 0
+            e.act_backward(E.ACT_SIGMOID, i_, d_i, out=self._step(self.dpre["i"], t))
+            e.act_backward(E.ACT_SIGMOID, f_, d_f, out=self._step(self.dpre["f"], t))
+            e.act_backward(E.ACT_TANH, g_, d_g, out=self._step(self.dpre["g"], t))
+            e.act_backward(E.ACT_SIGMOID, o, d_o, out=self._step(self.dpre["o"], t))
+            if t > 0:           # gradient w.r.t. h_{t-1}: one product per gate, summed above
+                dh_rec = []
+                for k, g in enumerate(self.GATES):
+                    buf = tmp[8 + k]
+                    e.gemm(self._step(self.dpre[g], t), self.U[g], buf)
+                    dh_rec.append(buf)
+        inv_b = 1.0 / B
+        first = True
+        for g in self.GATES:
+            # dW_g = (1/B) * dZ_all^T X_all ; dU_g = (1/B) * dZ_all^T Hprev_all ; db_g = (1/B) colsum
+            e.gemm(self.dpre[g], self.X, self.dW[g], transA=True, alpha=inv_b)
+            e.gemm(self.dpre[g], self.Hprev, self.dU[g], transA=True, alpha=inv_b)
+            e.add_broadcast_backward(self.dpre[g], dbias=self.db[g])
+            e.scale(self.db[g], inv_b, out=self.db[g])
+            # dX_all = sum over gates of dZ_g W_g (left fold in gate order)
+            e.gemm(self.dpre[g], self.W[g], self.dX, beta=0.0 if first else 1.0)
+            first = False
+
+
+class SwinBlock:
+    """One Swin-style windowed self-attention block, forward and full backward (benchmark
+    config 4, PRADLite float).  Composition of the RMAD operations: LayerNormalization,
+    MatrixMultiply + MatrixAddBroadcasting (QKV / output projection / MLP), BatchMatrixMultiply
+    (Q K^T and P V per window and head), MatrixMultiplyScalar (1/sqrt(d)), Softmax, GELU,
+    MatrixAdd (residuals).  The Swin *example* of the reference cannot run its attention
+    (Tensor.MatrixMultiply throws for non-2-D input, src/PRAD/Tensor.cs:572-577), so the RMAD
+    composition is the semantics.
+
+    Heads are never materialised: every per-(window, head) product is a strided-batched GEMM
+    addressing the [tokens x 3*dim] QKV matrix in place (leading dimension 3*dim, window stride
+    ws*3*dim, one call per head), so head split / merge and all transposes cost no copies.
+    """
+
+    def __init__(self, eng: E.Engine, dtype, dim=96, heads=3, window=49, mlp_ratio=4):
+        self.eng, self.dtype = eng, np.dtype(dtype)
+        self.dim, self.heads, self.ws, self.hd = dim, heads, window, dim // heads
+        self.hidden = dim * mlp_ratio
+        z = lambda *s: eng.zeros(s, dtype)  # noqa: E731
+        d, h = dim, self.hidden
+        self.p = {"Wqkv": z(d, 3 * d), "bqkv": z(1, 3 * d), "Wproj": z(d, d), "bproj": z(1, d),
+                  "W1": z(d, h), "b1": z(1, h), "W2": z(h, d), "b2": z(1, d)}
+        self.g = {k: z(*v.shape) for k, v in self.p.items()}
+        self.scale = 1.0 / float(np.sqrt(self.hd))
+
+    def set_parameters(self, params):
+        for k, v in params.items():
+            self.eng.upload(np.ascontiguousarray(v, self.dtype).reshape(self.p[k].shape), out=self.p[k])
+
+    def _attn_gemm(self, A, a_off, lda, sA, Bm, b_off, ldb, sB, Cm, c_off, ldc, sC, M, N, K, transA=False,
+                   transB=False, alpha=1.0, beta=0.0, batch=1):
+        e = self.eng
+        e.gemm(A.view((1, 1), a_off), Bm.view((1, 1), b_off), Cm.view((1, 1), c_off), transA=transA, transB=transB,
+               alpha=alpha, beta=beta, M=M, N=N, K=K, lda=lda, ldb=ldb, ldc=ldc, batch=batch, strideA=sA,
+               strideB=sB, strideC=sC)
+
+    def forward(self, x: E.DeviceMatrix):
+        e, d, ws, H, hd = self.eng, self.dim, self.ws, self.heads, self.hd
+        T = x.shape[0]
+        nw = T // ws
+        self.x, self.nw = x, nw
+        self.ln1, self.mu1, self.sd1 = e.layernorm_forward(x)
+        self.qkv = e.matmul_forward(self.ln1, self.p["Wqkv"], bias=self.p["bqkv"])
+        self.S = e.empty((nw * H * ws, ws), self.dtype)           # [window][head][ws x ws]
+        for h in range(H):                                        # S = (Q K^T) * scale
+            self._attn_gemm(self.qkv, h * hd, 3 * d, ws * 3 * d, self.qkv, d + h * hd, 3 * d, ws * 3 * d,
+                            self.S, h * ws * ws, ws, H * ws * ws, ws, ws, hd, transB=True, alpha=self.scale, batch=nw)
+        self.P = e.softmax_forward(self.S)
+        self.attn = e.empty((T, d), self.dtype)
+        for h in range(H):                                        # O_h = P V, written at column h*hd
+            self._attn_gemm(self.P, h * ws * ws, ws, H * ws * ws, self.qkv, 2 * d + h * hd, 3 * d, ws * 3 * d,
+                            self.attn, h * hd, d, ws * d, ws, hd, ws, batch=nw)
+        self.proj = e.matmul_forward(self.attn, self.p["Wproj"], bias=self.p["bproj"])
+        self.r1 = e.add_forward(x, self.proj)
+        self.ln2, self.mu2, self.sd2 = e.layernorm_forward(self.r1)
+        self.z1 = e.empty((T, self.hidden), self.dtype)
+        self.a1 = e.matmul_forward(self.ln2, self.p["W1"], bias=self.p["b1"], Z_out=self.z1, act=E.ACT_GELU)
+        self.m2 = e.matmul_forward(self.a1, self.p["W2"], bias=self.p["b2"])
+        self.out = e.add_forward(self.r1, self.m2)
+        return self.out
+
+    def backward(self, d_out: E.DeviceMatrix):
+        e, d, ws, H, hd, nw = self.eng, self.dim, self.ws, self.heads, self.hd, self.nw
+        g, p = self.g, self.p
+        T = d_out.shape[0]
+        # out = r1 + m2 : both receive d_out (MatrixAddOperation.Backward)
+        e.add_broadcast_backward(d_out, dbias=g["b2"])
+        d_z1, _ = e.matmul_backward(self.a1, p["W2"], d_out, dB=g["W2"], act_below=E.ACT_GELU, saved_below=self.z1)
+        e.add_broadcast_backward(d_z1, dbias=g["b1"])
+        d_ln2, _ = e.matmul_backward(self.ln2, p["W1"], d_z1, dB=g["W1"])
+        d_r1_b = e.layernorm_backward(self.r1, self.mu2, self.sd2, d_ln2)
+        d_r1 = e.segmented_sum([d_out, d_r1_b])                    # fan-in at r1: residual + LN2 branch
+        # r1 = x + proj
+        e.add_broadcast_backward(d_r1, dbias=g["bproj"])
+        d_attn, _ = e.matmul_backward(self.attn, p["Wproj"], d_r1, dB=g["Wproj"])
+        d_qkv = e.zeros((T, 3 * d), self.dtype)
+        dP = e.empty(self.P.shape, self.dtype)
+        for h in range(H):
+            # O_h = P_h V_h :  dP_h = dO_h V_h^T ,  dV_h = P_h^T dO_h
+            self._attn_gemm(d_attn, h * hd, d, ws * d, self.qkv, 2 * d + h * hd, 3 * d, ws * 3 * d,
+                            dP, h * ws * ws, ws, H * ws * ws, ws, ws, hd, transB=True, batch=nw)
+            self._attn_gemm(self.P, h * ws * ws, ws, H * ws * ws, d_attn, h * hd, d, ws * d,
+                            d_qkv, 2 * d + h * hd, 3 * d, ws * 3 * d, ws, hd, ws, transA=True, batch=nw)
+        dS = e.softmax_backward(self.P, dP)
+        for h in range(H):
+            # S_h = scale * Q_h K_h^T :  dQ_h = scale * dS_h K_h ,  dK_h = scale * dS_h^T Q_h
+            self._attn_gemm(dS, h * ws * ws, ws, H * ws * ws, self.qkv, d + h * hd, 3 * d, ws * 3 * d,
+                            d_qkv, h * hd, 3 * d, ws * 3 * d, ws, hd, ws, alpha=self.scale, batch=nw)
+            self._attn_gemm(dS, h * ws * ws, ws, H * ws * ws, self.qkv, h * hd, 3 * d, ws * 3 * d,
+                            d_qkv, d + h * hd, 3 * d, ws * 3 * d, ws, hd, ws, transA=True, alpha=self.scale, batch=nw)
+        e.add_broadcast_backward(d_qkv, dbias=g["bqkv"])
+        d_ln1, _ = e.matmul_backward(self.ln1, p["Wqkv"], d_qkv, dB=g["Wqkv"])
+        d_x_b = e.layernorm_backward(self.x, self.mu1, self.sd1, d_ln1)
+        self.d_x = e.segmented_sum([d_r1, d_x_b])                  # fan-in at x: residual + LN1 branch
+        self.d_qkv, self.dS, self.dP, self.d_attn = d_qkv, dS, dP, d_attn
+        return self.d_x

@@ -1,0 +1,314 @@
+"""The five benchmark configurations end to end: the CUDA path (through the C ABI and the
+host drivers in networks.py) against the same graph composed from CPU-oracle operations on
+identical seeded inputs.  C1-C3 run at their full sizes; C4 and C5 at reduced batch (the
+oracle's naive loops would take minutes at full size), C5's full size being covered by
+size-independent properties in test_gpu_properties.py.
+"""
+import numpy as np
+import pytest
+
+import oracle as O
+from parallelreverseautodiff_b200 import engine as E
+from parallelreverseautodiff_b200.networks import FeedForwardNetwork, LstmNetwork, SwinBlock
+from util import assert_close, rms
+
+pytestmark = pytest.mark.gpu
+
+
+# ------------------------------------------------------------------ C1
+def test_c1_matmul_leakyrelu_node_double(engine):
+    """A[512x784]~U(-1,1), B[784x256]~N(0,2/784), dOut~N(0,1), seed 42: dPre, dA, dB."""
+    r = np.random.default_rng(42)
+    A = r.uniform(-1, 1, (512, 784))
+    B = r.standard_normal((784, 256)) * np.sqrt(2.0 / 784)
+    dOut = r.standard_normal((512, 256))
+    pre = O.matmul_forward(A, B)
+    dPre_ref = O.leaky_relu_backward(pre, dOut, 0.01)
+    dA_ref, dB_ref = O.matmul_backward(A, B, dPre_ref)
+    a, b = engine.upload(A), engine.upload(B)
+    pre_dev = engine.matmul_forward(a, b)
+    dPre, dA, dB = engine.matmul_act_backward(a, b, engine.upload(dOut), E.ACT_LEAKY_RELU, pre_dev, 0.01)
+    # every operation on this path rounds exactly as the C# loops do: identical bits
+    np.testing.assert_array_equal(pre_dev.numpy(), pre)
+    np.testing.assert_array_equal(dPre.numpy(), dPre_ref)
+    np.testing.assert_array_equal(dA.numpy(), dA_ref)
+    np.testing.assert_array_equal(dB.numpy(), dB_ref)
+    # the tensor-core variant of the double GEMM stays within 1e-12 relative / 1e-14 absolute
+    # of it, the absolute part scaled by the size of the summed terms
+    engine.set_option("gemm_f64", "dmma")
+    try:
+        _, dA2, dB2 = engine.matmul_act_backward(a, b, engine.upload(dOut), E.ACT_LEAKY_RELU, pre_dev, 0.01)
+        assert_close(dA2.numpy(), dA_ref, np.abs(dPre_ref) @ np.abs(B.T), "dA (dmma)")
+        assert_close(dB2.numpy(), dB_ref, np.abs(A.T) @ np.abs(dPre_ref), "dB (dmma)")
+    finally:
+        engine.set_option("gemm_f64", "auto")
+
+
+# ------------------------------------------------------------------ C2
+def _mlp_oracle(x, onehot, Ws, bs, alpha):
+    acts, pres = [x], []
+    for l, (W, b) in enumerate(zip(Ws, bs)):
+        z = O.add_broadcast_forward(O.matmul_forward(acts[-1], W), b)
+        pres.append(z)
+        acts.append(O.leaky_relu_forward(z, alpha) if l < len(Ws) - 1 else z)
+    probs = O.softmax_forward(acts[-1])
+    d = O.softmax_backward(probs, O.cce_backward(probs, onehot))
+    dW, db = [None] * len(Ws), [None] * len(Ws)
+    for l in range(len(Ws) - 1, -1, -1):
+        if l < len(Ws) - 1:
+            d = O.leaky_relu_backward(pres[l], d, alpha)
+        db[l] = O.add_broadcast_backward(d)[1]
+        dA, dW[l] = O.matmul_backward(acts[l], Ws[l], d)
+        d = dA
+    return probs, dW, db, d
+
+
+@pytest.mark.parametrize("clip", ["reference", "global_norm"])
+def test_c2_mlp_float_backward_clip_adam(engine, clip):
+    """784->512->512->10, LeakyReLU, softmax + CCE, batch 256; clip + one Adam step."""
+    r = np.random.default_rng(42)
+    sizes = [784, 512, 512, 10]
+    x = r.uniform(0, 1, (256, 784)).astype(np.float32)
+    onehot = np.eye(10, dtype=np.float32)[r.integers(0, 10, 256)]
+    Ws = [(r.standard_normal((sizes[i], sizes[i + 1])) * np.sqrt(2.0 / sizes[i])).astype(np.float32) for i in range(3)]
+    bs = [np.zeros((1, sizes[i + 1]), np.float32) for i in range(3)]
+    probs_ref, dW_ref, db_ref, dx_ref = _mlp_oracle(x, onehot, Ws, bs, np.float32(0.01))
+    mode = E.CLIP_REFERENCE if clip == "reference" else E.CLIP_GLOBAL_NORM
+    net = FeedForwardNetwork(engine, np.float32, sizes, hidden_act=E.ACT_LEAKY_RELU, softmax_output=True,
+                             loss="cce", use_bias=True, clip_mode=mode)
+    net.set_weights(Ws, bs)
+    net._ensure_buffers(256)
+    engine.upload(x, out=net.A[0])
+    engine.upload(onehot, out=net.target)
+    probs = net.forward()
+    assert_close(probs.numpy(), probs_ref, 0.1, "probabilities")
+    net.backward()
+    for l in range(3):
+        scale = np.abs(dW_ref[l]).max()
+        assert_close(net.dW[l].numpy(), dW_ref[l], scale, f"dW{l}")
+        assert_close(net.db[l].numpy(), db_ref[l], np.abs(db_ref[l]).max(), f"db{l}")
+    assert_close(net.dX.numpy(), dx_ref, np.abs(dx_ref).max(), "dX")
+    # clip + Adam on the oracle's gradients vs the device step on the device's gradients
+    grads_ref = [g.copy() for g in dW_ref + db_ref]
+    if clip == "reference":
+        for g in grads_ref:
+            O.clip_reference(g, np.float32(4.0), np.float32(1e-8))
+    else:
+        O.clip_global_norm(grads_ref, 4.0)
+    w_ref = [w.copy() for w in Ws + bs]
+    for w, g in zip(w_ref, grads_ref):
+        O.adam_rmad(w, np.zeros_like(w), np.zeros_like(w), g, 1e-3, 0.9, 0.999, 1e-8, 1.0)
+    net.clip_and_optimize(zero_grad=True)
+    for k, (p, w) in enumerate(zip(net.params, w_ref)):
+        # first Adam step moves every weight by ~lr*sign(g): compare the update, not the weight
+        upd = p.numpy() - (Ws + bs)[k]
+        upd_ref = w - (Ws + bs)[k]
+        big = np.abs(grads_ref[k]) > 1e-6           # where g ~ 0 the direction is rounding noise
+        assert_close(upd[big], upd_ref[big], 1e-3, f"Adam update {k}")
+    assert not net.grads[0].numpy().any()
+
+
+# ------------------------------------------------------------------ C3
+def _lstm_oracle(x, y, W, U, b):
+    """Column-vector spelling of the reference: per sample columns, weights [hidden x in];
+    per-step weight gradients are the left-fold batch mean, summed over steps last to first."""
+    T, B, n_in = x.shape
+    nh = y.shape[2]
+    sig, tanh = O.sigmoid_forward, O.tanh_forward
+    G = ("i", "f", "g", "o")
+    act = {"i": sig, "f": sig, "g": tanh, "o": sig}
+    h = np.zeros((nh, B))
+    c = np.zeros((nh, B))
+    st = []
+    for t in range(T):
+        xt = np.ascontiguousarray(x[t].T)                       # [in x B]: one column per sample
+        gate = {}
+        for g in G:
+            wx = O.matmul_forward(W[g], xt)
+            if t > 0:
+                wx = O.add_forward(wx, O.matmul_forward(U[g], h))
+            pre = O.add_forward(wx, np.repeat(b[g].reshape(-1, 1), B, 1))
+            gate[g] = act[g](pre)
+        ig = O.hadamard_forward(gate["i"], gate["g"])
+        fc = O.hadamard_forward(gate["f"], c) if t > 0 else np.zeros_like(c)
+        c_new = O.add_forward(fc, ig)
+        tc = tanh(c_new)
+        h_new = O.hadamard_forward(gate["o"], tc)
+        st.append(dict(x=xt, hprev=h, cprev=c, gate=gate, tc=tc, h=h_new, c=c_new))
+        h, c = h_new, c_new
+    dW = {g: np.zeros_like(W[g]) for g in G}
+    dU = {g: np.zeros_like(U[g]) for g in G}
+    db = {g: np.zeros(nh) for g in G}
+    dX = np.zeros((T, B, n_in))
+    dh_rec, dc_next = None, None
+    inv = 1.0 / B
+    for t in range(T - 1, -1, -1):
+        s = st[t]
+        yt = np.ascontiguousarray(y[t].T)
+        dloss = (2.0 / nh) * (s["h"] - yt)                       # per-sample MSE on a [hidden x 1] column
+        dh = dloss if dh_rec is None else O.accumulate_gradients([dloss] + dh_rec)
+        d_o, d_tc = O.hadamard_backward(s["gate"]["o"], s["tc"], dh)
+        dc_a = O.tanh_backward(s["tc"], d_tc)
+        dc = dc_a if dc_next is None else O.accumulate_gradients([dc_a, dc_next])
+        d_i, d_g = O.hadamard_backward(s["gate"]["i"], s["gate"]["g"], dc)
+        if t > 0:
+            d_f, dc_next = O.hadamard_backward(s["gate"]["f"], s["cprev"], dc)
+        else:
+            d_f = np.zeros_like(dc)
+        dz = {"i": O.sigmoid_backward(s["gate"]["i"], d_i), "f": O.sigmoid_backward(s["gate"]["f"], d_f),
+              "g": O.tanh_backward(s["gate"]["g"], d_g), "o": O.sigmoid_backward(s["gate"]["o"], d_o)}
+        dx_parts, dh_rec = [], []
+        for g in G:
+            # batch mean of the per-sample outer products == sequential sum over samples * (1/B)
+            O.accumulate_into(dW[g], O.matmul_forward(dz[g], np.ascontiguousarray(s["x"].T)) * inv)
+            if t > 0:
+                O.accumulate_into(dU[g], O.matmul_forward(dz[g], np.ascontiguousarray(s["hprev"].T)) * inv)
+                dh_rec.append(O.matmul_forward(np.ascontiguousarray(U[g].T), dz[g]))
+            db[g] = db[g] + dz[g].sum(1) * inv
+            dx_parts.append(O.matmul_forward(np.ascontiguousarray(W[g].T), dz[g]))
+        dX[t] = O.accumulate_gradients(dx_parts).T
+        if t == 0:
+            dh_rec = None
+    H = np.stack([s["h"].T for s in st])
+    return H, dW, dU, db, dX
+
+
+@pytest.mark.parametrize("shape", [(5, 3, 12, 16), (64, 32, 128, 256)])
+def test_c3_lstm_double_bptt(engine, shape):
+    """Input 128, hidden 256, 64 steps, batch 32 (and a tiny case): full BPTT."""
+    T, B, n_in, nh = shape
+    r = np.random.default_rng(42)
+    x = r.standard_normal((T, B, n_in))
+    y = r.standard_normal((T, B, nh))
+    G = ("i", "f", "g", "o")
+    W = {g: r.uniform(-1, 1, (nh, n_in)) * np.sqrt(6.0 / (nh + n_in)) for g in G}
+    U = {g: r.uniform(-1, 1, (nh, nh)) * np.sqrt(6.0 / (nh + nh)) for g in G}
+    b = {g: r.standard_normal(nh) * 0.1 for g in G}
+    H_ref, dW_ref, dU_ref, db_ref, dX_ref = _lstm_oracle(x, y, W, U, b)
+    net = LstmNetwork(engine, np.float64, n_in, nh, T, B)
+    net.set_parameters(W, U, b)
+    H = net.forward(x, y)
+    assert_close(H.numpy().reshape(T, B, nh), H_ref, 10.0, "h")
+    net.backward()
+    for g in G:
+        assert_close(net.dW[g].numpy(), dW_ref[g], 10.0, f"dW_{g}")
+        assert_close(net.dU[g].numpy(), dU_ref[g], 10.0, f"dU_{g}")
+        assert_close(net.db[g].numpy().ravel(), db_ref[g], 10.0, f"db_{g}")
+    assert_close(net.dX.numpy().reshape(T, B, n_in), dX_ref, 10.0, "dX")
+
+
+# ------------------------------------------------------------------ C4
+def _swin_oracle(x, d_out, p, heads, ws):
+    T, d = x.shape
+    hd = d // heads
+    nw = T // ws
+    scale = np.float32(1.0 / np.sqrt(hd))
+    ln1, mu1, sd1 = O.layernorm_forward(x)
+    qkv = O.add_broadcast_forward(O.matmul_forward(ln1, p["Wqkv"]), p["bqkv"])
+
+    def heads_of(m, off):       # [T x 3d] -> DeepMatrix [nw*heads, ws, hd] (window-major, then head)
+        return np.ascontiguousarray(m[:, off:off + d].reshape(nw, ws, heads, hd).transpose(0, 2, 1, 3)
+                                    .reshape(nw * heads, ws, hd))
+
+    def merge(m):               # inverse of heads_of for one d-wide block
+        return np.ascontiguousarray(m.reshape(nw, heads, ws, hd).transpose(0, 2, 1, 3).reshape(T, d))
+
+    Q, K, V = heads_of(qkv, 0), heads_of(qkv, d), heads_of(qkv, 2 * d)
+    Kt = np.ascontiguousarray(K.transpose(0, 2, 1))
+    S = O.scale(O.batch_matmul_forward(Q, Kt), scale)
+    P = O.softmax_forward(S.reshape(-1, ws)).reshape(S.shape)
+    attn = merge(O.batch_matmul_forward(P, V))
+    proj = O.add_broadcast_forward(O.matmul_forward(attn, p["Wproj"]), p["bproj"])
+    r1 = O.add_forward(x, proj)
+    ln2, mu2, sd2 = O.layernorm_forward(r1)
+    z1 = O.add_broadcast_forward(O.matmul_forward(ln2, p["W1"]), p["b1"])
+    a1 = O.gelu_forward(z1)
+    m2 = O.add_broadcast_forward(O.matmul_forward(a1, p["W2"]), p["b2"])
+    out = O.add_forward(r1, m2)
+    g = {}
+    g["b2"] = O.add_broadcast_backward(d_out)[1]
+    d_a1, g["W2"] = O.matmul_backward(a1, p["W2"], d_out)
+    d_z1 = O.gelu_backward(z1, d_a1)
+    g["b1"] = O.add_broadcast_backward(d_z1)[1]
+    d_ln2, g["W1"] = O.matmul_backward(ln2, p["W1"], d_z1)
+    d_r1 = O.accumulate_gradients([d_out, O.layernorm_backward(r1, mu2, sd2, d_ln2)])
+    g["bproj"] = O.add_broadcast_backward(d_r1)[1]
+    d_attn, g["Wproj"] = O.matmul_backward(attn, p["Wproj"], d_r1)
+    dO = heads_of(np.concatenate([d_attn, d_attn, d_attn], 1), 0)
+    dP, dV = O.batch_matmul_backward(P, V, dO)
+    dS = O.softmax_backward(P.reshape(-1, ws), dP.reshape(-1, ws)).reshape(S.shape)
+    dSs = O.scale(dS, scale)
+    dQ, dKt = O.batch_matmul_backward(Q, Kt, dSs)
+    dK = np.ascontiguousarray(dKt.transpose(0, 2, 1))
+    d_qkv = np.concatenate([merge(dQ), merge(dK), merge(dV)], 1)
+    g["bqkv"] = O.add_broadcast_backward(d_qkv)[1]
+    d_ln1, g["Wqkv"] = O.matmul_backward(ln1, p["Wqkv"], d_qkv)
+    d_x = O.accumulate_gradients([d_r1, O.layernorm_backward(x, mu1, sd1, d_ln1)])
+    return out, g, d_x, dict(P=P, d_qkv=d_qkv, dS=dS)
+
+
+@pytest.mark.parametrize("images", [1])
+def test_c4_swin_block_float(engine, images):
+    """dim 96, 3 heads, 7x7 windows over a 56x56 token map (one image = 64 windows here)."""
+    d, heads, ws, hidden = 96, 3, 49, 384
+    T = images * 3136
+    r = np.random.default_rng(42)
+    f = np.float32
+    x = r.standard_normal((T, d)).astype(f)
+    d_out = r.standard_normal((T, d)).astype(f)
+    p = {"Wqkv": (r.standard_normal((d, 3 * d)) * np.sqrt(2.0 / d)).astype(f), "bqkv": (r.standard_normal((1, 3 * d)) * 0.1).astype(f),
+         "Wproj": (r.standard_normal((d, d)) * np.sqrt(2.0 / d)).astype(f), "bproj": (r.standard_normal((1, d)) * 0.1).astype(f),
+         "W1": (r.standard_normal((d, hidden)) * np.sqrt(2.0 / d)).astype(f), "b1": (r.standard_normal((1, hidden)) * 0.1).astype(f),
+         "W2": (r.standard_normal((hidden, d)) * np.sqrt(2.0 / hidden)).astype(f), "b2": (r.standard_normal((1, d)) * 0.1).astype(f)}
+    out_ref, g_ref, dx_ref, mid = _swin_oracle(x, d_out, p, heads, ws)
+    blk = SwinBlock(engine, f, d, heads, ws, hidden // d)
+    blk.set_parameters(p)
+    out = blk.forward(engine.upload(x))
+    assert_close(out.numpy(), out_ref, 10 * rms(out_ref), "block output")
+    nw = T // ws
+    assert_close(blk.P.numpy().reshape(nw * heads, ws, ws), mid["P"], 1.0, "attention probabilities")
+    dx = blk.backward(engine.upload(d_out))
+    assert_close(blk.d_qkv.numpy(), mid["d_qkv"], 10 * rms(mid["d_qkv"]), "d_qkv")
+    for k in g_ref:
+        # weight gradients sum over all T tokens: the error scale is sum |terms| ~ T * typical product
+        assert_close(blk.g[k].numpy(), g_ref[k], 30 * rms(g_ref[k]), f"grad {k}")
+    assert_close(dx.numpy(), dx_ref, 10 * rms(dx_ref), "d_x")
+
+
+# ------------------------------------------------------------------ C5 (reduced rows)
+@pytest.mark.parametrize("gemm", ["simt", "auto"])
+def test_c5_wide_mlp_float_reduced(engine, gemm):
+    """Same graph as the benchmark (width x width GELU layers, MSE) at 3 x 1024 wide, 384 rows."""
+    engine.set_option("gemm_f32", gemm)
+    try:
+        r = np.random.default_rng(42)
+        width, L, rows = 1024, 3, 384
+        f = np.float32
+        x = r.standard_normal((rows, width)).astype(f)
+        t = r.standard_normal((rows, width)).astype(f)
+        Ws = [(r.standard_normal((width, width)) * np.sqrt(2.0 / width)).astype(f) for _ in range(L)]
+        acts, pres = [x], []
+        for W in Ws:
+            z = O.matmul_forward(acts[-1], W)
+            pres.append(z)
+            acts.append(O.gelu_forward(z))
+        d = O.mse_backward(acts[-1], t)
+        dW_ref = [None] * L
+        for l in range(L - 1, -1, -1):
+            d = O.gelu_backward(pres[l], d)
+            dA, dW_ref[l] = O.matmul_backward(acts[l], Ws[l], d)
+            d = dA
+        net = FeedForwardNetwork(engine, f, [width] * (L + 1), hidden_act=E.ACT_GELU, output_act=E.ACT_GELU,
+                                 loss="mse", use_bias=False)
+        net.set_weights(Ws)
+        net._ensure_buffers(rows)
+        engine.upload(x, out=net.A[0])
+        engine.upload(t, out=net.target)
+        net.forward()
+        assert_close(net.A[L].numpy(), acts[-1], 10 * rms(acts[-1]), "output")
+        net.backward()
+        for l in range(L):
+            assert_close(net.dW[l].numpy(), dW_ref[l], 30 * rms(dW_ref[l]), f"dW{l}")
+        assert_close(net.dX.numpy(), d, 30 * rms(d), "dX")
+    finally:
+        engine.set_option("gemm_f32", "auto")
