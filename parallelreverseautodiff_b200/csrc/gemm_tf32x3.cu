@@ -25,6 +25,7 @@
 // error flag (which all other waiters poll and obey), the CTA drains, frees its tensor
 // memory and returns; the host then reports PRAD_ERR_TIMEOUT.
 #include <cuda.h>
+#include <cuda_bf16.h>
 
 #include <mutex>
 
@@ -45,15 +46,24 @@ constexpr int THREADS = 64 + EPI_WARPS * 32;     // producer warp, MMA warp, epi
 
 // Pipeline shape: a k-block of BK floats is one swizzle atom wide (BK*4 = 128, 64 or 32
 // bytes); STAGES k-blocks of the four operand tiles (A_hi, A_lo, B_hi, B_lo) are in flight.
-template <int BK_, int STAGES_> struct Cfg {
-  static constexpr int BK = BK_, STAGES = STAGES_;
+// MODE 0: three TF32 products per k-slice (a_hi*b_hi + a_lo*b_hi + a_hi*b_lo), all operands
+//         kept as FP32 containers.
+// MODE 1: one TF32 product (a_hi*b_hi) plus the two correction products in BF16
+//         (bf16(a_lo)*bf16(b) + bf16(a)*bf16(b_lo), kind::f16 with K = 16): the corrections are
+//         2^-11 of the result, so BF16's 8-bit significand leaves them accurate to 2^-19 of it,
+//         and they cost half a TF32 product each -- two thirds of the tensor work of MODE 0
+//         for the same shared-memory footprint (4 + 2 + 2 bytes per operand element).
+template <int BK_, int STAGES_, int MODE_ = 0> struct Cfg {
+  static constexpr int BK = BK_, STAGES = STAGES_, MODE = MODE_;
   static constexpr int SWIZZLE_BYTES = BK * 4;
+  static constexpr int SWIZZLE_BYTES_BF16 = BK * 2;
   static constexpr int A_TILE_BYTES = BM * BK * 4;
   static constexpr int B_TILE_BYTES = BN * BK * 4;
   static constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;
   static constexpr int CHUNK_KB = CHUNK_K / BK;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
   static_assert(SWIZZLE_BYTES == 128 || SWIZZLE_BYTES == 64 || SWIZZLE_BYTES == 32, "BK must be 32, 16 or 8");
+  static_assert(MODE == 0 || BK >= 16, "BF16 tiles need rows of at least 32 bytes");
   static_assert(SMEM_BYTES <= 227 * 1024, "stages do not fit in shared memory");
 };
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
@@ -150,6 +160,18 @@ __host__ __device__ constexpr uint32_t idesc_tf32() {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
+// Instruction descriptor: D = F32, A = B = BF16, both K-major, M = 128, N = 256 (kind::f16).
+__host__ __device__ constexpr uint32_t idesc_bf16() {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 struct Epi {
   const float* bias;
   float* z_out;
@@ -224,8 +246,13 @@ template <class CFG>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                    const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                   const __grid_constant__ CUtensorMap map_a_x, const __grid_constant__ CUtensorMap map_b_x,
                    int M, int N, int K, float* __restrict__ C, int64_t ldc, bool vecC, Epi epi,
                    int* __restrict__ err_flag) {
+  // MODE 0 tiles per stage: A_hi, A_lo (FP32) | B_hi, B_lo (FP32);  map_*_x unused.
+  // MODE 1 tiles per stage: A_hi (FP32), A_hb, A_lb (BF16) | B_hi (FP32), B_hb, B_lb (BF16);
+  //        map_*_lo address the bf16(x - hi) arrays, map_*_x the bf16(x) arrays.
+  constexpr int MODE = CFG::MODE, SWB = CFG::SWIZZLE_BYTES_BF16;
   constexpr int BK = CFG::BK, STAGES = CFG::STAGES, STAGE_BYTES = CFG::STAGE_BYTES;
   constexpr int A_TILE_BYTES = CFG::A_TILE_BYTES, B_TILE_BYTES = CFG::B_TILE_BYTES;
   constexpr int CHUNK_KB = CFG::CHUNK_KB, SW = CFG::SWIZZLE_BYTES;
@@ -277,9 +304,16 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
         const uint32_t st = base + s * STAGE_BYTES;
         mbar_expect_tx(full_bar(s), STAGE_BYTES);
         tma_load_2d(st, &map_a_hi, full_bar(s), kb * BK, m0);
-        tma_load_2d(st + A_TILE_BYTES, &map_a_lo, full_bar(s), kb * BK, m0);
         tma_load_2d(st + 2 * A_TILE_BYTES, &map_b_hi, full_bar(s), kb * BK, n0);
-        tma_load_2d(st + 2 * A_TILE_BYTES + B_TILE_BYTES, &map_b_lo, full_bar(s), kb * BK, n0);
+        if (MODE == 0) {
+          tma_load_2d(st + A_TILE_BYTES, &map_a_lo, full_bar(s), kb * BK, m0);
+          tma_load_2d(st + 2 * A_TILE_BYTES + B_TILE_BYTES, &map_b_lo, full_bar(s), kb * BK, n0);
+        } else {   // two half-size BF16 tiles where MODE 0 has one FP32 tile
+          tma_load_2d(st + A_TILE_BYTES, &map_a_x, full_bar(s), kb * BK, m0);
+          tma_load_2d(st + A_TILE_BYTES + A_TILE_BYTES / 2, &map_a_lo, full_bar(s), kb * BK, m0);
+          tma_load_2d(st + 2 * A_TILE_BYTES + B_TILE_BYTES, &map_b_x, full_bar(s), kb * BK, n0);
+          tma_load_2d(st + 2 * A_TILE_BYTES + B_TILE_BYTES + B_TILE_BYTES / 2, &map_b_lo, full_bar(s), kb * BK, n0);
+        }
       }
     }
   } else if (warp == 1) {
@@ -308,17 +342,36 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
           if (!ok) break;
           tc_fence_after();
           const uint32_t st = base + s * STAGE_BYTES;
-          const uint64_t a_hi = kmajor_desc<SW>(st);
-          const uint64_t a_lo = kmajor_desc<SW>(st + A_TILE_BYTES);
-          const uint64_t b_hi = kmajor_desc<SW>(st + 2 * A_TILE_BYTES);
-          const uint64_t b_lo = kmajor_desc<SW>(st + 2 * A_TILE_BYTES + B_TILE_BYTES);
           const bool first_kb = kb == ch * CHUNK_KB;
+          const uint64_t a_hi = kmajor_desc<SW>(st);
+          const uint64_t b_hi = kmajor_desc<SW>(st + 2 * A_TILE_BYTES);
+          if (MODE == 0) {
+            const uint64_t a_lo = kmajor_desc<SW>(st + A_TILE_BYTES);
+            const uint64_t b_lo = kmajor_desc<SW>(st + 2 * A_TILE_BYTES + B_TILE_BYTES);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t adv = (uint64_t)((k * UMMA_K * 4) >> 4);   // +32 bytes per k-slice
-            umma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, !(first_kb && k == 0));
-            umma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1);
-            umma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1);
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint64_t adv = (uint64_t)((k * UMMA_K * 4) >> 4);   // +32 bytes per k-slice
+              umma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, !(first_kb && k == 0));
+              umma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1);
+              umma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1);
+            }
+          } else {
+            constexpr uint32_t idesc_h = idesc_bf16();
+            const uint64_t a_hb = kmajor_desc<SWB>(st + A_TILE_BYTES);
+            const uint64_t a_lb = kmajor_desc<SWB>(st + A_TILE_BYTES + A_TILE_BYTES / 2);
+            const uint64_t b_hb = kmajor_desc<SWB>(st + 2 * A_TILE_BYTES + B_TILE_BYTES);
+            const uint64_t b_lb = kmajor_desc<SWB>(st + 2 * A_TILE_BYTES + B_TILE_BYTES + B_TILE_BYTES / 2);
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k) {      // BF16 slices are 16 wide = 32 bytes
+              const uint64_t adv = (uint64_t)((k * 16 * 2) >> 4);
+              umma_f16(d_tmem, a_lb + adv, b_hb + adv, idesc_h, !(first_kb && k == 0));
+              umma_f16(d_tmem, a_hb + adv, b_lb + adv, idesc_h, 1);
+            }
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint64_t adv = (uint64_t)((k * UMMA_K * 4) >> 4);
+              umma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1);
+            }
           }
           umma_commit(empty_bar(s));   // the stage may be refilled once these MMAs have read it
         }
@@ -385,9 +438,10 @@ __device__ __forceinline__ float to_tf32(float x) {
   return __uint_as_float(r);
 }
 // src is rows x cols (ld = src_ld); dst_hi/dst_lo are rows x dst_ld with the same orientation
+// With xb/lb given (MODE 1) the FP32 `lo` array is not written; xb = bf16(x), lb = bf16(x - hi).
 __global__ void __launch_bounds__(256)
 split_kernel(const float* __restrict__ src, int64_t src_ld, float* __restrict__ hi, float* __restrict__ lo,
-             int64_t dst_ld, int rows, int cols) {
+             __nv_bfloat16* __restrict__ xb, __nv_bfloat16* __restrict__ lb, int64_t dst_ld, int rows, int cols) {
   const int64_t total = (int64_t)rows * (dst_ld / 4);
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const bool vec = ((src_ld & 3) == 0) && (((uintptr_t)src & 15) == 0);
@@ -404,15 +458,26 @@ split_kernel(const float* __restrict__ src, int64_t src_ld, float* __restrict__ 
     }
     float h[4], l[4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) { h[q] = to_tf32(x[q]); l[q] = to_tf32(x[q] - h[q]); }
+    for (int q = 0; q < 4; ++q) { h[q] = to_tf32(x[q]); l[q] = x[q] - h[q]; }
     *reinterpret_cast<float4*>(hi + (int64_t)r * dst_ld + c) = make_float4(h[0], h[1], h[2], h[3]);
-    *reinterpret_cast<float4*>(lo + (int64_t)r * dst_ld + c) = make_float4(l[0], l[1], l[2], l[3]);
+    if (xb) {
+      __nv_bfloat162 x01 = __floats2bfloat162_rn(x[0], x[1]), x23 = __floats2bfloat162_rn(x[2], x[3]);
+      __nv_bfloat162 l01 = __floats2bfloat162_rn(l[0], l[1]), l23 = __floats2bfloat162_rn(l[2], l[3]);
+      uint2 xv = make_uint2(*reinterpret_cast<uint32_t*>(&x01), *reinterpret_cast<uint32_t*>(&x23));
+      uint2 lv = make_uint2(*reinterpret_cast<uint32_t*>(&l01), *reinterpret_cast<uint32_t*>(&l23));
+      *reinterpret_cast<uint2*>(xb + (int64_t)r * dst_ld + c) = xv;
+      *reinterpret_cast<uint2*>(lb + (int64_t)r * dst_ld + c) = lv;
+    } else {
+      *reinterpret_cast<float4*>(lo + (int64_t)r * dst_ld + c) =
+          make_float4(to_tf32(l[0]), to_tf32(l[1]), to_tf32(l[2]), to_tf32(l[3]));
+    }
   }
 }
 // src is rows x cols; dst is cols x dst_ld (transposed), dst_ld >= rows
 __global__ void __launch_bounds__(256)
 split_transpose_kernel(const float* __restrict__ src, int64_t src_ld, float* __restrict__ hi,
-                       float* __restrict__ lo, int64_t dst_ld, int rows, int cols) {
+                       float* __restrict__ lo, __nv_bfloat16* __restrict__ xb, __nv_bfloat16* __restrict__ lb,
+                       int64_t dst_ld, int rows, int cols) {
   __shared__ float tile[32][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
   const int c = blockIdx.x * 32 + tx;
@@ -430,7 +495,12 @@ split_transpose_kernel(const float* __restrict__ src, int64_t src_ld, float* __r
       const float x = tile[tx][j];       // zero beyond `rows` (padding columns of dst)
       const float h = to_tf32(x);
       hi[(int64_t)c2 * dst_ld + r2] = h;
-      lo[(int64_t)c2 * dst_ld + r2] = to_tf32(x - h);
+      if (xb) {
+        xb[(int64_t)c2 * dst_ld + r2] = __float2bfloat16_rn(x);
+        lb[(int64_t)c2 * dst_ld + r2] = __float2bfloat16_rn(x - h);
+      } else {
+        lo[(int64_t)c2 * dst_ld + r2] = to_tf32(x - h);
+      }
     }
   }
 }
@@ -457,13 +527,17 @@ static EncodeTiledFn encode_fn() {
 }
 
 // K-major operand: `rows` rows of `k` floats, row pitch ld floats (ld % 4 == 0)
-static bool make_map(CUtensorMap* map, const float* ptr, int rows, int k, int64_t ld, int box_rows, int bk) {
+static bool make_map(CUtensorMap* map, const void* ptr, int rows, int k, int64_t ld, int box_rows, int bk,
+                     int elem_bytes = 4) {
   cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * elem_bytes};
   cuuint32_t box[2] = {(cuuint32_t)bk, (cuuint32_t)box_rows};
-  CUtensorMapSwizzle sw = bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : (bk == 16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+  const int row_bytes = bk * elem_bytes;
+  CUtensorMapSwizzle sw = row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                           : (row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)ptr, dims, strides, box, estr,
+  CUresult r = encode_fn()(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                           2, (void*)ptr, dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
@@ -471,10 +545,18 @@ static bool make_map(CUtensorMap* map, const float* ptr, int rows, int k, int64_
 
 
 
+// Operand scratch in K-major form.  MODE 0: hi, lo as FP32.  MODE 1: hi as FP32, xb = bf16(x)
+// and lb = bf16(x - hi) as BF16.
+struct SplitOperand {
+  float* hi = nullptr;
+  float* lo = nullptr;
+  __nv_bfloat16* xb = nullptr;
+  __nv_bfloat16* lb = nullptr;
+};
+
 template <class CFG>
-static prad_status launch_tf32x3(prad_ctx* ctx, const float* a_hi, const float* a_lo, const float* b_hi,
-                                 const float* b_lo, int M, int N, int64_t kp, float* C, int64_t ldc,
-                                 bool vecC, const Epi& epi) {
+static prad_status launch_tf32x3(prad_ctx* ctx, const SplitOperand& a, const SplitOperand& b, int M, int N,
+                                 int64_t kp, float* C, int64_t ldc, bool vecC, const Epi& epi) {
   static std::once_flag attr_once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(attr_once, [] {
@@ -483,16 +565,37 @@ static prad_status launch_tf32x3(prad_ctx* ctx, const float* a_hi, const float* 
   });
   PRAD_REQUIRE(attr_err == cudaSuccess, PRAD_ERR_CUDA, "gemm tf32x3: cannot reserve %d bytes of shared memory: %s",
                CFG::SMEM_BYTES, cudaGetErrorString(attr_err));
-  CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
-  bool ok = make_map(&ma_hi, a_hi, M, (int)kp, kp, BM, CFG::BK) && make_map(&ma_lo, a_lo, M, (int)kp, kp, BM, CFG::BK) &&
-            make_map(&mb_hi, b_hi, N, (int)kp, kp, BN, CFG::BK) && make_map(&mb_lo, b_lo, N, (int)kp, kp, BN, CFG::BK);
+  CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo, ma_x, mb_x;
+  bool ok = make_map(&ma_hi, a.hi, M, (int)kp, kp, BM, CFG::BK) && make_map(&mb_hi, b.hi, N, (int)kp, kp, BN, CFG::BK);
+  if (CFG::MODE == 0) {
+    ok = ok && make_map(&ma_lo, a.lo, M, (int)kp, kp, BM, CFG::BK) && make_map(&mb_lo, b.lo, N, (int)kp, kp, BN, CFG::BK);
+    ma_x = ma_lo;
+    mb_x = mb_lo;
+  } else {
+    ok = ok && make_map(&ma_lo, a.lb, M, (int)kp, kp, BM, CFG::BK, 2) && make_map(&mb_lo, b.lb, N, (int)kp, kp, BN, CFG::BK, 2) &&
+         make_map(&ma_x, a.xb, M, (int)kp, kp, BM, CFG::BK, 2) && make_map(&mb_x, b.xb, N, (int)kp, kp, BN, CFG::BK, 2);
+  }
   PRAD_REQUIRE(ok, PRAD_ERR_CUDA, "gemm tf32x3: cuTensorMapEncodeTiled failed (M %d N %d K %lld)", M, N, (long long)kp);
   dim3 grid((unsigned)ceil_div(N, BN), (unsigned)ceil_div(M, BM));
   PRAD_REQUIRE(grid.y <= 65535, PRAD_ERR_UNSUPPORTED, "gemm tf32x3: too many row tiles (%u)", grid.y);
-  gemm_tf32x3_kernel<CFG><<<grid, THREADS, CFG::SMEM_BYTES, ctx->stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, M, N, (int)kp,
-                                                                         C, ldc, vecC, epi, ctx->tc_err);
+  gemm_tf32x3_kernel<CFG><<<grid, THREADS, CFG::SMEM_BYTES, ctx->stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, ma_x, mb_x, M, N,
+                                                                         (int)kp, C, ldc, vecC, epi, ctx->tc_err);
   PRAD_LAUNCHED(ctx);
   ctx->tc_pending_check = true;
+  return PRAD_OK;
+}
+
+// writes the split form of one operand; `transposed` = the caller's matrix has k as its slow index
+static prad_status split_operand(prad_ctx* ctx, const float* src, int64_t ld, bool transposed, int rows, int K,
+                                 int64_t kp, const SplitOperand& o) {
+  if (!transposed) {
+    int grid = stream_grid(ctx, (int64_t)rows * (kp / 4), 256, 8);
+    split_kernel<<<grid, 256, 0, ctx->stream>>>(src, ld, o.hi, o.lo, o.xb, o.lb, kp, rows, K);
+  } else {
+    dim3 grid((unsigned)ceil_div(rows, 32), (unsigned)ceil_div(kp, 32));
+    split_transpose_kernel<<<grid, 256, 0, ctx->stream>>>(src, ld, o.hi, o.lo, o.xb, o.lb, kp, K, rows);
+  }
+  PRAD_LAUNCHED(ctx);
   return PRAD_OK;
 }
 
@@ -505,7 +608,7 @@ prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, do
   using namespace tc;
   (void)sA; (void)sB; (void)sC;
   // shapes this kernel is meant for; everything else stays on the SIMT variant
-  const bool forced = ctx->gemm_f32 == GemmF32::Tf32x3;
+  const bool forced = ctx->gemm_f32 == GemmF32::Tf32x3 || ctx->gemm_f32 == GemmF32::Tf32B16;
   const bool big = (int64_t)M * N * K >= ((int64_t)1 << 27) && M >= BM && N >= 128 && K >= KPAD;
   if (batch != 1 || K < 1 || !(big || forced) || encode_fn() == nullptr) {
     if (probe_only || !forced) return PRAD_ERR_UNSUPPORTED;
@@ -513,47 +616,46 @@ prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, do
     return PRAD_ERR_UNSUPPORTED;
   }
   if (probe_only) return PRAD_OK;
+  const int mode = ctx->gemm_f32 == GemmF32::Tf32x3 ? 0 : (ctx->gemm_f32 == GemmF32::Tf32B16 ? 1 : ctx->tc_auto_mode);
 
-  // scratch: [A_hi | A_lo | B_hi | B_lo], operands K-major with pitch kp
+  // scratch: both operands K-major with pitch kp, 8 bytes per element in either mode
   const int64_t kp = ceil_div(K, KPAD) * KPAD;
   const size_t a_elems = (size_t)M * kp, b_elems = (size_t)N * kp;
   const size_t need = 2 * (a_elems + b_elems) * sizeof(float);
   prad_status s = ensure_workspace(ctx, need);
   if (s) return s;
-  float* a_hi = (float*)ctx->ws;
-  float* a_lo = a_hi + a_elems;
-  float* b_hi = a_lo + a_elems;
-  float* b_lo = b_hi + b_elems;
-
-  const float* Af = (const float*)A;
-  const float* Bf = (const float*)B;
-  // op(A) is M x K.  !tA: memory already M x K (k contiguous).  tA: memory is K x M.
-  if (!tA) {
-    int grid = stream_grid(ctx, (int64_t)M * (kp / 4), 256, 8);
-    split_kernel<<<grid, 256, 0, ctx->stream>>>(Af, lda, a_hi, a_lo, kp, M, K);
+  SplitOperand a, b;
+  a.hi = (float*)ctx->ws;
+  b.hi = a.hi + 2 * a_elems;
+  if (mode == 0) {
+    a.lo = a.hi + a_elems;
+    b.lo = b.hi + b_elems;
   } else {
-    dim3 grid((unsigned)ceil_div(M, 32), (unsigned)ceil_div(kp, 32));
-    split_transpose_kernel<<<grid, 256, 0, ctx->stream>>>(Af, lda, a_hi, a_lo, kp, K, M);
+    a.xb = (__nv_bfloat16*)(a.hi + a_elems);
+    a.lb = a.xb + a_elems;
+    b.xb = (__nv_bfloat16*)(b.hi + b_elems);
+    b.lb = b.xb + b_elems;
   }
-  PRAD_LAUNCHED(ctx);
-  // op(B) is K x N; the kernel wants B^T = N x K (k contiguous).  tB: memory is N x K already.
-  if (tB) {
-    int grid = stream_grid(ctx, (int64_t)N * (kp / 4), 256, 8);
-    split_kernel<<<grid, 256, 0, ctx->stream>>>(Bf, ldb, b_hi, b_lo, kp, N, K);
-  } else {
-    dim3 grid((unsigned)ceil_div(N, 32), (unsigned)ceil_div(kp, 32));
-    split_transpose_kernel<<<grid, 256, 0, ctx->stream>>>(Bf, ldb, b_hi, b_lo, kp, K, N);
-  }
-  PRAD_LAUNCHED(ctx);
+  // op(A) is M x K: memory is M x K (k contiguous) unless tA.  op(B) is K x N and the kernel
+  // wants its transpose N x K (k contiguous): memory already is that when tB.
+  s = split_operand(ctx, (const float*)A, lda, tA, M, K, kp, a);
+  if (s) return s;
+  s = split_operand(ctx, (const float*)B, ldb, !tB, N, K, kp, b);
+  if (s) return s;
 
   Epi epi{(const float*)e.bias, (float*)e.z_out, (int)e.act, (int)e.dact, (const float*)e.saved,
           (float)e.act_alpha, (float)alpha, (float)beta};
   const bool vecC = (((uintptr_t)C & 15) == 0) && (ldc % 4 == 0) &&
                     (!e.saved || ((uintptr_t)e.saved & 15) == 0);
+  float* Cf = (float*)C;
+  if (mode == 1) {
+    if (ctx->tc_variant == 1) return launch_tf32x3<Cfg<32, 2, 1>>(ctx, a, b, M, N, kp, Cf, ldc, vecC, epi);
+    return launch_tf32x3<Cfg<16, 4, 1>>(ctx, a, b, M, N, kp, Cf, ldc, vecC, epi);
+  }
   switch (ctx->tc_variant) {
-    case 1: return launch_tf32x3<Cfg<32, 2>>(ctx, a_hi, a_lo, b_hi, b_lo, M, N, kp, (float*)C, ldc, vecC, epi);
-    case 2: return launch_tf32x3<Cfg<8, 8>>(ctx, a_hi, a_lo, b_hi, b_lo, M, N, kp, (float*)C, ldc, vecC, epi);
-    default: return launch_tf32x3<Cfg<16, 4>>(ctx, a_hi, a_lo, b_hi, b_lo, M, N, kp, (float*)C, ldc, vecC, epi);
+    case 1: return launch_tf32x3<Cfg<32, 2>>(ctx, a, b, M, N, kp, Cf, ldc, vecC, epi);
+    case 2: return launch_tf32x3<Cfg<8, 8>>(ctx, a, b, M, N, kp, Cf, ldc, vecC, epi);
+    default: return launch_tf32x3<Cfg<16, 4>>(ctx, a, b, M, N, kp, Cf, ldc, vecC, epi);
   }
 }
 

@@ -10,9 +10,10 @@ from util import assert_close, normal, rng, uniform
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture()
-def tc_engine(engine):
-    engine.set_option("gemm_f32", "tf32x3")
+@pytest.fixture(params=["tf32x3", "tf32b16"])
+def tc_engine(engine, request):
+    """Both split schemes: three TF32 products, or one TF32 product + two BF16 corrections."""
+    engine.set_option("gemm_f32", request.param)
     yield engine
     engine.set_option("gemm_f32", "auto")
 
