@@ -44,7 +44,8 @@ def parse():
     ap.add_argument("--width", type=int, default=WIDTH)
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--clip", default="reference", choices=["reference", "global_norm", "none"])
-    ap.add_argument("--gemm", default="auto", choices=["auto", "simt", "tf32x3"])
+    ap.add_argument("--gemm", default="auto", choices=["auto", "simt", "simt_fma", "tf32x3", "tf32b16", "bf16x3"])
+    ap.add_argument("--tc-pipeline", default=None, choices=[None, "16x4", "32x2", "8x8"])
     ap.add_argument("--lr", type=float, default=1e-5,
                     help="Adam learning rate (1e-3, the reference default, makes this 8-layer GELU net "
                          "diverge within ten steps on random targets; the arithmetic per step is the same)")
@@ -203,6 +204,8 @@ def run_native(args, rank, world, local_rank):
 
     eng = E.Engine(local_rank)
     eng.set_option("gemm_f32", args.gemm)
+    if args.tc_pipeline:
+        eng.set_option("tc_pipeline", args.tc_pipeline)
     if world > 1:
         ids = [E.Engine.dp_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)

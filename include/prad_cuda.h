@@ -71,11 +71,15 @@ const char* prad_last_error(void);
 /* library version string and the sm architecture it was built for */
 const char* prad_version(void);
 /* options:
- *  "gemm_f32" = "auto" | "simt" | "simt_fma" | "tf32x3"; "gemm_f64" = "auto" | "simt" | "simt_fma" | "dmma"
+ *  "gemm_f32" = "auto" | "simt" | "simt_fma" | "tf32x3" | "tf32b16" | "bf16x3";
+ *  "gemm_f64" = "auto" | "simt" | "simt_fma" | "dmma"
  *    simt     : multiply and add rounded separately, k ascending -- bit-identical to the managed
  *               code's sequential `Output[i][j] += a*b` loop (the default for small products);
  *    simt_fma : same order with fused multiply-add (twice the rate, one rounding per step);
- *    tf32x3 / dmma : tensor-core kernels (results within the documented tolerance);
+ *    tf32x3   : tcgen05 kernel, three TF32 products per term (a_hi*b_hi + a_lo*b_hi + a_hi*b_lo);
+ *    tf32b16  : tcgen05 kernel, one TF32 product + two BF16 correction products (what "auto" uses);
+ *    bf16x3   : tcgen05 kernel, six BF16 products of three-piece operands;
+ *    dmma     : FP64 mma.sync kernel; all tensor-core kernels stay within the documented tolerance;
  *    auto     : tensor-core kernel for large products, "simt" otherwise;
  * "tc_pipeline" = "16x4" | "32x2" | "8x8" (k-block floats x stages of the tensor-core GEMM) */
 prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value);

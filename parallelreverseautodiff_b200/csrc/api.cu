@@ -133,7 +133,8 @@ prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value) {
     else if (!strcmp(value, "simt_fma")) ctx->gemm_f32 = GemmF32::SimtFma;
     else if (!strcmp(value, "tf32x3")) ctx->gemm_f32 = GemmF32::Tf32x3;
     else if (!strcmp(value, "tf32b16")) ctx->gemm_f32 = GemmF32::Tf32B16;
-    else { set_error("prad_set_option: gemm_f32 must be auto|simt|simt_fma|tf32x3|tf32b16, got '%s'", value); return PRAD_ERR_INVALID; }
+    else if (!strcmp(value, "bf16x3")) ctx->gemm_f32 = GemmF32::Bf16x3;
+    else { set_error("prad_set_option: gemm_f32 must be auto|simt|simt_fma|tf32x3|tf32b16|bf16x3, got '%s'", value); return PRAD_ERR_INVALID; }
     return PRAD_OK;
   }
   if (!strcmp(key, "gemm_f64")) {

@@ -15,7 +15,7 @@ namespace prad {
 
 void set_error(const char* fmt, ...);
 
-enum class GemmF32 { Auto, Simt, SimtFma, Tf32x3, Tf32B16 };
+enum class GemmF32 { Auto, Simt, SimtFma, Tf32x3, Tf32B16, Bf16x3 };
 enum class GemmF64 { Auto, Simt, SimtFma, Dmma };
 
 struct DpState;  // data-parallel state (dp.cu)
@@ -43,7 +43,7 @@ struct prad_ctx {
   int* tc_err = nullptr;
   bool tc_pending_check = false;
   int tc_variant = 0;  // pipeline shape of the tensor-core GEMM (option "tc_pipeline")
-  int tc_auto_mode = 0;  // split scheme "auto" picks: 0 = 3xTF32, 1 = TF32 + BF16 corrections
+  int tc_auto_mode = 1;  // split scheme "auto" picks: 0 = 3xTF32, 1 = TF32 + BF16 corrections
   uint32_t magic = 0x50524144u;  // "PRAD"
 };
 

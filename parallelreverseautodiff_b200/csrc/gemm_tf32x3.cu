@@ -53,13 +53,21 @@ constexpr int THREADS = 64 + EPI_WARPS * 32;     // producer warp, MMA warp, epi
 //         2^-11 of the result, so BF16's 8-bit significand leaves them accurate to 2^-19 of it,
 //         and they cost half a TF32 product each -- two thirds of the tensor work of MODE 0
 //         for the same shared-memory footprint (4 + 2 + 2 bytes per operand element).
+// MODE 2: everything in BF16: x = b0 + b1 + b2 (each piece the BF16 rounding of what is left),
+//         six products b0*b0' + b0*b1' + b1*b0' + b1*b1' + b0*b2' + b2*b0' (kind::f16, K = 16).
+//         The dropped terms are below 2^-24 of the result.  Same tensor work as MODE 0 but only
+//         6 bytes per operand element travel from L2 to shared memory instead of 8, which is
+//         what bounds this kernel (operand delivery, not the tensor pipe).
 template <int BK_, int STAGES_, int MODE_ = 0> struct Cfg {
   static constexpr int BK = BK_, STAGES = STAGES_, MODE = MODE_;
   static constexpr int SWIZZLE_BYTES = BK * 4;
   static constexpr int SWIZZLE_BYTES_BF16 = BK * 2;
   static constexpr int A_TILE_BYTES = BM * BK * 4;
   static constexpr int B_TILE_BYTES = BN * BK * 4;
-  static constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;
+  // bytes per operand element in a stage: 8 (FP32 hi + FP32 lo, or FP32 hi + two BF16), or 6
+  // in MODE 2 (three BF16 pieces)
+  static constexpr int STAGE_BYTES = MODE == 2 ? (A_TILE_BYTES + B_TILE_BYTES) * 3 / 2
+                                               : 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;
   static constexpr int CHUNK_KB = CHUNK_K / BK;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
   static_assert(SWIZZLE_BYTES == 128 || SWIZZLE_BYTES == 64 || SWIZZLE_BYTES == 32, "BK must be 32, 16 or 8");
@@ -303,6 +311,16 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
         if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, err_flag, 1)) break;
         const uint32_t st = base + s * STAGE_BYTES;
         mbar_expect_tx(full_bar(s), STAGE_BYTES);
+        if (MODE == 2) {   // six BF16 tiles: A b0, b1, b2 then B b0, b1, b2
+          constexpr int AT = A_TILE_BYTES / 2, BT = B_TILE_BYTES / 2;
+          tma_load_2d(st, &map_a_hi, full_bar(s), kb * BK, m0);
+          tma_load_2d(st + AT, &map_a_x, full_bar(s), kb * BK, m0);
+          tma_load_2d(st + 2 * AT, &map_a_lo, full_bar(s), kb * BK, m0);
+          tma_load_2d(st + 3 * AT, &map_b_hi, full_bar(s), kb * BK, n0);
+          tma_load_2d(st + 3 * AT + BT, &map_b_x, full_bar(s), kb * BK, n0);
+          tma_load_2d(st + 3 * AT + 2 * BT, &map_b_lo, full_bar(s), kb * BK, n0);
+          continue;
+        }
         tma_load_2d(st, &map_a_hi, full_bar(s), kb * BK, m0);
         tma_load_2d(st + 2 * A_TILE_BYTES, &map_b_hi, full_bar(s), kb * BK, n0);
         if (MODE == 0) {
@@ -343,6 +361,25 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
           tc_fence_after();
           const uint32_t st = base + s * STAGE_BYTES;
           const bool first_kb = kb == ch * CHUNK_KB;
+          if (MODE == 2) {
+            constexpr uint32_t idesc_h = idesc_bf16();
+            constexpr int AT = A_TILE_BYTES / 2, BT = B_TILE_BYTES / 2;
+            const uint64_t a0 = kmajor_desc<SWB>(st), a1 = kmajor_desc<SWB>(st + AT), a2 = kmajor_desc<SWB>(st + 2 * AT);
+            const uint64_t b0 = kmajor_desc<SWB>(st + 3 * AT), b1 = kmajor_desc<SWB>(st + 3 * AT + BT),
+                           b2 = kmajor_desc<SWB>(st + 3 * AT + 2 * BT);
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k) {      // smallest terms first
+              const uint64_t adv = (uint64_t)((k * 16 * 2) >> 4);
+              umma_f16(d_tmem, a2 + adv, b0 + adv, idesc_h, !(first_kb && k == 0));
+              umma_f16(d_tmem, a0 + adv, b2 + adv, idesc_h, 1);
+              umma_f16(d_tmem, a1 + adv, b1 + adv, idesc_h, 1);
+              umma_f16(d_tmem, a1 + adv, b0 + adv, idesc_h, 1);
+              umma_f16(d_tmem, a0 + adv, b1 + adv, idesc_h, 1);
+              umma_f16(d_tmem, a0 + adv, b0 + adv, idesc_h, 1);
+            }
+            umma_commit(empty_bar(s));
+            continue;
+          }
           const uint64_t a_hi = kmajor_desc<SW>(st);
           const uint64_t b_hi = kmajor_desc<SW>(st + 2 * A_TILE_BYTES);
           if (MODE == 0) {
@@ -439,9 +476,18 @@ __device__ __forceinline__ float to_tf32(float x) {
 }
 // src is rows x cols (ld = src_ld); dst_hi/dst_lo are rows x dst_ld with the same orientation
 // With xb/lb given (MODE 1) the FP32 `lo` array is not written; xb = bf16(x), lb = bf16(x - hi).
+// With b0 given (MODE 2) only the three BF16 pieces b0, xb (= b1), lb (= b2) are written.
+__device__ __forceinline__ void bf16_pieces(float x, __nv_bfloat16& p0, __nv_bfloat16& p1, __nv_bfloat16& p2) {
+  p0 = __float2bfloat16_rn(x);
+  const float r1 = x - __bfloat162float(p0);     // exact
+  p1 = __float2bfloat16_rn(r1);
+  const float r2 = r1 - __bfloat162float(p1);    // exact
+  p2 = __float2bfloat16_rn(r2);
+}
 __global__ void __launch_bounds__(256)
 split_kernel(const float* __restrict__ src, int64_t src_ld, float* __restrict__ hi, float* __restrict__ lo,
-             __nv_bfloat16* __restrict__ xb, __nv_bfloat16* __restrict__ lb, int64_t dst_ld, int rows, int cols) {
+             __nv_bfloat16* __restrict__ xb, __nv_bfloat16* __restrict__ lb, __nv_bfloat16* __restrict__ b0,
+             int64_t dst_ld, int rows, int cols) {
   const int64_t total = (int64_t)rows * (dst_ld / 4);
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   const bool vec = ((src_ld & 3) == 0) && (((uintptr_t)src & 15) == 0);
@@ -455,6 +501,17 @@ split_kernel(const float* __restrict__ src, int64_t src_ld, float* __restrict__ 
     } else {
 #pragma unroll
       for (int q = 0; q < 4; ++q) x[q] = (c + q < cols) ? src[(int64_t)r * src_ld + c + q] : 0.f;
+    }
+    if (b0) {
+      __align__(8) __nv_bfloat16 p0[4];
+      __align__(8) __nv_bfloat16 p1[4];
+      __align__(8) __nv_bfloat16 p2[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) bf16_pieces(x[q], p0[q], p1[q], p2[q]);
+      *reinterpret_cast<uint2*>(b0 + (int64_t)r * dst_ld + c) = *reinterpret_cast<uint2*>(p0);
+      *reinterpret_cast<uint2*>(xb + (int64_t)r * dst_ld + c) = *reinterpret_cast<uint2*>(p1);
+      *reinterpret_cast<uint2*>(lb + (int64_t)r * dst_ld + c) = *reinterpret_cast<uint2*>(p2);
+      continue;
     }
     float h[4], l[4];
 #pragma unroll
@@ -477,7 +534,7 @@ split_kernel(const float* __restrict__ src, int64_t src_ld, float* __restrict__ 
 __global__ void __launch_bounds__(256)
 split_transpose_kernel(const float* __restrict__ src, int64_t src_ld, float* __restrict__ hi,
                        float* __restrict__ lo, __nv_bfloat16* __restrict__ xb, __nv_bfloat16* __restrict__ lb,
-                       int64_t dst_ld, int rows, int cols) {
+                       __nv_bfloat16* __restrict__ b0, int64_t dst_ld, int rows, int cols) {
   __shared__ float tile[32][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
   const int c = blockIdx.x * 32 + tx;
@@ -493,6 +550,14 @@ split_transpose_kernel(const float* __restrict__ src, int64_t src_ld, float* __r
     const int c2 = blockIdx.x * 32 + j;
     if (c2 < cols && r2 < dst_ld) {
       const float x = tile[tx][j];       // zero beyond `rows` (padding columns of dst)
+      if (b0) {
+        __nv_bfloat16 p0, p1, p2;
+        bf16_pieces(x, p0, p1, p2);
+        b0[(int64_t)c2 * dst_ld + r2] = p0;
+        xb[(int64_t)c2 * dst_ld + r2] = p1;
+        lb[(int64_t)c2 * dst_ld + r2] = p2;
+        continue;
+      }
       const float h = to_tf32(x);
       hi[(int64_t)c2 * dst_ld + r2] = h;
       if (xb) {
@@ -552,6 +617,7 @@ struct SplitOperand {
   float* lo = nullptr;
   __nv_bfloat16* xb = nullptr;
   __nv_bfloat16* lb = nullptr;
+  __nv_bfloat16* b0 = nullptr;   // MODE 2: pieces are b0, xb (= b1), lb (= b2)
 };
 
 template <class CFG>
@@ -566,8 +632,16 @@ static prad_status launch_tf32x3(prad_ctx* ctx, const SplitOperand& a, const Spl
   PRAD_REQUIRE(attr_err == cudaSuccess, PRAD_ERR_CUDA, "gemm tf32x3: cannot reserve %d bytes of shared memory: %s",
                CFG::SMEM_BYTES, cudaGetErrorString(attr_err));
   CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo, ma_x, mb_x;
-  bool ok = make_map(&ma_hi, a.hi, M, (int)kp, kp, BM, CFG::BK) && make_map(&mb_hi, b.hi, N, (int)kp, kp, BN, CFG::BK);
-  if (CFG::MODE == 0) {
+  bool ok = true;
+  if (CFG::MODE == 2) {
+    ok = make_map(&ma_hi, a.b0, M, (int)kp, kp, BM, CFG::BK, 2) && make_map(&ma_x, a.xb, M, (int)kp, kp, BM, CFG::BK, 2) &&
+         make_map(&ma_lo, a.lb, M, (int)kp, kp, BM, CFG::BK, 2) && make_map(&mb_hi, b.b0, N, (int)kp, kp, BN, CFG::BK, 2) &&
+         make_map(&mb_x, b.xb, N, (int)kp, kp, BN, CFG::BK, 2) && make_map(&mb_lo, b.lb, N, (int)kp, kp, BN, CFG::BK, 2);
+  } else {
+    ok = make_map(&ma_hi, a.hi, M, (int)kp, kp, BM, CFG::BK) && make_map(&mb_hi, b.hi, N, (int)kp, kp, BN, CFG::BK);
+  }
+  if (CFG::MODE == 2) {
+  } else if (CFG::MODE == 0) {
     ok = ok && make_map(&ma_lo, a.lo, M, (int)kp, kp, BM, CFG::BK) && make_map(&mb_lo, b.lo, N, (int)kp, kp, BN, CFG::BK);
     ma_x = ma_lo;
     mb_x = mb_lo;
@@ -590,10 +664,10 @@ static prad_status split_operand(prad_ctx* ctx, const float* src, int64_t ld, bo
                                  int64_t kp, const SplitOperand& o) {
   if (!transposed) {
     int grid = stream_grid(ctx, (int64_t)rows * (kp / 4), 256, 8);
-    split_kernel<<<grid, 256, 0, ctx->stream>>>(src, ld, o.hi, o.lo, o.xb, o.lb, kp, rows, K);
+    split_kernel<<<grid, 256, 0, ctx->stream>>>(src, ld, o.hi, o.lo, o.xb, o.lb, o.b0, kp, rows, K);
   } else {
     dim3 grid((unsigned)ceil_div(rows, 32), (unsigned)ceil_div(kp, 32));
-    split_transpose_kernel<<<grid, 256, 0, ctx->stream>>>(src, ld, o.hi, o.lo, o.xb, o.lb, kp, K, rows);
+    split_transpose_kernel<<<grid, 256, 0, ctx->stream>>>(src, ld, o.hi, o.lo, o.xb, o.lb, o.b0, kp, K, rows);
   }
   PRAD_LAUNCHED(ctx);
   return PRAD_OK;
@@ -608,7 +682,8 @@ prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, do
   using namespace tc;
   (void)sA; (void)sB; (void)sC;
   // shapes this kernel is meant for; everything else stays on the SIMT variant
-  const bool forced = ctx->gemm_f32 == GemmF32::Tf32x3 || ctx->gemm_f32 == GemmF32::Tf32B16;
+  const bool forced = ctx->gemm_f32 == GemmF32::Tf32x3 || ctx->gemm_f32 == GemmF32::Tf32B16 ||
+                      ctx->gemm_f32 == GemmF32::Bf16x3;
   const bool big = (int64_t)M * N * K >= ((int64_t)1 << 27) && M >= BM && N >= 128 && K >= KPAD;
   if (batch != 1 || K < 1 || !(big || forced) || encode_fn() == nullptr) {
     if (probe_only || !forced) return PRAD_ERR_UNSUPPORTED;
@@ -616,7 +691,9 @@ prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, do
     return PRAD_ERR_UNSUPPORTED;
   }
   if (probe_only) return PRAD_OK;
-  const int mode = ctx->gemm_f32 == GemmF32::Tf32x3 ? 0 : (ctx->gemm_f32 == GemmF32::Tf32B16 ? 1 : ctx->tc_auto_mode);
+  const int mode = ctx->gemm_f32 == GemmF32::Tf32x3 ? 0
+                   : ctx->gemm_f32 == GemmF32::Tf32B16 ? 1
+                   : ctx->gemm_f32 == GemmF32::Bf16x3 ? 2 : ctx->tc_auto_mode;
 
   // scratch: both operands K-major with pitch kp, 8 bytes per element in either mode
   const int64_t kp = ceil_div(K, KPAD) * KPAD;
@@ -627,7 +704,14 @@ prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, do
   SplitOperand a, b;
   a.hi = (float*)ctx->ws;
   b.hi = a.hi + 2 * a_elems;
-  if (mode == 0) {
+  if (mode == 2) {
+    a.b0 = (__nv_bfloat16*)a.hi;
+    a.xb = a.b0 + a_elems;
+    a.lb = a.xb + a_elems;
+    b.b0 = (__nv_bfloat16*)b.hi;
+    b.xb = b.b0 + b_elems;
+    b.lb = b.xb + b_elems;
+  } else if (mode == 0) {
     a.lo = a.hi + a_elems;
     b.lo = b.hi + b_elems;
   } else {
@@ -648,10 +732,10 @@ prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, do
   const bool vecC = (((uintptr_t)C & 15) == 0) && (ldc % 4 == 0) &&
                     (!e.saved || ((uintptr_t)e.saved & 15) == 0);
   float* Cf = (float*)C;
-  if (mode == 1) {
-    if (ctx->tc_variant == 1) return launch_tf32x3<Cfg<32, 2, 1>>(ctx, a, b, M, N, kp, Cf, ldc, vecC, epi);
-    return launch_tf32x3<Cfg<16, 4, 1>>(ctx, a, b, M, N, kp, Cf, ldc, vecC, epi);
-  }
+  if (mode == 2) return launch_tf32x3<Cfg<32, 3, 2>>(ctx, a, b, M, N, kp, Cf, ldc, vecC, epi);
+  // MODE 1 always runs 32-float k-blocks: with 16 its BF16 tiles would have 32-byte rows, and
+  // 32-byte TMA boxes / 32-byte swizzle measured 30 % slower
+  if (mode == 1) return launch_tf32x3<Cfg<32, 2, 1>>(ctx, a, b, M, N, kp, Cf, ldc, vecC, epi);
   switch (ctx->tc_variant) {
     case 1: return launch_tf32x3<Cfg<32, 2>>(ctx, a, b, M, N, kp, Cf, ldc, vecC, epi);
     case 2: return launch_tf32x3<Cfg<8, 8>>(ctx, a, b, M, N, kp, Cf, ldc, vecC, epi);

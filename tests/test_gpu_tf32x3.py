@@ -10,9 +10,10 @@ from util import assert_close, normal, rng, uniform
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=["tf32x3", "tf32b16"])
+@pytest.fixture(params=["tf32x3", "tf32b16", "bf16x3"])
 def tc_engine(engine, request):
-    """Both split schemes: three TF32 products, or one TF32 product + two BF16 corrections."""
+    """Every split scheme: three TF32 products; one TF32 product + two BF16 corrections; six
+    BF16 products of three-piece operands."""
     engine.set_option("gemm_f32", request.param)
     yield engine
     engine.set_option("gemm_f32", "auto")
