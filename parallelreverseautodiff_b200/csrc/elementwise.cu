@@ -188,9 +188,96 @@ __global__ void colsum_final_kernel(const double* __restrict__ partial, T* __res
   out[col] = accumulate ? add_rn(out[col], v) : v;
 }
 
+// Streaming form of the same column sums for matrices whose rows are a whole number of
+// 128-bit vectors: the matrix is read like a copy (thread t takes vectors t, t+S, t+2S, ...
+// with S a multiple of the vectors per row, so a thread always sees the same column group),
+// every thread writes its partial sums, and one CTA per column group adds the partials of
+// the threads that share the group in thread order.  Fully coalesced, deterministic.
+template <typename T>
+__global__ void __launch_bounds__(256)
+colsum_flat_partial_kernel(const T* __restrict__ x, double* __restrict__ partial, int64_t nvec,
+                           int64_t stride_threads) {
+  constexpr int VEC = Vec16<T>::N;
+  using V = typename Vec16<T>::type;
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= stride_threads) return;
+  double acc[VEC];
+#pragma unroll
+  for (int q = 0; q < VEC; ++q) acc[q] = 0.0;
+  const V* xv = reinterpret_cast<const V*>(x);
+  int64_t i = t;
+  for (; i + 3 * stride_threads < nvec; i += 4 * stride_threads) {   // four loads in flight
+    V v0 = __ldcs(xv + i), v1 = __ldcs(xv + i + stride_threads);
+    V v2 = __ldcs(xv + i + 2 * stride_threads), v3 = __ldcs(xv + i + 3 * stride_threads);
+#pragma unroll
+    for (int q = 0; q < VEC; ++q) {
+      acc[q] += (double)reinterpret_cast<const T*>(&v0)[q];
+      acc[q] += (double)reinterpret_cast<const T*>(&v1)[q];
+      acc[q] += (double)reinterpret_cast<const T*>(&v2)[q];
+      acc[q] += (double)reinterpret_cast<const T*>(&v3)[q];
+    }
+  }
+  for (; i < nvec; i += stride_threads) {
+    V v = __ldcs(xv + i);
+#pragma unroll
+    for (int q = 0; q < VEC; ++q) acc[q] += (double)reinterpret_cast<const T*>(&v)[q];
+  }
+#pragma unroll
+  for (int q = 0; q < VEC; ++q) partial[t * VEC + q] = acc[q];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+colsum_flat_final_kernel(const double* __restrict__ partial, T* __restrict__ out, int vec_per_row,
+                         int64_t stride_threads, int accumulate) {
+  constexpr int VEC = Vec16<T>::N;
+  __shared__ double sm[4][VEC];
+  const int group = blockIdx.x;            // column group = VEC consecutive columns
+  double acc[VEC];
+#pragma unroll
+  for (int q = 0; q < VEC; ++q) acc[q] = 0.0;
+  for (int64_t t = group + (int64_t)threadIdx.x * vec_per_row; t < stride_threads; t += (int64_t)128 * vec_per_row)
+#pragma unroll
+    for (int q = 0; q < VEC; ++q) acc[q] += partial[t * VEC + q];
+#pragma unroll
+  for (int q = 0; q < VEC; ++q)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc[q] += __shfl_xor_sync(0xffffffffu, acc[q], o);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  if (lane == 0)
+#pragma unroll
+    for (int q = 0; q < VEC; ++q) sm[w][q] = acc[q];
+  __syncthreads();
+  if (threadIdx.x < VEC) {
+    const int q = threadIdx.x;
+    const T v = (T)(((sm[0][q] + sm[1][q]) + sm[2][q]) + sm[3][q]);
+    T* o = out + group * VEC + q;
+    *o = accumulate ? add_rn(*o, v) : v;
+  }
+}
+
 template <typename T>
 static prad_status add_broadcast_backward_t(prad_ctx* ctx, const void* dy, void* dbias,
                                             int64_t rows, int cols, int accumulate) {
+  constexpr int VEC = Vec16<T>::N;
+  if (cols % VEC == 0 && ((uintptr_t)dy & 15) == 0 && rows * (int64_t)cols >= (1 << 20)) {
+    const int vec_per_row = cols / VEC;
+    int64_t threads = (int64_t)ctx->sm_count * 8 * 256;
+    const int64_t nvec = rows * vec_per_row;
+    if (threads > nvec) threads = nvec;
+    threads -= threads % vec_per_row;
+    if (threads >= vec_per_row) {
+      prad_status s = ensure_workspace(ctx, (size_t)threads * VEC * sizeof(double));
+      if (s) return s;
+      colsum_flat_partial_kernel<T><<<(unsigned)ceil_div(threads, 256), 256, 0, ctx->stream>>>(
+          (const T*)dy, (double*)ctx->ws, nvec, threads);
+      PRAD_LAUNCHED(ctx);
+      colsum_flat_final_kernel<T><<<vec_per_row, 128, 0, ctx->stream>>>((const double*)ctx->ws, (T*)dbias,
+                                                                      vec_per_row, threads, accumulate);
+      PRAD_LAUNCHED(ctx);
+      return PRAD_OK;
+    }
+  }
   int strips = (int)ceil_div(cols, 32);
   int64_t want_bands = ceil_div((int64_t)ctx->sm_count * 8, strips);
   int64_t max_bands = ceil_div(rows, 64);
@@ -231,25 +318,61 @@ __global__ void transpose_kernel(const T* __restrict__ x, T* __restrict__ y, int
 }
 
 // ---------------------------------------------------------------- n-ary sums
-#define PRAD_MAX_SRCS 16
+#define PRAD_MAX_SRCS 8
 struct SrcTable { const void* p[PRAD_MAX_SRCS]; int count; };
 
 // out[i] = sum_g src_g[i] in list order (GradientUtils.cs:33-39).  LINQ's Sum over float
 // accumulates in double and casts once; for double it is a plain left fold.
 template <typename T>
+__device__ __forceinline__ T nary_combine(const T (&v)[PRAD_MAX_SRCS], int count, int mode, T inv_count) {
+  if (mode == 0) {  // segmented sum, double accumulator
+    double acc = 0.0;
+#pragma unroll
+    for (int g = 0; g < PRAD_MAX_SRCS; ++g)
+      if (g < count) acc += (double)v[g];
+    return (T)acc;
+  }
+  T acc = v[0];     // batch mean: left fold in T, then * (1/count)
+#pragma unroll
+  for (int g = 1; g < PRAD_MAX_SRCS; ++g)
+    if (g < count) acc = add_rn(acc, v[g]);
+  return mul_rn(acc, inv_count);
+}
+
+template <typename T>
 __global__ void __launch_bounds__(256)
-nary_sum_kernel(SrcTable t, T* __restrict__ out, int64_t n, int mode, T inv_count) {
+nary_sum_kernel(SrcTable t, T* __restrict__ out, int64_t n, int mode, T inv_count, bool vec) {
+  constexpr int VEC = Vec16<T>::N;
+  using V = typename Vec16<T>::type;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-    if (mode == 0) {  // segmented sum, double accumulator
-      double acc = 0.0;
-      for (int g = 0; g < t.count; ++g) acc += (double)reinterpret_cast<const T*>(t.p[g])[i];
-      out[i] = (T)acc;
-    } else {  // batch mean: left fold in T, then * (1/count)
-      T acc = reinterpret_cast<const T*>(t.p[0])[i];
-      for (int g = 1; g < t.count; ++g) acc = add_rn(acc, reinterpret_cast<const T*>(t.p[g])[i]);
-      out[i] = mul_rn(acc, inv_count);
+  int64_t done = 0;
+  if (vec) {      // 128-bit loads of every source, all issued before the first use
+    const int64_t nvec = n / VEC;
+    for (int64_t i = tid; i < nvec; i += stride) {
+      V in[PRAD_MAX_SRCS];
+#pragma unroll
+      for (int g = 0; g < PRAD_MAX_SRCS; ++g)
+        if (g < t.count) in[g] = __ldcs(reinterpret_cast<const V*>(t.p[g]) + i);
+      V o;
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) {
+        T v[PRAD_MAX_SRCS];
+#pragma unroll
+        for (int g = 0; g < PRAD_MAX_SRCS; ++g)
+          if (g < t.count) v[g] = reinterpret_cast<const T*>(&in[g])[q];
+        reinterpret_cast<T*>(&o)[q] = nary_combine<T>(v, t.count, mode, inv_count);
+      }
+      __stcs(reinterpret_cast<V*>(out) + i, o);
     }
+    done = nvec * VEC;
+  }
+  for (int64_t i = done + tid; i < n; i += stride) {
+    T v[PRAD_MAX_SRCS];
+#pragma unroll
+    for (int g = 0; g < PRAD_MAX_SRCS; ++g)
+      if (g < t.count) v[g] = reinterpret_cast<const T*>(t.p[g])[i];
+    out[i] = nary_combine<T>(v, t.count, mode, inv_count);
   }
 }
 
@@ -259,7 +382,7 @@ static prad_status nary_t(prad_ctx* ctx, const void* const* srcs, int count, voi
   if (n <= 0) return PRAD_OK;
   // more than PRAD_MAX_SRCS sources: fold in groups, keeping list order.  The running value
   // is carried in `out`, which is exact for mode 1 (left fold) and for double mode 0; for
-  // float mode 0 the carry rounds to float between groups of 15.
+  // float mode 0 the carry rounds to float between groups of 7.
   T inv = (T)1 / (T)count;
   int done = 0;
   bool first = true;
@@ -270,10 +393,12 @@ static prad_status nary_t(prad_ctx* ctx, const void* const* srcs, int count, voi
     while (k < PRAD_MAX_SRCS && done < count) t.p[k++] = srcs[done++];
     t.count = k;
     bool last = done == count;
-    int grid = stream_grid(ctx, n, 256, 8);
+    int grid = stream_grid(ctx, ceil_div(n, Vec16<T>::N), 256, 8);
     int m = mode == 0 ? 0 : 1;
+    bool vec = ((uintptr_t)out & 15) == 0;
+    for (int g = 0; g < t.count; ++g) vec = vec && (((uintptr_t)t.p[g] & 15) == 0);
     nary_sum_kernel<T><<<grid, 256, 0, ctx->stream>>>(t, (T*)out, n, m,
-                                                      (mode == 1 && last) ? inv : (T)1);
+                                                      (mode == 1 && last) ? inv : (T)1, vec);
     PRAD_LAUNCHED(ctx);
     first = false;
   }

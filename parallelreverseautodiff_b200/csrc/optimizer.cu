@@ -14,7 +14,12 @@ constexpr int MT_MAX = 48;          // tensors per launch (table is a kernel arg
 constexpr int MT_THREADS = 256;
 constexpr int MT_CHUNK = 256 * 32;  // elements a CTA covers
 
+template <typename T> struct MtVec;
+template <> struct MtVec<float> { using type = float4; };
+template <> struct MtVec<double> { using type = double2; };
+
 struct MultiTensor {
+  bool vec;   // every pointer of every tensor is 16-byte aligned
   void* w[MT_MAX];
   void* g[MT_MAX];
   void* m[MT_MAX];
@@ -49,12 +54,24 @@ mt_partial_kernel(MultiTensor t, double* __restrict__ stats, int kind) {
   const T* g = (const T*)t.g[ti];
   const T mean = kind == 1 ? (T)stats[ST_MEAN + ti] : (T)0;
   double acc = 0.0;
-  for (int64_t i = start + threadIdx.x; i < end; i += MT_THREADS) {
-    T x = g[i];
+  auto term = [&](T x) {
     if (kind == 0) acc += (double)x;
     else if (kind == 1) { T d = sub_rn(x, mean); acc += (double)mul_rn(d, d); }
     else acc += (double)x * (double)x;
+  };
+  int64_t i0 = start;
+  if (t.vec) {    // 128-bit loads; chunk starts are multiples of the vector width
+    constexpr int VEC = 16 / sizeof(T);
+    using V = typename MtVec<T>::type;
+    const int64_t vend = end - ((end - start) % VEC);
+    for (int64_t i = start + (int64_t)threadIdx.x * VEC; i < vend; i += MT_THREADS * VEC) {
+      V v = *reinterpret_cast<const V*>(g + i);
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) term(reinterpret_cast<const T*>(&v)[q]);
+    }
+    i0 = vend;
   }
+  for (int64_t i = i0 + threadIdx.x; i < end; i += MT_THREADS) term(g[i]);
   double s = block_sum_d<MT_THREADS>(acc);
   if (threadIdx.x == 0) stats[ST_PART + blockIdx.x] = s;
 }
@@ -152,10 +169,42 @@ mt_apply_kernel(MultiTensor t, const double* __restrict__ stats, int clip_mode, 
     double norm = sqrt(stats[ST_SS]);
     if (norm > max_norm) { gscale = (T)(max_norm / norm); scale_on = true; }
   }
-  for (int64_t i = start + threadIdx.x; i < end; i += MT_THREADS) {
-    T gi = g[i];
-    if (clip_mode == 1) gi = clip_reference_value<T>(gi, mean, sd, clip, minv);
-    else if (scale_on) gi = mul_rn(gi, gscale);
+  auto clip_one = [&](T gi) {
+    if (clip_mode == 1) return clip_reference_value<T>(gi, mean, sd, clip, minv);
+    if (scale_on) return mul_rn(gi, gscale);
+    return gi;
+  };
+  int64_t i0 = start;
+  if (t.vec) {
+    constexpr int VEC = 16 / sizeof(T);
+    using V = typename MtVec<T>::type;
+    const int64_t vend = end - ((end - start) % VEC);
+    for (int64_t i = start + (int64_t)threadIdx.x * VEC; i < vend; i += MT_THREADS * VEC) {
+      V gv = *reinterpret_cast<const V*>(g + i);
+      V wv, mv, vv;
+      if (do_adam) {
+        wv = *reinterpret_cast<const V*>(w + i);
+        mv = *reinterpret_cast<const V*>(m + i);
+        vv = *reinterpret_cast<const V*>(v + i);
+      }
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) {
+        T gi = clip_one(reinterpret_cast<T*>(&gv)[q]);
+        if (do_adam)
+          adam_value<T>(a, gi, reinterpret_cast<T*>(&wv)[q], reinterpret_cast<T*>(&mv)[q], reinterpret_cast<T*>(&vv)[q]);
+        reinterpret_cast<T*>(&gv)[q] = zero_grad ? (T)0 : gi;
+      }
+      if (do_adam) {
+        *reinterpret_cast<V*>(w + i) = wv;
+        *reinterpret_cast<V*>(m + i) = mv;
+        *reinterpret_cast<V*>(v + i) = vv;
+      }
+      if (zero_grad || clip_mode != 0) *reinterpret_cast<V*>(g + i) = gv;
+    }
+    i0 = vend;
+  }
+  for (int64_t i = i0 + threadIdx.x; i < end; i += MT_THREADS) {
+    T gi = clip_one(g[i]);
     if (do_adam) {
       T wi = w[i], mi = m[i], vi = v[i];
       adam_value<T>(a, gi, wi, mi, vi);
@@ -192,7 +241,11 @@ static int build_table(MultiTensor& t, void* const* w, void* const* g, void* con
                        void* const* v, const int64_t* sizes, int first, int cnt) {
   int blk = 0;
   t.count = cnt;
+  t.vec = true;
+  auto al = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
   for (int k = 0; k < cnt; ++k) {
+    t.vec = t.vec && al(w ? w[first + k] : nullptr) && al(g ? g[first + k] : nullptr) &&
+            al(m ? m[first + k] : nullptr) && al(v ? v[first + k] : nullptr);
     t.w[k] = w ? w[first + k] : nullptr;
     t.g[k] = g ? g[first + k] : nullptr;
     t.m[k] = m ? m[first + k] : nullptr;

@@ -123,6 +123,243 @@ layernorm_backward_kernel(const T* __restrict__ x, const T* __restrict__ mean,
   }
 }
 
+// ---- short rows (cols <= 256): register-cached, several rows per warp -----------------------
+// A lane keeps E = ceil(cols/32) elements of each of R rows in registers, so every input is
+// read exactly once and R*E independent loads are in flight per lane; the R row reductions
+// are independent shuffle chains.  Same arithmetic as the streaming kernels above.
+constexpr int SR = 4;   // rows per warp pass
+
+template <typename T, int E>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+softmax_forward_short(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int cols) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * ROW_WARPS;
+  for (int64_t r0 = warp * SR; r0 < rows; r0 += nwarps * SR) {
+    T v[SR][E];
+#pragma unroll
+    for (int i = 0; i < SR; ++i)
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const int j = lane + 32 * e;
+        v[i][e] = (r0 + i < rows && j < cols) ? x[(r0 + i) * cols + j] : (T)-INFINITY;
+      }
+    T mx[SR], sum[SR];
+#pragma unroll
+    for (int i = 0; i < SR; ++i) {
+      mx[i] = v[i][0];
+#pragma unroll
+      for (int e = 1; e < E; ++e) mx[i] = v[i][e] > mx[i] ? v[i][e] : mx[i];
+      mx[i] = warp_max(mx[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < SR; ++i) {
+      sum[i] = 0;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const int j = lane + 32 * e;
+        v[i][e] = (r0 + i < rows && j < cols) ? t_exp(sub_rn(v[i][e], mx[i])) : (T)0;
+        sum[i] += v[i][e];
+      }
+      sum[i] = warp_sum(sum[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < SR; ++i)
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const int j = lane + 32 * e;
+        if (r0 + i < rows && j < cols) y[(r0 + i) * cols + j] = div_rn(v[i][e], sum[i]);
+      }
+  }
+}
+
+template <typename T, int E>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+softmax_backward_short(const T* __restrict__ y, const T* __restrict__ dy, T* __restrict__ dx,
+                       int64_t rows, int cols) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * ROW_WARPS;
+  for (int64_t r0 = warp * SR; r0 < rows; r0 += nwarps * SR) {
+    T yv[SR][E], dv[SR][E];
+#pragma unroll
+    for (int i = 0; i < SR; ++i)
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const int j = lane + 32 * e;
+        const bool ok = r0 + i < rows && j < cols;
+        yv[i][e] = ok ? y[(r0 + i) * cols + j] : (T)0;
+        dv[i][e] = ok ? dy[(r0 + i) * cols + j] : (T)0;
+      }
+    T dot[SR];
+#pragma unroll
+    for (int i = 0; i < SR; ++i) {
+      dot[i] = 0;
+#pragma unroll
+      for (int e = 0; e < E; ++e) dot[i] += mul_rn(dv[i][e], yv[i][e]);
+      dot[i] = warp_sum(dot[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < SR; ++i)
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const int j = lane + 32 * e;
+        if (r0 + i < rows && j < cols) dx[(r0 + i) * cols + j] = mul_rn(yv[i][e], sub_rn(dv[i][e], dot[i]));
+      }
+  }
+}
+
+template <typename T, int E>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+layernorm_forward_short(const T* __restrict__ x, T* __restrict__ y, T* __restrict__ mean,
+                        T* __restrict__ stdv, int64_t rows, int cols) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * ROW_WARPS;
+  for (int64_t r0 = warp * SR; r0 < rows; r0 += nwarps * SR) {
+    T v[SR][E];
+#pragma unroll
+    for (int i = 0; i < SR; ++i)
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const int j = lane + 32 * e;
+        v[i][e] = (r0 + i < rows && j < cols) ? x[(r0 + i) * cols + j] : (T)0;
+      }
+#pragma unroll
+    for (int i = 0; i < SR; ++i) {
+      double s = 0.0;
+#pragma unroll
+      for (int e = 0; e < E; ++e) s += (double)v[i][e];   // padding lanes hold 0
+      s = warp_sum(s);
+      const T mu = (T)(s / (double)cols);
+      double q = 0.0;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const int j = lane + 32 * e;
+        if (j < cols) { T d = sub_rn(v[i][e], mu); q += (double)mul_rn(d, d); }
+      }
+      q = warp_sum(q);
+      const T sd = sqrt_rn(div_rn((T)q, (T)cols));
+      if (r0 + i < rows) {
+        if (lane == 0) { mean[r0 + i] = mu; stdv[r0 + i] = sd; }
+        const T den = add_rn(sd, LnEps<T>::v());
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const int j = lane + 32 * e;
+          if (j < cols) y[(r0 + i) * cols + j] = div_rn(sub_rn(v[i][e], mu), den);
+        }
+      }
+    }
+  }
+}
+
+template <typename T, int E>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+layernorm_backward_short(const T* __restrict__ x, const T* __restrict__ mean,
+                         const T* __restrict__ stdv, const T* __restrict__ dy, T* __restrict__ dx,
+                         int64_t rows, int cols) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * ROW_WARPS;
+  for (int64_t r0 = warp * SR; r0 < rows; r0 += nwarps * SR) {
+    T xv[SR][E], dv[SR][E], mu[SR], sd[SR];
+#pragma unroll
+    for (int i = 0; i < SR; ++i) {
+      const bool rok = r0 + i < rows;
+      mu[i] = rok ? mean[r0 + i] : (T)0;
+      sd[i] = rok ? stdv[r0 + i] : (T)1;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const int j = lane + 32 * e;
+        const bool ok = rok && j < cols;
+        xv[i][e] = ok ? x[(r0 + i) * cols + j] : (T)0;
+        dv[i][e] = ok ? dy[(r0 + i) * cols + j] : (T)0;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < SR; ++i) {
+      const T se = add_rn(sd[i], LnEps<T>::v());
+      const T inv = div_rn((T)1, se);
+      const T exp1 = mul_rn(sub_rn((T)1, div_rn((T)1, (T)cols)), inv);
+      const T den = mul_rn((T)cols, mul_rn(mul_rn(se, se), se));
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const int j = lane + 32 * e;
+        if (r0 + i < rows && j < cols) {
+          T d = sub_rn(xv[i][e], mu[i]);
+          dx[(r0 + i) * cols + j] = mul_rn(dv[i][e], sub_rn(exp1, div_rn(mul_rn(d, d), den)));
+        }
+      }
+    }
+  }
+}
+
+// LayerNorm backward is elementwise once the row statistics are known: for rows that are a
+// whole number of 128-bit vectors it streams like a copy (row index = vector index / vectors
+// per row; mean and sigma come from L1/L2).  Same arithmetic as layernorm_backward_kernel.
+template <typename T> struct RowVec;
+template <> struct RowVec<float> { using type = float4; static constexpr int N = 4; };
+template <> struct RowVec<double> { using type = double2; static constexpr int N = 2; };
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+layernorm_backward_flat(const T* __restrict__ x, const T* __restrict__ mean, const T* __restrict__ stdv,
+                        const T* __restrict__ dy, T* __restrict__ dx, int64_t nvec, int vec_per_row, int cols) {
+  constexpr int VEC = RowVec<T>::N;
+  using V = typename RowVec<T>::type;
+  constexpr int U = 4;   // vectors in flight per thread
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const T one_minus = sub_rn((T)1, div_rn((T)1, (T)cols));
+  for (int64_t base = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; base < nvec; base += stride * U) {
+    V xv[U], dv[U];
+    T mu[U], sg[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = base + u * stride;
+      if (i < nvec) {
+        xv[u] = __ldcs(reinterpret_cast<const V*>(x) + i);
+        dv[u] = __ldcs(reinterpret_cast<const V*>(dy) + i);
+        const int64_t r = i / vec_per_row;
+        mu[u] = mean[r];
+        sg[u] = stdv[r];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = base + u * stride;
+      if (i < nvec) {
+        const T se = add_rn(sg[u], LnEps<T>::v());
+        const T exp1 = mul_rn(one_minus, div_rn((T)1, se));
+        const T den = mul_rn((T)cols, mul_rn(mul_rn(se, se), se));
+        V o;
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) {
+          T d = sub_rn(reinterpret_cast<const T*>(&xv[u])[q], mu[u]);
+          reinterpret_cast<T*>(&o)[q] =
+              mul_rn(reinterpret_cast<const T*>(&dv[u])[q], sub_rn(exp1, div_rn(mul_rn(d, d), den)));
+        }
+        __stcs(reinterpret_cast<V*>(dx) + i, o);
+      }
+    }
+  }
+}
+
+static inline int short_e(int cols) { return cols <= 32 ? 1 : cols <= 64 ? 2 : cols <= 128 ? 4 : cols <= 256 ? 8 : 0; }
+static inline int short_grid(const prad_ctx* ctx, int64_t rows) {
+  return stream_grid(ctx, ceil_div(rows, SR), ROW_WARPS, 8);
+}
+// runs KERNEL<T, E> for the E that fits `cols`
+#define PRAD_SHORT_ROWS(KERNEL, T, ...)                                                          \
+  do {                                                                                           \
+    const int g_ = short_grid(ctx, rows);                                                        \
+    switch (short_e(cols)) {                                                                     \
+      case 1: KERNEL<T, 1><<<g_, ROW_WARPS * 32, 0, ctx->stream>>>(__VA_ARGS__); break;          \
+      case 2: KERNEL<T, 2><<<g_, ROW_WARPS * 32, 0, ctx->stream>>>(__VA_ARGS__); break;          \
+      case 4: KERNEL<T, 4><<<g_, ROW_WARPS * 32, 0, ctx->stream>>>(__VA_ARGS__); break;          \
+      default: KERNEL<T, 8><<<g_, ROW_WARPS * 32, 0, ctx->stream>>>(__VA_ARGS__); break;         \
+    }                                                                                            \
+  } while (0)
+
 static inline int row_grid(const prad_ctx* ctx, int64_t rows) {
   return stream_grid(ctx, rows, ROW_WARPS, 8);
 }
@@ -139,7 +376,10 @@ prad_status prad_softmax_forward(prad_ctx* ctx, prad_dtype dt, const void* x, vo
   PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0, PRAD_ERR_INVALID, "prad_softmax_forward: bad argument");
   if (rows == 0 || cols == 0) return PRAD_OK;
   PRAD_REQUIRE(x && y, PRAD_ERR_INVALID, "prad_softmax_forward: null pointer");
-  if (dt == PRAD_F32) softmax_forward_kernel<float><<<row_grid(ctx, rows), ROW_WARPS * 32, 0, ctx->stream>>>((const float*)x, (float*)y, rows, cols);
+  if (short_e(cols)) {
+    if (dt == PRAD_F32) PRAD_SHORT_ROWS(softmax_forward_short, float, (const float*)x, (float*)y, rows, cols);
+    else PRAD_SHORT_ROWS(softmax_forward_short, double, (const double*)x, (double*)y, rows, cols);
+  } else if (dt == PRAD_F32) softmax_forward_kernel<float><<<row_grid(ctx, rows), ROW_WARPS * 32, 0, ctx->stream>>>((const float*)x, (float*)y, rows, cols);
   else softmax_forward_kernel<double><<<row_grid(ctx, rows), ROW_WARPS * 32, 0, ctx->stream>>>((const double*)x, (double*)y, rows, cols);
   PRAD_LAUNCHED(ctx);
   return PRAD_OK;
@@ -151,7 +391,10 @@ prad_status prad_softmax_backward(prad_ctx* ctx, prad_dtype dt, const void* y, c
   PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0, PRAD_ERR_INVALID, "prad_softmax_backward: bad argument");
   if (rows == 0 || cols == 0) return PRAD_OK;
   PRAD_REQUIRE(y && dy && dx, PRAD_ERR_INVALID, "prad_softmax_backward: null pointer");
-  if (dt == PRAD_F32) softmax_backward_kernel<float><<<row_grid(ctx, rows), ROW_WARPS * 32, 0, ctx->stream>>>((const float*)y, (const float*)dy, (float*)dx, rows, cols);
+  if (short_e(cols)) {
+    if (dt == PRAD_F32) PRAD_SHORT_ROWS(softmax_backward_short, float, (const float*)y, (const float*)dy, (float*)dx, rows, cols);
+    else PRAD_SHORT_ROWS(softmax_backward_short, double, (const double*)y, (const double*)dy, (double*)dx, rows, cols);
+  } else if (dt == PRAD_F32) softmax_backward_kernel<float><<<row_grid(ctx, rows), ROW_WARPS * 32, 0, ctx->stream>>>((const float*)y, (const float*)dy, (float*)dx, rows, cols);
   else softmax_backward_kernel<double><<<row_grid(ctx, rows), ROW_WARPS * 32, 0, ctx->stream>>>((const double*)y, (const double*)dy, (double*)dx, rows, cols);
   PRAD_LAUNCHED(ctx);
   return PRAD_OK;
@@ -163,7 +406,10 @@ prad_status prad_layernorm_forward(prad_ctx* ctx, prad_dtype dt, const void* x, 
   PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0, PRAD_ERR_INVALID, "prad_layernorm_forward: bad argument");
   if (rows == 0 || cols == 0) return PRAD_OK;
   PRAD_REQUIRE(x && y && mean && stdv, PRAD_ERR_INVALID, "prad_layernorm_forward: null pointer");
-  if (dt == PRAD_F32) layernorm_forward_kernel<float><<<row_grid(ctx, rows), ROW_WARPS * 32, 0, ctx->stream>>>((const float*)x, (float*)y, (float*)mean, (float*)stdv, rows, cols);
+  if (short_e(cols)) {
+    if (dt == PRAD_F32) PRAD_SHORT_ROWS(layernorm_forward_short, float, (const float*)x, (float*)y, (float*)mean, (float*)stdv, rows, cols);
+    else PRAD_SHORT_ROWS(layernorm_forward_short, double, (const double*)x, (double*)y, (double*)mean, (double*)stdv, rows, cols);
+  } else if (dt == PRAD_F32) layernorm_forward_kernel<float><<<row_grid(ctx, rows), ROW_WARPS * 32, 0, ctx->stream>>>((const float*)x, (float*)y, (float*)mean, (float*)stdv, rows, cols);
   else layernorm_forward_kernel<double><<<row_grid(ctx, rows), ROW_WARPS * 32, 0, ctx->stream>>>((const double*)x, (double*)y, (double*)mean, (double*)stdv, rows, cols);
   PRAD_LAUNCHED(ctx);
   return PRAD_OK;
@@ -176,7 +422,16 @@ prad_status prad_layernorm_backward(prad_ctx* ctx, prad_dtype dt, const void* x,
   PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0, PRAD_ERR_INVALID, "prad_layernorm_backward: bad argument");
   if (rows == 0 || cols == 0) return PRAD_OK;
   PRAD_REQUIRE(x && mean && stdv && dy && dx, PRAD_ERR_INVALID, "prad_layernorm_backward: null pointer");
-  if (dt == PRAD_F32) layernorm_backward_kernel<float><<<row_grid(ctx, rows), ROW_WARPS * 32, 0, ctx->stream>>>((const float*)x, (const float*)mean, (const float*)stdv, (const float*)dy, (float*)dx, rows, cols);
+  const int vecn = dt == PRAD_F32 ? 4 : 2;
+  if (cols % vecn == 0 && (((uintptr_t)x | (uintptr_t)dy | (uintptr_t)dx) & 15) == 0) {
+    const int64_t nvec = rows * (cols / vecn);
+    const int grid = stream_grid(ctx, ceil_div(nvec, 4), 256, 8);
+    if (dt == PRAD_F32) layernorm_backward_flat<float><<<grid, 256, 0, ctx->stream>>>((const float*)x, (const float*)mean, (const float*)stdv, (const float*)dy, (float*)dx, nvec, cols / vecn, cols);
+    else layernorm_backward_flat<double><<<grid, 256, 0, ctx->stream>>>((const double*)x, (const double*)mean, (const double*)stdv, (const double*)dy, (double*)dx, nvec, cols / vecn, cols);
+  } else if (short_e(cols)) {
+    if (dt == PRAD_F32) PRAD_SHORT_ROWS(layernorm_backward_short, float, (const float*)x, (const float*)mean, (const float*)stdv, (const float*)dy, (float*)dx, rows, cols);
+    else PRAD_SHORT_ROWS(layernorm_backward_short, double, (const double*)x, (const double*)mean, (const double*)stdv, (const double*)dy, (double*)dx, rows, cols);
+  } else if (dt == PRAD_F32) layernorm_backward_kernel<float><<<row_grid(ctx, rows), ROW_WARPS * 32, 0, ctx->stream>>>((const float*)x, (const float*)mean, (const float*)stdv, (const float*)dy, (float*)dx, rows, cols);
   else layernorm_backward_kernel<double><<<row_grid(ctx, rows), ROW_WARPS * 32, 0, ctx->stream>>>((const double*)x, (const double*)mean, (const double*)stdv, (const double*)dy, (double*)dx, rows, cols);
   PRAD_LAUNCHED(ctx);
   return PRAD_OK;

@@ -392,11 +392,14 @@ class Engine:
                                              y.size // y.shape[-1], y.shape[-1]))
         return out
 
-    def layernorm_forward(self, x):
+    def layernorm_forward(self, x, out=None):
         rows = x.size // x.shape[-1]
-        y = self.empty(x.shape, x.dtype)
-        mean = self.empty((rows,), x.dtype)
-        std = self.empty((rows,), x.dtype)
+        if out is not None:
+            y, mean, std = out
+        else:
+            y = self.empty(x.shape, x.dtype)
+            mean = self.empty((rows,), x.dtype)
+            std = self.empty((rows,), x.dtype)
         check(self.lib.prad_layernorm_forward(self.ctx, dtype_code(x.dtype), x.ptr, y.ptr, mean.ptr,
                                               std.ptr, rows, x.shape[-1]))
         return y, mean, std

@@ -210,7 +210,7 @@ def test_hadamard_add_scale_transpose(engine, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("shape", [(1, 1), (256, 10), (333, 96), (4097, 33), (64, 4096)])
+@pytest.mark.parametrize("shape", [(1, 1), (256, 10), (333, 96), (4097, 33), (64, 4096), (20001, 96), (700, 4096), (9000, 130)])
 def test_add_broadcast(engine, dtype, shape):
     r = rng(shape[1])
     x, dy = normal(r, shape, 1, dtype), normal(r, shape, 1, dtype)
@@ -239,7 +239,7 @@ def test_softmax(engine, dtype, shape):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("shape", [(1, 2), (22, 22), (333, 96), (5, 4097)])
+@pytest.mark.parametrize("shape", [(1, 2), (22, 22), (333, 96), (5, 4097), (1001, 49), (7, 300)])
 def test_layernorm(engine, dtype, shape):
     r = rng(shape[1])
     x, dy = normal(r, shape, 3.0, dtype) + dtype(0.5), normal(r, shape, 1.0, dtype)
@@ -304,7 +304,7 @@ def test_segmented_sum_accumulate_batch_mean(engine, dtype, count):
     gs = [normal(r, (64, 33), 1, dtype) for _ in range(count)]
     dev = [engine.upload(g) for g in gs]
     got = engine.segmented_sum(dev).numpy()
-    if count <= 16 or dtype == np.float64:
+    if count <= 8 or dtype == np.float64:
         np.testing.assert_array_equal(got, O.accumulate_gradients(gs))
     else:
         assert_close(got, O.accumulate_gradients(gs), count, "segmented sum")
