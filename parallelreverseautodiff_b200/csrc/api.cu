@@ -145,6 +145,10 @@ prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value) {
     else { set_error("prad_set_option: gemm_f64 must be auto|simt|simt_fma|dmma, got '%s'", value); return PRAD_ERR_INVALID; }
     return PRAD_OK;
   }
+  if (!strcmp(key, "tc_split_k")) {
+    ctx->tc_split_k = strcmp(value, "off") != 0 && strcmp(value, "0") != 0;
+    return PRAD_OK;
+  }
   if (!strcmp(key, "tc_pipeline")) {  // tensor-core GEMM pipeline: k-block floats x stages
     if (!strcmp(value, "16x4")) ctx->tc_variant = 0;
     else if (!strcmp(value, "32x2")) ctx->tc_variant = 1;

@@ -43,6 +43,7 @@ struct prad_ctx {
   int* tc_err = nullptr;
   bool tc_pending_check = false;
   int tc_variant = 0;  // pipeline shape of the tensor-core GEMM (option "tc_pipeline")
+  bool tc_split_k = true;  // option "tc_split_k": cut k across CTAs when the tile count wastes SMs
   int tc_auto_mode = 1;  // split scheme "auto" picks: 0 = 3xTF32, 1 = TF32 + BF16 corrections
   uint32_t magic = 0x50524144u;  // "PRAD"
 };

@@ -256,7 +256,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
                    const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
                    const __grid_constant__ CUtensorMap map_a_x, const __grid_constant__ CUtensorMap map_b_x,
                    int M, int N, int K, float* __restrict__ C, int64_t ldc, bool vecC, Epi epi,
-                   int* __restrict__ err_flag) {
+                   int* __restrict__ err_flag, int kb_per_split, int64_t split_stride) {
+  // blockIdx.z selects a slice of the k range (split-K); slice z writes its partial product
+  // to C + z * split_stride and a later pass adds the slices in order.
   // MODE 0 tiles per stage: A_hi, A_lo (FP32) | B_hi, B_lo (FP32);  map_*_x unused.
   // MODE 1 tiles per stage: A_hi (FP32), A_hb, A_lb (BF16) | B_hi (FP32), B_hb, B_lb (BF16);
   //        map_*_lo address the bf16(x - hi) arrays, map_*_x the bf16(x) arrays.
@@ -279,7 +281,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  const int num_kb = (K + BK - 1) / BK;
+  const int kb0 = blockIdx.z * kb_per_split;
+  const int num_kb = min((K + BK - 1) / BK - kb0, kb_per_split);
+  C += (int64_t)blockIdx.z * split_stride;
   const int num_chunks = (num_kb + CHUNK_KB - 1) / CHUNK_KB;
 
   // an earlier CTA gave up: do not start (one read per CTA so that all threads agree)
@@ -313,24 +317,24 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
         mbar_expect_tx(full_bar(s), STAGE_BYTES);
         if (MODE == 2) {   // six BF16 tiles: A b0, b1, b2 then B b0, b1, b2
           constexpr int AT = A_TILE_BYTES / 2, BT = B_TILE_BYTES / 2;
-          tma_load_2d(st, &map_a_hi, full_bar(s), kb * BK, m0);
-          tma_load_2d(st + AT, &map_a_x, full_bar(s), kb * BK, m0);
-          tma_load_2d(st + 2 * AT, &map_a_lo, full_bar(s), kb * BK, m0);
-          tma_load_2d(st + 3 * AT, &map_b_hi, full_bar(s), kb * BK, n0);
-          tma_load_2d(st + 3 * AT + BT, &map_b_x, full_bar(s), kb * BK, n0);
-          tma_load_2d(st + 3 * AT + 2 * BT, &map_b_lo, full_bar(s), kb * BK, n0);
+          tma_load_2d(st, &map_a_hi, full_bar(s), (kb0 + kb) * BK, m0);
+          tma_load_2d(st + AT, &map_a_x, full_bar(s), (kb0 + kb) * BK, m0);
+          tma_load_2d(st + 2 * AT, &map_a_lo, full_bar(s), (kb0 + kb) * BK, m0);
+          tma_load_2d(st + 3 * AT, &map_b_hi, full_bar(s), (kb0 + kb) * BK, n0);
+          tma_load_2d(st + 3 * AT + BT, &map_b_x, full_bar(s), (kb0 + kb) * BK, n0);
+          tma_load_2d(st + 3 * AT + 2 * BT, &map_b_lo, full_bar(s), (kb0 + kb) * BK, n0);
           continue;
         }
-        tma_load_2d(st, &map_a_hi, full_bar(s), kb * BK, m0);
-        tma_load_2d(st + 2 * A_TILE_BYTES, &map_b_hi, full_bar(s), kb * BK, n0);
+        tma_load_2d(st, &map_a_hi, full_bar(s), (kb0 + kb) * BK, m0);
+        tma_load_2d(st + 2 * A_TILE_BYTES, &map_b_hi, full_bar(s), (kb0 + kb) * BK, n0);
         if (MODE == 0) {
-          tma_load_2d(st + A_TILE_BYTES, &map_a_lo, full_bar(s), kb * BK, m0);
-          tma_load_2d(st + 2 * A_TILE_BYTES + B_TILE_BYTES, &map_b_lo, full_bar(s), kb * BK, n0);
+          tma_load_2d(st + A_TILE_BYTES, &map_a_lo, full_bar(s), (kb0 + kb) * BK, m0);
+          tma_load_2d(st + 2 * A_TILE_BYTES + B_TILE_BYTES, &map_b_lo, full_bar(s), (kb0 + kb) * BK, n0);
         } else {   // two half-size BF16 tiles where MODE 0 has one FP32 tile
-          tma_load_2d(st + A_TILE_BYTES, &map_a_x, full_bar(s), kb * BK, m0);
-          tma_load_2d(st + A_TILE_BYTES + A_TILE_BYTES / 2, &map_a_lo, full_bar(s), kb * BK, m0);
-          tma_load_2d(st + 2 * A_TILE_BYTES + B_TILE_BYTES, &map_b_x, full_bar(s), kb * BK, n0);
-          tma_load_2d(st + 2 * A_TILE_BYTES + B_TILE_BYTES + B_TILE_BYTES / 2, &map_b_lo, full_bar(s), kb * BK, n0);
+          tma_load_2d(st + A_TILE_BYTES, &map_a_x, full_bar(s), (kb0 + kb) * BK, m0);
+          tma_load_2d(st + A_TILE_BYTES + A_TILE_BYTES / 2, &map_a_lo, full_bar(s), (kb0 + kb) * BK, m0);
+          tma_load_2d(st + 2 * A_TILE_BYTES + B_TILE_BYTES, &map_b_x, full_bar(s), (kb0 + kb) * BK, n0);
+          tma_load_2d(st + 2 * A_TILE_BYTES + B_TILE_BYTES + B_TILE_BYTES / 2, &map_b_lo, full_bar(s), (kb0 + kb) * BK, n0);
         }
       }
     }
@@ -570,6 +574,21 @@ split_transpose_kernel(const float* __restrict__ src, int64_t src_ld, float* __r
   }
 }
 
+// C = alpha * (P_0 + P_1 + ... ) + beta * C, slices added in order; P_s are dense M x N.
+__global__ void __launch_bounds__(256)
+splitk_combine_kernel(const float* __restrict__ part, int splits, int64_t mn, int M, int N,
+                      float* __restrict__ C, int64_t ldc, float alpha, float beta) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < mn; i += stride) {
+    float acc = part[i];
+    for (int s = 1; s < splits; ++s) acc = __fadd_rn(acc, part[(int64_t)s * mn + i]);
+    const int64_t off = (i / N) * ldc + (i % N);
+    float v = __fmul_rn(alpha, acc);
+    if (beta != 0.f) v = (beta == 1.f) ? __fadd_rn(C[off], v) : fmaf(beta, C[off], v);
+    C[off] = v;
+  }
+}
+
 // ---- host side --------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -652,9 +671,47 @@ static prad_status launch_tf32x3(prad_ctx* ctx, const SplitOperand& a, const Spl
   PRAD_REQUIRE(ok, PRAD_ERR_CUDA, "gemm tf32x3: cuTensorMapEncodeTiled failed (M %d N %d K %lld)", M, N, (long long)kp);
   dim3 grid((unsigned)ceil_div(N, BN), (unsigned)ceil_div(M, BM));
   PRAD_REQUIRE(grid.y <= 65535, PRAD_ERR_UNSUPPORTED, "gemm tf32x3: too many row tiles (%u)", grid.y);
-  gemm_tf32x3_kernel<CFG><<<grid, THREADS, CFG::SMEM_BYTES, ctx->stream>>>(ma_hi, ma_lo, mb_hi, mb_lo, ma_x, mb_x, M, N,
-                                                                         (int)kp, C, ldc, vecC, epi, ctx->tc_err);
-  PRAD_LAUNCHED(ctx);
+  // Split-K against wave quantisation: with few output tiles and a long k range (the weight
+  // gradient dW = A^T dZ) the last wave of CTAs leaves most SMs idle.  Cutting k into `splits`
+  // slices multiplies the CTA count; each slice writes its own partial product and a
+  // streaming pass adds them in slice order (deterministic), applying alpha and beta.
+  const int total_kb = (int)(kp / CFG::BK);
+  const int64_t tiles = (int64_t)grid.x * grid.y;
+  int splits = 1;
+  const bool plain_epi = !epi.bias && !epi.z_out && epi.act == PRAD_ACT_NONE && epi.dact == PRAD_ACT_NONE;
+  if (plain_epi && ctx->tc_split_k) {
+    auto eff = [&](int sp) {
+      const int64_t ctas = tiles * sp;
+      return (double)ctas / (double)(ceil_div(ctas, ctx->sm_count) * ctx->sm_count);
+    };
+    double best = eff(1) * 1.08;   // a split must pay for its extra pass
+    for (int sp = 2; sp <= 4; ++sp)
+      if (kp / sp >= 2048 && eff(sp) > best) { best = eff(sp); splits = sp; }
+  }
+  if (splits == 1) {
+    gemm_tf32x3_kernel<CFG><<<grid, THREADS, CFG::SMEM_BYTES, ctx->stream>>>(
+        ma_hi, ma_lo, mb_hi, mb_lo, ma_x, mb_x, M, N, (int)kp, C, ldc, vecC, epi, ctx->tc_err, total_kb, 0);
+    PRAD_LAUNCHED(ctx);
+  } else {
+    const int64_t mn = (int64_t)M * N;
+    prad_status st = ensure_stage(ctx, (size_t)splits * mn * sizeof(float));
+    if (st) return st;
+    float* part = (float*)ctx->stage;
+    Epi raw = epi;
+    raw.alpha = 1.f;
+    raw.beta = 0.f;
+    grid.z = (unsigned)splits;
+    // k-blocks per slice rounded up to whole accumulation chunks, so slices start on chunk boundaries
+    int kbps = (int)ceil_div(ceil_div(total_kb, splits), CFG::CHUNK_KB) * CFG::CHUNK_KB;
+    splits = (int)ceil_div(total_kb, kbps);   // no empty slice
+    grid.z = (unsigned)splits;
+    gemm_tf32x3_kernel<CFG><<<grid, THREADS, CFG::SMEM_BYTES, ctx->stream>>>(
+        ma_hi, ma_lo, mb_hi, mb_lo, ma_x, mb_x, M, N, (int)kp, part, N, true, raw, ctx->tc_err, kbps, mn);
+    PRAD_LAUNCHED(ctx);
+    const int cg = stream_grid(ctx, ceil_div(mn, 4), 256, 8);
+    splitk_combine_kernel<<<cg, 256, 0, ctx->stream>>>(part, splits, mn, M, N, C, ldc, epi.alpha, epi.beta);
+    PRAD_LAUNCHED(ctx);
+  }
   ctx->tc_pending_check = true;
   return PRAD_OK;
 }
