@@ -315,6 +315,58 @@ prad_status prad_clip_adam(prad_ctx* ctx, prad_dtype dt, void* const* w_host,
                            double beta2, double eps, double iteration, prad_adam_form form,
                            int zero_grad);
 
+/* ---------------------------------------------------------------- graph mode
+ * Static-schedule replacement of OperationNeuralNetworkVisitor.Traverse
+ * (src/RMAD/OperationNeuralNetworkVisitor.cs:143-337) and of the consumer counting of
+ * OperationGraphVisitor (src/RMAD/OperationGraphVisitor.cs:124-162).  The managed side keeps
+ * building the graph from JSON (ComputationGraph.ConstructFromArchitecture) and hands the
+ * resulting DAG over: values (matrices) and nodes (operations on values, added in forward
+ * order).  prad_graph_backward walks the nodes once in reverse order on the context's
+ * stream -- no tasks, locks or semaphores:
+ *   - the gradient of a value with several consumers is the sum of the consumers'
+ *     contributions in the order the consumers were added (GradientUtils.AccumulateGradients,
+ *     src/RMAD/GradientUtils.cs:22-42), one deterministic prad_segmented_sum;
+ *   - a value with a gradient destination (a weight) gets `destination += gradient`
+ *     (OperationBase.AccumulateGradient, src/RMAD/OperationBase.cs:273-304), so a weight
+ *     shared by several nodes or time steps accumulates all of them;
+ *   - every Backward runs once per node (the visitor re-runs it once per incoming edge).
+ * Buffers of intermediate values and gradients are allocated on first use and reused. */
+typedef struct prad_graph prad_graph;
+typedef enum {
+  PRAD_OP_MATMUL = 0,        /* MatrixMultiplyOperation(a, b)                     */
+  PRAD_OP_ADD = 1,           /* MatrixAddOperation(a, b)                          */
+  PRAD_OP_ADD3 = 2,          /* MatrixAddThreeOperation(a, b, c)                  */
+  PRAD_OP_ADD_BROADCAST = 3, /* MatrixAddBroadcastingOperation(x, bias[1 x cols]) */
+  PRAD_OP_HADAMARD = 4,      /* HadamardProductOperation(a, b)                    */
+  PRAD_OP_LEAKY_RELU = 5,    /* scalar = alpha                                    */
+  PRAD_OP_SIGMOID = 6,
+  PRAD_OP_TANH = 7,
+  PRAD_OP_GELU = 8,
+  PRAD_OP_SOFTMAX = 9,
+  PRAD_OP_LAYERNORM = 10,
+  PRAD_OP_SCALE = 11,        /* MatrixMultiplyScalarOperation, scalar = factor    */
+  PRAD_OP_TRANSPOSE = 12
+} prad_op;
+
+prad_status prad_graph_create(prad_ctx* ctx, prad_dtype dt, prad_graph** out_graph);
+prad_status prad_graph_destroy(prad_graph* g);
+/* A value is a rows x cols matrix.  data != NULL: caller-owned device matrix (input, weight,
+ * constant); data == NULL: produced by a node, owned by the graph. */
+prad_status prad_graph_add_value(prad_graph* g, int rows, int cols, void* data, int* out_value);
+/* Weight-style value: its gradient is ADDED into this caller-owned matrix on every backward. */
+prad_status prad_graph_set_gradient_destination(prad_graph* g, int value, void* grad_matrix);
+/* Nodes must be added in forward (topological) order; `out_value` must be graph-owned. */
+prad_status prad_graph_add_node(prad_graph* g, prad_op op, const int* in_values, int n_in,
+                                int out_value, double scalar, int* out_node);
+prad_status prad_graph_forward(prad_graph* g);
+/* Backward from `start_value` with upstream gradient d_start (device matrix of that shape). */
+prad_status prad_graph_backward(prad_graph* g, int start_value, const void* d_start);
+/* Device pointers valid until the next forward/backward (NULL gradient = not reached). */
+prad_status prad_graph_value_data(prad_graph* g, int value, void** out_data);
+prad_status prad_graph_value_gradient(prad_graph* g, int value, void** out_grad);
+/* How many consumers each value had in the last backward (BackwardDependencyCounts). */
+prad_status prad_graph_consumer_count(prad_graph* g, int value, int* out_count);
+
 /* ---------------------------------------------------------------- data parallel
  * Not in the reference (it has no multi-device code; its closest relative is the offline
  * averaging of GradientStore.AverageGradients, src/RMAD/GradientStore.cs:24-104).

@@ -74,6 +74,16 @@ SIGNATURES = {
     "prad_adam": [vp, i32, pvp, pvp, pvp, pvp, pi64, i32, f64, f64, f64, f64, f64, i32, i32],
     "prad_clip_adam": [vp, i32, pvp, pvp, pvp, pvp, pi64, i32, i32, f64, f64, f64, f64, f64, f64,
                        f64, i32, i32],
+    "prad_graph_create": [vp, i32, pvp],
+    "prad_graph_destroy": [vp],
+    "prad_graph_add_value": [vp, i32, i32, vp, C.POINTER(C.c_int)],
+    "prad_graph_set_gradient_destination": [vp, i32, vp],
+    "prad_graph_add_node": [vp, i32, C.POINTER(C.c_int), i32, i32, f64, C.POINTER(C.c_int)],
+    "prad_graph_forward": [vp],
+    "prad_graph_backward": [vp, i32, vp],
+    "prad_graph_value_data": [vp, i32, pvp],
+    "prad_graph_value_gradient": [vp, i32, pvp],
+    "prad_graph_consumer_count": [vp, i32, C.POINTER(C.c_int)],
     "prad_dp_unique_id": [vp],
     "prad_dp_init": [vp, vp, i32, i32],
     "prad_dp_allreduce": [vp, i32, vp, i64],

@@ -1,0 +1,386 @@
+// Graph mode: a static-schedule backward over an operation DAG, replacing the managed
+// visitor's tasks, locks and semaphores (OperationNeuralNetworkVisitor.cs:143-337) by one
+// reverse walk on a stream.  Host-side C++ only; every arithmetic step is a call to one of the
+// library's own entry points.
+#include <algorithm>
+#include <memory>
+
+#include "common.cuh"
+
+namespace prad {
+
+struct GValue {
+  int rows = 0, cols = 0;
+  void* data = nullptr;        // caller-owned or graph-owned
+  bool owned = false;
+  void* grad_dst = nullptr;    // weight-style destination (+=)
+  void* grad = nullptr;        // gradient after the last backward (may alias a contribution)
+  std::vector<void*> contrib;  // contributions of the consumers, in consumer order
+  void* sum_buf = nullptr;     // fan-in sum (graph-owned, reused)
+  int consumers = 0;
+};
+
+struct GNode {
+  prad_op op;
+  std::vector<int> in;
+  int out = -1;
+  double scalar = 0.0;
+  // per-node state kept between forward and backward
+  void* aux0 = nullptr;        // LayerNorm mean
+  void* aux1 = nullptr;        // LayerNorm sigma
+  std::vector<void*> in_grad;  // gradient buffers of the inputs (graph-owned, reused)
+};
+
+}  // namespace prad
+
+struct prad_graph {
+  prad_ctx* ctx = nullptr;
+  prad_dtype dt = PRAD_F32;
+  std::vector<prad::GValue> values;
+  std::vector<prad::GNode> nodes;
+  std::vector<void*> owned;    // every device block the graph allocated
+  uint32_t magic = 0x47524146u;
+};
+
+namespace prad {
+
+static bool graph_ok(const prad_graph* g) { return g && g->magic == 0x47524146u && ctx_ok(g->ctx); }
+
+#define PRAD_CHECK_GRAPH(g)                                                          \
+  do {                                                                               \
+    if (!prad::graph_ok(g)) {                                                        \
+      prad::set_error("graph handle is null, destroyed, or its context was shut down"); \
+      return PRAD_ERR_NOT_INITIALIZED;                                               \
+    }                                                                                \
+  } while (0)
+
+static prad_status g_alloc(prad_graph* g, size_t elems, void** out) {
+  prad_status s = prad_alloc(g->ctx, elems * dtype_size(g->dt), out);
+  if (s == PRAD_OK) g->owned.push_back(*out);
+  return s;
+}
+
+static int arity(prad_op op) {
+  switch (op) {
+    case PRAD_OP_MATMUL: case PRAD_OP_ADD: case PRAD_OP_ADD_BROADCAST: case PRAD_OP_HADAMARD: return 2;
+    case PRAD_OP_ADD3: return 3;
+    default: return 1;
+  }
+}
+
+static prad_act act_of(prad_op op) {
+  switch (op) {
+    case PRAD_OP_LEAKY_RELU: return PRAD_ACT_LEAKY_RELU;
+    case PRAD_OP_SIGMOID: return PRAD_ACT_SIGMOID;
+    case PRAD_OP_TANH: return PRAD_ACT_TANH;
+    case PRAD_OP_GELU: return PRAD_ACT_GELU;
+    default: return PRAD_ACT_NONE;
+  }
+}
+
+}  // namespace prad
+
+using namespace prad;
+
+extern "C" {
+
+prad_status prad_graph_create(prad_ctx* ctx, prad_dtype dt, prad_graph** out_graph) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(out_graph && dtype_ok(dt), PRAD_ERR_INVALID, "prad_graph_create: bad argument");
+  prad_graph* g = new prad_graph();
+  g->ctx = ctx;
+  g->dt = dt;
+  *out_graph = g;
+  return PRAD_OK;
+}
+
+prad_status prad_graph_destroy(prad_graph* g) {
+  PRAD_CHECK_GRAPH(g);
+  for (void* p : g->owned) prad_free(g->ctx, p);
+  g->magic = 0;
+  delete g;
+  return PRAD_OK;
+}
+
+prad_status prad_graph_add_value(prad_graph* g, int rows, int cols, void* data, int* out_value) {
+  PRAD_CHECK_GRAPH(g);
+  PRAD_REQUIRE(rows > 0 && cols > 0 && out_value, PRAD_ERR_SHAPE, "prad_graph_add_value: bad shape or null output");
+  GValue v;
+  v.rows = rows;
+  v.cols = cols;
+  v.data = data;
+  g->values.push_back(v);
+  *out_value = (int)g->values.size() - 1;
+  return PRAD_OK;
+}
+
+prad_status prad_graph_set_gradient_destination(prad_graph* g, int value, void* grad_matrix) {
+  PRAD_CHECK_GRAPH(g);
+  PRAD_REQUIRE(value >= 0 && value < (int)g->values.size() && grad_matrix, PRAD_ERR_INVALID,
+               "prad_graph_set_gradient_destination: bad value id or null matrix");
+  g->values[value].grad_dst = grad_matrix;
+  return PRAD_OK;
+}
+
+prad_status prad_graph_add_node(prad_graph* g, prad_op op, const int* in_values, int n_in,
+                                int out_value, double scalar, int* out_node) {
+  PRAD_CHECK_GRAPH(g);
+  PRAD_REQUIRE(op >= PRAD_OP_MATMUL && op <= PRAD_OP_TRANSPOSE && in_values, PRAD_ERR_INVALID,
+               "prad_graph_add_node: unknown operation or null inputs");
+  PRAD_REQUIRE(n_in == arity(op), PRAD_ERR_INVALID, "prad_graph_add_node: operation %d takes %d inputs, got %d",
+               (int)op, arity(op), n_in);
+  const int nv = (int)g->values.size();
+  PRAD_REQUIRE(out_value >= 0 && out_value < nv, PRAD_ERR_INVALID, "prad_graph_add_node: bad output value id");
+  for (int i = 0; i < n_in; ++i)
+    PRAD_REQUIRE(in_values[i] >= 0 && in_values[i] < nv && in_values[i] != out_value, PRAD_ERR_INVALID,
+                 "prad_graph_add_node: bad input value id at position %d", i);
+  GValue& o = g->values[out_value];
+  PRAD_REQUIRE(o.data == nullptr || o.owned, PRAD_ERR_INVALID,
+               "prad_graph_add_node: the output value must be graph-owned (added with data == NULL)");
+  auto& V = g->values;
+  const GValue& a = V[in_values[0]];
+  // shape rules of the managed operations
+  bool ok = true;
+  switch (op) {
+    case PRAD_OP_MATMUL: {
+      const GValue& b = V[in_values[1]];
+      PRAD_REQUIRE(a.cols == b.rows, PRAD_ERR_SHAPE, "Input 1 columns do not match Input 2 rows");
+      ok = o.rows == a.rows && o.cols == b.cols;
+      break;
+    }
+    case PRAD_OP_ADD_BROADCAST: {
+      const GValue& b = V[in_values[1]];
+      PRAD_REQUIRE(b.rows == 1 && b.cols == a.cols, PRAD_ERR_SHAPE,
+                   "The length of the bias vector must be the same as the number of columns in the input matrix.");
+      ok = o.rows == a.rows && o.cols == a.cols;
+      break;
+    }
+    case PRAD_OP_TRANSPOSE: ok = o.rows == a.cols && o.cols == a.rows; break;
+    default:
+      for (int i = 1; i < n_in; ++i) ok = ok && V[in_values[i]].rows == a.rows && V[in_values[i]].cols == a.cols;
+      ok = ok && o.rows == a.rows && o.cols == a.cols;
+  }
+  PRAD_REQUIRE(ok, PRAD_ERR_SHAPE, "prad_graph_add_node: operand shapes do not fit operation %d", (int)op);
+  if (!o.data) {
+    prad_status s = g_alloc(g, (size_t)o.rows * o.cols, &o.data);
+    if (s) return s;
+    o.owned = true;
+  }
+  GNode n;
+  n.op = op;
+  n.in.assign(in_values, in_values + n_in);
+  n.out = out_value;
+  n.scalar = scalar;
+  n.in_grad.assign(n_in, nullptr);
+  g->nodes.push_back(n);
+  if (out_node) *out_node = (int)g->nodes.size() - 1;
+  return PRAD_OK;
+}
+
+prad_status prad_graph_value_data(prad_graph* g, int value, void** out_data) {
+  PRAD_CHECK_GRAPH(g);
+  PRAD_REQUIRE(value >= 0 && value < (int)g->values.size() && out_data, PRAD_ERR_INVALID, "prad_graph_value_data: bad argument");
+  *out_data = g->values[value].data;
+  return PRAD_OK;
+}
+
+prad_status prad_graph_value_gradient(prad_graph* g, int value, void** out_grad) {
+  PRAD_CHECK_GRAPH(g);
+  PRAD_REQUIRE(value >= 0 && value < (int)g->values.size() && out_grad, PRAD_ERR_INVALID, "prad_graph_value_gradient: bad argument");
+  *out_grad = g->values[value].grad;
+  return PRAD_OK;
+}
+
+prad_status prad_graph_consumer_count(prad_graph* g, int value, int* out_count) {
+  PRAD_CHECK_GRAPH(g);
+  PRAD_REQUIRE(value >= 0 && value < (int)g->values.size() && out_count, PRAD_ERR_INVALID, "prad_graph_consumer_count: bad argument");
+  *out_count = g->values[value].consumers;
+  return PRAD_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------- forward / backward walks
+namespace prad {
+
+#define G_TRY(call)                   \
+  do {                                \
+    prad_status s_ = (call);          \
+    if (s_ != PRAD_OK) return s_;     \
+  } while (0)
+
+static prad_status node_forward(prad_graph* g, GNode& n) {
+  auto& V = g->values;
+  prad_ctx* c = g->ctx;
+  const prad_dtype dt = g->dt;
+  GValue& o = V[n.out];
+  const GValue& a = V[n.in[0]];
+  const int64_t cnt = (int64_t)o.rows * o.cols;
+  switch (n.op) {
+    case PRAD_OP_MATMUL:
+      return prad_matmul_forward(c, dt, a.data, V[n.in[1]].data, o.data, a.rows, a.cols, V[n.in[1]].cols, nullptr,
+                                 nullptr, PRAD_ACT_NONE, 0.0);
+    case PRAD_OP_ADD: return prad_add_forward(c, dt, a.data, V[n.in[1]].data, nullptr, o.data, cnt);
+    case PRAD_OP_ADD3: return prad_add_forward(c, dt, a.data, V[n.in[1]].data, V[n.in[2]].data, o.data, cnt);
+    case PRAD_OP_ADD_BROADCAST: return prad_add_broadcast_forward(c, dt, a.data, V[n.in[1]].data, o.data, a.rows, a.cols);
+    case PRAD_OP_HADAMARD: return prad_hadamard_forward(c, dt, a.data, V[n.in[1]].data, o.data, cnt);
+    case PRAD_OP_LEAKY_RELU: case PRAD_OP_SIGMOID: case PRAD_OP_TANH: case PRAD_OP_GELU:
+      return prad_act_forward(c, dt, act_of(n.op), a.data, o.data, cnt, n.scalar);
+    case PRAD_OP_SOFTMAX: return prad_softmax_forward(c, dt, a.data, o.data, a.rows, a.cols);
+    case PRAD_OP_LAYERNORM:
+      if (!n.aux0) {
+        G_TRY(g_alloc(g, (size_t)a.rows, &n.aux0));
+        G_TRY(g_alloc(g, (size_t)a.rows, &n.aux1));
+      }
+      return prad_layernorm_forward(c, dt, a.data, o.data, n.aux0, n.aux1, a.rows, a.cols);
+    case PRAD_OP_SCALE: return prad_scale(c, dt, a.data, o.data, cnt, n.scalar);
+    case PRAD_OP_TRANSPOSE: return prad_transpose(c, dt, a.data, o.data, a.rows, a.cols, 1);
+  }
+  return PRAD_ERR_INVALID;
+}
+
+// gradient buffer of input i of node n (allocated once)
+static prad_status in_grad_buf(prad_graph* g, GNode& n, int i, void** out) {
+  if (!n.in_grad[i]) {
+    const GValue& v = g->values[n.in[i]];
+    G_TRY(g_alloc(g, (size_t)v.rows * v.cols, &n.in_grad[i]));
+  }
+  *out = n.in_grad[i];
+  return PRAD_OK;
+}
+
+// Runs the Backward of one node for upstream gradient d (shape of its output) and hands each
+// input's gradient to that input value.  MatrixAdd-style operations pass d on by reference,
+// exactly as MatrixAddBroadcastingOperation.Backward returns dOutput itself.
+static prad_status node_backward(prad_graph* g, GNode& n, void* d) {
+  auto& V = g->values;
+  prad_ctx* c = g->ctx;
+  const prad_dtype dt = g->dt;
+  const GValue& o = V[n.out];
+  const GValue& a = V[n.in[0]];
+  const int64_t cnt = (int64_t)o.rows * o.cols;
+  void* ga = nullptr;
+  void* gb = nullptr;
+  switch (n.op) {
+    case PRAD_OP_MATMUL: {
+      const GValue& b = V[n.in[1]];
+      G_TRY(in_grad_buf(g, n, 0, &ga));
+      G_TRY(in_grad_buf(g, n, 1, &gb));
+      G_TRY(prad_matmul_backward(c, dt, a.data, b.data, d, ga, gb, a.rows, a.cols, b.cols, 0, 1.0, PRAD_ACT_NONE,
+                                 nullptr, 0.0));
+      V[n.in[0]].contrib.push_back(ga);
+      V[n.in[1]].contrib.push_back(gb);
+      return PRAD_OK;
+    }
+    case PRAD_OP_ADD: case PRAD_OP_ADD3:
+      for (int i : n.in) V[i].contrib.push_back(d);
+      return PRAD_OK;
+    case PRAD_OP_ADD_BROADCAST:
+      G_TRY(in_grad_buf(g, n, 1, &gb));
+      G_TRY(prad_add_broadcast_backward(c, dt, d, gb, o.rows, o.cols, 0));
+      V[n.in[0]].contrib.push_back(d);
+      V[n.in[1]].contrib.push_back(gb);
+      return PRAD_OK;
+    case PRAD_OP_HADAMARD:
+      G_TRY(in_grad_buf(g, n, 0, &ga));
+      G_TRY(in_grad_buf(g, n, 1, &gb));
+      G_TRY(prad_hadamard_backward(c, dt, a.data, V[n.in[1]].data, d, ga, gb, cnt));
+      V[n.in[0]].contrib.push_back(ga);
+      V[n.in[1]].contrib.push_back(gb);
+      return PRAD_OK;
+    case PRAD_OP_LEAKY_RELU: case PRAD_OP_GELU:     // Backward reads the input
+      G_TRY(in_grad_buf(g, n, 0, &ga));
+      G_TRY(prad_act_backward(c, dt, act_of(n.op), a.data, d, ga, cnt, n.scalar));
+      break;
+    case PRAD_OP_SIGMOID: case PRAD_OP_TANH:        // Backward reads the output
+      G_TRY(in_grad_buf(g, n, 0, &ga));
+      G_TRY(prad_act_backward(c, dt, act_of(n.op), o.data, d, ga, cnt, n.scalar));
+      break;
+    case PRAD_OP_SOFTMAX:
+      G_TRY(in_grad_buf(g, n, 0, &ga));
+      G_TRY(prad_softmax_backward(c, dt, o.data, d, ga, o.rows, o.cols));
+      break;
+    case PRAD_OP_LAYERNORM:
+      PRAD_REQUIRE(n.aux0, PRAD_ERR_INVALID, "prad_graph_backward: LayerNorm node has no forward state (run prad_graph_forward)");
+      G_TRY(in_grad_buf(g, n, 0, &ga));
+      G_TRY(prad_layernorm_backward(c, dt, a.data, n.aux0, n.aux1, d, ga, a.rows, a.cols));
+      break;
+    case PRAD_OP_SCALE:
+      G_TRY(in_grad_buf(g, n, 0, &ga));
+      G_TRY(prad_scale(c, dt, d, ga, cnt, n.scalar));
+      break;
+    case PRAD_OP_TRANSPOSE:
+      G_TRY(in_grad_buf(g, n, 0, &ga));
+      G_TRY(prad_transpose(c, dt, d, ga, o.rows, o.cols, 1));
+      break;
+  }
+  V[n.in[0]].contrib.push_back(ga);
+  return PRAD_OK;
+}
+
+}  // namespace prad
+
+extern "C" {
+
+prad_status prad_graph_forward(prad_graph* g) {
+  PRAD_CHECK_GRAPH(g);
+  for (GNode& n : g->nodes) {
+    for (int i : n.in)
+      PRAD_REQUIRE(g->values[i].data, PRAD_ERR_INVALID, "prad_graph_forward: value %d has no data and no producer before its use", i);
+    G_TRY(node_forward(g, n));
+  }
+  return PRAD_OK;
+}
+
+prad_status prad_graph_backward(prad_graph* g, int start_value, const void* d_start) {
+  PRAD_CHECK_GRAPH(g);
+  auto& V = g->values;
+  PRAD_REQUIRE(start_value >= 0 && start_value < (int)V.size() && d_start, PRAD_ERR_INVALID,
+               "prad_graph_backward: bad start value or null gradient");
+  // 1. which nodes lie on a path to the start value, and how many consumers each value has
+  //    there (OperationGraphVisitor's dependency counts)
+  std::vector<char> needed(V.size(), 0);
+  needed[start_value] = 1;
+  for (GValue& v : V) { v.contrib.clear(); v.grad = nullptr; v.consumers = 0; }
+  std::vector<char> live(g->nodes.size(), 0);
+  for (int k = (int)g->nodes.size() - 1; k >= 0; --k) {
+    GNode& n = g->nodes[k];
+    if (!needed[n.out]) continue;
+    live[k] = 1;
+    for (int i : n.in) { needed[i] = 1; V[i].consumers++; }
+  }
+  // 2. one reverse walk.  Nodes were added in forward order, so every consumer of a value
+  //    has delivered its contribution before the value's producer is reached; contributions
+  //    arrive in reverse consumer order and are summed in consumer (registration) order.
+  V[start_value].contrib.push_back(const_cast<void*>(d_start));
+  auto finalize = [&](GValue& v) -> prad_status {
+    if (v.contrib.empty()) return PRAD_OK;
+    if (v.contrib.size() == 1) {
+      v.grad = v.contrib[0];
+    } else {
+      std::reverse(v.contrib.begin(), v.contrib.end());
+      if (!v.sum_buf) G_TRY(g_alloc(g, (size_t)v.rows * v.cols, &v.sum_buf));
+      G_TRY(prad_segmented_sum(g->ctx, g->dt, v.contrib.data(), (int)v.contrib.size(), v.sum_buf,
+                               (int64_t)v.rows * v.cols));
+      v.grad = v.sum_buf;
+    }
+    if (v.grad_dst) G_TRY(prad_accumulate(g->ctx, g->dt, v.grad_dst, v.grad, (int64_t)v.rows * v.cols));
+    return PRAD_OK;
+  };
+  for (int k = (int)g->nodes.size() - 1; k >= 0; --k) {
+    if (!live[k]) continue;
+    GNode& n = g->nodes[k];
+    GValue& o = V[n.out];
+    G_TRY(finalize(o));
+    PRAD_REQUIRE(o.grad, PRAD_ERR_INVALID, "prad_graph_backward: node %d is on the path but received no gradient", k);
+    G_TRY(node_backward(g, n, o.grad));
+  }
+  // 3. leaves (inputs, weights): fan-in sum and `destination += gradient`
+  std::vector<char> produced(V.size(), 0);
+  for (GNode& n : g->nodes) produced[n.out] = 1;
+  for (size_t i = 0; i < V.size(); ++i)
+    if (!produced[i] && (int)i != start_value) G_TRY(finalize(V[i]));
+  return PRAD_OK;
+}
+
+}  // extern "C"
