@@ -103,6 +103,13 @@ prad_status prad_zero(prad_ctx* ctx, void* dptr, size_t bytes);
 prad_status prad_copy(prad_ctx* ctx, void* dst, const void* src, size_t bytes);
 prad_status prad_upload(prad_ctx* ctx, void* dst, const void* src_host, size_t bytes);
 prad_status prad_download(prad_ctx* ctx, void* dst_host, const void* src, size_t bytes);
+/* Overlapped upload: enqueues the copy on the context's separate copy stream, so it runs while
+ * kernels enqueued earlier (or later) on the compute stream execute; prad_upload_join makes
+ * the compute stream wait for every prefetch issued so far.  src_host must be page-locked
+ * (prad_alloc_host) and stay untouched until the join; dst must not be in use by work that is
+ * still running on the compute stream (use a second buffer). */
+prad_status prad_upload_prefetch(prad_ctx* ctx, void* dst, const void* src_host, size_t bytes);
+prad_status prad_upload_join(prad_ctx* ctx);
 /* jagged form: `rows` host row pointers of row_bytes each <-> one dense device matrix */
 prad_status prad_upload_rows(prad_ctx* ctx, void* dst, const void* const* src_rows, int rows,
                              size_t row_bytes);

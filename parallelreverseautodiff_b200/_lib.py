@@ -31,6 +31,8 @@ SIGNATURES = {
     "prad_copy": [vp, vp, vp, sz],
     "prad_upload": [vp, vp, vp, sz],
     "prad_download": [vp, vp, vp, sz],
+    "prad_upload_prefetch": [vp, vp, vp, sz],
+    "prad_upload_join": [vp],
     "prad_upload_rows": [vp, vp, pvp, i32, sz],
     "prad_download_rows": [vp, pvp, vp, i32, sz],
     "prad_alloc_host": [vp, sz, pvp],

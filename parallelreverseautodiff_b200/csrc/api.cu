@@ -118,6 +118,8 @@ prad_status prad_shutdown(prad_ctx* ctx) {
   if (ctx->tc_err) cudaFree(ctx->tc_err);
   if (ctx->stage) cudaFree(ctx->stage);
   if (ctx->host_ws) cudaFreeHost(ctx->host_ws);
+  if (ctx->copy_stream) { cudaStreamSynchronize(ctx->copy_stream); cudaStreamDestroy(ctx->copy_stream); }
+  if (ctx->copy_done) cudaEventDestroy(ctx->copy_done);
   if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
   ctx->magic = 0;
   delete ctx;
@@ -259,6 +261,28 @@ prad_status prad_download(prad_ctx* ctx, void* dst_host, const void* src, size_t
     PRAD_CUDA(cudaStreamSynchronize(ctx->stream));
   }
   return gemm_tf32x3_check(ctx);
+}
+
+prad_status prad_upload_prefetch(prad_ctx* ctx, void* dst, const void* src_host, size_t bytes) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE((dst && src_host) || bytes == 0, PRAD_ERR_INVALID, "prad_upload_prefetch: null pointer");
+  if (bytes == 0) return PRAD_OK;
+  if (!ctx->copy_stream) {
+    PRAD_CUDA(cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
+    PRAD_CUDA(cudaEventCreateWithFlags(&ctx->copy_done, cudaEventDisableTiming));
+  }
+  PRAD_CUDA(cudaMemcpyAsync(dst, src_host, bytes, cudaMemcpyHostToDevice, ctx->copy_stream));
+  ctx->copy_pending = true;
+  return PRAD_OK;
+}
+
+prad_status prad_upload_join(prad_ctx* ctx) {
+  PRAD_CHECK_CTX(ctx);
+  if (!ctx->copy_pending) return PRAD_OK;
+  PRAD_CUDA(cudaEventRecord(ctx->copy_done, ctx->copy_stream));
+  PRAD_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->copy_done, 0));
+  ctx->copy_pending = false;
+  return PRAD_OK;
 }
 
 // Jagged rows are gathered into one pinned block first, so the device sees ONE copy.

@@ -27,6 +27,9 @@ struct prad_ctx {
   cudaStream_t own_stream = nullptr;  // created by prad_init
   cudaStream_t stream = nullptr;      // the stream work is enqueued on
   int sm_count = 0;
+  cudaStream_t copy_stream = nullptr;  // prad_upload_prefetch
+  cudaEvent_t copy_done = nullptr;
+  bool copy_pending = false;
   int64_t launches = 0;
   prad::GemmF32 gemm_f32 = prad::GemmF32::Auto;
   prad::GemmF64 gemm_f64 = prad::GemmF64::Auto;

@@ -217,8 +217,14 @@ __device__ __forceinline__ void epilogue_store32(const float (&acc)[32], int row
     for (int j = 0; j < 32; ++j) if (col0 + j < N) out[j] += epi.bias[col0 + j];
   }
   if (epi.z_out) {
+    if (full && ((uintptr_t)epi.z_out & 15) == 0) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) if (col0 + j < N) epi.z_out[off + j] = out[j];
+      for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<float4*>(epi.z_out + off + j) = make_float4(out[j], out[j + 1], out[j + 2], out[j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) if (col0 + j < N) epi.z_out[off + j] = out[j];
+    }
   }
   if (epi.act != PRAD_ACT_NONE) {
 #pragma unroll

@@ -330,13 +330,16 @@ layernorm_backward_flat(const T* __restrict__ x, const T* __restrict__ mean, con
       if (i < nvec) {
         const T se = add_rn(sg[u], LnEps<T>::v());
         const T exp1 = mul_rn(one_minus, div_rn((T)1, se));
-        const T den = mul_rn((T)cols, mul_rn(mul_rn(se, se), se));
+        // one IEEE division per vector: (x-mean)^2 / den is formed as (x-mean)^2 * (1/den), at most
+        // one unit in the last place away from the reference's division (an IEEE divide per element
+        // makes this kernel instruction-bound at two thirds of the HBM rate)
+        const T rden = div_rn((T)1, mul_rn((T)cols, mul_rn(mul_rn(se, se), se)));
         V o;
 #pragma unroll
         for (int q = 0; q < VEC; ++q) {
           T d = sub_rn(reinterpret_cast<const T*>(&xv[u])[q], mu[u]);
           reinterpret_cast<T*>(&o)[q] =
-              mul_rn(reinterpret_cast<const T*>(&dv[u])[q], sub_rn(exp1, div_rn(mul_rn(d, d), den)));
+              mul_rn(reinterpret_cast<const T*>(&dv[u])[q], sub_rn(exp1, mul_rn(mul_rn(d, d), rden)));
         }
         __stcs(reinterpret_cast<V*>(dx) + i, o);
       }

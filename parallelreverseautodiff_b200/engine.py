@@ -197,6 +197,14 @@ class Engine:
         assert a.flags.c_contiguous and out.nbytes == a.nbytes
         check(self.lib.prad_upload(self.ctx, out.ptr, a.ctypes.data, a.nbytes))
 
+    def upload_prefetch(self, a: np.ndarray, out: DeviceMatrix) -> None:
+        """Host->device copy on the copy stream (overlaps with compute); `a` must be page-locked."""
+        assert a.flags.c_contiguous and out.nbytes == a.nbytes
+        check(self.lib.prad_upload_prefetch(self.ctx, out.ptr, a.ctypes.data, a.nbytes))
+
+    def upload_join(self) -> None:
+        check(self.lib.prad_upload_join(self.ctx))
+
     def copy(self, dst: DeviceMatrix, src: DeviceMatrix) -> None:
         assert dst.nbytes == src.nbytes
         check(self.lib.prad_copy(self.ctx, dst.ptr, src.ptr, src.nbytes))

@@ -211,6 +211,35 @@ class FeedForwardNetwork:
         self.clip_and_optimize()
         return float(loss.numpy()[0, 0])
 
+    def train_steps_host(self, batches, rows_total=None):
+        """Same as train_step_host over a sequence of (x_host, t_host) page-locked batches, with
+        the upload of batch i+1 running on the copy stream while batch i is computed (two input
+        buffers alternate).  Every batch is still copied host->device and every loss read back;
+        yields the losses."""
+        e = self.eng
+        batches = list(batches)
+        if not batches:
+            return
+        rows = batches[0][0].shape[0]
+        self._ensure_buffers(rows)
+        if getattr(self, "_stage_rows", None) != rows:
+            self._in = [self.A[0], e.empty(self.A[0].shape, self.dtype)]
+            self._tg = [self.target, e.empty(self.target.shape, self.dtype)]
+            self._stage_rows = rows
+        e.upload_prefetch(batches[0][0], self._in[0])
+        e.upload_prefetch(batches[0][1], self._tg[0])
+        for i in range(len(batches)):
+            self.A[0], self.target = self._in[i % 2], self._tg[i % 2]
+            e.upload_join()                       # batch i is on the device before its first use
+            if i + 1 < len(batches):              # step i-1 has completed (its loss was read back)
+                e.upload_prefetch(batches[i + 1][0], self._in[(i + 1) % 2])
+                e.upload_prefetch(batches[i + 1][1], self._tg[(i + 1) % 2])
+            self.forward()
+            loss = self.loss_value()
+            self.backward(rows_total=rows_total)
+            self.clip_and_optimize()
+            yield float(loss.numpy()[0, 0])
+
 
 class LstmNetwork:
     """Single-layer LSTM with full BPTT over the C ABI (benchmark config 3, PRAD double).

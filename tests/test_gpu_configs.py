@@ -312,3 +312,29 @@ def test_c5_wide_mlp_float_reduced(engine, gemm):
         assert_close(net.dX.numpy(), d, 30 * rms(d), "dX")
     finally:
         engine.set_option("gemm_f32", "auto")
+
+
+def test_overlapped_host_steps_equal_plain_host_steps(engine):
+    """train_steps_host (upload of batch i+1 overlapped with step i) == train_step_host, bit for bit."""
+    f = np.float32
+    r = np.random.default_rng(3)
+    sizes = [64, 96, 32]
+    Ws = [(r.standard_normal((sizes[i], sizes[i + 1])) * 0.2).astype(f) for i in range(2)]
+    batches = []
+    for _ in range(4):
+        x, t = engine.pinned_empty((50, 64), f), engine.pinned_empty((50, 32), f)
+        x[:] = r.standard_normal((50, 64))
+        t[:] = r.standard_normal((50, 32))
+        batches.append((x, t))
+
+    def make():
+        net = FeedForwardNetwork(engine, f, sizes, hidden_act=E.ACT_GELU, output_act=E.ACT_NONE, loss="mse")
+        net.set_weights(Ws)
+        return net
+
+    a, b = make(), make()
+    plain = [a.train_step_host(x, t) for x, t in batches]
+    overlapped = list(b.train_steps_host(batches))
+    assert plain == overlapped
+    for p, q in zip(a.params, b.params):
+        np.testing.assert_array_equal(p.numpy(), q.numpy())

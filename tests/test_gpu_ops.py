@@ -251,7 +251,9 @@ def test_layernorm(engine, dtype, shape):
     assert_close(y.numpy(), y_ref, 1.0, "layernorm")
     dx = engine.layernorm_backward(engine.upload(x), engine.upload(mean_ref), engine.upload(std_ref),
                                    engine.upload(dy))
-    assert_close(dx.numpy(), dx_ref, rms(dx_ref), "layernorm backward")
+    # the two terms of the derivative cancel (completely for 2 columns), so the error scale is
+    # the size of the terms, dy/(sigma+eps), not of the result
+    assert_close(dx.numpy(), dx_ref, rms(dy / (std_ref[:, None] + 1e-9)), "layernorm backward")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
