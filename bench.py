@@ -40,6 +40,9 @@ def parse():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--workload", default="c5", choices=["c1", "c2", "c3", "c4", "c5"],
+                    help="benchmark configuration (c5, the large data-parallel MLP, is the headline)")
+    ap.add_argument("--images", type=int, default=64, help="c4: images per batch")
     ap.add_argument("--batch", type=int, default=GLOBAL_BATCH, help="global batch rows")
     ap.add_argument("--width", type=int, default=WIDTH)
     ap.add_argument("--layers", type=int, default=LAYERS)
@@ -331,17 +334,157 @@ def run_native(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------ small configurations
+def cpu_small(workload, inp):
+    """CPU restatement of one whole forward + backward of the configuration (forward needed to
+    produce what the backward reads; only the backward part is timed where separable)."""
+    import oracle as O
+    from oracle import configs as OC
+
+    t0 = time.perf_counter()
+    if workload == "c1":
+        pre = O.matmul_forward(inp["A"], inp["B"])
+        t0 = time.perf_counter()
+        dPre = O.leaky_relu_backward(pre, inp["dOut"], 0.01)
+        O.matmul_backward(inp["A"], inp["B"], dPre)
+        return time.perf_counter() - t0, "backward only, full size", 1.0
+    if workload == "c2":
+        OC.mlp_oracle(inp["x"], inp["onehot"], inp["Ws"], inp["bs"], np.float32(0.01))
+        return time.perf_counter() - t0, "forward + backward, full size (backward is 2/3 of the flops)", 2.0 / 3.0
+    if workload == "c3":
+        OC.lstm_oracle(inp["x"], inp["y"], inp["W"], inp["U"], inp["b"])
+        return time.perf_counter() - t0, "forward + backward, full size (backward is 2/3 of the flops)", 2.0 / 3.0
+    imgs = min(2, inp["images"])
+    T = imgs * 3136
+    OC.swin_oracle(inp["x"][:T], inp["d_out"][:T], inp["p"], inp["heads"], inp["ws"])
+    scale = inp["images"] / imgs
+    return (time.perf_counter() - t0) * scale, f"forward + backward on {imgs} images, scaled linearly to {inp['images']}", 2.0 / 3.0
+
+
+def run_small(args, rank, world, local_rank):
+    """C1-C4: too small to shard, so N GPUs run N independent replicas (weak scaling)."""
+    import torch
+
+    from parallelreverseautodiff_b200 import engine as E
+    from parallelreverseautodiff_b200 import workloads as WL
+
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    eng = E.Engine(local_rank)
+    make = {"c1": WL.make_c1, "c2": WL.make_c2, "c3": WL.make_c3, "c4": lambda: WL.make_c4(images=args.images)}[args.workload]
+    inp = make()
+    runner = {"c1": WL.C1Runner, "c2": WL.C2Runner, "c3": WL.C3Runner, "c4": WL.C4Runner}[args.workload](eng, inp)
+    stream = torch.cuda.ExternalStream(eng.stream(), device=torch.device("cuda", local_rank))
+    flush = eng.empty((64 * 1024 * 1024,), np.float32)     # 256 MiB > L2: written between timed steps
+
+    def barrier():
+        eng.sync()
+        torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
+
+    for _ in range(max(args.warmup, 3)):
+        runner.backward()
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    n0 = eng.launch_count()
+    total_ms = 0.0
+    for _ in range(args.steps):
+        eng.zero_(flush)                                   # L2 flush, outside the timed bracket
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        runner.backward()
+        e1.record(stream)
+        eng.sync()
+        total_ms += e0.elapsed_time(e1)
+    launches = eng.launch_count() - n0
+    barrier()
+    clocks = sampler.stop()
+    ms = total_ms / args.steps
+    if dist:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    # end to end for C1: the host-buffer entry point (numpy in, numpy out)
+    e2e = None
+    if args.workload == "c1":
+        pre = runner.pre.numpy()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            eng.matmul_act_backward_host(inp["A"], inp["B"], inp["dOut"], E.ACT_LEAKY_RELU, pre, 0.01)
+        dt = (time.perf_counter() - t0) / args.steps
+        nbytes = sum(inp[k].nbytes for k in ("A", "B", "dOut")) + pre.nbytes
+        e2e = {"value": world * runner.samples / dt, "unit": UNIT, "h2d_bytes_per_step": int(nbytes),
+               "d2h_bytes_per_step": int(inp["A"].nbytes + inp["B"].nbytes + pre.nbytes), "ms_per_step": dt * 1e3,
+               "note": "prad_matmul_act_backward_host, pageable host arrays, wall clock"}
+    if rank == 0:
+        cpu = None
+        if not args.no_cpu_baseline:
+            import oracle as O
+
+            secs, what, bwd_frac = cpu_small(args.workload, inp)
+            cpu = {"value": runner.samples / (secs * bwd_frac), "unit": UNIT, "cores": O.num_threads(), "kind": "port",
+                   "sample": what + "; C++ restatement of the C# loops with OpenMP, not the .NET runtime"}
+        peaks = measured_peaks()
+        tflops = runner.flops / (ms * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": world * runner.samples / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": runner.dtype, "data": "synthetic",
+            "config": {"workload": runner.name, "parallelism": f"replicas x{world}",
+                       "l2": "256 MiB buffer written between timed steps (L2 flush)"},
+            "tflops": tflops * world,
+            "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["tensor_tflops"], "unit": "TFLOP/s",
+                         "frac": tflops / peaks["tensor_tflops"], "traffic": None,
+                         "kernel": "whole backward step (launch-latency-bound at this size)",
+                         "peak_source": peaks["source"] + " dense bf16, sustained"},
+            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    eng.close()
+    if dist:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
+        if args.workload != "c5":
+            if rank == 0:
+                from parallelreverseautodiff_b200 import workloads as WL
+                import oracle as O
+
+                make = {"c1": WL.make_c1, "c2": WL.make_c2, "c3": WL.make_c3,
+                        "c4": lambda: WL.make_c4(images=args.images)}[args.workload]
+                inp = make()
+                samples = {"c1": 512, "c2": 256, "c3": 32, "c4": args.images}[args.workload]
+                secs, what, frac = cpu_small(args.workload, inp)
+                v = samples / (secs * frac)
+                print(json.dumps({"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus,
+                                  "steps": 1, "warmup": 0, "ms_per_step": secs * frac * 1e3, "higher_is_better": True,
+                                  "scaling": "weak", "vs_baseline": None, "data": "synthetic",
+                                  "config": {"workload": args.workload, "parallelism": "cpu"},
+                                  "cpu_baseline": {"value": v, "unit": UNIT, "cores": O.num_threads(), "kind": "port", "sample": what},
+                                  "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                                  "gpu_launches": 0}), flush=True)
+            return
         run_reference(args, rank)
         return
     if world != args.gpus:
         if world == 1 and args.gpus > 1:
             raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
+    if args.workload != "c5":
+        run_small(args, rank, world, local_rank)
+        return
     run_native(args, rank, world, local_rank)
 
 

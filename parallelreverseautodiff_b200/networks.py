@@ -284,7 +284,7 @@ class LstmNetwork:
         self.IG = z(TB, n_hidden)                                 # i (.) g
         self.dpre = {g: z(TB, n_hidden) for g in self.GATES}
         self.dX = z(TB, n_in)
-        self._tmp = [z(batch, n_hidden) for _ in range(12)]
+        self._tmp = [z(batch, n_hidden) for _ in range(18)]
 
     def set_parameters(self, W, U, b):
         for g in self.GATES:
@@ -355,9 +355,11 @@ class LstmNetwork:
                 e.segmented_sum([dc_a, dc_next], out=dc)
             # c = f*c_prev + i*g : MatrixAdd copies dc to both products
             i_, g_, f_ = (self._step(self.gate[k], t) for k in ("i", "g", "f"))
-            d_i, d_g = e.hadamard_backward(i_, g_, dc)
+            d_i, d_g = e.hadamard_backward(i_, g_, dc, out=(tmp[12], tmp[13]))
             if t > 0:
-                d_f, dc_next = e.hadamard_backward(f_, self._step(self.C, t - 1), dc)
+                # dc_next alternates between two buffers: the one read as dc_next above stays intact
+                d_f, dc_next = e.hadamard_backward(f_, self._step(self.C, t - 1), dc,
+                                                   out=(tmp[14], tmp[15 + (t & 1)]))
             else:
                 d_f = tmp[7]
                 e.zero_(d_f)    # c_{-1} = 0 -> dc (.) 0
@@ -408,6 +410,15 @@ class SwinBlock:
                   "W1": z(d, h), "b1": z(1, h), "W2": z(h, d), "b2": z(1, d)}
         self.g = {k: z(*v.shape) for k, v in self.p.items()}
         self.scale = 1.0 / float(np.sqrt(self.hd))
+        self._cache = {}
+
+    def _buf(self, name, shape):
+        """Device buffer reused across calls (no allocation in the steady state)."""
+        b = self._cache.get(name)
+        if b is None or b.shape != tuple(shape):
+            b = self.eng.empty(shape, self.dtype)
+            self._cache[name] = b
+        return b
 
     def set_parameters(self, params):
         for k, v in params.items():
@@ -451,23 +462,25 @@ class SwinBlock:
         T = d_out.shape[0]
         # out = r1 + m2 : both receive d_out (MatrixAddOperation.Backward)
         e.add_broadcast_backward(d_out, dbias=g["b2"])
-        d_z1, _ = e.matmul_backward(self.a1, p["W2"], d_out, dB=g["W2"], act_below=E.ACT_GELU, saved_below=self.z1)
+        B_ = self._buf
+        d_z1, _ = e.matmul_backward(self.a1, p["W2"], d_out, dA=B_("d_z1", (T, self.hidden)), dB=g["W2"],
+                                    act_below=E.ACT_GELU, saved_below=self.z1)
         e.add_broadcast_backward(d_z1, dbias=g["b1"])
-        d_ln2, _ = e.matmul_backward(self.ln2, p["W1"], d_z1, dB=g["W1"])
-        d_r1_b = e.layernorm_backward(self.r1, self.mu2, self.sd2, d_ln2)
-        d_r1 = e.segmented_sum([d_out, d_r1_b])                    # fan-in at r1: residual + LN2 branch
+        d_ln2, _ = e.matmul_backward(self.ln2, p["W1"], d_z1, dA=B_("d_ln2", (T, d)), dB=g["W1"])
+        d_r1_b = e.layernorm_backward(self.r1, self.mu2, self.sd2, d_ln2, out=B_("d_r1_b", (T, d)))
+        d_r1 = e.segmented_sum([d_out, d_r1_b], out=B_("d_r1", (T, d)))   # fan-in at r1: residual + LN2 branch
         # r1 = x + proj
         e.add_broadcast_backward(d_r1, dbias=g["bproj"])
-        d_attn, _ = e.matmul_backward(self.attn, p["Wproj"], d_r1, dB=g["Wproj"])
-        d_qkv = e.zeros((T, 3 * d), self.dtype)
-        dP = e.empty(self.P.shape, self.dtype)
+        d_attn, _ = e.matmul_backward(self.attn, p["Wproj"], d_r1, dA=B_("d_attn", (T, d)), dB=g["Wproj"])
+        d_qkv = B_("d_qkv", (T, 3 * d))     # every element is written by the three per-head products below
+        dP = B_("dP", self.P.shape)
         for h in range(H):
             # O_h = P_h V_h :  dP_h = dO_h V_h^T ,  dV_h = P_h^T dO_h
             self._attn_gemm(d_attn, h * hd, d, ws * d, self.qkv, 2 * d + h * hd, 3 * d, ws * 3 * d,
                             dP, h * ws * ws, ws, H * ws * ws, ws, ws, hd, transB=True, batch=nw)
             self._attn_gemm(self.P, h * ws * ws, ws, H * ws * ws, d_attn, h * hd, d, ws * d,
                             d_qkv, 2 * d + h * hd, 3 * d, ws * 3 * d, ws, hd, ws, transA=True, batch=nw)
-        dS = e.softmax_backward(self.P, dP)
+        dS = e.softmax_backward(self.P, dP, out=B_("dS", self.P.shape))
         for h in range(H):
             # S_h = scale * Q_h K_h^T :  dQ_h = scale * dS_h K_h ,  dK_h = scale * dS_h^T Q_h
             self._attn_gemm(dS, h * ws * ws, ws, H * ws * ws, self.qkv, d + h * hd, 3 * d, ws * 3 * d,
@@ -475,8 +488,8 @@ class SwinBlock:
             self._attn_gemm(dS, h * ws * ws, ws, H * ws * ws, self.qkv, h * hd, 3 * d, ws * 3 * d,
                             d_qkv, d + h * hd, 3 * d, ws * 3 * d, ws, hd, ws, transA=True, alpha=self.scale, batch=nw)
         e.add_broadcast_backward(d_qkv, dbias=g["bqkv"])
-        d_ln1, _ = e.matmul_backward(self.ln1, p["Wqkv"], d_qkv, dB=g["Wqkv"])
-        d_x_b = e.layernorm_backward(self.x, self.mu1, self.sd1, d_ln1)
-        self.d_x = e.segmented_sum([d_r1, d_x_b])                  # fan-in at x: residual + LN1 branch
+        d_ln1, _ = e.matmul_backward(self.ln1, p["Wqkv"], d_qkv, dA=B_("d_ln1", (T, d)), dB=g["Wqkv"])
+        d_x_b = e.layernorm_backward(self.x, self.mu1, self.sd1, d_ln1, out=B_("d_x_b", (T, d)))
+        self.d_x = e.segmented_sum([d_r1, d_x_b], out=B_("d_x", (T, d)))  # fan-in at x: residual + LN1 branch
         self.d_qkv, self.dS, self.dP, self.d_attn = d_qkv, dS, dP, d_attn
         return self.d_x
