@@ -691,8 +691,8 @@ static prad_status launch_tf32x3(prad_ctx* ctx, const SplitOperand& a, const Spl
       return (double)ctas / (double)(ceil_div(ctas, ctx->sm_count) * ctx->sm_count);
     };
     double best = eff(1) * 1.08;   // a split must pay for its extra pass
-    for (int sp = 2; sp <= 4; ++sp)
-      if (kp / sp >= 2048 && eff(sp) > best) { best = eff(sp); splits = sp; }
+    for (int sp = 2; sp <= 64; ++sp)
+      if (kp / sp >= 1024 && eff(sp) > best * 1.02) { best = eff(sp); splits = sp; }
   }
   if (splits == 1) {
     gemm_tf32x3_kernel<CFG><<<grid, THREADS, CFG::SMEM_BYTES, ctx->stream>>>(
@@ -747,7 +747,9 @@ prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, do
   // shapes this kernel is meant for; everything else stays on the SIMT variant
   const bool forced = ctx->gemm_f32 == GemmF32::Tf32x3 || ctx->gemm_f32 == GemmF32::Tf32B16 ||
                       ctx->gemm_f32 == GemmF32::Bf16x3;
-  const bool big = (int64_t)M * N * K >= ((int64_t)1 << 27) && M >= BM && N >= 128 && K >= KPAD;
+  // large products; a short M or N only wastes part of the 128 x 256 tile (TMA zero-fills it),
+  // which still beats ten CTAs walking a 200 000-long k range one after the other
+  const bool big = (int64_t)M * N * K >= ((int64_t)1 << 27) && M >= 64 && N >= 64 && K >= KPAD;
   if (batch != 1 || K < 1 || !(big || forced) || encode_fn() == nullptr) {
     if (probe_only || !forced) return PRAD_ERR_UNSUPPORTED;
     set_error("gemm tf32x3: unsupported shape (batch %d) or driver without cuTensorMapEncodeTiled", batch);
