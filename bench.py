@@ -47,7 +47,7 @@ def parse():
     ap.add_argument("--width", type=int, default=WIDTH)
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--clip", default="reference", choices=["reference", "global_norm", "none"])
-    ap.add_argument("--gemm", default="auto", choices=["auto", "simt", "simt_fma", "tf32x3", "tf32b16", "bf16x3"])
+    ap.add_argument("--gemm", default="auto", choices=["auto", "simt", "simt_fma", "tf32x3", "tf32b16", "bf16x3", "fp16x3"])
     ap.add_argument("--tc-pipeline", default=None, choices=[None, "16x4", "32x2", "8x8"])
     ap.add_argument("--lr", type=float, default=1e-5,
                     help="Adam learning rate (1e-3, the reference default, makes this 8-layer GELU net "

@@ -136,7 +136,8 @@ prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value) {
     else if (!strcmp(value, "tf32x3")) ctx->gemm_f32 = GemmF32::Tf32x3;
     else if (!strcmp(value, "tf32b16")) ctx->gemm_f32 = GemmF32::Tf32B16;
     else if (!strcmp(value, "bf16x3")) ctx->gemm_f32 = GemmF32::Bf16x3;
-    else { set_error("prad_set_option: gemm_f32 must be auto|simt|simt_fma|tf32x3|tf32b16|bf16x3, got '%s'", value); return PRAD_ERR_INVALID; }
+    else if (!strcmp(value, "fp16x3")) ctx->gemm_f32 = GemmF32::Fp16x3;
+    else { set_error("prad_set_option: gemm_f32 must be auto|simt|simt_fma|tf32x3|tf32b16|bf16x3|fp16x3, got '%s'", value); return PRAD_ERR_INVALID; }
     return PRAD_OK;
   }
   if (!strcmp(key, "gemm_f64")) {
@@ -145,6 +146,18 @@ prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value) {
     else if (!strcmp(value, "simt_fma")) ctx->gemm_f64 = GemmF64::SimtFma;
     else if (!strcmp(value, "dmma")) ctx->gemm_f64 = GemmF64::Dmma;
     else { set_error("prad_set_option: gemm_f64 must be auto|simt|simt_fma|dmma, got '%s'", value); return PRAD_ERR_INVALID; }
+    return PRAD_OK;
+  }
+  if (!strcmp(key, "tc_auto")) {   // which split scheme gemm_f32=auto uses for large products
+    if (!strcmp(value, "tf32x3")) ctx->tc_auto_mode = 0;
+    else if (!strcmp(value, "tf32b16")) ctx->tc_auto_mode = 1;
+    else if (!strcmp(value, "bf16x3")) ctx->tc_auto_mode = 2;
+    else if (!strcmp(value, "fp16x3")) ctx->tc_auto_mode = 3;
+    else { set_error("prad_set_option: tc_auto must be tf32x3|tf32b16|bf16x3|fp16x3, got '%s'", value); return PRAD_ERR_INVALID; }
+    return PRAD_OK;
+  }
+  if (!strcmp(key, "tc_persistent")) {
+    ctx->tc_persistent = strcmp(value, "off") != 0 && strcmp(value, "0") != 0;
     return PRAD_OK;
   }
   if (!strcmp(key, "tc_split_k")) {

@@ -15,7 +15,7 @@ namespace prad {
 
 void set_error(const char* fmt, ...);
 
-enum class GemmF32 { Auto, Simt, SimtFma, Tf32x3, Tf32B16, Bf16x3 };
+enum class GemmF32 { Auto, Simt, SimtFma, Tf32x3, Tf32B16, Bf16x3, Fp16x3 };
 enum class GemmF64 { Auto, Simt, SimtFma, Dmma };
 
 struct DpState;  // data-parallel state (dp.cu)
@@ -47,7 +47,8 @@ struct prad_ctx {
   bool tc_pending_check = false;
   int tc_variant = 0;  // pipeline shape of the tensor-core GEMM (option "tc_pipeline")
   bool tc_split_k = true;  // option "tc_split_k": cut k across CTAs when the tile count wastes SMs
-  int tc_auto_mode = 1;  // split scheme "auto" picks: 0 = 3xTF32, 1 = TF32 + BF16 corrections
+  bool tc_persistent = true;  // option "tc_persistent": TF32+BF16 products run on the persistent kernel
+  int tc_auto_mode = 3;  // split scheme "auto" picks: 0 = 3xTF32, 1 = TF32 + BF16 corrections, 2 = BF16 x 6, 3 = FP16 x 3
   uint32_t magic = 0x50524144u;  // "PRAD"
 };
 

@@ -26,6 +26,7 @@
 // memory and returns; the host then reports PRAD_ERR_TIMEOUT.
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include <mutex>
 
@@ -172,6 +173,10 @@ __host__ __device__ constexpr uint32_t idesc_tf32() {
 __host__ __device__ constexpr uint32_t idesc_bf16() {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
+// Instruction descriptor: D = F32, A = B = FP16, both K-major, M = 128, N = 256 (kind::f16).
+__host__ __device__ constexpr uint32_t idesc_fp16() {
+  return (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
 __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
@@ -188,7 +193,14 @@ struct Epi {
   const float* saved;
   float act_alpha;
   float alpha, beta;
+  // operands scaled by powers of two (FP16 split): the product of row i and column j is
+  // multiplied by 2^(row_exp[i] + col_exp[j]) first; null when the operands are unscaled
+  const int* row_exp;
+  const int* col_exp;
 };
+
+// 2^e as a float, |e| <= 126
+__device__ __forceinline__ float pow2i(int e) { return __int_as_float((e + 127) << 23); }
 
 // One epilogue thread's share of the finished tile: 32 consecutive columns of one row.
 __device__ __forceinline__ void epilogue_store32(const float (&acc)[32], int row, int col0, int M, int N,
@@ -197,8 +209,18 @@ __device__ __forceinline__ void epilogue_store32(const float (&acc)[32], int row
   const int64_t off = (int64_t)row * ldc + col0;
   const bool full = vecC && (col0 + 32 <= N);
   float out[32];
+  if (epi.row_exp) {   // exact: two multiplications by powers of two, each half of the exponent
+    const int er = epi.row_exp[row];
 #pragma unroll
-  for (int j = 0; j < 32; ++j) out[j] = epi.alpha * acc[j];
+    for (int j = 0; j < 32; ++j) {
+      const int e = er + (col0 + j < N ? epi.col_exp[col0 + j] : 0);
+      const int h = e >> 1;
+      out[j] = epi.alpha * ((acc[j] * pow2i(h)) * pow2i(e - h));
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) out[j] = epi.alpha * acc[j];
+  }
   if (epi.beta != 0.f) {
     if (full) {
 #pragma unroll
@@ -478,6 +500,244 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
   }
 }
 
+// ---- persistent variant of MODE 1 (TF32 product + two BF16 corrections) -----------------
+// Same arithmetic and tile as gemm_tf32x3_kernel<Cfg<32,2,1>>, organised differently:
+//   * one CTA per SM walks output tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (n-tile
+//     fastest, then m-tile, then k-slice), so the epilogue warps store tile i while the
+//     producer and MMA warps already work on tile i+1 (the two TMEM accumulators decouple
+//     them by two 256-k chunks);
+//   * the operand ring holds four units of 48 KB instead of two stages of 96 KB: a k-block
+//     of 32 arrives as unit H (the four BF16 tiles a_hb, a_lb, b_hb, b_lb) and unit F (the
+//     two FP32 tiles a_hi, b_hi), each with its own full/empty barrier pair, so a unit is
+//     refilled as soon as the two or four MMAs that read it retire and three loads are in
+//     flight while one is multiplied.
+namespace p1 {
+constexpr int BK = 32;
+constexpr int UNITS = 4;
+constexpr int UNIT_BYTES = 48 * 1024;
+constexpr int CHUNK_KB = CHUNK_K / BK;
+constexpr int SMEM_BYTES = UNITS * UNIT_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+static_assert(SMEM_BYTES <= 227 * 1024, "unit ring does not fit in shared memory");
+}  // namespace p1
+
+struct TileSched {
+  int tiles_m, tiles_n, splits;   // tile t -> (t % tiles_n, (t / tiles_n) % tiles_m, t / (tiles_n * tiles_m))
+  int kb_per_split, total_kb;     // k-blocks per slice and in all
+  int64_t split_stride;           // elements between the partial products of consecutive slices
+};
+
+template <int PMODE>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_xb,
+                               const __grid_constant__ CUtensorMap map_a_lb, const __grid_constant__ CUtensorMap map_b_hi,
+                               const __grid_constant__ CUtensorMap map_b_xb, const __grid_constant__ CUtensorMap map_b_lb,
+                               int M, int N, float* __restrict__ C, int64_t ldc, bool vecC, Epi epi,
+                               int* __restrict__ err_flag, TileSched ts) {
+  using namespace p1;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = base + UNITS * UNIT_BYTES;
+  auto full_bar = [&](uint32_t s) { return bars + 8u * s; };
+  auto empty_bar = [&](uint32_t s) { return bars + 8u * (UNITS + s); };
+  auto acc_full = [&](uint32_t b) { return bars + 8u * (2 * UNITS + b); };
+  auto acc_empty = [&](uint32_t b) { return bars + 8u * (2 * UNITS + 2 + b); };
+  const uint32_t tmem_slot = bars + 8u * (2 * UNITS + 4);
+  uint8_t* generic_base = smem_raw + (base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(generic_base + UNITS * UNIT_BYTES + 8 * (2 * UNITS + 4));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_tiles = ts.tiles_m * ts.tiles_n * ts.splits;
+
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) s_abort = *((volatile int*)err_flag);
+  __syncthreads();
+  if (s_abort != 0) return;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < UNITS; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), EPI_WARPS); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  // tile t of this CTA: origin of the output tile and its k range
+  auto tile_of = [&](int t, int& m0, int& n0, int& z, int& kb0, int& num_kb) {
+    n0 = (t % ts.tiles_n) * BN;
+    m0 = ((t / ts.tiles_n) % ts.tiles_m) * BM;
+    z = t / (ts.tiles_n * ts.tiles_m);
+    kb0 = z * ts.kb_per_split;
+    num_kb = min(ts.total_kb - kb0, ts.kb_per_split);
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t g = 0;   // units issued so far, over all tiles of this CTA
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int m0, n0, z, kb0, num_kb;
+        tile_of(t, m0, n0, z, kb0, num_kb);
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+          const int x = (kb0 + kb) * BK;
+#pragma unroll
+          for (int half = 0; half < (PMODE == 1 ? 2 : 1); ++half, ++g) {
+            const uint32_t slot = g & (UNITS - 1), round = g / UNITS;
+            if (round > 0 && !mbar_wait(empty_bar(slot), (round - 1) & 1, err_flag, 1)) { ok = false; break; }
+            const uint32_t st = base + slot * UNIT_BYTES;
+            mbar_expect_tx(full_bar(slot), UNIT_BYTES);
+            if (half == 0) {   // unit H: a_hb 8 KB | a_lb 8 KB | b_hb 16 KB | b_lb 16 KB  (PMODE 3: a_h0 a_h1 b_h0 b_h1)
+              tma_load_2d(st, &map_a_xb, full_bar(slot), x, m0);
+              tma_load_2d(st + 8 * 1024, &map_a_lb, full_bar(slot), x, m0);
+              tma_load_2d(st + 16 * 1024, &map_b_xb, full_bar(slot), x, n0);
+              tma_load_2d(st + 32 * 1024, &map_b_lb, full_bar(slot), x, n0);
+            } else {           // unit F: a_hi 16 KB | b_hi 32 KB
+              tma_load_2d(st, &map_a_hi, full_bar(slot), x, m0);
+              tma_load_2d(st + 16 * 1024, &map_b_hi, full_bar(slot), x, n0);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_tf32(), idesc_h = idesc_bf16();
+      uint32_t g = 0, gc = 0;   // units consumed, chunks started
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int m0, n0, z, kb0, num_kb;
+        tile_of(t, m0, n0, z, kb0, num_kb);
+        const int num_chunks = (num_kb + CHUNK_KB - 1) / CHUNK_KB;
+        for (int ch = 0; ch < num_chunks && ok; ++ch, ++gc) {
+          const uint32_t buf = gc & 1, use = gc >> 1;
+          if (use > 0) {
+            ok = mbar_wait(acc_empty(buf), (use - 1) & 1, err_flag, 4);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          const uint32_t d_tmem = tmem_base + buf * (uint32_t)BN;
+          const int kb_end = min(num_kb, (ch + 1) * CHUNK_KB);
+          for (int kb = ch * CHUNK_KB; kb < kb_end && ok; ++kb) {
+            if (PMODE == 3) {   // one unit: a_h0 | a_h1 | b_h0 | b_h1, three FP16 products, smallest first
+              constexpr uint32_t idesc_q = idesc_fp16();
+              const uint32_t slot = g & (UNITS - 1);
+              ok = mbar_wait(full_bar(slot), (g / UNITS) & 1, err_flag, 2);
+              if (!ok) break;
+              tc_fence_after();
+              const uint32_t st = base + slot * UNIT_BYTES;
+              const uint64_t a_0 = kmajor_desc<64>(st), a_1 = kmajor_desc<64>(st + 8 * 1024);
+              const uint64_t b_0 = kmajor_desc<64>(st + 16 * 1024), b_1 = kmajor_desc<64>(st + 32 * 1024);
+#pragma unroll
+              for (int k = 0; k < BK / 16; ++k) {
+                const uint64_t adv = (uint64_t)((k * 16 * 2) >> 4);
+                umma_f16(d_tmem, a_1 + adv, b_0 + adv, idesc_q, !(kb == ch * CHUNK_KB && k == 0));
+                umma_f16(d_tmem, a_0 + adv, b_1 + adv, idesc_q, 1);
+                umma_f16(d_tmem, a_0 + adv, b_0 + adv, idesc_q, 1);
+              }
+              umma_commit(empty_bar(slot));
+              ++g;
+              continue;
+            }
+            {   // unit H: the two BF16 correction products, two 16-wide k-slices
+              const uint32_t slot = g & (UNITS - 1);
+              ok = mbar_wait(full_bar(slot), (g / UNITS) & 1, err_flag, 2);
+              if (!ok) break;
+              tc_fence_after();
+              const uint32_t st = base + slot * UNIT_BYTES;
+              const uint64_t a_hb = kmajor_desc<64>(st), a_lb = kmajor_desc<64>(st + 8 * 1024);
+              const uint64_t b_hb = kmajor_desc<64>(st + 16 * 1024), b_lb = kmajor_desc<64>(st + 32 * 1024);
+#pragma unroll
+              for (int k = 0; k < BK / 16; ++k) {
+                const uint64_t adv = (uint64_t)((k * 16 * 2) >> 4);
+                umma_f16(d_tmem, a_lb + adv, b_hb + adv, idesc_h, !(kb == ch * CHUNK_KB && k == 0));
+                umma_f16(d_tmem, a_hb + adv, b_lb + adv, idesc_h, 1);
+              }
+              umma_commit(empty_bar(slot));
+              ++g;
+            }
+            {   // unit F: the TF32 product, four 8-wide k-slices
+              const uint32_t slot = g & (UNITS - 1);
+              ok = mbar_wait(full_bar(slot), (g / UNITS) & 1, err_flag, 2);
+              if (!ok) break;
+              tc_fence_after();
+              const uint32_t st = base + slot * UNIT_BYTES;
+              const uint64_t a_hi = kmajor_desc<128>(st), b_hi = kmajor_desc<128>(st + 16 * 1024);
+#pragma unroll
+              for (int k = 0; k < BK / UMMA_K; ++k) {
+                const uint64_t adv = (uint64_t)((k * UMMA_K * 4) >> 4);
+                umma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1);
+              }
+              umma_commit(empty_bar(slot));
+              ++g;
+            }
+          }
+          umma_commit(acc_full(buf));    // chunk complete (arrives even after a give-up)
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..9)
+    const int sub = warp & 3;                 // TMEM sub-partition this warp may read
+    const int half = (warp - 2) >> 2;         // which 128 columns of the tile
+    uint32_t gc = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int m0, n0, z, kb0, num_kb;
+      tile_of(t, m0, n0, z, kb0, num_kb);
+      const int num_chunks = (num_kb + CHUNK_KB - 1) / CHUNK_KB;
+      float sum[4][32];
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+#pragma unroll
+        for (int j = 0; j < 32; ++j) sum[g][j] = 0.f;
+      for (int ch = 0; ch < num_chunks; ++ch, ++gc) {
+        const uint32_t buf = gc & 1;
+        ok = mbar_wait(acc_full(buf), (gc >> 1) & 1, err_flag, 3);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + buf * (uint32_t)BN + (uint32_t)(half * 128);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint32_t v[32];
+          tmem_ld32(taddr + (uint32_t)(g * 32), v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) sum[g][j] = __fadd_rn(sum[g][j], __uint_as_float(v[j]));
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty(buf));
+      }
+      if (!ok || *((volatile int*)err_flag) != 0) { ok = false; break; }
+      float* Ct = C + (int64_t)z * ts.split_stride;
+      const int row = m0 + sub * 32 + lane;
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+        epilogue_store32(sum[g], row, n0 + half * 128 + g * 32, M, N, Ct, ldc, vecC, epi);
+    }
+  }
+
+  // drain, as in the one-tile kernel
+  tc_fence_before();
+  __syncthreads();
+  if (*((volatile int*)err_flag) != 0) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 // ---- operand preparation: hi/lo split (optionally transposing) into K-major scratch -----
 __device__ __forceinline__ float to_tf32(float x) {
   uint32_t r;
@@ -580,6 +840,126 @@ split_transpose_kernel(const float* __restrict__ src, int64_t src_ld, float* __r
   }
 }
 
+// ---- MODE 3 operand preparation: per-row power-of-two scaling and a two-piece FP16 split --
+// Every row of a K-major operand (an output row of A, an output column of B) is multiplied by
+// 2^s with s chosen so that its largest magnitude lands in [2^14, 2^15), then written as
+// h0 = fp16(x 2^s) and h1 = fp16(x 2^s - h0): 22 significant bits, the same as the TF32
+// pair.  FP16's narrow exponent is harmless after the scaling: what underflows is below
+// 2^-39 of the row's maximum.  exps[row] = -s is applied to the products in the epilogue.
+__device__ __forceinline__ int shift_of(uint32_t absbits) {
+  const int e = (int)((absbits >> 23) & 0xffu);
+  if (e == 0 || e == 255) return 0;            // all zero / denormal, or Inf / NaN present: unscaled
+  const int s = 14 - (e - 127);
+  return s < -100 ? -100 : (s > 100 ? 100 : s);
+}
+__device__ __forceinline__ void fp16_pieces(float xs, __half& p0, __half& p1) {
+  p0 = __float2half_rn(xs);
+  p1 = __float2half_rn(xs - __half2float(p0));   // the difference is exact in FP32
+}
+// src is rows x cols with k contiguous; one warp per row, two passes (the second hits L1/L2)
+__global__ void __launch_bounds__(256)
+split16_rows_kernel(const float* __restrict__ src, int64_t src_ld, __half* __restrict__ h0, __half* __restrict__ h1,
+                    int* __restrict__ exps, int64_t dst_ld, int rows, int cols) {
+  const int lane = threadIdx.x & 31;
+  const bool vec = ((src_ld & 3) == 0) && (((uintptr_t)src & 15) == 0);
+  for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * 8) {
+    const float* s = src + row * src_ld;
+    uint32_t mx = 0;
+    if (vec) {
+      for (int c = lane * 4; c + 4 <= cols; c += 128) {
+        const float4 v = *reinterpret_cast<const float4*>(s + c);
+        mx = max(max(mx, __float_as_uint(fabsf(v.x))), __float_as_uint(fabsf(v.y)));
+        mx = max(max(mx, __float_as_uint(fabsf(v.z))), __float_as_uint(fabsf(v.w)));
+      }
+      for (int c = (cols & ~3) + lane; c < cols; c += 32) mx = max(mx, __float_as_uint(fabsf(s[c])));
+    } else {
+      for (int c = lane; c < cols; c += 32) mx = max(mx, __float_as_uint(fabsf(s[c])));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const int sh = shift_of(mx);
+    const float scale = pow2i(sh);
+    if (lane == 0) exps[row] = -sh;
+    __half* d0 = h0 + row * dst_ld;
+    __half* d1 = h1 + row * dst_ld;
+    for (int c = lane * 4; c < dst_ld; c += 128) {
+      float x[4];
+      if (vec && c + 4 <= cols) {
+        const float4 v = *reinterpret_cast<const float4*>(s + c);
+        x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) x[q] = (c + q < cols) ? s[c + q] : 0.f;
+      }
+      __align__(8) __half p0[4];
+      __align__(8) __half p1[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) fp16_pieces(x[q] * scale, p0[q], p1[q]);
+      *reinterpret_cast<uint2*>(d0 + c) = *reinterpret_cast<uint2*>(p0);
+      *reinterpret_cast<uint2*>(d1 + c) = *reinterpret_cast<uint2*>(p1);
+    }
+  }
+}
+// Largest magnitude of every column of src (rows x cols), as the bit pattern of |x| (for
+// non-negative floats the integer order is the float order, so atomicMax is exact and the
+// result does not depend on the order of arrival).  umax must be zero on entry.
+// Block = cpb column lanes x (256 / cpb) row lanes; VEC: a column lane is four columns.
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+absmax_cols_kernel(const float* __restrict__ src, int64_t ld, int rows, int cols, unsigned* __restrict__ umax,
+                   int cpb, int rows_per_block) {
+  const int cl = threadIdx.x % cpb, rl = threadIdx.x / cpb, rpb = 256 / cpb;
+  const int cg = blockIdx.x * cpb + cl;
+  const int c0 = VEC ? cg * 4 : cg;
+  if (rl >= rpb || c0 >= cols) return;
+  const int r_end = min(rows, (int)((blockIdx.y + 1) * rows_per_block));
+  uint32_t m[4] = {0, 0, 0, 0};
+  if (VEC && c0 + 4 <= cols) {
+    for (int r = blockIdx.y * rows_per_block + rl; r < r_end; r += rpb) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(src + (int64_t)r * ld + c0));
+      m[0] = max(m[0], __float_as_uint(fabsf(v.x))); m[1] = max(m[1], __float_as_uint(fabsf(v.y)));
+      m[2] = max(m[2], __float_as_uint(fabsf(v.z))); m[3] = max(m[3], __float_as_uint(fabsf(v.w)));
+    }
+  } else {
+    const int w = VEC ? min(4, cols - c0) : 1;
+    for (int r = blockIdx.y * rows_per_block + rl; r < r_end; r += rpb)
+      for (int q = 0; q < w; ++q) m[q] = max(m[q], __float_as_uint(fabsf(src[(int64_t)r * ld + c0 + q])));
+  }
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    if (m[q] != 0 && c0 + q < cols) atomicMax(umax + c0 + q, m[q]);
+}
+// src is k_rows x r_cols (k slow); dst is r_cols x dst_ld (k fast), row c scaled by 2^shift_of(umax[c])
+__global__ void __launch_bounds__(256)
+split16_transpose_kernel(const float* __restrict__ src, int64_t src_ld, __half* __restrict__ h0,
+                         __half* __restrict__ h1, const unsigned* __restrict__ umax, int* __restrict__ exps,
+                         int64_t dst_ld, int k_rows, int r_cols) {
+  __shared__ float tile[64][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
+  const int c = blockIdx.x * 32 + tx;
+#pragma unroll
+  for (int j = ty; j < 64; j += 8) {
+    const int r = blockIdx.y * 64 + j;
+    tile[j][tx] = (r < k_rows && c < r_cols) ? src[(int64_t)r * src_ld + c] : 0.f;
+  }
+  __syncthreads();
+  const int k = blockIdx.y * 64 + 2 * tx;    // this lane's pair of k positions
+#pragma unroll
+  for (int j = ty; j < 32; j += 8) {
+    const int c2 = blockIdx.x * 32 + j;
+    if (c2 >= r_cols) continue;
+    const int sh = shift_of(umax[c2]);
+    if (blockIdx.y == 0 && tx == 0) exps[c2] = -sh;
+    if (k >= dst_ld) continue;               // dst_ld is even, so k + 1 < dst_ld as well
+    const float scale = pow2i(sh);
+    __half a0, a1, b0, b1;
+    fp16_pieces(tile[2 * tx][j] * scale, a0, a1);
+    fp16_pieces(tile[2 * tx + 1][j] * scale, b0, b1);
+    *reinterpret_cast<__half2*>(h0 + (int64_t)c2 * dst_ld + k) = __halves2half2(a0, b0);
+    *reinterpret_cast<__half2*>(h1 + (int64_t)c2 * dst_ld + k) = __halves2half2(a1, b1);
+  }
+}
+
 // C = alpha * (P_0 + P_1 + ... ) + beta * C, slices added in order; P_s are dense M x N.
 __global__ void __launch_bounds__(256)
 splitk_combine_kernel(const float* __restrict__ part, int splits, int64_t mn, int M, int N,
@@ -618,7 +998,7 @@ static EncodeTiledFn encode_fn() {
 
 // K-major operand: `rows` rows of `k` floats, row pitch ld floats (ld % 4 == 0)
 static bool make_map(CUtensorMap* map, const void* ptr, int rows, int k, int64_t ld, int box_rows, int bk,
-                     int elem_bytes = 4) {
+                     int elem_bytes = 4, bool fp16 = false) {
   cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * elem_bytes};
   cuuint32_t box[2] = {(cuuint32_t)bk, (cuuint32_t)box_rows};
@@ -626,8 +1006,9 @@ static bool make_map(CUtensorMap* map, const void* ptr, int rows, int k, int64_t
   CUtensorMapSwizzle sw = row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
                                            : (row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = encode_fn()(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
-                           2, (void*)ptr, dims, strides, box, estr,
+  const CUtensorMapDataType dt = elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : (fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+  CUresult r = encode_fn()(map, dt, 2, (void*)ptr, dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
@@ -643,29 +1024,43 @@ struct SplitOperand {
   __nv_bfloat16* xb = nullptr;
   __nv_bfloat16* lb = nullptr;
   __nv_bfloat16* b0 = nullptr;   // MODE 2: pieces are b0, xb (= b1), lb (= b2)
+  // MODE 3: x * 2^-exps[row] = h0 + h1 (+ 2^-22 of it), both FP16; umax is scratch for the
+  // column maxima of a transposed source
+  __half* h0 = nullptr;
+  __half* h1 = nullptr;
+  int* exps = nullptr;
+  unsigned* umax = nullptr;
 };
 
 template <class CFG>
 static prad_status launch_tf32x3(prad_ctx* ctx, const SplitOperand& a, const SplitOperand& b, int M, int N,
                                  int64_t kp, float* C, int64_t ldc, bool vecC, const Epi& epi) {
-  static std::once_flag attr_once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(attr_once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_tf32x3_kernel<CFG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    CFG::SMEM_BYTES);
-  });
-  PRAD_REQUIRE(attr_err == cudaSuccess, PRAD_ERR_CUDA, "gemm tf32x3: cannot reserve %d bytes of shared memory: %s",
-               CFG::SMEM_BYTES, cudaGetErrorString(attr_err));
+  constexpr bool ONLY_PERSISTENT = CFG::MODE == 3;
+  if constexpr (!ONLY_PERSISTENT) {
+    static std::once_flag attr_once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(attr_once, [] {
+      attr_err = cudaFuncSetAttribute(gemm_tf32x3_kernel<CFG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      CFG::SMEM_BYTES);
+    });
+    PRAD_REQUIRE(attr_err == cudaSuccess, PRAD_ERR_CUDA, "gemm tf32x3: cannot reserve %d bytes of shared memory: %s",
+                 CFG::SMEM_BYTES, cudaGetErrorString(attr_err));
+  }
   CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo, ma_x, mb_x;
   bool ok = true;
-  if (CFG::MODE == 2) {
+  if (CFG::MODE == 3) {
+    ok = make_map(&ma_x, a.h0, M, (int)kp, kp, BM, CFG::BK, 2, true) && make_map(&ma_lo, a.h1, M, (int)kp, kp, BM, CFG::BK, 2, true) &&
+         make_map(&mb_x, b.h0, N, (int)kp, kp, BN, CFG::BK, 2, true) && make_map(&mb_lo, b.h1, N, (int)kp, kp, BN, CFG::BK, 2, true);
+    ma_hi = ma_x;
+    mb_hi = mb_x;
+  } else if (CFG::MODE == 2) {
     ok = make_map(&ma_hi, a.b0, M, (int)kp, kp, BM, CFG::BK, 2) && make_map(&ma_x, a.xb, M, (int)kp, kp, BM, CFG::BK, 2) &&
          make_map(&ma_lo, a.lb, M, (int)kp, kp, BM, CFG::BK, 2) && make_map(&mb_hi, b.b0, N, (int)kp, kp, BN, CFG::BK, 2) &&
          make_map(&mb_x, b.xb, N, (int)kp, kp, BN, CFG::BK, 2) && make_map(&mb_lo, b.lb, N, (int)kp, kp, BN, CFG::BK, 2);
   } else {
     ok = make_map(&ma_hi, a.hi, M, (int)kp, kp, BM, CFG::BK) && make_map(&mb_hi, b.hi, N, (int)kp, kp, BN, CFG::BK);
   }
-  if (CFG::MODE == 2) {
+  if (CFG::MODE >= 2) {
   } else if (CFG::MODE == 0) {
     ok = ok && make_map(&ma_lo, a.lo, M, (int)kp, kp, BM, CFG::BK) && make_map(&mb_lo, b.lo, N, (int)kp, kp, BN, CFG::BK);
     ma_x = ma_lo;
@@ -694,9 +1089,35 @@ static prad_status launch_tf32x3(prad_ctx* ctx, const SplitOperand& a, const Spl
     for (int sp = 2; sp <= 64; ++sp)
       if (kp / sp >= 1024 && eff(sp) > best * 1.02) { best = eff(sp); splits = sp; }
   }
+  // MODE 1 and MODE 3 on the persistent kernel: one CTA per SM walks the tiles (and k-slices)
+  constexpr int PMODE = CFG::MODE == 3 ? 3 : 1;
+  const bool persistent = ONLY_PERSISTENT || (CFG::MODE == 1 && CFG::BK == p1::BK && ctx->tc_persistent);
+  if (persistent) {
+    static std::once_flag p_once;
+    static cudaError_t p_err = cudaSuccess;
+    std::call_once(p_once, [] {
+      p_err = cudaFuncSetAttribute(gemm_persistent_kernel<PMODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   p1::SMEM_BYTES);
+    });
+    PRAD_REQUIRE(p_err == cudaSuccess, PRAD_ERR_CUDA, "gemm (persistent): cannot reserve %d bytes of shared memory: %s",
+                 p1::SMEM_BYTES, cudaGetErrorString(p_err));
+  }
+  auto launch = [&](int nsplit, int kbps, int64_t stride, float* out, int64_t ldo, bool vec_out, const Epi& ep) {
+    if (persistent) {
+      TileSched ts{(int)grid.y, (int)grid.x, nsplit, kbps, total_kb, stride};
+      const int64_t total = tiles * nsplit;
+      const unsigned ctas = (unsigned)(total < ctx->sm_count ? total : ctx->sm_count);
+      gemm_persistent_kernel<PMODE><<<ctas, THREADS, p1::SMEM_BYTES, ctx->stream>>>(
+          ma_hi, ma_x, ma_lo, mb_hi, mb_x, mb_lo, M, N, out, ldo, vec_out, ep, ctx->tc_err, ts);
+    } else if constexpr (!ONLY_PERSISTENT) {
+      dim3 g3 = grid;
+      g3.z = (unsigned)nsplit;
+      gemm_tf32x3_kernel<CFG><<<g3, THREADS, CFG::SMEM_BYTES, ctx->stream>>>(
+          ma_hi, ma_lo, mb_hi, mb_lo, ma_x, mb_x, M, N, (int)kp, out, ldo, vec_out, ep, ctx->tc_err, kbps, stride);
+    }
+  };
   if (splits == 1) {
-    gemm_tf32x3_kernel<CFG><<<grid, THREADS, CFG::SMEM_BYTES, ctx->stream>>>(
-        ma_hi, ma_lo, mb_hi, mb_lo, ma_x, mb_x, M, N, (int)kp, C, ldc, vecC, epi, ctx->tc_err, total_kb, 0);
+    launch(1, total_kb, 0, C, ldc, vecC, epi);
     PRAD_LAUNCHED(ctx);
   } else {
     const int64_t mn = (int64_t)M * N;
@@ -706,13 +1127,10 @@ static prad_status launch_tf32x3(prad_ctx* ctx, const SplitOperand& a, const Spl
     Epi raw = epi;
     raw.alpha = 1.f;
     raw.beta = 0.f;
-    grid.z = (unsigned)splits;
     // k-blocks per slice rounded up to whole accumulation chunks, so slices start on chunk boundaries
     int kbps = (int)ceil_div(ceil_div(total_kb, splits), CFG::CHUNK_KB) * CFG::CHUNK_KB;
     splits = (int)ceil_div(total_kb, kbps);   // no empty slice
-    grid.z = (unsigned)splits;
-    gemm_tf32x3_kernel<CFG><<<grid, THREADS, CFG::SMEM_BYTES, ctx->stream>>>(
-        ma_hi, ma_lo, mb_hi, mb_lo, ma_x, mb_x, M, N, (int)kp, part, N, true, raw, ctx->tc_err, kbps, mn);
+    launch(splits, kbps, mn, part, N, true, raw);
     PRAD_LAUNCHED(ctx);
     const int cg = stream_grid(ctx, ceil_div(mn, 4), 256, 8);
     splitk_combine_kernel<<<cg, 256, 0, ctx->stream>>>(part, splits, mn, M, N, C, ldc, epi.alpha, epi.beta);
@@ -725,6 +1143,33 @@ static prad_status launch_tf32x3(prad_ctx* ctx, const SplitOperand& a, const Spl
 // writes the split form of one operand; `transposed` = the caller's matrix has k as its slow index
 static prad_status split_operand(prad_ctx* ctx, const float* src, int64_t ld, bool transposed, int rows, int K,
                                  int64_t kp, const SplitOperand& o) {
+  if (o.h0) {   // MODE 3: scaled FP16 pieces
+    if (!transposed) {
+      const int grid = (int)std::min<int64_t>(ceil_div(rows, 8), (int64_t)ctx->sm_count * 32);
+      split16_rows_kernel<<<grid, 256, 0, ctx->stream>>>(src, ld, o.h0, o.h1, o.exps, kp, rows, K);
+      PRAD_LAUNCHED(ctx);
+      return PRAD_OK;
+    }
+    // source is K x rows: column maxima first, then the transposing split
+    PRAD_CUDA(cudaMemsetAsync(o.umax, 0, (size_t)rows * sizeof(unsigned), ctx->stream));
+    const bool vec = (ld % 4 == 0) && (((uintptr_t)src & 15) == 0);
+    const int lanes = vec ? (int)ceil_div(rows, 4) : rows;      // column lanes in all
+    int cpb = 256;
+    while (cpb > 1 && cpb / 2 >= lanes) cpb /= 2;               // power of two, so 256 / cpb is whole
+    const int gx = (int)ceil_div(lanes, cpb);
+    // enough row slices to fill the machine, each at least 64 rows per row lane
+    int gy = (int)std::max<int64_t>(1, std::min<int64_t>(ceil_div((int64_t)ctx->sm_count * 8, gx),
+                                                          ceil_div(K, (int64_t)64 * (256 / cpb))));
+    const int rows_per_block = (int)ceil_div(K, gy);
+    gy = (int)ceil_div(K, rows_per_block);
+    if (vec) absmax_cols_kernel<true><<<dim3(gx, gy), 256, 0, ctx->stream>>>(src, ld, K, rows, o.umax, cpb, rows_per_block);
+    else absmax_cols_kernel<false><<<dim3(gx, gy), 256, 0, ctx->stream>>>(src, ld, K, rows, o.umax, cpb, rows_per_block);
+    PRAD_LAUNCHED(ctx);
+    dim3 grid((unsigned)ceil_div(rows, 32), (unsigned)ceil_div(kp, 64));
+    split16_transpose_kernel<<<grid, 256, 0, ctx->stream>>>(src, ld, o.h0, o.h1, o.umax, o.exps, kp, K, rows);
+    PRAD_LAUNCHED(ctx);
+    return PRAD_OK;
+  }
   if (!transposed) {
     int grid = stream_grid(ctx, (int64_t)rows * (kp / 4), 256, 8);
     split_kernel<<<grid, 256, 0, ctx->stream>>>(src, ld, o.hi, o.lo, o.xb, o.lb, o.b0, kp, rows, K);
@@ -746,7 +1191,7 @@ prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, do
   (void)sA; (void)sB; (void)sC;
   // shapes this kernel is meant for; everything else stays on the SIMT variant
   const bool forced = ctx->gemm_f32 == GemmF32::Tf32x3 || ctx->gemm_f32 == GemmF32::Tf32B16 ||
-                      ctx->gemm_f32 == GemmF32::Bf16x3;
+                      ctx->gemm_f32 == GemmF32::Bf16x3 || ctx->gemm_f32 == GemmF32::Fp16x3;
   // large products; a short M or N only wastes part of the 128 x 256 tile (TMA zero-fills it),
   // which still beats ten CTAs walking a 200 000-long k range one after the other
   const bool big = (int64_t)M * N * K >= ((int64_t)1 << 27) && M >= 64 && N >= 64 && K >= KPAD;
@@ -758,7 +1203,33 @@ prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, do
   if (probe_only) return PRAD_OK;
   const int mode = ctx->gemm_f32 == GemmF32::Tf32x3 ? 0
                    : ctx->gemm_f32 == GemmF32::Tf32B16 ? 1
-                   : ctx->gemm_f32 == GemmF32::Bf16x3 ? 2 : ctx->tc_auto_mode;
+                   : ctx->gemm_f32 == GemmF32::Bf16x3 ? 2
+                   : ctx->gemm_f32 == GemmF32::Fp16x3 ? 3 : ctx->tc_auto_mode;
+  const int64_t kp3 = ceil_div(K, KPAD) * KPAD;
+  if (mode == 3) {
+    // scratch: two FP16 pieces per element of both operands, then the exponents and column maxima
+    const size_t a_el = (size_t)M * kp3, b_el = (size_t)N * kp3;
+    const size_t ints = (size_t)ceil_div(M, 4) * 4 + (size_t)ceil_div(N, 4) * 4;
+    prad_status s3 = ensure_workspace(ctx, 2 * (a_el + b_el) * sizeof(__half) + 2 * ints * sizeof(int));
+    if (s3) return s3;
+    SplitOperand a3, b3;
+    a3.h0 = (__half*)ctx->ws;
+    a3.h1 = a3.h0 + a_el;
+    b3.h0 = a3.h1 + a_el;
+    b3.h1 = b3.h0 + b_el;
+    a3.exps = (int*)(b3.h1 + b_el);
+    b3.exps = a3.exps + ceil_div(M, 4) * 4;
+    a3.umax = (unsigned*)(a3.exps + ints);
+    b3.umax = a3.umax + ceil_div(M, 4) * 4;
+    s3 = split_operand(ctx, (const float*)A, lda, tA, M, K, kp3, a3);
+    if (s3) return s3;
+    s3 = split_operand(ctx, (const float*)B, ldb, !tB, N, K, kp3, b3);
+    if (s3) return s3;
+    Epi epi3{(const float*)e.bias, (float*)e.z_out, (int)e.act, (int)e.dact, (const float*)e.saved,
+             (float)e.act_alpha, (float)alpha, (float)beta, a3.exps, b3.exps};
+    const bool vec3 = (((uintptr_t)C & 15) == 0) && (ldc % 4 == 0) && (!e.saved || ((uintptr_t)e.saved & 15) == 0);
+    return launch_tf32x3<Cfg<32, 1, 3>>(ctx, a3, b3, M, N, kp3, (float*)C, ldc, vec3, epi3);
+  }
 
   // scratch: both operands K-major with pitch kp, 8 bytes per element in either mode
   const int64_t kp = ceil_div(K, KPAD) * KPAD;
@@ -793,7 +1264,7 @@ prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, do
   if (s) return s;
 
   Epi epi{(const float*)e.bias, (float*)e.z_out, (int)e.act, (int)e.dact, (const float*)e.saved,
-          (float)e.act_alpha, (float)alpha, (float)beta};
+          (float)e.act_alpha, (float)alpha, (float)beta, nullptr, nullptr};
   const bool vecC = (((uintptr_t)C & 15) == 0) && (ldc % 4 == 0) &&
                     (!e.saved || ((uintptr_t)e.saved & 15) == 0);
   float* Cf = (float*)C;

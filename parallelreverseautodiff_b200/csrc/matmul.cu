@@ -30,7 +30,8 @@ prad_status gemm_dispatch(prad_ctx* ctx, prad_dtype dt, bool tA, bool tB, int M,
   if (M == 0 || N == 0 || batch == 0) return PRAD_OK;
   if (dt == PRAD_F32) {
     const bool want_tc = ctx->gemm_f32 == GemmF32::Auto || ctx->gemm_f32 == GemmF32::Tf32x3 ||
-                         ctx->gemm_f32 == GemmF32::Tf32B16 || ctx->gemm_f32 == GemmF32::Bf16x3;
+                         ctx->gemm_f32 == GemmF32::Tf32B16 || ctx->gemm_f32 == GemmF32::Bf16x3 ||
+                         ctx->gemm_f32 == GemmF32::Fp16x3;
     if (want_tc) {
       prad_status p = gemm_tf32x3(ctx, tA, tB, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc,
                                   batch, sA, sB, sC, epi, true);

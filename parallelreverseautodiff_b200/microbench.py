@@ -92,7 +92,7 @@ def hbm_kernels(eng, only=None, rows=65536, cols=4096):
     return res
 
 
-def gemm_variants(eng, rows=16384, width=4096, modes=("simt_fma", "tf32x3", "tf32b16", "bf16x3")):
+def gemm_variants(eng, rows=16384, width=4096, modes=("simt_fma", "tf32x3", "tf32b16", "bf16x3", "fp16x3")):
     f = np.float32
     t = _Timer(eng)
     A, C_ = eng.zeros((rows, width), f), eng.zeros((rows, width), f)
@@ -118,10 +118,14 @@ def main():
     ap.add_argument("--only", default=None)
     ap.add_argument("--gemm", action="store_true")
     ap.add_argument("--rows", type=int, default=None)
+    ap.add_argument("--opt", action="append", default=[], metavar="KEY=VALUE", help="prad_set_option before running")
+    ap.add_argument("--modes", default="simt_fma,tf32x3,tf32b16,bf16x3,fp16x3")
     args = ap.parse_args()
     with E.Engine(0) as eng:
+        for kv in args.opt:
+            eng.set_option(*kv.split("=", 1))
         if args.gemm:
-            gemm_variants(eng, rows=args.rows or 16384)
+            gemm_variants(eng, rows=args.rows or 16384, modes=tuple(args.modes.split(",")))
         else:
             hbm_kernels(eng, only=args.only, rows=args.rows or 65536)
 

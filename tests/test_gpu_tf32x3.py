@@ -10,10 +10,10 @@ from util import assert_close, normal, rng, uniform
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=["tf32x3", "tf32b16", "bf16x3"])
+@pytest.fixture(params=["tf32x3", "tf32b16", "bf16x3", "fp16x3"])
 def tc_engine(engine, request):
     """Every split scheme: three TF32 products; one TF32 product + two BF16 corrections; six
-    BF16 products of three-piece operands."""
+    BF16 products of three-piece operands; three FP16 products of row-scaled two-piece operands."""
     engine.set_option("gemm_f32", request.param)
     yield engine
     engine.set_option("gemm_f32", "auto")
@@ -35,7 +35,9 @@ def test_tf32x3_matmul_forward_backward(tc_engine, shape):
     n0 = eng.launch_count()
     C = eng.matmul_forward(a, b).numpy()
     dA, dB = eng.matmul_backward(a, b, dc)
-    assert eng.launch_count() - n0 in (9, 10)    # 3 products x (2 operand splits + 1 GEMM) (+ split-K combine)
+    # 3 products x (2 operand splits + 1 GEMM) (+ split-K combine); the FP16 scheme adds a
+    # column-maximum pass before each of its three transposing splits
+    assert eng.launch_count() - n0 in (9, 10, 12, 13)
     assert_close(C, O.matmul_forward(A, B), np.abs(A).astype(np.float64) @ np.abs(B), "C")
     dA_ref, dB_ref = O.matmul_backward(A, B, dC)
     assert_close(dA.numpy(), dA_ref, np.abs(dC).astype(np.float64) @ np.abs(B.T), "dA")
@@ -89,3 +91,27 @@ def test_tf32x3_deterministic(tc_engine):
     A, B = normal(r, (300, 200), 1, np.float32), normal(r, (200, 280), 1, np.float32)
     a, b = eng.upload(A), eng.upload(B)
     np.testing.assert_array_equal(eng.matmul_forward(a, b).numpy(), eng.matmul_forward(a, b).numpy())
+
+
+@pytest.mark.parametrize("shape", [(256, 512, 256), (130, 333, 257)])
+def test_fp16x3_row_scaling_over_the_float_range(engine, shape):
+    """Rows of A and columns of B spread over 40 decades: the power-of-two row scaling keeps
+    every output element at FP32 accuracy relative to its own |A||B| bound."""
+    engine.set_option("gemm_f32", "fp16x3")
+    try:
+        M, K, N = shape
+        r = rng(11)
+        A = (normal(r, (M, K), 1, np.float64) * 10.0 ** r.uniform(-12, 12, (M, 1))).astype(np.float32)
+        B = (normal(r, (K, N), 1, np.float64) * 10.0 ** r.uniform(-7, 7, (1, N))).astype(np.float32)
+        A[3] = 0                     # an all-zero row stays zero
+        dC = (normal(r, (M, N), 1, np.float64) * 10.0 ** r.uniform(-5, 5, (M, 1))).astype(np.float32)
+        a, b, dc = engine.upload(A), engine.upload(B), engine.upload(dC)
+        C = engine.matmul_forward(a, b).numpy()
+        assert not C[3].any()
+        assert_close(C, O.matmul_forward(A, B), np.abs(A).astype(np.float64) @ np.abs(B), "C")
+        dA, dB = engine.matmul_backward(a, b, dc)
+        dA_ref, dB_ref = O.matmul_backward(A, B, dC)
+        assert_close(dA.numpy(), dA_ref, np.abs(dC).astype(np.float64) @ np.abs(B.T), "dA")
+        assert_close(dB.numpy(), dB_ref, np.abs(A.T).astype(np.float64) @ np.abs(dC), "dB")
+    finally:
+        engine.set_option("gemm_f32", "auto")
