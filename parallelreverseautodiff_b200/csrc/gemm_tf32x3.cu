@@ -502,10 +502,15 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
 
 // ---- persistent variant of MODE 1 (TF32 product + two BF16 corrections) -----------------
 // Same arithmetic and tile as gemm_tf32x3_kernel<Cfg<32,2,1>>, organised differently:
-//   * one CTA per SM walks output tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... (n-tile
-//     fastest, then m-tile, then k-slice), so the epilogue warps store tile i while the
-//     producer and MMA warps already work on tile i+1 (the two TMEM accumulators decouple
-//     them by two 256-k chunks);
+//   * one CTA per SM walks output tiles (n-tile fastest, then m-tile, then k-slice): its
+//     first tile is blockIdx.x, every further one comes from a global counter
+//     (gridDim.x + atomicAdd), so a CTA that starts late -- its SM was busy with a
+//     collective's kernel, say -- simply takes fewer tiles.  The producer publishes each
+//     tile index to the other warps through a four-entry queue in shared memory.  The
+//     epilogue warps store tile i while the producer and MMA warps already work on tile
+//     i+1 (the two TMEM accumulators decouple them by two 256-k chunks).  Which CTA
+//     computes a tile does not change its result.  The last CTA to finish resets the
+//     counters for the next launch;
 //   * the operand ring holds four units of 48 KB instead of two stages of 96 KB: a k-block
 //     of 32 arrives as unit H (the four BF16 tiles a_hb, a_lb, b_hb, b_lb) and unit F (the
 //     two FP32 tiles a_hi, b_hi), each with its own full/empty barrier pair, so a unit is
@@ -542,12 +547,19 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
   auto acc_full = [&](uint32_t b) { return bars + 8u * (2 * UNITS + b); };
   auto acc_empty = [&](uint32_t b) { return bars + 8u * (2 * UNITS + 2 + b); };
   const uint32_t tmem_slot = bars + 8u * (2 * UNITS + 4);
+  constexpr int TQ = 4;                       // depth of the tile-index queue
+  auto tile_full = [&](uint32_t i) { return bars + 8u * (2 * UNITS + 5 + i); };
+  auto tile_empty = [&](uint32_t i) { return bars + 8u * (2 * UNITS + 5 + TQ + i); };
   uint8_t* generic_base = smem_raw + (base - smem_u32(smem_raw));
   volatile uint32_t* tmem_slot_ptr =
       reinterpret_cast<volatile uint32_t*>(generic_base + UNITS * UNIT_BYTES + 8 * (2 * UNITS + 4));
+  volatile int* tile_q =
+      reinterpret_cast<volatile int*>(generic_base + UNITS * UNIT_BYTES + 8 * (2 * UNITS + 5 + 2 * TQ));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total_tiles = ts.tiles_m * ts.tiles_n * ts.splits;
+  int* const tile_counter = err_flag + 32;    // tiles handed out beyond the first gridDim.x
+  int* const done_counter = err_flag + 33;    // CTAs that have finished
 
   __shared__ int s_abort;
   if (threadIdx.x == 0) s_abort = *((volatile int*)err_flag);
@@ -557,6 +569,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
   if (threadIdx.x == 0) {
     for (int s = 0; s < UNITS; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), EPI_WARPS); }
+    for (int i = 0; i < TQ; ++i) { mbar_init(tile_full(i), 1); mbar_init(tile_empty(i), 1 + EPI_WARPS); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -567,6 +580,19 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+
+  // consumers: next tile index from the queue (-1 = no more tiles, -2 = gave up)
+  // (whole_warp: called by all 32 lanes, which then agree on the outcome)
+  auto next_tile = [&](uint32_t qi, int role, bool whole_warp) -> int {
+    const uint32_t slot = qi % TQ;
+    bool got = mbar_wait(tile_full(slot), (qi / TQ) & 1, err_flag, role);
+    if (whole_warp) got = __all_sync(0xffffffffu, got);
+    if (!got) return -2;
+    const int t = tile_q[slot];
+    if (whole_warp) __syncwarp();
+    if (lane == 0) mbar_arrive(tile_empty(slot));
+    return t;
+  };
 
   // tile t of this CTA: origin of the output tile and its k range
   auto tile_of = [&](int t, int& m0, int& n0, int& z, int& kb0, int& num_kb) {
@@ -580,9 +606,17 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      uint32_t g = 0;   // units issued so far, over all tiles of this CTA
+      uint32_t g = 0;    // units issued so far, over all tiles of this CTA
+      uint32_t qi = 0;   // tile indices published so far
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int t = blockIdx.x;
+      while (ok) {
+        const uint32_t qslot = qi % TQ, qround = qi / TQ;
+        if (qround > 0 && !mbar_wait(tile_empty(qslot), (qround - 1) & 1, err_flag, 5)) break;
+        tile_q[qslot] = t < total_tiles ? t : -1;
+        mbar_arrive(tile_full(qslot));        // release: the entry is visible to whoever sees the phase
+        ++qi;
+        if (t >= total_tiles) break;
         int m0, n0, z, kb0, num_kb;
         tile_of(t, m0, n0, z, kb0, num_kb);
         for (int kb = 0; kb < num_kb && ok; ++kb) {
@@ -604,15 +638,18 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
             }
           }
         }
+        t = (int)gridDim.x + atomicAdd(tile_counter, 1);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = idesc_tf32(), idesc_h = idesc_bf16();
-      uint32_t g = 0, gc = 0;   // units consumed, chunks started
+      uint32_t g = 0, gc = 0, qi = 0;   // units consumed, chunks started, tiles taken
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      while (ok) {
+        const int t = next_tile(qi++, 6, false);
+        if (t < 0) break;
         int m0, n0, z, kb0, num_kb;
         tile_of(t, m0, n0, z, kb0, num_kb);
         const int num_chunks = (num_kb + CHUNK_KB - 1) / CHUNK_KB;
@@ -687,9 +724,11 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
     // ------------------------------------------------------------ epilogue (warps 2..9)
     const int sub = warp & 3;                 // TMEM sub-partition this warp may read
     const int half = (warp - 2) >> 2;         // which 128 columns of the tile
-    uint32_t gc = 0;
+    uint32_t gc = 0, qi = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+    while (ok) {
+      const int t = next_tile(qi++, 7, true);
+      if (t < 0) break;
       int m0, n0, z, kb0, num_kb;
       tile_of(t, m0, n0, z, kb0, num_kb);
       const int num_chunks = (num_kb + CHUNK_KB - 1) / CHUNK_KB;
@@ -700,7 +739,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
         for (int j = 0; j < 32; ++j) sum[g][j] = 0.f;
       for (int ch = 0; ch < num_chunks; ++ch, ++gc) {
         const uint32_t buf = gc & 1;
-        ok = mbar_wait(acc_full(buf), (gc >> 1) & 1, err_flag, 3);
+        ok = __all_sync(0xffffffffu, mbar_wait(acc_full(buf), (gc >> 1) & 1, err_flag, 3));
         if (!ok) break;
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + buf * (uint32_t)BN + (uint32_t)(half * 128);
@@ -735,6 +774,16 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  // the last CTA to get here (every producer has drawn its final index by then) zeroes the
+  // counters for the next launch on this stream
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(done_counter, 1) == (int)gridDim.x - 1) {
+      *((volatile int*)tile_counter) = 0;
+      *((volatile int*)done_counter) = 0;
+      __threadfence();
+    }
   }
 }
 
@@ -1286,9 +1335,10 @@ prad_status gemm_tf32x3_check(prad_ctx* ctx) {
   int flag = 0;
   PRAD_CUDA(cudaMemcpyAsync(&flag, ctx->tc_err, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
   PRAD_CUDA(cudaStreamSynchronize(ctx->stream));
-  if (flag != 0) PRAD_CUDA(cudaMemsetAsync(ctx->tc_err, 0, sizeof(int), ctx->stream));
+  if (flag != 0) PRAD_CUDA(cudaMemsetAsync(ctx->tc_err, 0, 256, ctx->stream));   // flag and tile counters
   PRAD_REQUIRE(flag == 0, PRAD_ERR_TIMEOUT,
-               "gemm tf32x3: a bounded wait ran out inside the kernel (role %d: 1 producer, 2 MMA, 3 epilogue); "
+               "gemm (tensor core): a bounded wait ran out inside the kernel (role %d: 1 producer, 2 MMA, 3 epilogue, "
+               "4 accumulator hand-back, 5-7 tile queue); "
                "the results of that product are invalid", flag);
   return PRAD_OK;
 }
