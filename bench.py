@@ -47,6 +47,8 @@ def parse():
     ap.add_argument("--width", type=int, default=WIDTH)
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--clip", default="reference", choices=["reference", "global_norm", "none"])
+    ap.add_argument("--opt", action="append", default=[], metavar="KEY=VALUE",
+                    help="library option set with prad_set_option before the run (repeatable)")
     ap.add_argument("--gemm", default="auto", choices=["auto", "simt", "simt_fma", "tf32x3", "tf32b16", "bf16x3", "fp16x3"])
     ap.add_argument("--tc-pipeline", default=None, choices=[None, "16x4", "32x2", "8x8"])
     ap.add_argument("--lr", type=float, default=1e-5,
@@ -216,6 +218,8 @@ def run_native(args, rank, world, local_rank):
 
     eng = E.Engine(local_rank)
     eng.set_option("gemm_f32", args.gemm)
+    for kv in args.opt:
+        eng.set_option(*kv.split("=", 1))
     if args.tc_pipeline:
         eng.set_option("tc_pipeline", args.tc_pipeline)
     if world > 1:

@@ -1,4 +1,5 @@
 // Lifecycle, error reporting and memory entry points of libprad_cuda.
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -154,6 +155,20 @@ prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value) {
     else if (!strcmp(value, "bf16x3")) ctx->tc_auto_mode = 2;
     else if (!strcmp(value, "fp16x3")) ctx->tc_auto_mode = 3;
     else { set_error("prad_set_option: tc_auto must be tf32x3|tf32b16|bf16x3|fp16x3, got '%s'", value); return PRAD_ERR_INVALID; }
+    return PRAD_OK;
+  }
+  if (!strcmp(key, "tc_chunk_k")) {
+    const int n = atoi(value);
+    PRAD_REQUIRE(n == 128 || n == 256 || n == 512 || n == 1024, PRAD_ERR_INVALID,
+                 "prad_set_option: tc_chunk_k must be 128, 256, 512 or 1024, got '%s'", value);
+    ctx->tc_chunk_k = n;
+    return PRAD_OK;
+  }
+  if (!strcmp(key, "tc_reserve_sms")) {
+    const int n = atoi(value);
+    PRAD_REQUIRE(n >= 0 && n < ctx->sm_count, PRAD_ERR_INVALID, "prad_set_option: tc_reserve_sms must be in [0, %d), got '%s'",
+                 ctx->sm_count, value);
+    ctx->tc_reserve_sms = n;
     return PRAD_OK;
   }
   if (!strcmp(key, "tc_persistent")) {

@@ -528,6 +528,7 @@ static_assert(SMEM_BYTES <= 227 * 1024, "unit ring does not fit in shared memory
 struct TileSched {
   int tiles_m, tiles_n, splits;   // tile t -> (t % tiles_n, (t / tiles_n) % tiles_m, t / (tiles_n * tiles_m))
   int kb_per_split, total_kb;     // k-blocks per slice and in all
+  int chunk_kb;                   // k-blocks per accumulation chunk
   int64_t split_stride;           // elements between the partial products of consecutive slices
 };
 
@@ -652,7 +653,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
         if (t < 0) break;
         int m0, n0, z, kb0, num_kb;
         tile_of(t, m0, n0, z, kb0, num_kb);
-        const int num_chunks = (num_kb + CHUNK_KB - 1) / CHUNK_KB;
+        const int num_chunks = (num_kb + ts.chunk_kb - 1) / ts.chunk_kb;
         for (int ch = 0; ch < num_chunks && ok; ++ch, ++gc) {
           const uint32_t buf = gc & 1, use = gc >> 1;
           if (use > 0) {
@@ -661,8 +662,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
             tc_fence_after();
           }
           const uint32_t d_tmem = tmem_base + buf * (uint32_t)BN;
-          const int kb_end = min(num_kb, (ch + 1) * CHUNK_KB);
-          for (int kb = ch * CHUNK_KB; kb < kb_end && ok; ++kb) {
+          const int kb_end = min(num_kb, (ch + 1) * ts.chunk_kb);
+          for (int kb = ch * ts.chunk_kb; kb < kb_end && ok; ++kb) {
             if (PMODE == 3) {   // one unit: a_h0 | a_h1 | b_h0 | b_h1, three FP16 products, smallest first
               constexpr uint32_t idesc_q = idesc_fp16();
               const uint32_t slot = g & (UNITS - 1);
@@ -675,7 +676,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
 #pragma unroll
               for (int k = 0; k < BK / 16; ++k) {
                 const uint64_t adv = (uint64_t)((k * 16 * 2) >> 4);
-                umma_f16(d_tmem, a_1 + adv, b_0 + adv, idesc_q, !(kb == ch * CHUNK_KB && k == 0));
+                umma_f16(d_tmem, a_1 + adv, b_0 + adv, idesc_q, !(kb == ch * ts.chunk_kb && k == 0));
                 umma_f16(d_tmem, a_0 + adv, b_1 + adv, idesc_q, 1);
                 umma_f16(d_tmem, a_0 + adv, b_0 + adv, idesc_q, 1);
               }
@@ -694,7 +695,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
 #pragma unroll
               for (int k = 0; k < BK / 16; ++k) {
                 const uint64_t adv = (uint64_t)((k * 16 * 2) >> 4);
-                umma_f16(d_tmem, a_lb + adv, b_hb + adv, idesc_h, !(kb == ch * CHUNK_KB && k == 0));
+                umma_f16(d_tmem, a_lb + adv, b_hb + adv, idesc_h, !(kb == ch * ts.chunk_kb && k == 0));
                 umma_f16(d_tmem, a_hb + adv, b_lb + adv, idesc_h, 1);
               }
               umma_commit(empty_bar(slot));
@@ -731,7 +732,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
       if (t < 0) break;
       int m0, n0, z, kb0, num_kb;
       tile_of(t, m0, n0, z, kb0, num_kb);
-      const int num_chunks = (num_kb + CHUNK_KB - 1) / CHUNK_KB;
+      const int num_chunks = (num_kb + ts.chunk_kb - 1) / ts.chunk_kb;
       float sum[4][32];
 #pragma unroll
       for (int g = 0; g < 4; ++g)
@@ -1153,9 +1154,10 @@ static prad_status launch_tf32x3(prad_ctx* ctx, const SplitOperand& a, const Spl
   }
   auto launch = [&](int nsplit, int kbps, int64_t stride, float* out, int64_t ldo, bool vec_out, const Epi& ep) {
     if (persistent) {
-      TileSched ts{(int)grid.y, (int)grid.x, nsplit, kbps, total_kb, stride};
+      TileSched ts{(int)grid.y, (int)grid.x, nsplit, kbps, total_kb, ctx->tc_chunk_k / p1::BK, stride};
       const int64_t total = tiles * nsplit;
-      const unsigned ctas = (unsigned)(total < ctx->sm_count ? total : ctx->sm_count);
+      const int64_t sms = ctx->sm_count - ctx->tc_reserve_sms;
+      const unsigned ctas = (unsigned)(total < sms ? total : sms);
       gemm_persistent_kernel<PMODE><<<ctas, THREADS, p1::SMEM_BYTES, ctx->stream>>>(
           ma_hi, ma_x, ma_lo, mb_hi, mb_x, mb_lo, M, N, out, ldo, vec_out, ep, ctx->tc_err, ts);
     } else if constexpr (!ONLY_PERSISTENT) {
