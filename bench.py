@@ -47,6 +47,8 @@ def parse():
     ap.add_argument("--width", type=int, default=WIDTH)
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--clip", default="reference", choices=["reference", "global_norm", "none"])
+    ap.add_argument("--no-sequence", action="store_true",
+                    help="c1..c4: call the entry points every step instead of replaying a recorded launch sequence")
     ap.add_argument("--opt", action="append", default=[], metavar="KEY=VALUE",
                     help="library option set with prad_set_option before the run (repeatable)")
     ap.add_argument("--gemm", default="auto", choices=["auto", "simt", "simt_fma", "tf32x3", "tf32b16", "bf16x3", "fp16x3"])
@@ -406,6 +408,10 @@ def run_small(args, rank, world, local_rank):
 
     for _ in range(max(args.warmup, 3)):
         runner.backward()
+    # the step as a recorded launch sequence (one submission per step) unless --no-sequence
+    seq = None if args.no_sequence else eng.record(runner.backward)
+    step = seq.launch if seq else runner.backward
+    step()
     sampler = ClockSampler(local_rank)
     barrier()
     sampler.start()
@@ -415,7 +421,7 @@ def run_small(args, rank, world, local_rank):
         eng.zero_(flush)                                   # L2 flush, outside the timed bracket
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
-        runner.backward()
+        step()
         e1.record(stream)
         eng.sync()
         total_ms += e0.elapsed_time(e1)
@@ -454,6 +460,7 @@ def run_small(args, rank, world, local_rank):
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": runner.dtype, "data": "synthetic",
             "config": {"workload": runner.name, "parallelism": f"replicas x{world}",
+                       "submission": "direct calls" if seq is None else "recorded launch sequence (prad_sequence_launch)",
                        "l2": "256 MiB buffer written between timed steps (L2 flush)"},
             "tflops": tflops * world,
             "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["tensor_tflops"], "unit": "TFLOP/s",

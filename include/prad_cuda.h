@@ -71,17 +71,26 @@ const char* prad_last_error(void);
 /* library version string and the sm architecture it was built for */
 const char* prad_version(void);
 /* options:
- *  "gemm_f32" = "auto" | "simt" | "simt_fma" | "tf32x3" | "tf32b16" | "bf16x3";
+ *  "gemm_f32" = "auto" | "simt" | "simt_fma" | "fp16x3" | "tf32b16" | "tf32x3" | "bf16x3";
  *  "gemm_f64" = "auto" | "simt" | "simt_fma" | "dmma"
  *    simt     : multiply and add rounded separately, k ascending -- bit-identical to the managed
  *               code's sequential `Output[i][j] += a*b` loop (the default for small products);
  *    simt_fma : same order with fused multiply-add (twice the rate, one rounding per step);
+ *    fp16x3   : tcgen05 kernel; every row of a K-major operand is scaled by a power of two and
+ *               split into two FP16 pieces (22 significant bits); three FP16 products per term
+ *               (h1*h0' + h0*h1' + h0*h0'); what "auto" uses for large products;
+ *    tf32b16  : tcgen05 kernel, one TF32 product + two BF16 correction products;
  *    tf32x3   : tcgen05 kernel, three TF32 products per term (a_hi*b_hi + a_lo*b_hi + a_hi*b_lo);
- *    tf32b16  : tcgen05 kernel, one TF32 product + two BF16 correction products (what "auto" uses);
  *    bf16x3   : tcgen05 kernel, six BF16 products of three-piece operands;
  *    dmma     : FP64 mma.sync kernel; all tensor-core kernels stay within the documented tolerance;
- *    auto     : tensor-core kernel for large products, "simt" otherwise;
- * "tc_pipeline" = "16x4" | "32x2" | "8x8" (k-block floats x stages of the tensor-core GEMM) */
+ *    auto     : tensor-core kernel for large products (>= 2^27 multiply-adds), "simt" otherwise;
+ *  "tc_auto" = "fp16x3" | "tf32b16" | "tf32x3" | "bf16x3": the scheme "auto" uses for large products;
+ *  "tc_chunk_k" = "128" | "256" | "512" | "1024": k summed inside the tensor core before the partial
+ *    sum is added in FP32 with round-to-nearest (the tensor core truncates; default 256: rms error
+ *    9e-7 of the result for any K; 512 is 4 % faster at 1.8e-6);
+ *  "tc_split_k" = "on" | "off"; "tc_persistent" = "on" | "off" (tf32b16 on the one-tile-per-CTA kernel);
+ *  "tc_reserve_sms" = n: SMs the persistent GEMM leaves idle (default 0);
+ *  "tc_pipeline" = "16x4" | "32x2" | "8x8" (k-block floats x stages of the tf32x3 kernel) */
 prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value);
 /* wait for everything enqueued on the context (what the managed code gets for free
  * because GetAsArray2D blocks, src/RMAD/GpuMatrixMultiplyOperation.cs:199-201) */
@@ -373,6 +382,29 @@ prad_status prad_graph_value_data(prad_graph* g, int value, void** out_data);
 prad_status prad_graph_value_gradient(prad_graph* g, int value, void** out_grad);
 /* How many consumers each value had in the last backward (BackwardDependencyCounts). */
 prad_status prad_graph_consumer_count(prad_graph* g, int value, int* out_count);
+
+/* ---------------------------------------------------------------- recorded launch sequences
+ * No counterpart in the reference, whose executor walks the operation list and calls each
+ * Backward from managed code every step (src/RMAD/ComputationGraph.cs, NeuralNetwork
+ * AutomaticBackwardPropagate).  For the small configurations that walk is the cost: hundreds
+ * of launches of a few microseconds each.  Between prad_capture_begin and prad_capture_end
+ * every entry point that only enqueues device work (GEMMs, elementwise and row operations,
+ * losses, accumulation, clip/Adam without a host result, prad_zero, prad_copy, graph-mode
+ * forward/backward) records into a launch sequence instead of running; nothing executes.
+ * prad_sequence_launch then replays the whole sequence with one submission, on the same
+ * buffers with whatever they hold at that moment.
+ * Entry points that wait for the device, move host data, check embedding indices or grow
+ * library scratch return PRAD_ERR_INVALID while a recording is open: run the step once
+ * unrecorded first, so that scratch has its final size.  Scratch that a live sequence may
+ * address is kept until the last sequence of the context is destroyed.  The buffers a
+ * sequence addresses must stay allocated while it is in use. */
+typedef struct prad_sequence prad_sequence;
+prad_status prad_capture_begin(prad_ctx* ctx);
+prad_status prad_capture_end(prad_ctx* ctx, prad_sequence** out_sequence);
+prad_status prad_sequence_launch(prad_ctx* ctx, prad_sequence* sequence);
+/* How many kernel launches one replay stands for (added to prad_launch_count per replay). */
+prad_status prad_sequence_launch_count(prad_sequence* sequence, int64_t* out_count);
+prad_status prad_sequence_destroy(prad_ctx* ctx, prad_sequence* sequence);
 
 /* ---------------------------------------------------------------- data parallel
  * Not in the reference (it has no multi-device code; its closest relative is the offline

@@ -23,6 +23,11 @@ SIGNATURES = {
     "prad_set_option": [vp, C.c_char_p, C.c_char_p],
     "prad_sync": [vp],
     "prad_launch_count": [vp, pi64],
+    "prad_capture_begin": [vp],
+    "prad_capture_end": [vp, pvp],
+    "prad_sequence_launch": [vp, vp],
+    "prad_sequence_launch_count": [vp, pi64],
+    "prad_sequence_destroy": [vp, vp],
     "prad_stream": [vp, pvp],
     "prad_use_stream": [vp, vp],
     "prad_alloc": [vp, sz, pvp],

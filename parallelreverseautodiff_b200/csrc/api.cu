@@ -15,16 +15,22 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
-static prad_status grow(void** p, size_t* have, size_t need, bool host) {
+static prad_status grow(prad_ctx* ctx, void** p, size_t* have, size_t need, bool host, const char* what) {
   if (*have >= need) return PRAD_OK;
+  PRAD_NOT_CAPTURING(ctx, what);
+  // earlier kernels may still read the old block
+  cudaError_t e = cudaStreamSynchronize(ctx->stream);
+  if (e != cudaSuccess) { set_error("sync before %s: %s", what, cudaGetErrorString(e)); return PRAD_ERR_CUDA; }
   size_t want = need + need / 4;
   want = (want + 255) & ~(size_t)255;
   if (*p) {
-    if (host) cudaFreeHost(*p); else cudaFree(*p);
+    if (host) cudaFreeHost(*p);
+    else if (ctx->live_sequences > 0) ctx->retired.push_back(*p);   // a recorded sequence may address it
+    else cudaFree(*p);
     *p = nullptr;
     *have = 0;
   }
-  cudaError_t e = host ? cudaMallocHost(p, want) : cudaMalloc(p, want);
+  e = host ? cudaMallocHost(p, want) : cudaMalloc(p, want);
   if (e != cudaSuccess) {
     (void)cudaGetLastError();
     set_error("scratch allocation of %zu bytes failed: %s", want, cudaGetErrorString(e));
@@ -35,26 +41,13 @@ static prad_status grow(void** p, size_t* have, size_t need, bool host) {
 }
 
 prad_status ensure_workspace(prad_ctx* ctx, size_t bytes) {
-  if (ctx->ws_bytes < bytes) {
-    // earlier kernels may still read the old block
-    cudaError_t e = cudaStreamSynchronize(ctx->stream);
-    if (e != cudaSuccess) { set_error("sync before workspace growth: %s", cudaGetErrorString(e)); return PRAD_ERR_CUDA; }
-  }
-  return grow(&ctx->ws, &ctx->ws_bytes, bytes, false);
+  return grow(ctx, &ctx->ws, &ctx->ws_bytes, bytes, false, "growth of the device scratch");
 }
 prad_status ensure_host_workspace(prad_ctx* ctx, size_t bytes) {
-  if (ctx->host_ws_bytes < bytes) {
-    cudaError_t e = cudaStreamSynchronize(ctx->stream);
-    if (e != cudaSuccess) { set_error("sync before host scratch growth: %s", cudaGetErrorString(e)); return PRAD_ERR_CUDA; }
-  }
-  return grow(&ctx->host_ws, &ctx->host_ws_bytes, bytes, true);
+  return grow(ctx, &ctx->host_ws, &ctx->host_ws_bytes, bytes, true, "growth of the pinned host scratch");
 }
 prad_status ensure_stage(prad_ctx* ctx, size_t bytes) {
-  if (ctx->stage_bytes < bytes) {
-    cudaError_t e = cudaStreamSynchronize(ctx->stream);
-    if (e != cudaSuccess) { set_error("sync before staging growth: %s", cudaGetErrorString(e)); return PRAD_ERR_CUDA; }
-  }
-  return grow(&ctx->stage, &ctx->stage_bytes, bytes, false);
+  return grow(ctx, &ctx->stage, &ctx->stage_bytes, bytes, false, "growth of the staging scratch");
 }
 
 prad_status dp_destroy(prad_ctx* ctx);  // dp.cu
@@ -117,6 +110,7 @@ prad_status prad_shutdown(prad_ctx* ctx) {
   dp_destroy(ctx);
   if (ctx->ws) cudaFree(ctx->ws);
   if (ctx->tc_err) cudaFree(ctx->tc_err);
+  for (void* r : ctx->retired) cudaFree(r);
   if (ctx->stage) cudaFree(ctx->stage);
   if (ctx->host_ws) cudaFreeHost(ctx->host_ws);
   if (ctx->copy_stream) { cudaStreamSynchronize(ctx->copy_stream); cudaStreamDestroy(ctx->copy_stream); }
@@ -192,6 +186,7 @@ prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value) {
 
 prad_status prad_sync(prad_ctx* ctx) {
   PRAD_CHECK_CTX(ctx);
+  PRAD_NOT_CAPTURING(ctx, "prad_sync");
   PRAD_CUDA(cudaStreamSynchronize(ctx->stream));
   return gemm_tf32x3_check(ctx);
 }
@@ -212,6 +207,7 @@ prad_status prad_stream(prad_ctx* ctx, void** out_stream) {
 
 prad_status prad_use_stream(prad_ctx* ctx, void* stream) {
   PRAD_CHECK_CTX(ctx);
+  PRAD_NOT_CAPTURING(ctx, "prad_use_stream");
   PRAD_CUDA(cudaStreamSynchronize(ctx->stream));
   ctx->stream = stream ? (cudaStream_t)stream : ctx->own_stream;
   return PRAD_OK;
@@ -233,6 +229,7 @@ prad_status prad_alloc(prad_ctx* ctx, size_t bytes, void** out_dptr) {
 
 prad_status prad_free(prad_ctx* ctx, void* dptr) {
   PRAD_CHECK_CTX(ctx);
+  PRAD_NOT_CAPTURING(ctx, "prad_free");
   if (!dptr) return PRAD_OK;
   PRAD_CUDA(cudaStreamSynchronize(ctx->stream));
   PRAD_CUDA(cudaFree(dptr));
@@ -276,6 +273,7 @@ prad_status prad_copy(prad_ctx* ctx, void* dst, const void* src, size_t bytes) {
 
 prad_status prad_upload(prad_ctx* ctx, void* dst, const void* src_host, size_t bytes) {
   PRAD_CHECK_CTX(ctx);
+  PRAD_NOT_CAPTURING(ctx, "prad_upload");
   PRAD_REQUIRE((dst && src_host) || bytes == 0, PRAD_ERR_INVALID, "prad_upload: null pointer");
   if (bytes) PRAD_CUDA(cudaMemcpyAsync(dst, src_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
   return PRAD_OK;
@@ -283,6 +281,7 @@ prad_status prad_upload(prad_ctx* ctx, void* dst, const void* src_host, size_t b
 
 prad_status prad_download(prad_ctx* ctx, void* dst_host, const void* src, size_t bytes) {
   PRAD_CHECK_CTX(ctx);
+  PRAD_NOT_CAPTURING(ctx, "prad_download");
   PRAD_REQUIRE((dst_host && src) || bytes == 0, PRAD_ERR_INVALID, "prad_download: null pointer");
   if (bytes) {
     PRAD_CUDA(cudaMemcpyAsync(dst_host, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
@@ -293,6 +292,7 @@ prad_status prad_download(prad_ctx* ctx, void* dst_host, const void* src, size_t
 
 prad_status prad_upload_prefetch(prad_ctx* ctx, void* dst, const void* src_host, size_t bytes) {
   PRAD_CHECK_CTX(ctx);
+  PRAD_NOT_CAPTURING(ctx, "prad_upload_prefetch");
   PRAD_REQUIRE((dst && src_host) || bytes == 0, PRAD_ERR_INVALID, "prad_upload_prefetch: null pointer");
   if (bytes == 0) return PRAD_OK;
   if (!ctx->copy_stream) {
@@ -306,6 +306,7 @@ prad_status prad_upload_prefetch(prad_ctx* ctx, void* dst, const void* src_host,
 
 prad_status prad_upload_join(prad_ctx* ctx) {
   PRAD_CHECK_CTX(ctx);
+  PRAD_NOT_CAPTURING(ctx, "prad_upload_join");
   if (!ctx->copy_pending) return PRAD_OK;
   PRAD_CUDA(cudaEventRecord(ctx->copy_done, ctx->copy_stream));
   PRAD_CUDA(cudaStreamWaitEvent(ctx->stream, ctx->copy_done, 0));
@@ -317,6 +318,7 @@ prad_status prad_upload_join(prad_ctx* ctx) {
 prad_status prad_upload_rows(prad_ctx* ctx, void* dst, const void* const* src_rows, int rows,
                              size_t row_bytes) {
   PRAD_CHECK_CTX(ctx);
+  PRAD_NOT_CAPTURING(ctx, "prad_upload_rows");
   PRAD_REQUIRE(rows >= 0, PRAD_ERR_INVALID, "prad_upload_rows: negative row count");
   if (rows == 0 || row_bytes == 0) return PRAD_OK;
   PRAD_REQUIRE(dst && src_rows, PRAD_ERR_INVALID, "prad_upload_rows: null pointer");
@@ -336,6 +338,7 @@ prad_status prad_upload_rows(prad_ctx* ctx, void* dst, const void* const* src_ro
 prad_status prad_download_rows(prad_ctx* ctx, void* const* dst_rows, const void* src, int rows,
                                size_t row_bytes) {
   PRAD_CHECK_CTX(ctx);
+  PRAD_NOT_CAPTURING(ctx, "prad_download_rows");
   PRAD_REQUIRE(rows >= 0, PRAD_ERR_INVALID, "prad_download_rows: negative row count");
   if (rows == 0 || row_bytes == 0) return PRAD_OK;
   PRAD_REQUIRE(dst_rows && src, PRAD_ERR_INVALID, "prad_download_rows: null pointer");
@@ -347,6 +350,80 @@ prad_status prad_download_rows(prad_ctx* ctx, void* const* dst_rows, const void*
   for (int i = 0; i < rows; ++i) {
     PRAD_REQUIRE(dst_rows[i], PRAD_ERR_INVALID, "prad_download_rows: row %d is null", i);
     memcpy(dst_rows[i], (const char*)ctx->host_ws + (size_t)i * row_bytes, row_bytes);
+  }
+  return PRAD_OK;
+}
+
+// ---- recorded launch sequences ---------------------------------------------------------
+prad_status prad_capture_begin(prad_ctx* ctx) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(!ctx->capturing, PRAD_ERR_INVALID, "prad_capture_begin: a recording is already open");
+  PRAD_REQUIRE(!ctx->copy_pending, PRAD_ERR_INVALID, "prad_capture_begin: join the pending prefetch first");
+  PRAD_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
+  ctx->capturing = true;
+  ctx->capture_launches0 = ctx->launches;
+  return PRAD_OK;
+}
+
+prad_status prad_capture_end(prad_ctx* ctx, prad_sequence** out_sequence) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(ctx->capturing, PRAD_ERR_INVALID, "prad_capture_end: no recording is open");
+  ctx->capturing = false;
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+  if (e != cudaSuccess || graph == nullptr) {
+    (void)cudaGetLastError();
+    set_error("prad_capture_end: the recording was invalidated (%s); an entry point that cannot be recorded "
+              "was probably called in between", cudaGetErrorString(e));
+    return PRAD_ERR_CUDA;
+  }
+  PRAD_REQUIRE(out_sequence, PRAD_ERR_INVALID, "prad_capture_end: null output");
+  prad_sequence* seq = new prad_sequence();
+  e = cudaGraphInstantiate(&seq->exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    delete seq;
+    set_error("prad_capture_end: cudaGraphInstantiate: %s", cudaGetErrorString(e));
+    return PRAD_ERR_CUDA;
+  }
+  seq->launches = ctx->launches - ctx->capture_launches0;
+  ctx->launches = ctx->capture_launches0;   // nothing ran while recording
+  seq->owner = ctx;
+  ctx->live_sequences++;
+  *out_sequence = seq;
+  return PRAD_OK;
+}
+
+prad_status prad_sequence_launch(prad_ctx* ctx, prad_sequence* seq) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(seq && seq->magic == 0x50534551u && seq->owner == ctx, PRAD_ERR_INVALID,
+               "prad_sequence_launch: not a sequence of this context");
+  PRAD_NOT_CAPTURING(ctx, "prad_sequence_launch");
+  PRAD_CUDA(cudaGraphLaunch(seq->exec, ctx->stream));
+  ctx->launches += seq->launches;
+  ctx->tc_pending_check = true;
+  return PRAD_OK;
+}
+
+prad_status prad_sequence_launch_count(prad_sequence* seq, int64_t* out_count) {
+  PRAD_REQUIRE(seq && seq->magic == 0x50534551u && out_count, PRAD_ERR_INVALID, "prad_sequence_launch_count: bad argument");
+  *out_count = seq->launches;
+  return PRAD_OK;
+}
+
+prad_status prad_sequence_destroy(prad_ctx* ctx, prad_sequence* seq) {
+  PRAD_CHECK_CTX(ctx);
+  if (!seq) return PRAD_OK;
+  PRAD_REQUIRE(seq->magic == 0x50534551u && seq->owner == ctx, PRAD_ERR_INVALID,
+               "prad_sequence_destroy: not a sequence of this context");
+  PRAD_CUDA(cudaStreamSynchronize(ctx->stream));
+  cudaGraphExecDestroy(seq->exec);
+  seq->magic = 0;
+  delete seq;
+  if (--ctx->live_sequences == 0) {
+    for (void* r : ctx->retired) cudaFree(r);
+    ctx->retired.clear();
   }
   return PRAD_OK;
 }

@@ -51,7 +51,19 @@ struct prad_ctx {
   int tc_reserve_sms = 0;  // option "tc_reserve_sms": SMs the persistent GEMM leaves free (for a collective's kernels)
   bool tc_persistent = true;  // option "tc_persistent": TF32+BF16 products run on the persistent kernel
   int tc_auto_mode = 3;  // split scheme "auto" picks: 0 = 3xTF32, 1 = TF32 + BF16 corrections, 2 = BF16 x 6, 3 = FP16 x 3
+  // recorded launch sequences (prad_capture_begin ... prad_sequence_launch)
+  bool capturing = false;
+  int64_t capture_launches0 = 0;
+  int live_sequences = 0;
+  std::vector<void*> retired;  // scratch blocks a live sequence may still address; freed with the last sequence
   uint32_t magic = 0x50524144u;  // "PRAD"
+};
+
+struct prad_sequence {
+  cudaGraphExec_t exec = nullptr;
+  int64_t launches = 0;
+  prad_ctx* owner = nullptr;
+  uint32_t magic = 0x50534551u;  // "PSEQ"
 };
 
 namespace prad {
@@ -78,6 +90,17 @@ inline bool ctx_ok(const prad_ctx* c) { return c != nullptr && c->magic == 0x505
       prad::set_error("%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__,  \
                       __LINE__);                                                         \
       return e_ == cudaErrorMemoryAllocation ? PRAD_ERR_OOM : PRAD_ERR_CUDA;             \
+    }                                                                                    \
+  } while (0)
+
+// entry points that must wait for the device (or move host data) cannot be recorded
+#define PRAD_NOT_CAPTURING(ctx, what)                                                    \
+  do {                                                                                   \
+    if ((ctx)->capturing) {                                                              \
+      prad::set_error("%s cannot be recorded into a launch sequence (it waits for the "  \
+                      "device, moves host data or grows scratch); call it outside "      \
+                      "prad_capture_begin/prad_capture_end", what);                      \
+      return PRAD_ERR_INVALID;                                                           \
     }                                                                                    \
   } while (0)
 

@@ -116,6 +116,7 @@ prad_status prad_dp_unique_id(void* out_id_128_bytes) {
 
 prad_status prad_dp_init(prad_ctx* ctx, const void* id_128_bytes, int rank, int world_size) {
   PRAD_CHECK_CTX(ctx);
+  PRAD_NOT_CAPTURING(ctx, "prad_dp_init");
   PRAD_REQUIRE(id_128_bytes && world_size >= 1 && rank >= 0 && rank < world_size, PRAD_ERR_INVALID,
                "prad_dp_init: bad rank/world size or null id");
   PRAD_REQUIRE(nccl().ok, PRAD_ERR_COMM, "prad_dp_init: %s", nccl().why.c_str());
@@ -137,6 +138,7 @@ prad_status prad_dp_init(prad_ctx* ctx, const void* id_128_bytes, int rank, int 
 
 prad_status prad_dp_allreduce(prad_ctx* ctx, prad_dtype dt, void* buf, int64_t n) {
   PRAD_CHECK_CTX(ctx);
+  PRAD_NOT_CAPTURING(ctx, "prad_dp_allreduce");
   PRAD_REQUIRE(ctx->dp && ctx->dp->comm, PRAD_ERR_NOT_INITIALIZED, "prad_dp_allreduce: call prad_dp_init first");
   PRAD_REQUIRE(dtype_ok(dt) && n >= 0 && (buf || n == 0), PRAD_ERR_INVALID, "prad_dp_allreduce: bad argument");
   if (n == 0) return PRAD_OK;
@@ -151,6 +153,7 @@ prad_status prad_dp_allreduce(prad_ctx* ctx, prad_dtype dt, void* buf, int64_t n
 
 prad_status prad_dp_wait(prad_ctx* ctx) {
   PRAD_CHECK_CTX(ctx);
+  PRAD_NOT_CAPTURING(ctx, "prad_dp_wait");
   PRAD_REQUIRE(ctx->dp && ctx->dp->comm, PRAD_ERR_NOT_INITIALIZED, "prad_dp_wait: call prad_dp_init first");
   DpState* d = ctx->dp;
   if (!d->pending) return PRAD_OK;
@@ -168,6 +171,7 @@ prad_status prad_dp_wait(prad_ctx* ctx) {
 
 prad_status prad_dp_shutdown(prad_ctx* ctx) {
   PRAD_CHECK_CTX(ctx);
+  PRAD_NOT_CAPTURING(ctx, "prad_dp_shutdown");
   return dp_destroy(ctx);
 }
 

@@ -168,6 +168,7 @@ embedding_scatter_ordered_kernel(const T* __restrict__ index_col, const T* __res
 }
 
 static prad_status check_bad_index(prad_ctx* ctx, int* d_bad, const char* who) {
+  PRAD_NOT_CAPTURING(ctx, who);   // the index check reads a flag back
   int h = 0;
   PRAD_CUDA(cudaMemcpyAsync(&h, d_bad, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
   PRAD_CUDA(cudaStreamSynchronize(ctx->stream));

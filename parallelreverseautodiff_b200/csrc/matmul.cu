@@ -203,6 +203,7 @@ prad_status prad_matmul_act_backward_host(prad_ctx* ctx, prad_dtype dt, const vo
   PRAD_CHECK_CTX(ctx);
   PRAD_REQUIRE(dtype_ok(dt), PRAD_ERR_INVALID, "prad_matmul_act_backward_host: bad dtype");
   CHECK_DIMS("prad_matmul_act_backward_host", M, K, N);
+  PRAD_NOT_CAPTURING(ctx, "prad_matmul_act_backward_host");
   PRAD_REQUIRE(A_host && B_host && dOut_host && dPre_host && dA_host && dB_host &&
                    (saved_host || act == PRAD_ACT_NONE),
                PRAD_ERR_INVALID, "prad_matmul_act_backward_host: null pointer");

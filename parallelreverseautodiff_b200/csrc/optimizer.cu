@@ -307,6 +307,7 @@ static prad_status clip_adam_t(prad_ctx* ctx, void* const* w, void* const* g, vo
     PRAD_LAUNCHED(ctx);
   }
   if (norm_out) {
+    PRAD_NOT_CAPTURING(ctx, "a clip call that returns the norm to the host");
     double ss = 0.0;
     PRAD_CUDA(cudaMemcpyAsync(&ss, stats + ST_SS, sizeof(double), cudaMemcpyDeviceToHost, ctx->stream));
     PRAD_CUDA(cudaStreamSynchronize(ctx->stream));

@@ -88,6 +88,25 @@ class DeviceMatrix:
             pass
 
 
+class Sequence:
+    """A recorded launch sequence of one Engine (prad_sequence)."""
+
+    def __init__(self, eng, handle, keep=()):
+        self.eng, self.handle, self._keep = eng, handle, list(keep)
+        n = C.c_int64()
+        check(eng.lib.prad_sequence_launch_count(handle, C.byref(n)))
+        self.launches = n.value
+
+    def launch(self) -> None:
+        check(self.eng.lib.prad_sequence_launch(self.eng.ctx, self.handle))
+
+    def close(self) -> None:
+        if self.handle is not None:
+            check(self.eng.lib.prad_sequence_destroy(self.eng.ctx, self.handle))
+            self.handle = None
+            self._keep = []
+
+
 class Engine:
     """One libprad_cuda context on one GPU (CudaBlas.Instance of the reference, per device)."""
 
@@ -121,6 +140,29 @@ class Engine:
         check(self.lib.prad_launch_count(self.ctx, C.byref(n)))
         return n.value
 
+    def record(self, fn) -> "Sequence":
+        """Runs `fn()` with the context recording (prad_capture_begin/end): its launches are not
+        executed but kept as a sequence that `Sequence.launch()` replays in one submission.  Run
+        `fn()` once unrecorded first so that library scratch has its final size."""
+        check(self.lib.prad_capture_begin(self.ctx))
+        self._record_keep = keep = []
+        self._deferred_free = []
+        try:
+            fn()
+        except BaseException:
+            self._record_keep = None
+            h = C.c_void_p()
+            self.lib.prad_capture_end(self.ctx, C.byref(h))      # close the recording; drop the result
+            if h.value:
+                self.lib.prad_sequence_destroy(self.ctx, h)
+            self._flush_deferred_free()
+            raise
+        self._record_keep = None
+        h = C.c_void_p()
+        check(self.lib.prad_capture_end(self.ctx, C.byref(h)))
+        self._flush_deferred_free()
+        return Sequence(self, h, keep)
+
     def stream(self) -> int:
         s = C.c_void_p()
         check(self.lib.prad_stream(self.ctx, C.byref(s)))
@@ -139,7 +181,11 @@ class Engine:
             n *= int(s)
         p = C.c_void_p()
         check(self.lib.prad_alloc(self.ctx, n * dtype.itemsize, C.byref(p)))
-        return DeviceMatrix(self, p.value, shape, dtype)
+        m = DeviceMatrix(self, p.value, shape, dtype)
+        keep = getattr(self, "_record_keep", None)
+        if keep is not None:       # a buffer born inside a recording lives as long as the sequence
+            keep.append(m)
+        return m
 
     def zeros(self, shape, dtype) -> DeviceMatrix:
         m = self.empty(shape, dtype)
@@ -150,7 +196,15 @@ class Engine:
         check(self.lib.prad_zero(self.ctx, m.ptr, m.nbytes))
 
     def _free(self, ptr: int) -> None:
+        if getattr(self, "_record_keep", None) is not None:    # prad_free cannot be recorded: do it afterwards
+            self._deferred_free.append(ptr)
+            return
         check(self.lib.prad_free(self.ctx, C.c_void_p(ptr)))
+
+    def _flush_deferred_free(self) -> None:
+        pending, self._deferred_free = self._deferred_free, []
+        for ptr in pending:
+            check(self.lib.prad_free(self.ctx, C.c_void_p(ptr)))
 
     def upload(self, a: np.ndarray, out: Optional[DeviceMatrix] = None) -> DeviceMatrix:
         a = np.ascontiguousarray(a)

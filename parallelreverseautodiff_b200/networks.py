@@ -265,16 +265,23 @@ class LstmNetwork:
         self.n_in, self.n_h, self.T, self.B = n_in, n_hidden, steps, batch
         e, dt = eng, self.dtype
         z = lambda *s: e.zeros(s, dt)  # noqa: E731
-        self.W = {g: z(n_hidden, n_in) for g in self.GATES}       # [hidden x in], as in the reference
-        self.U = {g: z(n_hidden, n_hidden) for g in self.GATES}
-        self.b = {g: z(1, n_hidden) for g in self.GATES}
-        self.dW = {g: z(n_hidden, n_in) for g in self.GATES}
-        self.dU = {g: z(n_hidden, n_hidden) for g in self.GATES}
-        self.db = {g: z(1, n_hidden) for g in self.GATES}
         TB = steps * batch
+        G = len(self.GATES)
+
+        def stacked(rows, cols):
+            """The four gates' matrices in one allocation, so that one strided-batched product serves all."""
+            whole = z(G * rows, cols)
+            return whole, {g: whole.view((rows, cols), k * rows * cols) for k, g in enumerate(self.GATES)}
+
+        self._W_all, self.W = stacked(n_hidden, n_in)             # [hidden x in], as in the reference
+        self._U_all, self.U = stacked(n_hidden, n_hidden)
+        self.b = {g: z(1, n_hidden) for g in self.GATES}
+        self._dW_all, self.dW = stacked(n_hidden, n_in)
+        self._dU_all, self.dU = stacked(n_hidden, n_hidden)
+        self.db = {g: z(1, n_hidden) for g in self.GATES}
         self.X = z(TB, n_in)
         self.Y = z(TB, n_hidden)                                  # targets
-        self.pre = {g: z(TB, n_hidden) for g in self.GATES}      # gate pre-activations
+        self._pre_all, self.pre = stacked(TB, n_hidden)           # gate pre-activations
         self.gate = {g: z(TB, n_hidden) for g in self.GATES}     # gate outputs
         self.C = z(TB, n_hidden)
         self.tanhC = z(TB, n_hidden)
@@ -282,9 +289,12 @@ class LstmNetwork:
         self.Hprev = z(TB, n_hidden)                              # H shifted by one step (h_{-1} = 0)
         self.FC = z(TB, n_hidden)                                 # f (.) c_{t-1}
         self.IG = z(TB, n_hidden)                                 # i (.) g
-        self.dpre = {g: z(TB, n_hidden) for g in self.GATES}
+        self._dpre_all, self.dpre = stacked(TB, n_hidden)
         self.dX = z(TB, n_in)
         self._tmp = [z(batch, n_hidden) for _ in range(18)]
+        self._rec_all, rec = stacked(batch, n_hidden)             # dZ_g(t) U_g for the four gates
+        for k, g in enumerate(self.GATES):
+            self._tmp[8 + k] = rec[g]
 
     def set_parameters(self, W, U, b):
         for g in self.GATES:
@@ -301,15 +311,19 @@ class LstmNetwork:
         e.upload(np.ascontiguousarray(x_host, self.dtype).reshape(T * B, -1), out=self.X)
         e.upload(np.ascontiguousarray(y_host, self.dtype).reshape(T * B, -1), out=self.Y)
         e.zero_(self.Hprev)
-        for g in self.GATES:    # input contribution of all steps: X_all * W_g^T
-            e.gemm(self.X, self.W[g], self.pre[g], transB=True)
+        nh, n_in, TB, G = self.n_h, self.n_in, T * B, len(self.GATES)
+        first = self.GATES[0]
+        # input contribution of all steps and gates: X_all * W_g^T, one strided-batched product
+        e.gemm(self.X, self.W[first], self.pre[first], transB=True, batch=G, strideA=0, strideB=nh * n_in,
+               strideC=TB * nh)
         acts = {"i": E.ACT_SIGMOID, "f": E.ACT_SIGMOID, "g": E.ACT_TANH, "o": E.ACT_SIGMOID}
         for t in range(T):
             hp = self._step(self.Hprev, t)
+            if t > 0:           # + h_{t-1} * U_g^T for the four gates (MatrixAddThree: (Wx + Uh) + b)
+                e.gemm(hp, self.U[first], self._step(self.pre[first], t), transB=True, beta=1.0, batch=G,
+                       strideA=0, strideB=nh * nh, strideC=TB * nh)
             for g in self.GATES:
                 p = self._step(self.pre[g], t)
-                if t > 0:       # + h_{t-1} * U_g^T (MatrixAddThree: (Wx + Uh) + b)
-                    e.gemm(hp, self.U[g], p, transB=True, beta=1.0)
                 e.add_broadcast_forward(p, self.b[g], out=p)
                 e.act_forward(acts[g], p, out=self._step(self.gate[g], t))
             c, fc, ig = self._step(self.C, t), self._step(self.FC, t), self._step(self.IG, t)
@@ -368,17 +382,20 @@ class LstmNetwork:
             e.act_backward(E.ACT_TANH, g_, d_g, out=self._step(self.dpre["g"], t))
             e.act_backward(E.ACT_SIGMOID, o, d_o, out=self._step(self.dpre["o"], t))
             if t > 0:           # gradient w.r.t. h_{t-1}: one product per gate, summed above
-                dh_rec = []
-                for k, g in enumerate(self.GATES):
-                    buf = tmp[8 + k]
-                    e.gemm(self._step(self.dpre[g], t), self.U[g], buf)
-                    dh_rec.append(buf)
+                g0 = self.GATES[0]
+                e.gemm(self._step(self.dpre[g0], t), self.U[g0], tmp[8], batch=len(self.GATES),
+                       strideA=T * B * nh, strideB=nh * nh, strideC=B * nh)
+                dh_rec = [tmp[8 + k] for k in range(len(self.GATES))]
         inv_b = 1.0 / B
         first = True
+        g0, G, TB = self.GATES[0], len(self.GATES), T * B
+        # dW_g = (1/B) * dZ_all^T X_all ; dU_g = (1/B) * dZ_all^T Hprev_all : the four gates per launch
+        e.gemm(self.dpre[g0], self.X, self.dW[g0], transA=True, alpha=inv_b, batch=G, strideA=TB * nh, strideB=0,
+               strideC=nh * self.n_in)
+        e.gemm(self.dpre[g0], self.Hprev, self.dU[g0], transA=True, alpha=inv_b, batch=G, strideA=TB * nh,
+               strideB=0, strideC=nh * nh)
         for g in self.GATES:
-            # dW_g = (1/B) * dZ_all^T X_all ; dU_g = (1/B) * dZ_all^T Hprev_all ; db_g = (1/B) colsum
-            e.gemm(self.dpre[g], self.X, self.dW[g], transA=True, alpha=inv_b)
-            e.gemm(self.dpre[g], self.Hprev, self.dU[g], transA=True, alpha=inv_b)
+            # db_g = (1/B) colsum
             e.add_broadcast_backward(self.dpre[g], dbias=self.db[g])
             e.scale(self.db[g], inv_b, out=self.db[g])
             # dX_all = sum over gates of dZ_g W_g (left fold in gate order)
