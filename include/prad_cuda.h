@@ -78,7 +78,12 @@ const char* prad_version(void);
  *    simt_fma : same order with fused multiply-add (twice the rate, one rounding per step);
  *    fp16x3   : tcgen05 kernel; every row of a K-major operand is scaled by a power of two and
  *               split into two FP16 pieces (22 significant bits); three FP16 products per term
- *               (h1*h0' + h0*h1' + h0*h0'); what "auto" uses for large products;
+ *               (h1*h0' + h0*h1' + h0*h0'); what "auto" uses for large products.  Error of an
+ *               output element: 2^-22 * sum_k |a_ik b_kj| like the TF32 pair, plus at most
+ *               sqrt(K) * 2^-39 * max_k|a_ik| * max_k|b_kj|: an element more than ~8 decades
+ *               below the largest of its row along k keeps fewer than 22 bits.  Irrelevant
+ *               for activations and gradients; a caller whose products pair a huge factor
+ *               with a tiny one at the same k should use "tf32b16";
  *    tf32b16  : tcgen05 kernel, one TF32 product + two BF16 correction products;
  *    tf32x3   : tcgen05 kernel, three TF32 products per term (a_hi*b_hi + a_lo*b_hi + a_hi*b_lo);
  *    bf16x3   : tcgen05 kernel, six BF16 products of three-piece operands;

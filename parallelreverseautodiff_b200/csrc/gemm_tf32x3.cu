@@ -899,8 +899,11 @@ split_transpose_kernel(const float* __restrict__ src, int64_t src_ld, float* __r
 __device__ __forceinline__ int shift_of(uint32_t absbits) {
   const int e = (int)((absbits >> 23) & 0xffu);
   if (e == 0 || e == 255) return 0;            // all zero / denormal, or Inf / NaN present: unscaled
+  // 14 - (e - 127) lies in [-113, 140]; the upper clamp keeps 2^s, 2^-s and the halves of the sum
+  // of two such exponents inside the normal float range (it only costs rows whose largest
+  // magnitude is below 2^-112 a few of their 22 bits)
   const int s = 14 - (e - 127);
-  return s < -100 ? -100 : (s > 100 ? 100 : s);
+  return s > 126 ? 126 : s;
 }
 __device__ __forceinline__ void fp16_pieces(float xs, __half& p0, __half& p1) {
   p0 = __float2half_rn(xs);

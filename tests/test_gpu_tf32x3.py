@@ -93,25 +93,44 @@ def test_tf32x3_deterministic(tc_engine):
     np.testing.assert_array_equal(eng.matmul_forward(a, b).numpy(), eng.matmul_forward(a, b).numpy())
 
 
+def _fp16x3_bound(P, Q):
+    """Error scale of P @ Q under the FP16 scheme: the usual sum |p||q| of a float product plus
+    what the narrow FP16 exponent adds -- an element more than ~8 decades below the largest of
+    its row (along k) keeps fewer than 22 bits, at worst an absolute 2^-39 of that largest
+    magnitude; times the other operand's largest magnitude and sqrt(k) for the sum.  (The 1e-5
+    of the float tolerance is applied on top, hence 2^-39 / 1e-5 ~ 2e-7.)"""
+    P, Q = np.abs(P).astype(np.float64), np.abs(Q).astype(np.float64)
+    return P @ Q + 2e-7 * np.sqrt(P.shape[1]) * np.outer(P.max(axis=1), Q.max(axis=0))
+
+
 @pytest.mark.parametrize("shape", [(256, 512, 256), (130, 333, 257)])
 def test_fp16x3_row_scaling_over_the_float_range(engine, shape):
     """Rows of A and columns of B spread over 40 decades: the power-of-two row scaling keeps
-    every output element at FP32 accuracy relative to its own |A||B| bound."""
+    every output element at FP32 accuracy relative to its own |A||B| bound, up to the stated
+    range term where one k carries a huge factor in one operand and a tiny one in the other."""
     engine.set_option("gemm_f32", "fp16x3")
     try:
         M, K, N = shape
         r = rng(11)
         A = (normal(r, (M, K), 1, np.float64) * 10.0 ** r.uniform(-12, 12, (M, 1))).astype(np.float32)
+        A[5] = normal(r, (K,), 1, np.float64) * 1e29      # a row near the top of the float range ...
+        A[6] = normal(r, (K,), 1, np.float64) * 1e-28     # ... and one near the bottom (products stay normal floats)
         B = (normal(r, (K, N), 1, np.float64) * 10.0 ** r.uniform(-7, 7, (1, N))).astype(np.float32)
         A[3] = 0                     # an all-zero row stays zero
         dC = (normal(r, (M, N), 1, np.float64) * 10.0 ** r.uniform(-5, 5, (M, 1))).astype(np.float32)
         a, b, dc = engine.upload(A), engine.upload(B), engine.upload(dC)
         C = engine.matmul_forward(a, b).numpy()
         assert not C[3].any()
+        # forward: the spread is across rows of A and columns of B only, never along k
         assert_close(C, O.matmul_forward(A, B), np.abs(A).astype(np.float64) @ np.abs(B), "C")
         dA, dB = engine.matmul_backward(a, b, dc)
         dA_ref, dB_ref = O.matmul_backward(A, B, dC)
-        assert_close(dA.numpy(), dA_ref, np.abs(dC).astype(np.float64) @ np.abs(B.T), "dA")
-        assert_close(dB.numpy(), dB_ref, np.abs(A.T).astype(np.float64) @ np.abs(dC), "dB")
+        assert_close(dA.numpy(), dA_ref, _fp16x3_bound(dC, B.T), "dA")
+        assert_close(dB.numpy(), dB_ref, _fp16x3_bound(A.T, dC), "dB")
+        # the TF32 + BF16 scheme has the full float exponent in every piece: plain bound
+        engine.set_option("gemm_f32", "tf32b16")
+        dA, dB = engine.matmul_backward(a, b, dc)
+        assert_close(dA.numpy(), dA_ref, np.abs(dC).astype(np.float64) @ np.abs(B.T), "dA (tf32b16)")
+        assert_close(dB.numpy(), dB_ref, np.abs(A.T).astype(np.float64) @ np.abs(dC), "dB (tf32b16)")
     finally:
         engine.set_option("gemm_f32", "auto")
