@@ -1255,6 +1255,32 @@ prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, do
     return PRAD_ERR_UNSUPPORTED;
   }
   if (probe_only) return PRAD_OK;
+  // Activation epilogues run as a separate streaming pass.  Measured on the 65536 x 4096 x 4096
+  // products: the epilogue warps hold the whole 128-column row slice in registers, so the
+  // activation's loads and transcendental chains run with next to no latency hiding and stall
+  // the tensor pipe behind them -- 9.1 ms with GELU and the pre-activation copy fused, 7.6 ms
+  // with the GELU derivative fused, against 5.0 ms plain plus 0.4 - 0.5 ms for the HBM-bound
+  // elementwise kernel.  (Strided outputs, or beta with a forward activation, stay fused.)
+  const bool has_act = e.act != PRAD_ACT_NONE, has_dact = e.dact != PRAD_ACT_NONE;
+  if ((has_act != has_dact) && ldc == N && ctx->tc_unfuse_act && !(has_act && beta != 0.0)) {
+    GemmEpilogue plain = e;
+    plain.act = PRAD_ACT_NONE;
+    plain.dact = PRAD_ACT_NONE;
+    plain.saved = nullptr;
+    const int64_t n = (int64_t)M * N;
+    if (has_act) {
+      void* pre = e.z_out ? e.z_out : C;   // the pre-activation lands where the caller keeps it
+      plain.z_out = nullptr;
+      prad_status st = gemm_tf32x3(ctx, tA, tB, M, N, K, alpha, A, lda, B, ldb, beta, pre, ldc, batch, sA, sB, sC,
+                                   plain, false);
+      if (st) return st;
+      return prad_act_forward(ctx, PRAD_F32, e.act, pre, C, n, e.act_alpha);
+    }
+    prad_status st = gemm_tf32x3(ctx, tA, tB, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, batch, sA, sB, sC, plain,
+                                 false);
+    if (st) return st;
+    return prad_act_backward(ctx, PRAD_F32, e.dact, e.saved, C, C, n, e.act_alpha);
+  }
   const int mode = ctx->gemm_f32 == GemmF32::Tf32x3 ? 0
                    : ctx->gemm_f32 == GemmF32::Tf32B16 ? 1
                    : ctx->gemm_f32 == GemmF32::Bf16x3 ? 2
