@@ -54,7 +54,9 @@ typedef enum {
   PRAD_ACT_LEAKY_RELU = 1, /* LeakyReLUOperation: backward reads the INPUT x           */
   PRAD_ACT_SIGMOID = 2,    /* SigmoidOperation:   backward reads the OUTPUT y          */
   PRAD_ACT_TANH = 3,       /* TanhOperation:      backward reads the OUTPUT y          */
-  PRAD_ACT_GELU = 4        /* GELUOperation:      backward reads the INPUT x           */
+  PRAD_ACT_GELU = 4,       /* GELUOperation:      backward reads the INPUT x           */
+  PRAD_ACT_RELU = 5,       /* ReLUOperation (src/RMAD/ReLUOperation.cs:38-78): reads the INPUT x */
+  PRAD_ACT_AMPLIFIED_SIGMOID = 6 /* AmplifiedSigmoidOperation.cs:45-83: reads the INPUT x      */
 } prad_act;
 
 typedef enum { PRAD_ADAM_RMAD = 0, PRAD_ADAM_PRAD = 1 } prad_adam_form;
@@ -269,6 +271,21 @@ prad_status prad_layernorm_forward(prad_ctx* ctx, prad_dtype dt, const void* x, 
 prad_status prad_layernorm_backward(prad_ctx* ctx, prad_dtype dt, const void* x,
                                     const void* mean, const void* stdv, const void* dy, void* dx,
                                     int64_t rows, int cols);
+/* ScaleAndShiftOperation.cs:55-106: y[i][j] = x[i][j] * beta[i] + gamma[i] with one beta and
+ * one gamma per ROW (the op's [rows x 1] matrices, passed as `rows` contiguous values).
+ * Backward: dx = dy * beta[i]; dbeta[i] = sum_j dy*x; dgamma[i] = sum_j dy. */
+prad_status prad_scale_shift_forward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* beta,
+                                     const void* gamma, void* y, int64_t rows, int cols);
+prad_status prad_scale_shift_backward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* beta,
+                                      const void* dy, void* dx, void* dbeta, void* dgamma,
+                                      int64_t rows, int cols);
+/* RMSNormOperation.cs:47-118: rms = sqrt(sum_j x^2 / cols) per row, y = (x / rms) * g with g
+ * [rows x cols]; the backward is the diagonal form written there,
+ * dx = dy * (g/rms - x*g*x / (cols * rms^3)), dg = dy * x / rms. */
+prad_status prad_rmsnorm_forward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* g, void* y,
+                                 int64_t rows, int cols);
+prad_status prad_rmsnorm_backward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* g,
+                                  const void* dy, void* dx, void* dg, int64_t rows, int cols);
 
 /* ---------------------------------------------------------------- losses
  * Loss/MeanSquaredErrorLossOperation.cs:37-84 and

@@ -176,6 +176,58 @@ def tanh_backward(y, dy):
     return _binary_bwd("tanh_backward", y, dy)
 
 
+def relu_forward(x):
+    return _unary("relu_forward", x)
+
+
+def relu_backward(x, dy):
+    return _binary_bwd("relu_backward", x, dy)
+
+
+def amplified_sigmoid_forward(x):
+    return _unary("amplified_sigmoid_forward", x)
+
+
+def amplified_sigmoid_backward(x, dy):
+    return _binary_bwd("amplified_sigmoid_backward", x, dy)
+
+
+def scale_shift_forward(x, beta, gamma):
+    """beta, gamma: one value per row (ScaleAndShiftOperation's [rows x 1] matrices)."""
+    x = _c(x)
+    beta, gamma = _c(np.reshape(beta, -1), x.dtype), _c(np.reshape(gamma, -1), x.dtype)
+    y = np.empty_like(x)
+    _fn("scale_shift_forward", x.dtype)(_p(x), _p(beta), _p(gamma), _p(y), x.shape[0], x.shape[1])
+    return y
+
+
+def scale_shift_backward(x, beta, dy):
+    """Returns (dx, dbeta[rows], dgamma[rows])."""
+    x = _c(x)
+    beta, dy = _c(np.reshape(beta, -1), x.dtype), _c(dy, x.dtype)
+    dx = np.empty_like(x)
+    db, dg = np.empty(x.shape[0], x.dtype), np.empty(x.shape[0], x.dtype)
+    _fn("scale_shift_backward", x.dtype)(_p(x), _p(beta), _p(dy), _p(dx), _p(db), _p(dg), x.shape[0], x.shape[1])
+    return dx, db, dg
+
+
+def rmsnorm_forward(x, g):
+    x = _c(x)
+    g = _c(g, x.dtype)
+    y = np.empty_like(x)
+    _fn("rmsnorm_forward", x.dtype)(_p(x), _p(g), _p(y), x.shape[0], x.shape[1])
+    return y
+
+
+def rmsnorm_backward(x, g, dy):
+    """Returns (dx, dg)."""
+    x = _c(x)
+    g, dy = _c(g, x.dtype), _c(dy, x.dtype)
+    dx, dg = np.empty_like(x), np.empty_like(x)
+    _fn("rmsnorm_backward", x.dtype)(_p(x), _p(g), _p(dy), _p(dx), _p(dg), x.shape[0], x.shape[1])
+    return dx, dg
+
+
 def gelu_forward(x):
     return _unary("gelu_forward", x)
 

@@ -253,6 +253,79 @@ void gelu_backward(const T* x, const T* dy, T* dx, size_t n) {
   for (long long i = 0; i < (long long)n; ++i) dx[i] = dy[i] * gelu_der(x[i]);
 }
 
+// ---- ReLUOperation.cs:38-78 -----------------------------------------------------------------
+template <typename T>
+void relu_forward(const T* x, T* y, size_t n) {
+  for (size_t i = 0; i < n; ++i) y[i] = x[i] > 0 ? x[i] : (T)0;
+}
+template <typename T>
+void relu_backward(const T* x, const T* dy, T* dx, size_t n) {
+  for (size_t i = 0; i < n; ++i) dx[i] = dy[i] * (x[i] > 0 ? (T)1 : (T)0);
+}
+
+// ---- AmplifiedSigmoidOperation.cs:45-83 -------------------------------------------------------
+// y = 1 / (1 + Pow(PI - 2, -x)) with PradMath.PI = (float)Math.PI in both precisions; the
+// derivative is the one written there, b^-x / (1 + b^-x)^2 (no ln b factor).
+template <typename T> inline T amp_base() { return (T)((float)M_PI) - (T)2; }
+template <typename T>
+void amplified_sigmoid_forward(const T* x, T* y, size_t n) {
+  for (size_t i = 0; i < n; ++i) y[i] = (T)1 / ((T)1 + p_pow<T>(amp_base<T>(), -x[i]));
+}
+template <typename T>
+void amplified_sigmoid_backward(const T* x, const T* dy, T* dx, size_t n) {
+  for (size_t i = 0; i < n; ++i) {
+    T d = p_pow<T>(amp_base<T>(), -x[i]) / p_pow<T>((T)1 + p_pow<T>(amp_base<T>(), -x[i]), (T)2);
+    dx[i] = dy[i] * d;
+  }
+}
+
+// ---- ScaleAndShiftOperation.cs:55-106: per-row beta and gamma ([rows x 1]) ----------------------
+template <typename T>
+void scale_shift_forward(const T* x, const T* beta, const T* gamma, T* y, int R, int C) {
+  for (int i = 0; i < R; ++i)
+    for (int j = 0; j < C; ++j) y[(size_t)i * C + j] = (x[(size_t)i * C + j] * beta[i]) + gamma[i];
+}
+template <typename T>
+void scale_shift_backward(const T* x, const T* beta, const T* dy, T* dx, T* dbeta, T* dgamma, int R, int C) {
+  for (int i = 0; i < R; ++i) {
+    T gb = 0, gg = 0;
+    for (int j = 0; j < C; ++j) {
+      const size_t k = (size_t)i * C + j;
+      dx[k] = dy[k] * beta[i];
+      gb += dy[k] * x[k];
+      gg += dy[k];
+    }
+    dbeta[i] = gb;
+    dgamma[i] = gg;
+  }
+}
+
+// ---- RMSNormOperation.cs:47-118: g is [rows x cols]; the backward is the diagonal form written there
+template <typename T>
+void rmsnorm_forward(const T* x, const T* g, T* y, int R, int C) {
+  for (int i = 0; i < R; ++i) {
+    T ss = 0;
+    for (int j = 0; j < C; ++j) ss += p_pow<T>(x[(size_t)i * C + j], (T)2);
+    const T rms = p_sqrt<T>(ss / C);
+    for (int j = 0; j < C; ++j) y[(size_t)i * C + j] = (x[(size_t)i * C + j] / rms) * g[(size_t)i * C + j];
+  }
+}
+template <typename T>
+void rmsnorm_backward(const T* x, const T* g, const T* dy, T* dx, T* dg, int R, int C) {
+  for (int i = 0; i < R; ++i) {
+    T ss = 0;
+    for (int j = 0; j < C; ++j) ss += p_pow<T>(x[(size_t)i * C + j], (T)2);
+    const T rms = p_sqrt<T>(ss / C);
+    for (int j = 0; j < C; ++j) {
+      const size_t k = (size_t)i * C + j;
+      T a = (g[k] / rms) - ((x[k] * g[k] * x[k]) / (C * p_pow<T>(rms, (T)3)));
+      T b = x[k] / rms;
+      dx[k] = a * dy[k];
+      dg[k] = b * dy[k];
+    }
+  }
+}
+
 // ---- HadamardProductOperation.cs:50-118 ---------------------------------------------------
 template <typename T>
 void hadamard_forward(const T* a, const T* b, T* y, size_t n) {
@@ -628,6 +701,30 @@ void adam_prad(T* w, T* m, T* v, const T* g, size_t n, T lr, T b1, T b2, T eps, 
   void oracle_tanh_forward_##S(const T* x, T* y, long long n) { tanh_forward<T>(x, y, (size_t)n); }\
   void oracle_tanh_backward_##S(const T* y, const T* dy, T* dx, long long n) {                     \
     tanh_backward<T>(y, dy, dx, (size_t)n);                                                        \
+  }                                                                                                \
+  void oracle_relu_forward_##S(const T* x, T* y, long long n) { relu_forward<T>(x, y, (size_t)n); }\
+  void oracle_relu_backward_##S(const T* x, const T* dy, T* dx, long long n) {                     \
+    relu_backward<T>(x, dy, dx, (size_t)n);                                                        \
+  }                                                                                                \
+  void oracle_amplified_sigmoid_forward_##S(const T* x, T* y, long long n) {                       \
+    amplified_sigmoid_forward<T>(x, y, (size_t)n);                                                 \
+  }                                                                                                \
+  void oracle_amplified_sigmoid_backward_##S(const T* x, const T* dy, T* dx, long long n) {        \
+    amplified_sigmoid_backward<T>(x, dy, dx, (size_t)n);                                           \
+  }                                                                                                \
+  void oracle_scale_shift_forward_##S(const T* x, const T* b, const T* g, T* y, int R, int C) {    \
+    scale_shift_forward<T>(x, b, g, y, R, C);                                                      \
+  }                                                                                                \
+  void oracle_scale_shift_backward_##S(const T* x, const T* b, const T* dy, T* dx, T* db, T* dg,   \
+                                       int R, int C) {                                             \
+    scale_shift_backward<T>(x, b, dy, dx, db, dg, R, C);                                           \
+  }                                                                                                \
+  void oracle_rmsnorm_forward_##S(const T* x, const T* g, T* y, int R, int C) {                    \
+    rmsnorm_forward<T>(x, g, y, R, C);                                                             \
+  }                                                                                                \
+  void oracle_rmsnorm_backward_##S(const T* x, const T* g, const T* dy, T* dx, T* dg, int R,       \
+                                   int C) {                                                        \
+    rmsnorm_backward<T>(x, g, dy, dx, dg, R, C);                                                   \
   }                                                                                                \
   void oracle_gelu_forward_##S(const T* x, T* y, long long n) { gelu_forward<T>(x, y, (size_t)n); }\
   void oracle_gelu_backward_##S(const T* x, const T* dy, T* dx, long long n) {                     \

@@ -67,6 +67,10 @@ SIGNATURES = {
     "prad_softmax_backward": [vp, i32, vp, vp, vp, i64, i32],
     "prad_layernorm_forward": [vp, i32, vp, vp, vp, vp, i64, i32],
     "prad_layernorm_backward": [vp, i32, vp, vp, vp, vp, vp, i64, i32],
+    "prad_scale_shift_forward": [vp, i32, vp, vp, vp, vp, i64, i32],
+    "prad_scale_shift_backward": [vp, i32, vp, vp, vp, vp, vp, vp, i64, i32],
+    "prad_rmsnorm_forward": [vp, i32, vp, vp, vp, i64, i32],
+    "prad_rmsnorm_backward": [vp, i32, vp, vp, vp, vp, vp, i64, i32],
     "prad_mse_forward": [vp, i32, vp, vp, vp, i64, i32],
     "prad_mse_backward": [vp, i32, vp, vp, vp, i64, i32, i64],
     "prad_cce_forward": [vp, i32, vp, vp, vp, i64, i32],

@@ -63,6 +63,21 @@ template <typename T> __device__ __forceinline__ T gelu_derivative(T x) {
   return add_rn(mul_rn(t0, t1), t2);
 }
 
+__device__ __forceinline__ float t_pow(float x, float y) { return (float)pow((double)x, (double)y); }
+__device__ __forceinline__ double t_pow(double x, double y) { return pow(x, y); }
+
+// AmplifiedSigmoidOperation.cs:45-83.  PradMath.PI is (float)Math.PI in both precisions, so the
+// base PI - 2 is 1.1415927410125732 either way; Pow goes through double and is cast back.
+template <typename T> __device__ __forceinline__ T amp_base() { return (T)1.1415927410125732; }
+template <typename T> __device__ __forceinline__ T amplified_sigmoid_value(T x) {
+  return div_rn((T)1, add_rn((T)1, t_pow(amp_base<T>(), -x)));
+}
+// as written there: b^-x / (1 + b^-x)^2 (no ln b factor)
+template <typename T> __device__ __forceinline__ T amplified_sigmoid_derivative(T x) {
+  const T p = t_pow(amp_base<T>(), -x);
+  return div_rn(p, t_pow(add_rn((T)1, p), (T)2));
+}
+
 // forward value of an activation
 template <typename T> __device__ __forceinline__ T act_value(prad_act act, T x, T alpha) {
   switch (act) {
@@ -70,6 +85,8 @@ template <typename T> __device__ __forceinline__ T act_value(prad_act act, T x, 
     case PRAD_ACT_SIGMOID: return div_rn((T)1, add_rn((T)1, t_exp(-x)));     // SigmoidOperation.cs:57
     case PRAD_ACT_TANH: return t_tanh(x);                                    // TanhOperation.cs:52
     case PRAD_ACT_GELU: return gelu_value<T>(x);
+    case PRAD_ACT_RELU: return x > (T)0 ? x : (T)0;                          // ReLUOperation.cs:50-51
+    case PRAD_ACT_AMPLIFIED_SIGMOID: return amplified_sigmoid_value<T>(x);
     default: return x;
   }
 }
@@ -81,6 +98,8 @@ template <typename T> __device__ __forceinline__ T act_derivative(prad_act act, 
     case PRAD_ACT_SIGMOID: return mul_rn(s, sub_rn((T)1, s));                // SigmoidOperation.cs:75
     case PRAD_ACT_TANH: return sub_rn((T)1, mul_rn(s, s));                   // TanhOperation.cs:70
     case PRAD_ACT_GELU: return gelu_derivative<T>(s);
+    case PRAD_ACT_RELU: return s > (T)0 ? (T)1 : (T)0;                       // ReLUOperation.cs:69-70
+    case PRAD_ACT_AMPLIFIED_SIGMOID: return amplified_sigmoid_derivative<T>(s);
     default: return (T)1;
   }
 }

@@ -143,9 +143,9 @@ static prad_status act_backward_t(prad_ctx* ctx, prad_act act, const void* saved
 }
 
 // ---------------------------------------------------------------- add-broadcast
+// (x and y may be the same buffer: no __restrict__ on them)
 template <typename T>
-__global__ void add_broadcast_kernel(const T* __restrict__ x, const T* __restrict__ bias,
-                                     T* __restrict__ y, int64_t n, int cols) {
+__global__ void add_broadcast_kernel(const T* x, const T* __restrict__ bias, T* y, int64_t n, int cols) {
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
     y[i] = add_rn(x[i], bias[i % cols]);
@@ -416,7 +416,7 @@ extern "C" {
 prad_status prad_act_forward(prad_ctx* ctx, prad_dtype dt, prad_act act, const void* x, void* y,
                              int64_t n, double act_alpha) {
   PRAD_CHECK_CTX(ctx);
-  PRAD_REQUIRE(dtype_ok(dt) && act >= PRAD_ACT_NONE && act <= PRAD_ACT_GELU, PRAD_ERR_INVALID,
+  PRAD_REQUIRE(dtype_ok(dt) && act >= PRAD_ACT_NONE && act <= PRAD_ACT_AMPLIFIED_SIGMOID, PRAD_ERR_INVALID,
                "prad_act_forward: bad dtype or activation");
   PRAD_REQUIRE(n >= 0 && (n == 0 || (x && y)), PRAD_ERR_INVALID, "prad_act_forward: null pointer or negative size");
   return DISPATCH_DT(dt, act_forward_t<float>(ctx, act, x, y, n, act_alpha),
@@ -426,7 +426,7 @@ prad_status prad_act_forward(prad_ctx* ctx, prad_dtype dt, prad_act act, const v
 prad_status prad_act_backward(prad_ctx* ctx, prad_dtype dt, prad_act act, const void* saved,
                               const void* dy, void* dx, int64_t n, double act_alpha) {
   PRAD_CHECK_CTX(ctx);
-  PRAD_REQUIRE(dtype_ok(dt) && act >= PRAD_ACT_NONE && act <= PRAD_ACT_GELU, PRAD_ERR_INVALID,
+  PRAD_REQUIRE(dtype_ok(dt) && act >= PRAD_ACT_NONE && act <= PRAD_ACT_AMPLIFIED_SIGMOID, PRAD_ERR_INVALID,
                "prad_act_backward: bad dtype or activation");
   PRAD_REQUIRE(n >= 0 && (n == 0 || (saved && dy && dx)), PRAD_ERR_INVALID,
                "prad_act_backward: null pointer or negative size");

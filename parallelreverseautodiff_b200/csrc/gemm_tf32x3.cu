@@ -146,13 +146,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
       : "r"(taddr) : "memory");
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-      : "r"(taddr) : "memory");
-}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor of a K-major tile stored as rows of SW bytes (SW = 128, 64
@@ -752,13 +745,12 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + buf * (uint32_t)BN + (uint32_t)(half * 128);
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {    // 16 columns per load: with 32 the register file spills in this loop
-          uint32_t v[16];
-          tmem_ld16(taddr + (uint32_t)(g * 16), v);
+        for (int g = 0; g < 4; ++g) {
+          uint32_t v[32];
+          tmem_ld32(taddr + (uint32_t)(g * 32), v);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            sum[g >> 1][(g & 1) * 16 + j] = __fadd_rn(sum[g >> 1][(g & 1) * 16 + j], __uint_as_float(v[j]));
+          for (int j = 0; j < 32; ++j) sum[g][j] = __fadd_rn(sum[g][j], __uint_as_float(v[j]));
         }
         tc_fence_before();
         __syncwarp();

@@ -123,6 +123,81 @@ layernorm_backward_kernel(const T* __restrict__ x, const T* __restrict__ mean,
   }
 }
 
+// ScaleAndShiftOperation.cs:60-73 / :84-98.  One warp per row; the two row sums accumulate in
+// double and are cast back (the managed loop adds in T, left to right).
+template <typename T>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+scale_shift_forward_kernel(const T* __restrict__ x, const T* __restrict__ beta, const T* __restrict__ gamma,
+                           T* __restrict__ y, int64_t rows, int cols) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * ROW_WARPS;
+  for (int64_t r = warp; r < rows; r += nwarps) {
+    const T b = beta[r], g = gamma[r];
+    for (int j = lane; j < cols; j += 32) y[r * cols + j] = add_rn(mul_rn(x[r * cols + j], b), g);
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+scale_shift_backward_kernel(const T* __restrict__ x, const T* __restrict__ beta, const T* __restrict__ dy,
+                            T* __restrict__ dx, T* __restrict__ dbeta, T* __restrict__ dgamma, int64_t rows,
+                            int cols) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * ROW_WARPS;
+  for (int64_t r = warp; r < rows; r += nwarps) {
+    const T b = beta[r];
+    double sb = 0.0, sg = 0.0;
+    for (int j = lane; j < cols; j += 32) {
+      const T d = dy[r * cols + j];
+      dx[r * cols + j] = mul_rn(d, b);
+      sb += (double)mul_rn(d, x[r * cols + j]);
+      sg += (double)d;
+    }
+    sb = warp_sum(sb);
+    sg = warp_sum(sg);
+    if (lane == 0) { dbeta[r] = (T)sb; dgamma[r] = (T)sg; }
+  }
+}
+
+// RMSNormOperation.cs:56-72 / :85-106 (Pow(x, 2) and Pow(rms, 3) as products)
+template <typename T>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+rmsnorm_forward_kernel(const T* __restrict__ x, const T* __restrict__ g, T* __restrict__ y, int64_t rows, int cols) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * ROW_WARPS;
+  for (int64_t r = warp; r < rows; r += nwarps) {
+    double ss = 0.0;
+    for (int j = lane; j < cols; j += 32) { const T v = x[r * cols + j]; ss += (double)mul_rn(v, v); }
+    ss = warp_sum(ss);
+    const T rms = sqrt_rn(div_rn((T)ss, (T)cols));
+    for (int j = lane; j < cols; j += 32)
+      y[r * cols + j] = mul_rn(div_rn(x[r * cols + j], rms), g[r * cols + j]);
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+rmsnorm_backward_kernel(const T* __restrict__ x, const T* __restrict__ g, const T* __restrict__ dy,
+                        T* __restrict__ dx, T* __restrict__ dg, int64_t rows, int cols) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * ROW_WARPS;
+  for (int64_t r = warp; r < rows; r += nwarps) {
+    double ss = 0.0;
+    for (int j = lane; j < cols; j += 32) { const T v = x[r * cols + j]; ss += (double)mul_rn(v, v); }
+    ss = warp_sum(ss);
+    const T rms = sqrt_rn(div_rn((T)ss, (T)cols));
+    const T den = mul_rn((T)cols, mul_rn(mul_rn(rms, rms), rms));
+    for (int j = lane; j < cols; j += 32) {
+      const T xv = x[r * cols + j], gv = g[r * cols + j], d = dy[r * cols + j];
+      const T a = sub_rn(div_rn(gv, rms), div_rn(mul_rn(mul_rn(xv, gv), xv), den));
+      dx[r * cols + j] = mul_rn(a, d);
+      dg[r * cols + j] = mul_rn(div_rn(xv, rms), d);
+    }
+  }
+}
+
 // ---- short rows (cols <= 256): register-cached, several rows per warp -----------------------
 // A lane keeps E = ceil(cols/32) elements of each of R rows in registers, so every input is
 // read exactly once and R*E independent loads are in flight per lane; the R row reductions
@@ -437,6 +512,63 @@ prad_status prad_layernorm_backward(prad_ctx* ctx, prad_dtype dt, const void* x,
   } else if (dt == PRAD_F32) layernorm_backward_kernel<float><<<row_grid(ctx, rows), ROW_WARPS * 32, 0, ctx->stream>>>((const float*)x, (const float*)mean, (const float*)stdv, (const float*)dy, (float*)dx, rows, cols);
   else layernorm_backward_kernel<double><<<row_grid(ctx, rows), ROW_WARPS * 32, 0, ctx->stream>>>((const double*)x, (const double*)mean, (const double*)stdv, (const double*)dy, (double*)dx, rows, cols);
   PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
+
+#define PRAD_ROW_LAUNCH(KERNEL, ...)                                                                     \
+  do {                                                                                                   \
+    if (dt == PRAD_F32) KERNEL<float><<<row_grid(ctx, rows), ROW_WARPS * 32, 0, ctx->stream>>>(__VA_ARGS__(float)); \
+    else KERNEL<double><<<row_grid(ctx, rows), ROW_WARPS * 32, 0, ctx->stream>>>(__VA_ARGS__(double));   \
+    PRAD_LAUNCHED(ctx);                                                                                  \
+  } while (0)
+
+prad_status prad_scale_shift_forward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* beta,
+                                     const void* gamma, void* y, int64_t rows, int cols) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0, PRAD_ERR_INVALID, "prad_scale_shift_forward: bad argument");
+  if (rows == 0 || cols == 0) return PRAD_OK;
+  PRAD_REQUIRE(x && beta && gamma && y, PRAD_ERR_INVALID, "prad_scale_shift_forward: null pointer");
+#define ARGS(T) (const T*)x, (const T*)beta, (const T*)gamma, (T*)y, rows, cols
+  PRAD_ROW_LAUNCH(scale_shift_forward_kernel, ARGS);
+#undef ARGS
+  return PRAD_OK;
+}
+
+prad_status prad_scale_shift_backward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* beta,
+                                      const void* dy, void* dx, void* dbeta, void* dgamma,
+                                      int64_t rows, int cols) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0, PRAD_ERR_INVALID, "prad_scale_shift_backward: bad argument");
+  if (rows == 0) return PRAD_OK;
+  PRAD_REQUIRE(beta && dbeta && dgamma && (cols == 0 || (x && dy && dx)), PRAD_ERR_INVALID,
+               "prad_scale_shift_backward: null pointer");
+#define ARGS(T) (const T*)x, (const T*)beta, (const T*)dy, (T*)dx, (T*)dbeta, (T*)dgamma, rows, cols
+  PRAD_ROW_LAUNCH(scale_shift_backward_kernel, ARGS);
+#undef ARGS
+  return PRAD_OK;
+}
+
+prad_status prad_rmsnorm_forward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* g, void* y,
+                                 int64_t rows, int cols) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0, PRAD_ERR_INVALID, "prad_rmsnorm_forward: bad argument");
+  if (rows == 0 || cols == 0) return PRAD_OK;
+  PRAD_REQUIRE(x && g && y, PRAD_ERR_INVALID, "prad_rmsnorm_forward: null pointer");
+#define ARGS(T) (const T*)x, (const T*)g, (T*)y, rows, cols
+  PRAD_ROW_LAUNCH(rmsnorm_forward_kernel, ARGS);
+#undef ARGS
+  return PRAD_OK;
+}
+
+prad_status prad_rmsnorm_backward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* g,
+                                  const void* dy, void* dx, void* dg, int64_t rows, int cols) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0, PRAD_ERR_INVALID, "prad_rmsnorm_backward: bad argument");
+  if (rows == 0 || cols == 0) return PRAD_OK;
+  PRAD_REQUIRE(x && g && dy && dx && dg, PRAD_ERR_INVALID, "prad_rmsnorm_backward: null pointer");
+#define ARGS(T) (const T*)x, (const T*)g, (const T*)dy, (T*)dx, (T*)dg, rows, cols
+  PRAD_ROW_LAUNCH(rmsnorm_backward_kernel, ARGS);
+#undef ARGS
   return PRAD_OK;
 }
 

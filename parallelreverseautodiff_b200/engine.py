@@ -14,7 +14,7 @@ from . import _lib
 from ._lib import check
 
 F32, F64 = 0, 1
-ACT_NONE, ACT_LEAKY_RELU, ACT_SIGMOID, ACT_TANH, ACT_GELU = range(5)
+ACT_NONE, ACT_LEAKY_RELU, ACT_SIGMOID, ACT_TANH, ACT_GELU, ACT_RELU, ACT_AMPLIFIED_SIGMOID = range(7)
 ADAM_RMAD, ADAM_PRAD = 0, 1
 CLIP_NONE, CLIP_REFERENCE, CLIP_GLOBAL_NORM = 0, 1, 2
 
@@ -472,6 +472,34 @@ class Engine:
                                                std.ptr, dy.ptr, out.ptr, x.size // x.shape[-1],
                                                x.shape[-1]))
         return out
+
+    def scale_shift_forward(self, x, beta, gamma, out=None):
+        """ScaleAndShiftOperation: beta, gamma hold one value per row of x."""
+        out = out or self.empty(x.shape, x.dtype)
+        check(self.lib.prad_scale_shift_forward(self.ctx, dtype_code(x.dtype), x.ptr, beta.ptr, gamma.ptr, out.ptr,
+                                                x.shape[0], x.shape[1]))
+        return out
+
+    def scale_shift_backward(self, x, beta, dy, out=None):
+        """Returns (dx, dbeta[rows], dgamma[rows])."""
+        dx, db, dg = out or (self.empty(x.shape, x.dtype), self.empty((x.shape[0], 1), x.dtype),
+                             self.empty((x.shape[0], 1), x.dtype))
+        check(self.lib.prad_scale_shift_backward(self.ctx, dtype_code(x.dtype), x.ptr, beta.ptr, dy.ptr, dx.ptr,
+                                                 db.ptr, dg.ptr, x.shape[0], x.shape[1]))
+        return dx, db, dg
+
+    def rmsnorm_forward(self, x, g, out=None):
+        out = out or self.empty(x.shape, x.dtype)
+        check(self.lib.prad_rmsnorm_forward(self.ctx, dtype_code(x.dtype), x.ptr, g.ptr, out.ptr, x.shape[0],
+                                            x.shape[1]))
+        return out
+
+    def rmsnorm_backward(self, x, g, dy, out=None):
+        """Returns (dx, dg)."""
+        dx, dg = out or (self.empty(x.shape, x.dtype), self.empty(x.shape, x.dtype))
+        check(self.lib.prad_rmsnorm_backward(self.ctx, dtype_code(x.dtype), x.ptr, g.ptr, dy.ptr, dx.ptr, dg.ptr,
+                                             x.shape[0], x.shape[1]))
+        return dx, dg
 
     # ------------------------------------------------------------ losses
     def _loss_fwd(self, fn, out, target):

@@ -72,6 +72,18 @@ def make(dtype):
     g["adam_w0"], g["adam_m0"], g["adam_v0"] = w.copy(), m.copy(), v.copy()
     O.adam_rmad(w, m, v, g["clip_out"], 1e-3, 0.9, 0.999, 1e-8, 3.0)
     g["adam_w1"], g["adam_m1"], g["adam_v1"] = w, m, v
+    # operations added after the first release of these files: appended, so that the draws above
+    # (and with them every earlier vector) stay what they were
+    g["relu_y"], g["relu_dx"] = O.relu_forward(x), O.relu_backward(x, dy)
+    g["ampsig_y"], g["ampsig_dx"] = O.amplified_sigmoid_forward(x), O.amplified_sigmoid_backward(x, dy)
+    beta, gamma = n(19, 1), n(19, 1)
+    g["ss_beta"], g["ss_gamma"] = beta, gamma
+    g["ss_y"] = O.scale_shift_forward(x, beta, gamma)
+    g["ss_dx"], g["ss_dbeta"], g["ss_dgamma"] = O.scale_shift_backward(x, beta, dy)
+    gain = n(19, 23)
+    g["rms_g"] = gain
+    g["rms_y"] = O.rmsnorm_forward(x, gain)
+    g["rms_dx"], g["rms_dg"] = O.rmsnorm_backward(x, gain, dy)
     return g
 
 

@@ -33,6 +33,19 @@ def test_kernels_reproduce_golden_vectors(engine, name):
                             (E.ACT_TANH, "tanh", up(g["tanh_y"])), (E.ACT_GELU, "gelu", x)):
         assert_close(engine.act_forward(act, x, 0.01).numpy(), g[f"{key}_y"], 1.0, key)
         assert_close(engine.act_backward(act, saved, dy, 0.01).numpy(), g[f"{key}_dx"], 1.0, key + " bwd")
+    for act, key in ((E.ACT_RELU, "relu"), (E.ACT_AMPLIFIED_SIGMOID, "ampsig")):
+        assert_close(engine.act_forward(act, x).numpy(), g[f"{key}_y"], 1.0, key)
+        assert_close(engine.act_backward(act, x, dy).numpy(), g[f"{key}_dx"], 1.0, key + " bwd")
+    beta, gamma, gain = up(g["ss_beta"]), up(g["ss_gamma"]), up(g["rms_g"])
+    np.testing.assert_array_equal(engine.scale_shift_forward(x, beta, gamma).numpy(), g["ss_y"])
+    sdx, sdb, sdg = engine.scale_shift_backward(x, beta, dy)
+    np.testing.assert_array_equal(sdx.numpy(), g["ss_dx"])
+    assert_close(sdb.numpy().reshape(-1), g["ss_dbeta"], 10.0, "scale-and-shift dbeta")
+    assert_close(sdg.numpy().reshape(-1), g["ss_dgamma"], 10.0, "scale-and-shift dgamma")
+    assert_close(engine.rmsnorm_forward(x, gain).numpy(), g["rms_y"], 3.0, "rmsnorm")
+    rdx, rdg = engine.rmsnorm_backward(x, gain, dy)
+    assert_close(rdx.numpy(), g["rms_dx"], 3.0, "rmsnorm dx")
+    assert_close(rdg.numpy(), g["rms_dg"], 3.0, "rmsnorm dg")
     da, db = engine.hadamard_backward(x, dy, dy)
     np.testing.assert_array_equal(da.numpy(), g["had_da"])
     np.testing.assert_array_equal(db.numpy(), g["had_db"])

@@ -18,12 +18,15 @@ ACTS = {
     "sigmoid": (E.ACT_SIGMOID, 0.0),
     "tanh": (E.ACT_TANH, 0.0),
     "gelu": (E.ACT_GELU, 0.0),
+    "relu": (E.ACT_RELU, 0.0),
+    "ampsig": (E.ACT_AMPLIFIED_SIGMOID, 0.0),
 }
 
 
 def _act_oracle(name, x, alpha):
     fwd = {"leaky": lambda v: O.leaky_relu_forward(v, alpha), "sigmoid": O.sigmoid_forward,
-           "tanh": O.tanh_forward, "gelu": O.gelu_forward}[name]
+           "tanh": O.tanh_forward, "gelu": O.gelu_forward, "relu": O.relu_forward,
+           "ampsig": O.amplified_sigmoid_forward}[name]
     return fwd(x)
 
 
@@ -34,6 +37,10 @@ def _act_oracle_bwd(name, x, y, dy, alpha):
         return O.sigmoid_backward(y, dy)
     if name == "tanh":
         return O.tanh_backward(y, dy)
+    if name == "relu":
+        return O.relu_backward(x, dy)
+    if name == "ampsig":
+        return O.amplified_sigmoid_backward(x, dy)
     return O.gelu_backward(x, dy)
 
 
@@ -102,7 +109,7 @@ def test_matmul_act_backward_node(engine, dtype, act):
     dPre, dA, dB = engine.matmul_act_backward(engine.upload(A), engine.upload(B), engine.upload(dOut),
                                               code, engine.upload(saved), alpha)
     assert_close(dPre.numpy(), dPre_ref, rms(dPre_ref), "dPre")
-    if act in ("leaky", "sigmoid"):     # dPre is bit-exact for these, and so are the products
+    if act in ("leaky", "sigmoid", "relu"):     # dPre is bit-exact for these, and so are the products
         np.testing.assert_array_equal(dA.numpy(), dA_ref)
         np.testing.assert_array_equal(dB.numpy(), dB_ref)
     else:
@@ -183,7 +190,9 @@ def test_activation_forward_backward(engine, dtype, act, n):
     assert_close(y.numpy(), y_ref, rms(y_ref), f"{act} forward")
     saved = engine.upload(y_ref) if act in ("sigmoid", "tanh") else xd
     dx = engine.act_backward(code, saved, engine.upload(dy), alpha)
-    if act in ("leaky", "sigmoid"):
+    if act == "relu":
+        np.testing.assert_array_equal(y.numpy(), y_ref)
+    if act in ("leaky", "sigmoid", "relu"):
         np.testing.assert_array_equal(dx.numpy(), dx_ref)   # same roundings: bit-exact
     else:
         assert_close(dx.numpy(), dx_ref, rms(dx_ref), f"{act} backward")
@@ -432,3 +441,48 @@ def test_determinism_run_twice(engine):
     db1 = engine.add_broadcast_backward(dc).numpy()
     db2 = engine.add_broadcast_backward(dc).numpy()
     np.testing.assert_array_equal(db1, db2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(1, 1), (7, 3), (64, 96), (33, 257), (500, 1000), (3, 4099)])
+def test_scale_and_shift(engine, dtype, shape):
+    """ScaleAndShiftOperation: per-row beta and gamma; the row sums of the backward accumulate in
+    double on the device and sequentially in T in the managed loop (tolerance-level)."""
+    r = rng(shape[0] + shape[1])
+    x, dy = normal(r, shape, 1, dtype), normal(r, shape, 1, dtype)
+    beta, gamma = normal(r, (shape[0], 1), 1, dtype), normal(r, (shape[0], 1), 1, dtype)
+    X, B, G, DY = (engine.upload(v) for v in (x, beta, gamma, dy))
+    np.testing.assert_array_equal(engine.scale_shift_forward(X, B, G).numpy(), O.scale_shift_forward(x, beta, gamma))
+    dx, db, dg = engine.scale_shift_backward(X, B, DY)
+    dx_ref, db_ref, dg_ref = O.scale_shift_backward(x, beta, dy)
+    np.testing.assert_array_equal(dx.numpy(), dx_ref)
+    sc = np.sqrt(shape[1])
+    assert_close(db.numpy().reshape(-1), db_ref, sc, "dbeta")
+    assert_close(dg.numpy().reshape(-1), dg_ref, sc, "dgamma")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(1, 1), (7, 3), (64, 96), (33, 257), (500, 1000), (3, 4099)])
+def test_rmsnorm(engine, dtype, shape):
+    """RMSNormOperation with its diagonal-form backward."""
+    r = rng(shape[0] * 3 + shape[1])
+    x, dy, g = normal(r, shape, 1, dtype), normal(r, shape, 1, dtype), normal(r, shape, 1, dtype)
+    X, Gm, DY = (engine.upload(v) for v in (x, g, dy))
+    y_ref = O.rmsnorm_forward(x, g)
+    assert_close(engine.rmsnorm_forward(X, Gm).numpy(), y_ref, np.abs(y_ref) + 1e-30, "y")
+    dx, dg = engine.rmsnorm_backward(X, Gm, DY)
+    dx_ref, dg_ref = O.rmsnorm_backward(x, g, dy)
+    # dx is a difference of two terms of the size of |dy g / rms|
+    rmsv = np.sqrt((x.astype(np.float64) ** 2).mean(axis=1, keepdims=True))
+    assert_close(dx.numpy(), dx_ref, np.abs(dy * g) / rmsv * (1 + (x / rmsv) ** 2 / shape[1]) + 1e-30, "dx")
+    assert_close(dg.numpy(), dg_ref, np.abs(dg_ref) + 1e-30, "dg")
+
+
+def test_new_row_ops_reject_bad_arguments(engine):
+    from parallelreverseautodiff_b200._lib import ERR_INVALID, PradError
+    x = engine.zeros((4, 4), np.float32)
+    with pytest.raises(PradError) as ei:
+        E.check(engine.lib.prad_rmsnorm_forward(engine.ctx, E.F32, x.ptr, None, x.ptr, 4, 4))
+    assert ei.value.status == ERR_INVALID
+    E.check(engine.lib.prad_rmsnorm_forward(engine.ctx, E.F32, None, None, None, 0, 4))     # empty: nothing to do
+    E.check(engine.lib.prad_scale_shift_forward(engine.ctx, E.F32, None, None, None, None, 0, 0))
