@@ -215,6 +215,14 @@ prad_status prad_act_forward(prad_ctx* ctx, prad_dtype dt, prad_act act, const v
                              int64_t n, double act_alpha);
 prad_status prad_act_backward(prad_ctx* ctx, prad_dtype dt, prad_act act, const void* saved,
                               const void* dy, void* dx, int64_t n, double act_alpha);
+/* SwishOperation.cs:41-107: y = x * sigmoid(beta x); beta and dbeta are device scalars (the op's
+ * [1 x 1] matrices); computed in double for either storage type, as the managed code does.
+ * Backward as written there: dx = dy * s * ((1 + beta x)(1 - s)), dbeta = sum dy * (x s (1 - s) -
+ * x^2 s^2); accumulate != 0 adds into dbeta. */
+prad_status prad_swish_forward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* beta, void* y,
+                               int64_t n);
+prad_status prad_swish_backward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* beta,
+                                const void* dy, void* dx, void* dbeta, int64_t n, int accumulate);
 /* HadamardProductOperation.cs:50-118 */
 prad_status prad_hadamard_forward(prad_ctx* ctx, prad_dtype dt, const void* a, const void* b,
                                   void* y, int64_t n);
@@ -386,7 +394,9 @@ typedef enum {
   PRAD_OP_SOFTMAX = 9,
   PRAD_OP_LAYERNORM = 10,
   PRAD_OP_SCALE = 11,        /* MatrixMultiplyScalarOperation, scalar = factor    */
-  PRAD_OP_TRANSPOSE = 12
+  PRAD_OP_TRANSPOSE = 12,
+  PRAD_OP_RELU = 13,
+  PRAD_OP_AMPLIFIED_SIGMOID = 14
 } prad_op;
 
 prad_status prad_graph_create(prad_ctx* ctx, prad_dtype dt, prad_graph** out_graph);

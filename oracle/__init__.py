@@ -228,6 +228,20 @@ def rmsnorm_backward(x, g, dy):
     return dx, dg
 
 
+def swish_forward(x, beta):
+    return _unary("swish_forward", x, beta)
+
+
+def swish_backward(x, beta, dy):
+    """Returns (dx, dbeta) with dbeta a scalar of x's dtype."""
+    x = _c(x)
+    dy = _c(dy, x.dtype)
+    dx = np.empty_like(x)
+    db = np.zeros(1, x.dtype)
+    _fn("swish_backward", x.dtype)(_p(x), _p(dy), _p(dx), C.c_longlong(x.size), _CT[x.dtype](beta), _p(db))
+    return dx, db[0]
+
+
 def gelu_forward(x):
     return _unary("gelu_forward", x)
 

@@ -326,6 +326,30 @@ void rmsnorm_backward(const T* x, const T* g, const T* dy, T* dx, T* dg, int R, 
   }
 }
 
+// ---- SwishOperation.cs:41-107: beta is a [1 x 1] matrix; everything is computed in double and
+// stored back in T; dBeta accumulates into a T cell element by element (dLdBeta[0][0] += ...).
+template <typename T>
+void swish_forward(const T* x, T beta, T* y, size_t n) {
+  for (size_t i = 0; i < n; ++i) {
+    double xv = x[i];
+    double sig = 1 / (1 + std::exp(-(double)beta * xv));
+    y[i] = (T)(xv * sig);
+  }
+}
+template <typename T>
+void swish_backward(const T* x, T beta, const T* dy, T* dx, T* dbeta, size_t n) {
+  T acc = 0;
+  for (size_t i = 0; i < n; ++i) {
+    double xv = x[i];
+    double sig = 1 / (1 + std::exp(-(double)beta * xv));
+    dx[i] = (T)(dy[i] * (sig * ((1 + ((double)beta * xv)) * (1 - sig))));
+    double sd = sig * (1 - sig);
+    double wrt_beta = (xv * sd) - (std::pow(xv, 2.0) * std::pow(sig, 2.0));
+    acc += (T)(dy[i] * wrt_beta);
+  }
+  *dbeta = acc;
+}
+
 // ---- HadamardProductOperation.cs:50-118 ---------------------------------------------------
 template <typename T>
 void hadamard_forward(const T* a, const T* b, T* y, size_t n) {
@@ -725,6 +749,12 @@ void adam_prad(T* w, T* m, T* v, const T* g, size_t n, T lr, T b1, T b2, T eps, 
   void oracle_rmsnorm_backward_##S(const T* x, const T* g, const T* dy, T* dx, T* dg, int R,       \
                                    int C) {                                                        \
     rmsnorm_backward<T>(x, g, dy, dx, dg, R, C);                                                   \
+  }                                                                                                \
+  void oracle_swish_forward_##S(const T* x, T* y, long long n, T beta) {                           \
+    swish_forward<T>(x, beta, y, (size_t)n);                                                       \
+  }                                                                                                \
+  void oracle_swish_backward_##S(const T* x, const T* dy, T* dx, long long n, T beta, T* dbeta) {  \
+    swish_backward<T>(x, beta, dy, dx, dbeta, (size_t)n);                                          \
   }                                                                                                \
   void oracle_gelu_forward_##S(const T* x, T* y, long long n) { gelu_forward<T>(x, y, (size_t)n); }\
   void oracle_gelu_backward_##S(const T* x, const T* dy, T* dx, long long n) {                     \

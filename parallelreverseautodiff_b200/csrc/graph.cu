@@ -74,6 +74,8 @@ static prad_act act_of(prad_op op) {
     case PRAD_OP_SIGMOID: return PRAD_ACT_SIGMOID;
     case PRAD_OP_TANH: return PRAD_ACT_TANH;
     case PRAD_OP_GELU: return PRAD_ACT_GELU;
+    case PRAD_OP_RELU: return PRAD_ACT_RELU;
+    case PRAD_OP_AMPLIFIED_SIGMOID: return PRAD_ACT_AMPLIFIED_SIGMOID;
     default: return PRAD_ACT_NONE;
   }
 }
@@ -125,7 +127,7 @@ prad_status prad_graph_set_gradient_destination(prad_graph* g, int value, void* 
 prad_status prad_graph_add_node(prad_graph* g, prad_op op, const int* in_values, int n_in,
                                 int out_value, double scalar, int* out_node) {
   PRAD_CHECK_GRAPH(g);
-  PRAD_REQUIRE(op >= PRAD_OP_MATMUL && op <= PRAD_OP_TRANSPOSE && in_values, PRAD_ERR_INVALID,
+  PRAD_REQUIRE(op >= PRAD_OP_MATMUL && op <= PRAD_OP_AMPLIFIED_SIGMOID && in_values, PRAD_ERR_INVALID,
                "prad_graph_add_node: unknown operation or null inputs");
   PRAD_REQUIRE(n_in == arity(op), PRAD_ERR_INVALID, "prad_graph_add_node: operation %d takes %d inputs, got %d",
                (int)op, arity(op), n_in);
@@ -225,6 +227,7 @@ static prad_status node_forward(prad_graph* g, GNode& n) {
     case PRAD_OP_ADD_BROADCAST: return prad_add_broadcast_forward(c, dt, a.data, V[n.in[1]].data, o.data, a.rows, a.cols);
     case PRAD_OP_HADAMARD: return prad_hadamard_forward(c, dt, a.data, V[n.in[1]].data, o.data, cnt);
     case PRAD_OP_LEAKY_RELU: case PRAD_OP_SIGMOID: case PRAD_OP_TANH: case PRAD_OP_GELU:
+    case PRAD_OP_RELU: case PRAD_OP_AMPLIFIED_SIGMOID:
       return prad_act_forward(c, dt, act_of(n.op), a.data, o.data, cnt, n.scalar);
     case PRAD_OP_SOFTMAX: return prad_softmax_forward(c, dt, a.data, o.data, a.rows, a.cols);
     case PRAD_OP_LAYERNORM:
@@ -288,7 +291,7 @@ static prad_status node_backward(prad_graph* g, GNode& n, void* d) {
       V[n.in[0]].contrib.push_back(ga);
       V[n.in[1]].contrib.push_back(gb);
       return PRAD_OK;
-    case PRAD_OP_LEAKY_RELU: case PRAD_OP_GELU:     // Backward reads the input
+    case PRAD_OP_LEAKY_RELU: case PRAD_OP_GELU: case PRAD_OP_RELU: case PRAD_OP_AMPLIFIED_SIGMOID:   // Backward reads the input
       G_TRY(in_grad_buf(g, n, 0, &ga));
       G_TRY(prad_act_backward(c, dt, act_of(n.op), a.data, d, ga, cnt, n.scalar));
       break;

@@ -78,6 +78,62 @@ static prad_status loss_forward_t(prad_ctx* ctx, const void* o, const void* t, v
   return PRAD_OK;
 }
 
+// ---------------------------------------------------------------- Swish
+// SwishOperation.cs:41-107: y = x * sigmoid(beta x) with beta a [1 x 1] weight; the managed code
+// computes in double whatever the storage type and stores back.  The backward is the one written
+// there: dx = dy * sigmoid * ((1 + beta x) * (1 - sigmoid)); dBeta = sum dy * (x s (1 - s) - x^2 s^2).
+template <typename T>
+__global__ void __launch_bounds__(LOSS_THREADS)
+swish_forward_kernel(const T* __restrict__ x, const T* __restrict__ beta, T* __restrict__ y, int64_t n) {
+  const double b = (double)beta[0];
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const double xv = (double)x[i];
+    const double sig = __ddiv_rn(1.0, __dadd_rn(1.0, exp(__dmul_rn(-b, xv))));
+    y[i] = (T)__dmul_rn(xv, sig);
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(LOSS_THREADS)
+swish_backward_kernel(const T* __restrict__ x, const T* __restrict__ beta, const T* __restrict__ dy,
+                      T* __restrict__ dx, double* __restrict__ partial, int64_t n) {
+  const double b = (double)beta[0];
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  double acc = 0.0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const double xv = (double)x[i], d = (double)dy[i];
+    const double sig = __ddiv_rn(1.0, __dadd_rn(1.0, exp(__dmul_rn(-b, xv))));
+    const double om = __dsub_rn(1.0, sig);
+    dx[i] = (T)__dmul_rn(d, __dmul_rn(sig, __dmul_rn(__dadd_rn(1.0, __dmul_rn(b, xv)), om)));
+    const double wrt = __dsub_rn(__dmul_rn(xv, __dmul_rn(sig, om)), __dmul_rn(__dmul_rn(xv, xv), __dmul_rn(sig, sig)));
+    acc += (double)(T)__dmul_rn(d, wrt);      // each term is rounded to T before it is added, as there
+  }
+  double s = block_sum_d<LOSS_THREADS>(acc);
+  if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+template <typename T>
+__global__ void swish_final_kernel(const double* __restrict__ partial, int nblocks, T* dbeta, int accumulate) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    double s = 0.0;
+    for (int b = 0; b < nblocks; ++b) s += partial[b];
+    dbeta[0] = accumulate ? add_rn(dbeta[0], (T)s) : (T)s;
+  }
+}
+
+template <typename T>
+static prad_status swish_backward_t(prad_ctx* ctx, const void* x, const void* beta, const void* dy, void* dx,
+                                    void* dbeta, int64_t n, int accumulate) {
+  int grid = stream_grid(ctx, n, LOSS_THREADS * 4, 4);
+  prad_status s = ensure_workspace(ctx, (size_t)grid * sizeof(double));
+  if (s) return s;
+  swish_backward_kernel<T><<<grid, LOSS_THREADS, 0, ctx->stream>>>((const T*)x, (const T*)beta, (const T*)dy,
+                                                                    (T*)dx, (double*)ctx->ws, n);
+  PRAD_LAUNCHED(ctx);
+  swish_final_kernel<T><<<1, 32, 0, ctx->stream>>>((const double*)ctx->ws, grid, (T*)dbeta, accumulate);
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
+
 // ---------------------------------------------------------------- embedding
 // EmbeddingOperation.cs:56-60: out[i] = W[(int)input[i,0]]
 template <typename T>
@@ -269,6 +325,27 @@ prad_status prad_embedding_backward(prad_ctx* ctx, prad_dtype dt, const void* in
   else embedding_scatter_ordered_kernel<double><<<grid, EMB_THREADS, 0, ctx->stream>>>((const double*)index_col, (const double*)dOut, (double*)dW, n, vocab, dim, bad);
   PRAD_LAUNCHED(ctx);
   return check_bad_index(ctx, bad, "prad_embedding_backward");
+}
+
+prad_status prad_swish_forward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* beta, void* y, int64_t n) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && n >= 0 && (n == 0 || (x && beta && y)), PRAD_ERR_INVALID,
+               "prad_swish_forward: bad dtype, null pointer or negative size");
+  if (n == 0) return PRAD_OK;
+  const int grid = stream_grid(ctx, n, LOSS_THREADS * 4, 4);
+  if (dt == PRAD_F32) swish_forward_kernel<float><<<grid, LOSS_THREADS, 0, ctx->stream>>>((const float*)x, (const float*)beta, (float*)y, n);
+  else swish_forward_kernel<double><<<grid, LOSS_THREADS, 0, ctx->stream>>>((const double*)x, (const double*)beta, (double*)y, n);
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
+
+prad_status prad_swish_backward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* beta, const void* dy,
+                                void* dx, void* dbeta, int64_t n, int accumulate) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && n >= 0 && beta && dbeta && (n == 0 || (x && dy && dx)), PRAD_ERR_INVALID,
+               "prad_swish_backward: bad dtype, null pointer or negative size");
+  return dt == PRAD_F32 ? swish_backward_t<float>(ctx, x, beta, dy, dx, dbeta, n, accumulate)
+                        : swish_backward_t<double>(ctx, x, beta, dy, dx, dbeta, n, accumulate);
 }
 
 }  // extern "C"

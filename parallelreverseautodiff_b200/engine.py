@@ -473,6 +473,19 @@ class Engine:
                                                x.shape[-1]))
         return out
 
+    def swish_forward(self, x, beta, out=None):
+        """SwishOperation: beta is a [1 x 1] device matrix."""
+        out = out or self.empty(x.shape, x.dtype)
+        check(self.lib.prad_swish_forward(self.ctx, dtype_code(x.dtype), x.ptr, beta.ptr, out.ptr, x.size))
+        return out
+
+    def swish_backward(self, x, beta, dy, out=None, accumulate=False):
+        """Returns (dx, dbeta[1 x 1])."""
+        dx, db = out or (self.empty(x.shape, x.dtype), self.zeros((1, 1), x.dtype))
+        check(self.lib.prad_swish_backward(self.ctx, dtype_code(x.dtype), x.ptr, beta.ptr, dy.ptr, dx.ptr, db.ptr,
+                                           x.size, int(accumulate)))
+        return dx, db
+
     def scale_shift_forward(self, x, beta, gamma, out=None):
         """ScaleAndShiftOperation: beta, gamma hold one value per row of x."""
         out = out or self.empty(x.shape, x.dtype)

@@ -141,6 +141,26 @@ def test_lstm_cell_steps_through_graph_mode(engine):
     g.close()
 
 
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+def test_relu_and_amplified_sigmoid_nodes(engine, dtype):
+    """x -> ReLU -> r ; x -> AmplifiedSigmoid -> s ; y = r (.) s : two consumers of x."""
+    r = np.random.default_rng(3)
+    x = r.standard_normal((17, 29)).astype(dtype)
+    d_out = r.standard_normal((17, 29)).astype(dtype)
+    rl, sg = O.relu_forward(x), O.amplified_sigmoid_forward(x)
+    d_r, d_s = O.hadamard_backward(rl, sg, d_out)
+    d_x = O.accumulate_gradients([O.relu_backward(x, d_r), O.amplified_sigmoid_backward(x, d_s)])
+    g = Graph(engine, dtype)
+    vx = g.input(engine.upload(x))
+    vy = g.node("HadamardProductOperation", [g.node("ReLUOperation", [vx]), g.node("AmplifiedSigmoidOperation", [vx])])
+    g.forward()
+    assert_close(g.data(vy).numpy(), O.hadamard_forward(rl, sg), 1.0, "forward")
+    g.backward(vy, engine.upload(d_out))
+    assert g.consumers(vx) == 2
+    assert_close(g.gradient(vx).numpy(), d_x, rms(d_x), "dX")
+    g.close()
+
+
 def test_graph_errors_are_status_codes(engine):
     g = Graph(engine, np.float32)
     a = g.input(engine.zeros((4, 5), np.float32))

@@ -478,6 +478,24 @@ def test_rmsnorm(engine, dtype, shape):
     assert_close(dg.numpy(), dg_ref, np.abs(dg_ref) + 1e-30, "dg")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n", [1, 77, 5000, 200003])
+def test_swish(engine, dtype, n):
+    r = rng(n)
+    x, dy = normal(r, (1, n), 2.0, dtype), normal(r, (1, n), 1.0, dtype)
+    beta = dtype(1.3)
+    X, DY, B = engine.upload(x), engine.upload(dy), engine.upload(np.full((1, 1), beta, dtype))
+    y_ref = O.swish_forward(x, beta)
+    assert_close(engine.swish_forward(X, B).numpy(), y_ref, np.abs(y_ref) + 1e-30, "swish")
+    dx, db = engine.swish_backward(X, B, DY)
+    dx_ref, db_ref = O.swish_backward(x, beta, dy)
+    assert_close(dx.numpy(), dx_ref, np.abs(dx_ref) + 1e-30, "swish dx")
+    # the managed loop adds n terms of size ~1 into a T cell one by one; the device sums in double
+    assert_close(db.numpy().reshape(()), np.asarray(db_ref, dtype), 3.0 * np.sqrt(n) * (50 if dtype == np.float32 else 1), "dbeta")
+    dx2, db2 = engine.swish_backward(X, B, DY, out=(dx, db), accumulate=True)
+    assert_close(db2.numpy().reshape(()), np.asarray(2 * db_ref, dtype), 6.0 * np.sqrt(n) * (50 if dtype == np.float32 else 1), "dbeta +=")
+
+
 def test_new_row_ops_reject_bad_arguments(engine):
     from parallelreverseautodiff_b200._lib import ERR_INVALID, PradError
     x = engine.zeros((4, 4), np.float32)
