@@ -95,9 +95,6 @@ const char* prad_version(void);
  *  "tc_chunk_k" = "128" | "256" | "512" | "1024": k summed inside the tensor core before the partial
  *    sum is added in FP32 with round-to-nearest (the tensor core truncates; default 256: rms error
  *    9e-7 of the result for any K; 512 is 4 % faster at 1.8e-6);
- *  "tc_fused_act" = "off" | "on": "on" applies a forward activation / activation derivative inside the
- *    tensor-core GEMM's epilogue; "off" (default) runs it as a separate streaming pass, which measured
- *    faster (the epilogue stalls the tensor pipe); results are identical either way;
  *  "tc_split_k" = "on" | "off"; "tc_persistent" = "on" | "off" (tf32b16 on the one-tile-per-CTA kernel);
  *  "tc_reserve_sms" = n: SMs the persistent GEMM leaves idle (default 0);
  *  "tc_pipeline" = "16x4" | "32x2" | "8x8" (k-block floats x stages of the tf32x3 kernel) */

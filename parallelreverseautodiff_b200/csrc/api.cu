@@ -151,10 +151,6 @@ prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value) {
     else { set_error("prad_set_option: tc_auto must be tf32x3|tf32b16|bf16x3|fp16x3, got '%s'", value); return PRAD_ERR_INVALID; }
     return PRAD_OK;
   }
-  if (!strcmp(key, "tc_fused_act")) {
-    ctx->tc_unfuse_act = !(strcmp(value, "off") != 0 && strcmp(value, "0") != 0);
-    return PRAD_OK;
-  }
   if (!strcmp(key, "tc_chunk_k")) {
     const int n = atoi(value);
     PRAD_REQUIRE(n == 128 || n == 256 || n == 512 || n == 1024, PRAD_ERR_INVALID,

@@ -500,6 +500,104 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_co
   }
 }
 
+// ---- quad-transposed epilogue -----------------------------------------------------------
+// After the accumulator is drained a lane holds 32 consecutive columns of ONE row per group, so
+// a direct 16-byte store touches 32 different rows per instruction.  Two butterfly exchanges
+// inside each quad of lanes (xor 2, then xor 1; registers only, the shared-memory pipe belongs
+// to the tensor core) re-deal a 32-column group so that lane i of quad q holds, for each of
+// the quad's four rows s, the columns 4 (i + 4 h) .. + 3 (h = 0, 1): the four lanes of a quad
+// then write 64 contiguous bytes of one row, and an instruction touches 8 rows instead of 32.
+// The epilogue applies the power-of-two scales, alpha, beta and the bias; activations run as a
+// separate pass (see gemm_tf32x3), which also keeps this fully unrolled code small.
+__device__ __forceinline__ void quad_transpose(float (&v)[32], int lane) {
+  const bool hi2 = (lane & 2) != 0, hi1 = (lane & 1) != 0;
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {     // column blocks c and c + 2 against lane ^ 2
+        float& lo = v[4 * (c + 4 * h) + k];
+        float& hi = v[4 * (c + 2 + 4 * h) + k];
+        const float recv = __shfl_xor_sync(0xffffffffu, hi2 ? lo : hi, 2);
+        if (hi2) lo = recv; else hi = recv;
+      }
+#pragma unroll
+  for (int h = 0; h < 2; ++h)
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {     // slots 2u and 2u + 1 against lane ^ 1
+        float& lo = v[4 * (2 * u + 4 * h) + k];
+        float& hi = v[4 * (2 * u + 1 + 4 * h) + k];
+        const float recv = __shfl_xor_sync(0xffffffffu, hi1 ? lo : hi, 1);
+        if (hi1) lo = recv; else hi = recv;
+      }
+  // now v[4 (s + 4 h) + k] = row 4 (lane / 4) + s, column 4 ((lane & 3) + 4 h) + k of the group
+}
+
+__device__ __forceinline__ void epilogue_quad(float o0, float o1, float o2, float o3, int row, int c, int er, int M,
+                                              int N, float* __restrict__ C, int64_t ldc, bool vecC, const Epi& epi) {
+  if (row >= M || c >= N) return;
+  const int64_t off = (int64_t)row * ldc + c;
+  const bool full = vecC && (c + 4 <= N);
+  float o[4] = {o0, o1, o2, o3};
+  if (epi.row_exp) {   // exact: two multiplications by powers of two, each half of the exponent
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int e = er + (c + q < N ? epi.col_exp[c + q] : 0);
+      const int h = e >> 1;
+      o[q] = epi.alpha * ((o[q] * pow2i(h)) * pow2i(e - h));
+    }
+  } else {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) o[q] = epi.alpha * o[q];
+  }
+  if (epi.beta != 0.f) {
+    if (full) {
+      const float4 old = *reinterpret_cast<const float4*>(C + off);
+      o[0] = fmaf(epi.beta, old.x, o[0]); o[1] = fmaf(epi.beta, old.y, o[1]);
+      o[2] = fmaf(epi.beta, old.z, o[2]); o[3] = fmaf(epi.beta, old.w, o[3]);
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) if (c + q < N) o[q] = fmaf(epi.beta, C[off + q], o[q]);
+    }
+  }
+  if (epi.bias) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) if (c + q < N) o[q] += epi.bias[c + q];
+  }
+  if (full) {
+    __stcs(reinterpret_cast<float4*>(C + off), make_float4(o[0], o[1], o[2], o[3]));
+  } else {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) if (c + q < N) C[off + q] = o[q];
+  }
+}
+
+// sum[g][j] = column col0 + 32 g + j of row row0 + lane (modified in place)
+__device__ __forceinline__ void epilogue_store_warp(float (&sum)[4][32], int lane, int row0, int col0, int M, int N,
+                                                    float* __restrict__ C, int64_t ldc, bool vecC, const Epi& epi) {
+  const int qrow = row0 + 4 * (lane >> 2), i = lane & 3;
+  int er[4] = {0, 0, 0, 0};
+  if (epi.row_exp) {
+#pragma unroll
+    for (int s = 0; s < 4; ++s) er[s] = qrow + s < M ? epi.row_exp[qrow + s] : 0;
+  }
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    quad_transpose(sum[g], lane);
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        const int j = 4 * (s + 4 * h);
+        epilogue_quad(sum[g][j], sum[g][j + 1], sum[g][j + 2], sum[g][j + 3], qrow + s,
+                      col0 + 32 * g + 4 * (i + 4 * h), er[s], M, N, C, ldc, vecC, epi);
+      }
+  }
+}
+
 // ---- persistent variant of MODE 1 (TF32 product + two BF16 corrections) -----------------
 // Same arithmetic and tile as gemm_tf32x3_kernel<Cfg<32,2,1>>, organised differently:
 //   * one CTA per SM walks output tiles (n-tile fastest, then m-tile, then k-slice): its
@@ -758,10 +856,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
       }
       if (!ok || *((volatile int*)err_flag) != 0) { ok = false; break; }
       float* Ct = C + (int64_t)z * ts.split_stride;
-      const int row = m0 + sub * 32 + lane;
-#pragma unroll
-      for (int g = 0; g < 4; ++g)
-        epilogue_store32(sum[g], row, n0 + half * 128 + g * 32, M, N, Ct, ldc, vecC, epi);
+      epilogue_store_warp(sum, lane, m0 + sub * 32, n0 + half * 128, M, N, Ct, ldc, vecC, epi);
     }
   }
 
@@ -1249,37 +1344,39 @@ prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, do
   // large products; a short M or N only wastes part of the 128 x 256 tile (TMA zero-fills it),
   // which still beats ten CTAs walking a 200 000-long k range one after the other
   const bool big = (int64_t)M * N * K >= ((int64_t)1 << 27) && M >= 64 && N >= 64 && K >= KPAD;
-  if (batch != 1 || K < 1 || !(big || forced) || encode_fn() == nullptr) {
+  // (an activation or pre-activation copy on a strided output would need a strided elementwise pass)
+  const bool strided_act = ldc != N && (e.act != PRAD_ACT_NONE || e.dact != PRAD_ACT_NONE || e.z_out);
+  if (batch != 1 || K < 1 || !(big || forced) || strided_act || encode_fn() == nullptr) {
     if (probe_only || !forced) return PRAD_ERR_UNSUPPORTED;
     set_error("gemm tf32x3: unsupported shape (batch %d) or driver without cuTensorMapEncodeTiled", batch);
     return PRAD_ERR_UNSUPPORTED;
   }
   if (probe_only) return PRAD_OK;
-  // Activation epilogues run as a separate streaming pass.  Measured on the 65536 x 4096 x 4096
-  // products: the epilogue warps hold the whole 128-column row slice in registers, so the
-  // activation's loads and transcendental chains run with next to no latency hiding and stall
-  // the tensor pipe behind them -- 9.1 ms with GELU and the pre-activation copy fused, 7.6 ms
-  // with the GELU derivative fused, against 5.0 ms plain plus 0.4 - 0.5 ms for the HBM-bound
-  // elementwise kernel.  (Strided outputs, or beta with a forward activation, stay fused.)
+  // Activations (and the pre-activation copy) run as separate streaming passes.  Measured on the
+  // 65536 x 4096 x 4096 products: the epilogue warps hold the whole 128-column row slice in
+  // registers, so an activation's loads and transcendental chains run with next to no latency
+  // hiding and stall the tensor pipe behind them -- 9.1 ms with GELU and the pre-activation copy
+  // fused, 7.6 ms with the GELU derivative fused, against 5.0 ms plain plus 0.4 - 0.5 ms for the
+  // HBM-bound elementwise kernel.  The tensor-core epilogues therefore carry no activation code.
   const bool has_act = e.act != PRAD_ACT_NONE, has_dact = e.dact != PRAD_ACT_NONE;
-  if ((has_act != has_dact) && ldc == N && ctx->tc_unfuse_act && !(has_act && beta != 0.0)) {
+  if (has_act || has_dact || e.z_out) {
     GemmEpilogue plain = e;
     plain.act = PRAD_ACT_NONE;
     plain.dact = PRAD_ACT_NONE;
     plain.saved = nullptr;
+    plain.z_out = nullptr;
     const int64_t n = (int64_t)M * N;
-    if (has_act) {
-      void* pre = e.z_out ? e.z_out : C;   // the pre-activation lands where the caller keeps it
-      plain.z_out = nullptr;
-      prad_status st = gemm_tf32x3(ctx, tA, tB, M, N, K, alpha, A, lda, B, ldb, beta, pre, ldc, batch, sA, sB, sC,
-                                   plain, false);
-      if (st) return st;
-      return prad_act_forward(ctx, PRAD_F32, e.act, pre, C, n, e.act_alpha);
-    }
-    prad_status st = gemm_tf32x3(ctx, tA, tB, M, N, K, alpha, A, lda, B, ldb, beta, C, ldc, batch, sA, sB, sC, plain,
+    // the pre-activation lands where the caller keeps it; beta needs the old C, so then it is copied
+    const bool direct = has_act && e.z_out && beta == 0.0;
+    void* pre = direct ? e.z_out : C;
+    prad_status st = gemm_tf32x3(ctx, tA, tB, M, N, K, alpha, A, lda, B, ldb, beta, pre, ldc, batch, sA, sB, sC, plain,
                                  false);
     if (st) return st;
-    return prad_act_backward(ctx, PRAD_F32, e.dact, e.saved, C, C, n, e.act_alpha);
+    if (e.z_out && !direct) PRAD_CUDA(cudaMemcpyAsync(e.z_out, C, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+    if (has_act) st = prad_act_forward(ctx, PRAD_F32, e.act, pre, C, n, e.act_alpha);
+    if (st) return st;
+    if (has_dact) st = prad_act_backward(ctx, PRAD_F32, e.dact, e.saved, C, C, n, e.act_alpha);
+    return st;
   }
   const int mode = ctx->gemm_f32 == GemmF32::Tf32x3 ? 0
                    : ctx->gemm_f32 == GemmF32::Tf32B16 ? 1
