@@ -220,6 +220,15 @@ prad_status prad_swish_forward(prad_ctx* ctx, prad_dtype dt, const void* x, cons
                                int64_t n);
 prad_status prad_swish_backward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* beta,
                                 const void* dy, void* dx, void* dbeta, int64_t n, int accumulate);
+/* SwigLUOperation.cs:59-145: y = swish(x w_j + b_j) * (x v_j + c_j); w, v, b, c hold one value per
+ * COLUMN (the op's [cols x 1] matrices, `cols` contiguous values each), beta is the constructor's
+ * scalar (NeuralNetworkParameters.SwigLUBeta).  Backward as written there (der = swish + beta *
+ * sigmoid * (1 - swish)); dw, dv, db, dc are `cols` long. */
+prad_status prad_swiglu_forward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* w, const void* v,
+                                const void* b, const void* c, double beta, void* y, int64_t rows, int cols);
+prad_status prad_swiglu_backward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* w, const void* v,
+                                 const void* b, const void* c, double beta, const void* dy, void* dx,
+                                 void* dw, void* dv, void* db, void* dc, int64_t rows, int cols);
 /* HadamardProductOperation.cs:50-118 */
 prad_status prad_hadamard_forward(prad_ctx* ctx, prad_dtype dt, const void* a, const void* b,
                                   void* y, int64_t n);

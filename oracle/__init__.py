@@ -242,6 +242,27 @@ def swish_backward(x, beta, dy):
     return dx, db[0]
 
 
+def swiglu_forward(x, w, v, b, c, beta):
+    """w, v, b, c: one value per column (SwigLUOperation's [cols x 1] matrices)."""
+    x = _c(x)
+    w, v, b, c = (_c(np.reshape(t, -1), x.dtype) for t in (w, v, b, c))
+    y = np.empty_like(x)
+    _fn("swiglu_forward", x.dtype)(_p(x), _p(w), _p(v), _p(b), _p(c), C.c_double(beta), _p(y), x.shape[0], x.shape[1])
+    return y
+
+
+def swiglu_backward(x, w, v, b, c, beta, dy):
+    """Returns (dx, dw, dv, db, dc)."""
+    x = _c(x)
+    w, v, b, c = (_c(np.reshape(t, -1), x.dtype) for t in (w, v, b, c))
+    dy = _c(dy, x.dtype)
+    dx = np.empty_like(x)
+    outs = [np.empty(x.shape[1], x.dtype) for _ in range(4)]
+    _fn("swiglu_backward", x.dtype)(_p(x), _p(w), _p(v), _p(b), _p(c), C.c_double(beta), _p(dy), _p(dx),
+                                    *[_p(o) for o in outs], x.shape[0], x.shape[1])
+    return (dx, *outs)
+
+
 def gelu_forward(x):
     return _unary("gelu_forward", x)
 

@@ -350,6 +350,40 @@ void swish_backward(const T* x, T beta, const T* dy, T* dx, T* dbeta, size_t n) 
   *dbeta = acc;
 }
 
+// ---- SwigLUOperation.cs:59-145: w, v, b, c are [cols x 1]; beta is the constructor's scalar; all
+// arithmetic in double, stored back in T; the four column sums accumulate in double over the rows.
+template <typename T>
+void swiglu_forward(const T* x, const T* w, const T* v, const T* b, const T* c, double beta, T* y, int R, int C) {
+  for (int i = 0; i < R; ++i)
+    for (int j = 0; j < C; ++j) {
+      double xv = x[(size_t)i * C + j];
+      double f = (xv * (double)w[j]) + (double)b[j];
+      double swish = f * (1 / (1 + std::exp(-beta * f)));
+      y[(size_t)i * C + j] = (T)(swish * ((xv * (double)v[j]) + (double)c[j]));
+    }
+}
+template <typename T>
+void swiglu_backward(const T* x, const T* w, const T* v, const T* b, const T* c, double beta, const T* dy, T* dx,
+                     T* dw, T* dv, T* db, T* dc, int R, int C) {
+  for (int j = 0; j < C; ++j) {
+    double s_w = 0, s_v = 0, s_b = 0, s_c = 0;
+    for (int i = 0; i < R; ++i) {
+      double xv = x[(size_t)i * C + j];
+      double f = (xv * (double)w[j]) + (double)b[j];
+      double sig = 1 / (1 + std::exp(-beta * f));
+      double swish = f * sig;
+      double der = swish + (beta * sig * (1 - swish));
+      double d = dy[(size_t)i * C + j];
+      dx[(size_t)i * C + j] = (T)(d * ((double)v[j] * der));
+      s_w += d * ((xv * der) * ((xv * (double)v[j]) + (double)c[j]));
+      s_v += d * (swish * xv);
+      s_b += d * (der * ((xv * (double)v[j]) + (double)c[j]));
+      s_c += d * swish;
+    }
+    dw[j] = (T)s_w; dv[j] = (T)s_v; db[j] = (T)s_b; dc[j] = (T)s_c;
+  }
+}
+
 // ---- HadamardProductOperation.cs:50-118 ---------------------------------------------------
 template <typename T>
 void hadamard_forward(const T* a, const T* b, T* y, size_t n) {
@@ -755,6 +789,15 @@ void adam_prad(T* w, T* m, T* v, const T* g, size_t n, T lr, T b1, T b2, T eps, 
   }                                                                                                \
   void oracle_swish_backward_##S(const T* x, const T* dy, T* dx, long long n, T beta, T* dbeta) {  \
     swish_backward<T>(x, beta, dy, dx, dbeta, (size_t)n);                                          \
+  }                                                                                                \
+  void oracle_swiglu_forward_##S(const T* x, const T* w, const T* v, const T* b, const T* c,       \
+                                 double beta, T* y, int R, int C) {                                \
+    swiglu_forward<T>(x, w, v, b, c, beta, y, R, C);                                               \
+  }                                                                                                \
+  void oracle_swiglu_backward_##S(const T* x, const T* w, const T* v, const T* b, const T* c,      \
+                                  double beta, const T* dy, T* dx, T* dw, T* dv, T* db, T* dc,     \
+                                  int R, int C) {                                                  \
+    swiglu_backward<T>(x, w, v, b, c, beta, dy, dx, dw, dv, db, dc, R, C);                         \
   }                                                                                                \
   void oracle_gelu_forward_##S(const T* x, T* y, long long n) { gelu_forward<T>(x, y, (size_t)n); }\
   void oracle_gelu_backward_##S(const T* x, const T* dy, T* dx, long long n) {                     \

@@ -67,6 +67,8 @@ SIGNATURES = {
     "prad_softmax_backward": [vp, i32, vp, vp, vp, i64, i32],
     "prad_layernorm_forward": [vp, i32, vp, vp, vp, vp, i64, i32],
     "prad_layernorm_backward": [vp, i32, vp, vp, vp, vp, vp, i64, i32],
+    "prad_swiglu_forward": [vp, i32, vp, vp, vp, vp, vp, f64, vp, i64, i32],
+    "prad_swiglu_backward": [vp, i32, vp, vp, vp, vp, vp, f64, vp, vp, vp, vp, vp, vp, i64, i32],
     "prad_swish_forward": [vp, i32, vp, vp, vp, i64],
     "prad_swish_backward": [vp, i32, vp, vp, vp, vp, vp, i64, i32],
     "prad_scale_shift_forward": [vp, i32, vp, vp, vp, vp, i64, i32],

@@ -134,6 +134,75 @@ static prad_status swish_backward_t(prad_ctx* ctx, const void* x, const void* be
   return PRAD_OK;
 }
 
+// ---------------------------------------------------------------- SwigLU
+// SwigLUOperation.cs:59-145: y = swish(x w_j + b_j) * (x v_j + c_j) with per-column w, v, b, c and
+// the constructor's scalar beta; double arithmetic throughout, as there.  Backward as written:
+// der = swish + beta * sigmoid * (1 - swish); the four per-column sums run over the rows.
+// One thread per column and band of rows (consecutive threads = consecutive columns, so a row
+// segment is read contiguously); bands are added in band order by the second kernel.
+struct SwigLUParams { const void *w, *v, *b, *c; double beta; };
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+swiglu_forward_kernel(const T* __restrict__ x, SwigLUParams p, T* __restrict__ y, int64_t rows, int cols,
+                      int64_t rows_per_band) {
+  const int j = blockIdx.x * 128 + threadIdx.x;
+  if (j >= cols) return;
+  const double w = (double)((const T*)p.w)[j], v = (double)((const T*)p.v)[j];
+  const double b = (double)((const T*)p.b)[j], c = (double)((const T*)p.c)[j];
+  const int64_t r1 = min(rows, (int64_t)(blockIdx.y + 1) * rows_per_band);
+  for (int64_t i = (int64_t)blockIdx.y * rows_per_band; i < r1; ++i) {
+    const double xv = (double)x[i * cols + j];
+    const double f = __dadd_rn(__dmul_rn(xv, w), b);
+    const double swish = __dmul_rn(f, __ddiv_rn(1.0, __dadd_rn(1.0, exp(__dmul_rn(-p.beta, f)))));
+    y[i * cols + j] = (T)__dmul_rn(swish, __dadd_rn(__dmul_rn(xv, v), c));
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(128)
+swiglu_backward_kernel(const T* __restrict__ x, SwigLUParams p, const T* __restrict__ dy, T* __restrict__ dx,
+                       double* __restrict__ partial, int64_t rows, int cols, int64_t rows_per_band) {
+  const int j = blockIdx.x * 128 + threadIdx.x;
+  if (j >= cols) return;
+  const double w = (double)((const T*)p.w)[j], v = (double)((const T*)p.v)[j];
+  const double b = (double)((const T*)p.b)[j], c = (double)((const T*)p.c)[j];
+  const int64_t r1 = min(rows, (int64_t)(blockIdx.y + 1) * rows_per_band);
+  double s_w = 0.0, s_v = 0.0, s_b = 0.0, s_c = 0.0;
+  for (int64_t i = (int64_t)blockIdx.y * rows_per_band; i < r1; ++i) {
+    const double xv = (double)x[i * cols + j], d = (double)dy[i * cols + j];
+    const double f = __dadd_rn(__dmul_rn(xv, w), b);
+    const double sig = __ddiv_rn(1.0, __dadd_rn(1.0, exp(__dmul_rn(-p.beta, f))));
+    const double swish = __dmul_rn(f, sig);
+    const double der = __dadd_rn(swish, __dmul_rn(__dmul_rn(p.beta, sig), __dsub_rn(1.0, swish)));
+    const double lin = __dadd_rn(__dmul_rn(xv, v), c);
+    dx[i * cols + j] = (T)__dmul_rn(d, __dmul_rn(v, der));
+    s_w = __dadd_rn(s_w, __dmul_rn(d, __dmul_rn(__dmul_rn(xv, der), lin)));
+    s_v = __dadd_rn(s_v, __dmul_rn(d, __dmul_rn(swish, xv)));
+    s_b = __dadd_rn(s_b, __dmul_rn(d, __dmul_rn(der, lin)));
+    s_c = __dadd_rn(s_c, __dmul_rn(d, swish));
+  }
+  double* out = partial + ((int64_t)blockIdx.y * 4) * cols + j;
+  out[0] = s_w; out[cols] = s_v; out[2 * (int64_t)cols] = s_b; out[3 * (int64_t)cols] = s_c;
+}
+template <typename T>
+__global__ void __launch_bounds__(128)
+swiglu_final_kernel(const double* __restrict__ partial, int bands, int cols, T* dw, T* dv, T* db, T* dc) {
+  const int j = blockIdx.x * 128 + threadIdx.x;
+  if (j >= cols) return;
+  double s[4] = {0.0, 0.0, 0.0, 0.0};
+  for (int band = 0; band < bands; ++band)
+#pragma unroll
+    for (int q = 0; q < 4; ++q) s[q] = __dadd_rn(s[q], partial[((int64_t)band * 4 + q) * cols + j]);
+  dw[j] = (T)s[0]; dv[j] = (T)s[1]; db[j] = (T)s[2]; dc[j] = (T)s[3];
+}
+
+static int swiglu_bands(const prad_ctx* ctx, int64_t rows, int cols) {
+  const int64_t col_blocks = ceil_div(cols, 128);
+  int64_t bands = ceil_div((int64_t)ctx->sm_count * 8, col_blocks);
+  if (bands > ceil_div(rows, 16)) bands = ceil_div(rows, 16);   // at least 16 rows per band
+  return (int)(bands < 1 ? 1 : bands);
+}
+
 // ---------------------------------------------------------------- embedding
 // EmbeddingOperation.cs:56-60: out[i] = W[(int)input[i,0]]
 template <typename T>
@@ -346,6 +415,50 @@ prad_status prad_swish_backward(prad_ctx* ctx, prad_dtype dt, const void* x, con
                "prad_swish_backward: bad dtype, null pointer or negative size");
   return dt == PRAD_F32 ? swish_backward_t<float>(ctx, x, beta, dy, dx, dbeta, n, accumulate)
                         : swish_backward_t<double>(ctx, x, beta, dy, dx, dbeta, n, accumulate);
+}
+
+prad_status prad_swiglu_forward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* w, const void* v,
+                                const void* b, const void* c, double beta, void* y, int64_t rows, int cols) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0, PRAD_ERR_INVALID, "prad_swiglu_forward: bad argument");
+  if (rows == 0 || cols == 0) return PRAD_OK;
+  PRAD_REQUIRE(x && w && v && b && c && y, PRAD_ERR_INVALID, "prad_swiglu_forward: null pointer");
+  int bands = swiglu_bands(ctx, rows, cols);
+  const int64_t rpb = ceil_div(rows, bands);
+  bands = (int)ceil_div(rows, rpb);
+  const dim3 grid((unsigned)ceil_div(cols, 128), (unsigned)bands);
+  SwigLUParams p{w, v, b, c, beta};
+  if (dt == PRAD_F32) swiglu_forward_kernel<float><<<grid, 128, 0, ctx->stream>>>((const float*)x, p, (float*)y, rows, cols, rpb);
+  else swiglu_forward_kernel<double><<<grid, 128, 0, ctx->stream>>>((const double*)x, p, (double*)y, rows, cols, rpb);
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
+
+prad_status prad_swiglu_backward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* w, const void* v,
+                                 const void* b, const void* c, double beta, const void* dy, void* dx, void* dw,
+                                 void* dv, void* db, void* dc, int64_t rows, int cols) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0, PRAD_ERR_INVALID, "prad_swiglu_backward: bad argument");
+  if (cols == 0) return PRAD_OK;
+  PRAD_REQUIRE(w && v && b && c && dw && dv && db && dc && (rows == 0 || (x && dy && dx)), PRAD_ERR_INVALID,
+               "prad_swiglu_backward: null pointer");
+  int bands = rows == 0 ? 0 : swiglu_bands(ctx, rows, cols);
+  const int64_t rpb = bands ? ceil_div(rows, bands) : 1;
+  bands = (int)ceil_div(rows, rpb);
+  prad_status st = ensure_workspace(ctx, (size_t)(bands ? bands : 1) * 4 * cols * sizeof(double));
+  if (st) return st;
+  SwigLUParams p{w, v, b, c, beta};
+  const unsigned cb = (unsigned)ceil_div(cols, 128);
+  if (bands) {
+    const dim3 grid(cb, (unsigned)bands);
+    if (dt == PRAD_F32) swiglu_backward_kernel<float><<<grid, 128, 0, ctx->stream>>>((const float*)x, p, (const float*)dy, (float*)dx, (double*)ctx->ws, rows, cols, rpb);
+    else swiglu_backward_kernel<double><<<grid, 128, 0, ctx->stream>>>((const double*)x, p, (const double*)dy, (double*)dx, (double*)ctx->ws, rows, cols, rpb);
+    PRAD_LAUNCHED(ctx);
+  }
+  if (dt == PRAD_F32) swiglu_final_kernel<float><<<cb, 128, 0, ctx->stream>>>((const double*)ctx->ws, bands, cols, (float*)dw, (float*)dv, (float*)db, (float*)dc);
+  else swiglu_final_kernel<double><<<cb, 128, 0, ctx->stream>>>((const double*)ctx->ws, bands, cols, (double*)dw, (double*)dv, (double*)db, (double*)dc);
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
 }
 
 }  // extern "C"

@@ -486,6 +486,22 @@ class Engine:
                                            x.size, int(accumulate)))
         return dx, db
 
+    def swiglu_forward(self, x, w, v, b, c, beta, out=None):
+        """SwigLUOperation: w, v, b, c hold one value per column of x."""
+        out = out or self.empty(x.shape, x.dtype)
+        check(self.lib.prad_swiglu_forward(self.ctx, dtype_code(x.dtype), x.ptr, w.ptr, v.ptr, b.ptr, c.ptr, beta,
+                                           out.ptr, x.shape[0], x.shape[1]))
+        return out
+
+    def swiglu_backward(self, x, w, v, b, c, beta, dy):
+        """Returns (dx, dw, dv, db, dc)."""
+        dx = self.empty(x.shape, x.dtype)
+        g = [self.empty((x.shape[1], 1), x.dtype) for _ in range(4)]
+        check(self.lib.prad_swiglu_backward(self.ctx, dtype_code(x.dtype), x.ptr, w.ptr, v.ptr, b.ptr, c.ptr, beta,
+                                            dy.ptr, dx.ptr, g[0].ptr, g[1].ptr, g[2].ptr, g[3].ptr, x.shape[0],
+                                            x.shape[1]))
+        return (dx, *g)
+
     def scale_shift_forward(self, x, beta, gamma, out=None):
         """ScaleAndShiftOperation: beta, gamma hold one value per row of x."""
         out = out or self.empty(x.shape, x.dtype)

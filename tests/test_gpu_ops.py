@@ -496,6 +496,27 @@ def test_swish(engine, dtype, n):
     assert_close(db2.numpy().reshape(()), np.asarray(2 * db_ref, dtype), 6.0 * np.sqrt(n) * (50 if dtype == np.float32 else 1), "dbeta +=")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(1, 1), (9, 5), (300, 96), (4100, 130), (17, 1000)])
+def test_swiglu(engine, dtype, shape):
+    r = rng(shape[0] + 7 * shape[1])
+    x, dy = normal(r, shape, 1.5, dtype), normal(r, shape, 1.0, dtype)
+    w, v, b, c = (normal(r, (shape[1], 1), 1.0, dtype) for _ in range(4))
+    beta = 1.1
+    X, DY, W, V, B, Cc = (engine.upload(t) for t in (x, dy, w, v, b, c))
+    y_ref = O.swiglu_forward(x, w, v, b, c, beta)
+    assert_close(engine.swiglu_forward(X, W, V, B, Cc, beta).numpy(), y_ref, np.abs(y_ref) + 1e-30, "swiglu")
+    got = engine.swiglu_backward(X, W, V, B, Cc, beta, DY)
+    ref = O.swiglu_backward(x, w, v, b, c, beta, dy)
+    assert_close(got[0].numpy(), ref[0], np.abs(ref[0]) + 1e-30, "dx")
+    # column sums over the rows: double accumulators on both sides, different grouping
+    f = x.astype(np.float64) * w.reshape(1, -1) + b.reshape(1, -1)
+    lin = np.abs(x.astype(np.float64) * v.reshape(1, -1) + c.reshape(1, -1))
+    bound = (np.abs(dy) * (1 + np.abs(f)) * (1 + np.abs(x)) * (1 + lin)).sum(axis=0)
+    for k, name in enumerate(("dw", "dv", "db", "dc"), start=1):
+        assert_close(got[k].numpy().reshape(-1), ref[k], bound, name)
+
+
 def test_new_row_ops_reject_bad_arguments(engine):
     from parallelreverseautodiff_b200._lib import ERR_INVALID, PradError
     x = engine.zeros((4, 4), np.float32)
