@@ -202,7 +202,8 @@ struct Epi {
 // 2^e as a float, |e| <= 126
 __device__ __forceinline__ float pow2i(int e) { return __int_as_float((e + 127) << 23); }
 
-// One epilogue thread's share of the finished tile: 32 consecutive columns of one row.
+// One epilogue thread's share of the finished tile: 32 consecutive columns of one row (scales,
+// alpha, beta, bias; activations run as separate passes, see gemm_tf32x3).
 __device__ __forceinline__ void epilogue_store32(const float (&acc)[32], int row, int col0, int M, int N,
                                                  float* __restrict__ C, int64_t ldc, bool vecC, const Epi& epi) {
   if (row >= M || col0 >= N) return;
@@ -237,36 +238,6 @@ __device__ __forceinline__ void epilogue_store32(const float (&acc)[32], int row
   if (epi.bias) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) if (col0 + j < N) out[j] += epi.bias[col0 + j];
-  }
-  if (epi.z_out) {
-    if (full && ((uintptr_t)epi.z_out & 15) == 0) {
-#pragma unroll
-      for (int j = 0; j < 32; j += 4)
-        *reinterpret_cast<float4*>(epi.z_out + off + j) = make_float4(out[j], out[j + 1], out[j + 2], out[j + 3]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) if (col0 + j < N) epi.z_out[off + j] = out[j];
-    }
-  }
-  if (epi.act != PRAD_ACT_NONE) {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) out[j] = act_value<float>((prad_act)epi.act, out[j], epi.act_alpha);
-  }
-  if (epi.dact != PRAD_ACT_NONE) {
-    if (full) {
-#pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        float4 sv = *reinterpret_cast<const float4*>(epi.saved + off + j);
-        out[j] = mul_rn(out[j], act_derivative<float>((prad_act)epi.dact, sv.x, epi.act_alpha));
-        out[j + 1] = mul_rn(out[j + 1], act_derivative<float>((prad_act)epi.dact, sv.y, epi.act_alpha));
-        out[j + 2] = mul_rn(out[j + 2], act_derivative<float>((prad_act)epi.dact, sv.z, epi.act_alpha));
-        out[j + 3] = mul_rn(out[j + 3], act_derivative<float>((prad_act)epi.dact, sv.w, epi.act_alpha));
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (col0 + j < N) out[j] = mul_rn(out[j], act_derivative<float>((prad_act)epi.dact, epi.saved[off + j], epi.act_alpha));
-    }
   }
   if (full) {
 #pragma unroll
