@@ -117,6 +117,12 @@ prad_status prad_alloc(prad_ctx* ctx, size_t bytes, void** out_dptr);
 prad_status prad_free(prad_ctx* ctx, void* dptr);
 prad_status prad_zero(prad_ctx* ctx, void* dptr, size_t bytes);
 prad_status prad_copy(prad_ctx* ctx, void* dst, const void* src, size_t bytes);
+/* Strided device-to-device copy of `rows` rows of `width_bytes` (pitches in bytes).  It is what
+ * MatrixConcatenateOperation / MatrixHorizontalConcatenateOperation do element by element
+ * (src/RMAD/MatrixConcatenateOperation.cs:41-96): Forward copies each input into its column range
+ * of the output, Backward copies each column range of dOutput back out. */
+prad_status prad_copy_2d(prad_ctx* ctx, void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                         size_t width_bytes, size_t rows);
 prad_status prad_upload(prad_ctx* ctx, void* dst, const void* src_host, size_t bytes);
 prad_status prad_download(prad_ctx* ctx, void* dst_host, const void* src, size_t bytes);
 /* Overlapped upload: enqueues the copy on the context's separate copy stream, so it runs while
@@ -285,6 +291,18 @@ prad_status prad_layernorm_forward(prad_ctx* ctx, prad_dtype dt, const void* x, 
 prad_status prad_layernorm_backward(prad_ctx* ctx, prad_dtype dt, const void* x,
                                     const void* mean, const void* stdv, const void* dy, void* dx,
                                     int64_t rows, int cols);
+/* MatrixSumOperation.cs:38-68 and MatrixAverageOperation.cs:38-67 (average != 0): y[i] = LINQ Sum /
+ * Average of row i (`rows` values); backward: dx[i][j] = dy[i] (or dy[i] / cols). */
+prad_status prad_row_sum_forward(prad_ctx* ctx, prad_dtype dt, const void* x, void* y, int64_t rows, int cols,
+                                 int average);
+prad_status prad_row_sum_backward(prad_ctx* ctx, prad_dtype dt, const void* dy, void* dx, int64_t rows, int cols,
+                                  int average);
+/* MatrixBroadcastOperation.cs:48-88: y[i][j] = x[i % in_rows][j % in_cols]; backward: every input
+ * element collects its copies, rows outer, columns inner, added in the storage type. */
+prad_status prad_broadcast_forward(prad_ctx* ctx, prad_dtype dt, const void* x, int in_rows, int in_cols, void* y,
+                                   int out_rows, int out_cols);
+prad_status prad_broadcast_backward(prad_ctx* ctx, prad_dtype dt, const void* dy, int out_rows, int out_cols,
+                                    void* dx, int in_rows, int in_cols);
 /* ScaleAndShiftOperation.cs:55-106: y[i][j] = x[i][j] * beta[i] + gamma[i] with one beta and
  * one gamma per ROW (the op's [rows x 1] matrices, passed as `rows` contiguous values).
  * Backward: dx = dy * beta[i]; dbeta[i] = sum_j dy*x; dgamma[i] = sum_j dy. */

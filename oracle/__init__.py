@@ -263,6 +263,35 @@ def swiglu_backward(x, w, v, b, c, beta, dy):
     return (dx, *outs)
 
 
+def row_sum_forward(x, average=False):
+    """MatrixSumOperation / MatrixAverageOperation: one value per row."""
+    x = _c(x)
+    y = np.empty(x.shape[0], x.dtype)
+    _fn("row_sum_forward", x.dtype)(_p(x), _p(y), x.shape[0], x.shape[1], int(average))
+    return y
+
+
+def row_sum_backward(dy, cols, average=False):
+    dy = _c(np.reshape(dy, -1))
+    dx = np.empty((dy.shape[0], cols), dy.dtype)
+    _fn("row_sum_backward", dy.dtype)(_p(dy), _p(dx), dy.shape[0], cols, int(average))
+    return dx
+
+
+def broadcast_forward(x, rows, cols):
+    x = _c(x)
+    y = np.empty((rows, cols), x.dtype)
+    _fn("broadcast_forward", x.dtype)(_p(x), x.shape[0], x.shape[1], _p(y), rows, cols)
+    return y
+
+
+def broadcast_backward(dy, in_rows, in_cols):
+    dy = _c(dy)
+    dx = np.empty((in_rows, in_cols), dy.dtype)
+    _fn("broadcast_backward", dy.dtype)(_p(dy), dy.shape[0], dy.shape[1], _p(dx), in_rows, in_cols)
+    return dx
+
+
 def gelu_forward(x):
     return _unary("gelu_forward", x)
 

@@ -384,6 +384,38 @@ void swiglu_backward(const T* x, const T* w, const T* v, const T* b, const T* c,
   }
 }
 
+// ---- MatrixSumOperation.cs:38-68 / MatrixAverageOperation.cs:38-67: LINQ Sum / Average per row
+template <typename T>
+void row_sum_forward(const T* x, T* y, int R, int C, int average) {
+  for (int i = 0; i < R; ++i) {
+    LinqSum<T> s;
+    for (int j = 0; j < C; ++j) s.add(x[(size_t)i * C + j]);
+    y[i] = average ? (T)(s.acc / (double)C) : s.result();   // LINQ Average divides the double sum
+  }
+}
+template <typename T>
+void row_sum_backward(const T* dy, T* dx, int R, int C, int average) {
+  for (int i = 0; i < R; ++i)
+    for (int j = 0; j < C; ++j) dx[(size_t)i * C + j] = average ? dy[i] / C : dy[i];
+}
+
+// ---- MatrixBroadcastOperation.cs:48-88: tile the input; the backward adds the tiles k outer, l inner
+template <typename T>
+void broadcast_forward(const T* x, int r, int c, T* y, int R, int C) {
+  for (int i = 0; i < R; ++i)
+    for (int j = 0; j < C; ++j) y[(size_t)i * C + j] = x[(size_t)(i % r) * c + (j % c)];
+}
+template <typename T>
+void broadcast_backward(const T* dy, int R, int C, T* dx, int r, int c) {
+  for (int i = 0; i < r; ++i)
+    for (int j = 0; j < c; ++j) {
+      T acc = 0;
+      for (int k = i; k < R; k += r)
+        for (int l = j; l < C; l += c) acc += dy[(size_t)k * C + l];
+      dx[(size_t)i * c + j] = acc;
+    }
+}
+
 // ---- HadamardProductOperation.cs:50-118 ---------------------------------------------------
 template <typename T>
 void hadamard_forward(const T* a, const T* b, T* y, size_t n) {
@@ -798,6 +830,18 @@ void adam_prad(T* w, T* m, T* v, const T* g, size_t n, T lr, T b1, T b2, T eps, 
                                   double beta, const T* dy, T* dx, T* dw, T* dv, T* db, T* dc,     \
                                   int R, int C) {                                                  \
     swiglu_backward<T>(x, w, v, b, c, beta, dy, dx, dw, dv, db, dc, R, C);                         \
+  }                                                                                                \
+  void oracle_row_sum_forward_##S(const T* x, T* y, int R, int C, int avg) {                       \
+    row_sum_forward<T>(x, y, R, C, avg);                                                           \
+  }                                                                                                \
+  void oracle_row_sum_backward_##S(const T* dy, T* dx, int R, int C, int avg) {                    \
+    row_sum_backward<T>(dy, dx, R, C, avg);                                                        \
+  }                                                                                                \
+  void oracle_broadcast_forward_##S(const T* x, int r, int c, T* y, int R, int C) {                \
+    broadcast_forward<T>(x, r, c, y, R, C);                                                        \
+  }                                                                                                \
+  void oracle_broadcast_backward_##S(const T* dy, int R, int C, T* dx, int r, int c) {             \
+    broadcast_backward<T>(dy, R, C, dx, r, c);                                                     \
   }                                                                                                \
   void oracle_gelu_forward_##S(const T* x, T* y, long long n) { gelu_forward<T>(x, y, (size_t)n); }\
   void oracle_gelu_backward_##S(const T* x, const T* dy, T* dx, long long n) {                     \

@@ -67,6 +67,11 @@ SIGNATURES = {
     "prad_softmax_backward": [vp, i32, vp, vp, vp, i64, i32],
     "prad_layernorm_forward": [vp, i32, vp, vp, vp, vp, i64, i32],
     "prad_layernorm_backward": [vp, i32, vp, vp, vp, vp, vp, i64, i32],
+    "prad_copy_2d": [vp, vp, sz, vp, sz, sz, sz],
+    "prad_row_sum_forward": [vp, i32, vp, vp, i64, i32, i32],
+    "prad_row_sum_backward": [vp, i32, vp, vp, i64, i32, i32],
+    "prad_broadcast_forward": [vp, i32, vp, i32, i32, vp, i32, i32],
+    "prad_broadcast_backward": [vp, i32, vp, i32, i32, vp, i32, i32],
     "prad_swiglu_forward": [vp, i32, vp, vp, vp, vp, vp, f64, vp, i64, i32],
     "prad_swiglu_backward": [vp, i32, vp, vp, vp, vp, vp, f64, vp, vp, vp, vp, vp, vp, i64, i32],
     "prad_swish_forward": [vp, i32, vp, vp, vp, i64],

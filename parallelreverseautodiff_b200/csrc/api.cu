@@ -271,6 +271,16 @@ prad_status prad_copy(prad_ctx* ctx, void* dst, const void* src, size_t bytes) {
   return PRAD_OK;
 }
 
+prad_status prad_copy_2d(prad_ctx* ctx, void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                         size_t width_bytes, size_t rows) {
+  PRAD_CHECK_CTX(ctx);
+  if (width_bytes == 0 || rows == 0) return PRAD_OK;
+  PRAD_REQUIRE(dst && src && dst_pitch >= width_bytes && src_pitch >= width_bytes, PRAD_ERR_INVALID,
+               "prad_copy_2d: null pointer or a pitch smaller than the row width");
+  PRAD_CUDA(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyDeviceToDevice, ctx->stream));
+  return PRAD_OK;
+}
+
 prad_status prad_upload(prad_ctx* ctx, void* dst, const void* src_host, size_t bytes) {
   PRAD_CHECK_CTX(ctx);
   PRAD_NOT_CAPTURING(ctx, "prad_upload");

@@ -198,6 +198,53 @@ rmsnorm_backward_kernel(const T* __restrict__ x, const T* __restrict__ g, const 
   }
 }
 
+// MatrixSumOperation.cs:45-50 / MatrixAverageOperation.cs:45-50: LINQ Sum / Average of a row
+// (double accumulator); backward :57-65 copies dOutput[i][0] (divided by cols for the average).
+template <typename T>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+row_sum_forward_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int cols, int average) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * ROW_WARPS;
+  for (int64_t r = warp; r < rows; r += nwarps) {
+    double s = 0.0;
+    for (int j = lane; j < cols; j += 32) s += (double)x[r * cols + j];
+    s = warp_sum(s);
+    if (lane == 0) y[r] = average ? (T)(s / (double)cols) : (T)s;
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(256)
+row_sum_backward_kernel(const T* __restrict__ dy, T* __restrict__ dx, int64_t n, int cols, int average) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const T d = dy[i / cols];
+    dx[i] = average ? div_rn(d, (T)cols) : d;
+  }
+}
+
+// MatrixBroadcastOperation.cs:55-62: y[i][j] = x[i % r][j % c]; backward :70-83 adds the tiles
+// into each input element k outer, l inner, in T -- one thread per input element, same order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+broadcast_forward_kernel(const T* __restrict__ x, int r, int c, T* __restrict__ y, int64_t n, int C) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    y[i] = x[(int64_t)((i / C) % r) * c + (int)((i % C) % c)];
+}
+template <typename T>
+__global__ void __launch_bounds__(256)
+broadcast_backward_kernel(const T* __restrict__ dy, int R, int C, T* __restrict__ dx, int r, int c) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < (int64_t)r * c; e += stride) {
+    const int i = (int)(e / c), j = (int)(e % c);
+    T acc = 0;
+    for (int k = i; k < R; k += r)
+      for (int l = j; l < C; l += c) acc = add_rn(acc, dy[(int64_t)k * C + l]);
+    dx[e] = acc;
+  }
+}
+
 // ---- short rows (cols <= 256): register-cached, several rows per warp -----------------------
 // A lane keeps E = ceil(cols/32) elements of each of R rows in registers, so every input is
 // read exactly once and R*E independent loads are in flight per lane; the R row reductions
@@ -569,6 +616,64 @@ prad_status prad_rmsnorm_backward(prad_ctx* ctx, prad_dtype dt, const void* x, c
 #define ARGS(T) (const T*)x, (const T*)g, (const T*)dy, (T*)dx, (T*)dg, rows, cols
   PRAD_ROW_LAUNCH(rmsnorm_backward_kernel, ARGS);
 #undef ARGS
+  return PRAD_OK;
+}
+
+prad_status prad_row_sum_forward(prad_ctx* ctx, prad_dtype dt, const void* x, void* y, int64_t rows, int cols,
+                                 int average) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0, PRAD_ERR_INVALID, "prad_row_sum_forward: bad argument");
+  if (rows == 0) return PRAD_OK;
+  PRAD_REQUIRE(y && (cols == 0 || x), PRAD_ERR_INVALID, "prad_row_sum_forward: null pointer");
+  PRAD_REQUIRE(!(average && cols == 0), PRAD_ERR_INVALID, "prad_row_sum_forward: average of an empty row");
+#define ARGS(T) (const T*)x, (T*)y, rows, cols, average
+  PRAD_ROW_LAUNCH(row_sum_forward_kernel, ARGS);
+#undef ARGS
+  return PRAD_OK;
+}
+
+prad_status prad_row_sum_backward(prad_ctx* ctx, prad_dtype dt, const void* dy, void* dx, int64_t rows, int cols,
+                                  int average) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0, PRAD_ERR_INVALID, "prad_row_sum_backward: bad argument");
+  const int64_t n = rows * cols;
+  if (n == 0) return PRAD_OK;
+  PRAD_REQUIRE(dy && dx, PRAD_ERR_INVALID, "prad_row_sum_backward: null pointer");
+  const int grid = stream_grid(ctx, n, 256, 8);
+  if (dt == PRAD_F32) row_sum_backward_kernel<float><<<grid, 256, 0, ctx->stream>>>((const float*)dy, (float*)dx, n, cols, average);
+  else row_sum_backward_kernel<double><<<grid, 256, 0, ctx->stream>>>((const double*)dy, (double*)dx, n, cols, average);
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
+
+prad_status prad_broadcast_forward(prad_ctx* ctx, prad_dtype dt, const void* x, int in_rows, int in_cols, void* y,
+                                   int out_rows, int out_cols) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && in_rows >= 0 && in_cols >= 0 && out_rows >= 0 && out_cols >= 0, PRAD_ERR_INVALID,
+               "prad_broadcast_forward: bad argument");
+  const int64_t n = (int64_t)out_rows * out_cols;
+  if (n == 0) return PRAD_OK;
+  PRAD_REQUIRE(in_rows > 0 && in_cols > 0, PRAD_ERR_SHAPE, "prad_broadcast_forward: empty input for a non-empty target");
+  PRAD_REQUIRE(x && y, PRAD_ERR_INVALID, "prad_broadcast_forward: null pointer");
+  const int grid = stream_grid(ctx, n, 256, 8);
+  if (dt == PRAD_F32) broadcast_forward_kernel<float><<<grid, 256, 0, ctx->stream>>>((const float*)x, in_rows, in_cols, (float*)y, n, out_cols);
+  else broadcast_forward_kernel<double><<<grid, 256, 0, ctx->stream>>>((const double*)x, in_rows, in_cols, (double*)y, n, out_cols);
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
+
+prad_status prad_broadcast_backward(prad_ctx* ctx, prad_dtype dt, const void* dy, int out_rows, int out_cols,
+                                    void* dx, int in_rows, int in_cols) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && in_rows >= 0 && in_cols >= 0 && out_rows >= 0 && out_cols >= 0, PRAD_ERR_INVALID,
+               "prad_broadcast_backward: bad argument");
+  const int64_t n = (int64_t)in_rows * in_cols;
+  if (n == 0) return PRAD_OK;
+  PRAD_REQUIRE(dx && ((int64_t)out_rows * out_cols == 0 || dy), PRAD_ERR_INVALID, "prad_broadcast_backward: null pointer");
+  const int grid = stream_grid(ctx, n, 256, 8);
+  if (dt == PRAD_F32) broadcast_backward_kernel<float><<<grid, 256, 0, ctx->stream>>>((const float*)dy, out_rows, out_cols, (float*)dx, in_rows, in_cols);
+  else broadcast_backward_kernel<double><<<grid, 256, 0, ctx->stream>>>((const double*)dy, out_rows, out_cols, (double*)dx, in_rows, in_cols);
+  PRAD_LAUNCHED(ctx);
   return PRAD_OK;
 }
 

@@ -486,6 +486,55 @@ class Engine:
                                            x.size, int(accumulate)))
         return dx, db
 
+    def row_sum_forward(self, x, average=False, out=None):
+        """MatrixSumOperation / MatrixAverageOperation: [rows x 1]."""
+        out = out or self.empty((x.shape[0], 1), x.dtype)
+        check(self.lib.prad_row_sum_forward(self.ctx, dtype_code(x.dtype), x.ptr, out.ptr, x.shape[0], x.shape[1],
+                                            int(average)))
+        return out
+
+    def row_sum_backward(self, dy, cols, average=False, out=None):
+        out = out or self.empty((dy.shape[0], cols), dy.dtype)
+        check(self.lib.prad_row_sum_backward(self.ctx, dtype_code(dy.dtype), dy.ptr, out.ptr, dy.shape[0], cols,
+                                             int(average)))
+        return out
+
+    def broadcast_forward(self, x, rows, cols, out=None):
+        out = out or self.empty((rows, cols), x.dtype)
+        check(self.lib.prad_broadcast_forward(self.ctx, dtype_code(x.dtype), x.ptr, x.shape[0], x.shape[1], out.ptr,
+                                              rows, cols))
+        return out
+
+    def broadcast_backward(self, dy, in_rows, in_cols, out=None):
+        out = out or self.empty((in_rows, in_cols), dy.dtype)
+        check(self.lib.prad_broadcast_backward(self.ctx, dtype_code(dy.dtype), dy.ptr, dy.shape[0], dy.shape[1],
+                                               out.ptr, in_rows, in_cols))
+        return out
+
+    def concatenate_forward(self, mats, out=None):
+        """MatrixConcatenateOperation: the inputs side by side (same row count)."""
+        rows, total = mats[0].shape[0], sum(m.shape[1] for m in mats)
+        if any(m.shape[0] != rows for m in mats):
+            raise _lib.PradError(_lib.ERR_SHAPE, "All input matrices must have the same number of rows.")
+        out = out or self.empty((rows, total), mats[0].dtype)
+        es, col = out.dtype.itemsize, 0
+        for m in mats:
+            check(self.lib.prad_copy_2d(self.ctx, out.ptr + col * es, total * es, m.ptr, m.shape[1] * es,
+                                        m.shape[1] * es, rows))
+            col += m.shape[1]
+        return out
+
+    def concatenate_backward(self, dy, widths):
+        """The column ranges of dOutput, one matrix per input."""
+        rows, total = dy.shape
+        es, col, outs = dy.dtype.itemsize, 0, []
+        for w in widths:
+            g = self.empty((rows, w), dy.dtype)
+            check(self.lib.prad_copy_2d(self.ctx, g.ptr, w * es, dy.ptr + col * es, total * es, w * es, rows))
+            outs.append(g)
+            col += w
+        return outs
+
     def swiglu_forward(self, x, w, v, b, c, beta, out=None):
         """SwigLUOperation: w, v, b, c hold one value per column of x."""
         out = out or self.empty(x.shape, x.dtype)

@@ -517,6 +517,32 @@ def test_swiglu(engine, dtype, shape):
         assert_close(got[k].numpy().reshape(-1), ref[k], bound, name)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(1, 1), (5, 3), (64, 96), (33, 4099)])
+def test_row_sum_average_broadcast_concatenate(engine, dtype, shape):
+    r = rng(shape[0] * 5 + shape[1])
+    x = normal(r, shape, 1, dtype)
+    X = engine.upload(x)
+    for avg in (False, True):
+        y = engine.row_sum_forward(X, avg).numpy().reshape(-1)
+        assert_close(y, O.row_sum_forward(x, avg), np.sqrt(shape[1]) if not avg else 1.0, "row sum")
+        dyv = normal(r, (shape[0], 1), 1, dtype)
+        np.testing.assert_array_equal(engine.row_sum_backward(engine.upload(dyv), shape[1], avg).numpy(),
+                                      O.row_sum_backward(dyv, shape[1], avg))
+    R, Cc = 2 * shape[0] + 1, 3 * shape[1] + 2
+    if R * Cc < 3_000_000:
+        np.testing.assert_array_equal(engine.broadcast_forward(X, R, Cc).numpy(), O.broadcast_forward(x, R, Cc))
+        dy = normal(r, (R, Cc), 1, dtype)
+        np.testing.assert_array_equal(engine.broadcast_backward(engine.upload(dy), *shape).numpy(),
+                                      O.broadcast_backward(dy, *shape))          # same order of additions: exact
+    other = normal(r, (shape[0], 7), 1, dtype)
+    cat = engine.concatenate_forward([X, engine.upload(other), X])
+    np.testing.assert_array_equal(cat.numpy(), np.concatenate([x, other, x], axis=1))
+    parts = engine.concatenate_backward(cat, [shape[1], 7, shape[1]])
+    for got, want in zip(parts, (x, other, x)):
+        np.testing.assert_array_equal(got.numpy(), want)
+
+
 def test_new_row_ops_reject_bad_arguments(engine):
     from parallelreverseautodiff_b200._lib import ERR_INVALID, PradError
     x = engine.zeros((4, 4), np.float32)
