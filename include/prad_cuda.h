@@ -97,6 +97,8 @@ const char* prad_version(void);
  *    9e-7 of the result for any K; 512 is 4 % faster at 1.8e-6);
  *  "tc_split_k" = "on" | "off"; "tc_persistent" = "on" | "off" (tf32b16 on the one-tile-per-CTA kernel);
  *  "tc_reserve_sms" = n: SMs the persistent GEMM leaves idle (default 0);
+ *  "tc_panel_n" = n: column tiles per panel of the persistent GEMM's tile walk (0 = automatic: two
+ *    panels when the column operand exceeds 40 MB, so that a panel of it stays in L2);
  *  "tc_pipeline" = "16x4" | "32x2" | "8x8" (k-block floats x stages of the tf32x3 kernel) */
 prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value);
 /* wait for everything enqueued on the context (what the managed code gets for free

@@ -47,6 +47,7 @@ struct prad_ctx {
   bool tc_pending_check = false;
   int tc_variant = 0;  // pipeline shape of the tensor-core GEMM (option "tc_pipeline")
   bool tc_split_k = true;  // option "tc_split_k": cut k across CTAs when the tile count wastes SMs
+  int tc_panel_n = 0;      // option "tc_panel_n": column tiles per panel of the persistent GEMM's tile walk (0 = automatic)
   int tc_chunk_k = 256;    // option "tc_chunk_k": k per accumulation chunk of the persistent GEMM
   int tc_reserve_sms = 0;  // option "tc_reserve_sms": SMs the persistent GEMM leaves free (for a collective's kernels)
   bool tc_persistent = true;  // option "tc_persistent": TF32+BF16 products run on the persistent kernel

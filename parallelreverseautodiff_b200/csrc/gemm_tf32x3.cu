@@ -598,6 +598,7 @@ struct TileSched {
   int tiles_m, tiles_n, splits;   // tile t -> (t % tiles_n, (t / tiles_n) % tiles_m, t / (tiles_n * tiles_m))
   int kb_per_split, total_kb;     // k-blocks per slice and in all
   int chunk_kb;                   // k-blocks per accumulation chunk
+  int panel_n;                    // column tiles per panel of the tile walk
   int64_t split_stride;           // elements between the partial products of consecutive slices
 };
 
@@ -665,10 +666,17 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
   };
 
   // tile t of this CTA: origin of the output tile and its k range
+  // Tiles are walked panel by panel: all row tiles of `panel_n` column tiles before the next panel, so
+  // that the column operand of a panel stays in L2 while the row operand streams past it.
   auto tile_of = [&](int t, int& m0, int& n0, int& z, int& kb0, int& num_kb) {
-    n0 = (t % ts.tiles_n) * BN;
-    m0 = ((t / ts.tiles_n) % ts.tiles_m) * BM;
-    z = t / (ts.tiles_n * ts.tiles_m);
+    const int per_slice = ts.tiles_n * ts.tiles_m;
+    z = t / per_slice;
+    const int t2 = t - z * per_slice;
+    const int p = t2 / (ts.tiles_m * ts.panel_n);
+    const int r = t2 - p * ts.tiles_m * ts.panel_n;
+    const int w = min(ts.panel_n, ts.tiles_n - p * ts.panel_n);
+    m0 = (r / w) * BM;
+    n0 = (p * ts.panel_n + r % w) * BN;
     kb0 = z * ts.kb_per_split;
     num_kb = min(ts.total_kb - kb0, ts.kb_per_split);
   };
@@ -1223,7 +1231,12 @@ static prad_status launch_tf32x3(prad_ctx* ctx, const SplitOperand& a, const Spl
   }
   auto launch = [&](int nsplit, int kbps, int64_t stride, float* out, int64_t ldo, bool vec_out, const Epi& ep) {
     if (persistent) {
-      TileSched ts{(int)grid.y, (int)grid.x, nsplit, kbps, total_kb, ctx->tc_chunk_k / p1::BK, stride};
+      // two panels when the column operand (N x k, 4 bytes per element in either scheme's main pieces)
+      // would not stay in L2 next to the streaming row operand
+      int panel_n = (int)grid.x;
+      if (ctx->tc_panel_n > 0) panel_n = ctx->tc_panel_n < (int)grid.x ? ctx->tc_panel_n : (int)grid.x;
+      else if ((int64_t)N * kp * 4 > ((int64_t)40 << 20) && grid.x >= 2) panel_n = ((int)grid.x + 1) / 2;
+      TileSched ts{(int)grid.y, (int)grid.x, nsplit, kbps, total_kb, ctx->tc_chunk_k / p1::BK, panel_n, stride};
       const int64_t total = tiles * nsplit;
       const int64_t sms = ctx->sm_count - ctx->tc_reserve_sms;
       const unsigned ctas = (unsigned)(total < sms ? total : sms);
