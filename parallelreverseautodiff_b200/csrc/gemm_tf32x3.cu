@@ -705,7 +705,10 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
             if (round > 0 && !mbar_wait(empty_bar(slot), (round - 1) & 1, err_flag, 1)) { ok = false; break; }
             const uint32_t st = base + slot * UNIT_BYTES;
             mbar_expect_tx(full_bar(slot), UNIT_BYTES);
-            if (half == 0) {   // unit H: a_hb 8 KB | a_lb 8 KB | b_hb 16 KB | b_lb 16 KB  (PMODE 3: a_h0 a_h1 b_h0 b_h1)
+            if (PMODE == 3) {  // one unit: A rows (h0 | h1) 16 KB, B rows (h0 | h1) 32 KB; x counts halves
+              tma_load_2d(st, &map_a_xb, full_bar(slot), 2 * x, m0);
+              tma_load_2d(st + 16 * 1024, &map_b_xb, full_bar(slot), 2 * x, n0);
+            } else if (half == 0) {   // unit H: a_hb 8 KB | a_lb 8 KB | b_hb 16 KB | b_lb 16 KB
               tma_load_2d(st, &map_a_xb, full_bar(slot), x, m0);
               tma_load_2d(st + 8 * 1024, &map_a_lb, full_bar(slot), x, m0);
               tma_load_2d(st + 16 * 1024, &map_b_xb, full_bar(slot), x, n0);
@@ -741,15 +744,16 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
           const uint32_t d_tmem = tmem_base + buf * (uint32_t)BN;
           const int kb_end = min(num_kb, (ch + 1) * ts.chunk_kb);
           for (int kb = ch * ts.chunk_kb; kb < kb_end && ok; ++kb) {
-            if (PMODE == 3) {   // one unit: a_h0 | a_h1 | b_h0 | b_h1, three FP16 products, smallest first
+            if (PMODE == 3) {   // one unit: A (h0 | h1 per row), B likewise; three FP16 products, smallest first
               constexpr uint32_t idesc_q = idesc_fp16();
               const uint32_t slot = g & (UNITS - 1);
               ok = mbar_wait(full_bar(slot), (g / UNITS) & 1, err_flag, 2);
               if (!ok) break;
               tc_fence_after();
               const uint32_t st = base + slot * UNIT_BYTES;
-              const uint64_t a_0 = kmajor_desc<64>(st), a_1 = kmajor_desc<64>(st + 8 * 1024);
-              const uint64_t b_0 = kmajor_desc<64>(st + 16 * 1024), b_1 = kmajor_desc<64>(st + 32 * 1024);
+              // rows of 128 bytes (128-byte swizzle): h0 at byte 0, h1 at byte 64, 16-k slices 32 bytes apart
+              const uint64_t a_0 = kmajor_desc<128>(st), a_1 = a_0 + 4;
+              const uint64_t b_0 = kmajor_desc<128>(st + 16 * 1024), b_1 = b_0 + 4;
 #pragma unroll
               for (int k = 0; k < BK / 16; ++k) {
                 const uint64_t adv = (uint64_t)((k * 16 * 2) >> 4);
@@ -979,13 +983,17 @@ __device__ __forceinline__ int shift_of(uint32_t absbits) {
   const int s = 14 - (e - 127);
   return s > 126 ? 126 : s;
 }
+// Both pieces of a row live in one array, interleaved per 32-k block: [h0 of k 0..31 | h1 of k 0..31 |
+// h0 of k 32..63 | ...], so that one 128-byte TMA row (128-byte swizzle) brings both pieces of a k-block
+// and a k-block of an operand is one TMA instruction.  Row pitch = 2 * kp halves.
+__device__ __forceinline__ int64_t il_index(int64_t k) { return (k >> 5) * 64 + (k & 31); }
 __device__ __forceinline__ void fp16_pieces(float xs, __half& p0, __half& p1) {
   p0 = __float2half_rn(xs);
   p1 = __float2half_rn(xs - __half2float(p0));   // the difference is exact in FP32
 }
 // src is rows x cols with k contiguous; one warp per row, two passes (the second hits L1/L2)
 __global__ void __launch_bounds__(256)
-split16_rows_kernel(const float* __restrict__ src, int64_t src_ld, __half* __restrict__ h0, __half* __restrict__ h1,
+split16_rows_kernel(const float* __restrict__ src, int64_t src_ld, __half* __restrict__ hh,
                     int* __restrict__ exps, int64_t dst_ld, int rows, int cols) {
   const int lane = threadIdx.x & 31;
   const bool vec = ((src_ld & 3) == 0) && (((uintptr_t)src & 15) == 0);
@@ -1007,8 +1015,7 @@ split16_rows_kernel(const float* __restrict__ src, int64_t src_ld, __half* __res
     const int sh = shift_of(mx);
     const float scale = pow2i(sh);
     if (lane == 0) exps[row] = -sh;
-    __half* d0 = h0 + row * dst_ld;
-    __half* d1 = h1 + row * dst_ld;
+    __half* d0 = hh + row * 2 * dst_ld;       // h0 of k at il_index(k), h1 32 halves further
     for (int c = lane * 4; c < dst_ld; c += 128) {
       float x[4];
       if (vec && c + 4 <= cols) {
@@ -1022,8 +1029,8 @@ split16_rows_kernel(const float* __restrict__ src, int64_t src_ld, __half* __res
       __align__(8) __half p1[4];
 #pragma unroll
       for (int q = 0; q < 4; ++q) fp16_pieces(x[q] * scale, p0[q], p1[q]);
-      *reinterpret_cast<uint2*>(d0 + c) = *reinterpret_cast<uint2*>(p0);
-      *reinterpret_cast<uint2*>(d1 + c) = *reinterpret_cast<uint2*>(p1);
+      *reinterpret_cast<uint2*>(d0 + il_index(c)) = *reinterpret_cast<uint2*>(p0);
+      *reinterpret_cast<uint2*>(d0 + il_index(c) + 32) = *reinterpret_cast<uint2*>(p1);
     }
   }
 }
@@ -1058,8 +1065,8 @@ absmax_cols_kernel(const float* __restrict__ src, int64_t ld, int rows, int cols
 }
 // src is k_rows x r_cols (k slow); dst is r_cols x dst_ld (k fast), row c scaled by 2^shift_of(umax[c])
 __global__ void __launch_bounds__(256)
-split16_transpose_kernel(const float* __restrict__ src, int64_t src_ld, __half* __restrict__ h0,
-                         __half* __restrict__ h1, const unsigned* __restrict__ umax, int* __restrict__ exps,
+split16_transpose_kernel(const float* __restrict__ src, int64_t src_ld, __half* __restrict__ hh,
+                         const unsigned* __restrict__ umax, int* __restrict__ exps,
                          int64_t dst_ld, int k_rows, int r_cols) {
   __shared__ float tile[64][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
@@ -1082,8 +1089,9 @@ split16_transpose_kernel(const float* __restrict__ src, int64_t src_ld, __half* 
     __half a0, a1, b0, b1;
     fp16_pieces(tile[2 * tx][j] * scale, a0, a1);
     fp16_pieces(tile[2 * tx + 1][j] * scale, b0, b1);
-    *reinterpret_cast<__half2*>(h0 + (int64_t)c2 * dst_ld + k) = __halves2half2(a0, b0);
-    *reinterpret_cast<__half2*>(h1 + (int64_t)c2 * dst_ld + k) = __halves2half2(a1, b1);
+    __half* d = hh + (int64_t)c2 * 2 * dst_ld + il_index(k);     // k is even: the pair stays inside one block
+    *reinterpret_cast<__half2*>(d) = __halves2half2(a0, b0);
+    *reinterpret_cast<__half2*>(d + 32) = __halves2half2(a1, b1);
   }
 }
 
@@ -1151,10 +1159,10 @@ struct SplitOperand {
   __nv_bfloat16* xb = nullptr;
   __nv_bfloat16* lb = nullptr;
   __nv_bfloat16* b0 = nullptr;   // MODE 2: pieces are b0, xb (= b1), lb (= b2)
-  // MODE 3: x * 2^-exps[row] = h0 + h1 (+ 2^-22 of it), both FP16; umax is scratch for the
-  // column maxima of a transposed source
+  // MODE 3: x * 2^-exps[row] = h0 + h1 (+ 2^-22 of it), both FP16, interleaved per 32-k block in
+  // the one array h0 (see il_index); umax is scratch for the column maxima of a transposed source
   __half* h0 = nullptr;
-  __half* h1 = nullptr;
+  __half* h1 = nullptr;   // unused
   int* exps = nullptr;
   unsigned* umax = nullptr;
 };
@@ -1176,10 +1184,11 @@ static prad_status launch_tf32x3(prad_ctx* ctx, const SplitOperand& a, const Spl
   CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo, ma_x, mb_x;
   bool ok = true;
   if (CFG::MODE == 3) {
-    ok = make_map(&ma_x, a.h0, M, (int)kp, kp, BM, CFG::BK, 2, true) && make_map(&ma_lo, a.h1, M, (int)kp, kp, BM, CFG::BK, 2, true) &&
-         make_map(&mb_x, b.h0, N, (int)kp, kp, BN, CFG::BK, 2, true) && make_map(&mb_lo, b.h1, N, (int)kp, kp, BN, CFG::BK, 2, true);
-    ma_hi = ma_x;
-    mb_hi = mb_x;
+    // interleaved pieces: a row is 2 kp halves, a k-block of 32 is one 128-byte box row (h0 | h1)
+    ok = make_map(&ma_x, a.h0, M, (int)(2 * kp), 2 * kp, BM, 2 * CFG::BK, 2, true) &&
+         make_map(&mb_x, b.h0, N, (int)(2 * kp), 2 * kp, BN, 2 * CFG::BK, 2, true);
+    ma_hi = ma_lo = ma_x;
+    mb_hi = mb_lo = mb_x;
   } else if (CFG::MODE == 2) {
     ok = make_map(&ma_hi, a.b0, M, (int)kp, kp, BM, CFG::BK, 2) && make_map(&ma_x, a.xb, M, (int)kp, kp, BM, CFG::BK, 2) &&
          make_map(&ma_lo, a.lb, M, (int)kp, kp, BM, CFG::BK, 2) && make_map(&mb_hi, b.b0, N, (int)kp, kp, BN, CFG::BK, 2) &&
@@ -1279,7 +1288,7 @@ static prad_status split_operand(prad_ctx* ctx, const float* src, int64_t ld, bo
   if (o.h0) {   // MODE 3: scaled FP16 pieces
     if (!transposed) {
       const int grid = (int)std::min<int64_t>(ceil_div(rows, 8), (int64_t)ctx->sm_count * 32);
-      split16_rows_kernel<<<grid, 256, 0, ctx->stream>>>(src, ld, o.h0, o.h1, o.exps, kp, rows, K);
+      split16_rows_kernel<<<grid, 256, 0, ctx->stream>>>(src, ld, o.h0, o.exps, kp, rows, K);
       PRAD_LAUNCHED(ctx);
       return PRAD_OK;
     }
@@ -1299,7 +1308,7 @@ static prad_status split_operand(prad_ctx* ctx, const float* src, int64_t ld, bo
     else absmax_cols_kernel<false><<<dim3(gx, gy), 256, 0, ctx->stream>>>(src, ld, K, rows, o.umax, cpb, rows_per_block);
     PRAD_LAUNCHED(ctx);
     dim3 grid((unsigned)ceil_div(rows, 32), (unsigned)ceil_div(kp, 64));
-    split16_transpose_kernel<<<grid, 256, 0, ctx->stream>>>(src, ld, o.h0, o.h1, o.umax, o.exps, kp, K, rows);
+    split16_transpose_kernel<<<grid, 256, 0, ctx->stream>>>(src, ld, o.h0, o.umax, o.exps, kp, K, rows);
     PRAD_LAUNCHED(ctx);
     return PRAD_OK;
   }
