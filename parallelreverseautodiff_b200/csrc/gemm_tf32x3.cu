@@ -580,11 +580,14 @@ __device__ __forceinline__ void epilogue_store_warp(float (&sum)[4][32], int lan
 //     i+1 (the two TMEM accumulators decouple them by two 256-k chunks).  Which CTA
 //     computes a tile does not change its result.  The last CTA to finish resets the
 //     counters for the next launch;
-//   * the operand ring holds four units of 48 KB instead of two stages of 96 KB: a k-block
-//     of 32 arrives as unit H (the four BF16 tiles a_hb, a_lb, b_hb, b_lb) and unit F (the
-//     two FP32 tiles a_hi, b_hi), each with its own full/empty barrier pair, so a unit is
-//     refilled as soon as the two or four MMAs that read it retire and three loads are in
-//     flight while one is multiplied.
+//   * the operand ring holds four units of 48 KB instead of two stages of 96 KB, each with its
+//     own full/empty barrier pair, so a unit is refilled as soon as the MMAs that read it retire
+//     and three loads are in flight while one is multiplied.  PMODE 1: a k-block of 32 arrives
+//     as unit H (the four BF16 tiles a_hb, a_lb, b_hb, b_lb) and unit F (the two FP32 tiles
+//     a_hi, b_hi).  PMODE 3: a k-block of 32 is one unit of two tiles whose 128-byte rows hold
+//     both FP16 pieces of a row (h0 | h1): two TMA instructions and 384 row requests per unit --
+//     with four tiles of 64-byte rows the TMA unit's request rate, not its bytes, held the kernel
+//     back (4 % slower; adding L2 prefetch requests on top cost another 10 %).
 namespace p1 {
 constexpr int BK = 32;
 constexpr int UNITS = 4;
