@@ -195,11 +195,11 @@ def measured_peaks():
 
 def gemm_traffic_bytes(rows, width, gemm):
     """DRAM bytes of one backward GEMM launch of the default kernel: one ncu capture of a 16384-row
-    launch (1.203 GB read + 0.270 GB written), scaled linearly in the rows -- the traffic is
+    launch (0.911 GB read + 0.259 GB written), scaled linearly in the rows -- the traffic is
     dominated by the row-proportional operand and result.  None for other kernels or widths."""
     if gemm != "auto" or width != 4096:
         return None
-    return 1.473e9 * rows / 16384.0
+    return 1.170e9 * rows / 16384.0
 
 
 def run_native(args, rank, world, local_rank):
@@ -333,7 +333,7 @@ def run_native(args, rank, world, local_rank):
                          "frac": (achieved_tflops / peaks["tensor_tflops"]) if achieved_tflops else None,
                          "traffic": gemm_traffic_bytes(rows, args.width, args.gemm),
                          "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one "
-                                           "16384 x 4096 x 4096 launch of the default kernel (1.473 GB), scaled by rows",
+                                           "16384 x 4096 x 4096 launch of the default kernel (1.170 GB), scaled by rows",
                          "kernel": "backward GEMMs (dW = A^T dZ, dA = dZ W^T)",
                          "peak_source": peaks["source"] + " dense bf16, sustained",
                          "launches_timed": n_gemm},
