@@ -1,25 +1,30 @@
-// FP32 GEMM on the 5th-generation tensor cores: C = alpha*op(A)*op(B) + beta*C computed as
-// three TF32 products per k-slice ("3xTF32"),
-//     a*b ~= a_hi*b_hi + a_lo*b_hi + a_hi*b_lo,   a_hi = tf32(a), a_lo = tf32(a - a_hi),
-// accumulated in FP32 in tensor memory.  The dropped a_lo*b_lo term is ~2^-22 relative, so
-// the result matches an FP32 FMA chain to well inside the 1e-5 PRADLite tolerance.
+// FP32 GEMM on the 5th-generation tensor cores: C = alpha*op(A)*op(B) + beta*C computed from
+// split operands, accumulated in FP32 in tensor memory.  Four split schemes share the code:
+//   fp16x3  (MODE 3, default): rows scaled by powers of two, two FP16 pieces per element,
+//           a*b ~= h1*h0' + h0*h1' + h0*h0'  (persistent kernel only);
+//   tf32b16 (MODE 1): a_hi*b_hi in TF32 plus two BF16 correction products;
+//   tf32x3  (MODE 0): a_hi*b_hi + a_lo*b_hi + a_hi*b_lo, a_hi = tf32(a), a_lo = tf32(a - a_hi);
+//   bf16x3  (MODE 2): six BF16 products of three-piece operands.
+// The dropped lowest-order term is ~2^-22 relative in every scheme, so the result matches an FP32
+// FMA chain to well inside the 1e-5 PRADLite tolerance.
 //
-// Structure of one CTA (320 threads, one 128 x 256 output tile; a k-block is one swizzle
-// atom wide, by default 16 floats = 64 bytes with 4 stages in flight):
-//   warp 0     TMA producer: cp.async.bulk.tensor loads of the four operand tiles of a
-//              k-block (A_hi, A_lo, B_hi, B_lo) into a ring of shared-memory stages;
-//   warp 1     allocates tensor memory, then one lane issues tcgen05.mma (kind::tf32,
-//              M=128, N=256, K=8): 3 products per 8-wide k-slice of a stage, releases the stage
-//              with tcgen05.commit, and finally signals the accumulator;
+// Two kernels.  gemm_tf32x3_kernel: one CTA = one 128 x 256 output tile (MODES 0, 1, 2);
+// gemm_persistent_kernel: one CTA per SM walking tiles (MODES 1 and 3; see its own comment).
+// Both have 320 threads:
+//   warp 0     TMA producer: cp.async.bulk.tensor loads of the operand tiles of a k-block into
+//              a ring of shared-memory stages;
+//   warp 1     allocates tensor memory, then one lane issues tcgen05.mma (M=128, N=256),
+//              releases each stage with tcgen05.commit, and signals finished accumulators;
 //   warps 2-9  epilogue: after every chunk of 256 k they tcgen05.ld that chunk's 128 x 256
 //              accumulator (each warp its own 32-lane TMEM sub-partition and half of the
-//              columns) and add it to running sums in registers; at the end they apply
-//              alpha/beta, bias, activation or activation derivative and store 128-byte
-//              row segments.  Two TMEM accumulators alternate, so chunk c+1 is multiplied
-//              while chunk c is drained.
-// Both operands are consumed K-major (k contiguous).  A pre-pass writes the hi/lo pair of
-// each operand into scratch in that orientation (transposing when the caller's matrix has
-// the other orientation), padded so every TMA coordinate is 16-byte aligned.
+//              columns) and add it to running sums in registers (the tensor core truncates when
+//              it adds into its accumulator; see the MMA issuer); at the end they apply the
+//              power-of-two scales, alpha, beta and the bias and store.  Two TMEM accumulators
+//              alternate, so chunk c+1 is multiplied while chunk c is drained.  Activations
+//              are not applied here: gemm_tf32x3() runs them as separate passes.
+// Both operands are consumed K-major (k contiguous).  A pre-pass writes the pieces of each operand
+// into scratch in that orientation (transposing when the caller's matrix has the other
+// orientation), padded so every TMA coordinate is 16-byte aligned.
 //
 // Every wait on an mbarrier is bounded: after SPIN_LIMIT polls the waiter raises a global
 // error flag (which all other waiters poll and obey), the CTA drains, frees its tensor
