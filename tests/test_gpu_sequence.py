@@ -88,3 +88,31 @@ def test_c3_bptt_replayed(engine):
     for ga, gb in zip(grads(a.net), grads(b.net)):
         np.testing.assert_array_equal(ga.numpy(), gb.numpy())
     seq.close()
+
+
+def test_tensor_core_product_replayed(engine):
+    """The persistent tensor-core GEMM (operand passes, dynamic tile hand-out, split-K combine)
+    inside a recorded sequence: replays give the bits of the direct call, every time."""
+    engine.set_option("gemm_f32", "fp16x3")
+    try:
+        r = np.random.default_rng(9)
+        A = engine.upload(r.standard_normal((640, 1100)).astype(np.float32))
+        B = engine.upload(r.standard_normal((1100, 520)).astype(np.float32))
+        dC = engine.upload(r.standard_normal((640, 520)).astype(np.float32))
+        dA, dB = engine.empty((640, 1100), np.float32), engine.empty((1100, 520), np.float32)
+
+        def step():
+            engine.matmul_backward(A, B, dC, dA=dA, dB=dB)
+
+        step()
+        want = dA.numpy(), dB.numpy()
+        seq = engine.record(step)
+        for _ in range(3):
+            engine.zero_(dA)
+            engine.zero_(dB)
+            seq.launch()
+            np.testing.assert_array_equal(dA.numpy(), want[0])
+            np.testing.assert_array_equal(dB.numpy(), want[1])
+        seq.close()
+    finally:
+        engine.set_option("gemm_f32", "auto")
