@@ -47,6 +47,8 @@ def parse():
     ap.add_argument("--width", type=int, default=WIDTH)
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--clip", default="reference", choices=["reference", "global_norm", "none"])
+    ap.add_argument("--dp-mode", default="overlap", choices=["overlap", "end"],
+                    help="N > 1: all-reduce each weight gradient beside the backward, or all of them in one collective after it")
     ap.add_argument("--no-sequence", action="store_true",
                     help="c1..c4: call the entry points every step instead of replaying a recorded launch sequence")
     ap.add_argument("--opt", action="append", default=[], metavar="KEY=VALUE",
@@ -232,7 +234,8 @@ def run_native(args, rank, world, local_rank):
     clip = {"reference": E.CLIP_REFERENCE, "global_norm": E.CLIP_GLOBAL_NORM, "none": E.CLIP_NONE}[args.clip]
     sizes = [args.width] * (args.layers + 1)
     net = FeedForwardNetwork(eng, np.float32, sizes, hidden_act=E.ACT_GELU, output_act=E.ACT_GELU,
-                             loss="mse", use_bias=False, clip_mode=clip, rank=rank, world=world)
+                             loss="mse", use_bias=False, clip_mode=clip, rank=rank, world=world,
+                             dp_overlap=args.dp_mode == "overlap")
     net.Parameters.LearningRate = args.lr
     wr = np.random.default_rng(42)  # identical weights on every rank
     net.set_weights([(wr.standard_normal((args.width, args.width), dtype=np.float32)
@@ -325,7 +328,7 @@ def run_native(args, rank, world, local_rank):
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"C5 data-parallel MLP {args.layers}x({args.width}x{args.width}, GELU), "
                                    f"MSE, global batch {args.batch}, clip={args.clip} + Adam",
-                       "global_batch": args.batch, "rows_per_gpu": rows, "parallelism": f"dp{world}",
+                       "global_batch": args.batch, "rows_per_gpu": rows, "parallelism": f"dp{world}", "dp_mode": args.dp_mode if world > 1 else None,
                        "gemm": args.gemm, "lr": args.lr, "l2": "inputs larger than L2 (activations >= 1 GiB per layer)"},
             "tflops": flops_step / (ms_step * 1e-3) / 1e12,
             "roofline": {"bound": "tensor", "achieved": achieved_tflops, "peak": peaks["tensor_tflops"],

@@ -56,8 +56,11 @@ def row_shard(total_rows: int, rank: int, world: int):
 class FeedForwardNetwork:
     def __init__(self, eng: E.Engine, dtype, sizes: Sequence[int], hidden_act=E.ACT_LEAKY_RELU,
                  output_act=E.ACT_NONE, softmax_output=False, loss="mse", use_bias=True,
-                 clip_mode=E.CLIP_REFERENCE, rank=0, world=1):
+                 clip_mode=E.CLIP_REFERENCE, rank=0, world=1, dp_overlap=True):
+        """dp_overlap: all-reduce each weight gradient right after its product (on the communication
+        stream, beside the rest of the backward), or all gradients in one collective at the end."""
         self.eng = eng
+        self.dp_overlap = dp_overlap
         self.dtype = np.dtype(dtype)
         self.sizes = list(sizes)
         self.L = len(sizes) - 1
@@ -76,7 +79,13 @@ class FeedForwardNetwork:
                 self.b.append(eng.zeros((1, sizes[l + 1]), dtype))
         params = self.W + self.b
         self.params = params
-        self.grads = [eng.zeros(p.shape, dtype) for p in params]
+        # one allocation for all gradients, so that they can also travel as one collective
+        sizes_ = [int(np.prod(p.shape)) for p in params]
+        self._grad_all = eng.zeros((sum(sizes_),), dtype)
+        self.grads, off = [], 0
+        for p, n in zip(params, sizes_):
+            self.grads.append(self._grad_all.view(p.shape, off))
+            off += n
         self.m = [eng.zeros(p.shape, dtype) for p in params]
         self.v = [eng.zeros(p.shape, dtype) for p in params]
         self.dW = self.grads[: self.L]
@@ -168,11 +177,11 @@ class FeedForwardNetwork:
             e.matmul_backward(self.A[l - 1], None, cur, dB=self.dW[l - 1], need_dA=False)
             if probe:
                 probe("gemm", False)
-            if self.world > 1:
+            if self.world > 1 and self.dp_overlap:
                 e.dp_allreduce(self.dW[l - 1])
             if self.use_bias:
                 e.add_broadcast_backward(cur, dbias=self.db[l - 1])
-                if self.world > 1:
+                if self.world > 1 and self.dp_overlap:
                     e.dp_allreduce(self.db[l - 1])
             if l > 1 or need_dx:
                 below = self.acts[l - 2] if l > 1 else E.ACT_NONE
@@ -189,6 +198,8 @@ class FeedForwardNetwork:
                 cur = nxt
         self.dX = cur
         if self.world > 1:
+            if not self.dp_overlap:
+                e.dp_allreduce(self._grad_all)
             e.dp_wait()
 
     # ---------------------------------------------------------------- clip + Adam
