@@ -33,6 +33,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "act_math.cuh"
@@ -1175,17 +1176,25 @@ struct SplitOperand {
   unsigned* umax = nullptr;
 };
 
+// cudaFuncSetAttribute applies to the current device only: once per kernel and device (a second,
+// concurrent call for the same pair is harmless)
+template <class F>
+static cudaError_t reserve_smem(F kernel, int bytes, int device, std::atomic<uint64_t>& done) {
+  const uint64_t bit = 1ull << (device & 63);
+  if (done.load(std::memory_order_acquire) & bit) return cudaSuccess;
+  const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) done.fetch_or(bit, std::memory_order_release);
+  else (void)cudaGetLastError();
+  return e;
+}
+
 template <class CFG>
 static prad_status launch_tf32x3(prad_ctx* ctx, const SplitOperand& a, const SplitOperand& b, int M, int N,
                                  int64_t kp, float* C, int64_t ldc, bool vecC, const Epi& epi) {
   constexpr bool ONLY_PERSISTENT = CFG::MODE == 3;
   if constexpr (!ONLY_PERSISTENT) {
-    static std::once_flag attr_once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(attr_once, [] {
-      attr_err = cudaFuncSetAttribute(gemm_tf32x3_kernel<CFG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      CFG::SMEM_BYTES);
-    });
+    static std::atomic<uint64_t> attr_done{0};
+    const cudaError_t attr_err = reserve_smem(gemm_tf32x3_kernel<CFG>, CFG::SMEM_BYTES, ctx->device, attr_done);
     PRAD_REQUIRE(attr_err == cudaSuccess, PRAD_ERR_CUDA, "gemm tf32x3: cannot reserve %d bytes of shared memory: %s",
                  CFG::SMEM_BYTES, cudaGetErrorString(attr_err));
   }
@@ -1237,12 +1246,8 @@ static prad_status launch_tf32x3(prad_ctx* ctx, const SplitOperand& a, const Spl
   constexpr int PMODE = CFG::MODE == 3 ? 3 : 1;
   const bool persistent = ONLY_PERSISTENT || (CFG::MODE == 1 && CFG::BK == p1::BK && ctx->tc_persistent);
   if (persistent) {
-    static std::once_flag p_once;
-    static cudaError_t p_err = cudaSuccess;
-    std::call_once(p_once, [] {
-      p_err = cudaFuncSetAttribute(gemm_persistent_kernel<PMODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   p1::SMEM_BYTES);
-    });
+    static std::atomic<uint64_t> p_done{0};
+    const cudaError_t p_err = reserve_smem(gemm_persistent_kernel<PMODE>, p1::SMEM_BYTES, ctx->device, p_done);
     PRAD_REQUIRE(p_err == cudaSuccess, PRAD_ERR_CUDA, "gemm (persistent): cannot reserve %d bytes of shared memory: %s",
                  p1::SMEM_BYTES, cudaGetErrorString(p_err));
   }
