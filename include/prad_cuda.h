@@ -305,6 +305,15 @@ prad_status prad_broadcast_forward(prad_ctx* ctx, prad_dtype dt, const void* x, 
                                    int out_rows, int out_cols);
 prad_status prad_broadcast_backward(prad_ctx* ctx, prad_dtype dt, const void* dy, int out_rows, int out_cols,
                                     void* dx, int in_rows, int in_cols);
+/* BatchNormalizationOperation.cs:52-158, as written: the whole matrix is one population, computed
+ * in double.  Its Forward normalises with the SUM of the elements and the sum of squared deviations
+ * from that sum (the local variables at that point, EPSILON 1e-6); its Backward reads the fields
+ * mean = sum / n and var = that second sum / n.  `stats` is the op's state on the device:
+ * 4 doubles { mean, var, sum, second sum }, written by forward, read by backward. */
+prad_status prad_batchnorm_forward(prad_ctx* ctx, prad_dtype dt, const void* x, void* y, void* stats, int64_t rows,
+                                   int cols);
+prad_status prad_batchnorm_backward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* stats, const void* dy,
+                                    void* dx, int64_t rows, int cols);
 /* ScaleAndShiftOperation.cs:55-106: y[i][j] = x[i][j] * beta[i] + gamma[i] with one beta and
  * one gamma per ROW (the op's [rows x 1] matrices, passed as `rows` contiguous values).
  * Backward: dx = dy * beta[i]; dbeta[i] = sum_j dy*x; dgamma[i] = sum_j dy. */

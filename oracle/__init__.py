@@ -292,6 +292,24 @@ def broadcast_backward(dy, in_rows, in_cols):
     return dx
 
 
+def batchnorm_forward(x):
+    """BatchNormalizationOperation as written.  Returns (y, stats) with stats = [this.mean, this.var] (float64)."""
+    x = _c(x)
+    y = np.empty_like(x)
+    stats = np.zeros(2, np.float64)
+    _fn("batchnorm_forward", x.dtype)(_p(x), _p(y), _p(stats), x.shape[0], x.shape[1])
+    return y, stats
+
+
+def batchnorm_backward(x, stats, dy):
+    x = _c(x)
+    dy = _c(dy, x.dtype)
+    stats = np.ascontiguousarray(stats, np.float64)
+    dx = np.empty_like(x)
+    _fn("batchnorm_backward", x.dtype)(_p(x), _p(stats), _p(dy), _p(dx), x.shape[0], x.shape[1])
+    return dx
+
+
 def gelu_forward(x):
     return _unary("gelu_forward", x)
 

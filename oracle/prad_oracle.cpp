@@ -416,6 +416,33 @@ void broadcast_backward(const T* dy, int R, int C, T* dx, int r, int c) {
     }
 }
 
+// ---- BatchNormalizationOperation.cs:52-158, as written: the whole matrix is one population; the
+// variance loop and the normalisation use the local `mean` and `var`, which at that point hold the
+// SUM of the elements and the SUM of squared deviations from that sum (the fields this.mean and
+// this.var, divided by n, are what the backward reads).  Double arithmetic, stored back in T.
+template <typename T>
+void batchnorm_forward(const T* x, T* y, double* stats, int R, int C) {
+  const size_t n = (size_t)R * C;
+  double mean = 0, var = 0;
+  for (size_t i = 0; i < n; ++i) mean += (double)x[i];
+  for (size_t i = 0; i < n; ++i) var += std::pow((double)x[i] - mean, 2);
+  stats[0] = mean / (double)n;
+  stats[1] = var / (double)n;
+  for (size_t i = 0; i < n; ++i) y[i] = (T)(((double)x[i] - mean) / std::sqrt(var + 1E-6));
+}
+template <typename T>
+void batchnorm_backward(const T* x, const double* stats, const T* dy, T* dx, int R, int C) {
+  const size_t n = (size_t)R * C;
+  for (size_t i = 0; i < n; ++i) {
+    double xm = (double)x[i] - stats[0];
+    double inv = 1 / std::sqrt(stats[1] + 1E-6);
+    double dy_dvar = -0.5 * xm * std::pow(inv, 3);
+    double dy_dmean = -inv / (double)n;
+    double dvar_dx = 2 * xm / (double)n;
+    dx[i] = (T)((inv + (dy_dvar * dvar_dx) + dy_dmean) * (double)dy[i]);
+  }
+}
+
 // ---- HadamardProductOperation.cs:50-118 ---------------------------------------------------
 template <typename T>
 void hadamard_forward(const T* a, const T* b, T* y, size_t n) {
@@ -842,6 +869,13 @@ void adam_prad(T* w, T* m, T* v, const T* g, size_t n, T lr, T b1, T b2, T eps, 
   }                                                                                                \
   void oracle_broadcast_backward_##S(const T* dy, int R, int C, T* dx, int r, int c) {             \
     broadcast_backward<T>(dy, R, C, dx, r, c);                                                     \
+  }                                                                                                \
+  void oracle_batchnorm_forward_##S(const T* x, T* y, double* stats, int R, int C) {               \
+    batchnorm_forward<T>(x, y, stats, R, C);                                                       \
+  }                                                                                                \
+  void oracle_batchnorm_backward_##S(const T* x, const double* stats, const T* dy, T* dx, int R,   \
+                                     int C) {                                                      \
+    batchnorm_backward<T>(x, stats, dy, dx, R, C);                                                 \
   }                                                                                                \
   void oracle_gelu_forward_##S(const T* x, T* y, long long n) { gelu_forward<T>(x, y, (size_t)n); }\
   void oracle_gelu_backward_##S(const T* x, const T* dy, T* dx, long long n) {                     \

@@ -72,6 +72,8 @@ SIGNATURES = {
     "prad_row_sum_backward": [vp, i32, vp, vp, i64, i32, i32],
     "prad_broadcast_forward": [vp, i32, vp, i32, i32, vp, i32, i32],
     "prad_broadcast_backward": [vp, i32, vp, i32, i32, vp, i32, i32],
+    "prad_batchnorm_forward": [vp, i32, vp, vp, vp, i64, i32],
+    "prad_batchnorm_backward": [vp, i32, vp, vp, vp, vp, i64, i32],
     "prad_swiglu_forward": [vp, i32, vp, vp, vp, vp, vp, f64, vp, i64, i32],
     "prad_swiglu_backward": [vp, i32, vp, vp, vp, vp, vp, f64, vp, vp, vp, vp, vp, vp, i64, i32],
     "prad_swish_forward": [vp, i32, vp, vp, vp, i64],

@@ -203,6 +203,59 @@ static int swiglu_bands(const prad_ctx* ctx, int64_t rows, int cols) {
   return (int)(bands < 1 ? 1 : bands);
 }
 
+// ---------------------------------------------------------------- BatchNormalization
+// BatchNormalizationOperation.cs:52-158, as written: one population over the whole matrix; the
+// variance loop and the normalisation use the SUM S of the elements and the sum V of squared
+// deviations from S (the local variables at that point), while the fields read by the backward
+// are S / n and V / n.  Everything in double.  stats (device, 4 doubles) = { S/n, V/n, S, V }.
+template <typename T>
+__global__ void __launch_bounds__(LOSS_THREADS)
+bn_partial_kernel(const T* __restrict__ x, const double* __restrict__ stats, double* __restrict__ partial,
+                  int64_t n, int second) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const double S = second ? stats[2] : 0.0;
+  double acc = 0.0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const double v = (double)x[i];
+    if (second) { const double d = __dsub_rn(v, S); acc += __dmul_rn(d, d); }
+    else acc += v;
+  }
+  double s = block_sum_d<LOSS_THREADS>(acc);
+  if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+__global__ void bn_final_kernel(const double* __restrict__ partial, int nblocks, double* stats, double n, int second) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    double s = 0.0;
+    for (int b = 0; b < nblocks; ++b) s += partial[b];
+    stats[second ? 3 : 2] = s;
+    stats[second ? 1 : 0] = s / n;
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(LOSS_THREADS)
+bn_forward_kernel(const T* __restrict__ x, const double* __restrict__ stats, T* __restrict__ y, int64_t n) {
+  const double S = stats[2], den = sqrt(__dadd_rn(stats[3], 1E-6));
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    y[i] = (T)__ddiv_rn(__dsub_rn((double)x[i], S), den);
+}
+template <typename T>
+__global__ void __launch_bounds__(LOSS_THREADS)
+bn_backward_kernel(const T* __restrict__ x, const double* __restrict__ stats, const T* __restrict__ dy,
+                   T* __restrict__ dx, int64_t n) {
+  const double mean = stats[0], nn = (double)n;
+  const double inv = __ddiv_rn(1.0, sqrt(__dadd_rn(stats[1], 1E-6)));
+  const double inv3 = __dmul_rn(__dmul_rn(inv, inv), inv);
+  const double dy_dmean = __ddiv_rn(-inv, nn);
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const double xm = __dsub_rn((double)x[i], mean);
+    const double dy_dvar = __dmul_rn(__dmul_rn(-0.5, xm), inv3);
+    const double dvar_dx = __ddiv_rn(__dmul_rn(2.0, xm), nn);
+    dx[i] = (T)__dmul_rn(__dadd_rn(__dadd_rn(inv, __dmul_rn(dy_dvar, dvar_dx)), dy_dmean), (double)dy[i]);
+  }
+}
+
 // ---------------------------------------------------------------- embedding
 // EmbeddingOperation.cs:56-60: out[i] = W[(int)input[i,0]]
 template <typename T>
@@ -457,6 +510,45 @@ prad_status prad_swiglu_backward(prad_ctx* ctx, prad_dtype dt, const void* x, co
   }
   if (dt == PRAD_F32) swiglu_final_kernel<float><<<cb, 128, 0, ctx->stream>>>((const double*)ctx->ws, bands, cols, (float*)dw, (float*)dv, (float*)db, (float*)dc);
   else swiglu_final_kernel<double><<<cb, 128, 0, ctx->stream>>>((const double*)ctx->ws, bands, cols, (double*)dw, (double*)dv, (double*)db, (double*)dc);
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
+
+prad_status prad_batchnorm_forward(prad_ctx* ctx, prad_dtype dt, const void* x, void* y, void* stats, int64_t rows,
+                                   int cols) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0, PRAD_ERR_INVALID, "prad_batchnorm_forward: bad argument");
+  const int64_t n = rows * cols;
+  if (n == 0) return PRAD_OK;
+  PRAD_REQUIRE(x && y && stats, PRAD_ERR_INVALID, "prad_batchnorm_forward: null pointer");
+  const int grid = stream_grid(ctx, n, LOSS_THREADS * 4, 4);
+  prad_status st = ensure_workspace(ctx, (size_t)grid * sizeof(double));
+  if (st) return st;
+  double* part = (double*)ctx->ws;
+  double* sd = (double*)stats;
+  for (int second = 0; second < 2; ++second) {
+    if (dt == PRAD_F32) bn_partial_kernel<float><<<grid, LOSS_THREADS, 0, ctx->stream>>>((const float*)x, sd, part, n, second);
+    else bn_partial_kernel<double><<<grid, LOSS_THREADS, 0, ctx->stream>>>((const double*)x, sd, part, n, second);
+    PRAD_LAUNCHED(ctx);
+    bn_final_kernel<<<1, 32, 0, ctx->stream>>>(part, grid, sd, (double)n, second);
+    PRAD_LAUNCHED(ctx);
+  }
+  if (dt == PRAD_F32) bn_forward_kernel<float><<<grid, LOSS_THREADS, 0, ctx->stream>>>((const float*)x, sd, (float*)y, n);
+  else bn_forward_kernel<double><<<grid, LOSS_THREADS, 0, ctx->stream>>>((const double*)x, sd, (double*)y, n);
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
+
+prad_status prad_batchnorm_backward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* stats, const void* dy,
+                                    void* dx, int64_t rows, int cols) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0, PRAD_ERR_INVALID, "prad_batchnorm_backward: bad argument");
+  const int64_t n = rows * cols;
+  if (n == 0) return PRAD_OK;
+  PRAD_REQUIRE(x && stats && dy && dx, PRAD_ERR_INVALID, "prad_batchnorm_backward: null pointer");
+  const int grid = stream_grid(ctx, n, LOSS_THREADS * 4, 4);
+  if (dt == PRAD_F32) bn_backward_kernel<float><<<grid, LOSS_THREADS, 0, ctx->stream>>>((const float*)x, (const double*)stats, (const float*)dy, (float*)dx, n);
+  else bn_backward_kernel<double><<<grid, LOSS_THREADS, 0, ctx->stream>>>((const double*)x, (const double*)stats, (const double*)dy, (double*)dx, n);
   PRAD_LAUNCHED(ctx);
   return PRAD_OK;
 }

@@ -535,6 +535,20 @@ class Engine:
             col += w
         return outs
 
+    def batchnorm_forward(self, x, out=None):
+        """BatchNormalizationOperation as written.  Returns (y, stats) with stats a device [1 x 4] float64."""
+        y = out or self.empty(x.shape, x.dtype)
+        stats = self.zeros((1, 4), np.float64)
+        check(self.lib.prad_batchnorm_forward(self.ctx, dtype_code(x.dtype), x.ptr, y.ptr, stats.ptr, x.shape[0],
+                                              x.shape[1]))
+        return y, stats
+
+    def batchnorm_backward(self, x, stats, dy, out=None):
+        out = out or self.empty(x.shape, x.dtype)
+        check(self.lib.prad_batchnorm_backward(self.ctx, dtype_code(x.dtype), x.ptr, stats.ptr, dy.ptr, out.ptr,
+                                               x.shape[0], x.shape[1]))
+        return out
+
     def swiglu_forward(self, x, w, v, b, c, beta, out=None):
         """SwigLUOperation: w, v, b, c hold one value per column of x."""
         out = out or self.empty(x.shape, x.dtype)

@@ -543,6 +543,21 @@ def test_row_sum_average_broadcast_concatenate(engine, dtype, shape):
         np.testing.assert_array_equal(got.numpy(), want)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(1, 1), (5, 7), (64, 96), (300, 1000)])
+def test_batchnorm_as_written(engine, dtype, shape):
+    r = rng(shape[0] + 11 * shape[1])
+    x, dy = normal(r, shape, 1.0, dtype) + dtype(0.3), normal(r, shape, 1.0, dtype)
+    X, DY = engine.upload(x), engine.upload(dy)
+    y_ref, st_ref = O.batchnorm_forward(x)
+    y, st = engine.batchnorm_forward(X)
+    n = shape[0] * shape[1]
+    assert_close(st.numpy().reshape(-1)[:2], st_ref, np.array([np.sqrt(n) / n * 4, max(st_ref[1], 1.0)]), "mean, var")
+    assert_close(y.numpy(), y_ref, np.abs(y_ref) + 1e-3, "y")
+    dx = engine.batchnorm_backward(X, st, DY)
+    assert_close(dx.numpy(), O.batchnorm_backward(x, st_ref, dy), np.abs(dy) * 2 + 1e-30, "dx")
+
+
 def test_new_row_ops_reject_bad_arguments(engine):
     from parallelreverseautodiff_b200._lib import ERR_INVALID, PradError
     x = engine.zeros((4, 4), np.float32)
