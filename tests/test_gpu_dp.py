@@ -11,7 +11,7 @@ import torch.multiprocessing as mp
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, id_path, out_dir):
+def _worker(rank, world, id_path, out_dir, overlap=True):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     import time
 
@@ -37,7 +37,7 @@ def _worker(rank, world, id_path, out_dir):
     t = r.standard_normal((batch, sizes[-1])).astype(np.float32)
     Ws = [(r.standard_normal((sizes[i], sizes[i + 1])) * np.sqrt(2.0 / sizes[i])).astype(np.float32) for i in range(2)]
     net = FeedForwardNetwork(eng, np.float32, sizes, hidden_act=E.ACT_GELU, output_act=E.ACT_GELU, loss="mse",
-                             use_bias=True, clip_mode=E.CLIP_REFERENCE, rank=rank, world=world)
+                             use_bias=True, clip_mode=E.CLIP_REFERENCE, rank=rank, world=world, dp_overlap=overlap)
     net.set_weights(Ws)
     a, b = row_shard(batch, rank, world)
     net._ensure_buffers(b - a)
@@ -54,11 +54,12 @@ def _worker(rank, world, id_path, out_dir):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_gpu_gradients_match_oracle(tmp_path):
+@pytest.mark.parametrize("overlap", [True, False], ids=["per-layer all-reduce", "one collective after the backward"])
+def test_two_gpu_gradients_match_oracle(tmp_path, overlap):
     import oracle as O
 
     world = 2
-    mp.spawn(_worker, args=(world, str(tmp_path / "nccl_id"), str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, str(tmp_path / "nccl_id"), str(tmp_path), overlap), nprocs=world, join=True)
     r = np.random.default_rng(42)
     batch, sizes = 96, [40, 64, 24]
     x = r.standard_normal((batch, sizes[0])).astype(np.float32)
