@@ -453,6 +453,39 @@ prad_status prad_graph_value_gradient(prad_graph* g, int value, void** out_grad)
 /* How many consumers each value had in the last backward (BackwardDependencyCounts). */
 prad_status prad_graph_consumer_count(prad_graph* g, int value, int* out_count);
 
+/* ---------------------------------------------------------------- Tensor elementwise operations
+ * The reference's second public API (PRAD `Tensor` / `TensorReverse`, src/PRAD/Tensor.Common.cs and
+ * src/PRAD/TensorReverse.Common.cs) evaluates these with MKL VML calls over flat arrays; the entry
+ * points follow the same sequence of roundings in the storage type.  Reverse formulas are the ones
+ * written there: LogReverse (base-10 forward) multiplies by 1/x like LnReverse;
+ * ElementwiseSquareRootReverse is 0.5 * dy / maxmag(sqrt x, 1e-10); ReciprocalReverse reads the
+ * forward RESULT (pass it as `saved`); every other reverse reads the input x.
+ * Binary reverse: add -> (dy, dy); sub -> (dy, -dy); mul -> (dy*b, dy*a); div -> (dy/b,
+ * -((dy*a)/(b*b))); da or db may be NULL. */
+typedef enum {
+  PRAD_TENSOR_EXP = 0,        /* Tensor.Exp / ExpReverse                                   */
+  PRAD_TENSOR_LN = 1,         /* Tensor.Ln / LnReverse                                     */
+  PRAD_TENSOR_LOG10 = 2,      /* Tensor.Log (Vml.Log10) / LogReverse                       */
+  PRAD_TENSOR_ABS = 3,        /* Tensor.Abs / AbsReverse                                   */
+  PRAD_TENSOR_SQUARE = 4,     /* ElementwiseSquare / ElementwiseSquareReverse              */
+  PRAD_TENSOR_SQRT = 5,       /* ElementwiseSquareRoot / ElementwiseSquareRootReverse      */
+  PRAD_TENSOR_SIN = 6,        /* ElementwiseSin / ElementwiseSinReverse                    */
+  PRAD_TENSOR_COS = 7,        /* ElementwiseCos / ElementwiseCosReverse                    */
+  PRAD_TENSOR_RECIPROCAL = 8, /* Reciprocal / ReciprocalReverse                            */
+  PRAD_TENSOR_NEGATE = 9,     /* ElementwiseNegate                                         */
+  PRAD_TENSOR_ADD = 16,       /* ElementwiseAdd / ElementwiseAddReverse                    */
+  PRAD_TENSOR_SUB = 17,       /* ElementwiseSub / ElementwiseSubReverse                    */
+  PRAD_TENSOR_MUL = 18,       /* ElementwiseMultiply / ElementwiseMultiplyReverse          */
+  PRAD_TENSOR_DIV = 19        /* ElementwiseDivide / ElementwiseDivideReverse              */
+} prad_tensor_op;
+prad_status prad_tensor_unary(prad_ctx* ctx, prad_dtype dt, prad_tensor_op op, const void* x, void* y, int64_t n);
+prad_status prad_tensor_unary_reverse(prad_ctx* ctx, prad_dtype dt, prad_tensor_op op, const void* saved,
+                                      const void* dy, void* dx, int64_t n);
+prad_status prad_tensor_binary(prad_ctx* ctx, prad_dtype dt, prad_tensor_op op, const void* a, const void* b, void* y,
+                               int64_t n);
+prad_status prad_tensor_binary_reverse(prad_ctx* ctx, prad_dtype dt, prad_tensor_op op, const void* a, const void* b,
+                                       const void* dy, void* da, void* db, int64_t n);
+
 /* ---------------------------------------------------------------- recorded launch sequences
  * No counterpart in the reference, whose executor walks the operation list and calls each
  * Backward from managed code every step (src/RMAD/ComputationGraph.cs, NeuralNetwork

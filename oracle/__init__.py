@@ -541,3 +541,68 @@ def adam_prad(w, m, v, g, lr, b1, b2, eps, t):
     ct = _CT[w.dtype]
     _fn("adam_prad", w.dtype)(_p(w), _p(m), _p(v), _p(g), C.c_longlong(w.size), ct(lr), ct(b1),
                               ct(b2), ct(eps), int(t))
+
+
+# ---------------------------------------------------------------- PRAD Tensor elementwise family
+# src/PRAD/Tensor.Common.cs / TensorReverse.Common.cs evaluate these with one MKL VML call per step
+# over flat arrays; numpy's elementwise operations in the storage dtype restate that (one rounding
+# per step).  Line references are in include/prad_cuda.h next to prad_tensor_op.
+def tensor_unary(op, x):
+    x = _c(x)
+    t = x.dtype.type
+    with np.errstate(all="ignore"):
+        return {"exp": np.exp, "ln": np.log, "log": np.log10, "abs": np.abs, "square": lambda v: v * v,
+                "sqrt": np.sqrt, "sin": np.sin, "cos": np.cos, "reciprocal": lambda v: t(1) / v,
+                "negate": lambda v: v * t(-1)}[op](x).astype(x.dtype)
+
+
+def tensor_unary_reverse(op, saved, dy):
+    """`saved` is the input x, except for "reciprocal" where it is the forward result."""
+    s = _c(saved)
+    dy = _c(dy, s.dtype)
+    t = s.dtype.type
+    with np.errstate(all="ignore"):
+        if op == "exp":
+            return (np.exp(s).astype(s.dtype) * dy).astype(s.dtype)
+        if op in ("ln", "log"):                      # LogReverse multiplies by 1/x as well
+            return ((t(1) / s).astype(s.dtype) * dy).astype(s.dtype)
+        if op == "abs":
+            return np.where(s >= 0, dy, -dy).astype(s.dtype)
+        if op == "square":
+            return (t(2) * (dy * s).astype(s.dtype)).astype(s.dtype)
+        if op == "sqrt":
+            r = np.sqrt(s).astype(s.dtype)
+            m = np.where(np.abs(r) >= np.abs(t(1e-10)), r, t(1e-10)).astype(s.dtype)      # Vml.MaxMag
+            return (t(0.5) * (dy / m).astype(s.dtype)).astype(s.dtype)
+        if op == "sin":
+            return (dy * np.cos(s).astype(s.dtype)).astype(s.dtype)
+        if op == "cos":
+            return (t(-1) * (dy * np.sin(s).astype(s.dtype)).astype(s.dtype)).astype(s.dtype)
+        if op == "reciprocal":
+            return ((dy * (s * s).astype(s.dtype)).astype(s.dtype) * t(-1)).astype(s.dtype)
+        if op == "negate":
+            return (dy * t(-1)).astype(s.dtype)
+    raise KeyError(op)
+
+
+def tensor_binary(op, a, b):
+    a = _c(a)
+    b = _c(b, a.dtype)
+    with np.errstate(all="ignore"):
+        return {"add": np.add, "sub": np.subtract, "mul": np.multiply, "div": np.divide}[op](a, b).astype(a.dtype)
+
+
+def tensor_binary_reverse(op, a, b, dy):
+    a = _c(a)
+    b, dy = _c(b, a.dtype), _c(dy, a.dtype)
+    t = a.dtype.type
+    with np.errstate(all="ignore"):
+        if op == "add":
+            return dy.copy(), dy.copy()
+        if op == "sub":
+            return dy.copy(), (t(-1) * dy).astype(a.dtype)
+        if op == "mul":
+            return (dy * b).astype(a.dtype), (dy * a).astype(a.dtype)
+        if op == "div":
+            return (dy / b).astype(a.dtype), (t(-1) * ((dy * a).astype(a.dtype) / (b * b).astype(a.dtype)).astype(a.dtype)).astype(a.dtype)
+    raise KeyError(op)

@@ -72,6 +72,10 @@ SIGNATURES = {
     "prad_row_sum_backward": [vp, i32, vp, vp, i64, i32, i32],
     "prad_broadcast_forward": [vp, i32, vp, i32, i32, vp, i32, i32],
     "prad_broadcast_backward": [vp, i32, vp, i32, i32, vp, i32, i32],
+    "prad_tensor_unary": [vp, i32, i32, vp, vp, i64],
+    "prad_tensor_unary_reverse": [vp, i32, i32, vp, vp, vp, i64],
+    "prad_tensor_binary": [vp, i32, i32, vp, vp, vp, i64],
+    "prad_tensor_binary_reverse": [vp, i32, i32, vp, vp, vp, vp, vp, i64],
     "prad_batchnorm_forward": [vp, i32, vp, vp, vp, i64, i32],
     "prad_batchnorm_backward": [vp, i32, vp, vp, vp, vp, i64, i32],
     "prad_swiglu_forward": [vp, i32, vp, vp, vp, vp, vp, f64, vp, i64, i32],

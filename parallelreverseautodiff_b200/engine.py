@@ -535,6 +535,33 @@ class Engine:
             col += w
         return outs
 
+    # ------------------------------------------------------------ Tensor elementwise family
+    TENSOR_OPS = {"exp": 0, "ln": 1, "log": 2, "abs": 3, "square": 4, "sqrt": 5, "sin": 6, "cos": 7,
+                  "reciprocal": 8, "negate": 9, "add": 16, "sub": 17, "mul": 18, "div": 19}
+
+    def tensor_unary(self, op: str, x, out=None):
+        out = out or self.empty(x.shape, x.dtype)
+        check(self.lib.prad_tensor_unary(self.ctx, dtype_code(x.dtype), self.TENSOR_OPS[op], x.ptr, out.ptr, x.size))
+        return out
+
+    def tensor_unary_reverse(self, op: str, saved, dy, out=None):
+        out = out or self.empty(dy.shape, dy.dtype)
+        check(self.lib.prad_tensor_unary_reverse(self.ctx, dtype_code(dy.dtype), self.TENSOR_OPS[op], saved.ptr, dy.ptr,
+                                                 out.ptr, dy.size))
+        return out
+
+    def tensor_binary(self, op: str, a, b, out=None):
+        out = out or self.empty(a.shape, a.dtype)
+        check(self.lib.prad_tensor_binary(self.ctx, dtype_code(a.dtype), self.TENSOR_OPS[op], a.ptr, b.ptr, out.ptr,
+                                          a.size))
+        return out
+
+    def tensor_binary_reverse(self, op: str, a, b, dy):
+        da, db = self.empty(dy.shape, dy.dtype), self.empty(dy.shape, dy.dtype)
+        check(self.lib.prad_tensor_binary_reverse(self.ctx, dtype_code(dy.dtype), self.TENSOR_OPS[op], self._p(a),
+                                                  self._p(b), dy.ptr, da.ptr, db.ptr, dy.size))
+        return da, db
+
     def batchnorm_forward(self, x, out=None):
         """BatchNormalizationOperation as written.  Returns (y, stats) with stats a device [1 x 4] float64."""
         y = out or self.empty(x.shape, x.dtype)

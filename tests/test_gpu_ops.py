@@ -558,6 +558,49 @@ def test_batchnorm_as_written(engine, dtype, shape):
     assert_close(dx.numpy(), O.batchnorm_backward(x, st_ref, dy), np.abs(dy) * 2 + 1e-30, "dx")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("op", ["exp", "ln", "log", "abs", "square", "sqrt", "sin", "cos", "reciprocal", "negate"])
+def test_tensor_unary_family(engine, dtype, op):
+    """PRAD Tensor / TensorReverse elementwise operations (MKL VML in the reference)."""
+    r = rng(len(op) * 7 + 1)
+    x = normal(r, (33, 77), 1.5, dtype)
+    if op in ("ln", "log", "sqrt"):
+        x = np.abs(x) + dtype(0.05)
+        x[0, :3] = 0 if op == "sqrt" else x[0, :3]          # sqrt(0): the reverse clamps the divisor to 1e-10
+    if op == "reciprocal":
+        x = x + np.sign(x) * dtype(0.1)
+    dy = normal(r, x.shape, 1.0, dtype)
+    X, DY = engine.upload(x), engine.upload(dy)
+    y_ref = O.tensor_unary(op, x)
+    y = engine.tensor_unary(op, X)
+    exact_fwd = op in ("abs", "square", "sqrt", "reciprocal", "negate")
+    if exact_fwd:
+        np.testing.assert_array_equal(y.numpy(), y_ref)
+    else:
+        assert_close(y.numpy(), y_ref, np.abs(y_ref) + 1e-30, op)
+    saved_h = y_ref if op == "reciprocal" else x
+    dx_ref = O.tensor_unary_reverse(op, saved_h, dy)
+    dx = engine.tensor_unary_reverse(op, engine.upload(saved_h), DY)
+    if op in ("ln", "log", "abs", "square", "sqrt", "reciprocal", "negate"):
+        np.testing.assert_array_equal(dx.numpy(), dx_ref)       # IEEE operations only: same bits
+    else:
+        assert_close(dx.numpy(), dx_ref, np.abs(dy) * (np.abs(y_ref) + 1) + 1e-30, op + " reverse")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("op", ["add", "sub", "mul", "div"])
+def test_tensor_binary_family(engine, dtype, op):
+    r = rng(len(op) + 40)
+    a, b, dy = normal(r, (50, 41), 1, dtype), normal(r, (50, 41), 1, dtype), normal(r, (50, 41), 1, dtype)
+    b = b + np.sign(b) * dtype(0.2)
+    A, B, DY = engine.upload(a), engine.upload(b), engine.upload(dy)
+    np.testing.assert_array_equal(engine.tensor_binary(op, A, B).numpy(), O.tensor_binary(op, a, b))
+    da, db = engine.tensor_binary_reverse(op, A, B, DY)
+    da_ref, db_ref = O.tensor_binary_reverse(op, a, b, dy)
+    np.testing.assert_array_equal(da.numpy(), da_ref)
+    np.testing.assert_array_equal(db.numpy(), db_ref)
+
+
 def test_new_row_ops_reject_bad_arguments(engine):
     from parallelreverseautodiff_b200._lib import ERR_INVALID, PradError
     x = engine.zeros((4, 4), np.float32)
