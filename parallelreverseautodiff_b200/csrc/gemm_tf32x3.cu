@@ -1051,26 +1051,46 @@ template <bool VEC>
 __global__ void __launch_bounds__(256)
 absmax_cols_kernel(const float* __restrict__ src, int64_t ld, int rows, int cols, unsigned* __restrict__ umax,
                    int cpb, int rows_per_block) {
+  // the row lanes of a block are combined in shared memory first, so that a block sends one atomic
+  // per column: with narrow matrices all blocks hit the same few addresses
+  __shared__ unsigned smax[1024];
+  for (int i = threadIdx.x; i < 4 * cpb; i += 256) smax[i] = 0;
+  __syncthreads();
   const int cl = threadIdx.x % cpb, rl = threadIdx.x / cpb, rpb = 256 / cpb;
   const int cg = blockIdx.x * cpb + cl;
   const int c0 = VEC ? cg * 4 : cg;
-  if (rl >= rpb || c0 >= cols) return;
+  const bool active = rl < rpb && c0 < cols;
   const int r_end = min(rows, (int)((blockIdx.y + 1) * rows_per_block));
   uint32_t m[4] = {0, 0, 0, 0};
-  if (VEC && c0 + 4 <= cols) {
-    for (int r = blockIdx.y * rows_per_block + rl; r < r_end; r += rpb) {
-      const float4 v = __ldg(reinterpret_cast<const float4*>(src + (int64_t)r * ld + c0));
+  if (active && VEC && c0 + 4 <= cols) {
+    auto take = [&](const float4& v) {
       m[0] = max(m[0], __float_as_uint(fabsf(v.x))); m[1] = max(m[1], __float_as_uint(fabsf(v.y)));
       m[2] = max(m[2], __float_as_uint(fabsf(v.z))); m[3] = max(m[3], __float_as_uint(fabsf(v.w)));
+    };
+    const float* p = src + c0;
+    int r = blockIdx.y * rows_per_block + rl;
+    for (; r + 3 * rpb < r_end; r += 4 * rpb) {     // four independent loads in flight per thread
+      const float4 v0 = __ldg(reinterpret_cast<const float4*>(p + (int64_t)r * ld));
+      const float4 v1 = __ldg(reinterpret_cast<const float4*>(p + (int64_t)(r + rpb) * ld));
+      const float4 v2 = __ldg(reinterpret_cast<const float4*>(p + (int64_t)(r + 2 * rpb) * ld));
+      const float4 v3 = __ldg(reinterpret_cast<const float4*>(p + (int64_t)(r + 3 * rpb) * ld));
+      take(v0); take(v1); take(v2); take(v3);
     }
-  } else {
+    for (; r < r_end; r += rpb) take(__ldg(reinterpret_cast<const float4*>(p + (int64_t)r * ld)));
+  } else if (active) {
     const int w = VEC ? min(4, cols - c0) : 1;
     for (int r = blockIdx.y * rows_per_block + rl; r < r_end; r += rpb)
       for (int q = 0; q < w; ++q) m[q] = max(m[q], __float_as_uint(fabsf(src[(int64_t)r * ld + c0 + q])));
   }
+  if (active) {
 #pragma unroll
-  for (int q = 0; q < 4; ++q)
-    if (m[q] != 0 && c0 + q < cols) atomicMax(umax + c0 + q, m[q]);
+    for (int q = 0; q < 4; ++q)
+      if (m[q] != 0) atomicMax(&smax[(VEC ? 4 * cl : cl) + q], m[q]);
+  }
+  __syncthreads();
+  const int width = VEC ? 4 * cpb : cpb, cbase = blockIdx.x * width;
+  for (int i = threadIdx.x; i < width; i += 256)
+    if (cbase + i < cols && smax[i] != 0) atomicMax(umax + cbase + i, smax[i]);
 }
 // src is k_rows x r_cols (k slow); dst is r_cols x dst_ld (k fast), row c scaled by 2^shift_of(umax[c])
 __global__ void __launch_bounds__(256)
@@ -1312,9 +1332,9 @@ static prad_status split_operand(prad_ctx* ctx, const float* src, int64_t ld, bo
     int cpb = 256;
     while (cpb > 1 && cpb / 2 >= lanes) cpb /= 2;               // power of two, so 256 / cpb is whole
     const int gx = (int)ceil_div(lanes, cpb);
-    // enough row slices to fill the machine, each at least 64 rows per row lane
-    int gy = (int)std::max<int64_t>(1, std::min<int64_t>(ceil_div((int64_t)ctx->sm_count * 8, gx),
-                                                          ceil_div(K, (int64_t)64 * (256 / cpb))));
+    // enough row slices to fill the machine, each at least 16 rows per row lane
+    int gy = (int)std::max<int64_t>(1, std::min<int64_t>(ceil_div((int64_t)ctx->sm_count * 4, gx),
+                                                          ceil_div(K, (int64_t)16 * (256 / cpb))));
     const int rows_per_block = (int)ceil_div(K, gy);
     gy = (int)ceil_div(K, rows_per_block);
     if (vec) absmax_cols_kernel<true><<<dim3(gx, gy), 256, 0, ctx->stream>>>(src, ld, K, rows, o.umax, cpb, rows_per_block);
