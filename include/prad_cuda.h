@@ -111,6 +111,35 @@ prad_status prad_stream(prad_ctx* ctx, void** out_stream);
 /* makes the context enqueue on a caller-provided cudaStream_t (NULL restores its own) */
 prad_status prad_use_stream(prad_ctx* ctx, void* stream);
 
+/* Device and library facts for the managed side (the reference exposes none; CudaBlas only has
+ * DeviceId, src/RMAD/CudaBlas.cs:104). */
+typedef struct {
+  int32_t device;                /* CUDA ordinal of the context                          */
+  int32_t sm_count;
+  int32_t cc_major, cc_minor;    /* compute capability (10.0 on B200)                    */
+  int32_t l2_bytes;
+  int32_t smem_per_block_optin;  /* largest dynamic shared memory a kernel may ask for   */
+  int32_t sm_clock_khz, mem_clock_khz; /* nominal maxima as the runtime reports them     */
+  uint64_t total_bytes, free_bytes;    /* device memory now                              */
+  uint64_t scratch_bytes;        /* library scratch currently held by this context       */
+  char name[64];
+} prad_device_info_t;
+prad_status prad_device_info(prad_ctx* ctx, prad_device_info_t* out);
+/* CUDA-event timing of caller-chosen regions of the context's stream (the reference has no timers;
+ * its only trace is Debug.WriteLine inside AdamOptimizer, src/RMAD/AdamOptimizer.cs:215-217).
+ * prad_timing_begin(label) ... prad_timing_end() bracket whatever is enqueued in between; brackets do
+ * not nest and cost two event records.  prad_get_timings waits for the stream, writes up to `capacity`
+ * finished brackets in the order they were opened, stores their total number in *out_count, and forgets
+ * them if they all fitted. */
+typedef struct {
+  char label[48];
+  double milliseconds;  /* device time between the two events */
+  int64_t launches;     /* kernels this library launched inside the bracket */
+} prad_timing_t;
+prad_status prad_timing_begin(prad_ctx* ctx, const char* label);
+prad_status prad_timing_end(prad_ctx* ctx);
+prad_status prad_get_timings(prad_ctx* ctx, prad_timing_t* out, int capacity, int* out_count);
+
 /* ---------------------------------------------------------------- memory
  * Stand in for accelerator.Allocate2DDenseX / CopyFromCPU / GetAsArray2D
  * (src/RMAD/GpuMatrixMultiplyOperation.cs:190-201) and for the jagged<->flat
@@ -139,6 +168,31 @@ prad_status prad_upload_rows(prad_ctx* ctx, void* dst, const void* const* src_ro
                              size_t row_bytes);
 prad_status prad_download_rows(prad_ctx* ctx, void* const* dst_rows, const void* src, int rows,
                                size_t row_bytes);
+/* Many device tensors <-> ONE packed host block, in list order, with a single wait: what
+ * ModelLayer.SaveWeightsAndMoments / LoadWeightsAndMoments need (src/RMAD/ModelLayer.cs:219-320; the
+ * file holds all weights, then all first moments, then all second moments, each in element order, so the
+ * caller lists the pointers in that order).  *_host arguments are host arrays of `count` entries. */
+prad_status prad_download_many(prad_ctx* ctx, void* dst_host, const void* const* srcs_host, const size_t* bytes_host,
+                               int count);
+prad_status prad_upload_many(prad_ctx* ctx, void* const* dsts_host, const void* src_host, const size_t* bytes_host,
+                             int count);
+/* Intermediate slots: the device form of IOperationBase.Store(Guid) / Restore(Guid)
+ * (src/RMAD/IOperationBase.cs:183-194, OperationBase.cs:251-258; e.g. MatrixMultiplyOperation.cs:31-42
+ * keeps { input1, input2 } per id in IntermediateMatrixArrays; ComputationGraph.StoreOperationIntermediates
+ * / RestoreOperationIntermediates, src/RMAD/ComputationGraph.cs:161-181, call it on every operation so
+ * that several forward passes can be replayed backwards later).  A slot is a list of device buffers
+ * under a 16-byte id:
+ *   copy == 0  the slot keeps the POINTERS, as the managed code keeps references: the caller must not
+ *              overwrite those buffers before the restore (it allocates fresh outputs per forward);
+ *   copy != 0  the slot keeps device COPIES made on the context's stream (for callers that reuse their
+ *              activation buffers from one forward pass to the next); restore returns the copies.
+ * Storing under an id that exists replaces it (AddOrUpdate); restoring an unknown id is
+ * PRAD_ERR_INVALID (the dictionary's KeyNotFoundException); prad_slot_drop frees a slot's copies. */
+prad_status prad_slot_store(prad_ctx* ctx, const void* guid_16_bytes, const void* const* ptrs_host,
+                            const size_t* bytes_host, int count, int copy);
+prad_status prad_slot_restore(prad_ctx* ctx, const void* guid_16_bytes, void** out_ptrs_host, int count);
+prad_status prad_slot_drop(prad_ctx* ctx, const void* guid_16_bytes);
+prad_status prad_slot_count(prad_ctx* ctx, int* out_count);
 /* pinned host staging memory for the two calls above and for *_host entry points */
 prad_status prad_alloc_host(prad_ctx* ctx, size_t bytes, void** out_hptr);
 prad_status prad_free_host(prad_ctx* ctx, void* hptr);
@@ -486,6 +540,44 @@ prad_status prad_tensor_binary(prad_ctx* ctx, prad_dtype dt, prad_tensor_op op, 
 prad_status prad_tensor_binary_reverse(prad_ctx* ctx, prad_dtype dt, prad_tensor_op op, const void* a, const void* b,
                                        const void* dy, void* da, void* db, int64_t n);
 
+/* Tensor.MatrixMultiply (src/PRAD/Tensor.cs:572-613, MKL dgemm / sgemm, row-major NN): C = alpha*A*B +
+ * beta*C for 2-D tensors.  The shape rule of :582-585 is kept: a_cols != b_rows returns PRAD_ERR_SHAPE
+ * with the managed message "Incompatible shapes for matrix multiplication.".
+ * TensorReverse.MatrixMultiplyReverse (src/PRAD/TensorReverse.cs:94-160): dA = dC * B^T (gemm NoTrans,
+ * Trans), dB = A^T * dC (gemm Trans, NoTrans); either result may be NULL.  Both run on the same GEMM
+ * kernels as prad_gemm (MKL's own summation order is not reproduced: tolerance-level parity). */
+prad_status prad_tensor_matmul(prad_ctx* ctx, prad_dtype dt, const void* A, int a_rows, int a_cols, const void* B,
+                               int b_rows, int b_cols, double alpha, double beta, void* C);
+prad_status prad_tensor_matmul_reverse(prad_ctx* ctx, prad_dtype dt, const void* A, int a_rows, int a_cols,
+                                       const void* B, int b_rows, int b_cols, const void* dC, void* dA, void* dB);
+/* Tensor.Gather (src/PRAD/Tensor.Common.cs:959-1090) along one axis: the tensor is passed as
+ * x[outer][axis_len][inner] (outer / inner = product of the dimensions before / after the axis), the
+ * `count` indices are values of the storage type (negative ones count from the end, :974), the result
+ * is y[outer][count][inner]; an index outside the axis returns PRAD_ERR_INVALID (ArgumentException).
+ * TensorReverse.GatherReverse (src/PRAD/TensorReverse.Common.cs:2358-2426): dx[o][indices[c]][i] +=
+ * upstream[o][c][i].  The managed loop is a Parallel.For with a lock, so duplicates are added in a
+ * thread-dependent order there; here they are added in ascending c (the order of a sequential loop),
+ * bit-identical for unique indices and deterministic for repeated ones. */
+prad_status prad_tensor_gather(prad_ctx* ctx, prad_dtype dt, const void* x, int64_t outer, int axis_len, int64_t inner,
+                               const void* indices, int count, void* y);
+prad_status prad_tensor_gather_reverse(prad_ctx* ctx, prad_dtype dt, const void* upstream, int64_t outer, int axis_len,
+                                       int64_t inner, const void* indices, int count, void* dx);
+/* Tensor.Tile (src/PRAD/Tensor.Common.cs:1096-1230) for 2-D tensors: y[r][c] = x[r % rows][c % cols], y is
+ * (rows*mult_rows) x (cols*mult_cols).  TensorReverse.TileReverse (src/PRAD/TensorReverse.Common.cs:
+ * 2713-2785): every input element collects its copies in the order of the upstream gradient's flat
+ * index.  As written there, multiples {m, 1} take a specialised routine (:3326-3370) that reads rows
+ * i*m .. i*m+m-1 of the upstream gradient for input row i; that is reproduced. */
+prad_status prad_tensor_tile(prad_ctx* ctx, prad_dtype dt, const void* x, int rows, int cols, int mult_rows, int mult_cols,
+                             void* y);
+prad_status prad_tensor_tile_reverse(prad_ctx* ctx, prad_dtype dt, const void* upstream, int rows, int cols, int mult_rows,
+                                     int mult_cols, void* dx);
+/* The remaining 2-D Tensor operations map onto existing entry points: Tensor.SumRows (src/PRAD/Tensor.cs:
+ * 769-786) = prad_row_sum_forward, TensorReverse.SumRowsReverse (TensorReverse.Common.cs:2936-2958) =
+ * prad_row_sum_backward; Tensor.Transpose {1,0} and {0,2,1} and TensorReverse.TransposeReverse
+ * (TensorReverse.Common.cs:2967-3040) = prad_transpose (the reverse of a transposition is the
+ * transposition of the upstream gradient with rows and cols exchanged); Tensor.Embedding /
+ * EmbeddingReverse = prad_embedding_forward / prad_embedding_backward. */
+
 /* ---------------------------------------------------------------- recorded launch sequences
  * No counterpart in the reference, whose executor walks the operation list and calls each
  * Backward from managed code every step (src/RMAD/ComputationGraph.cs, NeuralNetwork
@@ -521,6 +613,22 @@ prad_status prad_dp_unique_id(void* out_id_128_bytes);
 prad_status prad_dp_init(prad_ctx* ctx, const void* id_128_bytes, int rank, int world_size);
 prad_status prad_dp_allreduce(prad_ctx* ctx, prad_dtype dt, void* buf, int64_t n);
 prad_status prad_dp_wait(prad_ctx* ctx);
+/* Sharded optimiser: prad_dp_reduce leaves the SUM over all ranks in `buf` of rank `root` only (the
+ * other ranks' buffers keep their partial sums); prad_dp_broadcast copies `buf` of rank `root` into `buf`
+ * of every rank.  Both are enqueued on the communication stream after everything enqueued so far on the
+ * compute stream, like prad_dp_allreduce; prad_dp_wait joins.  The owner of a tensor clips and updates
+ * it alone (the reference's clip needs only that tensor's own statistics, src/RMAD/GradientClipper.cs:
+ * 118-157) and broadcasts the new weights. */
+prad_status prad_dp_reduce(prad_ctx* ctx, prad_dtype dt, void* buf, int64_t n, int root);
+prad_status prad_dp_broadcast(prad_ctx* ctx, prad_dtype dt, void* buf, int64_t n, int root);
+/* Host-side join with a deadline, the counterpart of the visitor's bounded wait on a sibling task
+ * (TimeoutInMinutes, src/RMAD/OperationNeuralNetworkVisitor.cs:27,264-270): blocks the calling thread
+ * until the outstanding collectives have completed (then the compute stream is joined as by
+ * prad_dp_wait), NCCL reports an asynchronous error (PRAD_ERR_COMM), or timeout_ms have passed
+ * (PRAD_ERR_TIMEOUT: a rank never arrived).  In both failure cases the communicator is aborted, so the
+ * kernels of the collective leave the GPU; every later prad_dp_* call fails with PRAD_ERR_COMM until
+ * prad_dp_shutdown + prad_dp_init build a new communicator. */
+prad_status prad_dp_wait_host(prad_ctx* ctx, double timeout_ms);
 prad_status prad_dp_shutdown(prad_ctx* ctx);
 
 #ifdef __cplusplus

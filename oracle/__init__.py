@@ -606,3 +606,78 @@ def tensor_binary_reverse(op, a, b, dy):
         if op == "div":
             return (dy / b).astype(a.dtype), (t(-1) * ((dy * a).astype(a.dtype) / (b * b).astype(a.dtype)).astype(a.dtype)).astype(a.dtype)
     raise KeyError(op)
+
+
+# ---------------------------------------------------------------- PRAD Tensor matmul / gather / tile
+def tensor_matmul(a, b, alpha=1.0, beta=0.0, c=None):
+    """Tensor.MatrixMultiply (src/PRAD/Tensor.cs:572-613): 2-D only, ArgumentException on a shape
+    mismatch; the product itself is MKL's (third party, summation order unknown) -- restated with the
+    sequential loops of matmul_forward."""
+    a, b = _c(a), _c(b)
+    if a.ndim != 2 or b.ndim != 2:
+        raise ValueError("Matrix multiplication is only supported for 2D tensors.")
+    if a.shape[1] != b.shape[0]:
+        raise ValueError("Incompatible shapes for matrix multiplication.")
+    t = a.dtype.type
+    prod = matmul_forward(a, b)
+    out = (t(alpha) * prod).astype(a.dtype)
+    if beta != 0.0:
+        out = (out + (t(beta) * _c(c, a.dtype)).astype(a.dtype)).astype(a.dtype)
+    return out
+
+
+def tensor_matmul_reverse(a, b, dc):
+    """TensorReverse.MatrixMultiplyReverse (src/PRAD/TensorReverse.cs:94-160): dA = dC B^T, dB = A^T dC."""
+    return matmul_backward(a, b, dc)
+
+
+def tensor_gather(x, indices, axis=0):
+    """Tensor.Gather (src/PRAD/Tensor.Common.cs:959-1090): negative indices count from the end;
+    result shape = x.shape[:axis] + indices.shape + x.shape[axis+1:]."""
+    x = _c(x)
+    idx = np.asarray(indices)
+    n = x.shape[axis]
+    w = np.where(idx < 0, n + idx.astype(np.int64), idx.astype(np.int64))
+    if ((w < 0) | (w >= n)).any():
+        raise ValueError("Index out of bounds.")
+    return np.ascontiguousarray(np.take(x, w, axis=axis))
+
+
+def tensor_gather_reverse(upstream, indices, input_shape, axis=0):
+    """TensorReverse.GatherReverse (src/PRAD/TensorReverse.Common.cs:2358-2426) with the contributions of
+    repeated indices added in the order of the upstream gradient's flat index (a sequential loop)."""
+    up = _c(upstream)
+    idx = np.asarray(indices)
+    n = input_shape[axis]
+    w = np.where(idx < 0, n + idx.astype(np.int64), idx.astype(np.int64)).ravel()
+    if ((w < 0) | (w >= n)).any():
+        raise ValueError("Index out of bounds.")
+    outer = int(np.prod(input_shape[:axis], dtype=np.int64))
+    inner = int(np.prod(input_shape[axis + 1:], dtype=np.int64))
+    up3 = up.reshape(outer, w.size, inner)
+    dx = np.zeros((outer, n, inner), up.dtype)
+    for c, v in enumerate(w):                       # ascending c == ascending flat index per element
+        dx[:, v, :] = (dx[:, v, :] + up3[:, c, :]).astype(up.dtype)
+    return dx.reshape(input_shape)
+
+
+def tensor_tile(x, multiples):
+    """Tensor.Tile (src/PRAD/Tensor.Common.cs:1096-1230), 2-D."""
+    return np.ascontiguousarray(np.tile(_c(x), tuple(multiples)))
+
+
+def tensor_tile_reverse(upstream, input_shape, multiples):
+    """TensorReverse.TileReverse (src/PRAD/TensorReverse.Common.cs:2713-2785; specialised cases
+    :3278-3370), 2-D, as written: multiples {m, 1} read rows i*m .. i*m+m-1 for input row i."""
+    up = _c(upstream)
+    rows, cols = input_shape
+    mr, mc = multiples
+    dx = np.zeros((rows, cols), up.dtype)
+    if mc == 1:
+        for m in range(mr):
+            dx = (dx + up.reshape(rows, mr, cols)[:, m, :]).astype(up.dtype)
+        return dx
+    for tr in range(mr):
+        for tc in range(mc):
+            dx = (dx + up[tr * rows:(tr + 1) * rows, tc * cols:(tc + 1) * cols]).astype(up.dtype)
+    return dx

@@ -76,6 +76,12 @@ SIGNATURES = {
     "prad_tensor_unary_reverse": [vp, i32, i32, vp, vp, vp, i64],
     "prad_tensor_binary": [vp, i32, i32, vp, vp, vp, i64],
     "prad_tensor_binary_reverse": [vp, i32, i32, vp, vp, vp, vp, vp, i64],
+    "prad_tensor_matmul": [vp, i32, vp, i32, i32, vp, i32, i32, f64, f64, vp],
+    "prad_tensor_matmul_reverse": [vp, i32, vp, i32, i32, vp, i32, i32, vp, vp, vp],
+    "prad_tensor_gather": [vp, i32, vp, i64, i32, i64, vp, i32, vp],
+    "prad_tensor_gather_reverse": [vp, i32, vp, i64, i32, i64, vp, i32, vp],
+    "prad_tensor_tile": [vp, i32, vp, i32, i32, i32, i32, vp],
+    "prad_tensor_tile_reverse": [vp, i32, vp, i32, i32, i32, i32, vp],
     "prad_batchnorm_forward": [vp, i32, vp, vp, vp, i64, i32],
     "prad_batchnorm_backward": [vp, i32, vp, vp, vp, vp, i64, i32],
     "prad_swiglu_forward": [vp, i32, vp, vp, vp, vp, vp, f64, vp, i64, i32],
@@ -114,9 +120,35 @@ SIGNATURES = {
     "prad_dp_init": [vp, vp, i32, i32],
     "prad_dp_allreduce": [vp, i32, vp, i64],
     "prad_dp_wait": [vp],
+    "prad_dp_reduce": [vp, i32, vp, i64, i32],
+    "prad_dp_broadcast": [vp, i32, vp, i64, i32],
+    "prad_dp_wait_host": [vp, f64],
     "prad_dp_shutdown": [vp],
+    "prad_download_many": [vp, vp, pvp, C.POINTER(sz), i32],
+    "prad_upload_many": [vp, pvp, vp, C.POINTER(sz), i32],
+    "prad_slot_store": [vp, vp, pvp, C.POINTER(sz), i32, i32],
+    "prad_slot_restore": [vp, vp, pvp, i32],
+    "prad_slot_drop": [vp, vp],
+    "prad_slot_count": [vp, C.POINTER(C.c_int)],
+    "prad_device_info": [vp, vp],
+    "prad_timing_begin": [vp, C.c_char_p],
+    "prad_timing_end": [vp],
+    "prad_get_timings": [vp, vp, i32, C.POINTER(C.c_int)],
 }
 STRING_FUNCS = ("prad_last_error", "prad_version")
+
+class DeviceInfo(C.Structure):
+    """prad_device_info_t"""
+    _fields_ = [("device", C.c_int32), ("sm_count", C.c_int32), ("cc_major", C.c_int32), ("cc_minor", C.c_int32),
+                ("l2_bytes", C.c_int32), ("smem_per_block_optin", C.c_int32), ("sm_clock_khz", C.c_int32),
+                ("mem_clock_khz", C.c_int32), ("total_bytes", C.c_uint64), ("free_bytes", C.c_uint64),
+                ("scratch_bytes", C.c_uint64), ("name", C.c_char * 64)]
+
+
+class Timing(C.Structure):
+    """prad_timing_t"""
+    _fields_ = [("label", C.c_char * 48), ("milliseconds", C.c_double), ("launches", C.c_int64)]
+
 
 _lib = None
 

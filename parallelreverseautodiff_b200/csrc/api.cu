@@ -51,6 +51,7 @@ prad_status ensure_stage(prad_ctx* ctx, size_t bytes) {
 }
 
 prad_status dp_destroy(prad_ctx* ctx);  // dp.cu
+void runtime_destroy(prad_ctx* ctx);    // runtime.cu
 
 }  // namespace prad
 
@@ -108,6 +109,7 @@ prad_status prad_shutdown(prad_ctx* ctx) {
   PRAD_CHECK_CTX(ctx);
   cudaStreamSynchronize(ctx->stream);
   dp_destroy(ctx);
+  runtime_destroy(ctx);
   if (ctx->ws) cudaFree(ctx->ws);
   if (ctx->tc_err) cudaFree(ctx->tc_err);
   for (void* r : ctx->retired) cudaFree(r);

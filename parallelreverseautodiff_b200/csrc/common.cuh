@@ -164,4 +164,8 @@ prad_status gemm_dispatch(prad_ctx* ctx, prad_dtype dt, bool transA, bool transB
                           double beta, void* C, int ldc, int batch, int64_t sA, int64_t sB,
                           int64_t sC, const GemmEpilogue& epi);
 
+// dW[idx[i]][:] += dOut[i][:] for i ascending (bit-identical to the sequential loop); loss_embedding.cu
+prad_status embedding_scatter_ordered(prad_ctx* ctx, prad_dtype dt, const void* index_col, const void* dOut,
+                                      void* dW, int n, int vocab, int dim, int* bad);
+
 }  // namespace prad

@@ -8,6 +8,15 @@
 // layer l overlaps with the backward kernels of layers l-1..0 that are enqueued afterwards;
 // prad_dp_wait joins the two streams again before the optimiser reads the gradients.
 //
+// Sharded optimiser: prad_dp_reduce sends the sum of a gradient to ONE rank (its owner) instead of
+// to all; the owner alone clips and updates that tensor (the reference's z-score clip needs only the
+// tensor's own mean and sigma) and prad_dp_broadcast returns the new weights to everybody, on the
+// communication stream, while the next step's first kernels already run.  Same bytes on the wire as an
+// all-reduce, 1/N of the optimiser work and of the moment memory per rank.
+//
+// prad_dp_wait_host is the failure path: a host-side wait with a deadline (dp_deadline.h); when a peer
+// never arrives the communicator is aborted and the call returns PRAD_ERR_TIMEOUT instead of hanging.
+//
 // NCCL is bound at run time with dlopen: the process may already hold the copy that ships
 // with PyTorch, and the library must still load on a machine without NCCL (every prad_dp_*
 // call then fails with PRAD_ERR_COMM; nothing else is affected).
@@ -17,6 +26,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "dp_deadline.h"
 
 namespace prad {
 
@@ -33,6 +43,8 @@ struct NcclApi {
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
   ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
   ncclResult_t (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*Reduce)(const void*, void*, size_t, int, int, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*Broadcast)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
   const char* (*GetErrorString)(ncclResult_t) = nullptr;
   bool ok = false;
@@ -60,6 +72,8 @@ static NcclApi& nccl() {
     LOAD(CommDestroy, "ncclCommDestroy")
     LOAD(CommAbort, "ncclCommAbort")
     LOAD(AllReduce, "ncclAllReduce")
+    LOAD(Reduce, "ncclReduce")
+    LOAD(Broadcast, "ncclBroadcast")
     LOAD(CommGetAsyncError, "ncclCommGetAsyncError")
     LOAD(GetErrorString, "ncclGetErrorString")
 #undef LOAD
@@ -75,6 +89,7 @@ struct DpState {
   cudaEvent_t done = nullptr;   // comm -> compute
   int rank = 0, world = 1;
   bool pending = false;
+  bool aborted = false;         // the communicator was aborted after a deadline or an asynchronous error
 };
 
 #define PRAD_NCCL(call)                                                                \
@@ -89,8 +104,8 @@ struct DpState {
 prad_status dp_destroy(prad_ctx* ctx) {
   DpState* d = ctx->dp;
   if (!d) return PRAD_OK;
-  if (d->comm_stream) cudaStreamSynchronize(d->comm_stream);
-  if (d->comm && nccl().ok) nccl().CommDestroy(d->comm);
+  if (d->comm_stream && !d->aborted) cudaStreamSynchronize(d->comm_stream);
+  if (d->comm && nccl().ok && !d->aborted) nccl().CommDestroy(d->comm);
   if (d->ready) cudaEventDestroy(d->ready);
   if (d->done) cudaEventDestroy(d->done);
   if (d->comm_stream) cudaStreamDestroy(d->comm_stream);
@@ -125,21 +140,118 @@ prad_status prad_dp_init(prad_ctx* ctx, const void* id_128_bytes, int rank, int 
   d->rank = rank;
   d->world = world_size;
   ctx->dp = d;
-  int lo = 0, hi = 0;
-  PRAD_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
-  PRAD_CUDA(cudaStreamCreateWithPriority(&d->comm_stream, cudaStreamNonBlocking, hi));
-  PRAD_CUDA(cudaEventCreateWithFlags(&d->ready, cudaEventDisableTiming));
-  PRAD_CUDA(cudaEventCreateWithFlags(&d->done, cudaEventDisableTiming));
-  ncclUniqueId id;
-  memcpy(&id, id_128_bytes, sizeof(id));
-  PRAD_NCCL(nccl().CommInitRank(&d->comm, world_size, id, rank));
+  // any failure below leaves the context as it was before the call, so that prad_dp_init can be retried
+  auto body = [&]() -> prad_status {
+    int lo = 0, hi = 0;
+    PRAD_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    PRAD_CUDA(cudaStreamCreateWithPriority(&d->comm_stream, cudaStreamNonBlocking, hi));
+    PRAD_CUDA(cudaEventCreateWithFlags(&d->ready, cudaEventDisableTiming));
+    PRAD_CUDA(cudaEventCreateWithFlags(&d->done, cudaEventDisableTiming));
+    ncclUniqueId id;
+    memcpy(&id, id_128_bytes, sizeof(id));
+    PRAD_NCCL(nccl().CommInitRank(&d->comm, world_size, id, rank));
+    return PRAD_OK;
+  };
+  const prad_status st = body();
+  if (st != PRAD_OK) dp_destroy(ctx);
+  return st;
+}
+
+namespace prad {
+// the communication stream picks up after everything enqueued so far on the compute stream
+static prad_status comm_after_compute(prad_ctx* ctx) {
+  DpState* d = ctx->dp;
+  PRAD_CUDA(cudaEventRecord(d->ready, ctx->stream));
+  PRAD_CUDA(cudaStreamWaitEvent(d->comm_stream, d->ready, 0));
   return PRAD_OK;
+}
+#define PRAD_DP_READY(ctx, who)                                                                              \
+  PRAD_REQUIRE((ctx)->dp && (ctx)->dp->comm, PRAD_ERR_NOT_INITIALIZED, who ": call prad_dp_init first");     \
+  PRAD_REQUIRE(!(ctx)->dp->aborted, PRAD_ERR_COMM, who ": the communicator was aborted after a failure; "    \
+               "call prad_dp_shutdown and prad_dp_init again")
+}  // namespace prad
+
+prad_status prad_dp_reduce(prad_ctx* ctx, prad_dtype dt, void* buf, int64_t n, int root) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_NOT_CAPTURING(ctx, "prad_dp_reduce");
+  PRAD_DP_READY(ctx, "prad_dp_reduce");
+  DpState* d = ctx->dp;
+  PRAD_REQUIRE(dtype_ok(dt) && n >= 0 && (buf || n == 0) && root >= 0 && root < d->world, PRAD_ERR_INVALID,
+               "prad_dp_reduce: bad argument (root %d of %d ranks)", root, d->world);
+  if (n == 0) return PRAD_OK;
+  prad_status s = comm_after_compute(ctx);
+  if (s) return s;
+  PRAD_NCCL(nccl().Reduce(buf, buf, (size_t)n, dt == PRAD_F32 ? ncclFloat32 : ncclFloat64, ncclSum, root, d->comm,
+                          d->comm_stream));
+  d->pending = true;
+  return PRAD_OK;
+}
+
+prad_status prad_dp_broadcast(prad_ctx* ctx, prad_dtype dt, void* buf, int64_t n, int root) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_NOT_CAPTURING(ctx, "prad_dp_broadcast");
+  PRAD_DP_READY(ctx, "prad_dp_broadcast");
+  DpState* d = ctx->dp;
+  PRAD_REQUIRE(dtype_ok(dt) && n >= 0 && (buf || n == 0) && root >= 0 && root < d->world, PRAD_ERR_INVALID,
+               "prad_dp_broadcast: bad argument (root %d of %d ranks)", root, d->world);
+  if (n == 0) return PRAD_OK;
+  prad_status s = comm_after_compute(ctx);
+  if (s) return s;
+  PRAD_NCCL(nccl().Broadcast(buf, buf, (size_t)n, dt == PRAD_F32 ? ncclFloat32 : ncclFloat64, root, d->comm,
+                             d->comm_stream));
+  d->pending = true;
+  return PRAD_OK;
+}
+
+prad_status prad_dp_wait_host(prad_ctx* ctx, double timeout_ms) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_NOT_CAPTURING(ctx, "prad_dp_wait_host");
+  PRAD_DP_READY(ctx, "prad_dp_wait_host");
+  PRAD_REQUIRE(timeout_ms > 0, PRAD_ERR_INVALID, "prad_dp_wait_host: the deadline must be positive");
+  DpState* d = ctx->dp;
+  PRAD_CUDA(cudaEventRecord(d->done, d->comm_stream));
+  cudaError_t query_failure = cudaSuccess;
+  ncclResult_t async = 0;
+  const WaitOutcome out = wait_with_deadline(
+      [&] {
+        const cudaError_t q = cudaEventQuery(d->done);
+        if (q == cudaSuccess) return true;
+        if (q != cudaErrorNotReady) { query_failure = q; (void)cudaGetLastError(); }
+        return false;
+      },
+      [&] {
+        if (query_failure != cudaSuccess) return true;
+        ncclResult_t r = 0;
+        if (nccl().CommGetAsyncError(d->comm, &r) != 0) return true;
+        async = r;
+        return r != 0;
+      },
+      [&] {
+        nccl().CommAbort(d->comm);   // returns the ranks that did arrive from the collective
+        d->aborted = true;
+        d->pending = false;
+      },
+      timeout_ms);
+  if (out == WaitOutcome::Done) {
+    PRAD_CUDA(cudaStreamWaitEvent(ctx->stream, d->done, 0));
+    d->pending = false;
+    return PRAD_OK;
+  }
+  if (out == WaitOutcome::TimedOut) {
+    set_error("prad_dp_wait_host: the collectives did not complete within %.0f ms (a rank never arrived?); "
+              "the communicator was aborted", timeout_ms);
+    return PRAD_ERR_TIMEOUT;
+  }
+  set_error("prad_dp_wait_host: %s; the communicator was aborted",
+            query_failure != cudaSuccess ? cudaGetErrorString(query_failure)
+                                         : (async ? nccl().GetErrorString(async) : "NCCL could not report its state"));
+  return PRAD_ERR_COMM;
 }
 
 prad_status prad_dp_allreduce(prad_ctx* ctx, prad_dtype dt, void* buf, int64_t n) {
   PRAD_CHECK_CTX(ctx);
   PRAD_NOT_CAPTURING(ctx, "prad_dp_allreduce");
-  PRAD_REQUIRE(ctx->dp && ctx->dp->comm, PRAD_ERR_NOT_INITIALIZED, "prad_dp_allreduce: call prad_dp_init first");
+  PRAD_DP_READY(ctx, "prad_dp_allreduce");
   PRAD_REQUIRE(dtype_ok(dt) && n >= 0 && (buf || n == 0), PRAD_ERR_INVALID, "prad_dp_allreduce: bad argument");
   if (n == 0) return PRAD_OK;
   DpState* d = ctx->dp;
@@ -154,7 +266,7 @@ prad_status prad_dp_allreduce(prad_ctx* ctx, prad_dtype dt, void* buf, int64_t n
 prad_status prad_dp_wait(prad_ctx* ctx) {
   PRAD_CHECK_CTX(ctx);
   PRAD_NOT_CAPTURING(ctx, "prad_dp_wait");
-  PRAD_REQUIRE(ctx->dp && ctx->dp->comm, PRAD_ERR_NOT_INITIALIZED, "prad_dp_wait: call prad_dp_init first");
+  PRAD_DP_READY(ctx, "prad_dp_wait");
   DpState* d = ctx->dp;
   if (!d->pending) return PRAD_OK;
   PRAD_CUDA(cudaEventRecord(d->done, d->comm_stream));

@@ -341,7 +341,9 @@ __device__ __forceinline__ T nary_combine(const T (&v)[PRAD_MAX_SRCS], int count
 
 template <typename T>
 __global__ void __launch_bounds__(256)
-nary_sum_kernel(SrcTable t, T* __restrict__ out, int64_t n, int mode, T inv_count, bool vec) {
+nary_sum_kernel(SrcTable t, T* out, int64_t n, int mode, T inv_count, bool vec) {
+  // `out` is not restrict-qualified: with more than PRAD_MAX_SRCS sources the running sum is read back
+  // through the source table (every thread loads its element before it stores it)
   constexpr int VEC = Vec16<T>::N;
   using V = typename Vec16<T>::type;
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;

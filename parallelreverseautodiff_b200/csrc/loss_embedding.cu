@@ -354,6 +354,17 @@ static prad_status check_bad_index(prad_ctx* ctx, int* d_bad, const char* who) {
   return PRAD_OK;
 }
 
+// Ordered scatter-add for other translation units (the PRAD Tensor gather reverse): dW[idx[i]] += dOut[i]
+// for i ascending; `bad` is a device int that receives 1 + the first offending position.
+prad_status embedding_scatter_ordered(prad_ctx* ctx, prad_dtype dt, const void* index_col, const void* dOut,
+                                      void* dW, int n, int vocab, int dim, int* bad) {
+  int grid = vocab < ctx->sm_count * 8 ? vocab : ctx->sm_count * 8;
+  if (dt == PRAD_F32) embedding_scatter_ordered_kernel<float><<<grid, EMB_THREADS, 0, ctx->stream>>>((const float*)index_col, (const float*)dOut, (float*)dW, n, vocab, dim, bad);
+  else embedding_scatter_ordered_kernel<double><<<grid, EMB_THREADS, 0, ctx->stream>>>((const double*)index_col, (const double*)dOut, (double*)dW, n, vocab, dim, bad);
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
+
 }  // namespace prad
 
 using namespace prad;

@@ -153,7 +153,11 @@ __device__ __forceinline__ void adam_value(const AdamScalars<T>& a, T g, T& w, T
 template <typename T>
 __global__ void __launch_bounds__(MT_THREADS)
 mt_apply_kernel(MultiTensor t, const double* __restrict__ stats, int clip_mode, T clip, T minv,
-                double max_norm, int do_adam, AdamScalars<T> a, int zero_grad) {
+                double max_norm, int do_adam, AdamScalars<T> a, int zero_grad, const int* __restrict__ gemm_gave_up) {
+  // A tensor-core product on this context ran out of a bounded wait: the gradients on the stream are
+  // not valid, so weights, moments and gradients are left exactly as they are (one load per CTA; the
+  // host learns of it at its next prad_sync / prad_download, which returns PRAD_ERR_TIMEOUT).
+  if (gemm_gave_up && *gemm_gave_up != 0) return;
   const int ti = find_tensor(t, blockIdx.x);
   const int64_t start = (int64_t)(blockIdx.x - t.blk_start[ti]) * MT_CHUNK;
   int64_t end = start + MT_CHUNK;
@@ -303,7 +307,7 @@ static prad_status clip_adam_t(prad_ctx* ctx, void* const* w, void* const* g, vo
     }
     mt_apply_kernel<T><<<nb, MT_THREADS, 0, ctx->stream>>>(t, stats, clip_mode, (T)clip_value,
                                                            (T)min_value, clip_value, do_adam, a,
-                                                           zero_grad);
+                                                           zero_grad, ctx->tc_err);
     PRAD_LAUNCHED(ctx);
   }
   if (norm_out) {

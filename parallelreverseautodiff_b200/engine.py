@@ -6,7 +6,7 @@ Nothing here computes: every method forwards to one ``prad_*`` entry point of
 from __future__ import annotations
 
 import ctypes as C
-from typing import Iterable, Optional, Sequence
+from typing import Iterable, List, Optional, Sequence
 
 import numpy as np
 
@@ -562,6 +562,55 @@ class Engine:
                                                   self._p(b), dy.ptr, da.ptr, db.ptr, dy.size))
         return da, db
 
+    # ------------------------------------------------------------ Tensor matmul / gather / tile
+    def tensor_matmul(self, a, b, alpha=1.0, beta=0.0, out=None):
+        """Tensor.MatrixMultiply (src/PRAD/Tensor.cs:572-613); raises PradError(ERR_SHAPE) as it throws."""
+        out = out or self.empty((a.shape[0], b.shape[1]), a.dtype)
+        check(self.lib.prad_tensor_matmul(self.ctx, dtype_code(a.dtype), a.ptr, a.shape[0], a.shape[1], b.ptr,
+                                          b.shape[0], b.shape[1], alpha, beta, out.ptr))
+        return out
+
+    def tensor_matmul_reverse(self, a, b, dc):
+        da, db = self.empty(a.shape, a.dtype), self.empty(b.shape, a.dtype)
+        check(self.lib.prad_tensor_matmul_reverse(self.ctx, dtype_code(a.dtype), a.ptr, a.shape[0], a.shape[1], b.ptr,
+                                                  b.shape[0], b.shape[1], dc.ptr, da.ptr, db.ptr))
+        return da, db
+
+    @staticmethod
+    def _axis_view(shape, axis):
+        outer = int(np.prod(shape[:axis], dtype=np.int64))
+        inner = int(np.prod(shape[axis + 1:], dtype=np.int64))
+        return outer, int(shape[axis]), inner
+
+    def tensor_gather(self, x, indices, axis=0):
+        """Tensor.Gather: result shape = x.shape[:axis] + indices.shape + x.shape[axis+1:]."""
+        outer, n, inner = self._axis_view(x.shape, axis)
+        shape = tuple(x.shape[:axis]) + tuple(indices.shape) + tuple(x.shape[axis + 1:])
+        out = self.empty(shape, x.dtype)
+        check(self.lib.prad_tensor_gather(self.ctx, dtype_code(x.dtype), x.ptr, outer, n, inner, indices.ptr,
+                                          indices.size, out.ptr))
+        return out
+
+    def tensor_gather_reverse(self, upstream, indices, input_shape, axis=0):
+        outer, n, inner = self._axis_view(input_shape, axis)
+        dx = self.empty(input_shape, upstream.dtype)
+        check(self.lib.prad_tensor_gather_reverse(self.ctx, dtype_code(upstream.dtype), upstream.ptr, outer, n, inner,
+                                                  indices.ptr, indices.size, dx.ptr))
+        return dx
+
+    def tensor_tile(self, x, multiples):
+        mr, mc = multiples
+        out = self.empty((x.shape[0] * mr, x.shape[1] * mc), x.dtype)
+        check(self.lib.prad_tensor_tile(self.ctx, dtype_code(x.dtype), x.ptr, x.shape[0], x.shape[1], mr, mc, out.ptr))
+        return out
+
+    def tensor_tile_reverse(self, upstream, input_shape, multiples):
+        mr, mc = multiples
+        dx = self.empty(input_shape, upstream.dtype)
+        check(self.lib.prad_tensor_tile_reverse(self.ctx, dtype_code(upstream.dtype), upstream.ptr, input_shape[0],
+                                                input_shape[1], mr, mc, dx.ptr))
+        return dx
+
     def batchnorm_forward(self, x, out=None):
         """BatchNormalizationOperation as written.  Returns (y, stats) with stats a device [1 x 4] float64."""
         y = out or self.empty(x.shape, x.dtype)
@@ -708,6 +757,75 @@ class Engine:
         self.clip_adam(w, g, m, v, CLIP_NONE, 0.0, 0.0, lr, beta1, beta2, eps, iteration, form,
                        zero_grad)
 
+    # ------------------------------------------------------------ slots, packed transfers, introspection
+    @staticmethod
+    def _guid_bytes(guid) -> bytes:
+        b = guid.bytes if hasattr(guid, "bytes") else bytes(guid)
+        if len(b) != 16:
+            raise ValueError("a slot id is 16 bytes (System.Guid)")
+        return b
+
+    def slot_store(self, guid, mats, copy=False) -> None:
+        """IOperationBase.Store(Guid): keep `mats` (references, or device copies) under the id."""
+        ptrs = (C.c_void_p * len(mats))(*[m.ptr for m in mats])
+        sizes = (C.c_size_t * len(mats))(*[m.nbytes for m in mats])
+        check(self.lib.prad_slot_store(self.ctx, self._guid_bytes(guid), ptrs, sizes, len(mats), int(copy)))
+
+    def slot_restore(self, guid, like):
+        """IOperationBase.Restore(Guid): the stored buffers as (non-owning) matrices shaped like `like`."""
+        out = (C.c_void_p * len(like))()
+        check(self.lib.prad_slot_restore(self.ctx, self._guid_bytes(guid), out, len(like)))
+        return [DeviceMatrix(self, out[i], m.shape, m.dtype, owned=False) for i, m in enumerate(like)]
+
+    def slot_drop(self, guid) -> None:
+        check(self.lib.prad_slot_drop(self.ctx, self._guid_bytes(guid)))
+
+    def slot_count(self) -> int:
+        n = C.c_int()
+        check(self.lib.prad_slot_count(self.ctx, C.byref(n)))
+        return n.value
+
+    def download_many(self, mats) -> List[np.ndarray]:
+        """One packed device-to-host transfer of all `mats` (one wait), split back into arrays."""
+        total = sum(m.nbytes for m in mats)
+        block = np.empty(max(total, 1), np.uint8)
+        ptrs = (C.c_void_p * len(mats))(*[m.ptr for m in mats])
+        sizes = (C.c_size_t * len(mats))(*[m.nbytes for m in mats])
+        check(self.lib.prad_download_many(self.ctx, block.ctypes.data, ptrs, sizes, len(mats)))
+        out, off = [], 0
+        for m in mats:
+            out.append(block[off:off + m.nbytes].view(m.dtype).reshape(m.shape).copy())
+            off += m.nbytes
+        return out
+
+    def upload_many(self, mats, arrays) -> None:
+        block = np.concatenate([np.ascontiguousarray(a, m.dtype).reshape(-1).view(np.uint8) for m, a in zip(mats, arrays)]) \
+            if mats else np.empty(1, np.uint8)
+        ptrs = (C.c_void_p * len(mats))(*[m.ptr for m in mats])
+        sizes = (C.c_size_t * len(mats))(*[m.nbytes for m in mats])
+        check(self.lib.prad_upload_many(self.ctx, ptrs, block.ctypes.data, sizes, len(mats)))
+
+    def device_info(self) -> dict:
+        info = _lib.DeviceInfo()
+        check(self.lib.prad_device_info(self.ctx, C.byref(info)))
+        return {k: (getattr(info, k).decode() if k == "name" else getattr(info, k)) for k, _ in info._fields_}
+
+    def timing_begin(self, label: str) -> None:
+        check(self.lib.prad_timing_begin(self.ctx, label.encode()))
+
+    def timing_end(self) -> None:
+        check(self.lib.prad_timing_end(self.ctx))
+
+    def get_timings(self):
+        """[(label, milliseconds, launches)] of the finished brackets; waits for the stream."""
+        n = C.c_int()
+        check(self.lib.prad_get_timings(self.ctx, None, 0, C.byref(n)))
+        if n.value == 0:
+            return []
+        buf = (_lib.Timing * n.value)()
+        check(self.lib.prad_get_timings(self.ctx, buf, n.value, C.byref(n)))
+        return [(t.label.decode(), t.milliseconds, t.launches) for t in buf]
+
     # ------------------------------------------------------------ data parallel
     @staticmethod
     def dp_unique_id() -> bytes:
@@ -723,6 +841,17 @@ class Engine:
 
     def dp_wait(self) -> None:
         check(self.lib.prad_dp_wait(self.ctx))
+
+    def dp_reduce(self, m: DeviceMatrix, root: int) -> None:
+        check(self.lib.prad_dp_reduce(self.ctx, dtype_code(m.dtype), m.ptr, m.size, root))
+
+    def dp_broadcast(self, m: DeviceMatrix, root: int) -> None:
+        check(self.lib.prad_dp_broadcast(self.ctx, dtype_code(m.dtype), m.ptr, m.size, root))
+
+    def dp_wait_host(self, timeout_ms: float) -> None:
+        """Host-side join with a deadline; raises PradError(ERR_TIMEOUT / ERR_COMM) and leaves the
+        communicator aborted when a peer never arrives."""
+        check(self.lib.prad_dp_wait_host(self.ctx, float(timeout_ms)))
 
     def dp_shutdown(self) -> None:
         check(self.lib.prad_dp_shutdown(self.ctx))

@@ -56,11 +56,20 @@ def row_shard(total_rows: int, rank: int, world: int):
 class FeedForwardNetwork:
     def __init__(self, eng: E.Engine, dtype, sizes: Sequence[int], hidden_act=E.ACT_LEAKY_RELU,
                  output_act=E.ACT_NONE, softmax_output=False, loss="mse", use_bias=True,
-                 clip_mode=E.CLIP_REFERENCE, rank=0, world=1, dp_overlap=True):
+                 clip_mode=E.CLIP_REFERENCE, rank=0, world=1, dp_overlap=True, dp_sharded=False):
         """dp_overlap: all-reduce each weight gradient right after its product (on the communication
-        stream, beside the rest of the backward), or all gradients in one collective at the end."""
+        stream, beside the rest of the backward), or all gradients in one collective at the end.
+        dp_sharded: sharded optimiser -- parameter tensor p belongs to rank p % world: its gradient is
+        reduced to that rank only, which alone clips and updates it (and alone keeps its Adam moments)
+        and broadcasts the new weights while the next step has already begun.  Needs a clip whose
+        statistics are per tensor (the reference's z-score clip, or none)."""
         self.eng = eng
         self.dp_overlap = dp_overlap
+        self.dp_sharded = bool(dp_sharded) and world > 1
+        if self.dp_sharded and clip_mode == E.CLIP_GLOBAL_NORM:
+            raise ValueError("the sharded optimiser needs per-tensor clip statistics; the global-norm clip "
+                             "sums over all tensors")
+        self._bcast_pending = False
         self.dtype = np.dtype(dtype)
         self.sizes = list(sizes)
         self.L = len(sizes) - 1
@@ -86,8 +95,10 @@ class FeedForwardNetwork:
         for p, n in zip(params, sizes_):
             self.grads.append(self._grad_all.view(p.shape, off))
             off += n
-        self.m = [eng.zeros(p.shape, dtype) for p in params]
-        self.v = [eng.zeros(p.shape, dtype) for p in params]
+        # Adam moments: every rank keeps all of them, or only those of the tensors it owns
+        self.owned = [i for i in range(len(params)) if not self.dp_sharded or i % world == rank]
+        self.m = [eng.zeros(p.shape, dtype) if i in self.owned else None for i, p in enumerate(params)]
+        self.v = [eng.zeros(p.shape, dtype) if i in self.owned else None for i, p in enumerate(params)]
         self.dW = self.grads[: self.L]
         self.db = self.grads[self.L:]
         self.rows = 0
@@ -124,6 +135,7 @@ class FeedForwardNetwork:
     def forward(self, x: Optional[E.DeviceMatrix] = None) -> E.DeviceMatrix:
         """Forward through every layer; keeps Z_l (pre-activation) and A_l for the backward."""
         e = self.eng
+        self._join_broadcasts()
         if x is not None:
             self._ensure_buffers(x.shape[0])
             e.copy(self.A[0], x)
@@ -146,6 +158,23 @@ class FeedForwardNetwork:
         return self.loss_dev
 
     # ---------------------------------------------------------------- backward
+    def _owner(self, p: int) -> int:
+        """Rank that owns parameter tensor p (index into self.params) under the sharded optimiser."""
+        return p % self.world
+
+    def _reduce_grad(self, p: int) -> None:
+        if self.dp_sharded:
+            self.eng.dp_reduce(self.grads[p], self._owner(p))
+        else:
+            self.eng.dp_allreduce(self.grads[p])
+
+    def _join_broadcasts(self) -> None:
+        """The weights broadcast by their owners after the last optimiser step must have arrived
+        before a kernel reads them."""
+        if self._bcast_pending:
+            self.eng.dp_wait()
+            self._bcast_pending = False
+
     def _saved(self, l: int):
         """Tensor the activation of layer l keeps for Backward (1-based l)."""
         return self.A[l] if self.acts[l - 1] in _SAVES_OUTPUT else self.Z[l]
@@ -177,12 +206,15 @@ class FeedForwardNetwork:
             e.matmul_backward(self.A[l - 1], None, cur, dB=self.dW[l - 1], need_dA=False)
             if probe:
                 probe("gemm", False)
+            # the first weight-gradient product reads no weights: the broadcasts of the previous step's
+            # new weights run beside it and are joined here, before the first collective of this step
+            self._join_broadcasts()
             if self.world > 1 and self.dp_overlap:
-                e.dp_allreduce(self.dW[l - 1])
+                self._reduce_grad(l - 1)
             if self.use_bias:
                 e.add_broadcast_backward(cur, dbias=self.db[l - 1])
                 if self.world > 1 and self.dp_overlap:
-                    e.dp_allreduce(self.db[l - 1])
+                    self._reduce_grad(L + l - 1)
             if l > 1 or need_dx:
                 below = self.acts[l - 2] if l > 1 else E.ACT_NONE
                 nxt = self.dZ[1].view((rows, self.sizes[l - 1]))
@@ -199,15 +231,30 @@ class FeedForwardNetwork:
         self.dX = cur
         if self.world > 1:
             if not self.dp_overlap:
-                e.dp_allreduce(self._grad_all)
+                if self.dp_sharded:
+                    for p in range(len(self.params)):
+                        self._reduce_grad(p)
+                else:
+                    e.dp_allreduce(self._grad_all)
             e.dp_wait()
 
     # ---------------------------------------------------------------- clip + Adam
     def clip_and_optimize(self, zero_grad: bool = True):
         p = self.Parameters
-        self.eng.clip_adam(self.params, self.grads, self.m, self.v, self.clip_mode, p.ClipValue,
-                           p.MinimumClipValue, p.LearningRate, p.AdamBeta1, p.AdamBeta2,
-                           p.AdamEpsilon, p.AdamIteration, E.ADAM_RMAD, zero_grad)
+        own = self.owned
+        pick = lambda xs: [xs[i] for i in own]
+        if own:
+            self.eng.clip_adam(pick(self.params), pick(self.grads), pick(self.m), pick(self.v), self.clip_mode,
+                               p.ClipValue, p.MinimumClipValue, p.LearningRate, p.AdamBeta1, p.AdamBeta2,
+                               p.AdamEpsilon, p.AdamIteration, E.ADAM_RMAD, zero_grad)
+        if self.dp_sharded:
+            # owners publish their new weights; the tensors the next backward needs first go first.
+            # (Gradients of tensors owned elsewhere keep this rank's partial sums: the next backward
+            # overwrites them.)
+            order = list(range(self.L - 1, -1, -1)) + list(range(self.L, len(self.params)))
+            for i in order:
+                self.eng.dp_broadcast(self.params[i], self._owner(i))
+            self._bcast_pending = True
 
     # ---------------------------------------------------------------- end to end
     def train_step_host(self, x_host: np.ndarray, t_host: np.ndarray, rows_total=None) -> float:

@@ -20,3 +20,17 @@ def engine():
     eng = Engine(0)
     yield eng
     eng.close()
+
+
+def pytest_terminal_summary(terminalreporter):
+    """Share of each stated tolerance that the comparisons of this run used (err / limit)."""
+    try:
+        from util import HEADROOM
+    except ImportError:
+        return
+    rows = [(k, v) for k, v in HEADROOM.items() if v > 0]
+    if not rows:
+        return
+    terminalreporter.write_line("tolerance used (max err / limit) per comparison:")
+    for k, v in sorted(rows, key=lambda kv: -kv[1])[:60]:
+        terminalreporter.write_line(f"  {v:8.4f}  {k}")

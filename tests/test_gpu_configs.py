@@ -117,9 +117,10 @@ def test_c3_lstm_double_bptt(engine, shape):
 
 
 # ------------------------------------------------------------------ C4
-@pytest.mark.parametrize("images", [1])
+@pytest.mark.parametrize("images", [1, 64])
 def test_c4_swin_block_float(engine, images):
-    """dim 96, 3 heads, 7x7 windows over a 56x56 token map (one image = 64 windows here)."""
+    """dim 96, 3 heads, 7x7 windows over a 56x56 token map (one image = 64 windows); 64 images is
+    the configured batch."""
     d, heads, ws, hidden = 96, 3, 49, 384
     T = images * 3136
     r = np.random.default_rng(42)
@@ -138,7 +139,7 @@ def test_c4_swin_block_float(engine, images):
     nw = T // ws
     assert_close(blk.P.numpy().reshape(nw * heads, ws, ws), mid["P"], 1.0, "attention probabilities")
     dx = blk.backward(engine.upload(d_out))
-    assert_close(blk.d_qkv.numpy(), mid["d_qkv"], 10 * rms(mid["d_qkv"]), "d_qkv")
+    assert_close(blk.d_qkv.numpy(), mid["d_qkv"], 10 * rms(mid["d_qkv"]), f"C4[{images}] d_qkv")
     for k in g_ref:
         # weight gradients sum over all T tokens: the error scale is sum |terms| ~ T * typical product
         assert_close(blk.g[k].numpy(), g_ref[k], 30 * rms(g_ref[k]), f"grad {k}")
@@ -178,10 +179,48 @@ def test_c5_wide_mlp_float_reduced(engine, gemm):
         assert_close(net.A[L].numpy(), acts[-1], 10 * rms(acts[-1]), "output")
         net.backward()
         for l in range(L):
-            assert_close(net.dW[l].numpy(), dW_ref[l], 30 * rms(dW_ref[l]), f"dW{l}")
-        assert_close(net.dX.numpy(), d, 30 * rms(d), "dX")
+            assert_close(net.dW[l].numpy(), dW_ref[l], 30 * rms(dW_ref[l]), f"C5 reduced [{gemm}] dW{l}")
+        assert_close(net.dX.numpy(), d, 30 * rms(d), f"C5 reduced [{gemm}] dX")
     finally:
         engine.set_option("gemm_f32", "auto")
+
+
+# ------------------------------------------------------------------ C5 at its real width
+@pytest.mark.parametrize("scheme", ["auto", "tf32b16"])
+def test_c5_layer_at_full_width_elementwise(engine, scheme):
+    """One 4096 x 4096 GELU layer of the benchmark network on 512 batch rows, every output element
+    against the oracle: forward product and GELU, then GELU', dW = A^T dZ and dA = dZ W^T through
+    the path `auto` takes at this size (the tensor-core kernel), and through the tf32b16 option."""
+    if scheme != "auto":
+        engine.set_option("tc_auto", scheme)
+    try:
+        r = np.random.default_rng(42)
+        width, rows = 4096, 512
+        f = np.float32
+        x = r.standard_normal((rows, width)).astype(f)
+        t = r.standard_normal((rows, width)).astype(f)
+        W = (r.standard_normal((width, width)) * np.sqrt(2.0 / width)).astype(f)
+        z = O.matmul_forward(x, W)
+        a = O.gelu_forward(z)
+        d = O.gelu_backward(z, O.mse_backward(a, t))
+        dA_ref, dW_ref = O.matmul_backward(x, W, d)
+        net = FeedForwardNetwork(engine, f, [width, width], hidden_act=E.ACT_GELU, output_act=E.ACT_GELU,
+                                 loss="mse", use_bias=False)
+        net.set_weights([W])
+        net._ensure_buffers(rows)
+        engine.upload(x, out=net.A[0])
+        engine.upload(t, out=net.target)
+        n0 = engine.launch_count()
+        net.forward()
+        # error of a dot product is proportional to sum_k |a_k||b_k|: that is the absolute scale
+        assert_close(net.Z[1].numpy(), z, np.abs(x) @ np.abs(W), f"C5 full width [{scheme}] Z")
+        assert_close(net.A[1].numpy(), a, np.abs(x) @ np.abs(W), f"C5 full width [{scheme}] A")
+        net.backward()
+        assert engine.launch_count() > n0
+        assert_close(net.dW[0].numpy(), dW_ref, np.abs(x.T) @ np.abs(d), f"C5 full width [{scheme}] dW")
+        assert_close(net.dX.numpy(), dA_ref, np.abs(d) @ np.abs(W.T), f"C5 full width [{scheme}] dX")
+    finally:
+        engine.set_option("tc_auto", "fp16x3")
 
 
 def test_overlapped_host_steps_equal_plain_host_steps(engine):

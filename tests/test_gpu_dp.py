@@ -11,7 +11,7 @@ import torch.multiprocessing as mp
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, id_path, out_dir, overlap=True):
+def _worker(rank, world, id_path, out_dir, overlap=True, sharded=False):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     import time
 
@@ -37,7 +37,8 @@ def _worker(rank, world, id_path, out_dir, overlap=True):
     t = r.standard_normal((batch, sizes[-1])).astype(np.float32)
     Ws = [(r.standard_normal((sizes[i], sizes[i + 1])) * np.sqrt(2.0 / sizes[i])).astype(np.float32) for i in range(2)]
     net = FeedForwardNetwork(eng, np.float32, sizes, hidden_act=E.ACT_GELU, output_act=E.ACT_GELU, loss="mse",
-                             use_bias=True, clip_mode=E.CLIP_REFERENCE, rank=rank, world=world, dp_overlap=overlap)
+                             use_bias=True, clip_mode=E.CLIP_REFERENCE, rank=rank, world=world, dp_overlap=overlap,
+                             dp_sharded=sharded)
     net.set_weights(Ws)
     a, b = row_shard(batch, rank, world)
     net._ensure_buffers(b - a)
@@ -47,19 +48,29 @@ def _worker(rank, world, id_path, out_dir, overlap=True):
     net.backward(rows_total=batch)
     grads = [g.numpy() for g in net.grads]
     net.clip_and_optimize(zero_grad=False)
+    net._join_broadcasts()
     weights = [w.numpy() for w in net.params]
-    np.savez(os.path.join(out_dir, f"rank{rank}.npz"), *grads, *weights)
+    # a second step exercises the hand-over of the broadcast weights to the next forward / backward
+    net.forward()
+    net.backward(rows_total=batch)
+    net.clip_and_optimize(zero_grad=False)
+    net._join_broadcasts()
+    weights2 = [w.numpy() for w in net.params]
+    owned = np.array(net.owned)
+    np.savez(os.path.join(out_dir, f"rank{rank}.npz"), *grads, *weights, *weights2, owned=owned)
     eng.dp_shutdown()
     eng.close()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("overlap", [True, False], ids=["per-layer all-reduce", "one collective after the backward"])
-def test_two_gpu_gradients_match_oracle(tmp_path, overlap):
+@pytest.mark.parametrize("overlap,sharded", [(True, False), (False, False), (True, True), (False, True)],
+                         ids=["per-layer all-reduce", "one collective after the backward",
+                              "sharded optimiser, per-layer reduce", "sharded optimiser, reduces after the backward"])
+def test_two_gpu_gradients_match_oracle(tmp_path, overlap, sharded):
     import oracle as O
 
     world = 2
-    mp.spawn(_worker, args=(world, str(tmp_path / "nccl_id"), str(tmp_path), overlap), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, str(tmp_path / "nccl_id"), str(tmp_path), overlap, sharded), nprocs=world, join=True)
     r = np.random.default_rng(42)
     batch, sizes = 96, [40, 64, 24]
     x = r.standard_normal((batch, sizes[0])).astype(np.float32)
@@ -78,9 +89,29 @@ def test_two_gpu_gradients_match_oracle(tmp_path, overlap):
         dA, dW[l] = O.matmul_backward(acts[l], Ws[l], d)
         d = dA
     ref = dW + db
-    r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
-    for k in r0.files:
-        np.testing.assert_array_equal(r0[k], r1[k])          # ranks hold identical results
+    ranks = [np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")]
+    n = len(ref)
     for i, g in enumerate(ref):
-        got = r0[f"arr_{i}"]
-        assert np.abs(got - g).max() <= 1e-5 * np.abs(g).max() + 1e-7, i
+        # the summed gradient lives on every rank (all-reduce) or on the tensor's owner (sharded)
+        holders = [rk for rk in ranks if not sharded or i in rk["owned"]]
+        assert holders
+        for rk in holders:
+            got = rk[f"arr_{i}"]
+            assert np.abs(got - g).max() <= 1e-5 * np.abs(g).max() + 1e-7, i
+        if not sharded:
+            np.testing.assert_array_equal(ranks[0][f"arr_{i}"], ranks[1][f"arr_{i}"])
+    # weights after clip + Adam: identical on both ranks (they were broadcast, or computed from identical
+    # gradients), and equal to the oracle's clip_reference + adam_rmad on the whole-batch gradients
+    params0 = Ws + [np.zeros((1, W.shape[1]), np.float32) for W in Ws]
+    for i in range(n):
+        w_ref, g_ref = params0[i].copy(), ref[i].copy()
+        O.clip_reference(g_ref, np.float32(4.0), np.float32(1e-8))
+        O.adam_rmad(w_ref, np.zeros_like(w_ref), np.zeros_like(w_ref), g_ref, 1e-3, 0.9, 0.999, 1e-8, 1.0)
+        for step in (0, 1):
+            np.testing.assert_array_equal(ranks[0][f"arr_{n * (1 + step) + i}"], ranks[1][f"arr_{n * (1 + step) + i}"])
+        got = ranks[0][f"arr_{n + i}"]
+        upd, upd_ref = got - params0[i], w_ref - params0[i]
+        big = np.abs(g_ref) > 1e-6            # where g ~ 0 the direction of the first Adam step is rounding noise
+        # the update itself is ~lr * sign(g); what can differ is the last bit of the updated weight
+        lim = 1e-5 * 1e-3 + 1e-5 * np.abs(upd_ref[big]) + np.spacing(np.abs(params0[i][big]) + 1e-3)
+        assert (np.abs(upd[big] - upd_ref[big]) <= lim).all(), i

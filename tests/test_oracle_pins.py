@@ -100,6 +100,88 @@ def test_gelu_derivative_is_the_reference_form_not_the_textbook_one():
     assert abs(got - textbook).max() > 1e-3
 
 
+# --- known-answer vectors of test/.../PRAD/TensorReverseTests.cs and PradOpTests.cs for the PRAD Tensor
+# family (transcribed in reference_vectors.py), against the numpy restatement in oracle/__init__.py
+import reference_vectors as RV
+
+
+@pytest.mark.parametrize("case", RV.BINARY_REVERSE, ids=lambda c: c[0].split()[-1])
+def test_reference_tensor_binary_reverse_vectors(case):
+    label, op, a, b, up, want_a, want_b, places = case
+    da, db = O.tensor_binary_reverse(op, np.array(a), np.array(b), np.array(up))
+    RV.check(da, want_a, places, label)
+    RV.check(db, want_b, places, label)
+
+
+@pytest.mark.parametrize("case", RV.BINARY_FORWARD, ids=lambda c: c[0].split()[-1])
+def test_reference_tensor_binary_forward_vectors(case):
+    label, op, a, b, want, places = case
+    RV.check(O.tensor_binary(op, np.array(a), np.array(b)), want, places, label)
+
+
+@pytest.mark.parametrize("case", RV.UNARY_REVERSE, ids=lambda c: c[0].split()[-2] + c[0].split()[-1])
+def test_reference_tensor_unary_reverse_vectors(case):
+    label, op, x, up, want, places = case
+    RV.check(O.tensor_unary_reverse(op, np.array(x), np.array(up)), want, places, label)
+
+
+@pytest.mark.parametrize("case", RV.UNARY_FORWARD, ids=lambda c: c[0].split()[-1])
+def test_reference_tensor_unary_forward_vectors(case):
+    label, op, x, want, places = case
+    RV.check(O.tensor_unary(op, np.array(x)), want, places, label)
+
+
+@pytest.mark.parametrize("case", RV.GATHER, ids=lambda c: c[0].split()[-1])
+def test_reference_tensor_gather_vectors(case):
+    label, shape, table, idx, want, up, want_rev = case
+    x = np.array(table).reshape(shape)
+    RV.check(O.tensor_gather(x, np.array(idx)), want, None, label)
+    RV.check(O.tensor_gather_reverse(np.array(up).reshape(len(idx), shape[1]), np.array(idx), shape), want_rev, None, label)
+
+
+@pytest.mark.parametrize("case", RV.TILE_REVERSE, ids=lambda c: c[0].split()[1])
+def test_reference_tensor_tile_reverse_vectors(case):
+    label, shape, mult, up, want = case
+    up = np.array(up).reshape(shape[0] * mult[0], shape[1] * mult[1])
+    RV.check(O.tensor_tile_reverse(up, shape, mult), want, None, label)
+
+
+@pytest.mark.parametrize("case", RV.TILE_FORWARD, ids=lambda c: c[0].split()[-1])
+def test_reference_tensor_tile_forward_vectors(case):
+    label, shape, x, mult, want = case
+    RV.check(O.tensor_tile(np.array(x).reshape(shape), mult), want, None, label)
+
+
+def test_reference_sum_rows_and_transpose_reverse_vectors():
+    label, shape, up, want = RV.SUM_ROWS_REVERSE
+    RV.check(O.row_sum_backward(np.array(up).reshape(shape[0], 1), shape[1]), want, None, label)
+    for label, (depth, rows, cols), up, want in RV.TRANSPOSE_REVERSE:
+        # the reverse of a transposition transposes the upstream gradient (cols x rows per slice) back
+        up = np.array(up, np.float64).reshape(depth, cols, rows)
+        got = np.stack([O.transpose(up[d]) for d in range(depth)])
+        RV.check(got, want, None, label)
+
+
+def test_tensor_matmul_shape_rule_and_reverse_relation():
+    """Tensor.MatrixMultiply throws on k != other.Shape[0] (src/PRAD/Tensor.cs:582-585); the reverse is the
+    NT / TN pair of TensorReverse.cs:118-156 (no known-answer test exists in the reference for it)."""
+    r = rng(5)
+    a, b, dc = r.standard_normal((7, 5)), r.standard_normal((5, 3)), r.standard_normal((7, 3))
+    with pytest.raises(ValueError, match="Incompatible shapes"):
+        O.tensor_matmul(a, r.standard_normal((4, 3)))
+    np.testing.assert_allclose(O.tensor_matmul(a, b, alpha=2.0), 2.0 * (a @ b), rtol=1e-13)
+    da, db = O.tensor_matmul_reverse(a, b, dc)
+    np.testing.assert_allclose(da, dc @ b.T, rtol=1e-13)
+    np.testing.assert_allclose(db, a.T @ dc, rtol=1e-13)
+
+
+def test_tile_reverse_specialised_rows_case_is_reproduced_as_written():
+    # multiples {2, 1} on a 2 x 2 tensor: the specialised routine adds upstream rows (0, 1) into row 0 and
+    # (2, 3) into row 1, not rows (0, 2) and (1, 3) as the tiling layout would suggest
+    up = np.arange(8.0).reshape(4, 2)
+    np.testing.assert_array_equal(O.tensor_tile_reverse(up, (2, 2), (2, 1)), np.array([[2.0, 4.0], [10.0, 12.0]]))
+
+
 @pytest.mark.parametrize("name", ["f32", "f64"])
 def test_oracle_reproduces_committed_golden_vectors(name):
     import importlib.util
