@@ -47,8 +47,11 @@ def parse():
     ap.add_argument("--width", type=int, default=WIDTH)
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--clip", default="reference", choices=["reference", "global_norm", "none"])
-    ap.add_argument("--dp-mode", default="overlap", choices=["overlap", "end"],
-                    help="N > 1: all-reduce each weight gradient beside the backward, or all of them in one collective after it")
+    ap.add_argument("--dp-mode", default="sharded", choices=["sharded", "overlap", "end"],
+                    help="N > 1: sharded = each weight gradient is reduced to the rank that owns the tensor, beside the "
+                         "backward; the owner alone clips and updates it and broadcasts the new weights beside the next "
+                         "step's first product.  overlap = all-reduce each weight gradient beside the backward, every rank "
+                         "runs the whole optimiser.  end = one all-reduce of all gradients after the backward")
     ap.add_argument("--no-sequence", action="store_true",
                     help="c1..c4: call the entry points every step instead of replaying a recorded launch sequence")
     ap.add_argument("--opt", action="append", default=[], metavar="KEY=VALUE",
@@ -300,7 +303,8 @@ def run_native(args, rank, world, local_rank):
     sizes = [args.width] * (args.layers + 1)
     net = FeedForwardNetwork(eng, np.float32, sizes, hidden_act=E.ACT_GELU, output_act=E.ACT_GELU,
                              loss="mse", use_bias=False, clip_mode=clip, rank=rank, world=world,
-                             dp_overlap=args.dp_mode == "overlap")
+                             dp_overlap=args.dp_mode != "end",
+                             dp_sharded=args.dp_mode == "sharded" and clip != E.CLIP_GLOBAL_NORM)
     net.Parameters.LearningRate = args.lr
     wr = np.random.default_rng(42)  # identical weights on every rank
     net.set_weights([(wr.standard_normal((args.width, args.width), dtype=np.float32)
@@ -337,12 +341,12 @@ def run_native(args, rank, world, local_rank):
         loss = net.train_step_host(x_host, t_host, rows_total=args.batch)
 
     # ---- (A) device-resident hot path: backward + clip + Adam ---------------------------
-    gemm_events = []
+    marks = {"gemm": [], "join": [], "opt": []}
 
     def probe(kind, begin):
         ev = torch.cuda.Event(enable_timing=True)
         ev.record(stream)
-        gemm_events.append(ev)
+        marks[kind].append(ev)
 
     sampler = ClockSampler(local_rank)
     barrier()
@@ -352,14 +356,30 @@ def run_native(args, rank, world, local_rank):
     ev0.record(stream)
     for _ in range(args.steps):
         net.backward(rows_total=args.batch, probe=probe)
+        probe("opt", True)
         net.clip_and_optimize()
+        probe("opt", False)
+    net._join_broadcasts()      # sharded optimiser: the last step's weight broadcasts belong to the timed region
     ev1.record(stream)
     barrier()
     launches = eng.launch_count() - launches0
     ms_total = max_over_ranks(ev0.elapsed_time(ev1))
     ms_step = ms_total / args.steps
-    gemm_ms = sum(gemm_events[i].elapsed_time(gemm_events[i + 1]) for i in range(0, len(gemm_events), 2))
-    n_gemm = len(gemm_events) // 2
+    def bracket_ms(kind):
+        evs = marks[kind]
+        return sum(evs[i].elapsed_time(evs[i + 1]) for i in range(0, len(evs), 2))
+
+    gemm_ms = bracket_ms("gemm")
+    n_gemm = len(marks["gemm"]) // 2
+    # where this rank's step went (device time per step): products with their operand passes, the join
+    # with the communication stream at the end of the backward, clip + Adam; the rest is the loss
+    # gradient, activation derivatives and whatever the stream waited for
+    mine = {"rank": rank, "step_ms": ev0.elapsed_time(ev1) / args.steps, "gemm_ms": gemm_ms / args.steps,
+            "join_ms": bracket_ms("join") / args.steps, "optimizer_ms": bracket_ms("opt") / args.steps}
+    per_rank = [mine]
+    if dist:
+        per_rank = [None] * world
+        dist.all_gather_object(per_rank, mine)
 
     # ---- (B) end to end through the host-buffer API -------------------------------------
     barrier()
@@ -405,6 +425,7 @@ def run_native(args, rank, world, local_rank):
                     "d2h_bytes_per_step": 4 * world, "ms_per_step": e2e_ms, "loss": loss},
             "gpu_launches": int(launches),
             "clocks": clocks,
+            "per_rank": [{k: (round(v, 3) if isinstance(v, float) else v) for k, v in r.items()} for r in per_rank],
         }
         print(json.dumps(line), flush=True)
     if world > 1:

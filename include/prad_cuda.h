@@ -78,14 +78,15 @@ const char* prad_version(void);
  *    simt     : multiply and add rounded separately, k ascending -- bit-identical to the managed
  *               code's sequential `Output[i][j] += a*b` loop (the default for small products);
  *    simt_fma : same order with fused multiply-add (twice the rate, one rounding per step);
- *    fp16x3   : tcgen05 kernel; every row of a K-major operand is scaled by a power of two and
- *               split into two FP16 pieces (22 significant bits); three FP16 products per term
- *               (h1*h0' + h0*h1' + h0*h0'); what "auto" uses for large products.  Error of an
- *               output element: 2^-22 * sum_k |a_ik b_kj| like the TF32 pair, plus at most
- *               sqrt(K) * 2^-39 * max_k|a_ik| * max_k|b_kj|: an element more than ~8 decades
- *               below the largest of its row along k keeps fewer than 22 bits.  Irrelevant
- *               for activations and gradients; a caller whose products pair a huge factor
- *               with a tiny one at the same k should use "tf32b16";
+ *    fp16x3   : tcgen05 kernel; every block of 128 or 256 consecutive k of an operand row is scaled by
+ *               its own power of two and split into two FP16 pieces (22 significant bits); three FP16
+ *               products per term (h1*h0' + h0*h1' + h0*h0'); what "auto" uses for large products.
+ *               Error of an output element: 2^-22 * sum_k |a_ik b_kj| like the TF32 pair, plus at most
+ *               sqrt(K) * 2^-39 * (largest |a| times largest |b| of a block): an element more than ~8
+ *               decades below the largest of its block keeps fewer than 22 bits.  Block scales are
+ *               limited to 2^+-62: blocks whose largest magnitude is below 2^-48 lose bits and values
+ *               above 2^77 overflow.  Irrelevant for activations and gradients; a caller whose
+ *               products pair a huge factor with a tiny one at the same k should use "tf32b16";
  *    tf32b16  : tcgen05 kernel, one TF32 product + two BF16 correction products;
  *    tf32x3   : tcgen05 kernel, three TF32 products per term (a_hi*b_hi + a_lo*b_hi + a_hi*b_lo);
  *    bf16x3   : tcgen05 kernel, six BF16 products of three-piece operands;
@@ -94,7 +95,8 @@ const char* prad_version(void);
  *  "tc_auto" = "fp16x3" | "tf32b16" | "tf32x3" | "bf16x3": the scheme "auto" uses for large products;
  *  "tc_chunk_k" = "128" | "256" | "512" | "1024": k summed inside the tensor core before the partial
  *    sum is added in FP32 with round-to-nearest (the tensor core truncates; default 256: rms error
- *    9e-7 of the result for any K; 512 is 4 % faster at 1.8e-6);
+ *    9e-7 of the result for any K; 512 is 4 % faster at 1.8e-6); for fp16x3 it is also the block
+ *    length of the scales and only 128 and 256 apply (larger values mean 256);
  *  "tc_split_k" = "on" | "off"; "tc_persistent" = "on" | "off" (tf32b16 on the one-tile-per-CTA kernel);
  *  "tc_reserve_sms" = n: SMs the persistent GEMM leaves idle (default 0);
  *  "tc_panel_n" = n: column tiles per panel of the persistent GEMM's tile walk (0 = automatic: two
@@ -206,6 +208,43 @@ prad_status prad_gemm(prad_ctx* ctx, prad_dtype dt, int transA, int transB, int 
                       double alpha, const void* A, int lda, const void* B, int ldb, double beta,
                       void* C, int ldc, int batch, int64_t strideA, int64_t strideB,
                       int64_t strideC);
+
+/* ---------------------------------------------------------------- packed operands (float32, tensor cores)
+ * The tensor-core path of the float GEMM multiplies operands that were first PACKED: cut into blocks of
+ * 128 or 256 consecutive k, every block scaled by its own power of two and every value written as two
+ * FP16 pieces (22 significant bits; see the option "fp16x3").  prad_gemm / prad_matmul_* pack their
+ * operands into scratch on every call.  A caller that keeps a matrix for several products -- the
+ * activation A_l of MatrixMultiplyOperation.Forward that its Backward multiplies again
+ * (src/RMAD/MatrixMultiplyOperation.cs:50-126), the gradient dZ_l that feeds both dA and dW -- packs it
+ * once into a prad_packed object, and can have an elementwise operation write the packed form directly:
+ * LeakyReLU / Sigmoid / Tanh / GELU ... .Forward followed by the next MatrixMultiplyOperation, or an
+ * activation's Backward (dx = dy (.) act'(saved), e.g. GELUOperation.cs:66-84) followed by the
+ * MatrixMultiplyOperation.Backward below it, without the FP32 tensor in between ever being stored.
+ * An object belongs to one R x C matrix shape and holds either or both orientations:
+ *   PRAD_PACK_ROWS  the matrix as an operand with R rows and k = C  (A in A*B; dZ in dZ*W^T; W in dZ*W^T)
+ *   PRAD_PACK_COLS  its transpose: C rows and k = R                 (A and dZ in A^T*dZ; W in A*W)
+ * block_* = 0 picks the block length: the "tc_chunk_k" option (256) for a single form; 128 by rows and
+ * the option's value by columns when both forms are requested (one pass then writes both; two passes
+ * when both are 256).  Two operands of a product need equal k and equal block length.
+ * prad_gemm_packed: C (M x N, pitch ldc) = alpha * opA * opB^T + beta * C (+ bias row), opA M x k, opB N x k.
+ * Accuracy is that of "fp16x3" with the range condition applying per block instead of per row. */
+typedef struct prad_packed prad_packed;
+enum { PRAD_PACK_ROWS = 1, PRAD_PACK_COLS = 2 };
+prad_status prad_packed_create(prad_ctx* ctx, int rows, int cols, int forms, int block_rows_form, int block_cols_form,
+                               prad_packed** out);
+prad_status prad_packed_destroy(prad_packed* p);
+/* rows, cols, forms and the block lengths of an object (any output may be NULL) */
+prad_status prad_packed_shape(const prad_packed* p, int* rows, int* cols, int* forms, int* block_rows_form,
+                              int* block_cols_form);
+/* packs the dense float matrix x (pitch ld floats) */
+prad_status prad_pack(prad_packed* p, const void* x, int64_t ld);
+/* y = act(x) packed; y (dense FP32 copy of the result) may be NULL */
+prad_status prad_act_forward_pack(prad_packed* p, prad_act act, const void* x, void* y, double act_alpha);
+/* dx = dy (.) act'(saved) packed; dx (dense FP32 copy) may be NULL; PRAD_ACT_NONE packs dy itself */
+prad_status prad_act_backward_pack(prad_packed* p, prad_act act, const void* saved, const void* dy, void* dx,
+                                   double act_alpha);
+prad_status prad_gemm_packed(prad_ctx* ctx, const prad_packed* A, int form_a, const prad_packed* B, int form_b,
+                             double alpha, double beta, void* C, int64_t ldc, const void* bias);
 
 /* MatrixMultiplyOperation.Forward (src/RMAD/MatrixMultiplyOperation.cs:50-80) with the
  * optional fused tail  Z = A*B (+ bias row), Y = act(Z):  bias, Z_out and the activation

@@ -44,6 +44,14 @@ SIGNATURES = {
     "prad_free_host": [vp, vp],
     "prad_gemm": [vp, i32, i32, i32, i32, i32, i32, f64, vp, i32, vp, i32, f64, vp, i32, i32, i64,
                   i64, i64],
+    "prad_packed_create": [vp, i32, i32, i32, i32, i32, pvp],
+    "prad_packed_destroy": [vp],
+    "prad_packed_shape": [vp, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int),
+                          C.POINTER(C.c_int)],
+    "prad_pack": [vp, vp, i64],
+    "prad_act_forward_pack": [vp, i32, vp, vp, f64],
+    "prad_act_backward_pack": [vp, i32, vp, vp, vp, f64],
+    "prad_gemm_packed": [vp, vp, i32, vp, i32, f64, f64, vp, i64, vp],
     "prad_matmul_forward": [vp, i32, vp, vp, vp, i32, i32, i32, vp, vp, i32, f64],
     "prad_matmul_backward": [vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, f64, i32, vp, f64],
     "prad_matmul_act_backward": [vp, i32, vp, vp, vp, i32, vp, f64, vp, vp, vp, i32, i32, i32],

@@ -1,7 +1,8 @@
 // FP32 GEMM on the 5th-generation tensor cores: C = alpha*op(A)*op(B) + beta*C computed from
 // split operands, accumulated in FP32 in tensor memory.  Four split schemes share the code:
-//   fp16x3  (MODE 3, default): rows scaled by powers of two, two FP16 pieces per element,
-//           a*b ~= h1*h0' + h0*h1' + h0*h0'  (persistent kernel only);
+//   fp16x3  (MODE 3, default): blocks of 128 or 256 k of every operand row scaled by powers of two,
+//           two FP16 pieces per element, a*b ~= h1*h0' + h0*h1' + h0*h0'  (persistent kernel only;
+//           operands arrive packed, see pack_fp16.cuh);
 //   tf32b16 (MODE 1): a_hi*b_hi in TF32 plus two BF16 correction products;
 //   tf32x3  (MODE 0): a_hi*b_hi + a_lo*b_hi + a_hi*b_lo, a_hi = tf32(a), a_lo = tf32(a - a_hi);
 //   bf16x3  (MODE 2): six BF16 products of three-piece operands.
@@ -38,6 +39,7 @@
 
 #include "act_math.cuh"
 #include "common.cuh"
+#include "pack_fp16.cuh"
 
 namespace prad {
 
@@ -199,10 +201,16 @@ struct Epi {
   const float* saved;
   float act_alpha;
   float alpha, beta;
-  // operands scaled by powers of two (FP16 split): the product of row i and column j is
-  // multiplied by 2^(row_exp[i] + col_exp[j]) first; null when the operands are unscaled
+  // operands scaled by powers of two, one scale for the whole row (unused by the packed FP16 form,
+  // kept for the one-tile kernel's interface): the product of row i and column j is multiplied by
+  // 2^(row_exp[i] + col_exp[j]) first; null when the operands are unscaled
   const int* row_exp;
   const int* col_exp;
+  // packed FP16 operands: block exponents, blk_a[c * blk_lda + i] = e << 23 for block c of row i of A
+  // (likewise B); the partial sum of block c is multiplied by 2^(e_a + e_b) as it is added
+  const int* blk_a = nullptr;
+  const int* blk_b = nullptr;
+  int blk_lda = 0, blk_ldb = 0;
 };
 
 // 2^e as a float, |e| <= 126
@@ -612,7 +620,7 @@ struct TileSched {
 };
 
 template <int PMODE>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __maxnreg__(200)      // 320 threads: 10 warps x 32 x 200 registers fit the 64 K file
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_xb,
                                const __grid_constant__ CUtensorMap map_a_lb, const __grid_constant__ CUtensorMap map_b_hi,
                                const __grid_constant__ CUtensorMap map_b_xb, const __grid_constant__ CUtensorMap map_b_lb,
@@ -828,8 +836,18 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
       for (int g = 0; g < 4; ++g)
 #pragma unroll
         for (int j = 0; j < 32; ++j) sum[g][j] = 0.f;
+      // packed FP16 operands: block c of this slice is block kb0 / chunk_kb + c of the operands
+      const int chunk0 = kb0 / ts.chunk_kb;
+      const int row_blk = min(m0 + sub * 32 + lane, M - 1);     // rows beyond M are never stored
       for (int ch = 0; ch < num_chunks; ++ch, ++gc) {
         const uint32_t buf = gc & 1;
+        // this thread's row exponent and the 128 column exponents of the block, fetched before the wait
+        int ea = 0;
+        const int4* ebp = nullptr;
+        if (PMODE == 3) {
+          ea = epi.blk_a[(int64_t)(chunk0 + ch) * epi.blk_lda + row_blk] + 0x3f800000;   // + the bias of a float's exponent
+          ebp = reinterpret_cast<const int4*>(epi.blk_b + (int64_t)(chunk0 + ch) * epi.blk_ldb + n0 + half * 128);
+        }
         ok = __all_sync(0xffffffffu, mbar_wait(acc_full(buf), (gc >> 1) & 1, err_flag, 3));
         if (!ok) break;
         tc_fence_after();
@@ -838,9 +856,22 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
         for (int g = 0; g < 4; ++g) {
           uint32_t v[32];
           tmem_ld32(taddr + (uint32_t)(g * 32), v);
-          tmem_ld_wait();
+          if (PMODE == 3) {
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) sum[g][j] = __fadd_rn(sum[g][j], __uint_as_float(v[j]));
+            for (int q = 0; q < 8; ++q) {     // the same address in every lane: one broadcast load each
+              const int4 t = __ldg(ebp + g * 8 + q);
+              // sum += partial * 2^(e_a + e_b), rounded once
+              sum[g][4 * q] = __fmaf_rn(__uint_as_float(v[4 * q]), __int_as_float(ea + t.x), sum[g][4 * q]);
+              sum[g][4 * q + 1] = __fmaf_rn(__uint_as_float(v[4 * q + 1]), __int_as_float(ea + t.y), sum[g][4 * q + 1]);
+              sum[g][4 * q + 2] = __fmaf_rn(__uint_as_float(v[4 * q + 2]), __int_as_float(ea + t.z), sum[g][4 * q + 2]);
+              sum[g][4 * q + 3] = __fmaf_rn(__uint_as_float(v[4 * q + 3]), __int_as_float(ea + t.w), sum[g][4 * q + 3]);
+            }
+          } else {
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) sum[g][j] = __fadd_rn(sum[g][j], __uint_as_float(v[j]));
+          }
         }
         tc_fence_before();
         __syncwarp();
@@ -977,153 +1008,6 @@ split_transpose_kernel(const float* __restrict__ src, int64_t src_ld, float* __r
   }
 }
 
-// ---- MODE 3 operand preparation: per-row power-of-two scaling and a two-piece FP16 split --
-// Every row of a K-major operand (an output row of A, an output column of B) is multiplied by
-// 2^s with s chosen so that its largest magnitude lands in [2^14, 2^15), then written as
-// h0 = fp16(x 2^s) and h1 = fp16(x 2^s - h0): 22 significant bits, the same as the TF32
-// pair.  FP16's narrow exponent is harmless after the scaling: what underflows is below
-// 2^-39 of the row's maximum.  exps[row] = -s is applied to the products in the epilogue.
-__device__ __forceinline__ int shift_of(uint32_t absbits) {
-  const int e = (int)((absbits >> 23) & 0xffu);
-  if (e == 0 || e == 255) return 0;            // all zero / denormal, or Inf / NaN present: unscaled
-  // 14 - (e - 127) lies in [-113, 140]; the upper clamp keeps 2^s, 2^-s and the halves of the sum
-  // of two such exponents inside the normal float range (it only costs rows whose largest
-  // magnitude is below 2^-112 a few of their 22 bits)
-  const int s = 14 - (e - 127);
-  return s > 126 ? 126 : s;
-}
-// Both pieces of a row live in one array, interleaved per 32-k block: [h0 of k 0..31 | h1 of k 0..31 |
-// h0 of k 32..63 | ...], so that one 128-byte TMA row (128-byte swizzle) brings both pieces of a k-block
-// and a k-block of an operand is one TMA instruction.  Row pitch = 2 * kp halves.
-__device__ __forceinline__ int64_t il_index(int64_t k) { return (k >> 5) * 64 + (k & 31); }
-__device__ __forceinline__ void fp16_pieces(float xs, __half& p0, __half& p1) {
-  p0 = __float2half_rn(xs);
-  p1 = __float2half_rn(xs - __half2float(p0));   // the difference is exact in FP32
-}
-// src is rows x cols with k contiguous; one warp per row, two passes (the second hits L1/L2)
-__global__ void __launch_bounds__(256)
-split16_rows_kernel(const float* __restrict__ src, int64_t src_ld, __half* __restrict__ hh,
-                    int* __restrict__ exps, int64_t dst_ld, int rows, int cols) {
-  const int lane = threadIdx.x & 31;
-  const bool vec = ((src_ld & 3) == 0) && (((uintptr_t)src & 15) == 0);
-  for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * 8) {
-    const float* s = src + row * src_ld;
-    uint32_t mx = 0;
-    if (vec) {
-      for (int c = lane * 4; c + 4 <= cols; c += 128) {
-        const float4 v = *reinterpret_cast<const float4*>(s + c);
-        mx = max(max(mx, __float_as_uint(fabsf(v.x))), __float_as_uint(fabsf(v.y)));
-        mx = max(max(mx, __float_as_uint(fabsf(v.z))), __float_as_uint(fabsf(v.w)));
-      }
-      for (int c = (cols & ~3) + lane; c < cols; c += 32) mx = max(mx, __float_as_uint(fabsf(s[c])));
-    } else {
-      for (int c = lane; c < cols; c += 32) mx = max(mx, __float_as_uint(fabsf(s[c])));
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    const int sh = shift_of(mx);
-    const float scale = pow2i(sh);
-    if (lane == 0) exps[row] = -sh;
-    __half* d0 = hh + row * 2 * dst_ld;       // h0 of k at il_index(k), h1 32 halves further
-    for (int c = lane * 4; c < dst_ld; c += 128) {
-      float x[4];
-      if (vec && c + 4 <= cols) {
-        const float4 v = *reinterpret_cast<const float4*>(s + c);
-        x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
-      } else {
-#pragma unroll
-        for (int q = 0; q < 4; ++q) x[q] = (c + q < cols) ? s[c + q] : 0.f;
-      }
-      __align__(8) __half p0[4];
-      __align__(8) __half p1[4];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) fp16_pieces(x[q] * scale, p0[q], p1[q]);
-      *reinterpret_cast<uint2*>(d0 + il_index(c)) = *reinterpret_cast<uint2*>(p0);
-      *reinterpret_cast<uint2*>(d0 + il_index(c) + 32) = *reinterpret_cast<uint2*>(p1);
-    }
-  }
-}
-// Largest magnitude of every column of src (rows x cols), as the bit pattern of |x| (for
-// non-negative floats the integer order is the float order, so atomicMax is exact and the
-// result does not depend on the order of arrival).  umax must be zero on entry.
-// Block = cpb column lanes x (256 / cpb) row lanes; VEC: a column lane is four columns.
-template <bool VEC>
-__global__ void __launch_bounds__(256)
-absmax_cols_kernel(const float* __restrict__ src, int64_t ld, int rows, int cols, unsigned* __restrict__ umax,
-                   int cpb, int rows_per_block) {
-  // the row lanes of a block are combined in shared memory first, so that a block sends one atomic
-  // per column: with narrow matrices all blocks hit the same few addresses
-  __shared__ unsigned smax[1024];
-  for (int i = threadIdx.x; i < 4 * cpb; i += 256) smax[i] = 0;
-  __syncthreads();
-  const int cl = threadIdx.x % cpb, rl = threadIdx.x / cpb, rpb = 256 / cpb;
-  const int cg = blockIdx.x * cpb + cl;
-  const int c0 = VEC ? cg * 4 : cg;
-  const bool active = rl < rpb && c0 < cols;
-  const int r_end = min(rows, (int)((blockIdx.y + 1) * rows_per_block));
-  uint32_t m[4] = {0, 0, 0, 0};
-  if (active && VEC && c0 + 4 <= cols) {
-    auto take = [&](const float4& v) {
-      m[0] = max(m[0], __float_as_uint(fabsf(v.x))); m[1] = max(m[1], __float_as_uint(fabsf(v.y)));
-      m[2] = max(m[2], __float_as_uint(fabsf(v.z))); m[3] = max(m[3], __float_as_uint(fabsf(v.w)));
-    };
-    const float* p = src + c0;
-    int r = blockIdx.y * rows_per_block + rl;
-    for (; r + 3 * rpb < r_end; r += 4 * rpb) {     // four independent loads in flight per thread
-      const float4 v0 = __ldg(reinterpret_cast<const float4*>(p + (int64_t)r * ld));
-      const float4 v1 = __ldg(reinterpret_cast<const float4*>(p + (int64_t)(r + rpb) * ld));
-      const float4 v2 = __ldg(reinterpret_cast<const float4*>(p + (int64_t)(r + 2 * rpb) * ld));
-      const float4 v3 = __ldg(reinterpret_cast<const float4*>(p + (int64_t)(r + 3 * rpb) * ld));
-      take(v0); take(v1); take(v2); take(v3);
-    }
-    for (; r < r_end; r += rpb) take(__ldg(reinterpret_cast<const float4*>(p + (int64_t)r * ld)));
-  } else if (active) {
-    const int w = VEC ? min(4, cols - c0) : 1;
-    for (int r = blockIdx.y * rows_per_block + rl; r < r_end; r += rpb)
-      for (int q = 0; q < w; ++q) m[q] = max(m[q], __float_as_uint(fabsf(src[(int64_t)r * ld + c0 + q])));
-  }
-  if (active) {
-#pragma unroll
-    for (int q = 0; q < 4; ++q)
-      if (m[q] != 0) atomicMax(&smax[(VEC ? 4 * cl : cl) + q], m[q]);
-  }
-  __syncthreads();
-  const int width = VEC ? 4 * cpb : cpb, cbase = blockIdx.x * width;
-  for (int i = threadIdx.x; i < width; i += 256)
-    if (cbase + i < cols && smax[i] != 0) atomicMax(umax + cbase + i, smax[i]);
-}
-// src is k_rows x r_cols (k slow); dst is r_cols x dst_ld (k fast), row c scaled by 2^shift_of(umax[c])
-__global__ void __launch_bounds__(256)
-split16_transpose_kernel(const float* __restrict__ src, int64_t src_ld, __half* __restrict__ hh,
-                         const unsigned* __restrict__ umax, int* __restrict__ exps,
-                         int64_t dst_ld, int k_rows, int r_cols) {
-  __shared__ float tile[64][33];
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
-  const int c = blockIdx.x * 32 + tx;
-#pragma unroll
-  for (int j = ty; j < 64; j += 8) {
-    const int r = blockIdx.y * 64 + j;
-    tile[j][tx] = (r < k_rows && c < r_cols) ? src[(int64_t)r * src_ld + c] : 0.f;
-  }
-  __syncthreads();
-  const int k = blockIdx.y * 64 + 2 * tx;    // this lane's pair of k positions
-#pragma unroll
-  for (int j = ty; j < 32; j += 8) {
-    const int c2 = blockIdx.x * 32 + j;
-    if (c2 >= r_cols) continue;
-    const int sh = shift_of(umax[c2]);
-    if (blockIdx.y == 0 && tx == 0) exps[c2] = -sh;
-    if (k >= dst_ld) continue;               // dst_ld is even, so k + 1 < dst_ld as well
-    const float scale = pow2i(sh);
-    __half a0, a1, b0, b1;
-    fp16_pieces(tile[2 * tx][j] * scale, a0, a1);
-    fp16_pieces(tile[2 * tx + 1][j] * scale, b0, b1);
-    __half* d = hh + (int64_t)c2 * 2 * dst_ld + il_index(k);     // k is even: the pair stays inside one block
-    *reinterpret_cast<__half2*>(d) = __halves2half2(a0, b0);
-    *reinterpret_cast<__half2*>(d + 32) = __halves2half2(a1, b1);
-  }
-}
-
 // C = alpha * (P_0 + P_1 + ... ) + beta * C, slices added in order; P_s are dense M x N.
 __global__ void __launch_bounds__(256)
 splitk_combine_kernel(const float* __restrict__ part, int splits, int64_t mn, int M, int N,
@@ -1188,12 +1072,6 @@ struct SplitOperand {
   __nv_bfloat16* xb = nullptr;
   __nv_bfloat16* lb = nullptr;
   __nv_bfloat16* b0 = nullptr;   // MODE 2: pieces are b0, xb (= b1), lb (= b2)
-  // MODE 3: x * 2^-exps[row] = h0 + h1 (+ 2^-22 of it), both FP16, interleaved per 32-k block in
-  // the one array h0 (see il_index); umax is scratch for the column maxima of a transposed source
-  __half* h0 = nullptr;
-  __half* h1 = nullptr;   // unused
-  int* exps = nullptr;
-  unsigned* umax = nullptr;
 };
 
 // cudaFuncSetAttribute applies to the current device only: once per kernel and device (a second,
@@ -1211,8 +1089,8 @@ static cudaError_t reserve_smem(F kernel, int bytes, int device, std::atomic<uin
 template <class CFG>
 static prad_status launch_tf32x3(prad_ctx* ctx, const SplitOperand& a, const SplitOperand& b, int M, int N,
                                  int64_t kp, float* C, int64_t ldc, bool vecC, const Epi& epi) {
-  constexpr bool ONLY_PERSISTENT = CFG::MODE == 3;
-  if constexpr (!ONLY_PERSISTENT) {
+  static_assert(CFG::MODE != 3, "packed FP16 operands go through gemm_fp16x3_packed");
+  {
     static std::atomic<uint64_t> attr_done{0};
     const cudaError_t attr_err = reserve_smem(gemm_tf32x3_kernel<CFG>, CFG::SMEM_BYTES, ctx->device, attr_done);
     PRAD_REQUIRE(attr_err == cudaSuccess, PRAD_ERR_CUDA, "gemm tf32x3: cannot reserve %d bytes of shared memory: %s",
@@ -1220,13 +1098,7 @@ static prad_status launch_tf32x3(prad_ctx* ctx, const SplitOperand& a, const Spl
   }
   CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo, ma_x, mb_x;
   bool ok = true;
-  if (CFG::MODE == 3) {
-    // interleaved pieces: a row is 2 kp halves, a k-block of 32 is one 128-byte box row (h0 | h1)
-    ok = make_map(&ma_x, a.h0, M, (int)(2 * kp), 2 * kp, BM, 2 * CFG::BK, 2, true) &&
-         make_map(&mb_x, b.h0, N, (int)(2 * kp), 2 * kp, BN, 2 * CFG::BK, 2, true);
-    ma_hi = ma_lo = ma_x;
-    mb_hi = mb_lo = mb_x;
-  } else if (CFG::MODE == 2) {
+  if (CFG::MODE == 2) {
     ok = make_map(&ma_hi, a.b0, M, (int)kp, kp, BM, CFG::BK, 2) && make_map(&ma_x, a.xb, M, (int)kp, kp, BM, CFG::BK, 2) &&
          make_map(&ma_lo, a.lb, M, (int)kp, kp, BM, CFG::BK, 2) && make_map(&mb_hi, b.b0, N, (int)kp, kp, BN, CFG::BK, 2) &&
          make_map(&mb_x, b.xb, N, (int)kp, kp, BN, CFG::BK, 2) && make_map(&mb_lo, b.lb, N, (int)kp, kp, BN, CFG::BK, 2);
@@ -1263,8 +1135,8 @@ static prad_status launch_tf32x3(prad_ctx* ctx, const SplitOperand& a, const Spl
       if (kp / sp >= 1024 && eff(sp) > best * 1.02) { best = eff(sp); splits = sp; }
   }
   // MODE 1 and MODE 3 on the persistent kernel: one CTA per SM walks the tiles (and k-slices)
-  constexpr int PMODE = CFG::MODE == 3 ? 3 : 1;
-  const bool persistent = ONLY_PERSISTENT || (CFG::MODE == 1 && CFG::BK == p1::BK && ctx->tc_persistent);
+  constexpr int PMODE = 1;
+  const bool persistent = CFG::MODE == 1 && CFG::BK == p1::BK && ctx->tc_persistent;
   if (persistent) {
     static std::atomic<uint64_t> p_done{0};
     const cudaError_t p_err = reserve_smem(gemm_persistent_kernel<PMODE>, p1::SMEM_BYTES, ctx->device, p_done);
@@ -1284,7 +1156,7 @@ static prad_status launch_tf32x3(prad_ctx* ctx, const SplitOperand& a, const Spl
       const unsigned ctas = (unsigned)(total < sms ? total : sms);
       gemm_persistent_kernel<PMODE><<<ctas, THREADS, p1::SMEM_BYTES, ctx->stream>>>(
           ma_hi, ma_x, ma_lo, mb_hi, mb_x, mb_lo, M, N, out, ldo, vec_out, ep, ctx->tc_err, ts);
-    } else if constexpr (!ONLY_PERSISTENT) {
+    } else {
       dim3 g3 = grid;
       g3.z = (unsigned)nsplit;
       gemm_tf32x3_kernel<CFG><<<g3, THREADS, CFG::SMEM_BYTES, ctx->stream>>>(
@@ -1318,33 +1190,6 @@ static prad_status launch_tf32x3(prad_ctx* ctx, const SplitOperand& a, const Spl
 // writes the split form of one operand; `transposed` = the caller's matrix has k as its slow index
 static prad_status split_operand(prad_ctx* ctx, const float* src, int64_t ld, bool transposed, int rows, int K,
                                  int64_t kp, const SplitOperand& o) {
-  if (o.h0) {   // MODE 3: scaled FP16 pieces
-    if (!transposed) {
-      const int grid = (int)std::min<int64_t>(ceil_div(rows, 8), (int64_t)ctx->sm_count * 32);
-      split16_rows_kernel<<<grid, 256, 0, ctx->stream>>>(src, ld, o.h0, o.exps, kp, rows, K);
-      PRAD_LAUNCHED(ctx);
-      return PRAD_OK;
-    }
-    // source is K x rows: column maxima first, then the transposing split
-    PRAD_CUDA(cudaMemsetAsync(o.umax, 0, (size_t)rows * sizeof(unsigned), ctx->stream));
-    const bool vec = (ld % 4 == 0) && (((uintptr_t)src & 15) == 0);
-    const int lanes = vec ? (int)ceil_div(rows, 4) : rows;      // column lanes in all
-    int cpb = 256;
-    while (cpb > 1 && cpb / 2 >= lanes) cpb /= 2;               // power of two, so 256 / cpb is whole
-    const int gx = (int)ceil_div(lanes, cpb);
-    // enough row slices to fill the machine, each at least 16 rows per row lane
-    int gy = (int)std::max<int64_t>(1, std::min<int64_t>(ceil_div((int64_t)ctx->sm_count * 4, gx),
-                                                          ceil_div(K, (int64_t)16 * (256 / cpb))));
-    const int rows_per_block = (int)ceil_div(K, gy);
-    gy = (int)ceil_div(K, rows_per_block);
-    if (vec) absmax_cols_kernel<true><<<dim3(gx, gy), 256, 0, ctx->stream>>>(src, ld, K, rows, o.umax, cpb, rows_per_block);
-    else absmax_cols_kernel<false><<<dim3(gx, gy), 256, 0, ctx->stream>>>(src, ld, K, rows, o.umax, cpb, rows_per_block);
-    PRAD_LAUNCHED(ctx);
-    dim3 grid((unsigned)ceil_div(rows, 32), (unsigned)ceil_div(kp, 64));
-    split16_transpose_kernel<<<grid, 256, 0, ctx->stream>>>(src, ld, o.h0, o.umax, o.exps, kp, K, rows);
-    PRAD_LAUNCHED(ctx);
-    return PRAD_OK;
-  }
   if (!transposed) {
     int grid = stream_grid(ctx, (int64_t)rows * (kp / 4), 256, 8);
     split_kernel<<<grid, 256, 0, ctx->stream>>>(src, ld, o.hi, o.lo, o.xb, o.lb, o.b0, kp, rows, K);
@@ -1356,7 +1201,80 @@ static prad_status split_operand(prad_ctx* ctx, const float* src, int64_t ld, bo
   return PRAD_OK;
 }
 
+// The persistent kernel on two packed FP16 operands (pack_fp16.cuh): C = alpha * A B^T + beta * C (+ bias).
+static prad_status launch_fp16x3(prad_ctx* ctx, const PackedForm& a, const PackedForm& b, float* C, int64_t ldc,
+                                 float alpha, float beta, const float* bias) {
+  const int M = a.rows, N = b.rows;
+  const int64_t kp = a.kp;
+  PRAD_REQUIRE(encode_fn() != nullptr, PRAD_ERR_UNSUPPORTED, "gemm (tensor core): the driver lacks cuTensorMapEncodeTiled");
+  PRAD_REQUIRE(a.kp == b.kp && a.chunk == b.chunk && a.chunk % p1::BK == 0, PRAD_ERR_SHAPE,
+               "gemm (tensor core): packed operands disagree in k (%lld, %lld) or block length (%d, %d)",
+               (long long)a.kp, (long long)b.kp, a.chunk, b.chunk);
+  CUtensorMap ma, mb;
+  // interleaved pieces: a row is 2 kp halves, a k-group of 32 is one 128-byte box row (h0 | h1)
+  const bool ok = make_map(&ma, a.h, M, (int)(2 * kp), 2 * kp, BM, 2 * p1::BK, 2, true) &&
+                  make_map(&mb, b.h, N, (int)(2 * kp), 2 * kp, BN, 2 * p1::BK, 2, true);
+  PRAD_REQUIRE(ok, PRAD_ERR_CUDA, "gemm (tensor core): cuTensorMapEncodeTiled failed (M %d N %d K %lld)", M, N, (long long)kp);
+  static std::atomic<uint64_t> p_done{0};
+  const cudaError_t p_err = reserve_smem(gemm_persistent_kernel<3>, p1::SMEM_BYTES, ctx->device, p_done);
+  PRAD_REQUIRE(p_err == cudaSuccess, PRAD_ERR_CUDA, "gemm (persistent): cannot reserve %d bytes of shared memory: %s",
+               p1::SMEM_BYTES, cudaGetErrorString(p_err));
+  const int tiles_m = (int)ceil_div(M, BM), tiles_n = (int)ceil_div(N, BN);
+  const int64_t tiles = (int64_t)tiles_m * tiles_n;
+  const int total_kb = (int)(kp / p1::BK), chunk_kb = a.chunk / p1::BK;
+  // Split-K against wave quantisation (see launch_tf32x3); slices start on block boundaries
+  int splits = 1;
+  if (!bias && ctx->tc_split_k) {
+    auto eff = [&](int sp) {
+      const int64_t ctas = tiles * sp;
+      return (double)ctas / (double)(ceil_div(ctas, ctx->sm_count) * ctx->sm_count);
+    };
+    double best = eff(1) * 1.08;   // a split must pay for its extra pass
+    for (int sp = 2; sp <= 64; ++sp)
+      if (kp / sp >= 1024 && eff(sp) > best * 1.02) { best = eff(sp); splits = sp; }
+  }
+  const bool vecC = (((uintptr_t)C & 15) == 0) && (ldc % 4 == 0);
+  Epi epi{bias, nullptr, 0, 0, nullptr, 0.f, alpha, beta, nullptr, nullptr, a.blk, b.blk, a.rows_ld, b.rows_ld};
+  auto launch = [&](int nsplit, int kbps, int64_t stride, float* out, int64_t ldo, bool vec_out, const Epi& ep) {
+    int panel_n = tiles_n;
+    if (ctx->tc_panel_n > 0) panel_n = ctx->tc_panel_n < tiles_n ? ctx->tc_panel_n : tiles_n;
+    else if ((int64_t)N * kp * 4 > ((int64_t)40 << 20) && tiles_n >= 2) panel_n = (tiles_n + 1) / 2;
+    TileSched ts{tiles_m, tiles_n, nsplit, kbps, total_kb, chunk_kb, panel_n, stride};
+    const int64_t total = tiles * nsplit;
+    const int64_t sms = ctx->sm_count - ctx->tc_reserve_sms;
+    const unsigned ctas = (unsigned)(total < sms ? total : sms);
+    gemm_persistent_kernel<3><<<ctas, THREADS, p1::SMEM_BYTES, ctx->stream>>>(ma, ma, ma, mb, mb, mb, M, N, out, ldo, vec_out,
+                                                                              ep, ctx->tc_err, ts);
+  };
+  if (splits == 1) {
+    launch(1, total_kb, 0, C, ldc, vecC, epi);
+    PRAD_LAUNCHED(ctx);
+  } else {
+    const int64_t mn = (int64_t)M * N;
+    prad_status st = ensure_stage(ctx, (size_t)splits * mn * sizeof(float));
+    if (st) return st;
+    float* part = (float*)ctx->stage;
+    Epi raw = epi;
+    raw.alpha = 1.f;
+    raw.beta = 0.f;
+    int kbps = (int)ceil_div(ceil_div(total_kb, splits), chunk_kb) * chunk_kb;
+    splits = (int)ceil_div(total_kb, kbps);   // no empty slice
+    launch(splits, kbps, mn, part, N, true, raw);
+    PRAD_LAUNCHED(ctx);
+    const int cg = stream_grid(ctx, ceil_div(mn, 4), 256, 8);
+    splitk_combine_kernel<<<cg, 256, 0, ctx->stream>>>(part, splits, mn, M, N, C, ldc, alpha, beta);
+    PRAD_LAUNCHED(ctx);
+  }
+  ctx->tc_pending_check = true;
+  return PRAD_OK;
+}
+
 }  // namespace tc
+
+prad_status gemm_fp16x3_packed(prad_ctx* ctx, const PackedForm& a, const PackedForm& b, float alpha, float beta,
+                               float* C, int64_t ldc, const float* bias) {
+  return tc::launch_fp16x3(ctx, a, b, C, ldc, alpha, beta, bias);
+}
 
 prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, double alpha,
                         const void* A, int lda, const void* B, int ldb, double beta, void* C,
@@ -1408,30 +1326,31 @@ prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, do
                    : ctx->gemm_f32 == GemmF32::Tf32B16 ? 1
                    : ctx->gemm_f32 == GemmF32::Bf16x3 ? 2
                    : ctx->gemm_f32 == GemmF32::Fp16x3 ? 3 : ctx->tc_auto_mode;
-  const int64_t kp3 = ceil_div(K, KPAD) * KPAD;
   if (mode == 3) {
-    // scratch: two FP16 pieces per element of both operands, then the exponents and column maxima
-    const size_t a_el = (size_t)M * kp3, b_el = (size_t)N * kp3;
-    const size_t ints = (size_t)ceil_div(M, 4) * 4 + (size_t)ceil_div(N, 4) * 4;
-    prad_status s3 = ensure_workspace(ctx, 2 * (a_el + b_el) * sizeof(__half) + 2 * ints * sizeof(int));
+    // both operands are packed into scratch (pieces, then block exponents), each in one pass
+    const int chunk = ctx->tc_chunk_k == 128 ? 128 : 256;
+    PackedForm fa = packed_form_shape(M, K, chunk), fb = packed_form_shape(N, K, chunk);
+    auto al = [](size_t x) { return (x + 255) & ~(size_t)255; };
+    const size_t need = al(fa.h_bytes()) + al(fb.h_bytes()) + al(fa.blk_bytes()) + al(fb.blk_bytes());
+    prad_status s3 = ensure_workspace(ctx, need);
     if (s3) return s3;
-    SplitOperand a3, b3;
-    a3.h0 = (__half*)ctx->ws;
-    a3.h1 = a3.h0 + a_el;
-    b3.h0 = a3.h1 + a_el;
-    b3.h1 = b3.h0 + b_el;
-    a3.exps = (int*)(b3.h1 + b_el);
-    b3.exps = a3.exps + ceil_div(M, 4) * 4;
-    a3.umax = (unsigned*)(a3.exps + ints);
-    b3.umax = a3.umax + ceil_div(M, 4) * 4;
-    s3 = split_operand(ctx, (const float*)A, lda, tA, M, K, kp3, a3);
+    char* w = (char*)ctx->ws;
+    fa.h = (__half*)w; w += al(fa.h_bytes());
+    fb.h = (__half*)w; w += al(fb.h_bytes());
+    fa.blk = (int*)w; w += al(fa.blk_bytes());
+    fb.blk = (int*)w;
+    // exponents of rows beyond the matrices are read by the last tiles: they must be valid (zero)
+    PRAD_CUDA(cudaMemsetAsync(fa.blk, 0, al(fa.blk_bytes()) + al(fb.blk_bytes()), ctx->stream));
+    PackSource sa, sb;
+    sa.x = (const float*)A; sa.ld = lda;
+    sb.x = (const float*)B; sb.ld = ldb;
+    // op(A) is M x K: memory is M x K unless tA (then K x M, packed by columns).  op(B) is K x N and the
+    // kernel wants N x K: memory already is that when tB, otherwise it is packed by columns.
+    s3 = tA ? pack_fp16(ctx, sa, K, M, nullptr, &fa) : pack_fp16(ctx, sa, M, K, &fa, nullptr);
     if (s3) return s3;
-    s3 = split_operand(ctx, (const float*)B, ldb, !tB, N, K, kp3, b3);
+    s3 = tB ? pack_fp16(ctx, sb, N, K, &fb, nullptr) : pack_fp16(ctx, sb, K, N, nullptr, &fb);
     if (s3) return s3;
-    Epi epi3{(const float*)e.bias, (float*)e.z_out, (int)e.act, (int)e.dact, (const float*)e.saved,
-             (float)e.act_alpha, (float)alpha, (float)beta, a3.exps, b3.exps};
-    const bool vec3 = (((uintptr_t)C & 15) == 0) && (ldc % 4 == 0) && (!e.saved || ((uintptr_t)e.saved & 15) == 0);
-    return launch_tf32x3<Cfg<32, 1, 3>>(ctx, a3, b3, M, N, kp3, (float*)C, ldc, vec3, epi3);
+    return launch_fp16x3(ctx, fa, fb, (float*)C, ldc, (float)alpha, (float)beta, (const float*)e.bias);
   }
 
   // scratch: both operands K-major with pitch kp, 8 bytes per element in either mode

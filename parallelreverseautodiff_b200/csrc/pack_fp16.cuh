@@ -1,0 +1,74 @@
+// Packed FP16-piece form of a float matrix: what the tensor-core FP32 GEMM (gemm_tf32x3.cu, scheme
+// fp16x3) consumes.  Shared between the packing kernels (pack_fp16.cu) and the GEMM.
+//
+// A form holds one orientation of a matrix as a K-major operand: `rows` operand rows of `k` values.
+// Every run of `chunk` consecutive k of a row (a block) is multiplied by its own power of two, chosen
+// so that the block's largest magnitude lands in [2^14, 2^15), and each value is then written as two
+// FP16 pieces h0 = fp16(x 2^s), h1 = fp16(x 2^s - h0): 22 significant bits.  The GEMM sums a block in
+// the tensor core and multiplies the block's partial sum by 2^-(s_a + s_b) when it adds it to the
+// running FP32 sum (one fused multiply-add), so the scales cost nothing and no pass over the matrix
+// is needed to find a whole-row maximum before the first element can be converted.
+//
+// Memory layout of a row: pitch 2*kp halves (kp = k rounded up to 32); the pieces are interleaved per
+// 32-k group, [h0 of k 0..31 | h1 of k 0..31 | h0 of k 32..63 | ...], so that one 128-byte TMA row
+// brings both pieces of a group.  Padding (k..kp) is zero.
+// Block exponents: blk[c * rows_ld + r] = (-s) << 23 for block c of row r (an addend for the exponent
+// field of a float); rows r >= rows hold zero.
+#pragma once
+
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace prad {
+
+constexpr int PACK_KPAD = 32;          // k granularity of the GEMM's operand tiles
+constexpr int PACK_ROWS_ALIGN = 256;   // rows_ld is a multiple of the widest output tile
+constexpr int PACK_EXP_LIMIT = 62;     // |block exponent| <= this, so that the sum of two stays a normal float
+
+struct PackedForm {
+  __half* h = nullptr;
+  int* blk = nullptr;
+  int rows = 0;       // operand rows
+  int64_t k = 0;      // contraction length
+  int64_t kp = 0;     // k rounded up to PACK_KPAD
+  int rows_ld = 0;    // pitch of blk
+  int nchunk = 0;     // blocks per row
+  int chunk = 0;      // k per block (a multiple of 32)
+  size_t h_bytes() const { return (size_t)rows * 2 * kp * sizeof(__half); }
+  size_t blk_bytes() const { return (size_t)nchunk * rows_ld * sizeof(int); }
+};
+
+inline PackedForm packed_form_shape(int rows, int64_t k, int chunk) {
+  PackedForm f;
+  f.rows = rows;
+  f.k = k;
+  f.kp = ceil_div(k, PACK_KPAD) * PACK_KPAD;
+  f.rows_ld = (int)(ceil_div(rows, PACK_ROWS_ALIGN) * PACK_ROWS_ALIGN);
+  f.chunk = chunk;
+  f.nchunk = (int)ceil_div(f.kp, chunk);
+  return f;
+}
+
+// What the packing kernel reads: a plain matrix, or an activation applied on the fly.
+struct PackSource {
+  int kind = 0;                   // 0 plain x ; 1 y = act(x) ; 2 dx = dy * act'(saved)
+  const float* x = nullptr;       // plain: the matrix; forward: pre-activation; backward: saved tensor
+  const float* dy = nullptr;      // backward: upstream gradient
+  float* out = nullptr;           // optional FP32 copy of the computed values (y or dx), same pitch as x
+  int64_t ld = 0;                 // pitch of x, dy and out in floats
+  int act = 0;
+  float act_alpha = 0.f;
+};
+
+// Packs the R x C matrix described by `src` into the requested forms (either may be null):
+//   by_rows: operand rows = R, k = C (the matrix as it is);  by_cols: operand rows = C, k = R (its transpose).
+prad_status pack_fp16(prad_ctx* ctx, const PackSource& src, int R, int C, const PackedForm* by_rows,
+                      const PackedForm* by_cols);
+
+// C (M x N, pitch ldc) = alpha * A B^T + beta * C for two packed operands of equal k, kp and chunk
+// (gemm_tf32x3.cu).
+prad_status gemm_fp16x3_packed(prad_ctx* ctx, const PackedForm& a, const PackedForm& b, float alpha, float beta,
+                               float* C, int64_t ldc, const float* bias);
+
+}  // namespace prad

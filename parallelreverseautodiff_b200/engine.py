@@ -17,6 +17,7 @@ F32, F64 = 0, 1
 ACT_NONE, ACT_LEAKY_RELU, ACT_SIGMOID, ACT_TANH, ACT_GELU, ACT_RELU, ACT_AMPLIFIED_SIGMOID = range(7)
 ADAM_RMAD, ADAM_PRAD = 0, 1
 CLIP_NONE, CLIP_REFERENCE, CLIP_GLOBAL_NORM = 0, 1, 2
+PACK_ROWS, PACK_COLS = 1, 2
 
 _DT = {np.dtype(np.float32): F32, np.dtype(np.float64): F64}
 
@@ -88,6 +89,47 @@ class DeviceMatrix:
             pass
 
 
+class PackedOperand:
+    """A float matrix in the packed FP16-piece form of the tensor-core GEMM (prad_packed): by rows
+    (the matrix as an operand with k = its columns), by columns (its transpose), or both."""
+
+    def __init__(self, engine: "Engine", rows: int, cols: int, forms: int, block_rows=0, block_cols=0):
+        self.engine, self.rows, self.cols, self.forms = engine, int(rows), int(cols), int(forms)
+        h = C.c_void_p()
+        check(engine.lib.prad_packed_create(engine.ctx, self.rows, self.cols, self.forms, block_rows, block_cols,
+                                            C.byref(h)))
+        self.handle = h
+
+    def blocks(self):
+        br, bc = C.c_int(), C.c_int()
+        check(self.engine.lib.prad_packed_shape(self.handle, None, None, None, C.byref(br), C.byref(bc)))
+        return br.value, bc.value
+
+    def pack(self, x: "DeviceMatrix", ld: Optional[int] = None) -> "PackedOperand":
+        check(self.engine.lib.prad_pack(self.handle, x.ptr, ld or self.cols))
+        return self
+
+    def act_forward(self, act: int, x: "DeviceMatrix", y: Optional["DeviceMatrix"] = None, alpha=0.0):
+        check(self.engine.lib.prad_act_forward_pack(self.handle, act, x.ptr, y.ptr if y is not None else None, alpha))
+        return self
+
+    def act_backward(self, act: int, saved, dy: "DeviceMatrix", dx: Optional["DeviceMatrix"] = None, alpha=0.0):
+        check(self.engine.lib.prad_act_backward_pack(self.handle, act, saved.ptr if saved is not None else None, dy.ptr,
+                                                     dx.ptr if dx is not None else None, alpha))
+        return self
+
+    def free(self) -> None:
+        if self.handle and self.engine is not None and self.engine.ctx:
+            self.engine.lib.prad_packed_destroy(self.handle)
+        self.handle = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
 class Sequence:
     """A recorded launch sequence of one Engine (prad_sequence)."""
 
@@ -116,6 +158,7 @@ class Engine:
         check(self.lib.prad_init(int(device), C.byref(ctx)))
         self.ctx = ctx
         self.device = device
+        self.options = {}          # what set_option was given (the library has no getter)
 
     # ------------------------------------------------------------ lifecycle
     def close(self) -> None:
@@ -134,6 +177,12 @@ class Engine:
 
     def set_option(self, key: str, value: str) -> None:
         check(self.lib.prad_set_option(self.ctx, key.encode(), value.encode()))
+        self.options[key] = value
+
+    def packs_large_float_products(self) -> bool:
+        """True while large float products take the packed FP16 tensor-core path (the defaults)."""
+        return (self.options.get("gemm_f32", "auto") in ("auto", "fp16x3")
+                and self.options.get("tc_auto", "fp16x3") == "fp16x3")
 
     def launch_count(self) -> int:
         n = C.c_int64()
@@ -296,6 +345,17 @@ class Engine:
         ldc = ldc or Cm.shape[-1]
         check(self.lib.prad_gemm(self.ctx, dt, int(transA), int(transB), M, N, K, alpha, A.ptr, lda,
                                  B.ptr, ldb, beta, Cm.ptr, ldc, batch, strideA, strideB, strideC))
+
+    def packed(self, rows, cols, forms, block_rows=0, block_cols=0) -> PackedOperand:
+        return PackedOperand(self, rows, cols, forms, block_rows, block_cols)
+
+    def gemm_packed(self, A: PackedOperand, form_a: int, B: PackedOperand, form_b: int, out: DeviceMatrix,
+                    alpha=1.0, beta=0.0, bias=None, ldc=None):
+        """out (M x N) = alpha * opA * opB^T + beta * out (+ bias row); prad_gemm_packed."""
+        n = B.rows if form_b == PACK_ROWS else B.cols
+        check(self.lib.prad_gemm_packed(self.ctx, A.handle, form_a, B.handle, form_b, alpha, beta, out.ptr,
+                                        ldc or n, self._p(bias)))
+        return out
 
     def matmul_forward(self, A, B, Y=None, bias=None, Z_out=None, act=ACT_NONE, act_alpha=0.0):
         M, K = A.shape

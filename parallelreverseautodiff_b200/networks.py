@@ -13,8 +13,14 @@ every rank holds a contiguous block of rows and the weight gradients are all-red
 Backward schedule per layer, last to first:
     dW_l = A_{l-1}^T dZ_l          -> all-reduce of dW_l starts on the communication stream
     db_l = column sums of dZ_l     -> all-reduce likewise
-    dZ_{l-1} = (dZ_l W_l^T) (.) act'(saved_{l-1})   (derivative fused into the GEMM epilogue)
+    dZ_{l-1} = (dZ_l W_l^T) (.) act'(saved_{l-1})
 so a layer's collective overlaps with the GEMMs of the layers below it.
+
+Large float networks run "packed": every tensor that feeds a product is written once, by the kernel
+that computes it, in the operand form of the tensor-core GEMM (prad_packed), in both orientations --
+the activation A_l by the forward activation pass (for Z_{l+1} = A_l W and, later, dW = A_l^T dZ), the
+gradient dZ_l by the activation's Backward (for dW and for dA = dZ_l W^T) -- so no product has to
+read an FP32 tensor back, find its maxima and convert it first.
 """
 from __future__ import annotations
 
@@ -56,7 +62,8 @@ def row_shard(total_rows: int, rank: int, world: int):
 class FeedForwardNetwork:
     def __init__(self, eng: E.Engine, dtype, sizes: Sequence[int], hidden_act=E.ACT_LEAKY_RELU,
                  output_act=E.ACT_NONE, softmax_output=False, loss="mse", use_bias=True,
-                 clip_mode=E.CLIP_REFERENCE, rank=0, world=1, dp_overlap=True, dp_sharded=False):
+                 clip_mode=E.CLIP_REFERENCE, rank=0, world=1, dp_overlap=True, dp_sharded=False, packed="auto",
+                 pack_block_cols=0):
         """dp_overlap: all-reduce each weight gradient right after its product (on the communication
         stream, beside the rest of the backward), or all gradients in one collective at the end.
         dp_sharded: sharded optimiser -- parameter tensor p belongs to rank p % world: its gradient is
@@ -64,6 +71,10 @@ class FeedForwardNetwork:
         and broadcasts the new weights while the next step has already begun.  Needs a clip whose
         statistics are per tensor (the reference's z-score clip, or none)."""
         self.eng = eng
+        self.packed_mode = packed          # "auto" | True | False: operands packed where they are produced
+        self.pack_block_cols = pack_block_cols   # block length of the by-columns forms (0 = the library's default)
+        self.packed = False                # decided per batch size in _ensure_buffers
+        self._w_dirty = True
         self.dp_overlap = dp_overlap
         self.dp_sharded = bool(dp_sharded) and world > 1
         if self.dp_sharded and clip_mode == E.CLIP_GLOBAL_NORM:
@@ -111,6 +122,7 @@ class FeedForwardNetwork:
 
     # ---------------------------------------------------------------- set-up
     def set_weights(self, weights: Sequence[np.ndarray], biases: Optional[Sequence[np.ndarray]] = None):
+        self._w_dirty = True
         for l, w in enumerate(weights):
             self.eng.upload(np.ascontiguousarray(w, self.dtype), out=self.W[l])
         if biases is not None:
@@ -122,6 +134,10 @@ class FeedForwardNetwork:
             return
         e, dt = self.eng, self.dtype
         self.rows = rows
+        self.packed = self._wants_packed(rows)
+        if self.packed:
+            self._make_packed(rows)
+            return
         self.A = [e.empty((rows, self.sizes[0]), dt)] + [e.empty((rows, n), dt) for n in self.sizes[1:]]
         self.Z = [None] + [e.empty((rows, n), dt) if self.acts[l] != E.ACT_NONE else None
                            for l, n in enumerate(self.sizes[1:])]
@@ -131,11 +147,113 @@ class FeedForwardNetwork:
         if self.softmax_output:
             self.probs = e.empty((rows, self.sizes[-1]), dt)
 
+    # ---------------------------------------------------------------- packed operands
+    def _wants_packed(self, rows: int) -> bool:
+        if self.packed_mode is False or self.dtype != np.float32 or self.softmax_output:
+            return False
+        if self.packed_mode is True:
+            return True
+        big = all(rows * a * b >= (1 << 27) for a, b in zip(self.sizes[:-1], self.sizes[1:]))
+        return big and rows >= 256 and min(self.sizes) >= 256 and self.eng.packs_large_float_products()
+
+    def _make_packed(self, rows: int) -> None:
+        e, dt, L = self.eng, self.dtype, self.L
+        both = E.PACK_ROWS | E.PACK_COLS
+        bc = self.pack_block_cols
+        # FP32 tensors that are still needed: the input, the saved tensor of every activation, the output
+        self.A = [e.empty((rows, self.sizes[0]), dt)] + [None] * L
+        self.Z = [None] * (L + 1)
+        for l in range(1, L + 1):
+            act = self.acts[l - 1]
+            if act != E.ACT_NONE and act not in _SAVES_OUTPUT:
+                self.Z[l] = e.empty((rows, self.sizes[l]), dt)
+            if l == L or act in _SAVES_OUTPUT or act == E.ACT_NONE:
+                self.A[l] = e.empty((rows, self.sizes[l]), dt)
+        widest = max(self.sizes)
+        self.dZ = [e.empty((rows * widest,), dt), e.empty((rows * widest,), dt)]
+        self.target = e.empty((rows, self.sizes[-1]), dt)
+        # A_0 .. A_{L-1}: by rows for the forward product, by columns for the weight gradient
+        self.PA = [e.packed(rows, self.sizes[l], both, 0, bc) for l in range(L)]
+        # dZ_l: by columns for the weight gradient, by rows for the gradient of the layer below; one object
+        # per width (layer l's is dead when layer l-1's is written)
+        self.PD = {}
+        for l in range(1, L + 1):
+            if self.sizes[l] not in self.PD:
+                self.PD[self.sizes[l]] = e.packed(rows, self.sizes[l], both, 0, bc)
+        # W_l: by columns it multiplies A_l (forward), by rows it multiplies dZ_{l+1} (backward); its block
+        # lengths are those of the by-rows forms it meets
+        blk_a = self.PA[0].blocks()[0]
+        blk_d = next(iter(self.PD.values())).blocks()[0]
+        self.PW = [e.packed(self.sizes[l], self.sizes[l + 1], both, blk_d, blk_a) for l in range(L)]
+        self._w_dirty = True
+
+    def _pack_weights(self) -> None:
+        if self._w_dirty:
+            for l in range(self.L):
+                self.PW[l].pack(self.W[l])
+            self._w_dirty = False
+
+    def _forward_packed(self) -> E.DeviceMatrix:
+        e, L = self.eng, self.L
+        alpha = self.Parameters.LeakyReLUAlpha
+        self._pack_weights()
+        self.PA[0].pack(self.A[0])
+        for l in range(L):
+            act = self.acts[l]
+            pre = self.Z[l + 1] if self.Z[l + 1] is not None else self.A[l + 1]
+            e.gemm_packed(self.PA[l], E.PACK_ROWS, self.PW[l], E.PACK_COLS, pre,
+                          bias=self.b[l] if self.use_bias else None)
+            if l + 1 < L:      # the activation writes the next layer's operand (and A_{l+1} in FP32 if kept)
+                self.PA[l + 1].act_forward(act, pre, self.A[l + 1], alpha)
+            elif act != E.ACT_NONE:
+                e.act_forward(act, pre, alpha, out=self.A[L])
+        return self.A[L]
+
+    def _backward_packed(self, g: E.DeviceMatrix, probe, need_dx: bool) -> None:
+        """g = gradient of the loss with respect to A_L (FP32)."""
+        e, L, rows = self.eng, self.L, self.rows
+        alpha = self.Parameters.LeakyReLUAlpha
+        for l in range(L, 0, -1):
+            act = self.acts[l - 1]
+            pd = self.PD[self.sizes[l]]
+            dz32 = None
+            if self.use_bias:                        # the bias gradient sums the FP32 gradient's columns
+                dz32 = self.dZ[1].view((rows, self.sizes[l]))
+            pd.act_backward(act, self._saved(l) if act != E.ACT_NONE else None, g, dz32, alpha)
+            if probe:
+                probe("gemm", True)
+            e.gemm_packed(self.PA[l - 1], E.PACK_COLS, pd, E.PACK_COLS, self.dW[l - 1])
+            if probe:
+                probe("gemm", False)
+            # the first weight-gradient product reads no weights: the previous step's weight broadcasts run
+            # beside it; they are joined here, and only then are the (new) weights packed
+            self._join_broadcasts()
+            self._pack_weights()
+            if self.world > 1 and self.dp_overlap:
+                self._reduce_grad(l - 1)
+            if self.use_bias:
+                e.add_broadcast_backward(dz32, dbias=self.db[l - 1])
+                if self.world > 1 and self.dp_overlap:
+                    self._reduce_grad(L + l - 1)
+            if l > 1 or need_dx:
+                g = self.dZ[0].view((rows, self.sizes[l - 1]))
+                if probe:
+                    probe("gemm", True)
+                e.gemm_packed(pd, E.PACK_ROWS, self.PW[l - 1], E.PACK_ROWS, g)
+                if probe:
+                    probe("gemm", False)
+        self.dX = g
+
     # ---------------------------------------------------------------- forward
     def forward(self, x: Optional[E.DeviceMatrix] = None) -> E.DeviceMatrix:
         """Forward through every layer; keeps Z_l (pre-activation) and A_l for the backward."""
         e = self.eng
         self._join_broadcasts()
+        if self.packed or (x is not None and self._wants_packed(x.shape[0])):
+            if x is not None:
+                self._ensure_buffers(x.shape[0])
+                e.copy(self.A[0], x)
+            return self._forward_packed()
         if x is not None:
             self._ensure_buffers(x.shape[0])
             e.copy(self.A[0], x)
@@ -198,6 +316,10 @@ class FeedForwardNetwork:
             e.softmax_backward(self.probs, cur, out=nxt)
             self.dZ.reverse()
             cur = nxt
+        if self.packed:
+            self._backward_packed(cur, probe, need_dx)
+            self._finish_backward(probe)
+            return
         if self.acts[L - 1] != E.ACT_NONE:
             e.act_backward(self.acts[L - 1], self._saved(L), cur, alpha, out=cur)
         for l in range(L, 0, -1):
@@ -229,6 +351,10 @@ class FeedForwardNetwork:
                 self.dZ.reverse()
                 cur = nxt
         self.dX = cur
+        self._finish_backward(probe)
+
+    def _finish_backward(self, probe=None) -> None:
+        e = self.eng
         if self.world > 1:
             if not self.dp_overlap:
                 if self.dp_sharded:
@@ -236,11 +362,16 @@ class FeedForwardNetwork:
                         self._reduce_grad(p)
                 else:
                     e.dp_allreduce(self._grad_all)
+            if probe:
+                probe("join", True)
             e.dp_wait()
+            if probe:
+                probe("join", False)
 
     # ---------------------------------------------------------------- clip + Adam
     def clip_and_optimize(self, zero_grad: bool = True):
         p = self.Parameters
+        self._w_dirty = True
         own = self.owned
         pick = lambda xs: [xs[i] for i in own]
         if own:
