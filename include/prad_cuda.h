@@ -540,6 +540,14 @@ prad_status prad_graph_add_node(prad_graph* g, prad_op op, const int* in_values,
 prad_status prad_graph_forward(prad_graph* g);
 /* Backward from `start_value` with upstream gradient d_start (device matrix of that shape). */
 prad_status prad_graph_backward(prad_graph* g, int start_value, const void* d_start);
+/* Backward from several start values at once (host arrays of `count` entries): one reverse walk in which
+ * every listed value receives its upstream gradient -- the losses of all time steps of an unrolled
+ * recurrent graph in one pass, where the managed code starts one visitor per time step
+ * (OperationNeuralNetworkVisitor with a startOperationIndex, src/RMAD/OperationNeuralNetworkVisitor.cs:
+ * 60-78) and every visitor walks the whole graph below its start again.  The result is the sum of the
+ * single-start backwards (the walk is linear in the upstream gradients); a start value that also has
+ * consumers inside the walk adds its upstream gradient first, then the consumers' in their order. */
+prad_status prad_graph_backward_multi(prad_graph* g, const int* start_values, const void* const* d_starts, int count);
 /* Device pointers valid until the next forward/backward (NULL gradient = not reached). */
 prad_status prad_graph_value_data(prad_graph* g, int value, void** out_data);
 prad_status prad_graph_value_gradient(prad_graph* g, int value, void** out_grad);

@@ -121,6 +121,7 @@ SIGNATURES = {
     "prad_graph_add_node": [vp, i32, C.POINTER(C.c_int), i32, i32, f64, C.POINTER(C.c_int)],
     "prad_graph_forward": [vp],
     "prad_graph_backward": [vp, i32, vp],
+    "prad_graph_backward_multi": [vp, C.POINTER(C.c_int), pvp, i32],
     "prad_graph_value_data": [vp, i32, pvp],
     "prad_graph_value_gradient": [vp, i32, pvp],
     "prad_graph_consumer_count": [vp, i32, C.POINTER(C.c_int)],

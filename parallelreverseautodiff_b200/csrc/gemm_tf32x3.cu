@@ -154,6 +154,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
       : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor of a K-major tile stored as rows of SW bytes (SW = 128, 64
@@ -620,7 +628,7 @@ struct TileSched {
 };
 
 template <int PMODE>
-__global__ void __maxnreg__(200)      // 320 threads: 10 warps x 32 x 200 registers fit the 64 K file
+__global__ void __maxnreg__(192)      // 320 threads: 10 warps x 6144 registers (allocated per warp in units of 512) fit the 64 K file
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_xb,
                                const __grid_constant__ CUtensorMap map_a_lb, const __grid_constant__ CUtensorMap map_b_hi,
                                const __grid_constant__ CUtensorMap map_b_xb, const __grid_constant__ CUtensorMap map_b_lb,
@@ -852,22 +860,29 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
         if (!ok) break;
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + buf * (uint32_t)BN + (uint32_t)(half * 128);
+        if (PMODE == 3) {
+          // 16 columns per load keep the live registers (128 running sums + one load) inside the budget
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint32_t v[32];
-          tmem_ld32(taddr + (uint32_t)(g * 32), v);
-          if (PMODE == 3) {
+          for (int g = 0; g < 8; ++g) {
+            uint32_t v[16];
+            tmem_ld16(taddr + (uint32_t)(g * 16), v);
             tmem_ld_wait();
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {     // the same address in every lane: one broadcast load each
-              const int4 t = __ldg(ebp + g * 8 + q);
+            for (int q = 0; q < 4; ++q) {     // the same address in every lane: one broadcast load each
+              const int4 t = __ldg(ebp + g * 4 + q);
+              float* acc = &sum[g >> 1][(g & 1) * 16 + 4 * q];
               // sum += partial * 2^(e_a + e_b), rounded once
-              sum[g][4 * q] = __fmaf_rn(__uint_as_float(v[4 * q]), __int_as_float(ea + t.x), sum[g][4 * q]);
-              sum[g][4 * q + 1] = __fmaf_rn(__uint_as_float(v[4 * q + 1]), __int_as_float(ea + t.y), sum[g][4 * q + 1]);
-              sum[g][4 * q + 2] = __fmaf_rn(__uint_as_float(v[4 * q + 2]), __int_as_float(ea + t.z), sum[g][4 * q + 2]);
-              sum[g][4 * q + 3] = __fmaf_rn(__uint_as_float(v[4 * q + 3]), __int_as_float(ea + t.w), sum[g][4 * q + 3]);
+              acc[0] = __fmaf_rn(__uint_as_float(v[4 * q]), __int_as_float(ea + t.x), acc[0]);
+              acc[1] = __fmaf_rn(__uint_as_float(v[4 * q + 1]), __int_as_float(ea + t.y), acc[1]);
+              acc[2] = __fmaf_rn(__uint_as_float(v[4 * q + 2]), __int_as_float(ea + t.z), acc[2]);
+              acc[3] = __fmaf_rn(__uint_as_float(v[4 * q + 3]), __int_as_float(ea + t.w), acc[3]);
             }
-          } else {
+          }
+        } else {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint32_t v[32];
+            tmem_ld32(taddr + (uint32_t)(g * 32), v);
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j) sum[g][j] = __fadd_rn(sum[g][j], __uint_as_float(v[j]));

@@ -18,6 +18,7 @@ struct GValue {
   std::vector<void*> contrib;  // contributions of the consumers, in consumer order
   void* sum_buf = nullptr;     // fan-in sum (graph-owned, reused)
   int consumers = 0;
+  int produced_by = -1;        // node that writes this value (-1: a leaf holding caller data)
 };
 
 struct GNode {
@@ -133,12 +134,20 @@ prad_status prad_graph_add_node(prad_graph* g, prad_op op, const int* in_values,
                (int)op, arity(op), n_in);
   const int nv = (int)g->values.size();
   PRAD_REQUIRE(out_value >= 0 && out_value < nv, PRAD_ERR_INVALID, "prad_graph_add_node: bad output value id");
-  for (int i = 0; i < n_in; ++i)
+  for (int i = 0; i < n_in; ++i) {
     PRAD_REQUIRE(in_values[i] >= 0 && in_values[i] < nv && in_values[i] != out_value, PRAD_ERR_INVALID,
                  "prad_graph_add_node: bad input value id at position %d", i);
+    // nodes arrive in forward order: an input is caller data or the output of an earlier node
+    const GValue& iv = g->values[in_values[i]];
+    PRAD_REQUIRE(iv.produced_by >= 0 || (iv.data != nullptr && !iv.owned), PRAD_ERR_INVALID,
+                 "prad_graph_add_node: input %d (value %d) has neither caller data nor an earlier producer", i,
+                 in_values[i]);
+  }
   GValue& o = g->values[out_value];
   PRAD_REQUIRE(o.data == nullptr || o.owned, PRAD_ERR_INVALID,
                "prad_graph_add_node: the output value must be graph-owned (added with data == NULL)");
+  PRAD_REQUIRE(o.produced_by < 0, PRAD_ERR_INVALID,
+               "prad_graph_add_node: value %d is already the output of node %d", out_value, o.produced_by);
   auto& V = g->values;
   const GValue& a = V[in_values[0]];
   // shape rules of the managed operations
@@ -175,6 +184,7 @@ prad_status prad_graph_add_node(prad_graph* g, prad_op op, const int* in_values,
   n.scalar = scalar;
   n.in_grad.assign(n_in, nullptr);
   g->nodes.push_back(n);
+  g->values[out_value].produced_by = (int)g->nodes.size() - 1;
   if (out_node) *out_node = (int)g->nodes.size() - 1;
   return PRAD_OK;
 }
@@ -335,15 +345,21 @@ prad_status prad_graph_forward(prad_graph* g) {
   return PRAD_OK;
 }
 
-prad_status prad_graph_backward(prad_graph* g, int start_value, const void* d_start) {
+prad_status prad_graph_backward_multi(prad_graph* g, const int* start_values, const void* const* d_starts, int count) {
   PRAD_CHECK_GRAPH(g);
   auto& V = g->values;
-  PRAD_REQUIRE(start_value >= 0 && start_value < (int)V.size() && d_start, PRAD_ERR_INVALID,
-               "prad_graph_backward: bad start value or null gradient");
-  // 1. which nodes lie on a path to the start value, and how many consumers each value has
+  PRAD_REQUIRE(count >= 1 && start_values && d_starts, PRAD_ERR_INVALID, "prad_graph_backward: no start value");
+  for (int i = 0; i < count; ++i) {
+    PRAD_REQUIRE(start_values[i] >= 0 && start_values[i] < (int)V.size() && d_starts[i], PRAD_ERR_INVALID,
+                 "prad_graph_backward: bad start value or null gradient at position %d", i);
+    for (int j = 0; j < i; ++j)
+      PRAD_REQUIRE(start_values[j] != start_values[i], PRAD_ERR_INVALID, "prad_graph_backward: start value %d is listed twice",
+                   start_values[i]);
+  }
+  // 1. which nodes lie on a path to a start value, and how many consumers each value has
   //    there (OperationGraphVisitor's dependency counts)
-  std::vector<char> needed(V.size(), 0);
-  needed[start_value] = 1;
+  std::vector<char> needed(V.size(), 0), is_start(V.size(), 0);
+  for (int i = 0; i < count; ++i) needed[start_values[i]] = is_start[start_values[i]] = 1;
   for (GValue& v : V) { v.contrib.clear(); v.grad = nullptr; v.consumers = 0; }
   std::vector<char> live(g->nodes.size(), 0);
   for (int k = (int)g->nodes.size() - 1; k >= 0; --k) {
@@ -354,14 +370,15 @@ prad_status prad_graph_backward(prad_graph* g, int start_value, const void* d_st
   }
   // 2. one reverse walk.  Nodes were added in forward order, so every consumer of a value
   //    has delivered its contribution before the value's producer is reached; contributions
-  //    arrive in reverse consumer order and are summed in consumer (registration) order.
-  V[start_value].contrib.push_back(const_cast<void*>(d_start));
-  auto finalize = [&](GValue& v) -> prad_status {
-    if (v.contrib.empty()) return PRAD_OK;
+  //    arrive in reverse consumer order and are summed in consumer (registration) order, an
+  //    upstream gradient handed in by the caller first.
+  auto finalize = [&](GValue& v, const void* external) -> prad_status {
+    if (v.contrib.empty() && !external) return PRAD_OK;
+    std::reverse(v.contrib.begin(), v.contrib.end());
+    if (external) v.contrib.insert(v.contrib.begin(), const_cast<void*>(external));
     if (v.contrib.size() == 1) {
       v.grad = v.contrib[0];
     } else {
-      std::reverse(v.contrib.begin(), v.contrib.end());
       if (!v.sum_buf) G_TRY(g_alloc(g, (size_t)v.rows * v.cols, &v.sum_buf));
       G_TRY(prad_segmented_sum(g->ctx, g->dt, v.contrib.data(), (int)v.contrib.size(), v.sum_buf,
                                (int64_t)v.rows * v.cols));
@@ -370,20 +387,28 @@ prad_status prad_graph_backward(prad_graph* g, int start_value, const void* d_st
     if (v.grad_dst) G_TRY(prad_accumulate(g->ctx, g->dt, v.grad_dst, v.grad, (int64_t)v.rows * v.cols));
     return PRAD_OK;
   };
+  auto external_of = [&](int value) -> const void* {
+    if (!is_start[value]) return nullptr;
+    for (int i = 0; i < count; ++i)
+      if (start_values[i] == value) return d_starts[i];
+    return nullptr;
+  };
   for (int k = (int)g->nodes.size() - 1; k >= 0; --k) {
     if (!live[k]) continue;
     GNode& n = g->nodes[k];
     GValue& o = V[n.out];
-    G_TRY(finalize(o));
+    G_TRY(finalize(o, external_of(n.out)));
     PRAD_REQUIRE(o.grad, PRAD_ERR_INVALID, "prad_graph_backward: node %d is on the path but received no gradient", k);
     G_TRY(node_backward(g, n, o.grad));
   }
   // 3. leaves (inputs, weights): fan-in sum and `destination += gradient`
-  std::vector<char> produced(V.size(), 0);
-  for (GNode& n : g->nodes) produced[n.out] = 1;
   for (size_t i = 0; i < V.size(); ++i)
-    if (!produced[i] && (int)i != start_value) G_TRY(finalize(V[i]));
+    if (V[i].produced_by < 0 && (needed[i] || is_start[i])) G_TRY(finalize(V[i], external_of((int)i)));
   return PRAD_OK;
+}
+
+prad_status prad_graph_backward(prad_graph* g, int start_value, const void* d_start) {
+  return prad_graph_backward_multi(g, &start_value, &d_start, 1);
 }
 
 }  // extern "C"

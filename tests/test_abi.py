@@ -53,3 +53,20 @@ def test_package_never_imports_the_oracle():
                 src = open(os.path.join(dirpath, f)).read()
                 assert "import oracle" not in src and "from oracle" not in src, f
                 assert "prad_oracle" not in src, f
+
+
+def test_managed_binding_file_is_current_and_complete():
+    """integration/PradCuda.cs is generated from the header: it must be up to date and carry one
+    [DllImport] for every exported function, and every enum value of the header."""
+    import importlib.util
+    path = os.path.join(ROOT, "integration", "make_bindings.py")
+    spec = importlib.util.spec_from_file_location("make_bindings", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    on_disk = open(os.path.join(ROOT, "integration", "PradCuda.cs")).read()
+    assert mod.generate() == on_disk, "run python integration/make_bindings.py"
+    for name in _declared():
+        assert re.search(r"extern\s+\w+\s+%s\(" % name, on_disk), name
+    assert on_disk.count("[DllImport(") == len(_declared())
+    for value in ("AmplifiedSigmoid = 6", "ErrTimeout = 8", "Div = 19"):
+        assert value in on_disk
