@@ -127,6 +127,11 @@ typedef struct {
   char name[64];
 } prad_device_info_t;
 prad_status prad_device_info(prad_ctx* ctx, prad_device_info_t* out);
+/* Arithmetic rate of one pipe of this device, measured now with a register-resident kernel (eight
+ * independent chains per thread, every SM full, best of three): pipe 0 = FP64 fused multiply-add,
+ * 1 = FP64 tensor-core MMA (mma.sync m8n8k4), 2 = FP32 fused multiply-add; in TFLOP/s.  It is the
+ * denominator for the SIMT and DMMA GEMM kernels (takes a few milliseconds). */
+prad_status prad_measure_pipe_rate(prad_ctx* ctx, int pipe, double* out_tflops);
 /* CUDA-event timing of caller-chosen regions of the context's stream (the reference has no timers;
  * its only trace is Debug.WriteLine inside AdamOptimizer, src/RMAD/AdamOptimizer.cs:215-217).
  * prad_timing_begin(label) ... prad_timing_end() bracket whatever is enqueued in between; brackets do

@@ -1,8 +1,10 @@
 """Per-kernel micro-benchmarks of libprad_cuda (CUDA-event timing on the context's stream).
 
-    python -m parallelreverseautodiff_b200.microbench                 # every HBM-bound kernel
-    python -m parallelreverseautodiff_b200.microbench --only gelu     # names containing "gelu"
-    python -m parallelreverseautodiff_b200.microbench --gemm          # GEMM variants at the C5 layer shape
+    python microbench.py                 # every HBM-bound kernel
+    python microbench.py --only gelu     # names containing "gelu"
+    python microbench.py --gemm          # float GEMM variants at the C5 layer shape
+    python microbench.py --packed        # packing kernels and products of packed operands (C5 layer shape)
+    python microbench.py --f64           # double GEMM variants and the FP64 FMA rate of the device
 
 HBM kernels are reported as algorithmic bytes / time against the measured copy bandwidth in
 MEASURED_PEAKS.json (6546 GB/s if that file is absent), GEMMs as 2*M*N*K / time.  Operands are
@@ -13,14 +15,19 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import sys
 
 import numpy as np
 
-from . import engine as E
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from parallelreverseautodiff_b200 import engine as E  # noqa: E402
 
 
 def _peak_gbs() -> float:
-    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
             return float(json.load(f).get("hbm_gbs", 6546.2))
@@ -55,6 +62,7 @@ def hbm_kernels(eng, only=None, rows=65536, cols=4096):
     x, dy, out, out2 = (eng.zeros((rows, cols), f) for _ in range(4))
     eng.upload(np.random.default_rng(0).standard_normal((min(rows, 4096), cols), dtype=f), out=x.view((min(rows, 4096), cols)))
     db = eng.empty((1, cols), f)
+    idx = eng.upload(np.random.default_rng(1).integers(0, 50000, (rows, 1)).astype(f))
     srows = n // 49
     S, dS, oS = x.view((srows, 49)), dy.view((srows, 49)), out.view((srows, 49))
     lrows = n // 96
@@ -73,6 +81,8 @@ def hbm_kernels(eng, only=None, rows=65536, cols=4096):
         ("bias_colsum", n * 4, lambda: eng.add_broadcast_backward(x, dbias=db)),
         ("accumulate", 3 * n * 4, lambda: eng.accumulate(out, x)),
         ("segmented_sum_3", 4 * n * 4, lambda: eng.segmented_sum([x, dy, out2], out=out)),
+        ("segmented_sum_2", 3 * n * 4, lambda: eng.segmented_sum([x, dy], out=out)),
+        ("embedding_scatter_ordered", 2 * n * 4 + rows * 4, lambda: eng.embedding_backward(idx, x, 50000)),
         ("softmax_backward_49", 3 * srows * 49 * 4, lambda: eng.softmax_backward(S, dS, out=oS)),
         ("layernorm_backward_96", 3 * lrows * 96 * 4, lambda: eng.layernorm_backward(Lx, mu, sd, dL, out=oL)),
         ("adam", 7 * npar * 4, lambda: eng.adam(P[0], P[1], P[2], P[3], 1e-3, .9, .999, 1e-8, 1.0)),
@@ -113,10 +123,81 @@ def gemm_variants(eng, rows=16384, width=4096, modes=("simt_fma", "tf32x3", "tf3
     eng.set_option("gemm_f32", "auto")
 
 
+def packed_operands(eng, rows=16384, width=4096, block_cols=0):
+    """Packing kernels (HBM-bound: bytes read + written / time) and the three products of one layer on
+    packed operands (2 * M * N * K / time, kernel only)."""
+    f = np.float32
+    peak = _peak_gbs()
+    t = _Timer(eng)
+    n = rows * width
+    z, dy, out = (eng.zeros((rows, width), f) for _ in range(3))
+    h = np.random.default_rng(0).standard_normal((min(rows, 4096), width), dtype=f)
+    for r0 in range(0, rows, h.shape[0]):
+        eng.upload(h, out=z.view(h.shape, r0 * width))
+        eng.upload(h * f(1e-3), out=dy.view(h.shape, r0 * width))
+    W = eng.upload(np.random.default_rng(1).standard_normal((width, width), dtype=f) * f(0.02))
+    both = E.PACK_ROWS | E.PACK_COLS
+    PA = eng.packed(rows, width, both, 0, block_cols)
+    PD = eng.packed(rows, width, both, 0, block_cols)
+    PR = eng.packed(rows, width, E.PACK_ROWS)
+    PC = eng.packed(rows, width, E.PACK_COLS)
+    PW = eng.packed(width, width, both, PD.blocks()[0], PA.blocks()[0])
+    piece = 4          # two FP16 pieces per element and form
+    cases = [
+        ("pack by rows", n * (4 + piece), lambda: PR.pack(z)),
+        ("pack by columns", n * (4 + piece), lambda: PC.pack(z)),
+        ("pack both forms", n * (4 + 2 * piece), lambda: PA.pack(z)),
+        ("gelu forward -> both forms", n * (4 + 2 * piece), lambda: PA.act_forward(E.ACT_GELU, z, None)),
+        ("gelu backward -> both forms", n * (8 + 2 * piece), lambda: PD.act_backward(E.ACT_GELU, z, dy, None)),
+        ("gelu backward -> both forms + fp32", n * (12 + 2 * piece), lambda: PD.act_backward(E.ACT_GELU, z, dy, out)),
+        ("pack weights both forms", width * width * (4 + 2 * piece), lambda: PW.pack(W)),
+    ]
+    print(f"blocks: activations by rows {PA.blocks()[0]}, by columns {PA.blocks()[1]}")
+    for name, nbytes, fn in cases:
+        ms = t(fn)
+        gbs = nbytes / ms / 1e6
+        print(f"{name:38s} {ms:8.3f} ms {gbs:8.0f} GB/s  {gbs / peak:5.2f} of measured copy peak", flush=True)
+    PA.act_forward(E.ACT_GELU, z, None)
+    PD.act_backward(E.ACT_GELU, z, dy, None)
+    PW.pack(W)
+    dW = eng.empty((width, width), f)
+    fl = 2.0 * rows * width * width
+    for name, fn in (("dA = dZ W^T", lambda: eng.gemm_packed(PD, E.PACK_ROWS, PW, E.PACK_ROWS, out)),
+                     ("dW = A^T dZ", lambda: eng.gemm_packed(PA, E.PACK_COLS, PD, E.PACK_COLS, dW)),
+                     ("Z = A W", lambda: eng.gemm_packed(PA, E.PACK_ROWS, PW, E.PACK_COLS, out))):
+        ms = t(fn, iters=5, warm=2)
+        print(f"packed {name:14s} {ms:8.3f} ms {fl / ms / 1e9:7.1f} TFLOP/s", flush=True)
+
+
+def f64_variants(eng, n=4096):
+    """Double-precision GEMM variants at n^3 and the device's FP64 multiply-add rate (a register-resident
+    chain of independent FMAs per thread, every SM full), the denominator for the FP64 kernels."""
+    t = _Timer(eng)
+    d = np.float64
+    A = eng.upload(np.random.default_rng(0).standard_normal((n, n)))
+    B = eng.upload(np.random.default_rng(1).standard_normal((n, n)))
+    Cm = eng.empty((n, n), d)
+    fl = 2.0 * n ** 3
+    peak = eng.pipe_rate(0)
+    mma = eng.pipe_rate(1)
+    print(f"FP64 FMA rate (register-resident chains): {peak:.1f} TFLOP/s; FP64 MMA (m8n8k4): {mma:.1f} TFLOP/s; "
+          f"FP32 FMA: {eng.pipe_rate(2):.1f} TFLOP/s", flush=True)
+    peak = max(peak, mma)
+    for mode in ("simt", "simt_fma", "dmma"):
+        eng.set_option("gemm_f64", mode)
+        for name, ta, tb in (("NN", False, False), ("NT", False, True), ("TN", True, False)):
+            ms = t(lambda: eng.gemm(A, B, Cm, transA=ta, transB=tb), iters=5, warm=2)
+            print(f"{mode:9s} {name} {ms:8.3f} ms {fl / ms / 1e9:7.1f} TFLOP/s  {fl / ms / 1e9 / peak:5.2f} of the faster FP64 pipe", flush=True)
+    eng.set_option("gemm_f64", "auto")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default=None)
     ap.add_argument("--gemm", action="store_true")
+    ap.add_argument("--packed", action="store_true")
+    ap.add_argument("--f64", action="store_true")
+    ap.add_argument("--block-cols", type=int, default=0, help="--packed: block length of the by-columns forms (0, 128, 256)")
     ap.add_argument("--rows", type=int, default=None)
     ap.add_argument("--opt", action="append", default=[], metavar="KEY=VALUE", help="prad_set_option before running")
     ap.add_argument("--modes", default="simt_fma,tf32x3,tf32b16,bf16x3,fp16x3")
@@ -124,7 +205,11 @@ def main():
     with E.Engine(0) as eng:
         for kv in args.opt:
             eng.set_option(*kv.split("=", 1))
-        if args.gemm:
+        if args.packed:
+            packed_operands(eng, rows=args.rows or 16384, block_cols=args.block_cols)
+        elif args.f64:
+            f64_variants(eng, n=args.rows or 4096)
+        elif args.gemm:
             gemm_variants(eng, rows=args.rows or 16384, modes=tuple(args.modes.split(",")))
         else:
             hbm_kernels(eng, only=args.only, rows=args.rows or 65536)

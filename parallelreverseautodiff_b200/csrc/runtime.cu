@@ -82,11 +82,97 @@ static Guid guid_of(const void* p) {
   return g;
 }
 
+// ---- pipe-rate probes: register-resident arithmetic, no memory traffic; every thread keeps eight
+// independent dependency chains so that the pipe's latency is covered
+__global__ void __launch_bounds__(256)
+probe_fp64_fma_kernel(double* __restrict__ out, int iters, double seed) {
+  double acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = seed + (double)(threadIdx.x + j) * 1e-9;
+  const double b = 0.99999999, c = 1e-9;
+  for (int i = 0; i < iters; ++i) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = fma(acc[j], b, c);
+  }
+  double s = 0.0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s += acc[j];
+  out[(size_t)blockIdx.x * blockDim.x + threadIdx.x] = s;
+}
+__global__ void __launch_bounds__(256)
+probe_fp32_fma_kernel(float* __restrict__ out, int iters, float seed) {
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = seed + (float)(threadIdx.x + j) * 1e-6f;
+  const float b = 0.999999f, c = 1e-6f;
+  for (int i = 0; i < iters; ++i) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = fmaf(acc[j], b, c);
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s += acc[j];
+  out[(size_t)blockIdx.x * blockDim.x + threadIdx.x] = s;
+}
+// mma.sync m8n8k4 f64: 8 x 8 x 4 x 2 = 512 flop per warp instruction, four independent accumulators
+__global__ void __launch_bounds__(256)
+probe_fp64_mma_kernel(double* __restrict__ out, int iters, double seed) {
+  double c[4][2];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { c[j][0] = seed; c[j][1] = -seed; }
+  const double a = 1.0 + (double)(threadIdx.x & 31) * 1e-9, b = 0.5;
+  for (int i = 0; i < iters; ++i) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0, %1}, {%2}, {%3}, {%0, %1};"
+                   : "+d"(c[j][0]), "+d"(c[j][1]) : "d"(a), "d"(b));
+  }
+  double s = 0.0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) s += c[j][0] + c[j][1];
+  out[(size_t)blockIdx.x * blockDim.x + threadIdx.x] = s;
+}
+
 }  // namespace prad
 
 using namespace prad;
 
 extern "C" {
+
+// ---------------------------------------------------------------- pipe rates
+prad_status prad_measure_pipe_rate(prad_ctx* ctx, int pipe, double* out_tflops) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_NOT_CAPTURING(ctx, "prad_measure_pipe_rate");
+  PRAD_REQUIRE(out_tflops && pipe >= 0 && pipe <= 2, PRAD_ERR_INVALID,
+               "prad_measure_pipe_rate: pipe is 0 (FP64 FMA), 1 (FP64 MMA) or 2 (FP32 FMA)");
+  const int blocks = ctx->sm_count * 8, threads = 256, iters = 1 << 14;
+  prad_status s = ensure_stage(ctx, (size_t)blocks * threads * sizeof(double));
+  if (s) return s;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  PRAD_CUDA(cudaEventCreate(&e0));
+  cudaError_t err = cudaEventCreate(&e1);
+  if (err != cudaSuccess) { cudaEventDestroy(e0); set_error("prad_measure_pipe_rate: %s", cudaGetErrorString(err)); return PRAD_ERR_CUDA; }
+  double best_ms = 1e30;
+  for (int rep = 0; rep < 4; ++rep) {   // the first repetition warms the clocks up
+    cudaEventRecord(e0, ctx->stream);
+    if (pipe == 0) probe_fp64_fma_kernel<<<blocks, threads, 0, ctx->stream>>>((double*)ctx->stage, iters, 1.0 + rep);
+    else if (pipe == 1) probe_fp64_mma_kernel<<<blocks, threads, 0, ctx->stream>>>((double*)ctx->stage, iters, 1.0 + rep);
+    else probe_fp32_fma_kernel<<<blocks, threads, 0, ctx->stream>>>((float*)ctx->stage, iters, 1.0f + rep);
+    ctx->launches++;
+    cudaEventRecord(e1, ctx->stream);
+    err = cudaEventSynchronize(e1);
+    float ms = 0.f;
+    if (err == cudaSuccess) err = cudaEventElapsedTime(&ms, e0, e1);
+    if (err != cudaSuccess) break;
+    if (rep > 0 && ms < best_ms) best_ms = ms;
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (err != cudaSuccess) { (void)cudaGetLastError(); set_error("prad_measure_pipe_rate: %s", cudaGetErrorString(err)); return PRAD_ERR_CUDA; }
+  const double per_thread = pipe == 1 ? 4.0 * 512.0 / 32.0 : 8.0 * 2.0;   // flop per thread and iteration
+  *out_tflops = per_thread * iters * (double)blocks * threads / (best_ms * 1e-3) / 1e12;
+  return PRAD_OK;
+}
 
 // ---------------------------------------------------------------- intermediate slots
 prad_status prad_slot_store(prad_ctx* ctx, const void* guid_16_bytes, const void* const* ptrs_host,

@@ -870,6 +870,12 @@ class Engine:
         check(self.lib.prad_device_info(self.ctx, C.byref(info)))
         return {k: (getattr(info, k).decode() if k == "name" else getattr(info, k)) for k, _ in info._fields_}
 
+    def pipe_rate(self, pipe: int) -> float:
+        """TFLOP/s of a pipe measured now: 0 FP64 FMA, 1 FP64 MMA, 2 FP32 FMA (prad_measure_pipe_rate)."""
+        out = C.c_double()
+        check(self.lib.prad_measure_pipe_rate(self.ctx, pipe, C.byref(out)))
+        return out.value
+
     def timing_begin(self, label: str) -> None:
         check(self.lib.prad_timing_begin(self.ctx, label.encode()))
 

@@ -113,3 +113,8 @@ def test_timing_brackets(engine):
     assert rows[0][1] > 0 and rows[0][2] >= 1 and rows[1][2] == 0
     assert rows[0][1] > rows[1][1]
     assert engine.get_timings() == []
+
+
+def test_pipe_rates_are_plausible(engine):
+    fma64, mma64, fma32 = engine.pipe_rate(0), engine.pipe_rate(1), engine.pipe_rate(2)
+    assert 5 < fma64 < 200 and 5 < mma64 < 400 and 20 < fma32 < 400
