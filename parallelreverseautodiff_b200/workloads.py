@@ -58,6 +58,8 @@ class C1Runner:
     """MatMul -> LeakyReLU(0.01) node, PRAD double: dPre, dA, dB."""
     name, dtype, samples = "C1 MatMul->LeakyReLU node 512x784x256 (double)", "f64", 512
     flops = 4.0 * 512 * 784 * 256
+    # algorithmic bytes of one step: A, B, dOut, saved pre-activation read; dPre, dA, dB written
+    bytes = 8.0 * (2 * 512 * 784 + 2 * 784 * 256 + 3 * 512 * 256)
 
     def __init__(self, eng, inp):
         self.eng = eng
@@ -76,6 +78,9 @@ class C2Runner:
     """MLP 784-512-512-10, PRADLite float, batch 256: backward + clip + Adam."""
     name, dtype, samples = "C2 MLP 784-512-512-10 batch 256 (float) + clip + Adam", "f32", 256
     flops = 4.0 * 256 * (784 * 512 + 512 * 512 + 512 * 10)
+    # per layer: A, W, dZ read, dA, dW written, three activation-backward streams; then 11 streams of
+    # 4 bytes per parameter for clip + Adam + clear
+    bytes = 4.0 * sum(2 * 256 * k + 2 * k * n + 4 * 256 * n for k, n in ((784, 512), (512, 512), (512, 10))) + 44.0 * 669706
 
     def __init__(self, eng, inp, clip_mode=E.CLIP_REFERENCE):
         net = FeedForwardNetwork(eng, np.float32, inp["sizes"], hidden_act=E.ACT_LEAKY_RELU, softmax_output=True,
@@ -96,6 +101,10 @@ class C3Runner:
     """Single-layer LSTM 128 -> 256, 64 steps, batch 32, PRAD double: full BPTT."""
     name, dtype, samples = "C3 LSTM in 128 hidden 256 T 64 batch 32 (double), BPTT", "f64", 32
     flops = 64 * 4.0 * 32 * 1024 * (128 + 256)
+    # per time step: the gate tensors (about twenty streams of 32 x 256 doubles) and the 32 x (128 + 256)
+    # inputs of the gate products; once per step of the optimiser: the 394 240 weights read and their
+    # gradients written
+    bytes = 64 * 8.0 * (20 * 32 * 256 + 2 * 32 * (128 + 256)) + 2 * 8.0 * 4 * (256 * 128 + 256 * 256 + 256)
 
     def __init__(self, eng, inp):
         T, B, n_in = inp["x"].shape
@@ -116,6 +125,10 @@ class C4Runner:
         self.samples = inp["images"]
         self.name = f"C4 Swin block dim 96, 3 heads, 7x7 windows, {inp['images']} images (float)"
         self.flops = 96.3e9 * inp["images"] / 64.0
+        # tokens x (LayerNorm backward 2 x 3 x 96, GELU backward 3 x 384, product operands and results of the
+        # five projections read and written once, attention scores 3 x 3 x 49 per token and head set) x 4 bytes
+        t = inp["images"] * 3136
+        self.bytes = 4.0 * t * (6 * 96 + 3 * 384 + 2 * (96 + 288) + 2 * (96 + 96) + 2 * (96 + 384) + 2 * (384 + 96) + 9 * 49 * 3)
         self.blk = SwinBlock(eng, np.float32, inp["d"], inp["heads"], inp["ws"], inp["hidden"] // inp["d"])
         self.blk.set_parameters(inp["p"])
         self.d_out = eng.upload(inp["d_out"])
