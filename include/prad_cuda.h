@@ -340,6 +340,21 @@ prad_status prad_hadamard_forward(prad_ctx* ctx, prad_dtype dt, const void* a, c
                                   void* y, int64_t n);
 prad_status prad_hadamard_backward(prad_ctx* ctx, prad_dtype dt, const void* a, const void* b,
                                    const void* dy, void* da, void* db, int64_t n);
+/* The Backward of one LSTM cell (one time step) as ONE kernel: the step's loss gradient
+ * (MeanSquaredErrorLossOperation.Backward, loss_scale = 2 / (rows_total * cols), target may be NULL), the
+ * fan-in sum at h_t in list order (GradientUtils.AccumulateGradients, src/RMAD/GradientUtils.cs:22-42; the
+ * loss gradient first, then the n_contrib <= 8 further gradients w.r.t. h_t), HadamardProductOperation
+ * .Backward for h = o (.) tanh(c), TanhOperation.Backward, the fan-in sum at c_t (+ dc_next, may be NULL),
+ * HadamardProductOperation.Backward for i (.) g and f (.) c_prev, and the four gate derivatives (Sigmoid for
+ * i, f, o; Tanh for g; both read their outputs).  Host arrays: gates_ifgo_host = { i, f, g, o } outputs,
+ * dpre_ifgo_host = the four gradients w.r.t. the gate pre-activations.  c_prev == NULL (first time step:
+ * c_{-1} = 0) gives dpre_f = 0 and needs dc_prev == NULL; otherwise dc_prev receives dc_t (.) f_t, the next
+ * call's dc_next.  Every element follows the rounding sequence of the separate operations, so the
+ * results are bit-identical to calling them one by one; n = elements per tensor. */
+prad_status prad_lstm_cell_backward(prad_ctx* ctx, prad_dtype dt, int64_t n, const void* h, const void* target,
+                                    double loss_scale, const void* const* dh_contrib_host, int n_contrib,
+                                    const void* dc_next, const void* const* gates_ifgo_host, const void* tanh_c,
+                                    const void* c_prev, void* const* dpre_ifgo_host, void* dc_prev);
 /* MatrixAddOperation.cs:29-68 / MatrixAddThreeOperation.cs:30-67 (c may be NULL).  Their
  * Backward returns copies of dOut; prad_copy (or simply aliasing dOut) provides that. */
 prad_status prad_add_forward(prad_ctx* ctx, prad_dtype dt, const void* a, const void* b,

@@ -65,6 +65,7 @@ SIGNATURES = {
     "prad_act_backward": [vp, i32, i32, vp, vp, vp, i64, f64],
     "prad_hadamard_forward": [vp, i32, vp, vp, vp, i64],
     "prad_hadamard_backward": [vp, i32, vp, vp, vp, vp, vp, i64],
+    "prad_lstm_cell_backward": [vp, i32, i64, vp, vp, f64, pvp, i32, vp, pvp, vp, vp, pvp, vp],
     "prad_add_forward": [vp, i32, vp, vp, vp, vp, i64],
     "prad_add_broadcast_forward": [vp, i32, vp, vp, vp, i32, i32],
     "prad_add_broadcast_backward": [vp, i32, vp, vp, i32, i32, i32],

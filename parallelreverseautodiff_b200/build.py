@@ -23,7 +23,7 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
           "-Xcompiler", "-fno-strict-aliasing"]
 # files whose kernels must not contract a*b+c into an FMA
-NO_FMAD = {"elementwise.cu", "rowops.cu", "loss_embedding.cu", "optimizer.cu", "matmul.cu", "tensor_ops.cu", "pack_fp16.cu"}
+NO_FMAD = {"elementwise.cu", "rowops.cu", "loss_embedding.cu", "optimizer.cu", "matmul.cu", "tensor_ops.cu", "pack_fp16.cu", "lstm_cell.cu"}
 
 
 def nvcc() -> str:

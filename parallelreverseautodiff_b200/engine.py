@@ -470,6 +470,17 @@ class Engine:
                                               da.ptr, db.ptr, a.size))
         return da, db
 
+    def lstm_cell_backward(self, h, target, loss_scale, dh_contrib, dc_next, gates_ifgo, tanh_c, c_prev, dpre_ifgo,
+                           dc_prev):
+        """One time step of BPTT in one launch (prad_lstm_cell_backward)."""
+        n = tanh_c.size
+        contrib = (C.c_void_p * max(1, len(dh_contrib)))(*[m.ptr for m in dh_contrib])
+        gates = (C.c_void_p * 4)(*[m.ptr for m in gates_ifgo])
+        dpre = (C.c_void_p * 4)(*[m.ptr for m in dpre_ifgo])
+        check(self.lib.prad_lstm_cell_backward(self.ctx, dtype_code(tanh_c.dtype), n, self._p(h), self._p(target),
+                                               loss_scale, contrib, len(dh_contrib), self._p(dc_next), gates, tanh_c.ptr,
+                                               self._p(c_prev), dpre, self._p(dc_prev)))
+
     def add_forward(self, a, b, c=None, out=None):
         out = out or self.empty(a.shape, a.dtype)
         check(self.lib.prad_add_forward(self.ctx, dtype_code(a.dtype), a.ptr, b.ptr, self._p(c),

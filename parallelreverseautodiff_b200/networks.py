@@ -449,8 +449,9 @@ class LstmNetwork:
 
     GATES = ("i", "f", "g", "o")
 
-    def __init__(self, eng: E.Engine, dtype, n_in: int, n_hidden: int, steps: int, batch: int):
+    def __init__(self, eng: E.Engine, dtype, n_in: int, n_hidden: int, steps: int, batch: int, fused_cell: bool = True):
         self.eng, self.dtype = eng, np.dtype(dtype)
+        self.fused_cell = fused_cell      # one kernel per time step for the elementwise part of the backward
         self.n_in, self.n_h, self.T, self.B = n_in, n_hidden, steps, batch
         e, dt = eng, self.dtype
         z = lambda *s: e.zeros(s, dt)  # noqa: E731
@@ -535,6 +536,47 @@ class LstmNetwork:
         BPTT, then the time- and batch-reduced weight gradients."""
         e, T, B, nh = self.eng, self.T, self.B, self.n_h
         tmp = self._tmp
+        if not self.fused_cell:
+            self._backward_steps_by_operation()
+        else:
+            # one launch per time step for everything elementwise (prad_lstm_cell_backward), one strided-batched
+            # product for the four recurrent gradients; bit-identical to the operation-by-operation path
+            dh_rec, dc_next = [], None
+            g0 = self.GATES[0]
+            for t in range(T - 1, -1, -1):
+                st = lambda m: self._step(m, t)        # noqa: E731
+                dc_prev = tmp[15 + (t & 1)] if t > 0 else None
+                e.lstm_cell_backward(st(self.H), st(self.Y), 2.0 / nh, dh_rec, dc_next,
+                                     [st(self.gate[k]) for k in ("i", "f", "g", "o")], st(self.tanhC),
+                                     self._step(self.C, t - 1) if t > 0 else None,
+                                     [st(self.dpre[k]) for k in ("i", "f", "g", "o")], dc_prev)
+                dc_next = dc_prev
+                if t > 0:           # gradient w.r.t. h_{t-1}: one product per gate, summed by the next call
+                    e.gemm(st(self.dpre[g0]), self.U[g0], tmp[8], batch=len(self.GATES),
+                           strideA=T * B * nh, strideB=nh * nh, strideC=B * nh)
+                    dh_rec = [tmp[8 + k] for k in range(len(self.GATES))]
+        inv_b = 1.0 / B
+        first = True
+        g0, G, TB = self.GATES[0], len(self.GATES), T * B
+        # dW_g = (1/B) * dZ_all^T X_all ; dU_g = (1/B) * dZ_all^T Hprev_all : the four gates per launch
+        e.gemm(self.dpre[g0], self.X, self.dW[g0], transA=True, alpha=inv_b, batch=G, strideA=TB * nh, strideB=0,
+               strideC=nh * self.n_in)
+        e.gemm(self.dpre[g0], self.Hprev, self.dU[g0], transA=True, alpha=inv_b, batch=G, strideA=TB * nh,
+               strideB=0, strideC=nh * nh)
+        for g in self.GATES:
+            # db_g = (1/B) colsum
+            e.add_broadcast_backward(self.dpre[g], dbias=self.db[g])
+            e.scale(self.db[g], inv_b, out=self.db[g])
+            # dX_all = sum over gates of dZ_g W_g (left fold in gate order)
+            e.gemm(self.dpre[g], self.W[g], self.dX, beta=0.0 if first else 1.0)
+            first = False
+
+
+
+    def _backward_steps_by_operation(self):
+        """The time loop of the backward with one library call per managed operation."""
+        e, T, B, nh = self.eng, self.T, self.B, self.n_h
+        tmp = self._tmp
         dh_rec = None           # four buffers: dZ_g(t+1) * U_g
         dc_next = None          # dc_{t+1} (.) f_{t+1}
         for t in range(T - 1, -1, -1):
@@ -575,21 +617,6 @@ class LstmNetwork:
                 e.gemm(self._step(self.dpre[g0], t), self.U[g0], tmp[8], batch=len(self.GATES),
                        strideA=T * B * nh, strideB=nh * nh, strideC=B * nh)
                 dh_rec = [tmp[8 + k] for k in range(len(self.GATES))]
-        inv_b = 1.0 / B
-        first = True
-        g0, G, TB = self.GATES[0], len(self.GATES), T * B
-        # dW_g = (1/B) * dZ_all^T X_all ; dU_g = (1/B) * dZ_all^T Hprev_all : the four gates per launch
-        e.gemm(self.dpre[g0], self.X, self.dW[g0], transA=True, alpha=inv_b, batch=G, strideA=TB * nh, strideB=0,
-               strideC=nh * self.n_in)
-        e.gemm(self.dpre[g0], self.Hprev, self.dU[g0], transA=True, alpha=inv_b, batch=G, strideA=TB * nh,
-               strideB=0, strideC=nh * nh)
-        for g in self.GATES:
-            # db_g = (1/B) colsum
-            e.add_broadcast_backward(self.dpre[g], dbias=self.db[g])
-            e.scale(self.db[g], inv_b, out=self.db[g])
-            # dX_all = sum over gates of dZ_g W_g (left fold in gate order)
-            e.gemm(self.dpre[g], self.W[g], self.dX, beta=0.0 if first else 1.0)
-            first = False
 
 
 class SwinBlock:

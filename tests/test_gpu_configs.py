@@ -116,6 +116,34 @@ def test_c3_lstm_double_bptt(engine, shape):
     assert_close(net.dX.numpy().reshape(T, B, n_in), dX_ref, 10.0, "dX")
 
 
+def test_c3_fused_cell_backward_is_bit_identical_to_the_operation_chain(engine):
+    """prad_lstm_cell_backward (one launch per time step) against the same step as eleven library calls."""
+    T, B, n_in, nh = 7, 5, 12, 16
+    r = np.random.default_rng(1)
+    x = r.standard_normal((T, B, n_in))
+    y = r.standard_normal((T, B, nh))
+    G = ("i", "f", "g", "o")
+    W = {g: r.uniform(-1, 1, (nh, n_in)) * 0.4 for g in G}
+    U = {g: r.uniform(-1, 1, (nh, nh)) * 0.4 for g in G}
+    b = {g: r.standard_normal(nh) * 0.1 for g in G}
+    nets = []
+    for fused in (True, False):
+        net = LstmNetwork(engine, np.float64, n_in, nh, T, B, fused_cell=fused)
+        net.set_parameters(W, U, b)
+        net.forward(x, y)
+        n0 = engine.launch_count()
+        net.backward()
+        nets.append((net, engine.launch_count() - n0))
+    (a, la), (c, lc) = nets
+    assert la < lc / 3
+    for g in G:
+        np.testing.assert_array_equal(a.dW[g].numpy(), c.dW[g].numpy())
+        np.testing.assert_array_equal(a.dU[g].numpy(), c.dU[g].numpy())
+        np.testing.assert_array_equal(a.db[g].numpy(), c.db[g].numpy())
+        np.testing.assert_array_equal(a.dpre[g].numpy(), c.dpre[g].numpy())
+    np.testing.assert_array_equal(a.dX.numpy(), c.dX.numpy())
+
+
 # ------------------------------------------------------------------ C4
 @pytest.mark.parametrize("images", [1, 64])
 def test_c4_swin_block_float(engine, images):
