@@ -248,6 +248,11 @@ prad_status prad_act_forward_pack(prad_packed* p, prad_act act, const void* x, v
 /* dx = dy (.) act'(saved) packed; dx (dense FP32 copy) may be NULL; PRAD_ACT_NONE packs dy itself */
 prad_status prad_act_backward_pack(prad_packed* p, prad_act act, const void* saved, const void* dy, void* dx,
                                    double act_alpha);
+/* The last layer's step: dx = [2 / (rows_total * cols) * (output - target)] (.) act'(saved) packed -- the
+ * MeanSquaredErrorLossOperation.Backward (Loss/MeanSquaredErrorLossOperation.cs:65-84) and the output
+ * activation's Backward in one pass, the loss gradient never stored. */
+prad_status prad_mse_act_backward_pack(prad_packed* p, prad_act act, const void* saved, const void* output, const void* target,
+                                       int64_t rows_total, void* dx, double act_alpha);
 prad_status prad_gemm_packed(prad_ctx* ctx, const prad_packed* A, int form_a, const prad_packed* B, int form_b,
                              double alpha, double beta, void* C, int64_t ldc, const void* bias);
 

@@ -51,6 +51,7 @@ SIGNATURES = {
     "prad_pack": [vp, vp, i64],
     "prad_act_forward_pack": [vp, i32, vp, vp, f64],
     "prad_act_backward_pack": [vp, i32, vp, vp, vp, f64],
+    "prad_mse_act_backward_pack": [vp, i32, vp, vp, vp, i64, vp, f64],
     "prad_gemm_packed": [vp, vp, i32, vp, i32, f64, f64, vp, i64, vp],
     "prad_matmul_forward": [vp, i32, vp, vp, vp, i32, i32, i32, vp, vp, i32, f64],
     "prad_matmul_backward": [vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, f64, i32, vp, f64],

@@ -43,19 +43,31 @@ __device__ __forceinline__ void fetch4(const PackSource& s, bool vec, int64_t r,
   v[0] = v[1] = v[2] = v[3] = 0.f;
   if (r >= R || c >= C) return;
   const int64_t off = r * s.ld + c;
-  float a[4] = {0.f, 0.f, 0.f, 0.f}, d[4] = {0.f, 0.f, 0.f, 0.f};
+  float a[4] = {0.f, 0.f, 0.f, 0.f}, d[4] = {0.f, 0.f, 0.f, 0.f}, tg[4] = {0.f, 0.f, 0.f, 0.f};
   const bool full = vec && c + 4 <= C;
   if (full) {
     const float4 t = __ldcs(reinterpret_cast<const float4*>(s.x + off));
     a[0] = t.x; a[1] = t.y; a[2] = t.z; a[3] = t.w;
-    if (s.kind == 2) {
+    if (s.kind >= 2) {
       const float4 u = __ldcs(reinterpret_cast<const float4*>(s.dy + off));
       d[0] = u.x; d[1] = u.y; d[2] = u.z; d[3] = u.w;
+    }
+    if (s.kind == 3) {
+      const float4 u = __ldcs(reinterpret_cast<const float4*>(s.target + off));
+      tg[0] = u.x; tg[1] = u.y; tg[2] = u.z; tg[3] = u.w;
     }
   } else {
 #pragma unroll
     for (int q = 0; q < 4; ++q)
-      if (c + q < C) { a[q] = s.x[off + q]; if (s.kind == 2) d[q] = s.dy[off + q]; }
+      if (c + q < C) {
+        a[q] = s.x[off + q];
+        if (s.kind >= 2) d[q] = s.dy[off + q];
+        if (s.kind == 3) tg[q] = s.target[off + q];
+      }
+  }
+  if (s.kind == 3) {     // MeanSquaredErrorLossOperation.Backward: scale * (output - target)
+#pragma unroll
+    for (int q = 0; q < 4; ++q) d[q] = mul_rn(s.loss_scale, sub_rn(d[q], tg[q]));
   }
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
@@ -208,7 +220,7 @@ prad_status pack_fp16(prad_ctx* ctx, const PackSource& src, int R, int C, const 
   if (R <= 0 || C <= 0 || (!by_rows && !by_cols)) return PRAD_OK;
   PackedForm none;
   bool vec = (src.ld % 4 == 0) && (((uintptr_t)src.x & 15) == 0) && (!src.dy || ((uintptr_t)src.dy & 15) == 0) &&
-             (!src.out || ((uintptr_t)src.out & 15) == 0);
+             (!src.out || ((uintptr_t)src.out & 15) == 0) && (!src.target || ((uintptr_t)src.target & 15) == 0);
   if (by_rows) {
     PRAD_REQUIRE(by_rows->rows == R && by_rows->k == C && (by_rows->chunk == 128 || by_rows->chunk == 256), PRAD_ERR_SHAPE,
                  "operand packing: the by-rows form does not fit a %d x %d matrix", R, C);
@@ -371,6 +383,26 @@ prad_status prad_act_backward_pack(prad_packed* p, prad_act act, const void* sav
     src.dy = (const float*)dy;
     src.out = (float*)dx;
   }
+  src.ld = p->cols;
+  src.act = (int)act;
+  src.act_alpha = (float)act_alpha;
+  return pack_into(p, src);
+}
+
+prad_status prad_mse_act_backward_pack(prad_packed* p, prad_act act, const void* saved, const void* output, const void* target,
+                                       int64_t rows_total, void* dx, double act_alpha) {
+  PRAD_CHECK_PACKED(p, "prad_mse_act_backward_pack");
+  PRAD_CHECK_CTX(p->ctx);
+  PRAD_REQUIRE(output && target && rows_total >= 1 && act >= PRAD_ACT_NONE && act <= PRAD_ACT_AMPLIFIED_SIGMOID &&
+                   (saved || act == PRAD_ACT_NONE),
+               PRAD_ERR_INVALID, "prad_mse_act_backward_pack: null input, bad row count or unknown activation");
+  PackSource src;
+  src.kind = 3;
+  src.x = (const float*)(act == PRAD_ACT_NONE ? output : saved);   // any readable tensor when there is no activation
+  src.dy = (const float*)output;
+  src.target = (const float*)target;
+  src.loss_scale = 2.0f / (float)(rows_total * p->cols);
+  src.out = (float*)dx;
   src.ld = p->cols;
   src.act = (int)act;
   src.act_alpha = (float)act_alpha;

@@ -52,9 +52,11 @@ inline PackedForm packed_form_shape(int rows, int64_t k, int chunk) {
 
 // What the packing kernel reads: a plain matrix, or an activation applied on the fly.
 struct PackSource {
-  int kind = 0;                   // 0 plain x ; 1 y = act(x) ; 2 dx = dy * act'(saved)
+  int kind = 0;                   // 0 plain x ; 1 y = act(x) ; 2 dx = dy * act'(saved) ; 3 like 2 with dy = scale * (dy - target)
   const float* x = nullptr;       // plain: the matrix; forward: pre-activation; backward: saved tensor
-  const float* dy = nullptr;      // backward: upstream gradient
+  const float* dy = nullptr;      // backward: upstream gradient (kind 3: the network output)
+  const float* target = nullptr;  // kind 3: the loss target
+  float loss_scale = 0.f;         // kind 3: 2 / (rows_total * cols) of the mean squared error
   float* out = nullptr;           // optional FP32 copy of the computed values (y or dx), same pitch as x
   int64_t ld = 0;                 // pitch of x, dy and out in floats
   int act = 0;

@@ -118,6 +118,14 @@ class PackedOperand:
                                                      dx.ptr if dx is not None else None, alpha))
         return self
 
+    def mse_act_backward(self, act: int, saved, output: "DeviceMatrix", target: "DeviceMatrix", rows_total: int,
+                         dx: Optional["DeviceMatrix"] = None, alpha=0.0):
+        """MSE gradient times the output activation's derivative, packed (prad_mse_act_backward_pack)."""
+        check(self.engine.lib.prad_mse_act_backward_pack(self.handle, act, saved.ptr if saved is not None else None,
+                                                         output.ptr, target.ptr, rows_total,
+                                                         dx.ptr if dx is not None else None, alpha))
+        return self
+
     def free(self) -> None:
         if self.handle and self.engine is not None and self.engine.ctx:
             self.engine.lib.prad_packed_destroy(self.handle)

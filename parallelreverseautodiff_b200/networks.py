@@ -122,7 +122,7 @@ class FeedForwardNetwork:
 
     # ---------------------------------------------------------------- set-up
     def set_weights(self, weights: Sequence[np.ndarray], biases: Optional[Sequence[np.ndarray]] = None):
-        self._w_dirty = True
+        self._w_dirty = self._wc_dirty = True
         for l, w in enumerate(weights):
             self.eng.upload(np.ascontiguousarray(w, self.dtype), out=self.W[l])
         if biases is not None:
@@ -184,24 +184,30 @@ class FeedForwardNetwork:
         # lengths are those of the by-rows forms it meets
         blk_a = self.PA[0].blocks()[0]
         blk_d = next(iter(self.PD.values())).blocks()[0]
-        self.PW = [e.packed(self.sizes[l], self.sizes[l + 1], both, blk_d, blk_a) for l in range(L)]
-        self._w_dirty = True
+        # (two objects: the backward needs only the by-rows form, and packs it again after every optimiser step)
+        self.PWr = [e.packed(self.sizes[l], self.sizes[l + 1], E.PACK_ROWS, blk_d, 0) for l in range(L)]
+        self.PWc = [e.packed(self.sizes[l], self.sizes[l + 1], E.PACK_COLS, 0, blk_a) for l in range(L)]
+        self._w_dirty = self._wc_dirty = True
 
-    def _pack_weights(self) -> None:
-        if self._w_dirty:
+    def _pack_weights(self, forward: bool) -> None:
+        if forward and self._wc_dirty:
             for l in range(self.L):
-                self.PW[l].pack(self.W[l])
+                self.PWc[l].pack(self.W[l])
+            self._wc_dirty = False
+        if not forward and self._w_dirty:
+            for l in range(self.L):
+                self.PWr[l].pack(self.W[l])
             self._w_dirty = False
 
     def _forward_packed(self) -> E.DeviceMatrix:
         e, L = self.eng, self.L
         alpha = self.Parameters.LeakyReLUAlpha
-        self._pack_weights()
+        self._pack_weights(forward=True)
         self.PA[0].pack(self.A[0])
         for l in range(L):
             act = self.acts[l]
             pre = self.Z[l + 1] if self.Z[l + 1] is not None else self.A[l + 1]
-            e.gemm_packed(self.PA[l], E.PACK_ROWS, self.PW[l], E.PACK_COLS, pre,
+            e.gemm_packed(self.PA[l], E.PACK_ROWS, self.PWc[l], E.PACK_COLS, pre,
                           bias=self.b[l] if self.use_bias else None)
             if l + 1 < L:      # the activation writes the next layer's operand (and A_{l+1} in FP32 if kept)
                 self.PA[l + 1].act_forward(act, pre, self.A[l + 1], alpha)
@@ -209,8 +215,9 @@ class FeedForwardNetwork:
                 e.act_forward(act, pre, alpha, out=self.A[L])
         return self.A[L]
 
-    def _backward_packed(self, g: E.DeviceMatrix, probe, need_dx: bool) -> None:
-        """g = gradient of the loss with respect to A_L (FP32)."""
+    def _backward_packed(self, g: Optional[E.DeviceMatrix], probe, need_dx: bool, mse=None) -> None:
+        """g = gradient of the loss with respect to A_L (FP32), or mse = (output, target, rows_total) to have
+        the mean-squared-error gradient formed on the fly."""
         e, L, rows = self.eng, self.L, self.rows
         alpha = self.Parameters.LeakyReLUAlpha
         for l in range(L, 0, -1):
@@ -219,7 +226,11 @@ class FeedForwardNetwork:
             dz32 = None
             if self.use_bias:                        # the bias gradient sums the FP32 gradient's columns
                 dz32 = self.dZ[1].view((rows, self.sizes[l]))
-            pd.act_backward(act, self._saved(l) if act != E.ACT_NONE else None, g, dz32, alpha)
+            saved = self._saved(l) if act != E.ACT_NONE else None
+            if l == L and mse is not None:
+                pd.mse_act_backward(act, saved, mse[0], mse[1], mse[2], dz32, alpha)
+            else:
+                pd.act_backward(act, saved, g, dz32, alpha)
             if probe:
                 probe("gemm", True)
             e.gemm_packed(self.PA[l - 1], E.PACK_COLS, pd, E.PACK_COLS, self.dW[l - 1])
@@ -228,7 +239,7 @@ class FeedForwardNetwork:
             # the first weight-gradient product reads no weights: the previous step's weight broadcasts run
             # beside it; they are joined here, and only then are the (new) weights packed
             self._join_broadcasts()
-            self._pack_weights()
+            self._pack_weights(forward=False)
             if self.world > 1 and self.dp_overlap:
                 self._reduce_grad(l - 1)
             if self.use_bias:
@@ -239,7 +250,7 @@ class FeedForwardNetwork:
                 g = self.dZ[0].view((rows, self.sizes[l - 1]))
                 if probe:
                     probe("gemm", True)
-                e.gemm_packed(pd, E.PACK_ROWS, self.PW[l - 1], E.PACK_ROWS, g)
+                e.gemm_packed(pd, E.PACK_ROWS, self.PWr[l - 1], E.PACK_ROWS, g)
                 if probe:
                     probe("gemm", False)
         self.dX = g
@@ -307,6 +318,11 @@ class FeedForwardNetwork:
         alpha = self.Parameters.LeakyReLUAlpha
         cur = self.dZ[0].view((rows, self.sizes[L]))
         out = self.probs if self.softmax_output else self.A[L]
+        if self.packed and self.loss == "mse":
+            # the loss gradient is formed inside the pass that packs dZ_L (never stored)
+            self._backward_packed(None, probe, need_dx, mse=(out, t, rows_total))
+            self._finish_backward(probe)
+            return
         if self.loss == "mse":
             e.mse_backward(out, t, rows_total=rows_total, grad=cur)
         else:
@@ -371,7 +387,7 @@ class FeedForwardNetwork:
     # ---------------------------------------------------------------- clip + Adam
     def clip_and_optimize(self, zero_grad: bool = True):
         p = self.Parameters
-        self._w_dirty = True
+        self._w_dirty = self._wc_dirty = True
         own = self.owned
         pick = lambda xs: [xs[i] for i in own]
         if own:

@@ -99,6 +99,29 @@ def test_activation_written_in_packed_form(engine, act):
     np.testing.assert_array_equal(dWt2.numpy(), dWt.numpy())
 
 
+def test_loss_gradient_formed_inside_the_packing_pass(engine):
+    """prad_mse_act_backward_pack == prad_mse_backward followed by prad_act_backward_pack, bit for bit."""
+    r = rng(12)
+    m, k = 300, 260
+    z = r.standard_normal((m, k)).astype(f)
+    out = O.gelu_forward(z)
+    t = r.standard_normal((m, k)).astype(f)
+    zd, od, td = engine.upload(z), engine.upload(out), engine.upload(t)
+    both = E.PACK_ROWS | E.PACK_COLS
+    P1, P2 = engine.packed(m, k, both), engine.packed(m, k, both)
+    dx1, dx2 = engine.empty((m, k), f), engine.empty((m, k), f)
+    g = engine.mse_backward(od, td, rows_total=4 * m)
+    P1.act_backward(E.ACT_GELU, zd, g, dx1)
+    P2.mse_act_backward(E.ACT_GELU, zd, od, td, 4 * m, dx2)
+    np.testing.assert_array_equal(dx1.numpy(), dx2.numpy())
+    assert_close(dx2.numpy(), O.gelu_backward(z, O.mse_backward(out, t, rows_total=4 * m)), 1e-6, "mse + gelu backward packed")
+    W = engine.packed(k, 128, both, 128, 128).pack(engine.upload((r.standard_normal((k, 128)) * 0.1).astype(f)))
+    a, b = engine.empty((m, 128), f), engine.empty((m, 128), f)
+    engine.gemm_packed(P1, E.PACK_ROWS, W, E.PACK_COLS, a)
+    engine.gemm_packed(P2, E.PACK_ROWS, W, E.PACK_COLS, b)
+    np.testing.assert_array_equal(a.numpy(), b.numpy())
+
+
 def test_block_scales_follow_the_data_range(engine):
     """Rows and columns whose magnitudes differ by 30 decades between blocks keep their 22 bits: every
     block has its own scale."""
