@@ -132,6 +132,16 @@ prad_status prad_device_info(prad_ctx* ctx, prad_device_info_t* out);
  * 1 = FP64 tensor-core MMA (mma.sync m8n8k4), 2 = FP32 fused multiply-add; in TFLOP/s.  It is the
  * denominator for the SIMT and DMMA GEMM kernels (takes a few milliseconds). */
 prad_status prad_measure_pipe_rate(prad_ctx* ctx, int pipe, double* out_tflops);
+/* Self-test of the give-up path of the tensor-core kernels.  Every wait inside those kernels is bounded;
+ * when one runs out the kernel raises a flag, frees what it holds and returns, later tensor-core
+ * products and optimiser steps on the context become no-ops (weights, moments and gradients are left
+ * untouched), and the next prad_sync / prad_download* / prad_get_timings returns PRAD_ERR_TIMEOUT and
+ * clears the flag -- the counterpart of the visitor's wait with TimeoutInMinutes whose failure surfaces
+ * as a queued exception (src/RMAD/OperationNeuralNetworkVisitor.cs:27,79-90,264-270).  This call
+ * enqueues a one-CTA kernel that waits `polls` polls on a barrier nobody arrives on, i.e. it makes that
+ * path run without any fault or hang; results computed between it and the next prad_sync are invalid,
+ * as after a real give-up. */
+prad_status prad_selftest_bounded_wait(prad_ctx* ctx, int polls);
 /* CUDA-event timing of caller-chosen regions of the context's stream (the reference has no timers;
  * its only trace is Debug.WriteLine inside AdamOptimizer, src/RMAD/AdamOptimizer.cs:215-217).
  * prad_timing_begin(label) ... prad_timing_end() bracket whatever is enqueued in between; brackets do

@@ -142,6 +142,7 @@ SIGNATURES = {
     "prad_slot_drop": [vp, vp],
     "prad_slot_count": [vp, C.POINTER(C.c_int)],
     "prad_device_info": [vp, vp],
+    "prad_selftest_bounded_wait": [vp, i32],
     "prad_measure_pipe_rate": [vp, i32, C.POINTER(f64)],
     "prad_timing_begin": [vp, C.c_char_p],
     "prad_timing_end": [vp],

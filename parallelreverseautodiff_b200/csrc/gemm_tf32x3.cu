@@ -1416,6 +1416,34 @@ prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, do
   }
 }
 
+// ---- self-test of the give-up path ----------------------------------------------------------
+// One CTA initialises an mbarrier that nothing will ever arrive on and waits for it with the same
+// polling loop as the GEMM kernels, but with a caller-chosen limit of a few polls: the wait runs out,
+// the kernel raises the give-up flag (role 9) and returns normally.  Nothing faults and nothing
+// hangs; the host then sees PRAD_ERR_TIMEOUT at its next prad_sync, exactly as after a real give-up.
+namespace tc {
+__global__ void bounded_wait_probe_kernel(int* __restrict__ err_flag, uint32_t polls) {
+  __shared__ __align__(8) uint64_t bar;
+  const uint32_t b = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    mbar_init(b, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    bool done = false;
+    for (uint32_t spins = 0; spins < polls && !done; ++spins) done = mbar_try_wait(b, 0);
+    if (!done) atomicCAS(err_flag, 0, 9);
+  }
+}
+}  // namespace tc
+
+extern "C" prad_status prad_selftest_bounded_wait(prad_ctx* ctx, int polls) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(polls >= 1 && polls <= (1 << 20), PRAD_ERR_INVALID, "prad_selftest_bounded_wait: polls must be in [1, 2^20]");
+  tc::bounded_wait_probe_kernel<<<1, 32, 0, ctx->stream>>>(ctx->tc_err, (uint32_t)polls);
+  PRAD_LAUNCHED(ctx);
+  ctx->tc_pending_check = true;
+  return PRAD_OK;
+}
+
 // Reads the give-up flag of the most recent tensor-core GEMMs (called by prad_sync).
 prad_status gemm_tf32x3_check(prad_ctx* ctx) {
   if (!ctx->tc_pending_check || !ctx->tc_err) return PRAD_OK;
@@ -1426,7 +1454,7 @@ prad_status gemm_tf32x3_check(prad_ctx* ctx) {
   if (flag != 0) PRAD_CUDA(cudaMemsetAsync(ctx->tc_err, 0, 256, ctx->stream));   // flag and tile counters
   PRAD_REQUIRE(flag == 0, PRAD_ERR_TIMEOUT,
                "gemm (tensor core): a bounded wait ran out inside the kernel (role %d: 1 producer, 2 MMA, 3 epilogue, "
-               "4 accumulator hand-back, 5-7 tile queue); "
+               "4 accumulator hand-back, 5-7 tile queue, 9 self-test); "
                "the results of that product are invalid", flag);
   return PRAD_OK;
 }

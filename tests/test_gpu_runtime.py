@@ -118,3 +118,37 @@ def test_timing_brackets(engine):
 def test_pipe_rates_are_plausible(engine):
     fma64, mma64, fma32 = engine.pipe_rate(0), engine.pipe_rate(1), engine.pipe_rate(2)
     assert 5 < fma64 < 200 and 5 < mma64 < 400 and 20 < fma32 < 400
+
+
+def test_a_wait_that_runs_out_is_reported_and_leaves_the_context_usable(engine):
+    """The give-up path without a fault or a hang: a one-CTA kernel waits a few polls on a barrier nobody
+    arrives on.  Until the host has seen the error, the optimiser must not touch weights or moments
+    (the gradients on the stream may be garbage); afterwards everything works again."""
+    r = rng(6)
+    f = np.float32
+    w0 = r.standard_normal((64, 48)).astype(f)
+    g0 = r.standard_normal((64, 48)).astype(f)
+    w, g = engine.upload(w0), engine.upload(g0)
+    m, v = engine.zeros((64, 48), f), engine.zeros((64, 48), f)
+    engine.sync()
+    _lib.check(engine.lib.prad_selftest_bounded_wait(engine.ctx, 16))
+    engine.clip_adam([w], [g], [m], [v], E.CLIP_REFERENCE, 4.0, 1e-8, 1e-3, 0.9, 0.999, 1e-8, 1.0, zero_grad=True)
+    with pytest.raises(_lib.PradError) as e:
+        engine.sync()
+    assert e.value.status == _lib.ERR_TIMEOUT and "self-test" in str(e.value)
+    np.testing.assert_array_equal(w.numpy(), w0)          # the step was skipped ...
+    np.testing.assert_array_equal(g.numpy(), g0)          # ... gradients not cleared, moments still zero
+    assert not m.numpy().any() and not v.numpy().any()
+    engine.sync()                                         # the flag was cleared by the failed sync
+    engine.clip_adam([w], [g], [m], [v], E.CLIP_REFERENCE, 4.0, 1e-8, 1e-3, 0.9, 0.999, 1e-8, 1.0, zero_grad=True)
+    assert np.abs(w.numpy() - w0).max() > 0 and not g.numpy().any()
+    # and a tensor-core product afterwards is correct
+    a = r.standard_normal((256, 512)).astype(f)
+    b = r.standard_normal((512, 256)).astype(f)
+    engine.set_option("gemm_f32", "fp16x3")
+    try:
+        got = engine.matmul_forward(engine.upload(a), engine.upload(b)).numpy()
+    finally:
+        engine.set_option("gemm_f32", "auto")
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    assert np.abs(got - ref).max() <= 1e-5 * (np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)).max()
