@@ -75,12 +75,15 @@ def build(force: bool = False, verbose: bool = False, ptxas_v: bool = False) -> 
         with cf.ThreadPoolExecutor(max_workers=min(8, len(todo))) as ex:
             list(ex.map(lambda s: _compile(s, verbose, ptxas_v), todo))
     if todo or not os.path.exists(LIB):
-        cmd = [nvcc(), *ARCH, "-shared", "-o", LIB, *objs, "-lcudart", "-ldl"]
+        # link beside the target and rename: whoever loads or copies the library never sees half of it
+        tmp = LIB + ".linking"
+        cmd = [nvcc(), *ARCH, "-shared", "-o", tmp, *objs, "-lcudart", "-ldl"]
         if verbose:
             print(" ".join(cmd), flush=True)
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+        os.replace(tmp, LIB)
     return LIB
 
 

@@ -628,7 +628,7 @@ struct TileSched {
 };
 
 template <int PMODE>
-__global__ void __maxnreg__(192)      // 320 threads: 10 warps x 6144 registers (allocated per warp in units of 512) fit the 64 K file
+__global__ void __launch_bounds__(THREADS, 1)   // 10 warps, at most 3 per scheduler: 3 x 32 x 168 registers fit its 16 K file
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_xb,
                                const __grid_constant__ CUtensorMap map_a_lb, const __grid_constant__ CUtensorMap map_b_hi,
                                const __grid_constant__ CUtensorMap map_b_xb, const __grid_constant__ CUtensorMap map_b_lb,

@@ -11,6 +11,9 @@ namespace prad {
 
 struct GValue {
   int rows = 0, cols = 0;
+  int depth = 1;               // DeepMatrix: `depth` consecutive rows x cols slices
+  int64_t count() const { return (int64_t)depth * rows * cols; }
+  int64_t slice() const { return (int64_t)rows * cols; }
   void* data = nullptr;        // caller-owned or graph-owned
   bool owned = false;
   void* grad_dst = nullptr;    // weight-style destination (+=)
@@ -27,7 +30,7 @@ struct GNode {
   int out = -1;
   double scalar = 0.0;
   // per-node state kept between forward and backward
-  void* aux0 = nullptr;        // LayerNorm mean
+  void* aux0 = nullptr;        // LayerNorm mean; batch product with a shared first operand: per-slice products
   void* aux1 = nullptr;        // LayerNorm sigma
   std::vector<void*> in_grad;  // gradient buffers of the inputs (graph-owned, reused)
 };
@@ -115,6 +118,14 @@ prad_status prad_graph_add_value(prad_graph* g, int rows, int cols, void* data, 
   g->values.push_back(v);
   *out_value = (int)g->values.size() - 1;
   return PRAD_OK;
+}
+
+prad_status prad_graph_add_deep_value(prad_graph* g, int depth, int rows, int cols, void* data, int* out_value) {
+  PRAD_CHECK_GRAPH(g);
+  PRAD_REQUIRE(depth > 0, PRAD_ERR_SHAPE, "prad_graph_add_deep_value: depth must be positive");
+  prad_status s = prad_graph_add_value(g, rows, cols, data, out_value);
+  if (s == PRAD_OK) g->values[*out_value].depth = depth;
+  return s;
 }
 
 prad_status prad_graph_set_gradient_destination(prad_graph* g, int value, void* grad_matrix) {
