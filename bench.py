@@ -62,6 +62,8 @@ def parse():
                     help="Adam learning rate (1e-3, the reference default, makes this 8-layer GELU net "
                          "diverge within ten steps on random targets; the arithmetic per step is the same)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--pack-block-cols", type=int, default=0, choices=[0, 128, 256],
+                    help="block length of the by-columns packed forms (0 = the library's default)")
     return ap.parse_args()
 
 
@@ -304,7 +306,8 @@ def run_native(args, rank, world, local_rank):
     net = FeedForwardNetwork(eng, np.float32, sizes, hidden_act=E.ACT_GELU, output_act=E.ACT_GELU,
                              loss="mse", use_bias=False, clip_mode=clip, rank=rank, world=world,
                              dp_overlap=args.dp_mode != "end",
-                             dp_sharded=args.dp_mode == "sharded" and clip != E.CLIP_GLOBAL_NORM)
+                             dp_sharded=args.dp_mode == "sharded" and clip != E.CLIP_GLOBAL_NORM,
+                             pack_block_cols=args.pack_block_cols)
     net.Parameters.LearningRate = args.lr
     wr = np.random.default_rng(42)  # identical weights on every rank
     net.set_weights([(wr.standard_normal((args.width, args.width), dtype=np.float32)

@@ -84,9 +84,9 @@ const char* prad_version(void);
  *               Error of an output element: 2^-22 * sum_k |a_ik b_kj| like the TF32 pair, plus at most
  *               sqrt(K) * 2^-39 * (largest |a| times largest |b| of a block): an element more than ~8
  *               decades below the largest of its block keeps fewer than 22 bits.  Block scales are
- *               limited to 2^+-62: blocks whose largest magnitude is below 2^-48 lose bits and values
- *               above 2^77 overflow.  Irrelevant for activations and gradients; a caller whose
- *               products pair a huge factor with a tiny one at the same k should use "tf32b16";
+ *               limited to 2^-126 .. 2^90: blocks whose largest magnitude is below 2^-112 lose bits and
+ *               values above 2^106 (8e31) overflow.  Irrelevant for activations and gradients; a caller
+ *               whose products pair a huge factor with a tiny one inside one block should use "tf32b16";
  *    tf32b16  : tcgen05 kernel, one TF32 product + two BF16 correction products;
  *    tf32x3   : tcgen05 kernel, three TF32 products per term (a_hi*b_hi + a_lo*b_hi + a_hi*b_lo);
  *    bf16x3   : tcgen05 kernel, six BF16 products of three-piece operands;
@@ -95,8 +95,8 @@ const char* prad_version(void);
  *  "tc_auto" = "fp16x3" | "tf32b16" | "tf32x3" | "bf16x3": the scheme "auto" uses for large products;
  *  "tc_chunk_k" = "128" | "256" | "512" | "1024": k summed inside the tensor core before the partial
  *    sum is added in FP32 with round-to-nearest (the tensor core truncates; default 256: rms error
- *    9e-7 of the result for any K; 512 is 4 % faster at 1.8e-6); for fp16x3 it is also the block
- *    length of the scales and only 128 and 256 apply (larger values mean 256);
+ *    9e-7 of the result for any K; 512 is 4 % faster at 1.8e-6); for fp16x3 the block length of the
+ *    scales is the chunk: 128 unless this option is set to 256 or more (then 256);
  *  "tc_split_k" = "on" | "off"; "tc_persistent" = "on" | "off" (tf32b16 on the one-tile-per-CTA kernel);
  *  "tc_reserve_sms" = n: SMs the persistent GEMM leaves idle (default 0);
  *  "tc_panel_n" = n: column tiles per panel of the persistent GEMM's tile walk (0 = automatic: two
@@ -238,9 +238,10 @@ prad_status prad_gemm(prad_ctx* ctx, prad_dtype dt, int transA, int transB, int 
  * An object belongs to one R x C matrix shape and holds either or both orientations:
  *   PRAD_PACK_ROWS  the matrix as an operand with R rows and k = C  (A in A*B; dZ in dZ*W^T; W in dZ*W^T)
  *   PRAD_PACK_COLS  its transpose: C rows and k = R                 (A and dZ in A^T*dZ; W in A*W)
- * block_* = 0 picks the block length: the "tc_chunk_k" option (256) for a single form; 128 by rows and
- * the option's value by columns when both forms are requested (one pass then writes both; two passes
- * when both are 256).  Two operands of a product need equal k and equal block length.
+ * block_* = 0 picks the block length: 128, unless the "tc_chunk_k" option was set to 256 or more (then
+ * 256).  With 128 one pass writes both forms out of a 128 x 128 tile; a 256 x 256 tile does not fit in
+ * shared memory, so an object with two 256-long forms is packed in two passes.  Two operands of a
+ * product need equal k and equal block length.
  * prad_gemm_packed: C (M x N, pitch ldc) = alpha * opA * opB^T + beta * C (+ bias row), opA M x k, opB N x k.
  * Accuracy is that of "fp16x3" with the range condition applying per block instead of per row. */
 typedef struct prad_packed prad_packed;

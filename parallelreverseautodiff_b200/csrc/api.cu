@@ -164,6 +164,7 @@ prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value) {
     PRAD_REQUIRE(n == 128 || n == 256 || n == 512 || n == 1024, PRAD_ERR_INVALID,
                  "prad_set_option: tc_chunk_k must be 128, 256, 512 or 1024, got '%s'", value);
     ctx->tc_chunk_k = n;
+    ctx->tc_chunk_k_set = true;
     return PRAD_OK;
   }
   if (!strcmp(key, "tc_reserve_sms")) {

@@ -49,6 +49,7 @@ struct prad_ctx {
   bool tc_split_k = true;  // option "tc_split_k": cut k across CTAs when the tile count wastes SMs
   int tc_panel_n = 0;      // option "tc_panel_n": column tiles per panel of the persistent GEMM's tile walk (0 = automatic)
   int tc_chunk_k = 256;    // option "tc_chunk_k": k per accumulation chunk of the persistent GEMM
+  bool tc_chunk_k_set = false;   // the option was given (packed FP16 operands default to 128-long blocks otherwise)
   int tc_reserve_sms = 0;  // option "tc_reserve_sms": SMs the persistent GEMM leaves free (for a collective's kernels)
   bool tc_persistent = true;  // option "tc_persistent": TF32+BF16 products run on the persistent kernel
   int tc_auto_mode = 3;  // split scheme "auto" picks: 0 = 3xTF32, 1 = TF32 + BF16 corrections, 2 = BF16 x 6, 3 = FP16 x 3

@@ -214,10 +214,10 @@ struct Epi {
   // 2^(row_exp[i] + col_exp[j]) first; null when the operands are unscaled
   const int* row_exp;
   const int* col_exp;
-  // packed FP16 operands: block exponents, blk_a[c * blk_lda + i] = e << 23 for block c of row i of A
-  // (likewise B); the partial sum of block c is multiplied by 2^(e_a + e_b) as it is added
-  const int* blk_a = nullptr;
-  const int* blk_b = nullptr;
+  // packed FP16 operands: block scales, blk_a[c * blk_lda + i] = 2^e for block c of row i of A (likewise
+  // B); the partial sum of block c is multiplied by both as it is added
+  const float* blk_a = nullptr;
+  const float* blk_b = nullptr;
   int blk_lda = 0, blk_ldb = 0;
 };
 
@@ -849,12 +849,12 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
       const int row_blk = min(m0 + sub * 32 + lane, M - 1);     // rows beyond M are never stored
       for (int ch = 0; ch < num_chunks; ++ch, ++gc) {
         const uint32_t buf = gc & 1;
-        // this thread's row exponent and the 128 column exponents of the block, fetched before the wait
-        int ea = 0;
-        const int4* ebp = nullptr;
+        // this thread's row scale and the 128 column scales of the block, fetched before the wait
+        float sa = 0.f;
+        const float4* sbp = nullptr;
         if (PMODE == 3) {
-          ea = epi.blk_a[(int64_t)(chunk0 + ch) * epi.blk_lda + row_blk] + 0x3f800000;   // + the bias of a float's exponent
-          ebp = reinterpret_cast<const int4*>(epi.blk_b + (int64_t)(chunk0 + ch) * epi.blk_ldb + n0 + half * 128);
+          sa = epi.blk_a[(int64_t)(chunk0 + ch) * epi.blk_lda + row_blk];
+          sbp = reinterpret_cast<const float4*>(epi.blk_b + (int64_t)(chunk0 + ch) * epi.blk_ldb + n0 + half * 128);
         }
         ok = __all_sync(0xffffffffu, mbar_wait(acc_full(buf), (gc >> 1) & 1, err_flag, 3));
         if (!ok) break;
@@ -869,13 +869,13 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
             tmem_ld_wait();
 #pragma unroll
             for (int q = 0; q < 4; ++q) {     // the same address in every lane: one broadcast load each
-              const int4 t = __ldg(ebp + g * 4 + q);
+              const float4 t = __ldg(sbp + g * 4 + q);
               float* acc = &sum[g >> 1][(g & 1) * 16 + 4 * q];
-              // sum += partial * 2^(e_a + e_b), rounded once
-              acc[0] = __fmaf_rn(__uint_as_float(v[4 * q]), __int_as_float(ea + t.x), acc[0]);
-              acc[1] = __fmaf_rn(__uint_as_float(v[4 * q + 1]), __int_as_float(ea + t.y), acc[1]);
-              acc[2] = __fmaf_rn(__uint_as_float(v[4 * q + 2]), __int_as_float(ea + t.z), acc[2]);
-              acc[3] = __fmaf_rn(__uint_as_float(v[4 * q + 3]), __int_as_float(ea + t.w), acc[3]);
+              // sum += (partial * 2^e_a) * 2^e_b: the first product is exact, the sum is rounded once
+              acc[0] = __fmaf_rn(__fmul_rn(__uint_as_float(v[4 * q]), sa), t.x, acc[0]);
+              acc[1] = __fmaf_rn(__fmul_rn(__uint_as_float(v[4 * q + 1]), sa), t.y, acc[1]);
+              acc[2] = __fmaf_rn(__fmul_rn(__uint_as_float(v[4 * q + 2]), sa), t.z, acc[2]);
+              acc[3] = __fmaf_rn(__fmul_rn(__uint_as_float(v[4 * q + 3]), sa), t.w, acc[3]);
             }
           }
         } else {
@@ -1343,7 +1343,7 @@ prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, do
                    : ctx->gemm_f32 == GemmF32::Fp16x3 ? 3 : ctx->tc_auto_mode;
   if (mode == 3) {
     // both operands are packed into scratch (pieces, then block exponents), each in one pass
-    const int chunk = ctx->tc_chunk_k == 128 ? 128 : 256;
+    const int chunk = (ctx->tc_chunk_k_set && ctx->tc_chunk_k >= 256) ? 256 : 128;   // 128: the packing kernel's fast tile
     PackedForm fa = packed_form_shape(M, K, chunk), fb = packed_form_shape(N, K, chunk);
     auto al = [](size_t x) { return (x + 255) & ~(size_t)255; };
     const size_t need = al(fa.h_bytes()) + al(fb.h_bytes()) + al(fa.blk_bytes()) + al(fb.blk_bytes());
@@ -1352,8 +1352,8 @@ prad_status gemm_tf32x3(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, do
     char* w = (char*)ctx->ws;
     fa.h = (__half*)w; w += al(fa.h_bytes());
     fb.h = (__half*)w; w += al(fb.h_bytes());
-    fa.blk = (int*)w; w += al(fa.blk_bytes());
-    fb.blk = (int*)w;
+    fa.blk = (float*)w; w += al(fa.blk_bytes());
+    fb.blk = (float*)w;
     // exponents of rows beyond the matrices are read by the last tiles: they must be valid (zero)
     PRAD_CUDA(cudaMemsetAsync(fa.blk, 0, al(fa.blk_bytes()) + al(fb.blk_bytes()), ctx->stream));
     PackSource sa, sb;

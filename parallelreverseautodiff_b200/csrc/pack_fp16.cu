@@ -30,7 +30,7 @@ __device__ __forceinline__ int shift_of(uint32_t absbits) {
   const int e = (int)((absbits >> 23) & 0xffu);
   if (e == 0 || e == 255) return 0;              // all zero / denormal, or Inf / NaN present: unscaled
   const int s = 14 - (e - 127);
-  return s > PACK_EXP_LIMIT ? PACK_EXP_LIMIT : (s < -PACK_EXP_LIMIT ? -PACK_EXP_LIMIT : s);
+  return s > PACK_SHIFT_MAX ? PACK_SHIFT_MAX : (s < PACK_SHIFT_MIN ? PACK_SHIFT_MIN : s);
 }
 __device__ __forceinline__ void pieces(float xs, __half& p0, __half& p1) {
   p0 = __float2half_rn(xs);
@@ -85,9 +85,151 @@ __device__ __forceinline__ void fetch4(const PackSource& s, bool vec, int64_t r,
   }
 }
 
+// ---------------------------------------------------------------- fast path: interior 128 x 128 tiles
+// The same two passes for tiles that lie completely inside the matrix, with 16-byte aligned operands and
+// 128-long blocks: no bounds tests, the operation fixed at compile time, conversions two values at a
+// time (cvt.rn.f16x2.f32).  OP: 0 plain; 1 / 2 / 3 forward GELU / LeakyReLU / any activation;
+// 4 / 5 / 6 backward likewise; 7 / 8 mean-squared-error gradient times the GELU / any derivative.
+__device__ __forceinline__ void pieces2(float x0, float x1, __half2& p0, __half2& p1) {
+  p0 = __floats2half2_rn(x0, x1);
+  const float2 b = __half22float2(p0);
+  p1 = __floats2half2_rn(x0 - b.x, x1 - b.y);      // the differences are exact in FP32
+}
+template <int OP>
+__device__ __forceinline__ float apply_op(const PackSource& s, float a, float d, float tg) {
+  if (OP == 0) return a;
+  if (OP == 1) return gelu_value<float>(a);
+  if (OP == 2) return a > 0.f ? a : mul_rn(s.act_alpha, a);
+  if (OP == 3) return act_value<float>((prad_act)s.act, a, s.act_alpha);
+  if (OP >= 7) d = mul_rn(s.loss_scale, sub_rn(d, tg));
+  if (OP == 4 || OP == 7) return mul_rn(d, gelu_derivative<float>(a));
+  if (OP == 5) return mul_rn(d, a > 0.f ? 1.f : s.act_alpha);
+  return mul_rn(d, act_derivative<float>((prad_act)s.act, a, s.act_alpha));
+}
+
+template <int OP, bool ROWS, bool COLS>
+__global__ void __launch_bounds__(256)
+pack_fast_kernel(PackSource src, PackedForm fr, PackedForm fc) {
+  constexpr int T = 128, STRIDE = T + 4, U = 4;
+  extern __shared__ float stash[];       // [T][STRIDE] when COLS
+  __shared__ unsigned colmax[T];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t r0 = (int64_t)blockIdx.y * T;
+  const int c0 = blockIdx.x * T, c = c0 + lane * 4;
+  if (COLS && threadIdx.x < T) colmax[threadIdx.x] = 0;
+  uint32_t cm[4] = {0, 0, 0, 0};
+  for (int it0 = 0; it0 < T / 8; it0 += U) {
+    float4 a[U], d[U], tg[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t off = (r0 + warp + 8 * (it0 + u)) * src.ld + c;
+      a[u] = __ldcs(reinterpret_cast<const float4*>(src.x + off));
+      if (OP >= 4) d[u] = __ldcs(reinterpret_cast<const float4*>(src.dy + off));
+      if (OP >= 7) tg[u] = __ldcs(reinterpret_cast<const float4*>(src.target + off));
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int tr = warp + 8 * (it0 + u);
+      const int64_t r = r0 + tr;
+      float v[4];
+      v[0] = apply_op<OP>(src, a[u].x, OP >= 4 ? d[u].x : 0.f, OP >= 7 ? tg[u].x : 0.f);
+      v[1] = apply_op<OP>(src, a[u].y, OP >= 4 ? d[u].y : 0.f, OP >= 7 ? tg[u].y : 0.f);
+      v[2] = apply_op<OP>(src, a[u].z, OP >= 4 ? d[u].z : 0.f, OP >= 7 ? tg[u].z : 0.f);
+      v[3] = apply_op<OP>(src, a[u].w, OP >= 4 ? d[u].w : 0.f, OP >= 7 ? tg[u].w : 0.f);
+      if (OP != 0 && src.out) __stcs(reinterpret_cast<float4*>(src.out + r * src.ld + c), make_float4(v[0], v[1], v[2], v[3]));
+      uint32_t m = 0;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t b = absbits(v[q]);
+        m = max(m, b);
+        if (COLS) cm[q] = max(cm[q], b);
+      }
+      if (COLS) *reinterpret_cast<float4*>(&stash[tr * STRIDE + lane * 4]) = make_float4(v[0], v[1], v[2], v[3]);
+      if (ROWS) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+        const int sh = shift_of(m);
+        const float scale = pow2f(sh);
+        if (lane == 0) fr.blk[(int64_t)blockIdx.x * fr.rows_ld + r] = pow2f(-sh);
+        __half2 p0[2], p1[2];
+        pieces2(v[0] * scale, v[1] * scale, p0[0], p1[0]);
+        pieces2(v[2] * scale, v[3] * scale, p0[1], p1[1]);
+        __half* dst = fr.h + r * 2 * fr.kp + (int64_t)(c >> 5) * 64 + (c & 31);
+        *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(p0);
+        *reinterpret_cast<uint2*>(dst + 32) = *reinterpret_cast<const uint2*>(p1);
+      }
+    }
+  }
+  if (!COLS) return;
+  __syncthreads();
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+    if (cm[q] != 0) atomicMax(&colmax[lane * 4 + q], cm[q]);
+  __syncthreads();
+  // 4 column groups x 4 k-groups of 32: two items per warp; a lane owns one column and 32 consecutive k
+  for (int item = warp; item < 16; item += 8) {
+    const int cg = item & 3, kg = item >> 2;
+    const int col = c0 + cg * 32 + lane;
+    const int sh = shift_of(colmax[cg * 32 + lane]);
+    const float scale = pow2f(sh);
+    if (kg == 0) fc.blk[(int64_t)blockIdx.y * fc.rows_ld + col] = pow2f(-sh);
+    __align__(16) __half2 p0[16];
+    __align__(16) __half2 p1[16];
+    const float* col_base = stash + (kg * 32) * STRIDE + cg * 32 + lane;
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      pieces2(col_base[(2 * j) * STRIDE] * scale, col_base[(2 * j + 1) * STRIDE] * scale, p0[j], p1[j]);
+    __half* dst = fc.h + (int64_t)col * 2 * fc.kp + ((r0 + kg * 32) >> 5) * 64;     // one 128-byte line: h0 | h1
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<const uint4*>(p0)[j];
+      reinterpret_cast<uint4*>(dst + 32)[j] = reinterpret_cast<const uint4*>(p1)[j];
+    }
+  }
+}
+
+template <int OP, bool ROWS, bool COLS>
+static prad_status launch_fast(prad_ctx* ctx, const PackSource& src, int tiles_r, int tiles_c, const PackedForm& fr,
+                               const PackedForm& fc) {
+  const int smem = COLS ? 128 * 132 * (int)sizeof(float) : 0;
+  if (COLS) {
+    static std::atomic<uint64_t> done{0};
+    const uint64_t bit = 1ull << (ctx->device & 63);
+    if (!(done.load(std::memory_order_acquire) & bit)) {
+      const cudaError_t e = cudaFuncSetAttribute(pack_fast_kernel<OP, ROWS, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        set_error("operand packing: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        return PRAD_ERR_CUDA;
+      }
+      done.fetch_or(bit, std::memory_order_release);
+    }
+  }
+  pack_fast_kernel<OP, ROWS, COLS><<<dim3((unsigned)tiles_c, (unsigned)tiles_r), 256, smem, ctx->stream>>>(src, fr, fc);
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
+template <int OP>
+static prad_status launch_fast_forms(prad_ctx* ctx, const PackSource& src, int tiles_r, int tiles_c, const PackedForm& fr,
+                                     const PackedForm& fc) {
+  if (fr.h && fc.h) return launch_fast<OP, true, true>(ctx, src, tiles_r, tiles_c, fr, fc);
+  if (fr.h) return launch_fast<OP, true, false>(ctx, src, tiles_r, tiles_c, fr, fc);
+  return launch_fast<OP, false, true>(ctx, src, tiles_r, tiles_c, fr, fc);
+}
+// which compile-time operation serves this source
+static int fast_op_of(const PackSource& s) {
+  if (s.kind == 0) return 0;
+  const bool gelu = s.act == PRAD_ACT_GELU, leaky = s.act == PRAD_ACT_LEAKY_RELU;
+  if (s.kind == 1) return gelu ? 1 : (leaky ? 2 : 3);
+  if (s.kind == 2) return gelu ? 4 : (leaky ? 5 : 6);
+  return gelu ? 7 : 8;
+}
+
 template <int TR, int TC>
 __global__ void __launch_bounds__(256)
-pack_tile_kernel(PackSource src, bool vec, int R, int C, PackedForm fr, PackedForm fc) {
+pack_tile_kernel(PackSource src, bool vec, int R, int C, PackedForm fr, PackedForm fc, int fast_tiles_r, int fast_tiles_c) {
+  // tiles inside the first fast_tiles_r x fast_tiles_c are written by pack_fast_kernel
+  if ((int)blockIdx.y < fast_tiles_r && (int)blockIdx.x < fast_tiles_c) return;
   constexpr int W = TC / 128;            // float4 per lane and tile row
   constexpr int STRIDE = TC + 4;         // stash pitch in floats (16-byte multiple; see pass 2)
   constexpr int U = 4;                   // tile rows a warp loads before it starts converting
@@ -137,7 +279,7 @@ pack_tile_kernel(PackSource src, bool vec, int R, int C, PackedForm fr, PackedFo
         for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
         const int sh = shift_of(m);
         const float scale = pow2f(sh);
-        if (lane == 0) fr.blk[(int64_t)(c0 / TC) * fr.rows_ld + r] = -sh * (1 << 23);
+        if (lane == 0) fr.blk[(int64_t)(c0 / TC) * fr.rows_ld + r] = pow2f(-sh);
         __half* drow = fr.h + r * 2 * fr.kp;
 #pragma unroll
         for (int w = 0; w < W; ++w) {
@@ -172,7 +314,7 @@ pack_tile_kernel(PackSource src, bool vec, int R, int C, PackedForm fr, PackedFo
     if (col >= C || kbase >= fc.kp) continue;
     const int sh = shift_of(colmax[cg * 32 + lane]);
     const float scale = pow2f(sh);
-    if (kg == 0) fc.blk[(int64_t)(r0 / TR) * fc.rows_ld + col] = -sh * (1 << 23);
+    if (kg == 0) fc.blk[(int64_t)(r0 / TR) * fc.rows_ld + col] = pow2f(-sh);
     __align__(16) __half p0[32];
     __align__(16) __half p1[32];
 #pragma unroll
@@ -188,7 +330,7 @@ pack_tile_kernel(PackSource src, bool vec, int R, int C, PackedForm fr, PackedFo
 
 template <int TR, int TC>
 static prad_status launch_pack(prad_ctx* ctx, const PackSource& src, bool vec, int R, int C, const PackedForm& fr,
-                               const PackedForm& fc) {
+                               const PackedForm& fc, int fast_tiles_r = 0, int fast_tiles_c = 0) {
   const int smem = fc.h ? TR * (TC + 4) * (int)sizeof(float) : 0;
   if (smem > 48 * 1024) {
     static std::atomic<uint64_t> done{0};
@@ -208,7 +350,8 @@ static prad_status launch_pack(prad_ctx* ctx, const PackSource& src, bool vec, i
   const int64_t cols_cover = fr.h ? (fr.kp > C ? fr.kp : C) : C;
   dim3 grid((unsigned)ceil_div(cols_cover, TC), (unsigned)ceil_div(rows_cover, TR));
   PRAD_REQUIRE(grid.y <= 65535, PRAD_ERR_UNSUPPORTED, "operand packing: too many row tiles (%u)", grid.y);
-  pack_tile_kernel<TR, TC><<<grid, 256, smem, ctx->stream>>>(src, vec, R, C, fr, fc);
+  if ((int)grid.y <= fast_tiles_r && (int)grid.x <= fast_tiles_c) return PRAD_OK;    // nothing left for this kernel
+  pack_tile_kernel<TR, TC><<<grid, 256, smem, ctx->stream>>>(src, vec, R, C, fr, fc, fast_tiles_r, fast_tiles_c);
   PRAD_LAUNCHED(ctx);
   return PRAD_OK;
 }
@@ -242,7 +385,26 @@ prad_status pack_fp16(prad_ctx* ctx, const PackSource& src, int R, int C, const 
   const PackedForm& fc = by_cols ? *by_cols : none;
   if (tr == 256) return pk::launch_pack<256, 128>(ctx, src, vec, R, C, fr, fc);
   if (tc == 256) return pk::launch_pack<128, 256>(ctx, src, vec, R, C, fr, fc);
-  return pk::launch_pack<128, 128>(ctx, src, vec, R, C, fr, fc);
+  // 128-long blocks: interior tiles through the specialised kernel, the ragged edges through the general one
+  int fr_t = 0, fc_t = 0;
+  if (vec && R >= 128 && C >= 128) {
+    fr_t = R / 128;
+    fc_t = C / 128;
+    prad_status s = PRAD_OK;
+    switch (pk::fast_op_of(src)) {
+      case 0: s = pk::launch_fast_forms<0>(ctx, src, fr_t, fc_t, fr, fc); break;
+      case 1: s = pk::launch_fast_forms<1>(ctx, src, fr_t, fc_t, fr, fc); break;
+      case 2: s = pk::launch_fast_forms<2>(ctx, src, fr_t, fc_t, fr, fc); break;
+      case 3: s = pk::launch_fast_forms<3>(ctx, src, fr_t, fc_t, fr, fc); break;
+      case 4: s = pk::launch_fast_forms<4>(ctx, src, fr_t, fc_t, fr, fc); break;
+      case 5: s = pk::launch_fast_forms<5>(ctx, src, fr_t, fc_t, fr, fc); break;
+      case 6: s = pk::launch_fast_forms<6>(ctx, src, fr_t, fc_t, fr, fc); break;
+      case 7: s = pk::launch_fast_forms<7>(ctx, src, fr_t, fc_t, fr, fc); break;
+      default: s = pk::launch_fast_forms<8>(ctx, src, fr_t, fc_t, fr, fc); break;
+    }
+    if (s) return s;
+  }
+  return pk::launch_pack<128, 128>(ctx, src, vec, R, C, fr, fc, fr_t, fc_t);
 }
 
 }  // namespace prad
@@ -278,7 +440,9 @@ static prad_status alloc_form(PackedForm& f) {
   }
   return PRAD_OK;
 }
-static int chunk_of(prad_ctx* ctx) { return ctx->tc_chunk_k == 128 ? 128 : 256; }
+// block length of a packed object unless the caller names one: 128 (one pass writes both forms from a
+// 128 x 128 tile, three CTAs per SM), or 256 when the option "tc_chunk_k" asks for at least that
+static int chunk_of(prad_ctx* ctx) { return ctx->tc_chunk_k >= 256 && ctx->tc_chunk_k_set ? 256 : 128; }
 }  // namespace prad
 
 extern "C" {
@@ -302,7 +466,7 @@ prad_status prad_packed_create(prad_ctx* ctx, int rows, int cols, int forms, int
   const int chunk = chunk_of(ctx);
   prad_status s = PRAD_OK;
   if (forms & PRAD_PACK_ROWS) {
-    const int b = block_rows_form ? block_rows_form : ((forms & PRAD_PACK_COLS) ? 128 : chunk);
+    const int b = block_rows_form ? block_rows_form : chunk;
     p->by_rows = packed_form_shape(rows, cols, b);
     s = alloc_form(p->by_rows);
   }

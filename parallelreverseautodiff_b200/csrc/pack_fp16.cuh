@@ -5,15 +5,18 @@
 // Every run of `chunk` consecutive k of a row (a block) is multiplied by its own power of two, chosen
 // so that the block's largest magnitude lands in [2^14, 2^15), and each value is then written as two
 // FP16 pieces h0 = fp16(x 2^s), h1 = fp16(x 2^s - h0): 22 significant bits.  The GEMM sums a block in
-// the tensor core and multiplies the block's partial sum by 2^-(s_a + s_b) when it adds it to the
-// running FP32 sum (one fused multiply-add), so the scales cost nothing and no pass over the matrix
-// is needed to find a whole-row maximum before the first element can be converted.
+// the tensor core and multiplies the block's partial sum by 2^-s_a and 2^-s_b when it adds it to the
+// running FP32 sum (one multiplication and one fused multiply-add), so the scales cost next to
+// nothing and no pass over the matrix is needed to find a whole-row maximum before the first element
+// can be converted.
 //
 // Memory layout of a row: pitch 2*kp halves (kp = k rounded up to 32); the pieces are interleaved per
 // 32-k group, [h0 of k 0..31 | h1 of k 0..31 | h0 of k 32..63 | ...], so that one 128-byte TMA row
 // brings both pieces of a group.  Padding (k..kp) is zero.
-// Block exponents: blk[c * rows_ld + r] = (-s) << 23 for block c of row r (an addend for the exponent
-// field of a float); rows r >= rows hold zero.
+// Block scales: blk[c * rows_ld + r] = 2^-s (a float) for block c of row r; rows r >= rows hold zero.
+// s is limited to [-90, 126]: values up to 2^104 keep all their bits (beyond 2^106 the pieces overflow),
+// blocks whose largest magnitude is below 2^-112 lose bits; 2^-s <= 2^90 keeps the product with a
+// block's partial sum (at most 2^37) finite.
 #pragma once
 
 #include <cuda_fp16.h>
@@ -24,11 +27,12 @@ namespace prad {
 
 constexpr int PACK_KPAD = 32;          // k granularity of the GEMM's operand tiles
 constexpr int PACK_ROWS_ALIGN = 256;   // rows_ld is a multiple of the widest output tile
-constexpr int PACK_EXP_LIMIT = 62;     // |block exponent| <= this, so that the sum of two stays a normal float
+constexpr int PACK_SHIFT_MIN = -90;    // limits of the power-of-two shift s of a block (see above)
+constexpr int PACK_SHIFT_MAX = 126;
 
 struct PackedForm {
   __half* h = nullptr;
-  int* blk = nullptr;
+  float* blk = nullptr;
   int rows = 0;       // operand rows
   int64_t k = 0;      // contraction length
   int64_t kp = 0;     // k rounded up to PACK_KPAD
@@ -36,7 +40,7 @@ struct PackedForm {
   int nchunk = 0;     // blocks per row
   int chunk = 0;      // k per block (a multiple of 32)
   size_t h_bytes() const { return (size_t)rows * 2 * kp * sizeof(__half); }
-  size_t blk_bytes() const { return (size_t)nchunk * rows_ld * sizeof(int); }
+  size_t blk_bytes() const { return (size_t)nchunk * rows_ld * sizeof(float); }
 };
 
 inline PackedForm packed_form_shape(int rows, int64_t k, int chunk) {
