@@ -344,7 +344,7 @@ def run_native(args, rank, world, local_rank):
         loss = net.train_step_host(x_host, t_host, rows_total=args.batch)
 
     # ---- (A) device-resident hot path: backward + clip + Adam ---------------------------
-    marks = {"gemm": [], "join": [], "opt": []}
+    marks = {"gemm": [], "join": [], "opt": [], "pack": []}
 
     def probe(kind, begin):
         ev = torch.cuda.Event(enable_timing=True)
@@ -378,7 +378,8 @@ def run_native(args, rank, world, local_rank):
     # with the communication stream at the end of the backward, clip + Adam; the rest is the loss
     # gradient, activation derivatives and whatever the stream waited for
     mine = {"rank": rank, "step_ms": ev0.elapsed_time(ev1) / args.steps, "gemm_ms": gemm_ms / args.steps,
-            "join_ms": bracket_ms("join") / args.steps, "optimizer_ms": bracket_ms("opt") / args.steps}
+            "pack_ms": bracket_ms("pack") / args.steps, "join_ms": bracket_ms("join") / args.steps,
+            "optimizer_ms": bracket_ms("opt") / args.steps}
     per_rank = [mine]
     if dist:
         per_rank = [None] * world

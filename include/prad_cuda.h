@@ -568,6 +568,15 @@ prad_status prad_graph_destroy(prad_graph* g);
 /* A value is a rows x cols matrix.  data != NULL: caller-owned device matrix (input, weight,
  * constant); data == NULL: produced by a node, owned by the graph. */
 prad_status prad_graph_add_value(prad_graph* g, int rows, int cols, void* data, int* out_value);
+/* A DeepMatrix value: `depth` consecutive rows x cols slices (the operand type of the Batch* operations,
+ * src/RMAD/BatchOperation.cs:11-58, one slice per sample).  A node whose output is deep runs the operation
+ * on every slice; an input is deep as well, or ONE Matrix shared by all slices where the managed Batch*
+ * class has such an overload -- the second operand of BatchMatrixAddOperation, the third of
+ * BatchMatrixAddThreeOperation, the bias of BatchMatrixAddBroadcastingOperation, either operand of
+ * Batch(Gpu)MatrixMultiplyOperation.  A shared Matrix must be a leaf; the gradient it receives is the
+ * visitor's combined result, the mean over the slices (CombineResults, src/RMAD/
+ * OperationNeuralNetworkVisitor.cs:449-478). */
+prad_status prad_graph_add_deep_value(prad_graph* g, int depth, int rows, int cols, void* data, int* out_value);
 /* Weight-style value: its gradient is ADDED into this caller-owned matrix on every backward. */
 prad_status prad_graph_set_gradient_destination(prad_graph* g, int value, void* grad_matrix);
 /* Nodes must be added in forward (topological) order; `out_value` must be graph-owned. */

@@ -119,6 +119,7 @@ SIGNATURES = {
     "prad_graph_create": [vp, i32, pvp],
     "prad_graph_destroy": [vp],
     "prad_graph_add_value": [vp, i32, i32, vp, C.POINTER(C.c_int)],
+    "prad_graph_add_deep_value": [vp, i32, i32, i32, vp, C.POINTER(C.c_int)],
     "prad_graph_set_gradient_destination": [vp, i32, vp],
     "prad_graph_add_node": [vp, i32, C.POINTER(C.c_int), i32, i32, f64, C.POINTER(C.c_int)],
     "prad_graph_forward": [vp],

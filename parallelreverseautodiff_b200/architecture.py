@@ -20,6 +20,11 @@ reference loads unmodified.
                Forward (NeuralNetwork.AutomaticForwardPropagate -> CopyResult)
     types      the JSON "type" is a class name of namespace ParallelReverseAutoDiff.RMAD
                (TypeRetrieved :1114-1117); Gpu* / Cuda* matrix products are the same node here
+    batches    Batch* operations (src/RMAD/BatchOperation.cs:11-58) work on DeepMatrix values, one slice per
+               sample: register such a matrix with a 3-D shape (depth, rows, cols).  A Matrix given where a
+               Batch* operation has a (DeepMatrix, Matrix) overload is shared by the slices, and its
+               gradient destination receives the mean over the slices (OperationNeuralNetworkVisitor
+               .CombineResults :449-478)
 """
 from __future__ import annotations
 
@@ -58,10 +63,19 @@ class OperationRef:
     result_to: Optional[str] = None
 
 
-# JSON type name -> node code.  The three spellings of the matrix product are one node.
+# JSON type name -> node code.  The three spellings of the matrix product are one node, and every
+# operation has its Batch* twin (the same node on DeepMatrix values).
+def _canonical(type_name: str) -> str:
+    name = type_name[5:] if type_name.startswith("Batch") else type_name
+    return {"GpuMatrixMultiplyOperation": "MatrixMultiplyOperation",
+            "CudaMatrixMultiplyOperation": "MatrixMultiplyOperation"}.get(name, name)
+
+
 TYPE_CODES = dict(_NODE_CODES)
-TYPE_CODES["GpuMatrixMultiplyOperation"] = TYPE_CODES["MatrixMultiplyOperation"]
-TYPE_CODES["CudaMatrixMultiplyOperation"] = TYPE_CODES["MatrixMultiplyOperation"]
+for _name in ("GpuMatrixMultiplyOperation", "CudaMatrixMultiplyOperation"):
+    TYPE_CODES[_name] = TYPE_CODES["MatrixMultiplyOperation"]
+for _name in list(TYPE_CODES):
+    TYPE_CODES["Batch" + _name] = TYPE_CODES[_name]
 
 _ARITY = {"MatrixMultiplyOperation": 2, "MatrixAddOperation": 2, "MatrixAddThreeOperation": 3,
           "MatrixAddBroadcastingOperation": 2, "HadamardProductOperation": 2, "MatrixMultiplyScalarOperation": 2}
@@ -140,10 +154,14 @@ class ArchitectureGraph:
     def _leaf(self, m: E.DeviceMatrix, grad: Optional[E.DeviceMatrix]):
         """A caller-owned matrix as a graph value.  Every USE gets its own value, because a gradient
         destination belongs to (operation, input position), not to the matrix."""
-        if len(m.shape) != 2:
-            raise ArchitectureError("graph values are matrices")
+        if len(m.shape) not in (2, 3):
+            raise ArchitectureError("graph values are matrices (rows, cols) or deep matrices (depth, rows, cols)")
         v = C.c_int()
-        check(self.eng.lib.prad_graph_add_value(self.h, m.shape[0], m.shape[1], C.c_void_p(m.ptr), C.byref(v)))
+        if len(m.shape) == 3:
+            check(self.eng.lib.prad_graph_add_deep_value(self.h, m.shape[0], m.shape[1], m.shape[2], C.c_void_p(m.ptr),
+                                                         C.byref(v)))
+        else:
+            check(self.eng.lib.prad_graph_add_value(self.h, m.shape[0], m.shape[1], C.c_void_p(m.ptr), C.byref(v)))
         self._keep.append(m)
         if grad is not None:
             if tuple(grad.shape) != tuple(m.shape):
@@ -158,8 +176,7 @@ class ArchitectureGraph:
             raise ArchitectureError(f"operation id '{info['id'] + str(li)}' occurs twice")
         if type_name not in TYPE_CODES:
             raise ArchitectureError(f"operation type '{type_name}' (operation '{info['id']}') is not available as a device node")
-        canonical = {"GpuMatrixMultiplyOperation": "MatrixMultiplyOperation",
-                     "CudaMatrixMultiplyOperation": "MatrixMultiplyOperation"}.get(type_name, type_name)
+        canonical = _canonical(type_name)
         inputs = list(info["inputs"])
         arity = _ARITY.get(canonical, 1)
         if len(inputs) != arity:
@@ -213,9 +230,10 @@ class ArchitectureGraph:
                 scalar = float(self._scalars[key](li))
                 continue
             raise ArchitectureError(f"Input name {key} not found in value map")
-        a = shapes[0]
+        depth = max((s[0] for s in shapes if len(s) == 3), default=0)     # 0: plain matrices
+        a = shapes[0][-2:]
         if canonical == "MatrixMultiplyOperation":
-            out_shape = (a[0], shapes[1][1])
+            out_shape = (a[0], shapes[1][-1])
         elif canonical == "MatrixTransposeOperation":
             out_shape = (a[1], a[0])
         else:
@@ -223,7 +241,11 @@ class ArchitectureGraph:
         if canonical == "LeakyReLUOperation":
             scalar = self.leaky_relu_alpha
         out = C.c_int()
-        check(self.eng.lib.prad_graph_add_value(self.h, out_shape[0], out_shape[1], None, C.byref(out)))
+        if depth:
+            check(self.eng.lib.prad_graph_add_deep_value(self.h, depth, out_shape[0], out_shape[1], None, C.byref(out)))
+            out_shape = (depth,) + tuple(out_shape)
+        else:
+            check(self.eng.lib.prad_graph_add_value(self.h, out_shape[0], out_shape[1], None, C.byref(out)))
         arr = (C.c_int * len(values))(*values)
         check(self.eng.lib.prad_graph_add_node(self.h, TYPE_CODES[type_name], arr, len(values), out.value, scalar, None))
         ref = OperationRef(info["id"] + str(li), info["id"], type_name, li, out.value, out_shape, inputs, dests,

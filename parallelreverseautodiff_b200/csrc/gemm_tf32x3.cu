@@ -1227,8 +1227,8 @@ static prad_status launch_fp16x3(prad_ctx* ctx, const PackedForm& a, const Packe
                (long long)a.kp, (long long)b.kp, a.chunk, b.chunk);
   CUtensorMap ma, mb;
   // interleaved pieces: a row is 2 kp halves, a k-group of 32 is one 128-byte box row (h0 | h1)
-  const bool ok = make_map(&ma, a.h, M, (int)(2 * kp), 2 * kp, BM, 2 * p1::BK, 2, true) &&
-                  make_map(&mb, b.h, N, (int)(2 * kp), 2 * kp, BN, 2 * p1::BK, 2, true);
+  const bool ok = make_map(&ma, a.h, M, (int)(2 * kp), a.pitch, BM, 2 * p1::BK, 2, true) &&
+                  make_map(&mb, b.h, N, (int)(2 * kp), b.pitch, BN, 2 * p1::BK, 2, true);
   PRAD_REQUIRE(ok, PRAD_ERR_CUDA, "gemm (tensor core): cuTensorMapEncodeTiled failed (M %d N %d K %lld)", M, N, (long long)kp);
   static std::atomic<uint64_t> p_done{0};
   const cudaError_t p_err = reserve_smem(gemm_persistent_kernel<3>, p1::SMEM_BYTES, ctx->device, p_done);

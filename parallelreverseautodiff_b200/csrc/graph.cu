@@ -161,6 +161,28 @@ prad_status prad_graph_add_node(prad_graph* g, prad_op op, const int* in_values,
                "prad_graph_add_node: value %d is already the output of node %d", out_value, o.produced_by);
   auto& V = g->values;
   const GValue& a = V[in_values[0]];
+  // Batch* operations: the output is a DeepMatrix of D slices; every input has D slices, or is one Matrix
+  // shared by all slices (BatchMatrixAddOperation.Forward(DeepMatrix, Matrix), BatchGpuMatrixMultiplyOperation
+  // .Forward(Matrix, DeepMatrix) ...).  A shared input must be a leaf: its gradient is the visitor's mean
+  // over the slices (OperationNeuralNetworkVisitor.cs:449-478), which only a destination can receive.
+  const int D = o.depth;
+  for (int i = 0; i < n_in; ++i) {
+    const GValue& iv = V[in_values[i]];
+    PRAD_REQUIRE(iv.depth == D || iv.depth == 1, PRAD_ERR_SHAPE,
+                 "prad_graph_add_node: input %d has %d slices, the output %d", i, iv.depth, D);
+    if (D > 1 && iv.depth == 1) {
+      const bool may_share = op == PRAD_OP_MATMUL || (op == PRAD_OP_ADD && i == 1) || (op == PRAD_OP_ADD3 && i == 2) ||
+                             (op == PRAD_OP_ADD_BROADCAST && i == 1);
+      PRAD_REQUIRE(may_share, PRAD_ERR_SHAPE, "prad_graph_add_node: input %d of operation %d cannot be shared by the slices", i,
+                   (int)op);
+      PRAD_REQUIRE(iv.produced_by < 0, PRAD_ERR_UNSUPPORTED,
+                   "prad_graph_add_node: a Matrix shared by the slices of a batch operation must be a leaf (weight or input)");
+    }
+  }
+  if (D > 1 && op == PRAD_OP_MATMUL)
+    PRAD_REQUIRE(a.depth == D || V[in_values[1]].depth == D, PRAD_ERR_SHAPE, "prad_graph_add_node: no operand has the output's depth");
+  if (D > 1 && op != PRAD_OP_MATMUL)
+    PRAD_REQUIRE(a.depth == D, PRAD_ERR_SHAPE, "prad_graph_add_node: the first input has to carry the slices");
   // shape rules of the managed operations
   bool ok = true;
   switch (op) {
@@ -184,7 +206,7 @@ prad_status prad_graph_add_node(prad_graph* g, prad_op op, const int* in_values,
   }
   PRAD_REQUIRE(ok, PRAD_ERR_SHAPE, "prad_graph_add_node: operand shapes do not fit operation %d", (int)op);
   if (!o.data) {
-    prad_status s = g_alloc(g, (size_t)o.rows * o.cols, &o.data);
+    prad_status s = g_alloc(g, (size_t)o.count(), &o.data);
     if (s) return s;
     o.owned = true;
   }
@@ -238,27 +260,45 @@ static prad_status node_forward(prad_graph* g, GNode& n) {
   const prad_dtype dt = g->dt;
   GValue& o = V[n.out];
   const GValue& a = V[n.in[0]];
-  const int64_t cnt = (int64_t)o.rows * o.cols;
+  const int64_t cnt = o.count();
+  const int D = o.depth;
+  const int64_t rows_all = (int64_t)D * a.rows;      // rows of all slices for the row-wise operations
   switch (n.op) {
-    case PRAD_OP_MATMUL:
-      return prad_matmul_forward(c, dt, a.data, V[n.in[1]].data, o.data, a.rows, a.cols, V[n.in[1]].cols, nullptr,
-                                 nullptr, PRAD_ACT_NONE, 0.0);
-    case PRAD_OP_ADD: return prad_add_forward(c, dt, a.data, V[n.in[1]].data, nullptr, o.data, cnt);
-    case PRAD_OP_ADD3: return prad_add_forward(c, dt, a.data, V[n.in[1]].data, V[n.in[2]].data, o.data, cnt);
-    case PRAD_OP_ADD_BROADCAST: return prad_add_broadcast_forward(c, dt, a.data, V[n.in[1]].data, o.data, a.rows, a.cols);
+    case PRAD_OP_MATMUL: {
+      const GValue& b = V[n.in[1]];
+      if (D == 1)
+        return prad_matmul_forward(c, dt, a.data, b.data, o.data, a.rows, a.cols, b.cols, nullptr, nullptr, PRAD_ACT_NONE, 0.0);
+      if (a.depth == D)    // (DeepMatrix, DeepMatrix) and (DeepMatrix, Matrix)
+        return prad_batch_matmul_forward(c, dt, a.data, b.data, o.data, D, a.rows, a.cols, b.cols, b.depth == 1);
+      // (Matrix, DeepMatrix): every slice is multiplied from the left by the same matrix
+      return prad_gemm(c, dt, 0, 0, a.rows, b.cols, a.cols, 1.0, a.data, a.cols, b.data, b.cols, 0.0, o.data, b.cols, D, 0,
+                       b.slice(), o.slice());
+    }
+    case PRAD_OP_ADD:
+      if (V[n.in[1]].depth != D)   // (DeepMatrix, Matrix): the matrix is a "row" added to each of the D slices
+        return prad_add_broadcast_forward(c, dt, a.data, V[n.in[1]].data, o.data, D, (int)a.slice());
+      return prad_add_forward(c, dt, a.data, V[n.in[1]].data, nullptr, o.data, cnt);
+    case PRAD_OP_ADD3:
+      if (V[n.in[2]].depth != D) {   // (a + b) + bias, the bias shared by the slices
+        G_TRY(prad_add_forward(c, dt, a.data, V[n.in[1]].data, nullptr, o.data, cnt));
+        return prad_add_broadcast_forward(c, dt, o.data, V[n.in[2]].data, o.data, D, (int)a.slice());
+      }
+      return prad_add_forward(c, dt, a.data, V[n.in[1]].data, V[n.in[2]].data, o.data, cnt);
+    case PRAD_OP_ADD_BROADCAST:
+      return prad_add_broadcast_forward(c, dt, a.data, V[n.in[1]].data, o.data, (int)rows_all, a.cols);
     case PRAD_OP_HADAMARD: return prad_hadamard_forward(c, dt, a.data, V[n.in[1]].data, o.data, cnt);
     case PRAD_OP_LEAKY_RELU: case PRAD_OP_SIGMOID: case PRAD_OP_TANH: case PRAD_OP_GELU:
     case PRAD_OP_RELU: case PRAD_OP_AMPLIFIED_SIGMOID:
       return prad_act_forward(c, dt, act_of(n.op), a.data, o.data, cnt, n.scalar);
-    case PRAD_OP_SOFTMAX: return prad_softmax_forward(c, dt, a.data, o.data, a.rows, a.cols);
+    case PRAD_OP_SOFTMAX: return prad_softmax_forward(c, dt, a.data, o.data, rows_all, a.cols);
     case PRAD_OP_LAYERNORM:
       if (!n.aux0) {
-        G_TRY(g_alloc(g, (size_t)a.rows, &n.aux0));
-        G_TRY(g_alloc(g, (size_t)a.rows, &n.aux1));
+        G_TRY(g_alloc(g, (size_t)rows_all, &n.aux0));
+        G_TRY(g_alloc(g, (size_t)rows_all, &n.aux1));
       }
-      return prad_layernorm_forward(c, dt, a.data, o.data, n.aux0, n.aux1, a.rows, a.cols);
+      return prad_layernorm_forward(c, dt, a.data, o.data, n.aux0, n.aux1, rows_all, a.cols);
     case PRAD_OP_SCALE: return prad_scale(c, dt, a.data, o.data, cnt, n.scalar);
-    case PRAD_OP_TRANSPOSE: return prad_transpose(c, dt, a.data, o.data, a.rows, a.cols, 1);
+    case PRAD_OP_TRANSPOSE: return prad_transpose(c, dt, a.data, o.data, a.rows, a.cols, D);
   }
   return PRAD_ERR_INVALID;
 }
@@ -267,7 +307,7 @@ static prad_status node_forward(prad_graph* g, GNode& n) {
 static prad_status in_grad_buf(prad_graph* g, GNode& n, int i, void** out) {
   if (!n.in_grad[i]) {
     const GValue& v = g->values[n.in[i]];
-    G_TRY(g_alloc(g, (size_t)v.rows * v.cols, &n.in_grad[i]));
+    G_TRY(g_alloc(g, (size_t)v.count(), &n.in_grad[i]));
   }
   *out = n.in_grad[i];
   return PRAD_OK;
@@ -276,13 +316,22 @@ static prad_status in_grad_buf(prad_graph* g, GNode& n, int i, void** out) {
 // Runs the Backward of one node for upstream gradient d (shape of its output) and hands each
 // input's gradient to that input value.  MatrixAdd-style operations pass d on by reference,
 // exactly as MatrixAddBroadcastingOperation.Backward returns dOutput itself.
+// mean over the D slices of `deep` (D x per elements) into `out` (per elements): the visitor's combined
+// gradient of a Matrix shared by the slices of a batch operation (sum of the slices times 1/D)
+static prad_status slice_mean(prad_graph* g, const void* deep, void* out, int D, int64_t per) {
+  G_TRY(prad_add_broadcast_backward(g->ctx, g->dt, deep, out, D, (int)per, 0));
+  return prad_scale(g->ctx, g->dt, out, out, per, 1.0 / (double)D);
+}
+
 static prad_status node_backward(prad_graph* g, GNode& n, void* d) {
   auto& V = g->values;
   prad_ctx* c = g->ctx;
   const prad_dtype dt = g->dt;
   const GValue& o = V[n.out];
   const GValue& a = V[n.in[0]];
-  const int64_t cnt = (int64_t)o.rows * o.cols;
+  const int64_t cnt = o.count();
+  const int D = o.depth;
+  const int64_t rows_all = (int64_t)D * a.rows;
   void* ga = nullptr;
   void* gb = nullptr;
   switch (n.op) {
@@ -290,18 +339,44 @@ static prad_status node_backward(prad_graph* g, GNode& n, void* d) {
       const GValue& b = V[n.in[1]];
       G_TRY(in_grad_buf(g, n, 0, &ga));
       G_TRY(in_grad_buf(g, n, 1, &gb));
-      G_TRY(prad_matmul_backward(c, dt, a.data, b.data, d, ga, gb, a.rows, a.cols, b.cols, 0, 1.0, PRAD_ACT_NONE,
-                                 nullptr, 0.0));
+      const int M = a.rows, K = a.cols, N = b.cols;
+      if (D == 1) {
+        G_TRY(prad_matmul_backward(c, dt, a.data, b.data, d, ga, gb, M, K, N, 0, 1.0, PRAD_ACT_NONE, nullptr, 0.0));
+      } else if (a.depth == D && b.depth == D) {
+        G_TRY(prad_batch_matmul_backward(c, dt, a.data, b.data, d, ga, gb, nullptr, D, M, K, N, 0));
+      } else if (a.depth == D) {   // shared second operand: its gradient is the mean of the slices' A_d^T dC_d
+        G_TRY(prad_batch_matmul_backward(c, dt, a.data, b.data, d, ga, nullptr, gb, D, M, K, N, 1));
+      } else {                     // shared first operand W: dX_d = W^T dC_d ; dW = (1/D) sum_d dC_d X_d^T
+        G_TRY(prad_gemm(c, dt, 1, 0, K, N, M, 1.0, a.data, K, d, N, 0.0, gb, N, D, 0, o.slice(), b.slice()));
+        if (N == 1) {              // column vectors: the slices of dC and X are the rows of two matrices
+          G_TRY(prad_gemm(c, dt, 1, 0, M, K, D, 1.0 / (double)D, d, M, b.data, K, 0.0, ga, K, 1, 0, 0, 0));
+        } else {
+          if (!n.aux0) G_TRY(g_alloc(g, (size_t)D * M * K, &n.aux0));
+          G_TRY(prad_gemm(c, dt, 0, 1, M, K, N, 1.0, d, N, b.data, N, 0.0, n.aux0, K, D, o.slice(), b.slice(), (int64_t)M * K));
+          G_TRY(slice_mean(g, n.aux0, ga, D, (int64_t)M * K));
+        }
+      }
       V[n.in[0]].contrib.push_back(ga);
       V[n.in[1]].contrib.push_back(gb);
       return PRAD_OK;
     }
     case PRAD_OP_ADD: case PRAD_OP_ADD3:
-      for (int i : n.in) V[i].contrib.push_back(d);
+      for (size_t i = 0; i < n.in.size(); ++i) {
+        GValue& iv = V[n.in[i]];
+        if (iv.depth == D) {
+          iv.contrib.push_back(d);
+        } else {                   // the Matrix shared by the slices
+          void* gs = nullptr;
+          G_TRY(in_grad_buf(g, n, (int)i, &gs));
+          G_TRY(slice_mean(g, d, gs, D, iv.slice()));
+          iv.contrib.push_back(gs);
+        }
+      }
       return PRAD_OK;
     case PRAD_OP_ADD_BROADCAST:
       G_TRY(in_grad_buf(g, n, 1, &gb));
-      G_TRY(prad_add_broadcast_backward(c, dt, d, gb, o.rows, o.cols, 0));
+      G_TRY(prad_add_broadcast_backward(c, dt, d, gb, (int)rows_all, o.cols, 0));
+      if (D > 1) G_TRY(prad_scale(c, dt, gb, gb, o.cols, 1.0 / (double)D));   // mean of the slices' column sums
       V[n.in[0]].contrib.push_back(d);
       V[n.in[1]].contrib.push_back(gb);
       return PRAD_OK;
@@ -322,12 +397,12 @@ static prad_status node_backward(prad_graph* g, GNode& n, void* d) {
       break;
     case PRAD_OP_SOFTMAX:
       G_TRY(in_grad_buf(g, n, 0, &ga));
-      G_TRY(prad_softmax_backward(c, dt, o.data, d, ga, o.rows, o.cols));
+      G_TRY(prad_softmax_backward(c, dt, o.data, d, ga, rows_all, o.cols));
       break;
     case PRAD_OP_LAYERNORM:
       PRAD_REQUIRE(n.aux0, PRAD_ERR_INVALID, "prad_graph_backward: LayerNorm node has no forward state (run prad_graph_forward)");
       G_TRY(in_grad_buf(g, n, 0, &ga));
-      G_TRY(prad_layernorm_backward(c, dt, a.data, n.aux0, n.aux1, d, ga, a.rows, a.cols));
+      G_TRY(prad_layernorm_backward(c, dt, a.data, n.aux0, n.aux1, d, ga, rows_all, a.cols));
       break;
     case PRAD_OP_SCALE:
       G_TRY(in_grad_buf(g, n, 0, &ga));
@@ -335,7 +410,7 @@ static prad_status node_backward(prad_graph* g, GNode& n, void* d) {
       break;
     case PRAD_OP_TRANSPOSE:
       G_TRY(in_grad_buf(g, n, 0, &ga));
-      G_TRY(prad_transpose(c, dt, d, ga, o.rows, o.cols, 1));
+      G_TRY(prad_transpose(c, dt, d, ga, o.rows, o.cols, D));
       break;
   }
   V[n.in[0]].contrib.push_back(ga);
@@ -390,12 +465,11 @@ prad_status prad_graph_backward_multi(prad_graph* g, const int* start_values, co
     if (v.contrib.size() == 1) {
       v.grad = v.contrib[0];
     } else {
-      if (!v.sum_buf) G_TRY(g_alloc(g, (size_t)v.rows * v.cols, &v.sum_buf));
-      G_TRY(prad_segmented_sum(g->ctx, g->dt, v.contrib.data(), (int)v.contrib.size(), v.sum_buf,
-                               (int64_t)v.rows * v.cols));
+      if (!v.sum_buf) G_TRY(g_alloc(g, (size_t)v.count(), &v.sum_buf));
+      G_TRY(prad_segmented_sum(g->ctx, g->dt, v.contrib.data(), (int)v.contrib.size(), v.sum_buf, v.count()));
       v.grad = v.sum_buf;
     }
-    if (v.grad_dst) G_TRY(prad_accumulate(g->ctx, g->dt, v.grad_dst, v.grad, (int64_t)v.rows * v.cols));
+    if (v.grad_dst) G_TRY(prad_accumulate(g->ctx, g->dt, v.grad_dst, v.grad, v.count()));
     return PRAD_OK;
   };
   auto external_of = [&](int value) -> const void* {

@@ -154,7 +154,7 @@ pack_fast_kernel(PackSource src, PackedForm fr, PackedForm fc) {
         __half2 p0[2], p1[2];
         pieces2(v[0] * scale, v[1] * scale, p0[0], p1[0]);
         pieces2(v[2] * scale, v[3] * scale, p0[1], p1[1]);
-        __half* dst = fr.h + r * 2 * fr.kp + (int64_t)(c >> 5) * 64 + (c & 31);
+        __half* dst = fr.h + r * fr.pitch + (int64_t)(c >> 5) * 64 + (c & 31);
         *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(p0);
         *reinterpret_cast<uint2*>(dst + 32) = *reinterpret_cast<const uint2*>(p1);
       }
@@ -179,7 +179,7 @@ pack_fast_kernel(PackSource src, PackedForm fr, PackedForm fc) {
 #pragma unroll
     for (int j = 0; j < 16; ++j)
       pieces2(col_base[(2 * j) * STRIDE] * scale, col_base[(2 * j + 1) * STRIDE] * scale, p0[j], p1[j]);
-    __half* dst = fc.h + (int64_t)col * 2 * fc.kp + ((r0 + kg * 32) >> 5) * 64;     // one 128-byte line: h0 | h1
+    __half* dst = fc.h + (int64_t)col * fc.pitch + ((r0 + kg * 32) >> 5) * 64;     // one 128-byte line: h0 | h1
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<const uint4*>(p0)[j];
@@ -280,7 +280,7 @@ pack_tile_kernel(PackSource src, bool vec, int R, int C, PackedForm fr, PackedFo
         const int sh = shift_of(m);
         const float scale = pow2f(sh);
         if (lane == 0) fr.blk[(int64_t)(c0 / TC) * fr.rows_ld + r] = pow2f(-sh);
-        __half* drow = fr.h + r * 2 * fr.kp;
+        __half* drow = fr.h + r * fr.pitch;
 #pragma unroll
         for (int w = 0; w < W; ++w) {
           const int c = c0 + lane * 4 + 128 * w;
@@ -319,7 +319,7 @@ pack_tile_kernel(PackSource src, bool vec, int R, int C, PackedForm fr, PackedFo
     __align__(16) __half p1[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) pieces(stash[(kg * 32 + j) * STRIDE + cg * 32 + lane] * scale, p0[j], p1[j]);
-    __half* d = fc.h + (int64_t)col * 2 * fc.kp + (kbase >> 5) * 64;     // one 128-byte line: h0 | h1
+    __half* d = fc.h + (int64_t)col * fc.pitch + (kbase >> 5) * 64;     // one 128-byte line: h0 | h1
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       reinterpret_cast<uint4*>(d)[j] = reinterpret_cast<const uint4*>(p0)[j];

@@ -10,9 +10,11 @@
 // nothing and no pass over the matrix is needed to find a whole-row maximum before the first element
 // can be converted.
 //
-// Memory layout of a row: pitch 2*kp halves (kp = k rounded up to 32); the pieces are interleaved per
-// 32-k group, [h0 of k 0..31 | h1 of k 0..31 | h0 of k 32..63 | ...], so that one 128-byte TMA row
-// brings both pieces of a group.  Padding (k..kp) is zero.
+// Memory layout of a row: 2*kp halves (kp = k rounded up to 32), the pieces interleaved per 32-k group,
+// [h0 of k 0..31 | h1 of k 0..31 | h0 of k 32..63 | ...], so that one 128-byte TMA row brings both pieces
+// of a group; padding (k..kp) is zero.  Rows are `pitch` halves apart: one 128-byte line more than the
+// row needs, so that a column of lines (the same k group of consecutive rows: what a tile load reads
+// and what the by-columns packing writes) does not sit at a power-of-two stride in one memory channel.
 // Block scales: blk[c * rows_ld + r] = 2^-s (a float) for block c of row r; rows r >= rows hold zero.
 // s is limited to [-90, 126]: values up to 2^104 keep all their bits (beyond 2^106 the pieces overflow),
 // blocks whose largest magnitude is below 2^-112 lose bits; 2^-s <= 2^90 keeps the product with a
@@ -36,10 +38,11 @@ struct PackedForm {
   int rows = 0;       // operand rows
   int64_t k = 0;      // contraction length
   int64_t kp = 0;     // k rounded up to PACK_KPAD
+  int64_t pitch = 0;  // halves between consecutive rows: 2 * kp + 64
   int rows_ld = 0;    // pitch of blk
   int nchunk = 0;     // blocks per row
   int chunk = 0;      // k per block (a multiple of 32)
-  size_t h_bytes() const { return (size_t)rows * 2 * kp * sizeof(__half); }
+  size_t h_bytes() const { return (size_t)rows * pitch * sizeof(__half); }
   size_t blk_bytes() const { return (size_t)nchunk * rows_ld * sizeof(float); }
 };
 
@@ -48,6 +51,7 @@ inline PackedForm packed_form_shape(int rows, int64_t k, int chunk) {
   f.rows = rows;
   f.k = k;
   f.kp = ceil_div(k, PACK_KPAD) * PACK_KPAD;
+  f.pitch = 2 * f.kp + 64;
   f.rows_ld = (int)(ceil_div(rows, PACK_ROWS_ALIGN) * PACK_ROWS_ALIGN);
   f.chunk = chunk;
   f.nchunk = (int)ceil_div(f.kp, chunk);

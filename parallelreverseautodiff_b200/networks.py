@@ -227,10 +227,14 @@ class FeedForwardNetwork:
             if self.use_bias:                        # the bias gradient sums the FP32 gradient's columns
                 dz32 = self.dZ[1].view((rows, self.sizes[l]))
             saved = self._saved(l) if act != E.ACT_NONE else None
+            if probe:
+                probe("pack", True)
             if l == L and mse is not None:
                 pd.mse_act_backward(act, saved, mse[0], mse[1], mse[2], dz32, alpha)
             else:
                 pd.act_backward(act, saved, g, dz32, alpha)
+            if probe:
+                probe("pack", False)
             if probe:
                 probe("gemm", True)
             e.gemm_packed(self.PA[l - 1], E.PACK_COLS, pd, E.PACK_COLS, self.dW[l - 1])
@@ -239,7 +243,11 @@ class FeedForwardNetwork:
             # the first weight-gradient product reads no weights: the previous step's weight broadcasts run
             # beside it; they are joined here, and only then are the (new) weights packed
             self._join_broadcasts()
+            if probe:
+                probe("pack", True)
             self._pack_weights(forward=False)
+            if probe:
+                probe("pack", False)
             if self.world > 1 and self.dp_overlap:
                 self._reduce_grad(l - 1)
             if self.use_bias:

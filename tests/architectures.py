@@ -140,29 +140,61 @@ class OracleInterpreter:
     def _val(self, ref):
         return self.by_id[ref[1]]["out"] if ref[0] == "op" else ref[1]
 
+    def _fwd_one(self, t, x, n, slot):
+        """One Forward on matrices; `slot` keeps what the Backward of that slice needs."""
+        if t == "MatrixMultiplyOperation": return O.matmul_forward(x[0], x[1])
+        if t == "MatrixAddOperation": return O.add_forward(x[0], x[1])
+        if t == "MatrixAddThreeOperation": return O.add3_forward(x[0], x[1], x[2])
+        if t == "MatrixTransposeOperation": return O.transpose(x[0])
+        if t == "LayerNormalizationOperation":
+            y, slot["mean"], slot["std"] = O.layernorm_forward(x[0])
+            return y
+        if t == "SigmoidOperation": return O.sigmoid_forward(x[0])
+        if t == "TanhOperation": return O.tanh_forward(x[0])
+        if t == "AmplifiedSigmoidOperation": return O.amplified_sigmoid_forward(x[0])
+        if t == "LeakyReLUOperation": return O.leaky_relu_forward(x[0], self.alpha)
+        if t == "HadamardProductOperation": return O.hadamard_forward(x[0], x[1])
+        if t == "MatrixMultiplyScalarOperation": return O.scale(x[0], x[1])
+        if t == "SoftmaxOperation": return O.softmax_forward(x[0])
+        raise KeyError(t)
+
+    def _bwd_one(self, t, x, y, d, slot):
+        if t == "MatrixMultiplyOperation": return list(O.matmul_backward(x[0], x[1], d))
+        if t == "MatrixAddOperation": return [d, d]
+        if t == "MatrixAddThreeOperation": return [d, d, d]
+        if t == "MatrixTransposeOperation": return [O.transpose(d)]
+        if t == "LayerNormalizationOperation": return [O.layernorm_backward(x[0], slot["mean"], slot["std"], d)]
+        if t == "SigmoidOperation": return [O.sigmoid_backward(y, d)]
+        if t == "TanhOperation": return [O.tanh_backward(y, d)]
+        if t == "AmplifiedSigmoidOperation": return [O.amplified_sigmoid_backward(x[0], d)]
+        if t == "LeakyReLUOperation": return [O.leaky_relu_backward(x[0], d, self.alpha)]
+        if t == "HadamardProductOperation": return list(O.hadamard_backward(x[0], x[1], d))
+        if t == "MatrixMultiplyScalarOperation": return [O.scale(d, x[1])]
+        if t == "SoftmaxOperation": return [O.softmax_backward(y, d)]
+        raise KeyError(t)
+
+    @staticmethod
+    def _slice(v, k):
+        return v[k] if isinstance(v, np.ndarray) and v.ndim == 3 else v
+
     def forward(self):
         for n in self.nodes:
             x = [self._val(r) for r in n["ins"]]
             t = n["type"]
-            if t == "MatrixMultiplyOperation": y = O.matmul_forward(x[0], x[1])
-            elif t == "MatrixAddOperation": y = O.add_forward(x[0], x[1])
-            elif t == "MatrixAddThreeOperation": y = O.add3_forward(x[0], x[1], x[2])
-            elif t == "MatrixTransposeOperation": y = O.transpose(x[0])
-            elif t == "LayerNormalizationOperation":
-                y, n["mean"], n["std"] = O.layernorm_forward(x[0])
-            elif t == "SigmoidOperation": y = O.sigmoid_forward(x[0])
-            elif t == "TanhOperation": y = O.tanh_forward(x[0])
-            elif t == "AmplifiedSigmoidOperation": y = O.amplified_sigmoid_forward(x[0])
-            elif t == "LeakyReLUOperation": y = O.leaky_relu_forward(x[0], self.alpha)
-            elif t == "HadamardProductOperation": y = O.hadamard_forward(x[0], x[1])
-            elif t == "MatrixMultiplyScalarOperation": y = O.scale(x[0], x[1])
-            elif t == "SoftmaxOperation": y = O.softmax_forward(x[0])
-            else: raise KeyError(t)
-            n["out"] = y
+            if t.startswith("Batch"):      # BatchOperation: one operation object per slice
+                depth = max(v.shape[0] for v in x if isinstance(v, np.ndarray) and v.ndim == 3)
+                n["slots"] = [dict() for _ in range(depth)]
+                n["out"] = np.stack([self._fwd_one(t[5:], [self._slice(v, k) for v in x], n, n["slots"][k])
+                                     for k in range(depth)])
+            else:
+                n["slots"] = [dict()]
+                n["out"] = self._fwd_one(t, x, n, n["slots"][0])
 
     def backward(self, starts):
         """starts: {specific id: upstream gradient}.  One reverse walk; contributions of the consumers of an
-        operation are summed in the order the consumers were added."""
+        operation are summed in the order the consumers were added.  A Batch* operation runs its slices'
+        Backward one by one; a Matrix shared by the slices receives the visitor's combined gradient, the
+        left-fold sum of the slices' gradients times 1 / depth."""
         order = {n["id"]: k for k, n in enumerate(self.nodes)}
         contrib = {n["id"]: [] for n in self.nodes}           # (consumer index, gradient)
         for sid, g in starts.items():
@@ -175,21 +207,47 @@ class OracleInterpreter:
             n["grad"] = d
             x = [self._val(r) for r in n["ins"]]
             t = n["type"]
-            if t == "MatrixMultiplyOperation": gs = list(O.matmul_backward(x[0], x[1], d))
-            elif t in ("MatrixAddOperation",): gs = [d, d]
-            elif t == "MatrixAddThreeOperation": gs = [d, d, d]
-            elif t == "MatrixTransposeOperation": gs = [O.transpose(d)]
-            elif t == "LayerNormalizationOperation": gs = [O.layernorm_backward(x[0], n["mean"], n["std"], d)]
-            elif t == "SigmoidOperation": gs = [O.sigmoid_backward(n["out"], d)]
-            elif t == "TanhOperation": gs = [O.tanh_backward(n["out"], d)]
-            elif t == "AmplifiedSigmoidOperation": gs = [O.amplified_sigmoid_backward(x[0], d)]
-            elif t == "LeakyReLUOperation": gs = [O.leaky_relu_backward(x[0], d, self.alpha)]
-            elif t == "HadamardProductOperation": gs = list(O.hadamard_backward(x[0], x[1], d))
-            elif t == "MatrixMultiplyScalarOperation": gs = [O.scale(d, x[1])]
-            elif t == "SoftmaxOperation": gs = [O.softmax_backward(n["out"], d)]
-            else: raise KeyError(t)
+            if t.startswith("Batch"):
+                depth = n["out"].shape[0]
+                per = [self._bwd_one(t[5:], [self._slice(v, k) for v in x], n["out"][k], d[k], n["slots"][k]) for k in range(depth)]
+                gs = []
+                for j, v in enumerate(x):
+                    if j >= len(per[0]):
+                        break
+                    if isinstance(v, np.ndarray) and v.ndim == 3:
+                        gs.append(np.stack([per[k][j] for k in range(depth)]))
+                    else:
+                        gs.append(O.batch_mean([np.ascontiguousarray(per[k][j]) for k in range(depth)]))
+            else:
+                gs = self._bwd_one(t, x, n["out"], d, n["slots"][0])
             for j, g in enumerate(gs):
                 if j < len(n["dests"]) and n["dests"][j] is not None:
                     O.accumulate_into(n["dests"][j], g)
                 if n["ins"][j][0] == "op":
                     contrib[n["ins"][j][1]].append((order[n["id"]], g))
+
+
+def batch_network_architecture():
+    """A small network in the spelling of test/.../GraphAttentionPaths/*/Architecture/*.json: Batch* operations
+    over per-sample column vectors held in DeepMatrix values, weights and biases shared by the samples."""
+    bmm = "BatchGpuMatrixMultiplyOperation"
+    start = [_op("projectedInput", bmm, ["We", "Input"], ["dWe", None]),
+             _op("embeddedInput", "BatchMatrixAddOperation", ["projectedInput", "be"], [None, "dbe"])]
+    layer = [_op("w_x", bmm, ["W[layerIndex]", "currentInput"], ["dW[layerIndex]", None]),
+             _op("u_x", bmm, ["U[layerIndex]", "embeddedInput"], ["dU[layerIndex]", None]),
+             _op("z", "BatchMatrixAddThreeOperation", ["w_x", "u_x", "b[layerIndex]"], [None, None, "db[layerIndex]"]),
+             _op("zT", "BatchMatrixTransposeOperation", ["z"]),
+             _op("zN", "BatchLayerNormalizationOperation", ["zT"]),
+             _op("zNT", "BatchMatrixTransposeOperation", ["zN"]),
+             _op("gate", "BatchAmplifiedSigmoidOperation", ["zNT"]),
+             _op("cand", "BatchTanhOperation", ["z"]),
+             _op("mix", "BatchHadamardProductOperation", ["gate", "cand"]),
+             _op("h", "BatchLeakyReLUOperation", ["mix"], result="H[layerIndex]")]
+    end = [_op("hT", "BatchMatrixTransposeOperation", ["hLast"]),
+           _op("outer", "BatchMatrixMultiplyOperation", ["hLast", "hT"]),
+           _op("scaled", "BatchMatrixMultiplyScalarOperation", ["outer", "scale"]),
+           _op("attn", "BatchSoftmaxOperation", ["scaled"]),
+           _op("mixed", "BatchMatrixMultiplyOperation", ["attn", "hLast"]),
+           _op("v_h", bmm, ["V", "mixed"], ["dV", None]),
+           _op("output", "BatchMatrixAddOperation", ["v_h", "bo"], [None, "dbo"], result="Output")]
+    return {"timeSteps": [{"startOperations": start, "layers": [{"operations": layer}], "endOperations": end}]}

@@ -189,3 +189,58 @@ def test_lstm_example_architecture_file(engine, one_walk):
         # h of a time step feeds the four gates and the attention queries of the next, the layer above and the output
         assert g.dependency_count("h_0_0") >= 5 and g.dependency_count("embeddedInput_0_0") >= 3
     g.close()
+
+
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+def test_batch_operations_on_deep_matrices(engine, dtype):
+    """Batch* operations (one slice per sample) with weights and biases shared by the samples: the shared
+    matrices receive the mean over the samples; deep values fan out (z, embeddedInput, hLast)."""
+    r = rng(21)
+    B, n_in, nh, n_out, L = 6, 9, 12, 4, 2
+    mk = lambda *s: (r.standard_normal(s) * 0.5).astype(dtype)
+    glob = _both(engine, dict(We=mk(nh, n_in), be=mk(nh, 1), V=mk(n_out, nh), bo=mk(n_out, 1)))
+    lay = [_both(engine, dict(W=mk(nh, nh), U=mk(nh, nh), b=mk(nh, 1))) for _ in range(L)]
+    gg = _both(engine, {"d" + k: np.zeros_like(v[0]) for k, v in glob.items()})
+    gl = [_both(engine, {"d" + k: np.zeros_like(v[0]) for k, v in lay[l].items()}) for l in range(L)]
+    x = mk(B, n_in, 1)
+    x_dev = engine.upload(x)
+    H = [engine.zeros((B, nh, 1), dtype) for _ in range(L)]
+    out_dev = engine.zeros((B, n_out, 1), dtype)
+    scale = 1.0 / np.sqrt(nh)
+
+    g = ArchitectureGraph(engine, dtype)
+    for k in glob:
+        g.AddWeight(k, lambda li, k=k: glob[k][1]).AddGradient("d" + k, lambda li, k=k: gg["d" + k][1])
+    for k in ("W", "U", "b"):
+        g.AddWeight(k, lambda li, k=k: lay[li.Layer][k][1]).AddGradient("d" + k, lambda li, k=k: gl[li.Layer]["d" + k][1])
+    g.AddIntermediate("Input", lambda li: x_dev).AddIntermediate("Output", lambda li: out_dev)
+    g.AddIntermediate("H", lambda li: H[li.Layer]).AddScalar("scale", lambda li: scale)
+    g.AddOperationFinder("currentInput", lambda li: g["embeddedInput_0_0"] if li.Layer == 0 else g[f"h_0_{li.Layer - 1}"])
+    g.AddOperationFinder("embeddedInput", lambda li: g["embeddedInput_0_0"])
+    g.AddOperationFinder("hLast", lambda li: g[f"h_0_{L - 1}"])
+    g.ConstructFromArchitecture(A.batch_network_architecture(), L)
+
+    leaves = {k: (lambda t, l, k=k: glob[k][0]) for k in glob}
+    leaves.update({k: (lambda t, l, k=k: lay[l][k][0]) for k in ("W", "U", "b")})
+    leaves.update(Input=lambda t, l: x, scale=lambda t, l: scale,
+                  currentInput=lambda t, l: ("op", "embeddedInput_0_0" if l == 0 else f"h_0_{l - 1}"),
+                  embeddedInput=lambda t, l: ("op", "embeddedInput_0_0"), hLast=lambda t, l: ("op", f"h_0_{L - 1}"))
+    grads = {"d" + k: (lambda t, l, k=k: gg["d" + k][0]) for k in glob}
+    grads.update({"d" + k: (lambda t, l, k=k: gl[l]["d" + k][0]) for k in ("W", "U", "b")})
+    it = A.OracleInterpreter(A.batch_network_architecture(), leaves, grads, L)
+
+    g.forward()
+    it.forward()
+    assert_close(out_dev.numpy(), it.by_id["output_0_0"]["out"], 10.0, "batch architecture Output")
+    for l in range(L):
+        assert_close(H[l].numpy(), it.by_id[f"h_0_{l}"]["out"], 10.0, "batch architecture H")
+    up = mk(B, n_out, 1)
+    g.backward("output_0_0", engine.upload(up))
+    it.backward({"output_0_0": up})
+    for k in gg:
+        assert_close(gg[k][1].numpy(), gg[k][0], 30 * rms(gg[k][0]) + 1e-3, f"batch architecture {k}")
+    for l in range(L):
+        for k in gl[l]:
+            assert_close(gl[l][k][1].numpy(), gl[l][k][0], 30 * rms(gl[l][k][0]) + 1e-3, f"batch architecture {k}[{l}]")
+    assert g.dependency_count("embeddedInput_0_0") == 1 + L      # the first layer's input and every layer's u_x
+    g.close()
