@@ -415,6 +415,12 @@ prad_status prad_softmax_forward(prad_ctx* ctx, prad_dtype dt, const void* x, vo
                                  int64_t rows, int cols);
 prad_status prad_softmax_backward(prad_ctx* ctx, prad_dtype dt, const void* y, const void* dy,
                                   void* dx, int64_t rows, int cols);
+/* SineSoftmaxOperation.cs:47-77,155-176 (the attention weights of the GraphAttentionPaths networks):
+ * y_j = e_j / (M + e_j) with e = exp(sin x) and M the row's sum of e; Backward as written there,
+ * dx_j = dy_j * (M * e_j * cos x_j) / (M + e_j)^2, reads the INPUT x. */
+prad_status prad_sine_softmax_forward(prad_ctx* ctx, prad_dtype dt, const void* x, void* y, int64_t rows, int cols);
+prad_status prad_sine_softmax_backward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* dy, void* dx, int64_t rows,
+                                       int cols);
 /* LayerNormalizationOperation.cs:56-112: population sigma, eps (1e-9) added to sigma; the
  * backward is the reference's diagonal-only form.  mean/stdv are rows long (the op's state). */
 prad_status prad_layernorm_forward(prad_ctx* ctx, prad_dtype dt, const void* x, void* y,
@@ -560,7 +566,8 @@ typedef enum {
   PRAD_OP_SCALE = 11,        /* MatrixMultiplyScalarOperation, scalar = factor    */
   PRAD_OP_TRANSPOSE = 12,
   PRAD_OP_RELU = 13,
-  PRAD_OP_AMPLIFIED_SIGMOID = 14
+  PRAD_OP_AMPLIFIED_SIGMOID = 14,
+  PRAD_OP_SINE_SOFTMAX = 15
 } prad_op;
 
 prad_status prad_graph_create(prad_ctx* ctx, prad_dtype dt, prad_graph** out_graph);

@@ -401,6 +401,21 @@ def softmax_backward(y, dy):
     return dx
 
 
+def sine_softmax_forward(x):
+    x = _c(x)
+    y = np.empty_like(x)
+    _fn("sine_softmax_forward", x.dtype)(_p(x), _p(y), x.shape[0], x.shape[1])
+    return y
+
+
+def sine_softmax_backward(x, dy):
+    x = _c(x)
+    dy = _c(dy, x.dtype)
+    dx = np.empty_like(x)
+    _fn("sine_softmax_backward", x.dtype)(_p(x), _p(dy), _p(dx), x.shape[0], x.shape[1])
+    return dx
+
+
 def layernorm_forward(x):
     """Returns (y, mean[R], std[R])."""
     x = _c(x)

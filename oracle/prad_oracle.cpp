@@ -511,6 +511,39 @@ void softmax_forward(const T* x, T* y, int R, int C) {
     for (int j = 0; j < C; ++j) yr[j] = yr[j] / sum;
   }
 }
+// ---- SineSoftmaxOperation.cs:47-77,155-176: y_j = e_j / (M + e_j) with e = exp(sin x) and M the row's
+// sum of e (accumulated in the storage type, j ascending); Backward as written: dx_j = dy_j * (M * e_j *
+// cos x_j) / (M + e_j)^2.  PradMath's float overloads compute in double and cast.
+template <typename T> inline T p_sin(T x) { return (T)std::sin((double)x); }
+template <typename T> inline T p_cos(T x) { return (T)std::cos((double)x); }
+template <typename T>
+void sine_softmax_forward(const T* x, T* y, int R, int C) {
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < R; ++i) {
+    const T* xr = x + (size_t)i * C;
+    T m = 0;
+    for (int j = 0; j < C; ++j) m = m + p_exp<T>(p_sin<T>(xr[j]));
+    for (int j = 0; j < C; ++j) {
+      T num = p_exp<T>(p_sin<T>(xr[j]));
+      y[(size_t)i * C + j] = num / (m + num);
+    }
+  }
+}
+template <typename T>
+void sine_softmax_backward(const T* x, const T* dy, T* dx, int R, int C) {
+#pragma omp parallel for schedule(static)
+  for (int i = 0; i < R; ++i) {
+    const T* xr = x + (size_t)i * C;
+    T m = 0;
+    for (int k = 0; k < C; ++k) m = m + p_exp<T>(p_sin<T>(xr[k]));
+    for (int j = 0; j < C; ++j) {
+      T e = p_exp<T>(p_sin<T>(xr[j]));
+      T num = m * e * p_cos<T>(xr[j]);
+      T den = p_pow<T>(m + e, (T)2);
+      dx[(size_t)i * C + j] = dy[(size_t)i * C + j] * (num / den);
+    }
+  }
+}
 // explicit Jacobian product accumulated in k order (SoftmaxOperation.cs:53-83)
 template <typename T>
 void softmax_backward(const T* y, const T* dy, T* dx, int R, int C) {
@@ -908,6 +941,12 @@ void adam_prad(T* w, T* m, T* v, const T* g, size_t n, T lr, T b1, T b2, T eps, 
   }                                                                                                \
   void oracle_softmax_backward_##S(const T* y, const T* dy, T* dx, int R, int C) {                 \
     softmax_backward<T>(y, dy, dx, R, C);                                                          \
+  }                                                                                                \
+  void oracle_sine_softmax_forward_##S(const T* x, T* y, int R, int C) {                           \
+    sine_softmax_forward<T>(x, y, R, C);                                                           \
+  }                                                                                                \
+  void oracle_sine_softmax_backward_##S(const T* x, const T* dy, T* dx, int R, int C) {            \
+    sine_softmax_backward<T>(x, dy, dx, R, C);                                                     \
   }                                                                                                \
   void oracle_layernorm_forward_##S(const T* x, T* y, T* mean, T* stdv, int R, int C) {            \
     layernorm_forward<T>(x, y, mean, stdv, R, C);                                                  \

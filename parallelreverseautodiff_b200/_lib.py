@@ -73,6 +73,8 @@ SIGNATURES = {
     "prad_add_broadcast_backward_static": [vp, i32, vp, vp, i32, i32, i32],
     "prad_scale": [vp, i32, vp, vp, i64, f64],
     "prad_transpose": [vp, i32, vp, vp, i32, i32, i32],
+    "prad_sine_softmax_forward": [vp, i32, vp, vp, i64, i32],
+    "prad_sine_softmax_backward": [vp, i32, vp, vp, vp, i64, i32],
     "prad_softmax_forward": [vp, i32, vp, vp, i64, i32],
     "prad_softmax_backward": [vp, i32, vp, vp, vp, i64, i32],
     "prad_layernorm_forward": [vp, i32, vp, vp, vp, vp, i64, i32],

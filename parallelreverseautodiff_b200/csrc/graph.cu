@@ -139,7 +139,7 @@ prad_status prad_graph_set_gradient_destination(prad_graph* g, int value, void* 
 prad_status prad_graph_add_node(prad_graph* g, prad_op op, const int* in_values, int n_in,
                                 int out_value, double scalar, int* out_node) {
   PRAD_CHECK_GRAPH(g);
-  PRAD_REQUIRE(op >= PRAD_OP_MATMUL && op <= PRAD_OP_AMPLIFIED_SIGMOID && in_values, PRAD_ERR_INVALID,
+  PRAD_REQUIRE(op >= PRAD_OP_MATMUL && op <= PRAD_OP_SINE_SOFTMAX && in_values, PRAD_ERR_INVALID,
                "prad_graph_add_node: unknown operation or null inputs");
   PRAD_REQUIRE(n_in == arity(op), PRAD_ERR_INVALID, "prad_graph_add_node: operation %d takes %d inputs, got %d",
                (int)op, arity(op), n_in);
@@ -291,6 +291,7 @@ static prad_status node_forward(prad_graph* g, GNode& n) {
     case PRAD_OP_RELU: case PRAD_OP_AMPLIFIED_SIGMOID:
       return prad_act_forward(c, dt, act_of(n.op), a.data, o.data, cnt, n.scalar);
     case PRAD_OP_SOFTMAX: return prad_softmax_forward(c, dt, a.data, o.data, rows_all, a.cols);
+    case PRAD_OP_SINE_SOFTMAX: return prad_sine_softmax_forward(c, dt, a.data, o.data, rows_all, a.cols);
     case PRAD_OP_LAYERNORM:
       if (!n.aux0) {
         G_TRY(g_alloc(g, (size_t)rows_all, &n.aux0));
@@ -398,6 +399,10 @@ static prad_status node_backward(prad_graph* g, GNode& n, void* d) {
     case PRAD_OP_SOFTMAX:
       G_TRY(in_grad_buf(g, n, 0, &ga));
       G_TRY(prad_softmax_backward(c, dt, o.data, d, ga, rows_all, o.cols));
+      break;
+    case PRAD_OP_SINE_SOFTMAX:                      // Backward reads the input
+      G_TRY(in_grad_buf(g, n, 0, &ga));
+      G_TRY(prad_sine_softmax_backward(c, dt, a.data, d, ga, rows_all, o.cols));
       break;
     case PRAD_OP_LAYERNORM:
       PRAD_REQUIRE(n.aux0, PRAD_ERR_INVALID, "prad_graph_backward: LayerNorm node has no forward state (run prad_graph_forward)");

@@ -89,11 +89,38 @@ __device__ __forceinline__ void fetch4(const PackSource& s, bool vec, int64_t r,
 // The same two passes for tiles that lie completely inside the matrix, with 16-byte aligned operands and
 // 128-long blocks: no bounds tests, the operation fixed at compile time, conversions two values at a
 // time (cvt.rn.f16x2.f32).  OP: 0 plain; 1 / 2 / 3 forward GELU / LeakyReLU / any activation;
-// 4 / 5 / 6 backward likewise; 7 / 8 mean-squared-error gradient times the GELU / any derivative.
+// 4 / 5 / 6 backward likewise; 7 / 8 mean-squared-error gradient times the GELU / any derivative;
+// 9 / 10 / 11 are 1 / 4 / 7 (the GELU cases) in short arithmetic, chosen when no FP32 copy is written.
+//
+// Short arithmetic: the copy-less result exists only as pieces of 22 significant bits, so the GELU terms
+// are contracted into fused multiply-adds and tanh is 1 - 2 / (1 + 2^(2 log2(e) u)) with the hardware's
+// exp2 and reciprocal approximations (absolute error about 3e-7, of the order of the pieces' own
+// rounding).  With an FP32 copy the arithmetic is the stand-alone activation kernels', operation by
+// operation, so that the copy is bit-identical to theirs.
 __device__ __forceinline__ void pieces2(float x0, float x1, __half2& p0, __half2& p1) {
   p0 = __floats2half2_rn(x0, x1);
   const float2 b = __half22float2(p0);
   p1 = __floats2half2_rn(x0 - b.x, x1 - b.y);      // the differences are exact in FP32
+}
+__device__ __forceinline__ float tanh_short(float u) {
+  float t, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(u * 2.885390081777927f));    // e^(2u); inf / 0 at the ends
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t + 1.0f));
+  return fmaf(-2.0f, r, 1.0f);
+}
+__device__ __forceinline__ float gelu_inner_short(float x, float x2) {
+  return x * fmaf(x2, 0.7978845f * 0.044715f, 0.7978845f);
+}
+__device__ __forceinline__ float gelu_value_short(float x) {
+  const float b = tanh_short(gelu_inner_short(x, x * x));
+  return x * fmaf(0.5f, b, 0.5f);
+}
+__device__ __forceinline__ float gelu_derivative_short(float x) {
+  const float x2 = x * x;
+  const float b = tanh_short(gelu_inner_short(x, x2));
+  const float omb2 = fmaf(-b, b, 1.0f);
+  const float d = fmaf(x2, 0.7978845f * (0.044715f * 3.0f), 0.7978845f);
+  return fmaf(0.5f * x, fmaf(omb2 * omb2, d, b), fmaf(0.5f, b, 0.5f));
 }
 template <int OP>
 __device__ __forceinline__ float apply_op(const PackSource& s, float a, float d, float tg) {
@@ -101,50 +128,66 @@ __device__ __forceinline__ float apply_op(const PackSource& s, float a, float d,
   if (OP == 1) return gelu_value<float>(a);
   if (OP == 2) return a > 0.f ? a : mul_rn(s.act_alpha, a);
   if (OP == 3) return act_value<float>((prad_act)s.act, a, s.act_alpha);
-  if (OP >= 7) d = mul_rn(s.loss_scale, sub_rn(d, tg));
+  if (OP == 9) return gelu_value_short(a);
+  if (OP == 7 || OP == 8 || OP == 11) d = mul_rn(s.loss_scale, sub_rn(d, tg));
   if (OP == 4 || OP == 7) return mul_rn(d, gelu_derivative<float>(a));
+  if (OP == 10 || OP == 11) return d * gelu_derivative_short(a);
   if (OP == 5) return mul_rn(d, a > 0.f ? 1.f : s.act_alpha);
   return mul_rn(d, act_derivative<float>((prad_act)s.act, a, s.act_alpha));
 }
 
+// Stash: the tile's values as floats, [128 k][128 columns] without padding; the float4 of columns 4q..4q+3
+// of tile row k sits in slot q ^ ((k >> 2) & 7) of its row.  Pass 1 stores whole float4 (any permutation of
+// slots is conflict-free); in pass 2 a lane reads four consecutive k of one column and the eight lanes that
+// share a column quad read eight different slot positions: 32 different banks.
 template <int OP, bool ROWS, bool COLS>
 __global__ void __launch_bounds__(256)
 pack_fast_kernel(PackSource src, PackedForm fr, PackedForm fc) {
-  constexpr int T = 128, STRIDE = T + 4, U = 4;
-  extern __shared__ float stash[];       // [T][STRIDE] when COLS
+  constexpr int T = 128, U = 2, NB = T / 8 / U;
+  constexpr bool HAS_DY = OP >= 4 && OP != 9, HAS_TG = OP == 7 || OP == 8 || OP == 11;
+  extern __shared__ float stash[];       // [T][T] when COLS
   __shared__ unsigned colmax[T];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t r0 = (int64_t)blockIdx.y * T;
   const int c0 = blockIdx.x * T, c = c0 + lane * 4;
   if (COLS && threadIdx.x < T) colmax[threadIdx.x] = 0;
   uint32_t cm[4] = {0, 0, 0, 0};
-  for (int it0 = 0; it0 < T / 8; it0 += U) {
-    float4 a[U], d[U], tg[U];
+  // pass 1: the loads of the next two tile rows are in flight while the current two are converted
+  float4 a[2][U], d[2][U], tg[2][U];
+  auto load = [&](int buf, int b) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int64_t off = (r0 + warp + 8 * (it0 + u)) * src.ld + c;
-      a[u] = __ldcs(reinterpret_cast<const float4*>(src.x + off));
-      if (OP >= 4) d[u] = __ldcs(reinterpret_cast<const float4*>(src.dy + off));
-      if (OP >= 7) tg[u] = __ldcs(reinterpret_cast<const float4*>(src.target + off));
+      const int64_t off = (r0 + warp + 8 * (b * U + u)) * src.ld + c;
+      a[buf][u] = __ldcs(reinterpret_cast<const float4*>(src.x + off));
+      if (HAS_DY) d[buf][u] = __ldcs(reinterpret_cast<const float4*>(src.dy + off));
+      if (HAS_TG) tg[buf][u] = __ldcs(reinterpret_cast<const float4*>(src.target + off));
     }
+  };
+  load(0, 0);
+#pragma unroll
+  for (int b = 0; b < NB; ++b) {
+    const int cur = b & 1;
+    if (b + 1 < NB) load(cur ^ 1, b + 1);
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int tr = warp + 8 * (it0 + u);
+      const int tr = warp + 8 * (b * U + u);
       const int64_t r = r0 + tr;
       float v[4];
-      v[0] = apply_op<OP>(src, a[u].x, OP >= 4 ? d[u].x : 0.f, OP >= 7 ? tg[u].x : 0.f);
-      v[1] = apply_op<OP>(src, a[u].y, OP >= 4 ? d[u].y : 0.f, OP >= 7 ? tg[u].y : 0.f);
-      v[2] = apply_op<OP>(src, a[u].z, OP >= 4 ? d[u].z : 0.f, OP >= 7 ? tg[u].z : 0.f);
-      v[3] = apply_op<OP>(src, a[u].w, OP >= 4 ? d[u].w : 0.f, OP >= 7 ? tg[u].w : 0.f);
-      if (OP != 0 && src.out) __stcs(reinterpret_cast<float4*>(src.out + r * src.ld + c), make_float4(v[0], v[1], v[2], v[3]));
+      v[0] = apply_op<OP>(src, a[cur][u].x, HAS_DY ? d[cur][u].x : 0.f, HAS_TG ? tg[cur][u].x : 0.f);
+      v[1] = apply_op<OP>(src, a[cur][u].y, HAS_DY ? d[cur][u].y : 0.f, HAS_TG ? tg[cur][u].y : 0.f);
+      v[2] = apply_op<OP>(src, a[cur][u].z, HAS_DY ? d[cur][u].z : 0.f, HAS_TG ? tg[cur][u].z : 0.f);
+      v[3] = apply_op<OP>(src, a[cur][u].w, HAS_DY ? d[cur][u].w : 0.f, HAS_TG ? tg[cur][u].w : 0.f);
+      if (OP >= 1 && OP <= 8 && src.out)
+        __stcs(reinterpret_cast<float4*>(src.out + r * src.ld + c), make_float4(v[0], v[1], v[2], v[3]));
       uint32_t m = 0;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const uint32_t b = absbits(v[q]);
-        m = max(m, b);
-        if (COLS) cm[q] = max(cm[q], b);
+        const uint32_t bits = absbits(v[q]);
+        m = max(m, bits);
+        if (COLS) cm[q] = max(cm[q], bits);
       }
-      if (COLS) *reinterpret_cast<float4*>(&stash[tr * STRIDE + lane * 4]) = make_float4(v[0], v[1], v[2], v[3]);
+      if (COLS)
+        *reinterpret_cast<float4*>(&stash[tr * T + ((lane ^ ((tr >> 2) & 7)) << 2)]) = make_float4(v[0], v[1], v[2], v[3]);
       if (ROWS) {
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
@@ -166,24 +209,25 @@ pack_fast_kernel(PackSource src, PackedForm fr, PackedForm fc) {
   for (int q = 0; q < 4; ++q)
     if (cm[q] != 0) atomicMax(&colmax[lane * 4 + q], cm[q]);
   __syncthreads();
-  // 4 column groups x 4 k-groups of 32: two items per warp; a lane owns one column and 32 consecutive k
-  for (int item = warp; item < 16; item += 8) {
-    const int cg = item & 3, kg = item >> 2;
-    const int col = c0 + cg * 32 + lane;
-    const int sh = shift_of(colmax[cg * 32 + lane]);
+  // pass 2: a warp owns 16 columns (four quads); per quad and 32-k group, lane (cc, g) converts k 4g..4g+3 of
+  // column cc of the quad, and the eight lanes of a column write 64 contiguous bytes of h0 and 64 of h1:
+  // whole sectors, four lines per store instruction.
+  const int cc = lane & 3, g = lane >> 2;
+#pragma unroll 1
+  for (int quad = warp * 4; quad < warp * 4 + 4; ++quad) {
+    const int tc = quad * 4 + cc;                    // column inside the tile
+    const int sh = shift_of(colmax[tc]);
     const float scale = pow2f(sh);
-    if (kg == 0) fc.blk[(int64_t)blockIdx.y * fc.rows_ld + col] = pow2f(-sh);
-    __align__(16) __half2 p0[16];
-    __align__(16) __half2 p1[16];
-    const float* col_base = stash + (kg * 32) * STRIDE + cg * 32 + lane;
+    if (g == 0) fc.blk[(int64_t)blockIdx.y * fc.rows_ld + c0 + tc] = pow2f(-sh);
+    const float* sp = stash + (4 * g) * T + (((quad ^ g) << 2) | cc);      // (k >> 2) & 7 == g for k = 32 kg + 4g + i
+    __half* dst = fc.h + (int64_t)(c0 + tc) * fc.pitch + (r0 >> 5) * 64 + 4 * g;
 #pragma unroll
-    for (int j = 0; j < 16; ++j)
-      pieces2(col_base[(2 * j) * STRIDE] * scale, col_base[(2 * j + 1) * STRIDE] * scale, p0[j], p1[j]);
-    __half* dst = fc.h + (int64_t)col * fc.pitch + ((r0 + kg * 32) >> 5) * 64;     // one 128-byte line: h0 | h1
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      reinterpret_cast<uint4*>(dst)[j] = reinterpret_cast<const uint4*>(p0)[j];
-      reinterpret_cast<uint4*>(dst + 32)[j] = reinterpret_cast<const uint4*>(p1)[j];
+    for (int kg = 0; kg < 4; ++kg) {
+      __half2 p0[2], p1[2];
+      pieces2(sp[(kg * 32) * T] * scale, sp[(kg * 32 + 1) * T] * scale, p0[0], p1[0]);
+      pieces2(sp[(kg * 32 + 2) * T] * scale, sp[(kg * 32 + 3) * T] * scale, p0[1], p1[1]);
+      *reinterpret_cast<uint2*>(dst + kg * 64) = *reinterpret_cast<const uint2*>(p0);
+      *reinterpret_cast<uint2*>(dst + kg * 64 + 32) = *reinterpret_cast<const uint2*>(p1);
     }
   }
 }
@@ -191,7 +235,7 @@ pack_fast_kernel(PackSource src, PackedForm fr, PackedForm fc) {
 template <int OP, bool ROWS, bool COLS>
 static prad_status launch_fast(prad_ctx* ctx, const PackSource& src, int tiles_r, int tiles_c, const PackedForm& fr,
                                const PackedForm& fc) {
-  const int smem = COLS ? 128 * 132 * (int)sizeof(float) : 0;
+  const int smem = COLS ? 128 * 128 * (int)sizeof(float) : 0;
   if (COLS) {
     static std::atomic<uint64_t> done{0};
     const uint64_t bit = 1ull << (ctx->device & 63);
@@ -220,6 +264,7 @@ static prad_status launch_fast_forms(prad_ctx* ctx, const PackSource& src, int t
 static int fast_op_of(const PackSource& s) {
   if (s.kind == 0) return 0;
   const bool gelu = s.act == PRAD_ACT_GELU, leaky = s.act == PRAD_ACT_LEAKY_RELU;
+  if (gelu && !s.out) return s.kind == 1 ? 9 : (s.kind == 2 ? 10 : 11);
   if (s.kind == 1) return gelu ? 1 : (leaky ? 2 : 3);
   if (s.kind == 2) return gelu ? 4 : (leaky ? 5 : 6);
   return gelu ? 7 : 8;
@@ -400,7 +445,10 @@ prad_status pack_fp16(prad_ctx* ctx, const PackSource& src, int R, int C, const 
       case 5: s = pk::launch_fast_forms<5>(ctx, src, fr_t, fc_t, fr, fc); break;
       case 6: s = pk::launch_fast_forms<6>(ctx, src, fr_t, fc_t, fr, fc); break;
       case 7: s = pk::launch_fast_forms<7>(ctx, src, fr_t, fc_t, fr, fc); break;
-      default: s = pk::launch_fast_forms<8>(ctx, src, fr_t, fc_t, fr, fc); break;
+      case 8: s = pk::launch_fast_forms<8>(ctx, src, fr_t, fc_t, fr, fc); break;
+      case 9: s = pk::launch_fast_forms<9>(ctx, src, fr_t, fc_t, fr, fc); break;
+      case 10: s = pk::launch_fast_forms<10>(ctx, src, fr_t, fc_t, fr, fc); break;
+      default: s = pk::launch_fast_forms<11>(ctx, src, fr_t, fc_t, fr, fc); break;
     }
     if (s) return s;
   }

@@ -48,6 +48,34 @@ softmax_forward_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows,
   }
 }
 
+// SineSoftmaxOperation.cs:47-77,155-176: e = exp(sin x), M = sum of e over the row, y_j = e_j / (M + e_j);
+// Backward as written there: dx_j = dy_j * (M * e_j * cos x_j) / (M + e_j)^2.  One warp per row; the
+// float overloads of PradMath go through double, so do these.
+template <typename T> __device__ __forceinline__ T sine_exp(T x) { return (T)exp((double)(T)sin((double)x)); }
+template <typename T, bool BACKWARD>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+sine_softmax_kernel(const T* __restrict__ x, const T* __restrict__ dy, T* __restrict__ out, int64_t rows, int cols) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * ROW_WARPS;
+  for (int64_t r = warp; r < rows; r += nwarps) {
+    const T* xr = x + r * cols;
+    T m = 0;
+    for (int j = lane; j < cols; j += 32) m += sine_exp<T>(xr[j]);
+    m = warp_sum(m);
+    for (int j = lane; j < cols; j += 32) {
+      const T e = sine_exp<T>(xr[j]);
+      if (!BACKWARD) {
+        out[r * cols + j] = div_rn(e, add_rn(m, e));
+      } else {
+        const T num = mul_rn(mul_rn(m, e), (T)cos((double)xr[j]));
+        const T s = add_rn(m, e);
+        out[r * cols + j] = mul_rn(dy[r * cols + j], div_rn(num, mul_rn(s, s)));
+      }
+    }
+  }
+}
+
 // SoftmaxOperation.cs:53-83.  The reference walks the explicit Jacobian; algebraically
 //   dx_j = dy_j*y_j*(1-y_j) - y_j*sum_{k!=j} dy_k*y_k = y_j*(dy_j - sum_k dy_k*y_k).
 template <typename T>
@@ -494,6 +522,29 @@ static inline int row_grid(const prad_ctx* ctx, int64_t rows) {
 using namespace prad;
 
 extern "C" {
+
+prad_status prad_sine_softmax_forward(prad_ctx* ctx, prad_dtype dt, const void* x, void* y, int64_t rows, int cols) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0, PRAD_ERR_INVALID, "prad_sine_softmax_forward: bad argument");
+  if (rows == 0 || cols == 0) return PRAD_OK;
+  PRAD_REQUIRE(x && y, PRAD_ERR_INVALID, "prad_sine_softmax_forward: null pointer");
+  if (dt == PRAD_F32) sine_softmax_kernel<float, false><<<row_grid(ctx, rows), ROW_WARPS * 32, 0, ctx->stream>>>((const float*)x, nullptr, (float*)y, rows, cols);
+  else sine_softmax_kernel<double, false><<<row_grid(ctx, rows), ROW_WARPS * 32, 0, ctx->stream>>>((const double*)x, nullptr, (double*)y, rows, cols);
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
+
+prad_status prad_sine_softmax_backward(prad_ctx* ctx, prad_dtype dt, const void* x, const void* dy, void* dx, int64_t rows,
+                                       int cols) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_REQUIRE(dtype_ok(dt) && rows >= 0 && cols >= 0, PRAD_ERR_INVALID, "prad_sine_softmax_backward: bad argument");
+  if (rows == 0 || cols == 0) return PRAD_OK;
+  PRAD_REQUIRE(x && dy && dx, PRAD_ERR_INVALID, "prad_sine_softmax_backward: null pointer");
+  if (dt == PRAD_F32) sine_softmax_kernel<float, true><<<row_grid(ctx, rows), ROW_WARPS * 32, 0, ctx->stream>>>((const float*)x, (const float*)dy, (float*)dx, rows, cols);
+  else sine_softmax_kernel<double, true><<<row_grid(ctx, rows), ROW_WARPS * 32, 0, ctx->stream>>>((const double*)x, (const double*)dy, (double*)dx, rows, cols);
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
 
 prad_status prad_softmax_forward(prad_ctx* ctx, prad_dtype dt, const void* x, void* y,
                                  int64_t rows, int cols) {

@@ -533,6 +533,20 @@ class Engine:
                                              y.size // y.shape[-1], y.shape[-1]))
         return out
 
+    def sine_softmax_forward(self, x, out=None):
+        """SineSoftmaxOperation.Forward: e / (sum e + e) with e = exp(sin x), row by row."""
+        out = out or self.empty(x.shape, x.dtype)
+        check(self.lib.prad_sine_softmax_forward(self.ctx, dtype_code(x.dtype), x.ptr, out.ptr,
+                                                 x.size // x.shape[-1], x.shape[-1]))
+        return out
+
+    def sine_softmax_backward(self, x, dy, out=None):
+        """SineSoftmaxOperation.Backward; `x` is the operation's input."""
+        out = out or self.empty(x.shape, x.dtype)
+        check(self.lib.prad_sine_softmax_backward(self.ctx, dtype_code(x.dtype), x.ptr, dy.ptr, out.ptr,
+                                                  x.size // x.shape[-1], x.shape[-1]))
+        return out
+
     def layernorm_forward(self, x, out=None):
         rows = x.size // x.shape[-1]
         if out is not None:

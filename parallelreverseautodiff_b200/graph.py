@@ -20,7 +20,7 @@ OPS = {
     "MatrixAddBroadcastingOperation": 3, "HadamardProductOperation": 4, "LeakyReLUOperation": 5,
     "SigmoidOperation": 6, "TanhOperation": 7, "GELUOperation": 8, "SoftmaxOperation": 9,
     "LayerNormalizationOperation": 10, "MatrixMultiplyScalarOperation": 11, "MatrixTransposeOperation": 12,
-    "ReLUOperation": 13, "AmplifiedSigmoidOperation": 14,
+    "ReLUOperation": 13, "AmplifiedSigmoidOperation": 14, "SineSoftmaxOperation": 15,
 }
 
 

@@ -42,54 +42,62 @@ def feedforward_architecture(matmul="GpuMatrixMultiplyOperation"):
     return {"timeSteps": [{"startOperations": start, "layers": [{"operations": layer}], "endOperations": end}]}
 
 
-def lstm_architecture():
-    """examples/lstm/ParallelReverseAutoDiff.LstmExample/architecture/SelfAttentionMultiLayerLSTMArchitectureAmplified.json"""
-    mm, tr, ln = "MatrixMultiplyOperation", "MatrixTransposeOperation", "LayerNormalizationOperation"
-    start = [_op("projectedInput", mm, ["We", "inputSequence[t]"], ["dWe", None]),
-             _op("embeddedInput", "MatrixAddOperation", ["projectedInput", "be"], [None, "dbe"])]
+def lstm_architecture(batch=False):
+    """examples/lstm/ParallelReverseAutoDiff.LstmExample/architecture/SelfAttentionMultiLayerLSTMArchitectureAmplified.json,
+    or with batch=True its DeepMatrix twin
+    test/ParallelReverseAutoDiff.Test/GraphAttentionPaths/LSTM/Architecture/NodeProcessing.json: every operation
+    is the Batch* one, the products are BatchGpuMatrixMultiplyOperation, the attention weights come from
+    BatchSineSoftmaxOperation, c and h are not copied out, and the output is a LeakyReLU."""
+    pre = "Batch" if batch else ""
+    mm = "BatchGpuMatrixMultiplyOperation" if batch else "MatrixMultiplyOperation"
+    tr, ln = pre + "MatrixTransposeOperation", pre + "LayerNormalizationOperation"
+    add, add3, had = pre + "MatrixAddOperation", pre + "MatrixAddThreeOperation", pre + "HadamardProductOperation"
+    start = [_op("projectedInput", mm, ["We", "InputNodeFeatures[t]" if batch else "inputSequence[t]"], ["dWe", None]),
+             _op("embeddedInput", add, ["projectedInput", "be"], [None, "dbe"])]
     ops = []
 
     def gate(name, w, act, normalized=True):
         ops.append(_op(f"w{w}_currentInput", mm, [f"W{w}[layerIndex]", "currentInput"], [f"dW{w}[layerIndex]", None]))
         ops.append(_op(f"u{w}_previousHiddenState", mm, [f"U{w}[layerIndex]", "previousHiddenState"], [f"dU{w}[layerIndex]", None]))
-        ops.append(_op(f"{name}_add", "MatrixAddThreeOperation",
+        ops.append(_op(f"{name}_add", add3,
                        [f"w{w}_currentInput", f"u{w}_previousHiddenState", f"b{w}[layerIndex]"], [None, None, f"db{w}[layerIndex]"]))
         last = f"{name}_add"
         if normalized:
-            ops.append(_op(f"intermediate_{name}_1", tr, [last]))
+            ops.append(_op(f"intermediate_{name}_1", tr, [f"{name}_add"]))
             ops.append(_op(f"intermediate_{name}_2", ln, [f"intermediate_{name}_1"]))
             ops.append(_op(f"intermediate_{name}_3", tr, [f"intermediate_{name}_2"]))
             last = f"intermediate_{name}_3"
-        ops.append(_op(name, act, [last]))
+        ops.append(_op(name, pre + act, [last]))
 
     gate("f", "f", "AmplifiedSigmoidOperation")
     gate("i", "i", "AmplifiedSigmoidOperation")
     gate("cHat", "c", "TanhOperation")
-    ops += [_op("f_previousMemoryCellState", "HadamardProductOperation", ["f[t][layerIndex]", "previousMemoryCellState"]),
-            _op("i_cHat", "HadamardProductOperation", ["i[t][layerIndex]", "cHat[t][layerIndex]"]),
-            _op("newC", "MatrixAddOperation", ["f_previousMemoryCellState", "i_cHat"]),
+    ops += [_op("f_previousMemoryCellState", had, ["f[t][layerIndex]", "previousMemoryCellState"]),
+            _op("i_cHat", had, ["i[t][layerIndex]", "cHat[t][layerIndex]"]),
+            _op("newC", add, ["f_previousMemoryCellState", "i_cHat"]),
             _op("newCTransposed", tr, ["newC"]),
             _op("newCNormalized", ln, ["newCTransposed"]),
-            _op("c", tr, ["newCNormalized"], result="c[t][layerIndex]")]
+            _op("c", tr, ["newCNormalized"], result=None if batch else "c[t][layerIndex]")]
     gate("o", "o", "LeakyReLUOperation", normalized=False)
-    ops += [_op("c_tanh", "TanhOperation", ["c"]),
-            _op("newH", "HadamardProductOperation", ["o[t][layerIndex]", "c_tanh"]),
+    ops += [_op("c_tanh", pre + "TanhOperation", ["c"]),
+            _op("newH", had, ["o[t][layerIndex]", "c_tanh"]),
             _op("keys", mm, ["Wk[layerIndex]", "embeddedInput"], ["dWk[layerIndex]", None]),
             _op("queries", mm, ["Wq[layerIndex]", "previousHiddenState"], ["dWq[layerIndex]", None]),
             _op("values", mm, ["Wv[layerIndex]", "embeddedInput"], ["dWv[layerIndex]", None]),
             _op("queriesTranspose", tr, ["queries"]),
             _op("dotProduct", mm, ["keys", "queriesTranspose"]),
-            _op("scaledDotProduct", "MatrixMultiplyScalarOperation", ["dotProduct", "scaledDotProductScalar"]),
+            _op("scaledDotProduct", pre + "MatrixMultiplyScalarOperation", ["dotProduct", "scaledDotProductScalar"]),
             _op("scaledDotProductTranspose", tr, ["scaledDotProduct"]),
-            _op("attentionWeights", "SoftmaxOperation", ["scaledDotProductTranspose"]),
+            _op("attentionWeights", "BatchSineSoftmaxOperation" if batch else "SoftmaxOperation", ["scaledDotProductTranspose"]),
             _op("attentionOutput", mm, ["attentionWeights", "values"]),
-            _op("newHWithAttentionOutput", "MatrixAddOperation", ["newH", "attentionOutput"]),
+            _op("newHWithAttentionOutput", add, ["newH", "attentionOutput"]),
             _op("newHWithAttentionOutputTranspose", tr, ["newHWithAttentionOutput"]),
             _op("normalizedNewH", ln, ["newHWithAttentionOutputTranspose"]),
-            _op("h", tr, ["normalizedNewH"], result="h[t][layerIndex]")]
+            _op("h", tr, ["normalizedNewH"], result=None if batch else "h[t][layerIndex]")]
     end = [_op("v_h", mm, ["V", "hFromCurrentTimeStepAndLastLayer"], ["dV", None]),
-           _op("v_h_b", "MatrixAddOperation", ["v_h", "b"], [None, "db"]),
-           _op("output_t", "AmplifiedSigmoidOperation", ["v_h_b"], result="output[t]")]
+           _op("v_h_b", add, ["v_h", "b"], [None, "db"]),
+           _op("output_t", "BatchLeakyReLUOperation" if batch else "AmplifiedSigmoidOperation", ["v_h_b"],
+               result="OutputPathFeatures[t]" if batch else "output[t]")]
     return {"timeSteps": [{"startOperations": start, "layers": [{"operations": ops}], "endOperations": end}]}
 
 
@@ -156,6 +164,7 @@ class OracleInterpreter:
         if t == "HadamardProductOperation": return O.hadamard_forward(x[0], x[1])
         if t == "MatrixMultiplyScalarOperation": return O.scale(x[0], x[1])
         if t == "SoftmaxOperation": return O.softmax_forward(x[0])
+        if t == "SineSoftmaxOperation": return O.sine_softmax_forward(x[0])
         raise KeyError(t)
 
     def _bwd_one(self, t, x, y, d, slot):
@@ -171,6 +180,7 @@ class OracleInterpreter:
         if t == "HadamardProductOperation": return list(O.hadamard_backward(x[0], x[1], d))
         if t == "MatrixMultiplyScalarOperation": return [O.scale(d, x[1])]
         if t == "SoftmaxOperation": return [O.softmax_backward(y, d)]
+        if t == "SineSoftmaxOperation": return [O.sine_softmax_backward(x[0], d)]
         raise KeyError(t)
 
     @staticmethod

@@ -19,6 +19,8 @@ FILES = {
         lambda: A.feedforward_architecture("GpuMatrixMultiplyOperation"),
     "examples/lstm/ParallelReverseAutoDiff.LstmExample/architecture/SelfAttentionMultiLayerLSTMArchitectureAmplified.json":
         A.lstm_architecture,
+    "test/ParallelReverseAutoDiff.Test/GraphAttentionPaths/LSTM/Architecture/NodeProcessing.json":
+        lambda: A.lstm_architecture(batch=True),
 }
 
 

@@ -100,39 +100,50 @@ def test_lstm_example_architecture_file(engine, one_walk):
     """SelfAttentionMultiLayerLSTM: T time steps x L layers unrolled by ConstructFromArchitecture(arch, T, L), with
     the registrations of examples/lstm/.../SelfAttentionMultiLayerLSTM.cs:295-328; shared weights accumulate
     over time steps; fan-out at h, c, the embedded input, the attention sources."""
+    _lstm_architecture_case(engine, one_walk, depth=0)
+
+
+def test_node_processing_architecture_file(engine):
+    """test/.../GraphAttentionPaths/LSTM/Architecture/NodeProcessing.json: the same network on DeepMatrix values
+    (one slice per sample) with Batch* operations, BatchGpuMatrixMultiplyOperation(Matrix, DeepMatrix) products
+    whose weights are shared by the slices (their gradient is the mean over the slices), and
+    BatchSineSoftmaxOperation attention weights."""
+    _lstm_architecture_case(engine, True, depth=3)
+
+
+def _lstm_architecture_case(engine, one_walk, depth):
     dtype = np.float64
     r = rng(8)
     T, L, n_in, nh, n_out, B = 3, 2, 6, 8, 5, 2
+    batch = depth > 0
     mk = lambda *s: r.standard_normal(s) * 0.4
-    names_l, shapes = [], {}
+    deep = (lambda *s: mk(depth, *s)) if batch else mk          # per-sample values
+    names_l = []
     for w in "fico":
         names_l += [f"W{w}", f"U{w}", f"b{w}"]
     names_l += ["Wq", "Wk", "Wv"]
 
     def shape_of(name, l):
-        if name.startswith("b"):
-            return (nh, B)
-        if name[0] == "U" or name == "Wq":
-            return (nh, nh)
-        if name in ("Wk", "Wv"):
-            return (nh, nh)                      # they multiply the embedded input (hidden-sized here)
-        return (nh, nh)                          # W*: current input is the embedding (layer 0) or h of the layer below
+        return (nh, B) if name.startswith("b") else (nh, nh)
 
     layer_p = [_both(engine, {n: mk(*shape_of(n, l)) for n in names_l}) for l in range(L)]
     layer_g = [_both(engine, {"d" + n: np.zeros(shape_of(n, l)) for n in names_l}) for l in range(L)]
     glob_p = _both(engine, dict(We=mk(nh, n_in), be=mk(nh, B), V=mk(n_out, nh), b=mk(n_out, B)))
     glob_g = _both(engine, dict(dWe=np.zeros((nh, n_in)), dbe=np.zeros((nh, B)), dV=np.zeros((n_out, nh)), db=np.zeros((n_out, B))))
-    xs = [mk(n_in, B) for _ in range(T)]
+    xs = [deep(n_in, B) for _ in range(T)]
     xs_dev = [engine.upload(x) for x in xs]
-    zero_h = engine.zeros((nh, B), dtype)
-    zero_np = np.zeros((nh, B))
-    out_dev = [engine.zeros((n_out, B), dtype) for _ in range(T)]
+    lead = (depth,) if batch else ()
+    zero_h = engine.zeros(lead + (nh, B), dtype)
+    zero_np = np.zeros(lead + (nh, B))
+    out_dev = [engine.zeros(lead + (n_out, B), dtype) for _ in range(T)]
     c_dev = [[engine.zeros((nh, B), dtype) for _ in range(L)] for _ in range(T)]
     h_dev = [[engine.zeros((nh, B), dtype) for _ in range(L)] for _ in range(T)]
     scalar = 1.0 / np.sqrt(nh)
+    in_name, out_name = ("InputNodeFeatures", "OutputPathFeatures") if batch else ("inputSequence", "output")
+    arch = A.lstm_architecture(batch=batch)
 
     g = ArchitectureGraph(engine, dtype, leaky_relu_alpha=0.01)
-    g.AddIntermediate("inputSequence", lambda x: xs_dev[x.TimeStep]).AddIntermediate("output", lambda x: out_dev[x.TimeStep])
+    g.AddIntermediate(in_name, lambda x: xs_dev[x.TimeStep]).AddIntermediate(out_name, lambda x: out_dev[x.TimeStep])
     g.AddIntermediate("c", lambda x: c_dev[x.TimeStep][x.Layer]).AddIntermediate("h", lambda x: h_dev[x.TimeStep][x.Layer])
     g.AddScalar("scaledDotProductScalar", lambda x: scalar)
     for n in names_l:
@@ -146,12 +157,12 @@ def test_lstm_example_architecture_file(engine, one_walk):
     g.AddOperationFinder("currentInput", lambda x: g[f"embeddedInput_{x.TimeStep}_0"] if x.Layer == 0 else g[f"h_{x.TimeStep}_{x.Layer - 1}"])
     g.AddOperationFinder("previousHiddenState", lambda x: zero_h if x.TimeStep == 0 else g[f"h_{x.TimeStep - 1}_{x.Layer}"])
     g.AddOperationFinder("previousMemoryCellState", lambda x: zero_h if x.TimeStep == 0 else g[f"c_{x.TimeStep - 1}_{x.Layer}"])
-    g.ConstructFromArchitecture(A.lstm_architecture(), L, T)
+    g.ConstructFromArchitecture(arch, L, T)
     assert len(g.order) == T * (2 + 46 * L + 3)
 
     leaves = {n: (lambda t, l, n=n: layer_p[l][n][0]) for n in names_l}
     leaves.update({n: (lambda t, l, n=n: glob_p[n][0]) for n in glob_p})
-    leaves.update(inputSequence=lambda t, l: xs[t], scaledDotProductScalar=lambda t, l: scalar,
+    leaves.update({in_name: lambda t, l: xs[t]}, scaledDotProductScalar=lambda t, l: scalar,
                   embeddedInput=lambda t, l: ("op", f"embeddedInput_{t}_0"),
                   hFromCurrentTimeStepAndLastLayer=lambda t, l: ("op", f"h_{t}_{L - 1}"),
                   currentInput=lambda t, l: ("op", f"embeddedInput_{t}_0" if l == 0 else f"h_{t}_{l - 1}"),
@@ -161,16 +172,18 @@ def test_lstm_example_architecture_file(engine, one_walk):
         leaves[n] = lambda t, l, n=n: ("op", f"{n}_{t}_{l}")
     grads = {"d" + n: (lambda t, l, n=n: layer_g[l]["d" + n][0]) for n in names_l}
     grads.update({"d" + n: (lambda t, l, n=n: glob_g["d" + n][0]) for n in glob_p})
-    it = A.OracleInterpreter(A.lstm_architecture(), leaves, grads, L, T)
+    it = A.OracleInterpreter(arch, leaves, grads, L, T)
 
     g.forward()
     it.forward()
+    what = "node processing" if batch else "lstm architecture"
     for t in range(T):
         ref = it.by_id[f"output_t_{t}_0"]["out"]
-        assert_close(out_dev[t].numpy(), ref, 1.0, "lstm architecture output[t]")
+        assert_close(out_dev[t].numpy(), ref, 1.0, f"{what} output[t]")
         for l in range(L):
-            assert_close(h_dev[t][l].numpy(), it.by_id[f"h_{t}_{l}"]["out"], 10.0, "lstm architecture h[t][l]")
-    ups = [mk(n_out, B) for _ in range(T)]
+            got = g.output(f"h_{t}_{l}") if batch else h_dev[t][l]       # the batch file copies neither c nor h out
+            assert_close(got.numpy(), it.by_id[f"h_{t}_{l}"]["out"], 10.0, f"{what} h[t][l]")
+    ups = [deep(n_out, B) for _ in range(T)]
     starts = [f"output_t_{t}_0" for t in range(T)]
     if one_walk:
         g.backward(starts, [engine.upload(u) for u in ups])
@@ -181,10 +194,10 @@ def test_lstm_example_architecture_file(engine, one_walk):
     for l in range(L):
         for n in names_l:
             ref = layer_g[l]["d" + n][0]
-            assert_close(layer_g[l]["d" + n][1].numpy(), ref, 100 * rms(ref) + 1e-6, f"lstm architecture d{n}[{l}]")
+            assert_close(layer_g[l]["d" + n][1].numpy(), ref, 100 * rms(ref) + 1e-6, f"{what} d{n}[{l}]")
     for n in glob_p:
         ref = glob_g["d" + n][0]
-        assert_close(glob_g["d" + n][1].numpy(), ref, 100 * rms(ref) + 1e-6, f"lstm architecture d{n}")
+        assert_close(glob_g["d" + n][1].numpy(), ref, 100 * rms(ref) + 1e-6, f"{what} d{n}")
     if one_walk:
         # h of a time step feeds the four gates and the attention queries of the next, the layer above and the output
         assert g.dependency_count("h_0_0") >= 5 and g.dependency_count("embeddedInput_0_0") >= 3

@@ -233,6 +233,20 @@ def test_add_broadcast(engine, dtype, shape):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(1, 1), (6, 120), (300, 17), (5, 1000), (2, 4099)])
+def test_sine_softmax(engine, dtype, shape):
+    """SineSoftmaxOperation: y = e / (sum e + e), e = exp(sin x); Backward reads the input."""
+    r = rng(shape[1])
+    x, dy = normal(r, shape, 2.0, dtype), normal(r, shape, 1.0, dtype)
+    y_ref = O.sine_softmax_forward(x)
+    y = engine.sine_softmax_forward(engine.upload(x))
+    assert_close(y.numpy(), y_ref, 0.0, "sine softmax")
+    dx = engine.sine_softmax_backward(engine.upload(x), engine.upload(dy))
+    assert_close(dx.numpy(), O.sine_softmax_backward(x, dy), 0.0, "sine softmax backward")
+    assert engine.sine_softmax_forward(engine.empty((0, 5), dtype)).shape == (0, 5)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("shape", [(1, 1), (256, 10), (49 * 12, 49), (7, 1000), (3, 4097)])
 def test_softmax(engine, dtype, shape):
     r = rng(shape[0])

@@ -76,6 +76,32 @@ def test_reference_matmul_relation_1e10():
     np.testing.assert_array_equal(np.round(dB, 10), np.round(A.T @ C, 10))
 
 
+# --- test/ParallelReverseAutoDiff.Test/SineSoftmaxTest.cs:8-24: on Xavier-initialised i x i inputs the rows of
+# SineSoftmaxOperation.Forward add up to more than 0.8 on average (Matrix.InitializeXavier: uniform in
+# +-sqrt(6 / (rows + cols))); a sample of the sizes 5..999 the reference walks.
+@pytest.mark.parametrize("dtype", [np.float64, np.float32])
+def test_reference_sine_softmax_rows_add_up_to_more_than_point_eight(dtype):
+    r = rng(77)
+    for n in (5, 6, 17, 64, 333, 999):
+        lim = np.sqrt(6.0 / (2 * n))
+        x = ((r.random((n, n)) * 2 - 1) * lim).astype(dtype)
+        y = O.sine_softmax_forward(x)
+        assert y.sum(1).mean() > 0.8
+        # the definition, element by element
+        e = np.exp(np.sin(x.astype(np.float64)))
+        np.testing.assert_allclose(y, e / (e.sum(1, keepdims=True) + e), rtol=1e-5 if dtype == np.float32 else 1e-13)
+
+
+def test_sine_softmax_backward_is_the_reference_formula():
+    # SineSoftmaxOperation.cs:155-176: dx = dy * M e cos(x) / (M + e)^2, which is the derivative of e / (M + e)
+    # with M held constant (not the full Jacobian)
+    r = rng(3)
+    x, dy = r.standard_normal((6, 120)), r.standard_normal((6, 120))
+    e = np.exp(np.sin(x))
+    m = e.sum(1, keepdims=True)
+    np.testing.assert_allclose(O.sine_softmax_backward(x, dy), dy * m * e * np.cos(x) / (m + e) ** 2, rtol=1e-13)
+
+
 def test_float_products_are_not_fused():
     # a*b+c with one rounding would give 1 + 2^-24... the managed code rounds twice
     a = np.array([[1 + 2.0 ** -12]], np.float32)
