@@ -417,6 +417,11 @@ def run_native(args, rank, world, local_rank):
             "roofline": {"bound": "tensor", "achieved": achieved_tflops, "peak": peaks["tensor_tflops"],
                          "unit": "TFLOP/s",
                          "frac": (achieved_tflops / peaks["tensor_tflops"]) if achieved_tflops else None,
+                         # an FP32-faithful product costs three FP16 tensor-core products (two-piece operands):
+                         # the tensor pipe's own share of the measured dense peak is three times `frac`
+                         "tensor_products_per_flop": 3 if args.gemm in ("auto", "fp16x3") else None,
+                         "tensor_pipe_frac": (3 * achieved_tflops / peaks["tensor_tflops"])
+                         if achieved_tflops and args.gemm in ("auto", "fp16x3") else None,
                          "traffic": gemm_traffic_bytes(rows, args.width, args.gemm),
                          "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one "
                                            "16384 x 4096 x 4096 launch of the default kernel (1.170 GB), scaled by rows",

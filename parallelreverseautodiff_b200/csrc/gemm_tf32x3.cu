@@ -162,7 +162,20 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
       : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+      : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// the same wait, naming the registers of the load it completes: whatever reads them is ordered after it even
+// while a later load into other registers is still in flight
+__device__ __forceinline__ void tmem_ld_wait8(uint32_t (&v)[8]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7])
+               :: "memory");
+}
 
 // Shared-memory matrix descriptor of a K-major tile stored as rows of SW bytes (SW = 128, 64
 // or 32) with the SW-byte swizzle, i.e. what TMA writes with CU_TENSOR_MAP_SWIZZLE_{SW}B:
@@ -615,7 +628,8 @@ constexpr int BK = 32;
 constexpr int UNITS = 4;
 constexpr int UNIT_BYTES = 48 * 1024;
 constexpr int CHUNK_KB = CHUNK_K / BK;
-constexpr int SMEM_BYTES = UNITS * UNIT_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int SCALE_BYTES = EPI_WARPS * 128 * 4;   // PMODE 3: each epilogue warp's copy of its 128 column scales of a block
+constexpr int SMEM_BYTES = UNITS * UNIT_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + SCALE_BYTES;
 static_assert(SMEM_BYTES <= 227 * 1024, "unit ring does not fit in shared memory");
 }  // namespace p1
 
@@ -847,35 +861,52 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
       // packed FP16 operands: block c of this slice is block kb0 / chunk_kb + c of the operands
       const int chunk0 = kb0 / ts.chunk_kb;
       const int row_blk = min(m0 + sub * 32 + lane, M - 1);     // rows beyond M are never stored
+      // PMODE 3: the scales of the next block are fetched while the current one is summed -- this thread's row
+      // scale into a register, the 128 column scales one float4 per lane; at the start of a block the lanes
+      // put theirs into the warp's slot of shared memory, from where every lane reads all of them (broadcast)
+      float sa_next = 0.f;
+      float4 sb_next = make_float4(0.f, 0.f, 0.f, 0.f);
+      float4* const sb_slot = reinterpret_cast<float4*>(generic_base + UNITS * UNIT_BYTES + 256) + (warp - 2) * 32;
+      auto fetch_scales = [&](int ch) {
+        sa_next = __ldg(epi.blk_a + (int64_t)(chunk0 + ch) * epi.blk_lda + row_blk);
+        sb_next = __ldg(reinterpret_cast<const float4*>(epi.blk_b + (int64_t)(chunk0 + ch) * epi.blk_ldb + n0 + half * 128) + lane);
+      };
+      if (PMODE == 3) fetch_scales(0);
       for (int ch = 0; ch < num_chunks; ++ch, ++gc) {
         const uint32_t buf = gc & 1;
-        // this thread's row scale and the 128 column scales of the block, fetched before the wait
         float sa = 0.f;
-        const float4* sbp = nullptr;
         if (PMODE == 3) {
-          sa = epi.blk_a[(int64_t)(chunk0 + ch) * epi.blk_lda + row_blk];
-          sbp = reinterpret_cast<const float4*>(epi.blk_b + (int64_t)(chunk0 + ch) * epi.blk_ldb + n0 + half * 128);
+          sa = sa_next;
+          sb_slot[lane] = sb_next;      // the previous block's readers passed the __syncwarp at its end
+          __syncwarp();
+          if (ch + 1 < num_chunks) fetch_scales(ch + 1);
         }
         ok = __all_sync(0xffffffffu, mbar_wait(acc_full(buf), (gc >> 1) & 1, err_flag, 3));
         if (!ok) break;
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + buf * (uint32_t)BN + (uint32_t)(half * 128);
         if (PMODE == 3) {
-          // 16 columns per load keep the live registers (128 running sums + one load) inside the budget
+          // eight columns per load, the next load in flight while the current eight are added: the live
+          // registers stay at 128 running sums + two loads
+          const float2 sa2 = make_float2(sa, sa);
+          uint32_t v[2][8];
+          tmem_ld8(taddr, v[0]);
 #pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            uint32_t v[16];
-            tmem_ld16(taddr + (uint32_t)(g * 16), v);
-            tmem_ld_wait();
+          for (int g = 0; g < 16; ++g) {
+            uint32_t (&cur)[8] = v[g & 1];
+            tmem_ld_wait8(cur);
+            if (g + 1 < 16) tmem_ld8(taddr + (uint32_t)((g + 1) * 8), v[(g + 1) & 1]);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {     // the same address in every lane: one broadcast load each
-              const float4 t = __ldg(sbp + g * 4 + q);
-              float* acc = &sum[g >> 1][(g & 1) * 16 + 4 * q];
-              // sum += (partial * 2^e_a) * 2^e_b: the first product is exact, the sum is rounded once
-              acc[0] = __fmaf_rn(__fmul_rn(__uint_as_float(v[4 * q]), sa), t.x, acc[0]);
-              acc[1] = __fmaf_rn(__fmul_rn(__uint_as_float(v[4 * q + 1]), sa), t.y, acc[1]);
-              acc[2] = __fmaf_rn(__fmul_rn(__uint_as_float(v[4 * q + 2]), sa), t.z, acc[2]);
-              acc[3] = __fmaf_rn(__fmul_rn(__uint_as_float(v[4 * q + 3]), sa), t.w, acc[3]);
+            for (int q = 0; q < 2; ++q) {
+              const float4 t = sb_slot[g * 2 + q];
+              float* acc = &sum[g >> 2][(g & 3) * 8 + 4 * q];
+              // sum += (partial * 2^e_a) * 2^e_b: the first product is exact, the sum is rounded once;
+              // two columns per instruction (packed FP32)
+              const float2 p01 = __fmul2_rn(make_float2(__uint_as_float(cur[4 * q]), __uint_as_float(cur[4 * q + 1])), sa2);
+              const float2 p23 = __fmul2_rn(make_float2(__uint_as_float(cur[4 * q + 2]), __uint_as_float(cur[4 * q + 3])), sa2);
+              const float2 r01 = __ffma2_rn(p01, make_float2(t.x, t.y), make_float2(acc[0], acc[1]));
+              const float2 r23 = __ffma2_rn(p23, make_float2(t.z, t.w), make_float2(acc[2], acc[3]));
+              acc[0] = r01.x; acc[1] = r01.y; acc[2] = r23.x; acc[3] = r23.y;
             }
           }
         } else {
