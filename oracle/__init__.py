@@ -5,9 +5,12 @@ reference's C# backward loops that the CUDA library is checked against and that 
 benchmark times as its CPU baseline.  Only ``tests/``, ``__graft_entry__.smoke()`` and the
 ``cpu_baseline`` / ``--impl reference`` legs of ``bench.py`` may import this package.
 
-Parity status: pinned only by the reference's own known-answer tests (gather/scatter
-vectors, LayerNorm dual-number relation, matmul GPU==CPU relation); everything else is
-"parity unpinned" because the C# reference cannot be executed where this is built.
+Parity status: pinned by the known-answer and relational tests the reference itself holds
+for this path (the Tensor / TensorReverse vectors for the elementwise family, gather, tile,
+sum-rows, transpose and matrix-multiply reverses; the LayerNorm dual-number relation; the
+matmul GPU == CPU relation; the SineSoftmax row-sum property) -- tests/test_oracle_pins.py.
+Values no reference test holds (activations, softmax, losses, clip, Adam) follow the cited
+lines only: "parity unpinned", because the C# reference cannot be executed where this is built.
 """
 from __future__ import annotations
 

@@ -9,7 +9,7 @@
 // built (no .NET runtime), so this restatement is pinned only by the few
 // known-answer / relational tests the reference itself holds for this path
 // (exact gather/scatter vectors, the LayerNorm dual-number relation at 1e-9, the
-// GPU==CPU matmul relation at 1e-10).  Activations, softmax, losses, clip and Adam
+// GPU==CPU matmul relation at 1e-10, the SineSoftmax row-sum property).  Activations, softmax, losses, clip and Adam
 // are PARITY UNPINNED: they follow the cited source lines, nothing more.
 //
 // Restatement rules (they decide bits):

@@ -32,5 +32,5 @@ def pytest_terminal_summary(terminalreporter):
     if not rows:
         return
     terminalreporter.write_line("tolerance used (max err / limit) per comparison:")
-    for k, v in sorted(rows, key=lambda kv: -kv[1])[:60]:
+    for k, v in sorted(rows, key=lambda kv: -kv[1]):
         terminalreporter.write_line(f"  {v:8.4f}  {k}")

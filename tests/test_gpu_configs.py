@@ -107,13 +107,13 @@ def test_c3_lstm_double_bptt(engine, shape):
     net = LstmNetwork(engine, np.float64, n_in, nh, T, B)
     net.set_parameters(W, U, b)
     H = net.forward(x, y)
-    assert_close(H.numpy().reshape(T, B, nh), H_ref, 10.0, "h")
+    assert_close(H.numpy().reshape(T, B, nh), H_ref, 1.0, "h")
     net.backward()
     for g in G:
-        assert_close(net.dW[g].numpy(), dW_ref[g], 10.0, f"dW_{g}")
-        assert_close(net.dU[g].numpy(), dU_ref[g], 10.0, f"dU_{g}")
-        assert_close(net.db[g].numpy().ravel(), db_ref[g], 10.0, f"db_{g}")
-    assert_close(net.dX.numpy().reshape(T, B, n_in), dX_ref, 10.0, "dX")
+        assert_close(net.dW[g].numpy(), dW_ref[g], 1.0, f"dW_{g}")
+        assert_close(net.dU[g].numpy(), dU_ref[g], 1.0, f"dU_{g}")
+        assert_close(net.db[g].numpy().ravel(), db_ref[g], 1.0, f"db_{g}")
+    assert_close(net.dX.numpy().reshape(T, B, n_in), dX_ref, 1.0, "dX")
 
 
 def test_c3_fused_cell_backward_is_bit_identical_to_the_operation_chain(engine):
@@ -163,15 +163,15 @@ def test_c4_swin_block_float(engine, images):
     blk = SwinBlock(engine, f, d, heads, ws, hidden // d)
     blk.set_parameters(p)
     out = blk.forward(engine.upload(x))
-    assert_close(out.numpy(), out_ref, 10 * rms(out_ref), "block output")
+    assert_close(out.numpy(), out_ref, 2 * rms(out_ref), "block output")
     nw = T // ws
     assert_close(blk.P.numpy().reshape(nw * heads, ws, ws), mid["P"], 1.0, "attention probabilities")
     dx = blk.backward(engine.upload(d_out))
-    assert_close(blk.d_qkv.numpy(), mid["d_qkv"], 10 * rms(mid["d_qkv"]), f"C4[{images}] d_qkv")
+    assert_close(blk.d_qkv.numpy(), mid["d_qkv"], 5 * rms(mid["d_qkv"]), f"C4[{images}] d_qkv")
     for k in g_ref:
         # weight gradients sum over all T tokens: the error scale is sum |terms| ~ T * typical product
-        assert_close(blk.g[k].numpy(), g_ref[k], 30 * rms(g_ref[k]), f"grad {k}")
-    assert_close(dx.numpy(), dx_ref, 10 * rms(dx_ref), "d_x")
+        assert_close(blk.g[k].numpy(), g_ref[k], 16 * rms(g_ref[k]), f"grad {k}")
+    assert_close(dx.numpy(), dx_ref, 3 * rms(dx_ref), "d_x")
 
 
 # ------------------------------------------------------------------ C5 (reduced rows)
@@ -204,11 +204,11 @@ def test_c5_wide_mlp_float_reduced(engine, gemm):
         engine.upload(x, out=net.A[0])
         engine.upload(t, out=net.target)
         net.forward()
-        assert_close(net.A[L].numpy(), acts[-1], 10 * rms(acts[-1]), "output")
+        assert_close(net.A[L].numpy(), acts[-1], 3 * rms(acts[-1]), "output")
         net.backward()
         for l in range(L):
-            assert_close(net.dW[l].numpy(), dW_ref[l], 30 * rms(dW_ref[l]), f"C5 reduced [{gemm}] dW{l}")
-        assert_close(net.dX.numpy(), d, 30 * rms(d), f"C5 reduced [{gemm}] dX")
+            assert_close(net.dW[l].numpy(), dW_ref[l], 10 * rms(dW_ref[l]), f"C5 reduced [{gemm}] dW{l}")
+        assert_close(net.dX.numpy(), d, 5 * rms(d), f"C5 reduced [{gemm}] dX")
     finally:
         engine.set_option("gemm_f32", "auto")
 
