@@ -148,7 +148,8 @@ def c5_config(args, world):
                         f"MSE, global batch {args.batch}, clip={args.clip} + Adam",
             "global_batch": args.batch, "rows_per_gpu": rows, "parallelism": f"dp{world}",
             "dp_mode": args.dp_mode if world > 1 else None, "gemm": args.gemm, "lr": args.lr,
-            "l2": "inputs larger than L2 (activations >= 1 GiB per layer)"}
+            "l2": f"inputs larger than L2: a step streams {args.layers * rows * args.width * 16 / 2**30:.1f} GiB of "
+                  f"activations, gradients and packed operands per GPU between two uses of the same line"}
 
 
 class CpuStep:
