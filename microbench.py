@@ -63,6 +63,7 @@ def hbm_kernels(eng, only=None, rows=65536, cols=4096):
     eng.upload(np.random.default_rng(0).standard_normal((min(rows, 4096), cols), dtype=f), out=x.view((min(rows, 4096), cols)))
     db = eng.empty((1, cols), f)
     idx = eng.upload(np.random.default_rng(1).integers(0, 50000, (rows, 1)).astype(f))
+    table = eng.empty((50000, cols), f)
     srows = n // 49
     S, dS, oS = x.view((srows, 49)), dy.view((srows, 49)), out.view((srows, 49))
     lrows = n // 96
@@ -82,7 +83,8 @@ def hbm_kernels(eng, only=None, rows=65536, cols=4096):
         ("accumulate", 3 * n * 4, lambda: eng.accumulate(out, x)),
         ("segmented_sum_3", 4 * n * 4, lambda: eng.segmented_sum([x, dy, out2], out=out)),
         ("segmented_sum_2", 3 * n * 4, lambda: eng.segmented_sum([x, dy], out=out)),
-        ("embedding_scatter_ordered", 2 * n * 4 + rows * 4, lambda: eng.embedding_backward(idx, x, 50000)),
+        # reads dOut and the indices, writes the whole 50000-row table (rows nobody hit are zeroed)
+        ("embedding_scatter_ordered", n * 4 + rows * 4 + 50000 * cols * 4, lambda: eng.embedding_backward(idx, x, 50000, out=table)),
         ("softmax_backward_49", 3 * srows * 49 * 4, lambda: eng.softmax_backward(S, dS, out=oS)),
         ("layernorm_backward_96", 3 * lrows * 96 * 4, lambda: eng.layernorm_backward(Lx, mu, sd, dL, out=oL)),
         ("adam", 7 * npar * 4, lambda: eng.adam(P[0], P[1], P[2], P[3], 1e-3, .9, .999, 1e-8, 1.0)),

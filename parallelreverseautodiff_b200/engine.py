@@ -797,8 +797,8 @@ class Engine:
                                               out.ptr, n, W.shape[0], W.shape[1]))
         return out
 
-    def embedding_backward(self, index_col, dOut, vocab):
-        dW = self.empty((vocab, dOut.shape[1]), dOut.dtype)
+    def embedding_backward(self, index_col, dOut, vocab, out=None):
+        dW = out or self.empty((vocab, dOut.shape[1]), dOut.dtype)
         check(self.lib.prad_embedding_backward(self.ctx, dtype_code(dOut.dtype), index_col.ptr,
                                                dOut.ptr, dW.ptr, index_col.size, vocab,
                                                dOut.shape[1]))
