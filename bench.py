@@ -346,6 +346,7 @@ def run_native(args, rank, world, local_rank):
         loss = net.train_step_host(x_host, t_host, rows_total=args.batch)
 
     # ---- (A) device-resident hot path: backward + clip + Adam ---------------------------
+    net.forward_follows = False     # a backward follows each optimiser step here: owners publish W_L-1 first
     marks = {"gemm": [], "join": [], "opt": [], "pack": []}
 
     def probe(kind, begin):

@@ -720,6 +720,13 @@ prad_status prad_dp_wait(prad_ctx* ctx);
  * 118-157) and broadcasts the new weights. */
 prad_status prad_dp_reduce(prad_ctx* ctx, prad_dtype dt, void* buf, int64_t n, int root);
 prad_status prad_dp_broadcast(prad_ctx* ctx, prad_dtype dt, void* buf, int64_t n, int root);
+/* Finer joins than prad_dp_wait: prad_dp_mark remembers, under `slot` (0 .. PRAD_DP_MARKS - 1), the position the
+ * communication stream has reached -- everything enqueued on it so far; prad_dp_wait_mark makes the compute stream
+ * wait for that position only.  With one mark per broadcast, the first layer of the next pass starts as soon
+ * as ITS weights have arrived while the other tensors are still on their way. */
+#define PRAD_DP_MARKS 256
+prad_status prad_dp_mark(prad_ctx* ctx, int slot);
+prad_status prad_dp_wait_mark(prad_ctx* ctx, int slot);
 /* Host-side join with a deadline, the counterpart of the visitor's bounded wait on a sibling task
  * (TimeoutInMinutes, src/RMAD/OperationNeuralNetworkVisitor.cs:27,264-270): blocks the calling thread
  * until the outstanding collectives have completed (then the compute stream is joined as by

@@ -136,6 +136,8 @@ SIGNATURES = {
     "prad_dp_wait": [vp],
     "prad_dp_reduce": [vp, i32, vp, i64, i32],
     "prad_dp_broadcast": [vp, i32, vp, i64, i32],
+    "prad_dp_mark": [vp, i32],
+    "prad_dp_wait_mark": [vp, i32],
     "prad_dp_wait_host": [vp, f64],
     "prad_dp_shutdown": [vp],
     "prad_download_many": [vp, vp, pvp, C.POINTER(sz), i32],

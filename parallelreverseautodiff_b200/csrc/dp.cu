@@ -90,6 +90,7 @@ struct DpState {
   int rank = 0, world = 1;
   bool pending = false;
   bool aborted = false;         // the communicator was aborted after a deadline or an asynchronous error
+  cudaEvent_t marks[PRAD_DP_MARKS] = {};   // prad_dp_mark: positions on the communication stream, created on first use
 };
 
 #define PRAD_NCCL(call)                                                                \
@@ -108,6 +109,8 @@ prad_status dp_destroy(prad_ctx* ctx) {
   if (d->comm && nccl().ok && !d->aborted) nccl().CommDestroy(d->comm);
   if (d->ready) cudaEventDestroy(d->ready);
   if (d->done) cudaEventDestroy(d->done);
+  for (cudaEvent_t& m : d->marks)
+    if (m) { cudaEventDestroy(m); m = nullptr; }
   if (d->comm_stream) cudaStreamDestroy(d->comm_stream);
   delete d;
   ctx->dp = nullptr;
@@ -278,6 +281,28 @@ prad_status prad_dp_wait(prad_ctx* ctx) {
     set_error("prad_dp_wait: NCCL reported an asynchronous error: %s", nccl().GetErrorString(async));
     return PRAD_ERR_COMM;
   }
+  return PRAD_OK;
+}
+
+prad_status prad_dp_mark(prad_ctx* ctx, int slot) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_NOT_CAPTURING(ctx, "prad_dp_mark");
+  PRAD_DP_READY(ctx, "prad_dp_mark");
+  PRAD_REQUIRE(slot >= 0 && slot < PRAD_DP_MARKS, PRAD_ERR_INVALID, "prad_dp_mark: slot %d outside 0..%d", slot, PRAD_DP_MARKS - 1);
+  DpState* d = ctx->dp;
+  if (!d->marks[slot]) PRAD_CUDA(cudaEventCreateWithFlags(&d->marks[slot], cudaEventDisableTiming));
+  PRAD_CUDA(cudaEventRecord(d->marks[slot], d->comm_stream));
+  return PRAD_OK;
+}
+
+prad_status prad_dp_wait_mark(prad_ctx* ctx, int slot) {
+  PRAD_CHECK_CTX(ctx);
+  PRAD_NOT_CAPTURING(ctx, "prad_dp_wait_mark");
+  PRAD_DP_READY(ctx, "prad_dp_wait_mark");
+  PRAD_REQUIRE(slot >= 0 && slot < PRAD_DP_MARKS, PRAD_ERR_INVALID, "prad_dp_wait_mark: slot %d outside 0..%d", slot, PRAD_DP_MARKS - 1);
+  DpState* d = ctx->dp;
+  PRAD_REQUIRE(d->marks[slot], PRAD_ERR_INVALID, "prad_dp_wait_mark: slot %d was never marked", slot);
+  PRAD_CUDA(cudaStreamWaitEvent(ctx->stream, d->marks[slot], 0));
   return PRAD_OK;
 }
 

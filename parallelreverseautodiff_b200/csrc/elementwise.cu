@@ -339,11 +339,12 @@ __device__ __forceinline__ T nary_combine(const T (&v)[PRAD_MAX_SRCS], int count
   return mul_rn(acc, inv_count);
 }
 
-template <typename T>
+template <typename T, int U, int S>
 __global__ void __launch_bounds__(256)
 nary_sum_kernel(SrcTable t, T* out, int64_t n, int mode, T inv_count, bool vec) {
   // `out` is not restrict-qualified: with more than PRAD_MAX_SRCS sources the running sum is read back
-  // through the source table (every thread loads its element before it stores it)
+  // through the source table (every thread loads its element before it stores it).
+  // U vectors per thread and trip and at most S sources (few sources: more trips' loads in flight).
   constexpr int VEC = Vec16<T>::N;
   using V = typename Vec16<T>::type;
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -351,21 +352,32 @@ nary_sum_kernel(SrcTable t, T* out, int64_t n, int mode, T inv_count, bool vec) 
   int64_t done = 0;
   if (vec) {      // 128-bit loads of every source, all issued before the first use
     const int64_t nvec = n / VEC;
-    for (int64_t i = tid; i < nvec; i += stride) {
-      V in[PRAD_MAX_SRCS];
+    for (int64_t i0 = tid; i0 < nvec; i0 += stride * U) {
+      V in[U][S];
 #pragma unroll
-      for (int g = 0; g < PRAD_MAX_SRCS; ++g)
-        if (g < t.count) in[g] = __ldcs(reinterpret_cast<const V*>(t.p[g]) + i);
-      V o;
+      for (int u = 0; u < U; ++u) {
+        const int64_t i = i0 + u * stride;
+        if (i < nvec) {
 #pragma unroll
-      for (int q = 0; q < VEC; ++q) {
-        T v[PRAD_MAX_SRCS];
-#pragma unroll
-        for (int g = 0; g < PRAD_MAX_SRCS; ++g)
-          if (g < t.count) v[g] = reinterpret_cast<const T*>(&in[g])[q];
-        reinterpret_cast<T*>(&o)[q] = nary_combine<T>(v, t.count, mode, inv_count);
+          for (int g = 0; g < S; ++g)
+            if (g < t.count) in[u][g] = __ldcs(reinterpret_cast<const V*>(t.p[g]) + i);
+        }
       }
-      __stcs(reinterpret_cast<V*>(out) + i, o);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int64_t i = i0 + u * stride;
+        if (i >= nvec) break;
+        V o;
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) {
+          T v[PRAD_MAX_SRCS];
+#pragma unroll
+          for (int g = 0; g < S; ++g)
+            if (g < t.count) v[g] = reinterpret_cast<const T*>(&in[u][g])[q];
+          reinterpret_cast<T*>(&o)[q] = nary_combine<T>(v, t.count, mode, inv_count);
+        }
+        __stcs(reinterpret_cast<V*>(out) + i, o);
+      }
     }
     done = nvec * VEC;
   }
@@ -399,8 +411,10 @@ static prad_status nary_t(prad_ctx* ctx, const void* const* srcs, int count, voi
     int m = mode == 0 ? 0 : 1;
     bool vec = ((uintptr_t)out & 15) == 0;
     for (int g = 0; g < t.count; ++g) vec = vec && (((uintptr_t)t.p[g] & 15) == 0);
-    nary_sum_kernel<T><<<grid, 256, 0, ctx->stream>>>(t, (T*)out, n, m,
-                                                      (mode == 1 && last) ? inv : (T)1, vec);
+    const T scale = (mode == 1 && last) ? inv : (T)1;
+    if (t.count <= 2) nary_sum_kernel<T, 4, 2><<<grid, 256, 0, ctx->stream>>>(t, (T*)out, n, m, scale, vec);
+    else if (t.count <= 4) nary_sum_kernel<T, 2, 4><<<grid, 256, 0, ctx->stream>>>(t, (T*)out, n, m, scale, vec);
+    else nary_sum_kernel<T, 1, PRAD_MAX_SRCS><<<grid, 256, 0, ctx->stream>>>(t, (T*)out, n, m, scale, vec);
     PRAD_LAUNCHED(ctx);
     first = false;
   }

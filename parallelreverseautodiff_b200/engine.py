@@ -947,6 +947,14 @@ class Engine:
     def dp_broadcast(self, m: DeviceMatrix, root: int) -> None:
         check(self.lib.prad_dp_broadcast(self.ctx, dtype_code(m.dtype), m.ptr, m.size, root))
 
+    def dp_mark(self, slot: int) -> None:
+        """Remember, under `slot`, what the communication stream has been given so far."""
+        check(self.lib.prad_dp_mark(self.ctx, slot))
+
+    def dp_wait_mark(self, slot: int) -> None:
+        """The compute stream waits for the collectives enqueued before dp_mark(slot), not for later ones."""
+        check(self.lib.prad_dp_wait_mark(self.ctx, slot))
+
     def dp_wait_host(self, timeout_ms: float) -> None:
         """Host-side join with a deadline; raises PradError(ERR_TIMEOUT / ERR_COMM) and leaves the
         communicator aborted when a peer never arrives."""

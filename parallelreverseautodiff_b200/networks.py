@@ -74,16 +74,19 @@ class FeedForwardNetwork:
         self.packed_mode = packed          # "auto" | True | False: operands packed where they are produced
         self.pack_block_cols = pack_block_cols   # block length of the by-columns forms (0 = the library's default)
         self.packed = False                # decided per batch size in _ensure_buffers
-        self._w_dirty = True
         self.dp_overlap = dp_overlap
         self.dp_sharded = bool(dp_sharded) and world > 1
         if self.dp_sharded and clip_mode == E.CLIP_GLOBAL_NORM:
             raise ValueError("the sharded optimiser needs per-tensor clip statistics; the global-norm clip "
                              "sums over all tensors")
         self._bcast_pending = False
+        self._bcast_marks = set()          # parameters whose broadcast has been enqueued and not joined yet
+        self.forward_follows = False       # which pass follows an optimiser step: owners broadcast in that pass's order
         self.dtype = np.dtype(dtype)
         self.sizes = list(sizes)
         self.L = len(sizes) - 1
+        self._w_dirty = [True] * self.L    # packed weight forms (by rows / by columns) older than the weights
+        self._wc_dirty = [True] * self.L
         self.acts = [hidden_act] * (self.L - 1) + [output_act]
         self.softmax_output = softmax_output
         self.loss = loss
@@ -122,7 +125,8 @@ class FeedForwardNetwork:
 
     # ---------------------------------------------------------------- set-up
     def set_weights(self, weights: Sequence[np.ndarray], biases: Optional[Sequence[np.ndarray]] = None):
-        self._w_dirty = self._wc_dirty = True
+        self._w_dirty = [True] * self.L
+        self._wc_dirty = [True] * self.L
         for l, w in enumerate(weights):
             self.eng.upload(np.ascontiguousarray(w, self.dtype), out=self.W[l])
         if biases is not None:
@@ -187,26 +191,28 @@ class FeedForwardNetwork:
         # (two objects: the backward needs only the by-rows form, and packs it again after every optimiser step)
         self.PWr = [e.packed(self.sizes[l], self.sizes[l + 1], E.PACK_ROWS, blk_d, 0) for l in range(L)]
         self.PWc = [e.packed(self.sizes[l], self.sizes[l + 1], E.PACK_COLS, 0, blk_a) for l in range(L)]
-        self._w_dirty = self._wc_dirty = True
+        self._w_dirty = [True] * L
+        self._wc_dirty = [True] * L
 
-    def _pack_weights(self, forward: bool) -> None:
-        if forward and self._wc_dirty:
-            for l in range(self.L):
-                self.PWc[l].pack(self.W[l])
-            self._wc_dirty = False
-        if not forward and self._w_dirty:
-            for l in range(self.L):
-                self.PWr[l].pack(self.W[l])
-            self._w_dirty = False
+    def _pack_weight(self, l: int, forward: bool) -> None:
+        """Packed form of W_l for the forward (by columns) or the backward (by rows) product, refreshed after
+        an optimiser step; waits for that tensor's broadcast only."""
+        dirty = self._wc_dirty if forward else self._w_dirty
+        if dirty[l]:
+            self._join_tensor(l)
+            (self.PWc if forward else self.PWr)[l].pack(self.W[l])
+            dirty[l] = False
 
     def _forward_packed(self) -> E.DeviceMatrix:
         e, L = self.eng, self.L
         alpha = self.Parameters.LeakyReLUAlpha
-        self._pack_weights(forward=True)
         self.PA[0].pack(self.A[0])
         for l in range(L):
             act = self.acts[l]
             pre = self.Z[l + 1] if self.Z[l + 1] is not None else self.A[l + 1]
+            self._pack_weight(l, forward=True)
+            if self.use_bias:
+                self._join_tensor(L + l)
             e.gemm_packed(self.PA[l], E.PACK_ROWS, self.PWc[l], E.PACK_COLS, pre,
                           bias=self.b[l] if self.use_bias else None)
             if l + 1 < L:      # the activation writes the next layer's operand (and A_{l+1} in FP32 if kept)
@@ -240,14 +246,6 @@ class FeedForwardNetwork:
             e.gemm_packed(self.PA[l - 1], E.PACK_COLS, pd, E.PACK_COLS, self.dW[l - 1])
             if probe:
                 probe("gemm", False)
-            # the first weight-gradient product reads no weights: the previous step's weight broadcasts run
-            # beside it; they are joined here, and only then are the (new) weights packed
-            self._join_broadcasts()
-            if probe:
-                probe("pack", True)
-            self._pack_weights(forward=False)
-            if probe:
-                probe("pack", False)
             if self.world > 1 and self.dp_overlap:
                 self._reduce_grad(l - 1)
             if self.use_bias:
@@ -256,6 +254,13 @@ class FeedForwardNetwork:
                     self._reduce_grad(L + l - 1)
             if l > 1 or need_dx:
                 g = self.dZ[0].view((rows, self.sizes[l - 1]))
+                # the weight-gradient product above read no weights: the previous step's weight broadcasts ran
+                # beside it, owner by owner in the order this loop needs them; only W_{l-1}'s is joined here
+                if probe:
+                    probe("pack", True)
+                self._pack_weight(l - 1, forward=False)
+                if probe:
+                    probe("pack", False)
                 if probe:
                     probe("gemm", True)
                 e.gemm_packed(pd, E.PACK_ROWS, self.PWr[l - 1], E.PACK_ROWS, g)
@@ -267,8 +272,10 @@ class FeedForwardNetwork:
     def forward(self, x: Optional[E.DeviceMatrix] = None) -> E.DeviceMatrix:
         """Forward through every layer; keeps Z_l (pre-activation) and A_l for the backward."""
         e = self.eng
-        self._join_broadcasts()
-        if self.packed or (x is not None and self._wants_packed(x.shape[0])):
+        packed = self.packed or (x is not None and self._wants_packed(x.shape[0]))
+        if not packed:               # (the packed path joins tensor by tensor, as it reaches them)
+            self._join_broadcasts()
+        if packed:
             if x is not None:
                 self._ensure_buffers(x.shape[0])
                 e.copy(self.A[0], x)
@@ -311,6 +318,15 @@ class FeedForwardNetwork:
         if self._bcast_pending:
             self.eng.dp_wait()
             self._bcast_pending = False
+            self._bcast_marks.clear()
+
+    def _join_tensor(self, p: int) -> None:
+        """Wait for the broadcast of parameter p alone (the others may still be on their way)."""
+        if p in self._bcast_marks:
+            self.eng.dp_wait_mark(p)
+            self._bcast_marks.discard(p)
+            if not self._bcast_marks:
+                self._bcast_pending = False
 
     def _saved(self, l: int):
         """Tensor the activation of layer l keeps for Backward (1-based l)."""
@@ -388,14 +404,17 @@ class FeedForwardNetwork:
                     e.dp_allreduce(self._grad_all)
             if probe:
                 probe("join", True)
-            e.dp_wait()
+            e.dp_wait()                  # every collective so far, the previous step's broadcasts included
+            self._bcast_marks.clear()
+            self._bcast_pending = False
             if probe:
                 probe("join", False)
 
     # ---------------------------------------------------------------- clip + Adam
     def clip_and_optimize(self, zero_grad: bool = True):
         p = self.Parameters
-        self._w_dirty = self._wc_dirty = True
+        self._w_dirty = [True] * self.L
+        self._wc_dirty = [True] * self.L
         own = self.owned
         pick = lambda xs: [xs[i] for i in own]
         if own:
@@ -406,15 +425,21 @@ class FeedForwardNetwork:
             # owners publish their new weights; the tensors the next backward needs first go first.
             # (Gradients of tensors owned elsewhere keep this rank's partial sums: the next backward
             # overwrites them.)
-            order = list(range(self.L - 1, -1, -1)) + list(range(self.L, len(self.params)))
+            if self.forward_follows:     # W_0 (and its bias) first
+                order = [i for l in range(self.L) for i in ([l, self.L + l] if self.use_bias else [l])]
+            else:
+                order = list(range(self.L - 1, -1, -1)) + list(range(self.L, len(self.params)))
             for i in order:
                 self.eng.dp_broadcast(self.params[i], self._owner(i))
+                self.eng.dp_mark(i)
+                self._bcast_marks.add(i)
             self._bcast_pending = True
 
     # ---------------------------------------------------------------- end to end
     def train_step_host(self, x_host: np.ndarray, t_host: np.ndarray, rows_total=None) -> float:
         """Host batch in, loss out: upload, forward, loss, backward, clip + Adam, download."""
         e = self.eng
+        self.forward_follows = True
         self._ensure_buffers(x_host.shape[0])
         e.upload(x_host, out=self.A[0])
         e.upload(t_host, out=self.target)
@@ -430,6 +455,7 @@ class FeedForwardNetwork:
         buffers alternate).  Every batch is still copied host->device and every loss read back;
         yields the losses."""
         e = self.eng
+        self.forward_follows = True
         batches = list(batches)
         if not batches:
             return

@@ -11,7 +11,7 @@ import torch.multiprocessing as mp
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, id_path, out_dir, overlap=True, sharded=False):
+def _worker(rank, world, id_path, out_dir, overlap=True, sharded=False, packed=False):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     import time
 
@@ -38,7 +38,8 @@ def _worker(rank, world, id_path, out_dir, overlap=True, sharded=False):
     Ws = [(r.standard_normal((sizes[i], sizes[i + 1])) * np.sqrt(2.0 / sizes[i])).astype(np.float32) for i in range(2)]
     net = FeedForwardNetwork(eng, np.float32, sizes, hidden_act=E.ACT_GELU, output_act=E.ACT_GELU, loss="mse",
                              use_bias=True, clip_mode=E.CLIP_REFERENCE, rank=rank, world=world, dp_overlap=overlap,
-                             dp_sharded=sharded)
+                             dp_sharded=sharded, packed=True if packed else "auto")
+    net.forward_follows = packed == "forward first"     # order in which the owners publish their tensors
     net.set_weights(Ws)
     a, b = row_shard(batch, rank, world)
     net._ensure_buffers(b - a)
@@ -63,14 +64,18 @@ def _worker(rank, world, id_path, out_dir, overlap=True, sharded=False):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("overlap,sharded", [(True, False), (False, False), (True, True), (False, True)],
+@pytest.mark.parametrize("overlap,sharded,packed",
+                         [(True, False, False), (False, False, False), (True, True, False), (False, True, False),
+                          (True, True, "backward first"), (True, True, "forward first")],
                          ids=["per-layer all-reduce", "one collective after the backward",
-                              "sharded optimiser, per-layer reduce", "sharded optimiser, reduces after the backward"])
-def test_two_gpu_gradients_match_oracle(tmp_path, overlap, sharded):
+                              "sharded optimiser, per-layer reduce", "sharded optimiser, reduces after the backward",
+                              "sharded optimiser on packed operands, tensors joined one by one",
+                              "the same with the broadcasts in forward order"])
+def test_two_gpu_gradients_match_oracle(tmp_path, overlap, sharded, packed):
     import oracle as O
 
     world = 2
-    mp.spawn(_worker, args=(world, str(tmp_path / "nccl_id"), str(tmp_path), overlap, sharded), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, str(tmp_path / "nccl_id"), str(tmp_path), overlap, sharded, packed), nprocs=world, join=True)
     r = np.random.default_rng(42)
     batch, sizes = 96, [40, 64, 24]
     x = r.standard_normal((batch, sizes[0])).astype(np.float32)
@@ -97,7 +102,8 @@ def test_two_gpu_gradients_match_oracle(tmp_path, overlap, sharded):
         assert holders
         for rk in holders:
             got = rk[f"arr_{i}"]
-            assert np.abs(got - g).max() <= 1e-5 * np.abs(g).max() + 1e-7, i
+            # (packed operands: tensor-core products, 22-bit pieces)
+            assert np.abs(got - g).max() <= (1e-4 if packed else 1e-5) * np.abs(g).max() + 1e-7, i
         if not sharded:
             np.testing.assert_array_equal(ranks[0][f"arr_{i}"], ranks[1][f"arr_{i}"])
     # weights after clip + Adam: identical on both ranks (they were broadcast, or computed from identical
