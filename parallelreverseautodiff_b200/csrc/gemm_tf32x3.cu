@@ -952,6 +952,360 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
   }
 }
 
+// ---- CTA-pair variant of the packed FP16 product (tcgen05 cta_group::2) --------------------
+// Two CTAs on neighbouring SMs (a cluster of two) share one 256 x 256 output tile: each holds 128 rows of
+// the row operand and HALF of the column operand's 256 rows in its shared memory, the tensor cores of both
+// SMs read both halves, and each CTA's TMEM receives its own 128 x 256 part of the product.  Per SM and
+// k-block that is 32 KB of operands instead of 48 KB: less traffic from L2 and through shared memory, and
+// six units fit where four did, so five loads are in flight while one is multiplied.
+//   * the even CTA of the pair (rank 0, "leader") draws the tile indices, issues every MMA and owns the
+//     barriers both CTAs report to: unit filled (`full`: the leader announces the bytes of both CTAs, both
+//     CTAs' TMA loads complete on it), accumulator drained (`acc_empty`: the epilogue warps of both CTAs
+//     arrive), queue entry consumed (`tile_empty`).  What the leader tells the pair -- unit free again,
+//     accumulator ready, next tile index -- it signals on the barrier of the same name in EACH CTA
+//     (two tcgen05.commit, or a remote store + remote arrive for the queue);
+//   * every CTA loads its own operand rows, drains its own TMEM rows and stores its own output rows;
+//   * the pair synchronises (barrier.cluster) after the barriers are initialised and before TMEM is freed,
+//     so no remote arrive meets an uninitialised barrier or a CTA that has left.
+// Every wait is bounded as in the other kernels; a CTA that gives up sets the error flag, the other one
+// of the pair sees it in its own waits, and both still reach the final cluster barrier.
+namespace p2 {
+constexpr int BK = 32;
+constexpr int UNITS = 6;
+constexpr int UNIT_BYTES = 32 * 1024;               // 128 rows of A + 128 rows of B, 128 bytes each
+constexpr int BAR_BYTES = 512;
+constexpr int SCALE_BYTES = EPI_WARPS * 128 * 4;
+constexpr int SMEM_BYTES = UNITS * UNIT_BYTES + 1024 /*alignment slack*/ + BAR_BYTES + SCALE_BYTES;
+constexpr int BM2 = 2 * BM;                          // rows of the pair's tile
+static_assert(SMEM_BYTES <= 227 * 1024, "unit ring does not fit in shared memory");
+}  // namespace p2
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void st_shared_cluster(uint32_t cluster_addr, int v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// bounded wait on a barrier of this CTA that the other CTA of the pair may arrive at
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int* err_flag, int code) {
+  for (uint32_t spins = 0;; ++spins) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((spins & 0x3ff) == 0x3ff) {
+      if (*((volatile int*)err_flag) != 0) return false;
+      if (spins >= SPIN_LIMIT) { atomicCAS(err_flag, 0, code); return false; }
+    }
+  }
+}
+// TMA load into this CTA's shared memory whose bytes are counted on a barrier of either CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on the barrier (any CTA of the cluster) once every MMA issued so far has completed in both CTAs
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+// Instruction descriptor of the pair's product: D = F32, A = B = FP16, K-major, M = 256 over two CTAs, N = 256.
+__host__ __device__ constexpr uint32_t idesc_fp16_pair() {
+  return (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(p2::BM2 >> 4) << 24);
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 int M, int N, float* __restrict__ C, int64_t ldc, bool vecC, Epi epi,
+                 int* __restrict__ err_flag, TileSched ts) {
+  using namespace p2;
+  extern __shared__ uint8_t smem_raw[];
+  // the same offsets in both CTAs: the dynamic shared memory of a kernel starts at the same window offset in each
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = base + UNITS * UNIT_BYTES;
+  constexpr int TQ = 4;
+  auto full_bar = [&](uint32_t s) { return bars + 8u * s; };
+  auto empty_bar = [&](uint32_t s) { return bars + 8u * (UNITS + s); };
+  auto acc_full = [&](uint32_t b) { return bars + 8u * (2 * UNITS + b); };
+  auto acc_empty = [&](uint32_t b) { return bars + 8u * (2 * UNITS + 2 + b); };
+  auto tile_full = [&](uint32_t i) { return bars + 8u * (2 * UNITS + 4 + i); };
+  auto tile_empty = [&](uint32_t i) { return bars + 8u * (2 * UNITS + 4 + TQ + i); };
+  const uint32_t tmem_slot = bars + 8u * (2 * UNITS + 4 + 2 * TQ);
+  const uint32_t tile_q_addr = tmem_slot + 8u;
+  uint8_t* generic_base = smem_raw + (base - smem_u32(smem_raw));
+  uint8_t* generic_bars = generic_base + UNITS * UNIT_BYTES;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(generic_bars + 8 * (2 * UNITS + 4 + 2 * TQ));
+  volatile int* tile_q = reinterpret_cast<volatile int*>(generic_bars + 8 * (2 * UNITS + 4 + 2 * TQ) + 8);
+  static_assert(8 * (2 * UNITS + 4 + 2 * TQ) + 8 + 4 * TQ <= BAR_BYTES, "barrier block too small");
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0 = leader
+  const bool leader = rank == 0;
+  const int num_pairs = (int)(gridDim.x >> 1), pair = (int)(blockIdx.x >> 1);
+  const int total_tiles = ts.tiles_m * ts.tiles_n * ts.splits;     // tiles of 256 x 256
+  int* const tile_counter = err_flag + 32;
+  int* const done_counter = err_flag + 33;
+
+  __shared__ int s_abort, s_run;
+  if (threadIdx.x == 0) {
+    s_abort = *((volatile int*)err_flag);
+    for (int s = 0; s < UNITS; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 2 * EPI_WARPS); }
+    // queue entries are consumed by the leader's MMA warp and epilogue warps and the other CTA's producer and epilogue warps
+    for (int i = 0; i < TQ; ++i) { mbar_init(tile_full(i), 1); mbar_init(tile_empty(i), 2 + 2 * EPI_WARPS); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  cluster_sync_all();          // barriers of both CTAs initialised before anybody arrives remotely
+  // the pair runs or stays out together: both CTAs go by what the leader saw in the error flag (the TMEM
+  // allocation below is an operation of the pair)
+  if (threadIdx.x == 0) {
+    int a;
+    asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(a) : "r"(mapa_shared(smem_u32(&s_abort), 0)) : "memory");
+    s_run = a == 0;
+  }
+  __syncthreads();
+  const bool run = s_run != 0;
+  if (run && warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // TMEM of both CTAs allocated before the leader multiplies into it
+  tc_fence_after();
+  const uint32_t tmem_base = run ? *tmem_slot_ptr : 0u;
+
+  auto next_tile = [&](uint32_t qi, int role, bool whole_warp) -> int {
+    const uint32_t slot = qi % TQ;
+    bool got = mbar_wait_cluster(tile_full(slot), (qi / TQ) & 1, err_flag, role);
+    if (whole_warp) got = __all_sync(0xffffffffu, got);
+    if (!got) return -2;
+    const int t = tile_q[slot];
+    if (whole_warp) __syncwarp();
+    if (lane == 0) mbar_arrive_cluster(mapa_shared(tile_empty(slot), 0));
+    return t;
+  };
+  auto tile_of = [&](int t, int& m0, int& n0, int& z, int& kb0, int& num_kb) {
+    const int per_slice = ts.tiles_n * ts.tiles_m;
+    z = t / per_slice;
+    const int t2 = t - z * per_slice;
+    const int p = t2 / (ts.tiles_m * ts.panel_n);
+    const int r = t2 - p * ts.tiles_m * ts.panel_n;
+    const int w = min(ts.panel_n, ts.tiles_n - p * ts.panel_n);
+    m0 = (r / w) * BM2 + (int)rank * BM;            // this CTA's 128 rows of the pair's tile
+    n0 = (p * ts.panel_n + r % w) * BN;
+    kb0 = z * ts.kb_per_split;
+    num_kb = min(ts.total_kb - kb0, ts.kb_per_split);
+  };
+
+  if (!run) {
+    // nothing: fall through to the final barrier
+  } else if (warp == 0) {
+    // ------------------------------------------------------------ tile scheduler (leader) + TMA producer (both)
+    if (lane == 0) {
+      uint32_t g = 0, qi = 0;
+      bool ok = true;
+      int t = pair;
+      while (ok) {
+        if (leader) {
+          const uint32_t qslot = qi % TQ, qround = qi / TQ;
+          if (qround > 0 && !mbar_wait_cluster(tile_empty(qslot), (qround - 1) & 1, err_flag, 5)) break;
+          const int pub = t < total_tiles ? t : -1;
+          tile_q[qslot] = pub;
+          st_shared_cluster(mapa_shared(tile_q_addr + 4u * qslot, 1), pub);
+          mbar_arrive(tile_full(qslot));
+          mbar_arrive_cluster(mapa_shared(tile_full(qslot), 1));     // release: the entry is visible with the phase
+          ++qi;
+          if (t >= total_tiles) break;
+        } else {
+          t = next_tile(qi++, 5, false);
+          if (t < 0) break;
+        }
+        int m0, n0, z, kb0, num_kb;
+        tile_of(t, m0, n0, z, kb0, num_kb);
+        for (int kb = 0; kb < num_kb && ok; ++kb, ++g) {
+          const int x = (kb0 + kb) * BK;
+          const uint32_t slot = g % UNITS, round = g / UNITS;
+          if (round > 0 && !mbar_wait_cluster(empty_bar(slot), (round - 1) & 1, err_flag, 1)) { ok = false; break; }
+          const uint32_t st = base + slot * UNIT_BYTES;
+          // the leader announces the unit's bytes of both CTAs; both CTAs' loads complete on the leader's barrier
+          if (leader) mbar_expect_tx(full_bar(slot), 2 * UNIT_BYTES);
+          const uint32_t fb = mapa_shared(full_bar(slot), 0);
+          tma_load_2d_pair(st, &map_a, fb, 2 * x, m0);
+          tma_load_2d_pair(st + 16 * 1024, &map_b, fb, 2 * x, n0 + (int)rank * (BN / 2));
+        }
+        if (leader) t = num_pairs + atomicAdd(tile_counter, 1);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader only)
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc_q = idesc_fp16_pair();
+      uint32_t g = 0, gc = 0, qi = 0;
+      bool ok = true;
+      while (ok) {
+        const int t = next_tile(qi++, 6, false);
+        if (t < 0) break;
+        int m0, n0, z, kb0, num_kb;
+        tile_of(t, m0, n0, z, kb0, num_kb);
+        const int num_chunks = (num_kb + ts.chunk_kb - 1) / ts.chunk_kb;
+        for (int ch = 0; ch < num_chunks && ok; ++ch, ++gc) {
+          const uint32_t buf = gc & 1, use = gc >> 1;
+          if (use > 0) {
+            ok = mbar_wait_cluster(acc_empty(buf), (use - 1) & 1, err_flag, 4);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          const uint32_t d_tmem = tmem_base + buf * (uint32_t)BN;
+          const int kb_end = min(num_kb, (ch + 1) * ts.chunk_kb);
+          for (int kb = ch * ts.chunk_kb; kb < kb_end && ok; ++kb, ++g) {
+            const uint32_t slot = g % UNITS;
+            ok = mbar_wait_cluster(full_bar(slot), (g / UNITS) & 1, err_flag, 2);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t st = base + slot * UNIT_BYTES;
+            const uint64_t a_0 = kmajor_desc<128>(st), a_1 = a_0 + 4;
+            const uint64_t b_0 = kmajor_desc<128>(st + 16 * 1024), b_1 = b_0 + 4;
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k) {
+              const uint64_t adv = (uint64_t)((k * 16 * 2) >> 4);
+              umma_f16_pair(d_tmem, a_1 + adv, b_0 + adv, idesc_q, !(kb == ch * ts.chunk_kb && k == 0));
+              umma_f16_pair(d_tmem, a_0 + adv, b_1 + adv, idesc_q, 1);
+              umma_f16_pair(d_tmem, a_0 + adv, b_0 + adv, idesc_q, 1);
+            }
+            umma_commit_pair(empty_bar(slot));                      // the unit is free again: here ...
+            umma_commit_pair(mapa_shared(empty_bar(slot), 1));      // ... and in the other CTA
+          }
+          umma_commit_pair(acc_full(buf));
+          umma_commit_pair(mapa_shared(acc_full(buf), 1));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..9 of both CTAs)
+    const int sub = warp & 3;
+    const int half = (warp - 2) >> 2;
+    uint32_t gc = 0, qi = 0;
+    bool ok = true;
+    float4* const sb_slot = reinterpret_cast<float4*>(generic_bars + BAR_BYTES) + (warp - 2) * 32;
+    while (ok) {
+      const int t = next_tile(qi++, 7, true);
+      if (t < 0) break;
+      int m0, n0, z, kb0, num_kb;
+      tile_of(t, m0, n0, z, kb0, num_kb);
+      const int num_chunks = (num_kb + ts.chunk_kb - 1) / ts.chunk_kb;
+      float sum[4][32];
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+#pragma unroll
+        for (int j = 0; j < 32; ++j) sum[g][j] = 0.f;
+      const int chunk0 = kb0 / ts.chunk_kb;
+      const int row_blk = min(m0 + sub * 32 + lane, M - 1);
+      float sa_next = 0.f;
+      float4 sb_next = make_float4(0.f, 0.f, 0.f, 0.f);
+      auto fetch_scales = [&](int ch) {
+        sa_next = __ldg(epi.blk_a + (int64_t)(chunk0 + ch) * epi.blk_lda + row_blk);
+        sb_next = __ldg(reinterpret_cast<const float4*>(epi.blk_b + (int64_t)(chunk0 + ch) * epi.blk_ldb + n0 + half * 128) + lane);
+      };
+      fetch_scales(0);
+      for (int ch = 0; ch < num_chunks; ++ch, ++gc) {
+        const uint32_t buf = gc & 1;
+        const float sa = sa_next;
+        sb_slot[lane] = sb_next;
+        __syncwarp();
+        if (ch + 1 < num_chunks) fetch_scales(ch + 1);
+        ok = __all_sync(0xffffffffu, mbar_wait_cluster(acc_full(buf), (gc >> 1) & 1, err_flag, 3));
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + buf * (uint32_t)BN + (uint32_t)(half * 128);
+        const float2 sa2 = make_float2(sa, sa);
+        uint32_t v[2][8];
+        tmem_ld8(taddr, v[0]);
+#pragma unroll
+        for (int g = 0; g < 16; ++g) {
+          uint32_t (&cur)[8] = v[g & 1];
+          tmem_ld_wait8(cur);
+          if (g + 1 < 16) tmem_ld8(taddr + (uint32_t)((g + 1) * 8), v[(g + 1) & 1]);
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const float4 tq = sb_slot[g * 2 + q];
+            float* acc = &sum[g >> 2][(g & 3) * 8 + 4 * q];
+            const float2 p01 = __fmul2_rn(make_float2(__uint_as_float(cur[4 * q]), __uint_as_float(cur[4 * q + 1])), sa2);
+            const float2 p23 = __fmul2_rn(make_float2(__uint_as_float(cur[4 * q + 2]), __uint_as_float(cur[4 * q + 3])), sa2);
+            const float2 r01 = __ffma2_rn(p01, make_float2(tq.x, tq.y), make_float2(acc[0], acc[1]));
+            const float2 r23 = __ffma2_rn(p23, make_float2(tq.z, tq.w), make_float2(acc[2], acc[3]));
+            acc[0] = r01.x; acc[1] = r01.y; acc[2] = r23.x; acc[3] = r23.y;
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_shared(acc_empty(buf), 0));
+      }
+      if (!ok || *((volatile int*)err_flag) != 0) { ok = false; break; }
+      float* Ct = C + (int64_t)z * ts.split_stride;
+      epilogue_store_warp(sum, lane, m0 + sub * 32, n0 + half * 128, M, N, Ct, ldc, vecC, epi);
+    }
+  }
+
+  // drain: nobody leaves (or frees TMEM) while the other CTA of the pair may still signal it or multiply into it
+  tc_fence_before();
+  __syncthreads();
+  if (*((volatile int*)err_flag) != 0) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  __syncthreads();
+  cluster_sync_all();
+  if (run && warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(done_counter, 1) == (int)gridDim.x - 1) {
+      *((volatile int*)tile_counter) = 0;
+      *((volatile int*)done_counter) = 0;
+      __threadfence();
+    }
+  }
+}
+
 // ---- operand preparation: hi/lo split (optionally transposing) into K-major scratch -----
 __device__ __forceinline__ float to_tf32(float x) {
   uint32_t r;
@@ -1268,6 +1622,18 @@ static prad_status launch_fp16x3(prad_ctx* ctx, const PackedForm& a, const Packe
   const int tiles_m = (int)ceil_div(M, BM), tiles_n = (int)ceil_div(N, BN);
   const int64_t tiles = (int64_t)tiles_m * tiles_n;
   const int total_kb = (int)(kp / p1::BK), chunk_kb = a.chunk / p1::BK;
+  // CTA pairs (256-row tiles over two SMs) when the output has at least two tile rows and the option allows
+  const int tiles_m2 = (int)ceil_div(M, p2::BM2);
+  const bool pair = ctx->tc_pair != 0 && M > BM && ctx->sm_count - ctx->tc_reserve_sms >= 2;
+  CUtensorMap mb_half;
+  if (pair) {
+    PRAD_REQUIRE(make_map(&mb_half, b.h, N, (int)(2 * kp), b.pitch, BN / 2, 2 * p1::BK, 2, true), PRAD_ERR_CUDA,
+                 "gemm (tensor core): cuTensorMapEncodeTiled failed for the half column tile (N %d K %lld)", N, (long long)kp);
+    static std::atomic<uint64_t> pair_done{0};
+    const cudaError_t q_err = reserve_smem(gemm_pair_kernel, p2::SMEM_BYTES, ctx->device, pair_done);
+    PRAD_REQUIRE(q_err == cudaSuccess, PRAD_ERR_CUDA, "gemm (CTA pairs): cannot reserve %d bytes of shared memory: %s",
+                 p2::SMEM_BYTES, cudaGetErrorString(q_err));
+  }
   // Split-K against wave quantisation (see launch_tf32x3); slices start on block boundaries
   int splits = 1;
   if (!bias && ctx->tc_split_k) {
@@ -1285,9 +1651,17 @@ static prad_status launch_fp16x3(prad_ctx* ctx, const PackedForm& a, const Packe
     int panel_n = tiles_n;
     if (ctx->tc_panel_n > 0) panel_n = ctx->tc_panel_n < tiles_n ? ctx->tc_panel_n : tiles_n;
     else if ((int64_t)N * kp * 4 > ((int64_t)40 << 20) && tiles_n >= 2) panel_n = (tiles_n + 1) / 2;
+    const int64_t sms = ctx->sm_count - ctx->tc_reserve_sms;
+    if (pair) {
+      TileSched ts{tiles_m2, tiles_n, nsplit, kbps, total_kb, chunk_kb, panel_n, stride};
+      const int64_t total = (int64_t)tiles_m2 * tiles_n * nsplit;
+      const int64_t pairs = sms / 2;
+      const unsigned ctas = 2u * (unsigned)(total < pairs ? total : pairs);
+      gemm_pair_kernel<<<ctas, THREADS, p2::SMEM_BYTES, ctx->stream>>>(ma, mb_half, M, N, out, ldo, vec_out, ep, ctx->tc_err, ts);
+      return;
+    }
     TileSched ts{tiles_m, tiles_n, nsplit, kbps, total_kb, chunk_kb, panel_n, stride};
     const int64_t total = tiles * nsplit;
-    const int64_t sms = ctx->sm_count - ctx->tc_reserve_sms;
     const unsigned ctas = (unsigned)(total < sms ? total : sms);
     gemm_persistent_kernel<3><<<ctas, THREADS, p1::SMEM_BYTES, ctx->stream>>>(ma, ma, ma, mb, mb, mb, M, N, out, ldo, vec_out,
                                                                               ep, ctx->tc_err, ts);

@@ -279,60 +279,137 @@ embedding_gather_kernel(const T* __restrict__ index_col, const T* __restrict__ W
 // the other; column j is always handled by the same thread, so every dW element sees its
 // contributions in input-row order and the sum is bit-identical to the sequential loop.
 // No floating-point atomics anywhere.
+template <typename T> struct EmbVec;
+template <> struct EmbVec<float> { using type = float4; static constexpr int N = 4; };
+template <> struct EmbVec<double> { using type = double2; static constexpr int N = 2; };
+
 constexpr int EMB_THREADS = 256;
 constexpr int EMB_ITEMS = 4;
 constexpr int EMB_TILE = EMB_THREADS * EMB_ITEMS;
+constexpr int EMB_CAP = 2048;       // positions a CTA keeps in shared memory before it falls back to adding in place
 
+// One tile of the index list: the positions whose vocabulary row this CTA owns (row % B == b), appended to
+// `list` in input order (thread order == element order).  Returns how many; all threads get the same count.
+template <typename T>
+__device__ __forceinline__ int emb_compact_tile(const T* __restrict__ index_col, int tile, int n, int vocab, int B, int b,
+                                                int* list, int cap_left, int* warp_cnt, int* tile_cnt, int* bad) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  int mine[EMB_ITEMS];
+  int c = 0;
+#pragma unroll
+  for (int q = 0; q < EMB_ITEMS; ++q) {
+    const int i = tile + threadIdx.x * EMB_ITEMS + q;
+    mine[q] = -1;
+    if (i < n) {
+      const int idx = (int)index_col[i];
+      if (idx < 0 || idx >= vocab) {
+        if (b == 0) atomicExch(bad, i + 1);
+      } else if (idx % B == b) {
+        mine[q] = i;
+        ++c;
+      }
+    }
+  }
+  int incl = c;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int u = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += u;
+  }
+  if (lane == 31) warp_cnt[w] = incl;
+  __syncthreads();
+  int base = 0;
+  for (int k = 0; k < w; ++k) base += warp_cnt[k];
+  if (threadIdx.x == EMB_THREADS - 1) *tile_cnt = base + incl;
+  int pos = base + incl - c;
+#pragma unroll
+  for (int q = 0; q < EMB_ITEMS; ++q)
+    if (mine[q] >= 0) {
+      if (pos < cap_left) list[pos] = mine[q];
+      ++pos;
+    }
+  __syncthreads();
+  return *tile_cnt;
+}
+
+// dW[idx[i]] += dOut[i] for i ascending (EmbeddingOperation.cs:70-86), without float atomics: vocabulary rows are
+// dealt to the CTAs round-robin and a CTA adds the rows of dOut that hit one of its rows in input order.
+// Usual case: all positions a CTA owns fit in shared memory; then every owned row is summed in registers and
+// written exactly once (rows nobody hit are written as zeros), so dOut is read once and the table written once.
+// Otherwise (more than EMB_CAP hits on one CTA's rows) the CTA zeroes its rows and adds tile by tile in place.
 template <typename T>
 __global__ void __launch_bounds__(EMB_THREADS)
 embedding_scatter_ordered_kernel(const T* __restrict__ index_col, const T* __restrict__ dOut,
                                  T* __restrict__ dW, int n, int vocab, int dim,
                                  int* __restrict__ bad) {
-  __shared__ int list[EMB_TILE];
+  __shared__ int list[EMB_CAP];
+  __shared__ int match[EMB_CAP];
   __shared__ int warp_cnt[EMB_THREADS / 32];
-  __shared__ int tile_cnt;
+  __shared__ int tile_cnt, match_cnt;
   const int B = gridDim.x, b = blockIdx.x;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
 
+  // ---- collect the owned positions
+  int total = 0;
+  bool fits = true;
+  for (int tile = 0; tile < n && fits; tile += EMB_TILE) {
+    const int cnt = emb_compact_tile<T>(index_col, tile, n, vocab, B, b, list + total, EMB_CAP - total, warp_cnt, &tile_cnt, bad);
+    if (total + cnt > EMB_CAP) fits = false;
+    else total += cnt;
+    __syncthreads();
+  }
+
+  if (fits) {
+    using V = typename EmbVec<T>::type;
+    constexpr int VEC = EmbVec<T>::N;
+    const bool vec = dim % VEC == 0 && (((uintptr_t)dOut | (uintptr_t)dW) & 15) == 0;
+    for (int v = b; v < vocab; v += B) {
+      // positions that hit row v, in input order (warp 0: ordered compaction of 32 list entries per trip)
+      if (w == 0) {
+        int mc = 0;
+        for (int e0 = 0; e0 < total; e0 += 32) {
+          const int e = e0 + lane;
+          const int i = e < total ? list[e] : -1;
+          const bool hit = i >= 0 && (int)index_col[i] == v;
+          const unsigned m = __ballot_sync(0xffffffffu, hit);
+          if (hit) match[mc + __popc(m & ((1u << lane) - 1u))] = i;
+          mc += __popc(m);
+        }
+        if (lane == 0) match_cnt = mc;
+      }
+      __syncthreads();
+      const int mc = match_cnt;
+      T* row = dW + (int64_t)v * dim;
+      if (vec) {
+        for (int j = threadIdx.x; j < dim / VEC; j += EMB_THREADS) {
+          T acc[VEC];
+#pragma unroll
+          for (int q = 0; q < VEC; ++q) acc[q] = (T)0;
+          for (int k = 0; k < mc; ++k) {
+            const V x = __ldcs(reinterpret_cast<const V*>(dOut + (int64_t)match[k] * dim) + j);
+#pragma unroll
+            for (int q = 0; q < VEC; ++q) acc[q] = add_rn(acc[q], reinterpret_cast<const T*>(&x)[q]);
+          }
+          __stcs(reinterpret_cast<V*>(row) + j, *reinterpret_cast<const V*>(acc));
+        }
+      } else {
+        for (int j = threadIdx.x; j < dim; j += EMB_THREADS) {
+          T acc = (T)0;
+          for (int k = 0; k < mc; ++k) acc = add_rn(acc, dOut[(int64_t)match[k] * dim + j]);
+          row[j] = acc;
+        }
+      }
+      __syncthreads();
+    }
+    return;
+  }
+
+  // ---- more hits than the list holds: zero the owned rows, then add tile by tile in place
   for (int v = b; v < vocab; v += B)
     for (int j = threadIdx.x; j < dim; j += EMB_THREADS) dW[(int64_t)v * dim + j] = (T)0;
   __syncthreads();
-
   for (int tile = 0; tile < n; tile += EMB_TILE) {
-    int mine[EMB_ITEMS];
-    int c = 0;
-#pragma unroll
-    for (int q = 0; q < EMB_ITEMS; ++q) {
-      int i = tile + threadIdx.x * EMB_ITEMS + q;
-      mine[q] = -1;
-      if (i < n) {
-        int idx = (int)index_col[i];
-        if (idx < 0 || idx >= vocab) {
-          if (b == 0) atomicExch(bad, i + 1);
-        } else if (idx % B == b) {
-          mine[q] = i;
-          ++c;
-        }
-      }
-    }
-    // exclusive scan of c over the block (thread order == element order)
-    int incl = c;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      int u = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += u;
-    }
-    if (lane == 31) warp_cnt[w] = incl;
-    __syncthreads();
-    int base = 0;
-    for (int k = 0; k < w; ++k) base += warp_cnt[k];
-    if (threadIdx.x == EMB_THREADS - 1) tile_cnt = base + incl;
-    int pos = base + incl - c;
-#pragma unroll
-    for (int q = 0; q < EMB_ITEMS; ++q)
-      if (mine[q] >= 0) list[pos++] = mine[q];
-    __syncthreads();
-    const int cnt = tile_cnt;
+    const int cnt = emb_compact_tile<T>(index_col, tile, n, vocab, B, b, list, EMB_CAP, warp_cnt, &tile_cnt, bad);
     for (int e = 0; e < cnt; ++e) {
       const int i = list[e];
       const int idx = (int)index_col[i];

@@ -298,7 +298,7 @@ def test_losses(engine, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("case", [(2, 3, 2, "unique"), (1000, 50, 96, "dups"), (5000, 7, 33, "heavy"),
-                                  (300, 2000, 8, "sparse")])
+                                  (300, 2000, 8, "sparse"), (9000, 3, 12, "more hits per row than a CTA lists")])
 def test_embedding_bit_exact(engine, dtype, case):
     n, vocab, dim, _ = case
     r = rng(n)

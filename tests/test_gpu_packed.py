@@ -17,11 +17,42 @@ def _absprod(a, b):
     return np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)
 
 
+@pytest.fixture(params=["0", "1"], ids=["one CTA per tile", "CTA pairs"])
+def tile_engine(engine, request):
+    """The engine with products of packed operands on one CTA per 128 x 256 tile, or on pairs of CTAs
+    (tcgen05 cta_group::2) that share a 256 x 256 tile."""
+    engine.set_option("tc_pair", request.param)
+    yield engine
+    engine.set_option("tc_pair", "0")
+
+
+@pytest.mark.parametrize("shape", [(257, 640, 300), (1024, 2048, 768), (2100, 4096, 520)])
+def test_products_on_cta_pairs_match_single_ctas(engine, shape):
+    """Several tiles per pair, ragged last tile rows and columns, split-K: the pair kernel adds the same block
+    sums in the same order as the one-CTA kernel, so the results are bit-identical."""
+    m, k, n = shape
+    r = rng(m + n)
+    X = r.standard_normal((m, k)).astype(f)
+    Y = (r.standard_normal((k, n)) * 0.1).astype(f)
+    PX = engine.packed(m, k, E.PACK_ROWS).pack(engine.upload(X))
+    PY = engine.packed(k, n, E.PACK_COLS, 0, PX.blocks()[0]).pack(engine.upload(Y))
+    outs = []
+    for mode in ("0", "1"):
+        engine.set_option("tc_pair", mode)
+        out = engine.zeros((m, n), f)
+        engine.gemm_packed(PX, E.PACK_ROWS, PY, E.PACK_COLS, out)
+        outs.append(out.numpy())
+    engine.set_option("tc_pair", "0")
+    assert_close(outs[1], O.matmul_forward(X, Y), _absprod(X, Y), f"pair product {shape}")
+    np.testing.assert_array_equal(outs[0], outs[1])
+
+
 @pytest.mark.parametrize("blocks", [(0, 0), (128, 128), (256, 128), (128, 256), (256, 256)])
 @pytest.mark.parametrize("shape", [(300, 200, 130), (512, 384, 256), (77, 1000, 33), (1, 40, 5), (260, 129, 257)])
-def test_products_of_packed_operands(engine, shape, blocks):
+def test_products_of_packed_operands(tile_engine, shape, blocks):
     """C = X Y for X (m x k), Y (k x n) through every pairing of forms: X by rows, Y by columns; and the two
     backward shapes dX = dC Y^T (dC by rows, Y by rows), dY = X^T dC (X by columns, dC by columns)."""
+    engine = tile_engine
     m, k, n = shape
     br, bc = blocks
     r = rng(m + k + n)
