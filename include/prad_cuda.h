@@ -99,6 +99,8 @@ const char* prad_version(void);
  *    scales is the chunk: 128 unless this option is set to 256 or more (then 256);
  *  "tc_split_k" = "on" | "off"; "tc_persistent" = "on" | "off" (tf32b16 on the one-tile-per-CTA kernel);
  *  "tc_reserve_sms" = n: SMs the persistent GEMM leaves idle (default 0);
+ *  "tc_prefetch" = n (0..64, default 0): the product of packed operands asks L2 for the row operand's tile n k-blocks
+ *    of 32 ahead of its load (measured: no gain on B200, the loads are not what the tensor pipe waits for);
  *  "tc_pair" = "0" | "1": products of packed operands on pairs of CTAs (tcgen05 cta_group::2: two neighbouring SMs
  *    share a 256 x 256 tile, each holding half of the column operand);
  *  "tc_panel_n" = n: column tiles per panel of the persistent GEMM's tile walk (0 = automatic: two

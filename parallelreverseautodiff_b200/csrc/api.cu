@@ -153,6 +153,12 @@ prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value) {
     else { set_error("prad_set_option: tc_auto must be tf32x3|tf32b16|bf16x3|fp16x3, got '%s'", value); return PRAD_ERR_INVALID; }
     return PRAD_OK;
   }
+  if (!strcmp(key, "tc_prefetch")) {
+    const int n = atoi(value);
+    PRAD_REQUIRE(n >= 0 && n <= 64, PRAD_ERR_INVALID, "prad_set_option: tc_prefetch must be 0..64, got '%s'", value);
+    ctx->tc_prefetch = n;
+    return PRAD_OK;
+  }
   if (!strcmp(key, "tc_pair")) {
     PRAD_REQUIRE(!strcmp(value, "0") || !strcmp(value, "1"), PRAD_ERR_INVALID, "prad_set_option: tc_pair must be 0 or 1, got '%s'", value);
     ctx->tc_pair = atoi(value);

@@ -122,6 +122,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+// asks L2 for a tile of the tensor without bringing it into shared memory
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
 }
@@ -639,6 +643,7 @@ struct TileSched {
   int chunk_kb;                   // k-blocks per accumulation chunk
   int panel_n;                    // column tiles per panel of the tile walk
   int64_t split_stride;           // elements between the partial products of consecutive slices
+  int prefetch_kb;                // PMODE 3: k-blocks by which an L2 prefetch of the row operand runs ahead of its load (0 = none)
 };
 
 template <int PMODE>
@@ -747,6 +752,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
             if (PMODE == 3) {  // one unit: A rows (h0 | h1) 16 KB, B rows (h0 | h1) 32 KB; x counts halves
               tma_load_2d(st, &map_a_xb, full_bar(slot), 2 * x, m0);
               tma_load_2d(st + 16 * 1024, &map_b_xb, full_bar(slot), 2 * x, n0);
+              // the row operand streams from DRAM: its tile of a later k-block is requested into L2 now
+              if (ts.prefetch_kb > 0 && kb + ts.prefetch_kb < num_kb) tma_prefetch_2d(&map_a_xb, 2 * (x + ts.prefetch_kb * BK), m0);
             } else if (half == 0) {   // unit H: a_hb 8 KB | a_lb 8 KB | b_hb 16 KB | b_lb 16 KB
               tma_load_2d(st, &map_a_xb, full_bar(slot), x, m0);
               tma_load_2d(st + 8 * 1024, &map_a_lb, full_bar(slot), x, m0);
@@ -1660,7 +1667,7 @@ static prad_status launch_fp16x3(prad_ctx* ctx, const PackedForm& a, const Packe
       gemm_pair_kernel<<<ctas, THREADS, p2::SMEM_BYTES, ctx->stream>>>(ma, mb_half, M, N, out, ldo, vec_out, ep, ctx->tc_err, ts);
       return;
     }
-    TileSched ts{tiles_m, tiles_n, nsplit, kbps, total_kb, chunk_kb, panel_n, stride};
+    TileSched ts{tiles_m, tiles_n, nsplit, kbps, total_kb, chunk_kb, panel_n, stride, ctx->tc_prefetch};
     const int64_t total = tiles * nsplit;
     const unsigned ctas = (unsigned)(total < sms ? total : sms);
     gemm_persistent_kernel<3><<<ctas, THREADS, p1::SMEM_BYTES, ctx->stream>>>(ma, ma, ma, mb, mb, mb, M, N, out, ldo, vec_out,

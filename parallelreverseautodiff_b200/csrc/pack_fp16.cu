@@ -140,10 +140,10 @@ __device__ __forceinline__ float apply_op(const PackSource& s, float a, float d,
 // of tile row k sits in slot q ^ ((k >> 2) & 7) of its row.  Pass 1 stores whole float4 (any permutation of
 // slots is conflict-free); in pass 2 a lane reads four consecutive k of one column and the eight lanes that
 // share a column quad read eight different slot positions: 32 different banks.
-template <int OP, bool ROWS, bool COLS>
-__global__ void __launch_bounds__(256)
+template <int OP, bool ROWS, bool COLS, int NT>
+__global__ void __launch_bounds__(NT, NT == 512 ? 2 : (OP == 0 ? 5 : 3))
 pack_fast_kernel(PackSource src, PackedForm fr, PackedForm fc) {
-  constexpr int T = 128, U = 2, NB = T / 8 / U;
+  constexpr int T = 128, U = 2, NW = NT / 32, NB = T / NW / U;      // NW warps, each takes every NW-th tile row
   constexpr bool HAS_DY = OP >= 4 && OP != 9, HAS_TG = OP == 7 || OP == 8 || OP == 11;
   extern __shared__ float stash[];       // [T][T] when COLS
   __shared__ unsigned colmax[T];
@@ -157,7 +157,7 @@ pack_fast_kernel(PackSource src, PackedForm fr, PackedForm fc) {
   auto load = [&](int buf, int b) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int64_t off = (r0 + warp + 8 * (b * U + u)) * src.ld + c;
+      const int64_t off = (r0 + warp + NW * (b * U + u)) * src.ld + c;
       a[buf][u] = __ldcs(reinterpret_cast<const float4*>(src.x + off));
       if (HAS_DY) d[buf][u] = __ldcs(reinterpret_cast<const float4*>(src.dy + off));
       if (HAS_TG) tg[buf][u] = __ldcs(reinterpret_cast<const float4*>(src.target + off));
@@ -170,7 +170,7 @@ pack_fast_kernel(PackSource src, PackedForm fr, PackedForm fc) {
     if (b + 1 < NB) load(cur ^ 1, b + 1);
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int tr = warp + 8 * (b * U + u);
+      const int tr = warp + NW * (b * U + u);
       const int64_t r = r0 + tr;
       float v[4];
       v[0] = apply_op<OP>(src, a[cur][u].x, HAS_DY ? d[cur][u].x : 0.f, HAS_TG ? tg[cur][u].x : 0.f);
@@ -209,12 +209,12 @@ pack_fast_kernel(PackSource src, PackedForm fr, PackedForm fc) {
   for (int q = 0; q < 4; ++q)
     if (cm[q] != 0) atomicMax(&colmax[lane * 4 + q], cm[q]);
   __syncthreads();
-  // pass 2: a warp owns 16 columns (four quads); per quad and 32-k group, lane (cc, g) converts k 4g..4g+3 of
+  // pass 2: a warp owns 32 / NW quads of columns; per quad and 32-k group, lane (cc, g) converts k 4g..4g+3 of
   // column cc of the quad, and the eight lanes of a column write 64 contiguous bytes of h0 and 64 of h1:
   // whole sectors, four lines per store instruction.
   const int cc = lane & 3, g = lane >> 2;
 #pragma unroll 1
-  for (int quad = warp * 4; quad < warp * 4 + 4; ++quad) {
+  for (int quad = warp * (32 / NW); quad < (warp + 1) * (32 / NW); ++quad) {
     const int tc = quad * 4 + cc;                    // column inside the tile
     const int sh = shift_of(colmax[tc]);
     const float scale = pow2f(sh);
@@ -235,12 +235,14 @@ pack_fast_kernel(PackSource src, PackedForm fr, PackedForm fc) {
 template <int OP, bool ROWS, bool COLS>
 static prad_status launch_fast(prad_ctx* ctx, const PackSource& src, int tiles_r, int tiles_c, const PackedForm& fr,
                                const PackedForm& fc) {
+  // with a stash (64 KB per tile) two CTAs of 16 warps hide the loads better than three of 8
+  constexpr int NT = COLS ? 512 : 256;
   const int smem = COLS ? 128 * 128 * (int)sizeof(float) : 0;
   if (COLS) {
     static std::atomic<uint64_t> done{0};
     const uint64_t bit = 1ull << (ctx->device & 63);
     if (!(done.load(std::memory_order_acquire) & bit)) {
-      const cudaError_t e = cudaFuncSetAttribute(pack_fast_kernel<OP, ROWS, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      const cudaError_t e = cudaFuncSetAttribute(pack_fast_kernel<OP, ROWS, COLS, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       if (e != cudaSuccess) {
         (void)cudaGetLastError();
         set_error("operand packing: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
@@ -249,7 +251,7 @@ static prad_status launch_fast(prad_ctx* ctx, const PackSource& src, int tiles_r
       done.fetch_or(bit, std::memory_order_release);
     }
   }
-  pack_fast_kernel<OP, ROWS, COLS><<<dim3((unsigned)tiles_c, (unsigned)tiles_r), 256, smem, ctx->stream>>>(src, fr, fc);
+  pack_fast_kernel<OP, ROWS, COLS, NT><<<dim3((unsigned)tiles_c, (unsigned)tiles_r), NT, smem, ctx->stream>>>(src, fr, fc);
   PRAD_LAUNCHED(ctx);
   return PRAD_OK;
 }
