@@ -774,8 +774,18 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
       constexpr uint32_t idesc = idesc_tf32(), idesc_h = idesc_bf16();
       uint32_t g = 0, gc = 0, qi = 0;   // units consumed, chunks started, tiles taken
       bool ok = true;
+      // -DPRAD_GEMM_STALL_PROBE: cycle counts of what this thread and one epilogue warp wait for, printed by
+      // CTA 0 at the end of every launch (a diagnostic build; the numbers quoted in the design notes come from it)
+#ifdef PRAD_GEMM_STALL_PROBE
+      long long w_full = 0, w_acc = 0, w_tile = 0;
+      const long long t_begin = clock64();
+#define PROBE_WAIT(acc, expr) { const long long p0_ = clock64(); expr; acc += clock64() - p0_; }
+#else
+#define PROBE_WAIT(acc, expr) { expr; }
+#endif
       while (ok) {
-        const int t = next_tile(qi++, 6, false);
+        int t;
+        PROBE_WAIT(w_tile, t = next_tile(qi++, 6, false));
         if (t < 0) break;
         int m0, n0, z, kb0, num_kb;
         tile_of(t, m0, n0, z, kb0, num_kb);
@@ -783,7 +793,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
         for (int ch = 0; ch < num_chunks && ok; ++ch, ++gc) {
           const uint32_t buf = gc & 1, use = gc >> 1;
           if (use > 0) {
-            ok = mbar_wait(acc_empty(buf), (use - 1) & 1, err_flag, 4);
+            PROBE_WAIT(w_acc, ok = mbar_wait(acc_empty(buf), (use - 1) & 1, err_flag, 4));
             if (!ok) break;
             tc_fence_after();
           }
@@ -793,7 +803,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
             if (PMODE == 3) {   // one unit: A (h0 | h1 per row), B likewise; three FP16 products, smallest first
               constexpr uint32_t idesc_q = idesc_fp16();
               const uint32_t slot = g & (UNITS - 1);
-              ok = mbar_wait(full_bar(slot), (g / UNITS) & 1, err_flag, 2);
+              PROBE_WAIT(w_full, ok = mbar_wait(full_bar(slot), (g / UNITS) & 1, err_flag, 2));
               if (!ok) break;
               tc_fence_after();
               const uint32_t st = base + slot * UNIT_BYTES;
@@ -847,6 +857,11 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
           umma_commit(acc_full(buf));    // chunk complete (arrives even after a give-up)
         }
       }
+#ifdef PRAD_GEMM_STALL_PROBE
+      if (blockIdx.x == 0)
+        printf("mma issuer: total %lld cycles, waited for operands %lld, for the accumulator %lld, for tiles %lld (units %u)\n",
+               clock64() - t_begin, w_full, w_acc, w_tile, g);
+#endif
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..9)
@@ -854,6 +869,10 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
     const int half = (warp - 2) >> 2;         // which 128 columns of the tile
     uint32_t gc = 0, qi = 0;
     bool ok = true;
+#ifdef PRAD_GEMM_STALL_PROBE
+    long long e_wait = 0, e_drain = 0, e_store = 0;
+    const long long e_begin = clock64();
+#endif
     while (ok) {
       const int t = next_tile(qi++, 7, true);
       if (t < 0) break;
@@ -888,9 +907,16 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
           __syncwarp();
           if (ch + 1 < num_chunks) fetch_scales(ch + 1);
         }
+#ifdef PRAD_GEMM_STALL_PROBE
+        const long long c1_ = clock64();
+#endif
         ok = __all_sync(0xffffffffu, mbar_wait(acc_full(buf), (gc >> 1) & 1, err_flag, 3));
         if (!ok) break;
         tc_fence_after();
+#ifdef PRAD_GEMM_STALL_PROBE
+        const long long c2_ = clock64();
+        e_wait += c2_ - c1_;
+#endif
         const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + buf * (uint32_t)BN + (uint32_t)(half * 128);
         if (PMODE == 3) {
           // eight columns per load, the next load in flight while the current eight are added: the live
@@ -929,11 +955,25 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty(buf));
+#ifdef PRAD_GEMM_STALL_PROBE
+        e_drain += clock64() - c2_;
+#endif
       }
+#ifdef PRAD_GEMM_STALL_PROBE
+      const long long st0_ = clock64();
+#endif
       if (!ok || *((volatile int*)err_flag) != 0) { ok = false; break; }
       float* Ct = C + (int64_t)z * ts.split_stride;
       epilogue_store_warp(sum, lane, m0 + sub * 32, n0 + half * 128, M, N, Ct, ldc, vecC, epi);
+#ifdef PRAD_GEMM_STALL_PROBE
+      e_store += clock64() - st0_;
+#endif
     }
+#ifdef PRAD_GEMM_STALL_PROBE
+    if (blockIdx.x == 0 && warp == 2 && lane == 0)
+      printf("epilogue warp: total %lld cycles, tiles %u, blocks %u: waited for a block %lld, summed blocks %lld, stored tiles %lld\n",
+             clock64() - e_begin, qi - 1, gc, e_wait, e_drain, e_store);
+#endif
   }
 
   // drain, as in the one-tile kernel
