@@ -45,6 +45,12 @@ def test_products_on_cta_pairs_match_single_ctas(engine, shape):
     engine.set_option("tc_pair", "0")
     assert_close(outs[1], O.matmul_forward(X, Y), _absprod(X, Y), f"pair product {shape}")
     np.testing.assert_array_equal(outs[0], outs[1])
+    # asking L2 for the row operand ahead of its loads changes nothing in the result
+    engine.set_option("tc_prefetch", "16")
+    out = engine.zeros((m, n), f)
+    engine.gemm_packed(PX, E.PACK_ROWS, PY, E.PACK_COLS, out)
+    engine.set_option("tc_prefetch", "0")
+    np.testing.assert_array_equal(outs[0], out.numpy())
 
 
 @pytest.mark.parametrize("blocks", [(0, 0), (128, 128), (256, 128), (128, 256), (256, 256)])
