@@ -101,8 +101,8 @@ const char* prad_version(void);
  *  "tc_reserve_sms" = n: SMs the persistent GEMM leaves idle (default 0);
  *  "tc_prefetch" = n (0..64, default 0): the product of packed operands asks L2 for the row operand's tile n k-blocks
  *    of 32 ahead of its load (measured: no gain on B200, the loads are not what the tensor pipe waits for);
- *  "tc_pair" = "0" | "1": products of packed operands on pairs of CTAs (tcgen05 cta_group::2: two neighbouring SMs
- *    share a 256 x 256 tile, each holding half of the column operand);
+ *  "tc_pair" = "1" (default) | "0": products of packed operands on pairs of CTAs (tcgen05 cta_group::2: two
+ *    neighbouring SMs share a 256 x 256 tile, each holding half of the column operand), or one CTA per 128 x 256 tile;
  *  "tc_panel_n" = n: column tiles per panel of the persistent GEMM's tile walk (0 = automatic: two
  *    panels when the column operand exceeds 40 MB, so that a panel of it stays in L2);
  *  "tc_pipeline" = "16x4" | "32x2" | "8x8" (k-block floats x stages of the tf32x3 kernel) */

@@ -1014,6 +1014,10 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
 //   * every CTA loads its own operand rows, drains its own TMEM rows and stores its own output rows;
 //   * the pair synchronises (barrier.cluster) after the barriers are initialised and before TMEM is freed,
 //     so no remote arrive meets an uninitialised barrier or a CTA that has left.
+//   * the accumulator hand-back of the other CTA's epilogue warps is a RELAXED remote arrive: with a release at
+//     cluster scope every arrive waited for the warp's outstanding global stores, and the tensor core stood idle
+//     for 28 % of the product waiting for accumulators (0.5 % with the relaxed arrive; what orders the TMEM reads
+//     is tcgen05.wait::ld + tcgen05.fence::before_thread_sync, and no memory is handed over).
 // Every wait is bounded as in the other kernels; a CTA that gives up sets the error flag, the other one
 // of the pair sees it in its own waits, and both still reach the final cluster barrier.
 namespace p2 {
@@ -1043,6 +1047,11 @@ __device__ __forceinline__ void cluster_sync_all() {
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// arrive that orders nothing but itself (the accumulator hand-back: the TMEM reads before it are ordered by
+// tcgen05.wait::ld and tcgen05.fence::before_thread_sync, and no memory is handed over)
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void st_shared_cluster(uint32_t cluster_addr, int v) {
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
@@ -1210,7 +1219,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         for (int kb = 0; kb < num_kb && ok; ++kb, ++g) {
           const int x = (kb0 + kb) * BK;
           const uint32_t slot = g % UNITS, round = g / UNITS;
-          if (round > 0 && !mbar_wait_cluster(empty_bar(slot), (round - 1) & 1, err_flag, 1)) { ok = false; break; }
+          if (round > 0 && !mbar_wait(empty_bar(slot), (round - 1) & 1, err_flag, 1)) { ok = false; break; }
           const uint32_t st = base + slot * UNIT_BYTES;
           // the leader announces the unit's bytes of both CTAs; both CTAs' loads complete on the leader's barrier
           if (leader) mbar_expect_tx(full_bar(slot), 2 * UNIT_BYTES);
@@ -1227,8 +1236,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       constexpr uint32_t idesc_q = idesc_fp16_pair();
       uint32_t g = 0, gc = 0, qi = 0;
       bool ok = true;
+#ifdef PRAD_GEMM_STALL_PROBE
+      long long w_full = 0, w_acc = 0, w_tile = 0;
+      const long long t_begin = clock64();
+#endif
       while (ok) {
-        const int t = next_tile(qi++, 6, false);
+        int t;
+        PROBE_WAIT(w_tile, t = next_tile(qi++, 6, false));
         if (t < 0) break;
         int m0, n0, z, kb0, num_kb;
         tile_of(t, m0, n0, z, kb0, num_kb);
@@ -1236,7 +1250,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         for (int ch = 0; ch < num_chunks && ok; ++ch, ++gc) {
           const uint32_t buf = gc & 1, use = gc >> 1;
           if (use > 0) {
-            ok = mbar_wait_cluster(acc_empty(buf), (use - 1) & 1, err_flag, 4);
+            PROBE_WAIT(w_acc, ok = mbar_wait_cluster(acc_empty(buf), (use - 1) & 1, err_flag, 4));
             if (!ok) break;
             tc_fence_after();
           }
@@ -1244,7 +1258,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const int kb_end = min(num_kb, (ch + 1) * ts.chunk_kb);
           for (int kb = ch * ts.chunk_kb; kb < kb_end && ok; ++kb, ++g) {
             const uint32_t slot = g % UNITS;
-            ok = mbar_wait_cluster(full_bar(slot), (g / UNITS) & 1, err_flag, 2);
+            PROBE_WAIT(w_full, ok = mbar_wait(full_bar(slot), (g / UNITS) & 1, err_flag, 2));
             if (!ok) break;
             tc_fence_after();
             const uint32_t st = base + slot * UNIT_BYTES;
@@ -1264,6 +1278,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           umma_commit_pair(mapa_shared(acc_full(buf), 1));
         }
       }
+#ifdef PRAD_GEMM_STALL_PROBE
+      if (blockIdx.x == 0)
+        printf("pair mma issuer: total %lld cycles, waited for operands %lld, for the accumulator %lld, for tiles %lld (units %u)\n",
+               clock64() - t_begin, w_full, w_acc, w_tile, g);
+#endif
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..9 of both CTAs)
@@ -1298,7 +1317,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         sb_slot[lane] = sb_next;
         __syncwarp();
         if (ch + 1 < num_chunks) fetch_scales(ch + 1);
-        ok = __all_sync(0xffffffffu, mbar_wait_cluster(acc_full(buf), (gc >> 1) & 1, err_flag, 3));
+        ok = __all_sync(0xffffffffu, mbar_wait(acc_full(buf), (gc >> 1) & 1, err_flag, 3));
         if (!ok) break;
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(sub * 32) << 16) + buf * (uint32_t)BN + (uint32_t)(half * 128);
@@ -1323,7 +1342,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(mapa_shared(acc_empty(buf), 0));
+        if (lane == 0) {
+          if (leader) mbar_arrive(acc_empty(buf));
+          else mbar_arrive_cluster_relaxed(mapa_shared(acc_empty(buf), 0));
+        }
       }
       if (!ok || *((volatile int*)err_flag) != 0) { ok = false; break; }
       float* Ct = C + (int64_t)z * ts.split_stride;

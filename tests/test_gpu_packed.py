@@ -23,7 +23,7 @@ def tile_engine(engine, request):
     (tcgen05 cta_group::2) that share a 256 x 256 tile."""
     engine.set_option("tc_pair", request.param)
     yield engine
-    engine.set_option("tc_pair", "0")
+    engine.set_option("tc_pair", "1")          # the default
 
 
 @pytest.mark.parametrize("shape", [(257, 640, 300), (1024, 2048, 768), (2100, 4096, 520)])
@@ -42,14 +42,15 @@ def test_products_on_cta_pairs_match_single_ctas(engine, shape):
         out = engine.zeros((m, n), f)
         engine.gemm_packed(PX, E.PACK_ROWS, PY, E.PACK_COLS, out)
         outs.append(out.numpy())
-    engine.set_option("tc_pair", "0")
     assert_close(outs[1], O.matmul_forward(X, Y), _absprod(X, Y), f"pair product {shape}")
     np.testing.assert_array_equal(outs[0], outs[1])
-    # asking L2 for the row operand ahead of its loads changes nothing in the result
+    # asking L2 for the row operand ahead of its loads changes nothing in the result (an option of the one-CTA kernel)
+    engine.set_option("tc_pair", "0")
     engine.set_option("tc_prefetch", "16")
     out = engine.zeros((m, n), f)
     engine.gemm_packed(PX, E.PACK_ROWS, PY, E.PACK_COLS, out)
     engine.set_option("tc_prefetch", "0")
+    engine.set_option("tc_pair", "1")          # the default
     np.testing.assert_array_equal(outs[0], out.numpy())
 
 
