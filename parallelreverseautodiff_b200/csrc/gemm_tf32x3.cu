@@ -98,6 +98,11 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// arrive without the release (CTA scope): for hand-backs that pass no memory on.  The default arrive is a
+// release, which makes the warp wait for its own outstanding stores first.
+__device__ __forceinline__ void mbar_arrive_relaxed(uint32_t bar) {
+  asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -954,7 +959,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(acc_empty(buf));
+        if (lane == 0) mbar_arrive_relaxed(acc_empty(buf));     // (the TMEM reads are ordered by the tcgen05 fence)
 #ifdef PRAD_GEMM_STALL_PROBE
         e_drain += clock64() - c2_;
 #endif
@@ -1343,7 +1348,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
-          if (leader) mbar_arrive(acc_empty(buf));
+          if (leader) mbar_arrive_relaxed(acc_empty(buf));
           else mbar_arrive_cluster_relaxed(mapa_shared(acc_empty(buf), 0));
         }
       }
