@@ -17,6 +17,7 @@ F32, F64 = 0, 1
 ACT_NONE, ACT_LEAKY_RELU, ACT_SIGMOID, ACT_TANH, ACT_GELU, ACT_RELU, ACT_AMPLIFIED_SIGMOID = range(7)
 ADAM_RMAD, ADAM_PRAD = 0, 1
 CLIP_NONE, CLIP_REFERENCE, CLIP_GLOBAL_NORM = 0, 1, 2
+DP_MARKS = 256          # PRAD_DP_MARKS: slots of prad_dp_mark
 PACK_ROWS, PACK_COLS = 1, 2
 
 _DT = {np.dtype(np.float32): F32, np.dtype(np.float64): F64}

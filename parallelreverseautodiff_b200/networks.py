@@ -325,8 +325,8 @@ class FeedForwardNetwork:
         if p in self._bcast_marks:
             self.eng.dp_wait_mark(p)
             self._bcast_marks.discard(p)
-            if not self._bcast_marks:
-                self._bcast_pending = False
+        elif self._bcast_pending and p >= E.DP_MARKS:
+            self._join_broadcasts()
 
     def _saved(self, l: int):
         """Tensor the activation of layer l keeps for Backward (1-based l)."""
@@ -431,8 +431,9 @@ class FeedForwardNetwork:
                 order = list(range(self.L - 1, -1, -1)) + list(range(self.L, len(self.params)))
             for i in order:
                 self.eng.dp_broadcast(self.params[i], self._owner(i))
-                self.eng.dp_mark(i)
-                self._bcast_marks.add(i)
+                if i < E.DP_MARKS:               # (a network with more tensors than marks joins the rest as a whole)
+                    self.eng.dp_mark(i)
+                    self._bcast_marks.add(i)
             self._bcast_pending = True
 
     # ---------------------------------------------------------------- end to end
