@@ -35,7 +35,9 @@ __global__ void __launch_bounds__(256)
 gemm_dmma_kernel(int M, int N, int K, double alpha, const double* __restrict__ A, int64_t lda,
                  const double* __restrict__ B, int64_t ldb, double beta, double* __restrict__ C,
                  int64_t ldc, int64_t sA, int64_t sB, int64_t sC, bool vecA, bool vecB, bool vecC,
-                 EpiParams<double> epi) {
+                 EpiParams<double> epi, int kslices = 1, int64_t kA = 0, int64_t kB = 0) {
+  // kslices > 1: blockIdx.z = batch * kslices + slice; slice s multiplies k range [s K, (s + 1) K) (operands kA / kB
+  // elements further on) into its own dense M x N block of C (sC apart, slices of a batch consecutive)
   constexpr int BM = 64, BN = 64, BK = 16, NT = 256, PAD = 8;
   __shared__ __align__(16) double As[2][BK][BM + PAD];
   __shared__ __align__(16) double Bs[2][BK][BN + PAD];
@@ -45,8 +47,14 @@ gemm_dmma_kernel(int M, int N, int K, double alpha, const double* __restrict__ A
   const int g = lane >> 2, q = lane & 3;                    // fragment row group / k index
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int64_t bz = blockIdx.z;
-  A += bz * sA;
-  B += bz * sB;
+  if (kslices > 1) {
+    const int64_t b = bz / kslices, sl = bz - b * kslices;
+    A += b * sA + sl * kA;
+    B += b * sB + sl * kB;
+  } else {
+    A += bz * sA;
+    B += bz * sB;
+  }
   C += bz * sC;
   const double* saved = epi.saved ? epi.saved + bz * sC : nullptr;
   double* z_out = epi.z_out ? epi.z_out + bz * sC : nullptr;
@@ -282,6 +290,23 @@ gemm_dmma_async_kernel(int M, int N, int K, double alpha, const double* __restri
   }
 }
 
+// C = alpha * (P_0 + P_1 + ...) + beta * C, slices added in order; P_s are dense M x N.
+__global__ void __launch_bounds__(256)
+splitk_combine_f64_kernel(const double* __restrict__ part, int splits, int64_t mn, int N, double* __restrict__ C,
+                          int64_t ldc, int64_t sC, double alpha, double beta) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  part += (int64_t)blockIdx.y * splits * mn;      // blockIdx.y = batch
+  C += (int64_t)blockIdx.y * sC;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < mn; i += stride) {
+    double acc = part[i];
+    for (int s = 1; s < splits; ++s) acc = __dadd_rn(acc, part[(int64_t)s * mn + i]);
+    const int64_t off = (i / N) * ldc + (i % N);
+    double v = __dmul_rn(alpha, acc);
+    if (beta != 0.0) v = (beta == 1.0) ? __dadd_rn(C[off], v) : fma(beta, C[off], v);
+    C[off] = v;
+  }
+}
+
 prad_status gemm_f64_dmma(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, double alpha,
                           const void* A, int lda, const void* B, int ldb, double beta, void* C,
                           int ldc, int batch, int64_t sA, int64_t sB, int64_t sC,
@@ -329,6 +354,41 @@ prad_status gemm_f64_dmma(prad_ctx* ctx, bool tA, bool tB, int M, int N, int K, 
 #undef PRAD_DMMA_ASYNC
     PRAD_LAUNCHED(ctx);
     return PRAD_OK;
+  }
+  // Few output tiles and a long k (the time-batched weight gradients of an LSTM: 128 x 1024 outputs over k = 2048 run on
+  // 32 CTAs): k is cut into slices that run as the "batch" dimension into scratch, and an ordered pass adds them.
+  const int64_t tiles = (int64_t)grid.x * grid.y * batch;
+  const bool plain = !e.bias && !e.z_out && e.act == PRAD_ACT_NONE && e.dact == PRAD_ACT_NONE;
+  if (plain && tiles * 2 <= ctx->sm_count && K >= 1024 && batch <= 65535) {
+    int S = (int)(ctx->sm_count / tiles);
+    if (S > K / 256) S = K / 256;
+    while (S > 1 && K % S != 0) --S;
+    if (S >= 2 && (int64_t)batch * S <= 65535) {
+      const int Ks = K / S;
+      const int64_t mn = (int64_t)M * N;
+      prad_status st = ensure_stage(ctx, (size_t)batch * S * mn * sizeof(double));
+      if (st) return st;
+      double* part = (double*)ctx->stage;
+      const int64_t zA = tA ? (int64_t)Ks * lda : Ks, zB = tB ? Ks : (int64_t)Ks * ldb;
+      const bool wA = vA && zA % 2 == 0, wB = vB && zB % 2 == 0;
+      const bool wC = N % 2 == 0;
+      dim3 gs(grid.x, grid.y, (unsigned)(batch * S));
+      EpiParams<double> none{nullptr, nullptr, 0, 0, nullptr, 0.0};
+#define PRAD_DMMA_SLICES(TA_, TB_)                                                                                 \
+  gemm_dmma_kernel<TA_, TB_><<<gs, 256, 0, ctx->stream>>>(M, N, Ks, 1.0, Ad, lda, Bd, ldb, 0.0, part, N, sA, sB, mn, \
+                                                          wA, wB, wC, none, S, zA, zB)
+      if (!tA && !tB) PRAD_DMMA_SLICES(false, false);
+      else if (!tA && tB) PRAD_DMMA_SLICES(false, true);
+      else if (tA && !tB) PRAD_DMMA_SLICES(true, false);
+      else PRAD_DMMA_SLICES(true, true);
+#undef PRAD_DMMA_SLICES
+      PRAD_LAUNCHED(ctx);
+      const int cg = stream_grid(ctx, mn, 256, 8);
+      splitk_combine_f64_kernel<<<dim3((unsigned)cg, (unsigned)batch), 256, 0, ctx->stream>>>(part, S, mn, N, Cd, ldc, sC,
+                                                                                           alpha, beta);
+      PRAD_LAUNCHED(ctx);
+      return PRAD_OK;
+    }
   }
 #define PRAD_DMMA_LAUNCH(TA_, TB_)                                                          \
   gemm_dmma_kernel<TA_, TB_><<<grid, 256, 0, ctx->stream>>>(M, N, K, alpha, Ad, lda, Bd, ldb, \

@@ -82,3 +82,34 @@ def test_dmma_large_tiles_with_the_asynchronous_ring(dmma_engine, shape):
     Y = eng.matmul_forward(a, b, bias=eng.upload(bias), Z_out=Z, act=E.ACT_TANH)
     assert_close(Z.numpy(), z, np.abs(A) @ np.abs(B) + 1.0, "Z (async dmma)")
     assert_close(Y.numpy(), O.tanh_forward(z), np.abs(A) @ np.abs(B) + 1.0, "tanh Z (async dmma)")
+
+
+@pytest.mark.parametrize("case", [(100, 2048, 130, 1), (128, 2048, 256, 4), (64, 3000, 66, 3), (33, 1024, 17, 2)])
+def test_dmma_few_tiles_over_a_long_k_are_cut_into_slices(dmma_engine, case):
+    """Outputs of a few tiles over k >= 1024 (the time-batched weight gradients of an LSTM) run as k slices
+    into scratch plus an ordered sum: one launch more, the same values, alpha and beta applied once, batches with
+    their own strides and a shared right operand."""
+    eng = dmma_engine
+    M, K, N, batch = case
+    r = rng(sum(case))
+    At = normal(r, (batch, K, M), 1.0, np.float64)          # A^T per batch: the product is At^T B
+    B = normal(r, (K, N), 1.0, np.float64)                  # shared by every batch (stride 0)
+    C0 = normal(r, (batch, M, N), 1.0, np.float64)
+    a, b, c = eng.upload(At), eng.upload(B), eng.upload(C0)
+    n0 = eng.launch_count()
+    eng.gemm(a, b, c, transA=True, alpha=0.25, beta=1.0, M=M, N=N, K=K, lda=M, ldb=N, ldc=N, batch=batch,
+             strideA=K * M, strideB=0, strideC=M * N)
+    assert eng.launch_count() == n0 + 2
+    ref = np.stack([C0[i] + 0.25 * (At[i].T @ B) for i in range(batch)])
+    mag = np.stack([np.abs(C0[i]) + 0.25 * (np.abs(At[i].T) @ np.abs(B)) for i in range(batch)])
+    assert_close(c.numpy(), ref, mag, "sliced At^T B")
+    # the other transpose forms through the public forward / backward of one product
+    A = uniform(r, (M, K), -1, 1, np.float64)
+    W = normal(r, (K, N), np.sqrt(2.0 / K), np.float64)
+    assert_close(eng.matmul_forward(eng.upload(A), eng.upload(W)).numpy(), O.matmul_forward(A, W),
+                 np.abs(A) @ np.abs(W), "sliced A W")
+    d = normal(r, (N, K), 1.0, np.float64)
+    X = normal(r, (M, K), 1.0, np.float64)
+    out = eng.empty((M, N), np.float64)
+    eng.gemm(eng.upload(X), eng.upload(d), out, transB=True, M=M, N=N, K=K, lda=K, ldb=K, ldc=N)
+    assert_close(out.numpy(), X @ d.T, np.abs(X) @ np.abs(d.T), "sliced X d^T")
