@@ -103,6 +103,9 @@ const char* prad_version(void);
  *    of 32 ahead of its load (measured: no gain on B200, the loads are not what the tensor pipe waits for);
  *  "tc_pair" = "1" (default) | "0": products of packed operands on pairs of CTAs (tcgen05 cta_group::2: two
  *    neighbouring SMs share a 256 x 256 tile, each holding half of the column operand), or one CTA per 128 x 256 tile;
+ *  "gemm_small" = "1" (default) | "0": strided batches of at least one product per SM whose outputs are at most
+ *    64 x 64 (per-window attention products) run on one CTA per product sized to the output, instead of 64 x 64 tiles;
+ *    the values are the same bit for bit;
  *  "tc_panel_n" = n: column tiles per panel of the persistent GEMM's tile walk (0 = automatic: two
  *    panels when the column operand exceeds 40 MB, so that a panel of it stays in L2);
  *  "tc_pipeline" = "16x4" | "32x2" | "8x8" (k-block floats x stages of the tf32x3 kernel) */

@@ -159,6 +159,11 @@ prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value) {
     ctx->tc_prefetch = n;
     return PRAD_OK;
   }
+  if (!strcmp(key, "gemm_small")) {
+    PRAD_REQUIRE(!strcmp(value, "0") || !strcmp(value, "1"), PRAD_ERR_INVALID, "prad_set_option: gemm_small must be 0 or 1, got '%s'", value);
+    ctx->gemm_small = atoi(value);
+    return PRAD_OK;
+  }
   if (!strcmp(key, "tc_pair")) {
     PRAD_REQUIRE(!strcmp(value, "0") || !strcmp(value, "1"), PRAD_ERR_INVALID, "prad_set_option: tc_pair must be 0 or 1, got '%s'", value);
     ctx->tc_pair = atoi(value);

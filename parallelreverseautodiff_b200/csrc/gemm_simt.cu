@@ -153,6 +153,149 @@ gemm_simt_kernel(int M, int N, int K, T alpha, const T* __restrict__ A, int64_t 
   }
 }
 
+// ---- many small products ----------------------------------------------------------------------
+// A strided batch of products whose whole output is at most 64 x 64 (the per-window, per-head
+// attention products Q K^T, P V and their four backward forms: 49 x 49 x 32 and 49 x 32 x 49).  The
+// 64 x 64 tile of the kernel above would spend more than half of its multiply-adds on rows, columns
+// and k beyond the matrices, and at these sizes the arithmetic, not the memory, is what takes the
+// time.  Here a CTA owns one product and has just the threads its output needs (4 x 4 outputs per
+// thread, rounded up to whole warps); both operands of up to KC values of k sit in shared memory in
+// k-major order, so a thread reads one 4-vector of each per k.  Same arithmetic per output element
+// as above (k ascending, one accumulator), hence bit-identical results.
+template <typename T> __device__ __forceinline__ void load4(const T* p, T (&v)[4]);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <> __device__ __forceinline__ void load4<double>(const double* p, double (&v)[4]) {
+  const double2 t = *reinterpret_cast<const double2*>(p), u = *reinterpret_cast<const double2*>(p + 2);
+  v[0] = t.x; v[1] = t.y; v[2] = u.x; v[3] = u.y;
+}
+
+// one operand chunk into shared memory as [k][XP]: X operand rows (M or N; columns X..XP-1 are zero-filled),
+// kc values of k starting at k0.  KMAJOR: memory is [K][X] (x contiguous), otherwise [X][K].
+template <typename T, bool KMAJOR>
+__device__ __forceinline__ void load_small_operand(T* __restrict__ s, int XP, const T* __restrict__ g, int64_t ld, int X,
+                                                   int k0, int kc, int warp, int lane, int nw) {
+  if (KMAJOR) {
+    for (int k = warp; k < kc; k += nw)
+      for (int x = lane; x < XP; x += 32) s[k * XP + x] = x < X ? g[(int64_t)(k0 + k) * ld + x] : (T)0;
+  } else {
+    for (int x = warp; x < XP; x += nw)
+      for (int k = lane; k < kc; k += 32) s[k * XP + x] = x < X ? g[(int64_t)x * ld + k0 + k] : (T)0;
+  }
+}
+
+template <typename T, bool TA, bool TB, bool EXACT>
+__global__ void __launch_bounds__(256)
+gemm_small_kernel(int M, int N, int K, int KC, int MP, int NP, T alpha, const T* __restrict__ A, int64_t lda,
+                  const T* __restrict__ B, int64_t ldb, T beta, T* __restrict__ C, int64_t ldc, int64_t sA, int64_t sB,
+                  int64_t sC, bool vecC) {
+  extern __shared__ __align__(16) unsigned char small_smem[];
+  T* As = reinterpret_cast<T*>(small_smem);   // [KC][MP]
+  T* Bs = As + KC * MP;                        // [KC][NP]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
+  const int txn = NP >> 2;
+  const int tx = tid % txn, ty = tid / txn;
+  const bool active = ty < (MP >> 2);
+  const int64_t bz = blockIdx.x;
+  A += bz * sA;
+  B += bz * sB;
+  C += bz * sC;
+
+  T acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = (T)0;
+
+  for (int k0 = 0; k0 < K; k0 += KC) {
+    const int kc = K - k0 < KC ? K - k0 : KC;
+    if (k0) __syncthreads();
+    load_small_operand<T, TA>(As, MP, A, lda, M, k0, kc, warp, lane, nw);     // op(A) is M x K: k-major memory when TA
+    load_small_operand<T, !TB>(Bs, NP, B, ldb, N, k0, kc, warp, lane, nw);    // op(B) is K x N: k-major memory unless TB
+    __syncthreads();
+    if (active) {
+      const T* ap = As + 4 * ty;
+      const T* bp = Bs + 4 * tx;
+#pragma unroll 4
+      for (int k = 0; k < kc; ++k) {
+        T a[4], b[4];
+        load4<T>(ap + k * MP, a);
+        load4<T>(bp + k * NP, b);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (EXACT) acc[i][j] = add_rn(acc[i][j], mul_rn(a[i], b[j]));
+            else acc[i][j] = fma(a[i], b[j], acc[i][j]);
+          }
+      }
+    }
+  }
+  if (!active) return;
+  const int n = 4 * tx;
+  const bool full = vecC && n + 4 <= N;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = 4 * ty + i;
+    if (m >= M) continue;
+    const int64_t off = (int64_t)m * ldc + n;
+    T out[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      T v = mul_rn(alpha, acc[i][q]);
+      if (beta != (T)0 && n + q < N) {
+        const T old = C[off + q];
+        v = (beta == (T)1) ? add_rn(old, v) : fma(beta, old, v);
+      }
+      out[q] = v;
+    }
+    if (full) {
+      if constexpr (sizeof(T) == 4) {
+        *reinterpret_cast<float4*>(C + off) = make_float4(out[0], out[1], out[2], out[3]);
+      } else {
+        *reinterpret_cast<double2*>(C + off) = make_double2(out[0], out[1]);
+        *reinterpret_cast<double2*>(C + off + 2) = make_double2(out[2], out[3]);
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        if (n + q < N) C[off + q] = out[q];
+    }
+  }
+}
+
+template <typename T>
+static prad_status launch_small(prad_ctx* ctx, bool exact, bool tA, bool tB, int M, int N, int K, T alpha, const T* A,
+                                int64_t lda, const T* B, int64_t ldb, T beta, T* C, int64_t ldc, int batch, int64_t sA,
+                                int64_t sB, int64_t sC) {
+  const int MP = (M + 3) & ~3, NP = (N + 3) & ~3;
+  const int kc_max = sizeof(T) == 4 ? 64 : 32;                  // at most 32 KB of shared memory
+  const int KC = K < kc_max ? K : kc_max;
+  int nt = (MP / 4) * (NP / 4);
+  nt = (nt + 31) & ~31;
+  if (nt < 64) nt = 64;
+  const size_t smem = (size_t)KC * (MP + NP) * sizeof(T);
+  const bool vC = (((uintptr_t)C & 15) == 0) && ldc % 4 == 0 && sC % 4 == 0;
+#define PRAD_SMALL_LAUNCH(TA_, TB_)                                                                          \
+  do {                                                                                                       \
+    if (exact)                                                                                               \
+      gemm_small_kernel<T, TA_, TB_, true><<<(unsigned)batch, nt, smem, ctx->stream>>>(                     \
+          M, N, K, KC, MP, NP, alpha, A, lda, B, ldb, beta, C, ldc, sA, sB, sC, vC);                         \
+    else                                                                                                     \
+      gemm_small_kernel<T, TA_, TB_, false><<<(unsigned)batch, nt, smem, ctx->stream>>>(                    \
+          M, N, K, KC, MP, NP, alpha, A, lda, B, ldb, beta, C, ldc, sA, sB, sC, vC);                         \
+  } while (0)
+  if (!tA && !tB) PRAD_SMALL_LAUNCH(false, false);
+  else if (!tA && tB) PRAD_SMALL_LAUNCH(false, true);
+  else if (tA && !tB) PRAD_SMALL_LAUNCH(true, false);
+  else PRAD_SMALL_LAUNCH(true, true);
+#undef PRAD_SMALL_LAUNCH
+  PRAD_LAUNCHED(ctx);
+  return PRAD_OK;
+}
+
 template <typename T> static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 
 template <typename T, int BM, int BN, int BK, int TM, int TN>
@@ -193,6 +336,11 @@ prad_status gemm_simt(prad_ctx* ctx, bool exact, bool tA, bool tB, int M, int N,
                       const GemmEpilogue& e) {
   EpiParams<T> epi{(const T*)e.bias, (T*)e.z_out, (int)e.act, (int)e.dact, (const T*)e.saved,
                    (T)e.act_alpha};
+  // a batch of products no larger than one small tile each, enough of them to fill the machine by themselves
+  const bool plain = !e.bias && !e.z_out && e.act == PRAD_ACT_NONE && e.dact == PRAD_ACT_NONE;
+  if (plain && M <= 64 && N <= 64 && K >= 1 && batch >= ctx->sm_count && ctx->gemm_small)
+    return launch_small<T>(ctx, exact, tA, tB, M, N, K, (T)alpha, (const T*)A, lda, (const T*)B, ldb, (T)beta, (T*)C, ldc,
+                           batch, sA, sB, sC);
   // tile choice: big tiles when the output fills the machine, small ones otherwise
   int64_t big_tiles = ceil_div(M, 128) * ceil_div(N, 128) * batch;
   const bool use_big = big_tiles >= ctx->sm_count && M >= 96 && N >= 96;

@@ -160,6 +160,49 @@ def test_batch_matmul(engine, dtype, shared):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(49, 32, 49), (49, 49, 32), (64, 64, 64), (5, 150, 7), (1, 1, 1), (33, 70, 64)])
+def test_many_small_products_take_one_cta_each(engine, dtype, shape):
+    """Strided batches of at least one product per SM with outputs of at most 64 x 64 (the attention products per
+    window and head) run on one CTA per product: bit-identical to the oracle's sequential sums and to the tiled
+    kernel, in every transpose form, with alpha and beta, addressing slices of wider matrices in place."""
+    M, K, N = shape
+    r = rng(sum(shape))
+    depth = 300
+    A = normal(r, (depth, M, K), 1, dtype)
+    B = normal(r, (depth, K, N), 1, dtype)
+    dC = normal(r, (depth, M, N), 1, dtype)
+    a, b, dc = engine.upload(A), engine.upload(B), engine.upload(dC)
+    wide_a = np.zeros((depth, M, K + 5), dtype)
+    wide_a[:, :, 3:3 + K] = A
+    wide_c0 = normal(r, (depth, M, N + 2), 1, dtype)
+    results = {}
+    for small in ("0", "1"):
+        engine.set_option("gemm_small", small)
+        try:
+            C = engine.batch_matmul_forward(a, b)
+            dA, dB, _ = engine.batch_matmul_backward(a, b, dc, per_slice_dB=True)
+            # in place: the product of batch i reads columns 3..3+K of a wide A and accumulates into columns 1..1+N of a wide C
+            wa, wc = engine.upload(wide_a), engine.upload(wide_c0)
+            engine.gemm(wa.view((1, 1), 3), b.view((1, 1), 0), wc.view((1, 1), 1), alpha=0.5, beta=1.0, M=M, N=N, K=K,
+                        lda=K + 5, ldb=N, ldc=N + 2, batch=depth, strideA=M * (K + 5), strideB=K * N, strideC=M * (N + 2))
+            results[small] = (C.numpy(), dA.numpy(), dB.numpy(), wc.numpy())
+        finally:
+            engine.set_option("gemm_small", "1")
+    C_ref = O.batch_matmul_forward(A, B)
+    dA_ref, dB_ref = O.batch_matmul_backward(A, B, dC)
+    for small in ("0", "1"):
+        C, dA, dB, wc = results[small]
+        wc0 = wide_c0
+        np.testing.assert_array_equal(C, C_ref)
+        np.testing.assert_array_equal(dA, dA_ref)
+        np.testing.assert_array_equal(dB, dB_ref)
+        half = (np.asarray(0.5, dtype) * C_ref).astype(dtype)
+        np.testing.assert_array_equal(wc[:, :, 1:1 + N], wc0[:, :, 1:1 + N] + half)
+        np.testing.assert_array_equal(wc[:, :, 0], wc0[:, :, 0])
+        np.testing.assert_array_equal(wc[:, :, N + 1], wc0[:, :, N + 1])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_matmul_and_sum(engine, dtype):
     r = rng(4)
     n, P = 24, 5
