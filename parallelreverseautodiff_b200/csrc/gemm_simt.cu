@@ -173,16 +173,38 @@ template <> __device__ __forceinline__ void load4<double>(const double* p, doubl
 }
 
 // one operand chunk into shared memory as [k][XP]: X operand rows (M or N; columns X..XP-1 are zero-filled),
-// kc values of k starting at k0.  KMAJOR: memory is [K][X] (x contiguous), otherwise [X][K].
+// kc values of k starting at k0.  KMAJOR: memory is [K][X] (x contiguous), otherwise [X][K].  A warp takes
+// every nw-th memory row, its lanes consecutive elements of it (at most 64: two trips); the loads of eight rows
+// are issued before the first of them is stored, so that a thread has up to sixteen loads in flight.
 template <typename T, bool KMAJOR>
 __device__ __forceinline__ void load_small_operand(T* __restrict__ s, int XP, const T* __restrict__ g, int64_t ld, int X,
                                                    int k0, int kc, int warp, int lane, int nw) {
-  if (KMAJOR) {
-    for (int k = warp; k < kc; k += nw)
-      for (int x = lane; x < XP; x += 32) s[k * XP + x] = x < X ? g[(int64_t)(k0 + k) * ld + x] : (T)0;
-  } else {
-    for (int x = warp; x < XP; x += nw)
-      for (int k = lane; k < kc; k += 32) s[k * XP + x] = x < X ? g[(int64_t)x * ld + k0 + k] : (T)0;
+  constexpr int U = 8;
+  const int rows = KMAJOR ? kc : XP;          // memory rows of the chunk (rows X..XP-1 of the [X][K] form are zeros)
+  const int cols = KMAJOR ? XP : kc;          // elements taken from each
+  const int rows_valid = KMAJOR ? kc : X, cols_valid = KMAJOR ? X : kc;
+  const T* base = KMAJOR ? g + (int64_t)k0 * ld : g + k0;
+  for (int r0 = warp; r0 < rows; r0 += nw * U) {
+    T v[U][2];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int r = r0 + u * nw;
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const int c = lane + 32 * t;
+        v[u][t] = (r < rows_valid && c < cols_valid) ? base[(int64_t)r * ld + c] : (T)0;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int r = r0 + u * nw;
+      if (r >= rows) break;
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const int c = lane + 32 * t;
+        if (c < cols) s[KMAJOR ? r * XP + c : c * XP + r] = v[u][t];
+      }
+    }
   }
 }
 
