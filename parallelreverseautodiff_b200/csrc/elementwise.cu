@@ -191,39 +191,60 @@ __global__ void colsum_final_kernel(const double* __restrict__ partial, T* __res
 // Streaming form of the same column sums for matrices whose rows are a whole number of
 // 128-bit vectors: the matrix is read like a copy (thread t takes vectors t, t+S, t+2S, ...
 // with S a multiple of the vectors per row, so a thread always sees the same column group),
-// every thread writes its partial sums, and one CTA per column group adds the partials of
-// the threads that share the group in thread order.  Fully coalesced, deterministic.
+// every CTA adds the sums of its threads that share a group (in thread order) and writes one
+// partial per group, and one CTA per column group adds the partials in CTA order.  Fully
+// coalesced, deterministic.
 template <typename T>
 __global__ void __launch_bounds__(256)
 colsum_flat_partial_kernel(const T* __restrict__ x, double* __restrict__ partial, int64_t nvec,
-                           int64_t stride_threads) {
+                           int64_t stride_threads, int vec_per_row) {
   constexpr int VEC = Vec16<T>::N;
   using V = typename Vec16<T>::type;
+  __shared__ double sm[256][VEC];
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= stride_threads) return;
   double acc[VEC];
 #pragma unroll
   for (int q = 0; q < VEC; ++q) acc[q] = 0.0;
-  const V* xv = reinterpret_cast<const V*>(x);
-  int64_t i = t;
-  for (; i + 3 * stride_threads < nvec; i += 4 * stride_threads) {   // four loads in flight
-    V v0 = __ldcs(xv + i), v1 = __ldcs(xv + i + stride_threads);
-    V v2 = __ldcs(xv + i + 2 * stride_threads), v3 = __ldcs(xv + i + 3 * stride_threads);
+  if (t < stride_threads) {
+    const V* xv = reinterpret_cast<const V*>(x);
+    int64_t i = t;
+    for (; i + 3 * stride_threads < nvec; i += 4 * stride_threads) {   // four loads in flight
+      V v0 = __ldcs(xv + i), v1 = __ldcs(xv + i + stride_threads);
+      V v2 = __ldcs(xv + i + 2 * stride_threads), v3 = __ldcs(xv + i + 3 * stride_threads);
 #pragma unroll
-    for (int q = 0; q < VEC; ++q) {
-      acc[q] += (double)reinterpret_cast<const T*>(&v0)[q];
-      acc[q] += (double)reinterpret_cast<const T*>(&v1)[q];
-      acc[q] += (double)reinterpret_cast<const T*>(&v2)[q];
-      acc[q] += (double)reinterpret_cast<const T*>(&v3)[q];
+      for (int q = 0; q < VEC; ++q) {
+        acc[q] += (double)reinterpret_cast<const T*>(&v0)[q];
+        acc[q] += (double)reinterpret_cast<const T*>(&v1)[q];
+        acc[q] += (double)reinterpret_cast<const T*>(&v2)[q];
+        acc[q] += (double)reinterpret_cast<const T*>(&v3)[q];
+      }
+    }
+    for (; i < nvec; i += stride_threads) {
+      V v = __ldcs(xv + i);
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) acc[q] += (double)reinterpret_cast<const T*>(&v)[q];
     }
   }
-  for (; i < nvec; i += stride_threads) {
-    V v = __ldcs(xv + i);
+  if (vec_per_row > 256) {          // fewer than one thread per column group in a CTA: every thread writes its own sums
+    if (t < stride_threads)
 #pragma unroll
-    for (int q = 0; q < VEC; ++q) acc[q] += (double)reinterpret_cast<const T*>(&v)[q];
+      for (int q = 0; q < VEC; ++q) partial[t * VEC + q] = acc[q];
+    return;
   }
+  // the threads of this CTA that share a column group (every vec_per_row-th) are added here, in thread order
 #pragma unroll
-  for (int q = 0; q < VEC; ++q) partial[t * VEC + q] = acc[q];
+  for (int q = 0; q < VEC; ++q) sm[threadIdx.x][q] = acc[q];
+  __syncthreads();
+  if ((int)threadIdx.x < vec_per_row) {
+    const int group = (int)(t % vec_per_row);
+#pragma unroll
+    for (int q = 0; q < VEC; ++q) acc[q] = 0.0;
+    for (int j = threadIdx.x; j < 256; j += vec_per_row)
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) acc[q] += sm[j][q];
+#pragma unroll
+    for (int q = 0; q < VEC; ++q) partial[((int64_t)blockIdx.x * vec_per_row + group) * VEC + q] = acc[q];
+  }
 }
 
 template <typename T>
@@ -269,11 +290,14 @@ static prad_status add_broadcast_backward_t(prad_ctx* ctx, const void* dy, void*
     if (threads >= vec_per_row) {
       prad_status s = ensure_workspace(ctx, (size_t)threads * VEC * sizeof(double));
       if (s) return s;
-      colsum_flat_partial_kernel<T><<<(unsigned)ceil_div(threads, 256), 256, 0, ctx->stream>>>(
-          (const T*)dy, (double*)ctx->ws, nvec, threads);
+      const int64_t ctas = ceil_div(threads, 256);
+      colsum_flat_partial_kernel<T><<<(unsigned)ctas, 256, 0, ctx->stream>>>((const T*)dy, (double*)ctx->ws, nvec, threads,
+                                                                           vec_per_row);
       PRAD_LAUNCHED(ctx);
+      // entries the final pass adds per column group: one per CTA, or one per thread for very wide rows
+      const int64_t entries = vec_per_row <= 256 ? ctas * vec_per_row : threads;
       colsum_flat_final_kernel<T><<<vec_per_row, 128, 0, ctx->stream>>>((const double*)ctx->ws, (T*)dbias,
-                                                                      vec_per_row, threads, accumulate);
+                                                                      vec_per_row, entries, accumulate);
       PRAD_LAUNCHED(ctx);
       return PRAD_OK;
     }

@@ -140,16 +140,22 @@ __device__ __forceinline__ float apply_op(const PackSource& s, float a, float d,
 // of tile row k sits in slot q ^ ((k >> 2) & 7) of its row.  Pass 1 stores whole float4 (any permutation of
 // slots is conflict-free); in pass 2 a lane reads four consecutive k of one column and the eight lanes that
 // share a column quad read eight different slot positions: 32 different banks.
-template <int OP, bool ROWS, bool COLS, int NT>
+//
+// EDGE: the one column tile that the matrix fills only in part (C is a multiple of four, so whole float4 lie inside or
+// outside): columns from C on read as zeros, pieces are written up to the padded k of the by-rows form and for the
+// existing operand rows of the by-columns form only.
+template <int OP, bool ROWS, bool COLS, int NT, bool EDGE>
 __global__ void __launch_bounds__(NT, NT == 512 ? 2 : (OP == 0 ? 5 : 3))
-pack_fast_kernel(PackSource src, PackedForm fr, PackedForm fc) {
+pack_fast_kernel(PackSource src, PackedForm fr, PackedForm fc, int tile_c0, int C) {
   constexpr int T = 128, U = 2, NW = NT / 32, NB = T / NW / U;      // NW warps, each takes every NW-th tile row
   constexpr bool HAS_DY = OP >= 4 && OP != 9, HAS_TG = OP == 7 || OP == 8 || OP == 11;
   extern __shared__ float stash[];       // [T][T] when COLS
   __shared__ unsigned colmax[T];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t r0 = (int64_t)blockIdx.y * T;
-  const int c0 = blockIdx.x * T, c = c0 + lane * 4;
+  const int ctile = tile_c0 + blockIdx.x;
+  const int c0 = ctile * T, c = c0 + lane * 4;
+  const bool inside = !EDGE || c < C;                  // this lane's four columns exist
   if (COLS && threadIdx.x < T) colmax[threadIdx.x] = 0;
   uint32_t cm[4] = {0, 0, 0, 0};
   // pass 1: the loads of the next two tile rows are in flight while the current two are converted
@@ -158,6 +164,10 @@ pack_fast_kernel(PackSource src, PackedForm fr, PackedForm fc) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int64_t off = (r0 + warp + NW * (b * U + u)) * src.ld + c;
+      if (EDGE && !inside) {
+        a[buf][u] = d[buf][u] = tg[buf][u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        continue;
+      }
       a[buf][u] = __ldcs(reinterpret_cast<const float4*>(src.x + off));
       if (HAS_DY) d[buf][u] = __ldcs(reinterpret_cast<const float4*>(src.dy + off));
       if (HAS_TG) tg[buf][u] = __ldcs(reinterpret_cast<const float4*>(src.target + off));
@@ -177,7 +187,8 @@ pack_fast_kernel(PackSource src, PackedForm fr, PackedForm fc) {
       v[1] = apply_op<OP>(src, a[cur][u].y, HAS_DY ? d[cur][u].y : 0.f, HAS_TG ? tg[cur][u].y : 0.f);
       v[2] = apply_op<OP>(src, a[cur][u].z, HAS_DY ? d[cur][u].z : 0.f, HAS_TG ? tg[cur][u].z : 0.f);
       v[3] = apply_op<OP>(src, a[cur][u].w, HAS_DY ? d[cur][u].w : 0.f, HAS_TG ? tg[cur][u].w : 0.f);
-      if (OP >= 1 && OP <= 8 && src.out)
+      if (EDGE && !inside) v[0] = v[1] = v[2] = v[3] = 0.f;      // an activation of zero need not be zero
+      if (OP >= 1 && OP <= 8 && src.out && inside)
         __stcs(reinterpret_cast<float4*>(src.out + r * src.ld + c), make_float4(v[0], v[1], v[2], v[3]));
       uint32_t m = 0;
 #pragma unroll
@@ -193,13 +204,15 @@ pack_fast_kernel(PackSource src, PackedForm fr, PackedForm fc) {
         for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
         const int sh = shift_of(m);
         const float scale = pow2f(sh);
-        if (lane == 0) fr.blk[(int64_t)blockIdx.x * fr.rows_ld + r] = pow2f(-sh);
+        if (lane == 0) fr.blk[(int64_t)ctile * fr.rows_ld + r] = pow2f(-sh);
         __half2 p0[2], p1[2];
         pieces2(v[0] * scale, v[1] * scale, p0[0], p1[0]);
         pieces2(v[2] * scale, v[3] * scale, p0[1], p1[1]);
         __half* dst = fr.h + r * fr.pitch + (int64_t)(c >> 5) * 64 + (c & 31);
-        *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(p0);
-        *reinterpret_cast<uint2*>(dst + 32) = *reinterpret_cast<const uint2*>(p1);
+        if (!EDGE || c < fr.kp) {                          // the row is padded with zeros up to kp and ends there
+          *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(p0);
+          *reinterpret_cast<uint2*>(dst + 32) = *reinterpret_cast<const uint2*>(p1);
+        }
       }
     }
   }
@@ -216,6 +229,7 @@ pack_fast_kernel(PackSource src, PackedForm fr, PackedForm fc) {
 #pragma unroll 1
   for (int quad = warp * (32 / NW); quad < (warp + 1) * (32 / NW); ++quad) {
     const int tc = quad * 4 + cc;                    // column inside the tile
+    if (EDGE && c0 + quad * 4 >= C) break;           // no operand rows from here on (whole quads: C is a multiple of 4)
     const int sh = shift_of(colmax[tc]);
     const float scale = pow2f(sh);
     if (g == 0) fc.blk[(int64_t)blockIdx.y * fc.rows_ld + c0 + tc] = pow2f(-sh);
@@ -234,7 +248,7 @@ pack_fast_kernel(PackSource src, PackedForm fr, PackedForm fc) {
 
 template <int OP, bool ROWS, bool COLS>
 static prad_status launch_fast(prad_ctx* ctx, const PackSource& src, int tiles_r, int tiles_c, const PackedForm& fr,
-                               const PackedForm& fc) {
+                               const PackedForm& fc, int C, bool edge) {
   // with a stash (64 KB per tile) two CTAs of 16 warps hide the loads better than three of 8
   constexpr int NT = COLS ? 512 : 256;
   const int smem = COLS ? 128 * 128 * (int)sizeof(float) : 0;
@@ -242,7 +256,9 @@ static prad_status launch_fast(prad_ctx* ctx, const PackSource& src, int tiles_r
     static std::atomic<uint64_t> done{0};
     const uint64_t bit = 1ull << (ctx->device & 63);
     if (!(done.load(std::memory_order_acquire) & bit)) {
-      const cudaError_t e = cudaFuncSetAttribute(pack_fast_kernel<OP, ROWS, COLS, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      cudaError_t e = cudaFuncSetAttribute(pack_fast_kernel<OP, ROWS, COLS, NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(pack_fast_kernel<OP, ROWS, COLS, NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       if (e != cudaSuccess) {
         (void)cudaGetLastError();
         set_error("operand packing: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
@@ -251,16 +267,22 @@ static prad_status launch_fast(prad_ctx* ctx, const PackSource& src, int tiles_r
       done.fetch_or(bit, std::memory_order_release);
     }
   }
-  pack_fast_kernel<OP, ROWS, COLS, NT><<<dim3((unsigned)tiles_c, (unsigned)tiles_r), NT, smem, ctx->stream>>>(src, fr, fc);
-  PRAD_LAUNCHED(ctx);
+  if (tiles_c > 0) {
+    pack_fast_kernel<OP, ROWS, COLS, NT, false><<<dim3((unsigned)tiles_c, (unsigned)tiles_r), NT, smem, ctx->stream>>>(src, fr, fc, 0, C);
+    PRAD_LAUNCHED(ctx);
+  }
+  if (edge) {
+    pack_fast_kernel<OP, ROWS, COLS, NT, true><<<dim3(1u, (unsigned)tiles_r), NT, smem, ctx->stream>>>(src, fr, fc, tiles_c, C);
+    PRAD_LAUNCHED(ctx);
+  }
   return PRAD_OK;
 }
 template <int OP>
 static prad_status launch_fast_forms(prad_ctx* ctx, const PackSource& src, int tiles_r, int tiles_c, const PackedForm& fr,
-                                     const PackedForm& fc) {
-  if (fr.h && fc.h) return launch_fast<OP, true, true>(ctx, src, tiles_r, tiles_c, fr, fc);
-  if (fr.h) return launch_fast<OP, true, false>(ctx, src, tiles_r, tiles_c, fr, fc);
-  return launch_fast<OP, false, true>(ctx, src, tiles_r, tiles_c, fr, fc);
+                                     const PackedForm& fc, int C, bool edge) {
+  if (fr.h && fc.h) return launch_fast<OP, true, true>(ctx, src, tiles_r, tiles_c, fr, fc, C, edge);
+  if (fr.h) return launch_fast<OP, true, false>(ctx, src, tiles_r, tiles_c, fr, fc, C, edge);
+  return launch_fast<OP, false, true>(ctx, src, tiles_r, tiles_c, fr, fc, C, edge);
 }
 // which compile-time operation serves this source
 static int fast_op_of(const PackSource& s) {
@@ -434,25 +456,28 @@ prad_status pack_fp16(prad_ctx* ctx, const PackSource& src, int R, int C, const 
   if (tc == 256) return pk::launch_pack<128, 256>(ctx, src, vec, R, C, fr, fc);
   // 128-long blocks: interior tiles through the specialised kernel, the ragged edges through the general one
   int fr_t = 0, fc_t = 0;
-  if (vec && R >= 128 && C >= 128) {
+  if (vec && R >= 128 && (C >= 128 || C % 4 == 0)) {
     fr_t = R / 128;
     fc_t = C / 128;
+    // the last, partly filled column tile takes the same kernel when whole float4 lie inside or outside the matrix
+    const bool edge = C % 128 != 0 && C % 4 == 0;
     prad_status s = PRAD_OK;
     switch (pk::fast_op_of(src)) {
-      case 0: s = pk::launch_fast_forms<0>(ctx, src, fr_t, fc_t, fr, fc); break;
-      case 1: s = pk::launch_fast_forms<1>(ctx, src, fr_t, fc_t, fr, fc); break;
-      case 2: s = pk::launch_fast_forms<2>(ctx, src, fr_t, fc_t, fr, fc); break;
-      case 3: s = pk::launch_fast_forms<3>(ctx, src, fr_t, fc_t, fr, fc); break;
-      case 4: s = pk::launch_fast_forms<4>(ctx, src, fr_t, fc_t, fr, fc); break;
-      case 5: s = pk::launch_fast_forms<5>(ctx, src, fr_t, fc_t, fr, fc); break;
-      case 6: s = pk::launch_fast_forms<6>(ctx, src, fr_t, fc_t, fr, fc); break;
-      case 7: s = pk::launch_fast_forms<7>(ctx, src, fr_t, fc_t, fr, fc); break;
-      case 8: s = pk::launch_fast_forms<8>(ctx, src, fr_t, fc_t, fr, fc); break;
-      case 9: s = pk::launch_fast_forms<9>(ctx, src, fr_t, fc_t, fr, fc); break;
-      case 10: s = pk::launch_fast_forms<10>(ctx, src, fr_t, fc_t, fr, fc); break;
-      default: s = pk::launch_fast_forms<11>(ctx, src, fr_t, fc_t, fr, fc); break;
+      case 0: s = pk::launch_fast_forms<0>(ctx, src, fr_t, fc_t, fr, fc, C, edge); break;
+      case 1: s = pk::launch_fast_forms<1>(ctx, src, fr_t, fc_t, fr, fc, C, edge); break;
+      case 2: s = pk::launch_fast_forms<2>(ctx, src, fr_t, fc_t, fr, fc, C, edge); break;
+      case 3: s = pk::launch_fast_forms<3>(ctx, src, fr_t, fc_t, fr, fc, C, edge); break;
+      case 4: s = pk::launch_fast_forms<4>(ctx, src, fr_t, fc_t, fr, fc, C, edge); break;
+      case 5: s = pk::launch_fast_forms<5>(ctx, src, fr_t, fc_t, fr, fc, C, edge); break;
+      case 6: s = pk::launch_fast_forms<6>(ctx, src, fr_t, fc_t, fr, fc, C, edge); break;
+      case 7: s = pk::launch_fast_forms<7>(ctx, src, fr_t, fc_t, fr, fc, C, edge); break;
+      case 8: s = pk::launch_fast_forms<8>(ctx, src, fr_t, fc_t, fr, fc, C, edge); break;
+      case 9: s = pk::launch_fast_forms<9>(ctx, src, fr_t, fc_t, fr, fc, C, edge); break;
+      case 10: s = pk::launch_fast_forms<10>(ctx, src, fr_t, fc_t, fr, fc, C, edge); break;
+      default: s = pk::launch_fast_forms<11>(ctx, src, fr_t, fc_t, fr, fc, C, edge); break;
     }
     if (s) return s;
+    if (edge) ++fc_t;
   }
   return pk::launch_pack<128, 128>(ctx, src, vec, R, C, fr, fc, fr_t, fc_t);
 }

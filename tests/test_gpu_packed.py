@@ -55,7 +55,8 @@ def test_products_on_cta_pairs_match_single_ctas(engine, shape):
 
 
 @pytest.mark.parametrize("blocks", [(0, 0), (128, 128), (256, 128), (128, 256), (256, 256)])
-@pytest.mark.parametrize("shape", [(300, 200, 130), (512, 384, 256), (77, 1000, 33), (1, 40, 5), (260, 129, 257)])
+@pytest.mark.parametrize("shape", [(300, 200, 130), (512, 384, 256), (77, 1000, 33), (1, 40, 5), (260, 129, 257),
+                                   (256, 96, 288)])
 def test_products_of_packed_operands(tile_engine, shape, blocks):
     """C = X Y for X (m x k), Y (k x n) through every pairing of forms: X by rows, Y by columns; and the two
     backward shapes dX = dC Y^T (dC by rows, Y by rows), dY = X^T dC (X by columns, dC by columns)."""
@@ -92,7 +93,7 @@ def test_products_of_packed_operands(tile_engine, shape, blocks):
     assert_close(out2.numpy(), want, _absprod(X, Y) + np.abs(base) + 1.0, f"packed alpha beta bias {shape} {blocks}")
 
 
-@pytest.mark.parametrize("act", [E.ACT_GELU, E.ACT_LEAKY_RELU, E.ACT_TANH, E.ACT_NONE])
+@pytest.mark.parametrize("act", [E.ACT_GELU, E.ACT_LEAKY_RELU, E.ACT_TANH, E.ACT_SIGMOID, E.ACT_NONE])
 def test_activation_written_in_packed_form(engine, act):
     """y = act(x) and dx = dy * act'(saved) packed on the fly: the FP32 copies are bit-identical to the
     stand-alone activation kernels, and products of the packed results match the oracle's."""
@@ -113,16 +114,17 @@ def test_activation_written_in_packed_form(engine, act):
     out = engine.empty((m, n), f)
     engine.gemm_packed(P, E.PACK_ROWS, PW, E.PACK_COLS, out)
     ref_y = {E.ACT_GELU: O.gelu_forward, E.ACT_LEAKY_RELU: lambda v: O.leaky_relu_forward(v, f(0.01)), E.ACT_TANH: O.tanh_forward,
-             E.ACT_NONE: lambda v: v}[act](x)
+             E.ACT_SIGMOID: O.sigmoid_forward, E.ACT_NONE: lambda v: v}[act](x)
     assert_close(out.numpy(), O.matmul_forward(ref_y, W), _absprod(ref_y, W), f"act {act} forward packed product")
-    # backward: the saved tensor is the input for GELU / LeakyReLU, the output for Tanh
-    saved = ref_y if act == E.ACT_TANH else x
+    # backward: the saved tensor is the input for GELU / LeakyReLU, the output for Tanh and Sigmoid (whose value at
+    # the zeros beyond a partly filled column tile is not zero: those must not reach the padding of the operand)
+    saved = ref_y if act in (E.ACT_TANH, E.ACT_SIGMOID) else x
     dx = engine.empty((m, k), f)
     P.act_backward(act, engine.upload(saved) if act != E.ACT_NONE else None, dyd, dx, 0.01)
     dx_alone = engine.act_backward(act, engine.upload(saved), dyd, 0.01).numpy() if act != E.ACT_NONE else dy
     np.testing.assert_array_equal(dx.numpy(), dx_alone)
     ref_dx = {E.ACT_GELU: O.gelu_backward, E.ACT_LEAKY_RELU: lambda s, d: O.leaky_relu_backward(s, d, f(0.01)),
-              E.ACT_TANH: O.tanh_backward, E.ACT_NONE: lambda s, d: d}[act](saved, dy)
+              E.ACT_TANH: O.tanh_backward, E.ACT_SIGMOID: O.sigmoid_backward, E.ACT_NONE: lambda s, d: d}[act](saved, dy)
     # weight-gradient shape: (k x m) (m x n'), both by columns
     G = (r.standard_normal((m, n)) * 1e-3).astype(f)
     PG = engine.packed(m, n, both).pack(engine.upload(G))

@@ -36,8 +36,9 @@ def test_tf32x3_matmul_forward_backward(tc_engine, shape):
     C = eng.matmul_forward(a, b).numpy()
     dA, dB = eng.matmul_backward(a, b, dc)
     # 3 products x (2 operand passes + 1 GEMM) (+ split-K combine); the FP16 scheme packs ragged
-    # operands with one launch for the interior tiles and one for the edges
-    assert 9 <= eng.launch_count() - n0 <= 16
+    # operands with one launch for the interior tiles, one for a partly filled last column tile and
+    # one for what is left at the edges
+    assert 9 <= eng.launch_count() - n0 <= 24
     assert_close(C, O.matmul_forward(A, B), np.abs(A).astype(np.float64) @ np.abs(B), "C")
     dA_ref, dB_ref = O.matmul_backward(A, B, dC)
     assert_close(dA.numpy(), dA_ref, np.abs(dC).astype(np.float64) @ np.abs(B.T), "dA")
