@@ -594,6 +594,42 @@ __device__ __forceinline__ void epilogue_quad(float o0, float o1, float o2, floa
 __device__ __forceinline__ void epilogue_store_warp(float (&sum)[4][32], int lane, int row0, int col0, int M, int N,
                                                     float* __restrict__ C, int64_t ldc, bool vecC, const Epi& epi) {
   const int qrow = row0 + 4 * (lane >> 2), i = lane & 3;
+  // A tile inside the matrix with a plain epilogue (nearly every store of a large product): no bounds tests, no
+  // per-quad address arithmetic -- four row pointers and immediate offsets.  This is about instruction fetch, not about
+  // executed work: the straight-line store code runs once per tile, so it is fetched anew every time, and the warps
+  // waited for instructions more than for anything else while it ran (warp state statistics of a short-k product:
+  // "no instruction" four cycles per issued instruction).  The general path below is three times as long.
+  // (Columns: the warp's 128 or, at the right edge, a multiple of 16, so that each store instruction is all or nothing.)
+  const int ncols = N - col0 < 128 ? N - col0 : 128;
+  if (ncols <= 0 || row0 >= M) return;
+  if (vecC && epi.beta == 0.f && !epi.bias && !epi.row_exp && row0 + 32 <= M && (ncols & 15) == 0) {
+    float* rp[4];
+#pragma unroll
+    for (int s = 0; s < 4; ++s) rp[s] = C + (int64_t)(qrow + s) * ldc + col0 + 4 * i;
+    if (epi.alpha != 1.f) {
+      const float alpha = epi.alpha;
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+#pragma unroll
+        for (int j = 0; j < 32; ++j) sum[g][j] = alpha * sum[g][j];
+    }
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (32 * g >= ncols) break;
+      quad_transpose(sum[g], lane);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        if (32 * g + 16 * h >= ncols) break;
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          const int j = 4 * (s + 4 * h);
+          __stcs(reinterpret_cast<float4*>(rp[s] + 32 * g + 16 * h),
+                 make_float4(sum[g][j], sum[g][j + 1], sum[g][j + 2], sum[g][j + 3]));
+        }
+      }
+    }
+    return;
+  }
   int er[4] = {0, 0, 0, 0};
   if (epi.row_exp) {
 #pragma unroll
