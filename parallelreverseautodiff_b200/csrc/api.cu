@@ -165,7 +165,7 @@ prad_status prad_set_option(prad_ctx* ctx, const char* key, const char* value) {
     return PRAD_OK;
   }
   if (!strcmp(key, "tc_pair")) {
-    PRAD_REQUIRE(!strcmp(value, "0") || !strcmp(value, "1"), PRAD_ERR_INVALID, "prad_set_option: tc_pair must be 0 or 1, got '%s'", value);
+    PRAD_REQUIRE(!strcmp(value, "0") || !strcmp(value, "1") || !strcmp(value, "2"), PRAD_ERR_INVALID, "prad_set_option: tc_pair must be 0, 1 or 2, got '%s'", value);
     ctx->tc_pair = atoi(value);
     return PRAD_OK;
   }

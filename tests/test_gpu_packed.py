@@ -17,10 +17,11 @@ def _absprod(a, b):
     return np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)
 
 
-@pytest.fixture(params=["0", "1"], ids=["one CTA per tile", "CTA pairs"])
+@pytest.fixture(params=["0", "2"], ids=["one CTA per tile", "CTA pairs"])
 def tile_engine(engine, request):
     """The engine with products of packed operands on one CTA per 128 x 256 tile, or on pairs of CTAs
-    (tcgen05 cta_group::2) that share a 256 x 256 tile."""
+    (tcgen05 cta_group::2) that share a 256 x 256 tile ("2": also for k below 1024, where the default
+    would take single CTAs)."""
     engine.set_option("tc_pair", request.param)
     yield engine
     engine.set_option("tc_pair", "1")          # the default
@@ -37,7 +38,7 @@ def test_products_on_cta_pairs_match_single_ctas(engine, shape):
     PX = engine.packed(m, k, E.PACK_ROWS).pack(engine.upload(X))
     PY = engine.packed(k, n, E.PACK_COLS, 0, PX.blocks()[0]).pack(engine.upload(Y))
     outs = []
-    for mode in ("0", "1"):
+    for mode in ("0", "2"):
         engine.set_option("tc_pair", mode)
         out = engine.zeros((m, n), f)
         engine.gemm_packed(PX, E.PACK_ROWS, PY, E.PACK_COLS, out)
