@@ -171,6 +171,21 @@ def packed_operands(eng, rows=16384, width=4096, block_cols=0):
         print(f"packed {name:14s} {ms:8.3f} ms {fl / ms / 1e9:7.1f} TFLOP/s", flush=True)
 
 
+def short_k_products(eng, rows=200704):
+    """Products of packed operands with a short k and few columns (the input-gradient products of a narrow
+    network: rows x 96 over k = 96 or 384, rows x 384 over k = 96): what they take is their tile stores."""
+    f = np.float32
+    t = _Timer(eng)
+    r = np.random.default_rng(0)
+    for K, N in ((96, 96), (384, 96), (96, 384)):
+        PA = eng.packed(rows, K, E.PACK_ROWS, 128, 128).pack(eng.upload(r.standard_normal((rows, K), dtype=f)))
+        PW = eng.packed(N, K, E.PACK_ROWS, 128, 128).pack(eng.upload(r.standard_normal((N, K), dtype=f)))
+        out = eng.empty((rows, N), f)
+        ms = t(lambda: eng.gemm_packed(PA, E.PACK_ROWS, PW, E.PACK_ROWS, out), iters=5, warm=2)
+        nbytes = rows * (2 * K + 64) * 2 + rows * N * 4
+        print(f"{rows} x {N} over k = {K}: {ms * 1e3:8.1f} us {nbytes / ms / 1e6:7.0f} GB/s (pieces read + output written)", flush=True)
+
+
 def f64_variants(eng, n=4096):
     """Double-precision GEMM variants at n^3 and the device's FP64 multiply-add rate (a register-resident
     chain of independent FMAs per thread, every SM full), the denominator for the FP64 kernels."""
@@ -199,6 +214,7 @@ def main():
     ap.add_argument("--gemm", action="store_true")
     ap.add_argument("--packed", action="store_true")
     ap.add_argument("--f64", action="store_true")
+    ap.add_argument("--short-k", action="store_true", help="packed products with k of 96 .. 384")
     ap.add_argument("--block-cols", type=int, default=0, help="--packed: block length of the by-columns forms (0, 128, 256)")
     ap.add_argument("--rows", type=int, default=None)
     ap.add_argument("--opt", action="append", default=[], metavar="KEY=VALUE", help="prad_set_option before running")
@@ -209,6 +225,8 @@ def main():
             eng.set_option(*kv.split("=", 1))
         if args.packed:
             packed_operands(eng, rows=args.rows or 16384, block_cols=args.block_cols)
+        elif args.short_k:
+            short_k_products(eng, rows=args.rows or 200704)
         elif args.f64:
             f64_variants(eng, n=args.rows or 4096)
         elif args.gemm:
