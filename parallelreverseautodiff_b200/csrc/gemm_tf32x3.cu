@@ -1003,9 +1003,12 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __gri
 #ifdef PRAD_GEMM_STALL_PROBE
       const long long st0_ = clock64();
 #endif
-      if (!ok || *((volatile int*)err_flag) != 0) { ok = false; break; }
+      if (!ok) break;
+      // has another CTA given up?  Asked before the stores and looked at after them: the answer takes a trip to L2
+      const int gave_up = *((volatile int*)err_flag);
       float* Ct = C + (int64_t)z * ts.split_stride;
       epilogue_store_warp(sum, lane, m0 + sub * 32, n0 + half * 128, M, N, Ct, ldc, vecC, epi);
+      if (gave_up != 0) { ok = false; break; }
 #ifdef PRAD_GEMM_STALL_PROBE
       e_store += clock64() - st0_;
 #endif
@@ -1388,9 +1391,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           else mbar_arrive_cluster_relaxed(mapa_shared(acc_empty(buf), 0));
         }
       }
-      if (!ok || *((volatile int*)err_flag) != 0) { ok = false; break; }
+      if (!ok) break;
+      // has another CTA given up?  Asked before the stores and looked at after them: the answer takes a trip to L2
+      const int gave_up = *((volatile int*)err_flag);
       float* Ct = C + (int64_t)z * ts.split_stride;
       epilogue_store_warp(sum, lane, m0 + sub * 32, n0 + half * 128, M, N, Ct, ldc, vecC, epi);
+      if (gave_up != 0) { ok = false; break; }
     }
   }
 
