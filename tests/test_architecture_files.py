@@ -11,7 +11,9 @@ import architectures as A
 import oracle as O
 from util import rng
 
-REF = "/root/reference"
+# the reference tree: named by PRAD_REFERENCE_TREE, else a directory "reference" beside the repository
+REF = os.environ.get("PRAD_REFERENCE_TREE") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 FILES = {
     "test/ParallelReverseAutoDiff.Test/FeedForward/Architecture/FeedForwardArchitecture.json":
         lambda: A.feedforward_architecture("GpuMatrixMultiplyOperation"),
