@@ -186,6 +186,30 @@ def short_k_products(eng, rows=200704):
         print(f"{rows} x {N} over k = {K}: {ms * 1e3:8.1f} us {nbytes / ms / 1e6:7.0f} GB/s (pieces read + output written)", flush=True)
 
 
+def small_products(eng, batch=4096):
+    """Strided batches of per-window attention products (49 x 49 over k = 32, 49 x 32 over k = 49): time per launch
+    and bytes moved (operands read once, output written once) against the copy bandwidth."""
+    f = np.float32
+    peak = _peak_gbs()
+    t = _Timer(eng)
+    r = np.random.default_rng(0)
+    for name, (M, K, N), ta, tb in (("S = Q K^T", (49, 32, 49), False, True), ("O = P V", (49, 49, 32), False, False),
+                                    ("dV = P^T dO", (49, 49, 32), True, False)):
+        a_shape = (batch, K, M) if ta else (batch, M, K)
+        b_shape = (batch, N, K) if tb else (batch, K, N)
+        a, b = eng.upload(r.standard_normal(a_shape, dtype=f)), eng.upload(r.standard_normal(b_shape, dtype=f))
+        c = eng.empty((batch, M, N), f)
+        for small in ("1", "0"):
+            eng.set_option("gemm_small", small)
+            ms = t(lambda: eng.gemm(a, b, c, transA=ta, transB=tb, M=M, N=N, K=K, lda=a_shape[2], ldb=b_shape[2], ldc=N,
+                                    batch=batch, strideA=M * K, strideB=K * N, strideC=M * N), iters=10, warm=3)
+            nbytes = 4.0 * batch * (M * K + K * N + M * N)
+            kern = "one CTA per product" if small == "1" else "64 x 64 tiles"
+            print(f"{name:12s} {kern:20s} {ms * 1e3:7.1f} us {nbytes / ms / 1e6:6.0f} GB/s {nbytes / ms / 1e6 / peak:5.2f} of measured copy peak",
+                  flush=True)
+        eng.set_option("gemm_small", "1")
+
+
 def f64_variants(eng, n=4096):
     """Double-precision GEMM variants at n^3 and the device's FP64 multiply-add rate (a register-resident
     chain of independent FMAs per thread, every SM full), the denominator for the FP64 kernels."""
@@ -215,6 +239,7 @@ def main():
     ap.add_argument("--packed", action="store_true")
     ap.add_argument("--f64", action="store_true")
     ap.add_argument("--short-k", action="store_true", help="packed products with k of 96 .. 384")
+    ap.add_argument("--small-products", action="store_true", help="strided batches of 49 x 49 x 32 products")
     ap.add_argument("--block-cols", type=int, default=0, help="--packed: block length of the by-columns forms (0, 128, 256)")
     ap.add_argument("--rows", type=int, default=None)
     ap.add_argument("--opt", action="append", default=[], metavar="KEY=VALUE", help="prad_set_option before running")
@@ -225,6 +250,8 @@ def main():
             eng.set_option(*kv.split("=", 1))
         if args.packed:
             packed_operands(eng, rows=args.rows or 16384, block_cols=args.block_cols)
+        elif args.small_products:
+            small_products(eng, batch=args.rows or 4096)
         elif args.short_k:
             short_k_products(eng, rows=args.rows or 200704)
         elif args.f64:
