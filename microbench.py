@@ -80,6 +80,7 @@ def hbm_kernels(eng, only=None, rows=65536, cols=4096):
         ("hadamard_backward", 5 * n * 4, lambda: eng.hadamard_backward(x, dy, out2, out=(out, out2.view(out2.shape)))),
         ("mse_backward", 3 * n * 4, lambda: eng.mse_backward(x, dy, grad=out)),
         ("bias_colsum", n * 4, lambda: eng.add_broadcast_backward(x, dbias=db)),
+        ("bias_colsum_96", lrows * 96 * 4, lambda: eng.add_broadcast_backward(Lx, dbias=db.view((1, 96)))),
         ("accumulate", 3 * n * 4, lambda: eng.accumulate(out, x)),
         ("segmented_sum_3", 4 * n * 4, lambda: eng.segmented_sum([x, dy, out2], out=out)),
         ("segmented_sum_2", 3 * n * 4, lambda: eng.segmented_sum([x, dy], out=out)),

@@ -194,56 +194,56 @@ __global__ void colsum_final_kernel(const double* __restrict__ partial, T* __res
 // every CTA adds the sums of its threads that share a group (in thread order) and writes one
 // partial per group, and one CTA per column group adds the partials in CTA order.  Fully
 // coalesced, deterministic.
-template <typename T>
+// CTA_SUM: the sums of the threads of a CTA that share a column group are added in shared memory (in thread order) and
+// the CTA writes one partial per group; otherwise (more than 256 groups: wide rows) every thread writes its own.
+template <typename T, bool CTA_SUM>
 __global__ void __launch_bounds__(256)
 colsum_flat_partial_kernel(const T* __restrict__ x, double* __restrict__ partial, int64_t nvec,
                            int64_t stride_threads, int vec_per_row) {
   constexpr int VEC = Vec16<T>::N;
   using V = typename Vec16<T>::type;
-  __shared__ double sm[256][VEC];
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (!CTA_SUM && t >= stride_threads) return;
+  if (CTA_SUM && t >= stride_threads) nvec = 0;      // the last CTA's surplus threads add nothing
   double acc[VEC];
 #pragma unroll
   for (int q = 0; q < VEC; ++q) acc[q] = 0.0;
-  if (t < stride_threads) {
-    const V* xv = reinterpret_cast<const V*>(x);
-    int64_t i = t;
-    for (; i + 3 * stride_threads < nvec; i += 4 * stride_threads) {   // four loads in flight
-      V v0 = __ldcs(xv + i), v1 = __ldcs(xv + i + stride_threads);
-      V v2 = __ldcs(xv + i + 2 * stride_threads), v3 = __ldcs(xv + i + 3 * stride_threads);
+  const V* xv = reinterpret_cast<const V*>(x);
+  int64_t i = t;
+  for (; i + 3 * stride_threads < nvec; i += 4 * stride_threads) {   // four loads in flight
+    V v0 = __ldcs(xv + i), v1 = __ldcs(xv + i + stride_threads);
+    V v2 = __ldcs(xv + i + 2 * stride_threads), v3 = __ldcs(xv + i + 3 * stride_threads);
 #pragma unroll
-      for (int q = 0; q < VEC; ++q) {
-        acc[q] += (double)reinterpret_cast<const T*>(&v0)[q];
-        acc[q] += (double)reinterpret_cast<const T*>(&v1)[q];
-        acc[q] += (double)reinterpret_cast<const T*>(&v2)[q];
-        acc[q] += (double)reinterpret_cast<const T*>(&v3)[q];
-      }
-    }
-    for (; i < nvec; i += stride_threads) {
-      V v = __ldcs(xv + i);
-#pragma unroll
-      for (int q = 0; q < VEC; ++q) acc[q] += (double)reinterpret_cast<const T*>(&v)[q];
+    for (int q = 0; q < VEC; ++q) {
+      acc[q] += (double)reinterpret_cast<const T*>(&v0)[q];
+      acc[q] += (double)reinterpret_cast<const T*>(&v1)[q];
+      acc[q] += (double)reinterpret_cast<const T*>(&v2)[q];
+      acc[q] += (double)reinterpret_cast<const T*>(&v3)[q];
     }
   }
-  if (vec_per_row > 256) {          // fewer than one thread per column group in a CTA: every thread writes its own sums
-    if (t < stride_threads)
+  for (; i < nvec; i += stride_threads) {
+    V v = __ldcs(xv + i);
 #pragma unroll
-      for (int q = 0; q < VEC; ++q) partial[t * VEC + q] = acc[q];
-    return;
+    for (int q = 0; q < VEC; ++q) acc[q] += (double)reinterpret_cast<const T*>(&v)[q];
   }
-  // the threads of this CTA that share a column group (every vec_per_row-th) are added here, in thread order
+  if constexpr (!CTA_SUM) {
 #pragma unroll
-  for (int q = 0; q < VEC; ++q) sm[threadIdx.x][q] = acc[q];
-  __syncthreads();
-  if ((int)threadIdx.x < vec_per_row) {
-    const int group = (int)(t % vec_per_row);
+    for (int q = 0; q < VEC; ++q) partial[t * VEC + q] = acc[q];
+  } else {
+    __shared__ double sm[256][VEC];
 #pragma unroll
-    for (int q = 0; q < VEC; ++q) acc[q] = 0.0;
-    for (int j = threadIdx.x; j < 256; j += vec_per_row)
+    for (int q = 0; q < VEC; ++q) sm[threadIdx.x][q] = acc[q];
+    __syncthreads();
+    if ((int)threadIdx.x < vec_per_row) {
+      const int group = (int)(t % vec_per_row);
 #pragma unroll
-      for (int q = 0; q < VEC; ++q) acc[q] += sm[j][q];
+      for (int q = 0; q < VEC; ++q) acc[q] = 0.0;
+      for (int j = threadIdx.x; j < 256; j += vec_per_row)
 #pragma unroll
-    for (int q = 0; q < VEC; ++q) partial[((int64_t)blockIdx.x * vec_per_row + group) * VEC + q] = acc[q];
+        for (int q = 0; q < VEC; ++q) acc[q] += sm[j][q];
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) partial[((int64_t)blockIdx.x * vec_per_row + group) * VEC + q] = acc[q];
+    }
   }
 }
 
@@ -291,8 +291,12 @@ static prad_status add_broadcast_backward_t(prad_ctx* ctx, const void* dy, void*
       prad_status s = ensure_workspace(ctx, (size_t)threads * VEC * sizeof(double));
       if (s) return s;
       const int64_t ctas = ceil_div(threads, 256);
-      colsum_flat_partial_kernel<T><<<(unsigned)ctas, 256, 0, ctx->stream>>>((const T*)dy, (double*)ctx->ws, nvec, threads,
-                                                                           vec_per_row);
+      if (vec_per_row <= 256)
+        colsum_flat_partial_kernel<T, true><<<(unsigned)ctas, 256, 0, ctx->stream>>>((const T*)dy, (double*)ctx->ws, nvec,
+                                                                                   threads, vec_per_row);
+      else
+        colsum_flat_partial_kernel<T, false><<<(unsigned)ctas, 256, 0, ctx->stream>>>((const T*)dy, (double*)ctx->ws, nvec,
+                                                                                    threads, vec_per_row);
       PRAD_LAUNCHED(ctx);
       // entries the final pass adds per column group: one per CTA, or one per thread for very wide rows
       const int64_t entries = vec_per_row <= 256 ? ctas * vec_per_row : threads;
