@@ -102,7 +102,7 @@ const char* prad_version(void);
  *  "tc_prefetch" = n (0..64, default 0): the product of packed operands asks L2 for the row operand's tile n k-blocks
  *    of 32 ahead of its load (measured: no gain on B200, the loads are not what the tensor pipe waits for);
  *  "tc_pair" = "1" (default) | "2" | "0": products of packed operands on pairs of CTAs (tcgen05 cta_group::2: two
- *    neighbouring SMs share a 256 x 256 tile, each holding half of the column operand) when k is at least 1024 ("1"),
+ *    neighbouring SMs share a 256 x 256 tile, each holding half of the column operand) when k or N is at least 1024 ("1"),
  *    whatever k is ("2"), or always on one CTA per 128 x 256 tile ("0");
  *  "gemm_small" = "1" (default) | "0": strided batches of at least one product per SM whose outputs are at most
  *    64 x 64 (per-window attention products) run on one CTA per product sized to the output, instead of 64 x 64 tiles;

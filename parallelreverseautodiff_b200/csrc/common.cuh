@@ -49,7 +49,7 @@ struct prad_ctx {
   bool tc_split_k = true;  // option "tc_split_k": cut k across CTAs when the tile count wastes SMs
   int tc_prefetch = 0;     // option "tc_prefetch": k-blocks of 32 by which the packed FP16 product prefetches its row operand into L2
   int gemm_small = 1;      // option "gemm_small": batches of products of at most 64 x 64 outputs on one CTA per product
-  int tc_pair = 1;         // option "tc_pair": packed FP16 products on CTA pairs (tcgen05 cta_group::2, 256-row tiles): 0 never, 1 for k >= 1024, 2 always
+  int tc_pair = 1;         // option "tc_pair": packed FP16 products on CTA pairs (tcgen05 cta_group::2, 256-row tiles): 0 never, 1 for k or N >= 1024, 2 always
   int tc_panel_n = 0;      // option "tc_panel_n": column tiles per panel of the persistent GEMM's tile walk (0 = automatic)
   int tc_chunk_k = 256;    // option "tc_chunk_k": k per accumulation chunk of the persistent GEMM
   bool tc_chunk_k_set = false;   // the option was given (packed FP16 operands default to 128-long blocks otherwise)

@@ -1740,10 +1740,12 @@ static prad_status launch_fp16x3(prad_ctx* ctx, const PackedForm& a, const Packe
   const int total_kb = (int)(kp / p1::BK), chunk_kb = a.chunk / p1::BK;
   // CTA pairs (256-row tiles over two SMs) when the output has at least two tile rows and the option allows
   const int tiles_m2 = (int)ceil_div(M, p2::BM2);
-  // (not for k below 1024: a pair halves the shared-memory traffic of the column operand, which only long k loops feel,
-  // while its tile transitions cost more -- 200704 x 96 outputs over k = 96 .. 384 take 52 .. 90 us on single CTAs
-  // and 61 .. 105 us on pairs)
-  const bool pair = ctx->tc_pair != 0 && M > BM && (kp >= 1024 || ctx->tc_pair == 2) && ctx->sm_count - ctx->tc_reserve_sms >= 2;
+  // (not for k below 1024 with fewer than 1024 columns: a pair halves the shared-memory traffic of the column operand,
+  // which long k loops and wide outputs feel, while its tile transitions cost more -- 200704 x 96 outputs over k = 96 ..
+  // 384 take 52 .. 90 us on single CTAs and 61 .. 105 us on pairs; 65536 x 4096 over k = 512 takes 733 and 721 us,
+  // 65536 x 1024 over k = 512 about 200 us either way)
+  const bool pair = ctx->tc_pair != 0 && M > BM && (kp >= 1024 || N >= 1024 || ctx->tc_pair == 2) &&
+                    ctx->sm_count - ctx->tc_reserve_sms >= 2;
   CUtensorMap mb_half;
   if (pair) {
     PRAD_REQUIRE(make_map(&mb_half, b.h, N, (int)(2 * kp), b.pitch, BN / 2, 2 * p1::BK, 2, true), PRAD_ERR_CUDA,
