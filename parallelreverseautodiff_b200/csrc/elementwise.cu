@@ -158,7 +158,8 @@ __global__ void add_broadcast_kernel(const T* x, const T* __restrict__ bias, T* 
 template <typename T>
 __global__ void __launch_bounds__(256)
 colsum_partial_kernel(const T* __restrict__ x, double* __restrict__ partial, int64_t rows,
-                      int cols, int rows_per_band) {
+                      int cols, int rows_per_band, T* __restrict__ direct_out, int accumulate) {
+  // direct_out: there is one band only (a short matrix) and the sums go straight to the result: one launch
   __shared__ double sm[8][33];
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int col = blockIdx.x * 32 + lane;
@@ -174,7 +175,14 @@ colsum_partial_kernel(const T* __restrict__ x, double* __restrict__ partial, int
     double s = 0.0;
 #pragma unroll
     for (int k = 0; k < 8; ++k) s += sm[k][lane];
-    if (col < cols) partial[(int64_t)blockIdx.y * cols + col] = s;
+    if (col < cols) {
+      if (direct_out) {
+        const T v = (T)s;
+        direct_out[col] = accumulate ? add_rn(direct_out[col], v) : v;
+      } else {
+        partial[(int64_t)blockIdx.y * cols + col] = s;
+      }
+    }
   }
 }
 template <typename T>
@@ -312,12 +320,19 @@ static prad_status add_broadcast_backward_t(prad_ctx* ctx, const void* dy, void*
   int bands = (int)(want_bands < max_bands ? want_bands : max_bands);
   if (bands < 1) bands = 1;
   if (bands > 65535) bands = 65535;
+  if (rows <= 512) bands = 1;      // a short matrix (the bias gradient of a small batch): one launch, no second pass
   int rows_per_band = (int)ceil_div(rows, bands);
   bands = (int)ceil_div(rows, rows_per_band);
+  if (bands == 1) {
+    colsum_partial_kernel<T><<<dim3(strips, 1), 256, 0, ctx->stream>>>((const T*)dy, nullptr, rows, cols, rows_per_band,
+                                                                      (T*)dbias, accumulate);
+    PRAD_LAUNCHED(ctx);
+    return PRAD_OK;
+  }
   prad_status s = ensure_workspace(ctx, (size_t)bands * cols * sizeof(double));
   if (s) return s;
   colsum_partial_kernel<T><<<dim3(strips, bands), 256, 0, ctx->stream>>>(
-      (const T*)dy, (double*)ctx->ws, rows, cols, rows_per_band);
+      (const T*)dy, (double*)ctx->ws, rows, cols, rows_per_band, nullptr, 0);
   PRAD_LAUNCHED(ctx);
   colsum_final_kernel<T><<<(unsigned)ceil_div(cols, 128), 128, 0, ctx->stream>>>(
       (const double*)ctx->ws, (T*)dbias, cols, bands, accumulate);
@@ -671,7 +686,7 @@ static prad_status colsum_static_t(cudaStream_t st, double* scratch, int sms, co
   // every partial that the second kernel reads is written by the first one in this call, so
   // nothing left in the array by an earlier call can leak into the result
   colsum_partial_kernel<T><<<dim3(strips, (unsigned)bands), 256, 0, st>>>(
-      (const T*)dy, scratch, rows, cols, rows_per_band);
+      (const T*)dy, scratch, rows, cols, rows_per_band, nullptr, 0);
   cudaError_t e = cudaPeekAtLastError();
   if (e == cudaSuccess) {
     colsum_final_kernel<T><<<(unsigned)ceil_div(cols, 128), 128, 0, st>>>(
