@@ -1524,22 +1524,75 @@ split_transpose_kernel(const float* __restrict__ src, int64_t src_ld, float* __r
   }
 }
 
-// C = alpha * (P_0 + P_1 + ... ) + beta * C, slices added in order; P_s are dense M x N.
+// C = alpha * (P_0 + P_1 + ... ) + beta * C, slices added in order; P_s are dense M x N.  V = 4: four consecutive
+// elements per thread (N, ldc and mn multiples of four, 16-byte aligned pointers).  The loads of eight slices are issued
+// before the first of them is added: with 64 slices of a small output (96 x 288 over k = 200 704) the pass was a chain of
+// 64 round trips to L2 per thread.
+template <int V>
 __global__ void __launch_bounds__(256)
 splitk_combine_kernel(const float* __restrict__ part, int splits, int64_t mn, int M, int N,
                       float* __restrict__ C, int64_t ldc, float alpha, float beta) {
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < mn; i += stride) {
-    float acc = part[i];
-    for (int s = 1; s < splits; ++s) acc = __fadd_rn(acc, part[(int64_t)s * mn + i]);
+  constexpr int U = 8;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x * V;
+  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * V; i < mn; i += stride) {
+    float acc[V];
+    auto fetch = [&](int sl, float (&v)[V]) {
+      if (V == 4) {
+        const float4 t = *reinterpret_cast<const float4*>(part + (int64_t)sl * mn + i);
+        v[0] = t.x; v[1 % V] = t.y; v[2 % V] = t.z; v[3 % V] = t.w;
+      } else {
+        v[0] = part[(int64_t)sl * mn + i];
+      }
+    };
+    fetch(0, acc);
+    int sl = 1;
+    for (; sl + U <= splits; sl += U) {
+      float v[U][V];
+#pragma unroll
+      for (int u = 0; u < U; ++u) fetch(sl + u, v[u]);
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int q = 0; q < V; ++q) acc[q] = __fadd_rn(acc[q], v[u][q]);
+    }
+    for (; sl < splits; ++sl) {
+      float v[V];
+      fetch(sl, v);
+#pragma unroll
+      for (int q = 0; q < V; ++q) acc[q] = __fadd_rn(acc[q], v[q]);
+    }
     const int64_t off = (i / N) * ldc + (i % N);
-    float v = __fmul_rn(alpha, acc);
-    if (beta != 0.f) v = (beta == 1.f) ? __fadd_rn(C[off], v) : fmaf(beta, C[off], v);
-    C[off] = v;
+    float o[V];
+#pragma unroll
+    for (int q = 0; q < V; ++q) o[q] = __fmul_rn(alpha, acc[q]);
+    if (beta != 0.f) {
+      float old[V];
+      if (V == 4) {
+        const float4 t = *reinterpret_cast<const float4*>(C + off);
+        old[0] = t.x; old[1 % V] = t.y; old[2 % V] = t.z; old[3 % V] = t.w;
+      } else {
+        old[0] = C[off];
+      }
+#pragma unroll
+      for (int q = 0; q < V; ++q) o[q] = (beta == 1.f) ? __fadd_rn(old[q], o[q]) : fmaf(beta, old[q], o[q]);
+    }
+    if (V == 4) *reinterpret_cast<float4*>(C + off) = make_float4(o[0], o[1 % V], o[2 % V], o[3 % V]);
+    else C[off] = o[0];
   }
 }
 
 // ---- host side --------------------------------------------------------------------------
+static void launch_splitk_combine(prad_ctx* ctx, const float* part, int splits, int64_t mn, int M, int N, float* C,
+                                  int64_t ldc, float alpha, float beta) {
+  const bool vec = N % 4 == 0 && ldc % 4 == 0 && (((uintptr_t)C | (uintptr_t)part) & 15) == 0;
+  if (vec) {
+    const int cg = stream_grid(ctx, mn / 4, 256, 8);
+    splitk_combine_kernel<4><<<cg, 256, 0, ctx->stream>>>(part, splits, mn, M, N, C, ldc, alpha, beta);
+  } else {
+    const int cg = stream_grid(ctx, mn, 256, 8);
+    splitk_combine_kernel<1><<<cg, 256, 0, ctx->stream>>>(part, splits, mn, M, N, C, ldc, alpha, beta);
+  }
+}
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -1695,8 +1748,7 @@ static prad_status launch_tf32x3(prad_ctx* ctx, const SplitOperand& a, const Spl
     splits = (int)ceil_div(total_kb, kbps);   // no empty slice
     launch(splits, kbps, mn, part, N, true, raw);
     PRAD_LAUNCHED(ctx);
-    const int cg = stream_grid(ctx, ceil_div(mn, 4), 256, 8);
-    splitk_combine_kernel<<<cg, 256, 0, ctx->stream>>>(part, splits, mn, M, N, C, ldc, epi.alpha, epi.beta);
+    launch_splitk_combine(ctx, part, splits, mn, M, N, C, ldc, epi.alpha, epi.beta);
     PRAD_LAUNCHED(ctx);
   }
   ctx->tc_pending_check = true;
@@ -1802,8 +1854,7 @@ static prad_status launch_fp16x3(prad_ctx* ctx, const PackedForm& a, const Packe
     splits = (int)ceil_div(total_kb, kbps);   // no empty slice
     launch(splits, kbps, mn, part, N, true, raw);
     PRAD_LAUNCHED(ctx);
-    const int cg = stream_grid(ctx, ceil_div(mn, 4), 256, 8);
-    splitk_combine_kernel<<<cg, 256, 0, ctx->stream>>>(part, splits, mn, M, N, C, ldc, alpha, beta);
+    launch_splitk_combine(ctx, part, splits, mn, M, N, C, ldc, alpha, beta);
     PRAD_LAUNCHED(ctx);
   }
   ctx->tc_pending_check = true;
