@@ -268,12 +268,12 @@ def measured_peaks():
 
 def gemm_traffic_bytes(rows, width, gemm):
     """DRAM bytes of one backward GEMM launch of the default kernel (CTA pairs): one ncu capture of a
-    16384-row launch on packed operands (0.868 GB read + 0.255 GB written; algorithmic 0.604 GB --
+    16384-row launch on packed operands (0.814 GB read + 0.250 GB written; algorithmic 0.604 GB --
     the row operand streams once per column panel), scaled linearly in the rows: the traffic is
     dominated by the row-proportional operand and result.  None for other kernels or widths."""
     if gemm != "auto" or width != 4096:
         return None
-    return 1.1225e9 * rows / 16384.0
+    return 1.0635e9 * rows / 16384.0
 
 
 def run_native(args, rank, world, local_rank):
@@ -427,7 +427,7 @@ def run_native(args, rank, world, local_rank):
                          if achieved_tflops and args.gemm in ("auto", "fp16x3") else None,
                          "traffic": gemm_traffic_bytes(rows, args.width, args.gemm),
                          "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one "
-                                           "16384 x 4096 x 4096 launch of the default kernel (CTA pairs) on packed operands (1.1225 GB), scaled by rows",
+                                           "16384 x 4096 x 4096 launch of the default kernel (CTA pairs) on packed operands (1.0635 GB), scaled by rows",
                          "kernel": "backward GEMMs (dW = A^T dZ, dA = dZ W^T)",
                          "peak_source": peaks["source"] + " dense bf16, sustained",
                          "launches_timed": n_gemm},
