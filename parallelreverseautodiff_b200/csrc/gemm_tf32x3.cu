@@ -1746,7 +1746,8 @@ static prad_status launch_tf32x3(prad_ctx* ctx, const SplitOperand& a, const Spl
     // k-blocks per slice rounded up to whole accumulation chunks, so slices start on chunk boundaries
     int kbps = (int)ceil_div(ceil_div(total_kb, splits), CFG::CHUNK_KB) * CFG::CHUNK_KB;
     splits = (int)ceil_div(total_kb, kbps);   // no empty slice
-    launch(splits, kbps, mn, part, N, true, raw);
+    // (the slices are dense M x N blocks: their rows are whole 16-byte vectors only when N is a multiple of four)
+    launch(splits, kbps, mn, part, N, N % 4 == 0, raw);
     PRAD_LAUNCHED(ctx);
     launch_splitk_combine(ctx, part, splits, mn, M, N, C, ldc, epi.alpha, epi.beta);
     PRAD_LAUNCHED(ctx);
@@ -1852,7 +1853,8 @@ static prad_status launch_fp16x3(prad_ctx* ctx, const PackedForm& a, const Packe
     raw.beta = 0.f;
     int kbps = (int)ceil_div(ceil_div(total_kb, splits), chunk_kb) * chunk_kb;
     splits = (int)ceil_div(total_kb, kbps);   // no empty slice
-    launch(splits, kbps, mn, part, N, true, raw);
+    // (the slices are dense M x N blocks: their rows are whole 16-byte vectors only when N is a multiple of four)
+    launch(splits, kbps, mn, part, N, N % 4 == 0, raw);
     PRAD_LAUNCHED(ctx);
     launch_splitk_combine(ctx, part, splits, mn, M, N, C, ldc, alpha, beta);
     PRAD_LAUNCHED(ctx);

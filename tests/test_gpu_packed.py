@@ -94,6 +94,32 @@ def test_products_of_packed_operands(tile_engine, shape, blocks):
     assert_close(out2.numpy(), want, _absprod(X, Y) + np.abs(base) + 1.0, f"packed alpha beta bias {shape} {blocks}")
 
 
+@pytest.mark.parametrize("shape", [(256, 4096, 130), (256, 4096, 128), (96, 16384, 288)])
+def test_k_slices_and_their_sum_pass(engine, shape):
+    """Few output tiles over a long k: the product runs as k slices into scratch and an ordered sum pass (four
+    columns per thread when the output's rows are whole float4, one otherwise), with alpha and beta applied once."""
+    m, k, n = shape
+    r = rng(m + k + n)
+    X = r.standard_normal((m, k)).astype(f)
+    Y = (r.standard_normal((k, n)) * 0.1).astype(f)
+    base = r.standard_normal((m, n)).astype(f)
+    PX = engine.packed(m, k, E.PACK_ROWS).pack(engine.upload(X))
+    PY = engine.packed(k, n, E.PACK_COLS, 0, PX.blocks()[0]).pack(engine.upload(Y))
+    n0 = engine.launch_count()
+    out = engine.upload(base)
+    engine.gemm_packed(PX, E.PACK_ROWS, PY, E.PACK_COLS, out, alpha=0.5, beta=2.0)
+    assert engine.launch_count() - n0 == 2          # the product and the sum pass
+    want = (0.5 * O.matmul_forward(X, Y).astype(np.float64) + 2.0 * base).astype(f)
+    assert_close(out.numpy(), want, _absprod(X, Y) + np.abs(base), f"sliced product {shape}")
+    engine.set_option("tc_split_k", "off")
+    try:
+        whole = engine.upload(base)
+        engine.gemm_packed(PX, E.PACK_ROWS, PY, E.PACK_COLS, whole, alpha=0.5, beta=2.0)
+    finally:
+        engine.set_option("tc_split_k", "on")
+    assert_close(out.numpy(), whole.numpy(), _absprod(X, Y) + np.abs(base), f"sliced against whole {shape}")
+
+
 @pytest.mark.parametrize("act", [E.ACT_GELU, E.ACT_LEAKY_RELU, E.ACT_TANH, E.ACT_SIGMOID, E.ACT_NONE])
 def test_activation_written_in_packed_form(engine, act):
     """y = act(x) and dx = dy * act'(saved) packed on the fly: the FP32 copies are bit-identical to the
