@@ -92,6 +92,11 @@ def test_products_of_packed_operands(tile_engine, shape, blocks):
     engine.gemm_packed(PX, E.PACK_ROWS, PY, E.PACK_COLS, out2, alpha=0.5, beta=2.0, bias=engine.upload(bias))
     want = (0.5 * O.matmul_forward(X, Y).astype(np.float64) + 2.0 * base + bias).astype(f)
     assert_close(out2.numpy(), want, _absprod(X, Y) + np.abs(base) + 1.0, f"packed alpha beta bias {shape} {blocks}")
+    # a bias row alone (the forward product of a layer)
+    out3 = engine.empty((m, n), f)
+    engine.gemm_packed(PX, E.PACK_ROWS, PY, E.PACK_COLS, out3, alpha=0.25, bias=engine.upload(bias))
+    want3 = (0.25 * O.matmul_forward(X, Y).astype(np.float64) + bias).astype(f)
+    assert_close(out3.numpy(), want3, _absprod(X, Y) + 1.0, f"packed alpha bias {shape} {blocks}")
 
 
 @pytest.mark.parametrize("shape", [(256, 4096, 130), (256, 4096, 128), (96, 16384, 288)])
